@@ -1,0 +1,205 @@
+"""exactinfer forward pass on B200 (sm_100a): Python host side over the C ABI of libelb.so.
+
+`Weight` and the free functions mirror the reference's operator interface (src/ops.h:11-29: matvec, get_row, rmsnorm);
+`Backend` mirrors el::Backend (src/model.h:42-51: cfg, n_ctx, name, eval). All arithmetic runs in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi, synth
+from .capi import Config, ElbError, check, lib
+
+__all__ = ["Weight", "Backend", "cuda_available", "matvec", "get_row", "rmsnorm", "split_limbs", "synth", "Config",
+           "ElbError"]
+
+
+def cuda_available():
+    """el::cuda_available (src/model.h:56): (ok, why)"""
+    n = lib().elb_device_count()
+    return (True, "") if n > 0 else (False, lib().elb_last_error().decode(errors="replace"))
+
+
+class DeviceBuffer:
+    def __init__(self, nbytes: int, device: int = 0):
+        p = C.c_void_p()
+        check(lib().elb_malloc(device, nbytes, C.byref(p)))
+        self.ptr, self.nbytes = p, nbytes
+
+    @classmethod
+    def from_array(cls, a: np.ndarray, device: int = 0):
+        a = np.ascontiguousarray(a)
+        b = cls(a.nbytes, device)
+        check(lib().elb_memcpy_h2d(b.ptr, a.ctypes.data_as(C.c_void_p), a.nbytes))
+        return b
+
+    def to_array(self, dtype, shape):
+        out = np.empty(shape, dtype=dtype)
+        check(lib().elb_memcpy_d2h(out.ctypes.data_as(C.c_void_p), self.ptr, out.nbytes))
+        return out
+
+    def free(self):
+        if self.ptr:
+            lib().elb_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        self.free()
+
+
+class Weight:
+    """One weight matrix in a ggml block format on the device (el::Tensor + upload_group of the reference)."""
+
+    def __init__(self, ggml_type: int, rows: int, n: int, data: np.ndarray, planes: bool = False, pair: bool = False,
+                 device: int = 0):
+        data = np.ascontiguousarray(data, dtype=np.uint8)
+        h = C.c_void_p()
+        flags = (capi.W_PLANES if planes else 0) | (capi.W_PAIR if pair else 0)
+        check(lib().elb_weight_create(device, ggml_type, rows, n, data.ctypes.data_as(C.c_void_p), data.nbytes, flags,
+                                      C.byref(h)))
+        self._h, self.type, self.device = h, ggml_type, device
+        self.rows, self.n = lib().elb_weight_rows(h), lib().elb_weight_cols(h)
+
+    @property
+    def device_bytes(self):
+        return lib().elb_weight_device_bytes(self._h)
+
+    def get_rows(self, row0: int, count: int = 1) -> np.ndarray:
+        out = np.empty((count, self.n), dtype=np.float32)
+        check(lib().elb_get_rows(self._h, row0, count, capi.fptr(out)))
+        return out
+
+    def matvec(self, x: np.ndarray, nl: int = 4) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.size != self.n:
+            raise ValueError("matvec: x has the wrong length")
+        y = np.empty(self.rows, dtype=np.float32)
+        check(lib().elb_matvec(self._h, capi.fptr(x), capi.fptr(y), nl))
+        return y
+
+    def matmul(self, x: np.ndarray, nl: int = 4) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        b = x.shape[0]
+        y = np.empty((b, self.rows), dtype=np.float32)
+        check(lib().elb_matmul(self._h, capi.fptr(x), b, capi.fptr(y), nl))
+        return y
+
+    def limb_sums(self, x: np.ndarray, nl: int = 4):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        sub = 16 if self.type == synth.Q6_K else 32
+        blk = 32 if self.type == synth.Q8_0 else 256
+        P = np.empty((self.rows, self.n // sub, nl), dtype=np.int32)
+        I = np.empty((self.rows, self.n // blk, nl), dtype=np.int32)
+        J = np.empty_like(I)
+        ip = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+        check(lib().elb_limb_sums(self._h, capi.fptr(x), nl, ip(P), ip(I), ip(J)))
+        return P, I, J
+
+    def close(self):
+        if getattr(self, '_h', None):
+            lib().elb_weight_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+
+def matvec(w: Weight, x: np.ndarray, nl: int = 4) -> np.ndarray:
+    """el::matvec (src/ops.h:23)"""
+    return w.matvec(x, nl)
+
+
+def get_row(w: Weight, row: int) -> np.ndarray:
+    """el::get_row (src/ops.h:20)"""
+    return w.get_rows(row, 1)[0]
+
+
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """el::rmsnorm (src/ops.h:26) over the last axis"""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n = x.shape[-1]
+    out = np.empty_like(x)
+    check(lib().elb_rmsnorm(capi.fptr(out), capi.fptr(x), capi.fptr(w), n, eps, x.size // n))
+    return out
+
+
+def split_limbs(x: np.ndarray, nl: int, device: int = 0):
+    """k_split8 of the reference: returns (limbs[nl][b][n] int8, inv_scale[b])"""
+    x = np.ascontiguousarray(np.atleast_2d(x), dtype=np.float32)
+    b, n = x.shape
+    limbs = np.empty((nl, b, n), dtype=np.int8)
+    inv = np.empty(b, dtype=np.float32)
+    check(lib().elb_split_limbs(device, capi.fptr(x), b, n, nl, limbs.ctypes.data_as(C.POINTER(C.c_int8)), capi.fptr(inv)))
+    return limbs, inv
+
+
+class Backend:
+    """el::Backend (src/model.h:42-51) on the CUDA library: cfg(), n_ctx(), name(), eval(tokens, pos0) -> logits."""
+
+    def __init__(self, spec: "synth.Spec", tensors, n_ctx: int, device: int = 0, max_batch: int = 0):
+        self.spec = spec
+        self._cfg = Config(spec.n_layer, spec.n_embd, spec.n_ff, spec.n_head, spec.n_head_kv, spec.head_dim, spec.n_vocab,
+                           spec.head_dim, spec.rope_base, spec.eps, max_batch)
+        self._n_ctx = n_ctx
+        h = C.c_void_p()
+        check(lib().elb_model_create(C.byref(self._cfg), n_ctx, device, C.byref(h)))
+        self._h = h
+        try:
+            keep = []
+            for role, layer, t, rows, n, data in tensors:
+                data = np.ascontiguousarray(data, dtype=np.uint8)
+                keep.append(data)  # bytes must stay valid until finalize
+                check(lib().elb_model_set_tensor(h, synth.ROLE_ID[role], max(layer, 0), t, rows, n,
+                                                 data.ctypes.data_as(C.c_void_p), data.nbytes))
+            check(lib().elb_model_finalize(h))
+        except Exception:
+            self.close()
+            raise
+        self._logits_host = None
+
+    def cfg(self):
+        return self._cfg
+
+    def n_ctx(self):
+        return self._n_ctx
+
+    def name(self):
+        return "cuda-b200"
+
+    def eval(self, tokens, pos0: int, want_logits: bool = True, out: np.ndarray | None = None):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = None
+        if want_logits:
+            logits = out if out is not None else np.empty(self.spec.n_vocab, dtype=np.float32)
+        check(lib().elb_model_eval(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), tokens.size, pos0,
+                                   logits.ctypes.data_as(C.c_void_p) if want_logits else None))
+        return logits
+
+    def last_eval_stats(self):
+        ms, n = C.c_float(), C.c_int64()
+        check(lib().elb_model_last_eval_stats(self._h, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def hidden(self):
+        out = np.empty(self.spec.n_embd, dtype=np.float32)
+        check(lib().elb_model_hidden(self._h, capi.fptr(out)))
+        return out
+
+    @property
+    def weight_bytes(self):
+        return lib().elb_model_weight_bytes(self._h)
+
+    @property
+    def kv_bytes_per_token(self):
+        return lib().elb_model_kv_bytes_per_token(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().elb_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()

@@ -1,0 +1,378 @@
+// Attention and the small per-head kernels around it, fp32 throughout (the KV cache stays fp32, as in the reference).
+//
+//   k_attn_decode   one token: per-head q/k RMSNorm + RoPE + KV store fused in front of a split-K flash decode; all
+//                   q heads of a KV group share one pass over K/V; splits meet in a scratch buffer summed by the
+//                   last CTA to arrive, in split order (deterministic).
+//   k_qkv_post      prompt chunk: per-head q/k RMSNorm + RoPE in place, K/V rows stored to the cache.
+//   k_attn_prefill  prompt chunk: causal tiled attention, 32 queries of one head per CTA, online softmax.
+// Semantics follow CpuModel::forward of the reference (src/model.cpp:176-214): scale = 1/sqrt(float(D)), scores
+// accumulated in dimension order without FMA contraction, max-subtracted softmax.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace elb {
+
+constexpr int D = 128;  // head_dim (checked at model creation)
+
+// RMSNorm over one 128-wide head followed by NEOX RoPE (rmsnorm + rope, src/ops.cpp:155-160, src/model.cpp:23-32).
+// One warp per head; lane owns elements lane, lane+32, lane+64, lane+96. Result goes to dst (shared or global).
+__device__ __forceinline__ void head_norm_rope(const float* src, const float* w, const float2* cs, int rope_dim,
+                                               float eps, float* dst, int lane) {
+    float v[4];
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[j] = src[lane + 32 * j];
+        ss += double(v[j]) * v[j];
+    }
+    ss = warp_sum(ss);
+    const float inv = float(1.0 / sqrt(ss / D + double(eps)));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], inv), w[lane + 32 * j]);
+    if (rope_dim == D) {  // pairs (i, i+64): both halves of a pair live in this lane
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float2 c = cs[lane + 32 * j];
+            const float a = v[j], b = v[j + 2];
+            v[j] = __fsub_rn(__fmul_rn(a, c.x), __fmul_rn(b, c.y));
+            v[j + 2] = __fadd_rn(__fmul_rn(a, c.y), __fmul_rn(b, c.x));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = v[j];
+    } else {  // partial rotary: pairs (i, i + rope_dim/2), the rest passes through
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = v[j];
+        __syncwarp();
+        const int half = rope_dim / 2;
+        for (int i = lane; i < half; i += 32) {
+            const float2 c = cs[i];
+            const float a = dst[i], b = dst[i + half];
+            dst[i] = __fsub_rn(__fmul_rn(a, c.x), __fmul_rn(b, c.y));
+            dst[i + half] = __fadd_rn(__fmul_rn(a, c.y), __fmul_rn(b, c.x));
+        }
+    }
+    __syncwarp();
+}
+
+// ---------------------------------------------------------------- decode
+
+constexpr int AD_THREADS = 256, AD_KT = 32, AD_MAXG = 8, AD_LDK = D + 1;
+
+struct AttnDecodeParams {
+    const float* qkv;  // [QD + 2 KD] of this token, q and k not yet normalised
+    const float *q_norm, *k_norm;
+    const float2* rope;  // [n_ctx][rope_dim/2] (cos, sin)
+    const int* pos;      // device scalar
+    float *kc, *vc;      // this layer's cache [n_ctx][KD]
+    float* att;          // [QD]
+    float* part;         // [HKV][nsplit][group][D + 2]
+    unsigned* counters;  // [HKV]
+    int H, HKV, rope_dim, nsplit;
+    float eps, scale;
+};
+
+__global__ void __launch_bounds__(AD_THREADS) k_attn_decode(const AttnDecodeParams p) {
+    __shared__ float qs[AD_MAXG][D];
+    __shared__ float knew[D], vnew[D];
+    __shared__ float Ks[AD_KT][AD_LDK];
+    __shared__ float Vs[AD_KT][D];
+    __shared__ float Ps[AD_MAXG][AD_KT];
+    __shared__ float corr_s[AD_MAXG], m_s[AD_MAXG], l_s[AD_MAXG];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x, split = blockIdx.y, group = p.H / p.HKV, QD = p.H * D, KD = p.HKV * D;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pos = *p.pos, T = pos + 1;
+    const float2* cs = p.rope + size_t(pos) * (p.rope_dim / 2);
+
+    for (int h = warp; h < group + 1; h += AD_THREADS / 32) {
+        if (h < group) head_norm_rope(p.qkv + (kvh * group + h) * D, p.q_norm, cs, p.rope_dim, p.eps, qs[h], lane);
+        else head_norm_rope(p.qkv + QD + kvh * D, p.k_norm, cs, p.rope_dim, p.eps, knew, lane);
+    }
+    if (tid < D) vnew[tid] = p.qkv[QD + KD + kvh * D + tid];
+    __syncthreads();
+    if (split == 0 && tid < D) {  // KV append (src/model.cpp:186-189): only row `pos` is written
+        p.kc[size_t(pos) * KD + kvh * D + tid] = knew[tid];
+        p.vc[size_t(pos) * KD + kvh * D + tid] = vnew[tid];
+    }
+    if (tid < AD_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+
+    // this split's key range, in whole tiles
+    const int tiles = (T + AD_KT - 1) / AD_KT, per = (tiles + p.nsplit - 1) / p.nsplit;
+    const int t_begin = min(T, split * per * AD_KT), t_end = min(T, (split + 1) * per * AD_KT);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // outputs (head tid/128 + 2i, dim tid%128)
+    const int od = tid & (D - 1), oh = tid >> 7;
+
+    for (int t0 = t_begin; t0 < t_end; t0 += AD_KT) {
+        const int nk = min(AD_KT, t_end - t0);
+        __syncthreads();
+        for (int idx = tid; idx < AD_KT * (D / 4); idx += AD_THREADS) {
+            const int j = idx / (D / 4), c = (idx % (D / 4)) * 4;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (j < nk) {
+                const int t = t0 + j;
+                if (t == pos) {  // the row this kernel appends: take it from shared memory, not from the cache
+                    kv = *reinterpret_cast<const float4*>(&knew[c]);
+                    vv = *reinterpret_cast<const float4*>(&vnew[c]);
+                } else {
+                    kv = *reinterpret_cast<const float4*>(p.kc + size_t(t) * KD + kvh * D + c);
+                    vv = *reinterpret_cast<const float4*>(p.vc + size_t(t) * KD + kvh * D + c);
+                }
+            }
+            Ks[j][c] = kv.x; Ks[j][c + 1] = kv.y; Ks[j][c + 2] = kv.z; Ks[j][c + 3] = kv.w;
+            *reinterpret_cast<float4*>(&Vs[j][c]) = vv;
+        }
+        __syncthreads();
+        // scores: warp = head, lane = key; dimension order, multiply then add (no contraction), as the CPU path does
+        if (warp < group) {
+            float s = -INFINITY;
+            if (lane < nk) {
+                float a = 0.f;
+#pragma unroll 8
+                for (int i = 0; i < D; ++i) a = __fadd_rn(a, __fmul_rn(qs[warp][i], Ks[lane][i]));
+                s = __fmul_rn(a, p.scale);
+            }
+            const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(s));
+            const float pj = lane < nk ? expf(s - m_new) : 0.f;
+            const float sum = warp_sum(pj);
+            Ps[warp][lane] = pj;
+            if (lane == 0) {
+                const float c = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                corr_s[warp] = c;
+                l_s[warp] = l_s[warp] * c + sum;
+                m_s[warp] = m_new;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = oh + 2 * i;
+            if (h >= group) continue;
+            float a = acc[i] * corr_s[h];
+            for (int j = 0; j < nk; ++j) a = fmaf(Ps[h][j], Vs[j][od], a);
+            acc[i] = a;
+        }
+    }
+    __syncthreads();
+
+    if (p.nsplit == 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = oh + 2 * i;
+            if (h < group) p.att[(kvh * group + h) * D + od] = acc[i] / l_s[h];
+        }
+        return;
+    }
+    // partial result of this split: [group][D] accumulators, then m and l per head
+    float* mine = p.part + (size_t(kvh) * p.nsplit + split) * group * (D + 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int h = oh + 2 * i;
+        if (h < group) mine[h * (D + 2) + od] = acc[i];
+    }
+    if (tid < group) {
+        mine[tid * (D + 2) + D] = m_s[tid];
+        mine[tid * (D + 2) + D + 1] = l_s[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned old = atomicAdd(&p.counters[kvh], 1u);
+        s_last = old == unsigned(p.nsplit - 1);
+        if (s_last) p.counters[kvh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* base = p.part + size_t(kvh) * p.nsplit * group * (D + 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int h = oh + 2 * i;
+        if (h >= group) continue;
+        float M = -INFINITY;
+        for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, __ldcg(base + (size_t(s) * group + h) * (D + 2) + D));
+        float L = 0.f, o = 0.f;
+        for (int s = 0; s < p.nsplit; ++s) {  // fixed split order
+            const float* ps = base + (size_t(s) * group + h) * (D + 2);
+            const float ms = __ldcg(ps + D);
+            if (ms == -INFINITY) continue;
+            const float w = expf(ms - M);
+            L = fmaf(__ldcg(ps + D + 1), w, L);
+            o = fmaf(__ldcg(ps + od), w, o);
+        }
+        p.att[(kvh * group + h) * D + od] = o / L;
+    }
+}
+
+// ---------------------------------------------------------------- prompt chunk
+
+// grid (B, H + 2 HKV), one warp per (token, head). q heads: norm + rope in place. k heads: norm + rope in place and
+// store to the cache row pos0 + b. v heads: store.
+__global__ void __launch_bounds__(32) k_qkv_post(float* qkv, int64_t ld, const float* q_norm, const float* k_norm,
+                                                 const float2* rope, int pos0, float* kc, float* vc, int H, int HKV,
+                                                 int rope_dim, float eps) {
+    const int b = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x, QD = H * D, KD = HKV * D;
+    const int pos = pos0 + b;
+    float* row = qkv + int64_t(b) * ld;
+    const float2* cs = rope + size_t(pos) * (rope_dim / 2);
+    if (hd < H) {
+        head_norm_rope(row + hd * D, q_norm, cs, rope_dim, eps, row + hd * D, lane);
+    } else if (hd < H + HKV) {
+        float* k = row + QD + (hd - H) * D;
+        head_norm_rope(k, k_norm, cs, rope_dim, eps, k, lane);
+        for (int i = lane; i < D; i += 32) kc[size_t(pos) * KD + (hd - H) * D + i] = k[i];
+    } else {
+        const float* v = row + QD + KD + (hd - H - HKV) * D;
+        for (int i = lane; i < D; i += 32) vc[size_t(pos) * KD + (hd - H - HKV) * D + i] = v[i];
+    }
+}
+
+constexpr int AP_Q = 32, AP_K = 32, AP_THREADS = 256, AP_LD = D + 1;
+constexpr size_t AP_SMEM = size_t(AP_Q * AP_LD + AP_K * AP_LD + AP_K * D + AP_Q * (AP_K + 1)) * sizeof(float);
+
+// grid (H, ceil(B/32)). Query b of the chunk sits at position pos0 + b and sees keys 0..pos0+b (causal).
+__global__ void __launch_bounds__(AP_THREADS) k_attn_prefill(const float* __restrict__ qkv, int64_t ld,
+                                                             const float* __restrict__ kc, const float* __restrict__ vc,
+                                                             float* __restrict__ att, int64_t ld_att, int pos0, int B, int H,
+                                                             int HKV, float scale) {
+    extern __shared__ __align__(16) float sm[];
+    float (*Qs)[AP_LD] = reinterpret_cast<float (*)[AP_LD]>(sm);
+    float (*Ks)[AP_LD] = reinterpret_cast<float (*)[AP_LD]>(sm + AP_Q * AP_LD);
+    float (*Vs)[D] = reinterpret_cast<float (*)[D]>(sm + AP_Q * AP_LD + AP_K * AP_LD);
+    float (*Ps)[AP_K + 1] = reinterpret_cast<float (*)[AP_K + 1]>(sm + AP_Q * AP_LD + AP_K * AP_LD + AP_K * D);
+    const int tid = threadIdx.x, hd = blockIdx.x, q0 = blockIdx.y * AP_Q, KD = HKV * D, kvh = hd / (H / HKV);
+    const int qi = tid >> 3, sub = tid & 7;  // 8 threads per query row
+    const int nq = min(AP_Q, B - q0);
+    for (int idx = tid; idx < AP_Q * D; idx += AP_THREADS) {
+        const int r = idx / D, c = idx % D;
+        Qs[r][c] = r < nq ? qkv[int64_t(q0 + r) * ld + hd * D + c] : 0.f;
+    }
+    float m = -INFINITY, l = 0.f, acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    const int my_last = pos0 + q0 + qi;            // last key this query may see
+    const int T = pos0 + q0 + nq;                  // keys needed by the tile
+    for (int t0 = 0; t0 < T; t0 += AP_K) {
+        __syncthreads();
+        for (int idx = tid; idx < AP_K * (D / 4); idx += AP_THREADS) {
+            const int j = idx / (D / 4), c = (idx % (D / 4)) * 4;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (t0 + j < T) {
+                kv = *reinterpret_cast<const float4*>(kc + size_t(t0 + j) * KD + kvh * D + c);
+                vv = *reinterpret_cast<const float4*>(vc + size_t(t0 + j) * KD + kvh * D + c);
+            }
+            Ks[j][c] = kv.x; Ks[j][c + 1] = kv.y; Ks[j][c + 2] = kv.z; Ks[j][c + 3] = kv.w;
+            *reinterpret_cast<float4*>(&Vs[j][c]) = vv;
+        }
+        __syncthreads();
+        float s[4] = {0.f, 0.f, 0.f, 0.f};  // keys sub + 8i
+#pragma unroll 4
+        for (int d = 0; d < D; ++d) {
+            const float q = Qs[qi][d];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] = __fadd_rn(s[i], __fmul_rn(q, Ks[sub + 8 * i][d]));
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s[i] = t0 + sub + 8 * i <= my_last ? __fmul_rn(s[i], scale) : -INFINITY;
+            mx = fmaxf(mx, s[i]);
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m, mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float pj = s[i] == -INFINITY ? 0.f : expf(s[i] - m_new);
+            Ps[qi][sub + 8 * i] = pj;
+            sum += pj;
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+        l = l * corr + sum;
+        m = m_new;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] *= corr;
+        const int nk = min(AP_K, T - t0);
+        for (int j = 0; j < nk; ++j) {
+            const float pj = Ps[qi][j];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(pj, Vs[j][sub + 8 * i], acc[i]);
+        }
+    }
+    if (qi < nq) {
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) att[int64_t(q0 + qi) * ld_att + hd * D + sub + 8 * i] = acc[i] * inv;
+    }
+}
+
+// ---------------------------------------------------------------- RMSNorm over rows (el::rmsnorm, src/ops.cpp:155-160)
+__global__ void __launch_bounds__(256) k_rmsnorm_rows(float* out, const float* x, const float* w, int n, float eps) {
+    __shared__ double red8[8];
+    const int tid = threadIdx.x;
+    const float* xr = x + int64_t(blockIdx.x) * n;
+    float* o = out + int64_t(blockIdx.x) * n;
+    double ss = 0.0;
+    for (int i = tid; i < n; i += 256) { const double v = xr[i]; ss += v * v; }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red8[tid >> 5] = ss;
+    __syncthreads();
+    ss = 0.0;
+    for (int i = 0; i < 8; ++i) ss += red8[i];
+    const float inv = float(1.0 / sqrt(ss / n + double(eps)));
+    for (int i = tid; i < n; i += 256) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+}
+
+// ---------------------------------------------------------------- host side
+
+int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s) {
+    if (a.H % a.HKV || a.H / a.HKV > AD_MAXG) return fail(ELB_ERR_UNSUPPORTED, "attention: at most 8 query heads per KV head");
+    AttnDecodeParams p{a.qkv, a.q_norm, a.k_norm, reinterpret_cast<const float2*>(a.rope), a.pos, a.kc, a.vc, a.att, a.part,
+                       a.counters, a.H, a.HKV, a.rope_dim, a.nsplit, a.eps, a.scale};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.HKV, a.nsplit);
+    cfg.blockDim = dim3(AD_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    ELB_CUDA(cudaLaunchKernelEx(&cfg, k_attn_decode, p));
+    return ELB_OK;
+}
+
+int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_norm, const float* rope, int pos0, int B,
+                    float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s) {
+    k_qkv_post<<<dim3(B, H + 2 * HKV), 32, 0, s>>>(qkv, ld, q_norm, k_norm, reinterpret_cast<const float2*>(rope), pos0, kc,
+                                                   vc, H, HKV, rope_dim, eps);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
+int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
+                        int pos0, int B, int H, int HKV, float scale, cudaStream_t s) {
+    static thread_local bool configured = false;
+    if (!configured) {
+        ELB_CUDA(cudaFuncSetAttribute(k_attn_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AP_SMEM)));
+        configured = true;
+    }
+    k_attn_prefill<<<dim3(H, (B + AP_Q - 1) / AP_Q), AP_THREADS, AP_SMEM, s>>>(qkv, ld, kc, vc, att, ld_att, pos0, B, H, HKV,
+                                                                             scale);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
+int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s) {
+    k_rmsnorm_rows<<<rows, 256, 0, s>>>(out, x, w, n, eps);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
+}  // namespace elb

@@ -1,0 +1,226 @@
+// Shared declarations of libelb: error handling, device helpers, and the tiled weight layouts.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/elb.h"
+
+namespace elb {
+
+// ---------------------------------------------------------------- errors (no exceptions cross the C ABI)
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+
+#define ELB_CUDA(expr)                                                                                         \
+    do {                                                                                                       \
+        cudaError_t e_ = (expr);                                                                               \
+        if (e_ != cudaSuccess)                                                                                 \
+            return ::elb::fail(ELB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));              \
+    } while (0)
+
+#define ELB_TRY(expr)                \
+    do {                             \
+        int rc_ = (expr);            \
+        if (rc_ != ELB_OK) return rc_; \
+    } while (0)
+
+// ---------------------------------------------------------------- block formats (src/quant.h:20-41 of the reference)
+constexpr int QK8_0 = 32, QK_K = 256;
+constexpr int Q8_0_BYTES = 34, Q4_K_BYTES = 144, Q6_K_BYTES = 210;
+constexpr int TILE_ROWS = 16;  // rows of one weight tile = M of mma.m16n8k*
+
+// Tiled device layouts. A weight is cut into tiles of 16 consecutive rows; within a tile, "lane" means the
+// lane of the warp that consumes it, lane = 4*g + t, which owns rows g and g+8 of the tile (the A-fragment rows
+// of mma.m16n8k32/k16) and 8 (Q4_K, Q8_0) or 4 (Q6_K) consecutive k positions of each sub-block. The bytes of a
+// tile are exactly the bytes of its 16 rows in the file, only permuted — nothing is widened or rounded.
+//
+// Q4_K, per (tile, 256-block): 2304 B = 16 * 144
+//     [  0, 256)  headers: for g in 0..7: 16 B of row g (fp16 d, fp16 dmin, 12 packed scale bytes), 16 B of row g+8
+//     [256,2304)  qs: for pair j in 0..3 (sub-blocks 2j low nibbles, 2j+1 high nibbles): lane * 16 B =
+//                 row g bytes [32j+8t, +8) then row g+8 bytes [32j+8t, +8)
+constexpr int Q4K_UNIT = 16 * Q4_K_BYTES;
+// Q6_K, per (tile, 256-block): 3360 B = 16 * 210
+//     [   0,  32)  fp16 d of rows g=0..7 interleaved as (row g, row g+8)
+//     [  32, 288)  int8 scales: for g: 16 B of row g, 16 B of row g+8
+//     [ 288,2336)  low nibbles: for quad c in 0..3 (sub-blocks 4c..4c+3): lane * 16 B = words i=0..3 (sub-block
+//                  4c+i): byte j = value k=16(4c+i)+4t+j of row g in the low nibble, of row g+8 in the high nibble
+//     [2336,3360)  high 2 bits: for quad c: lane * 8 B = word for row g, word for row g+8; in each word byte j
+//                  holds, at bits 2i..2i+1, the top two bits of value k=16(4c+i)+4t+j
+constexpr int Q6K_UNIT = 16 * Q6_K_BYTES;
+// Q8_0, per (tile, group of 4 32-blocks): 2176 B = 16 * 4 * 34
+//     [  0, 128)  fp16 d: for g: (row g blocks 0..3), (row g+8 blocks 0..3)  -> 16 B per g
+//     [128,2176)  qs: for block i in 0..3: lane * 16 B = row g bytes [8t, +8) then row g+8 bytes [8t, +8)
+constexpr int Q8_UNIT = 16 * 4 * Q8_0_BYTES;
+constexpr int Q8_GROUP = 4;  // 32-blocks per unit (row length must be a multiple of 128)
+
+struct Weight {
+    int device = 0;
+    int type = 0;          // ggml type id
+    int64_t rows = 0;      // logical rows (2x the per-matrix rows for a gate|up pair)
+    int64_t n = 0;         // row length
+    int64_t tiles = 0;     // ceil(rows / 16)
+    int64_t units_per_tile = 0;
+    int unit_bytes = 0;
+    bool pair = false;     // gate|up interleaved in 8-row groups
+    uint8_t* tiled = nullptr;  // tiled layout (quantized types) or plain row-major fp16 (F16)
+    size_t tiled_bytes = 0;
+    // digit planes for the tensor-core path: plane p holds digit p of the integer weight, row-major [rows16][n]
+    int n_planes = 0;
+    int8_t* planes = nullptr;  // [n_planes][tiles*16][n]
+    __half* pl_d = nullptr;    // [tiles*16][n/blk] block scale d (blk = 256, Q8_0: 32)
+    float* pl_dm = nullptr;    // Q4_K: [tiles*16][n/32] fl(dmin * m)
+    // scratch of the split-K matvec (per weight so that matvecs of different weights may overlap)
+    float* part = nullptr;     // [grid][2][16]
+    unsigned* counters = nullptr;  // [tiles]
+    int max_grid = 0;
+};
+
+// ---------------------------------------------------------------- device helpers
+__device__ __forceinline__ float h2f_bits(uint32_t h16) { return __half2float(__ushort_as_half((unsigned short)h16)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// 6-bit scale / min of sub-block j from the 12 packed bytes (q4k_scale_min, src/quant.h:44-52 of the reference)
+__host__ __device__ __forceinline__ void q4k_scale_min(int j, const uint8_t* q, int& sc, int& m) {
+    if (j < 4) {
+        sc = q[j] & 63;
+        m = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+        m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+// exact int -> float for |v| <= 2^22 (adds 1.5*2^23 in the integer domain, subtracts it as a float)
+__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// mma.sync m16n8k32 / m16n8k16, A unsigned or signed 8-bit, B signed 8-bit, int32 accumulate (exact)
+__device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+
+// programmatic dependent launch: let the next kernel of the stream start its prologue / wait for the previous one
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------- host-side declarations shared between files
+struct DeviceInfo {
+    int sm_count = 0;
+    size_t smem_optin = 0;
+};
+int device_info(int device, DeviceInfo* out);
+
+// weights.cu
+int weight_create(int device, int type, int64_t rows_one, int64_t n, const void* bytes, size_t nbytes, int flags,
+                  Weight** out);
+void weight_destroy(Weight* w);
+int get_rows_dev(const Weight* w, int64_t row0, int64_t count, float* d_out, cudaStream_t s);
+int launch_gather_rows(const Weight* w, const int32_t* d_tokens, int count, float* d_out, cudaStream_t s);
+
+// gemv.cu — decode matvec. Prologue: what the kernel does to x before the limb split; epilogue: what it does
+// with the row sums.
+enum { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SILU = 2 };
+struct GemvArgs {
+    const float* x = nullptr;       // [n] input activation (device)
+    const float* norm_w = nullptr;  // [n] RMSNorm weight (PRO_RMSNORM)
+    float eps = 0.f;
+    float* y = nullptr;             // [rows] (EPI_SILU: [rows/2])
+    const float* resid = nullptr;   // EPI_ADD: y = resid + W x (may alias y)
+    int prologue = PRO_PLAIN, epilogue = EPI_STORE;
+    int nl = 4;
+    bool pdl = false;               // launch with programmatic stream serialization
+    int32_t *dbgP = nullptr, *dbgI = nullptr, *dbgJ = nullptr;  // parity dumps
+};
+// linear.cu — several tokens at once
+int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const float* d_norm_w, float eps,
+                 int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s);
+int gemm_planes_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B,
+                       float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
+int gemm_f16_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, float* d_y,
+                    int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
+
+// attn.cu
+struct AttnDecodeArgs {
+    const float* qkv; const float *q_norm, *k_norm; const float* rope; const int* pos;
+    float *kc, *vc, *att, *part; unsigned* counters;
+    int H, HKV, rope_dim, nsplit; float eps, scale; bool pdl;
+};
+int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s);
+int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_norm, const float* rope, int pos0, int B,
+                    float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s);
+int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
+                        int pos0, int B, int H, int HKV, float scale, cudaStream_t s);
+int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s);
+
+int gemv_prepare(Weight* w);  // allocates the split-K scratch (once per weight)
+int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s);
+
+}  // namespace elb
+
+// model.cu
+namespace elb {
+struct Model;
+int model_create(const elb_config* cfg, int n_ctx, int device, Model** out);
+int model_set_tensor(Model* m, int role, int layer, int type, int64_t rows, int64_t n, const void* bytes, size_t nbytes);
+int model_finalize(Model* m);
+void model_destroy(Model* m);
+int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits);
+int model_stats(const Model* m, float* ms, int64_t* launches);
+int model_hidden(Model* m, float* out);
+size_t model_weight_bytes(const Model* m);
+size_t model_kv_bytes_per_token(const Model* m);
+}  // namespace elb

@@ -1,0 +1,482 @@
+// The Qwen3 forward pass behind el::Backend::eval of the reference (src/model.h:42-51): weight table, KV cache,
+// the layer loop (CpuModel::forward order, src/model.cpp:157-234), prompt chunking and the captured decode step.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+
+namespace elb {
+
+namespace {
+
+struct HostTensor {
+    int type = -1;
+    int64_t rows = 0, n = 0;
+    const uint8_t* bytes = nullptr;
+    size_t nbytes = 0;
+};
+
+struct Seg {
+    Weight* w = nullptr;
+    int64_t col = 0;  // first output column of this segment
+};
+
+struct Layer {
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    std::vector<Seg> qkv;  // neighbours of equal type are one matrix (upload_lin of the reference, :1509-1528)
+    Weight *wo = nullptr, *gu = nullptr, *down = nullptr;
+};
+
+bool env_on(const char* name) {
+    const char* v = std::getenv(name);
+    return v && v[0] == '1';
+}
+
+}  // namespace
+
+struct Model {
+    elb_config cfg{};
+    int n_ctx = 0, device = 0, max_batch = 512;
+    bool finalized = false;
+    std::vector<HostTensor> pending;  // [3 + n_layer * 11], valid until finalize
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    Weight *embd = nullptr, *head = nullptr;  // head == embd when tied
+    float* output_norm = nullptr;
+    std::vector<Layer> layers;
+    float* rope = nullptr;
+    float *kcache = nullptr, *vcache = nullptr;
+    float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
+    int8_t* limbs = nullptr;
+    float *inv_scale = nullptr, *xsum = nullptr;
+    int32_t* tokens_dev = nullptr;
+    int* pos_dev = nullptr;
+    int32_t* tokens_host = nullptr;  // pinned
+    int* pos_host = nullptr;         // pinned
+    float* attn_part = nullptr;
+    unsigned* attn_counters = nullptr;
+    int attn_split = 1;
+    cudaGraphExec_t graph = nullptr;
+    bool use_graph = true, use_pdl = true;
+    int nl_qkv = 4, nl_wo = 3, nl_gu = 3, nl_down = 4;  // limbs per linear (reference defaults, :1871-1877)
+    float last_ms = 0.f;
+    int64_t last_launches = 0, launches = 0, graph_launches_ = 0;
+    int last_rows = 1, decode_calls = 0;
+    size_t weight_bytes = 0;
+};
+
+namespace {
+
+int64_t slot_of(const Model* m, int role, int layer) { return role <= ELB_OUTPUT_NORM ? role : 3 + int64_t(layer) * 11 + (role - 3); }
+
+int upload_f32(const HostTensor& t, float** out) {
+    if (!t.bytes) return fail(ELB_ERR_STATE, "model: a norm tensor is missing");
+    std::vector<float> v(size_t(t.rows * t.n));
+    if (t.type == ELB_F32) {
+        std::memcpy(v.data(), t.bytes, v.size() * 4);
+    } else if (t.type == ELB_F16) {
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(t.bytes);
+        for (size_t i = 0; i < v.size(); ++i) v[i] = __half2float(__ushort_as_half(h[i]));
+    } else {
+        return fail(ELB_ERR_UNSUPPORTED, "model: norm weights must be F32 or F16");
+    }
+    ELB_CUDA(cudaMalloc(out, v.size() * 4));
+    ELB_CUDA(cudaMemcpy(*out, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+    return ELB_OK;
+}
+
+// consecutive tensors of one type and row length -> one weight; returns segments with their output columns
+int upload_linear(Model* m, std::initializer_list<const HostTensor*> parts, int flags, std::vector<Seg>* out) {
+    std::vector<const HostTensor*> group;
+    int64_t col = 0;
+    auto flush = [&]() -> int {
+        if (group.empty()) return ELB_OK;
+        int64_t rows = 0;
+        size_t bytes = 0;
+        for (auto* t : group) { rows += t->rows; bytes += t->nbytes; }
+        Seg s;
+        s.col = col;
+        if (group.size() == 1) {
+            ELB_TRY(weight_create(m->device, group[0]->type, rows, group[0]->n, group[0]->bytes, bytes, flags, &s.w));
+        } else {
+            std::vector<uint8_t> cat(bytes);
+            size_t off = 0;
+            for (auto* t : group) { std::memcpy(cat.data() + off, t->bytes, t->nbytes); off += t->nbytes; }
+            ELB_TRY(weight_create(m->device, group[0]->type, rows, group[0]->n, cat.data(), bytes, flags, &s.w));
+        }
+        ELB_TRY(gemv_prepare(s.w));
+        m->weight_bytes += s.w->tiled_bytes;
+        out->push_back(s);
+        col += rows;
+        group.clear();
+        return ELB_OK;
+    };
+    for (auto* t : parts) {
+        if (!t->bytes) return fail(ELB_ERR_STATE, "model: a weight tensor is missing");
+        if (!group.empty() && (group[0]->type != t->type || group[0]->n != t->n)) ELB_TRY(flush());
+        group.push_back(t);
+    }
+    return flush();
+}
+
+int upload_pair(Model* m, const HostTensor& gate, const HostTensor& up, Weight** out) {
+    if (!gate.bytes || !up.bytes) return fail(ELB_ERR_STATE, "model: ffn_gate / ffn_up missing");
+    if (gate.type != up.type || gate.n != up.n || gate.rows != up.rows)
+        return fail(ELB_ERR_UNSUPPORTED, "model: ffn_gate and ffn_up must have the same type and shape");
+    std::vector<uint8_t> cat(gate.nbytes + up.nbytes);
+    std::memcpy(cat.data(), gate.bytes, gate.nbytes);
+    std::memcpy(cat.data() + gate.nbytes, up.bytes, up.nbytes);
+    ELB_TRY(weight_create(m->device, gate.type, gate.rows, gate.n, cat.data(), cat.size(), ELB_W_PLANES | ELB_W_PAIR, out));
+    ELB_TRY(gemv_prepare(*out));
+    m->weight_bytes += (*out)->tiled_bytes;
+    return ELB_OK;
+}
+
+int check_shape(const HostTensor& t, int64_t rows, int64_t n, const char* what) {
+    if (t.bytes && (t.rows != rows || t.n != n)) return fail(ELB_ERR_UNSUPPORTED, std::string("model: unexpected shape of ") + what);
+    return ELB_OK;
+}
+
+// ---- one linear layer over B tokens (linear() of the reference, :1706-1780), limbs already split when quantized
+int linear_tokens(Model* m, const Weight* w, const float* xin, int64_t ldx, const float* norm_w, int B, float* y,
+                  int64_t ldy, const float* resid, int epi) {
+    ++m->launches;
+    if (w->type == ELB_F16) return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
+    return gemm_planes_launch(w, m->limbs, m->inv_scale, m->xsum, B, y, ldy, resid, epi, m->stream);
+}
+
+int split_tokens(Model* m, const float* xin, int64_t ldx, int n, int nl, const float* norm_w, int B, bool any_quant) {
+    if (!any_quant) return ELB_OK;
+    ++m->launches;
+    return split_launch(xin, ldx, B, n, nl, norm_w, m->cfg.eps, m->limbs, m->inv_scale, m->xsum, m->stream);
+}
+
+int body_prefill(Model* m, int B, int pos0) {
+    const elb_config& c = m->cfg;
+    const int E = c.n_embd, F = c.n_ff, H = c.n_head, HKV = c.n_head_kv, QD = H * 128, KD = HKV * 128, QKV = QD + 2 * KD;
+    const float scale = 1.0f / std::sqrt(float(c.head_dim));
+    for (int l = 0; l < c.n_layer; ++l) {
+        Layer& L = m->layers[size_t(l)];
+        float* kc = m->kcache + size_t(l) * m->n_ctx * KD;
+        float* vc = m->vcache + size_t(l) * m->n_ctx * KD;
+        bool q = false;
+        for (auto& s : L.qkv) q |= s.w->type != ELB_F16;
+        ELB_TRY(split_tokens(m, m->x, E, E, m->nl_qkv, L.attn_norm, B, q));
+        for (auto& s : L.qkv) ELB_TRY(linear_tokens(m, s.w, m->x, E, L.attn_norm, B, m->qkv + s.col, QKV, nullptr, EPI_STORE));
+        ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, pos0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream));
+        ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream));
+        m->launches += 2;
+        ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16));
+        ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, m->x, E, m->x, EPI_ADD));
+        ELB_TRY(split_tokens(m, m->x, E, E, m->nl_gu, L.ffn_norm, B, L.gu->type != ELB_F16));
+        ELB_TRY(linear_tokens(m, L.gu, m->x, E, L.ffn_norm, B, m->act, F, nullptr, EPI_SILU));
+        ELB_TRY(split_tokens(m, m->act, F, F, m->nl_down, nullptr, B, L.down->type != ELB_F16));
+        ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, m->x, E, m->x, EPI_ADD));
+    }
+    return ELB_OK;
+}
+
+int gemv(Model* m, const Weight* w, const float* xin, const float* norm_w, float* y, const float* resid, int epi, int nl) {
+    GemvArgs a;
+    a.x = xin; a.norm_w = norm_w; a.eps = m->cfg.eps; a.y = y; a.resid = resid;
+    a.prologue = norm_w ? PRO_RMSNORM : PRO_PLAIN;
+    a.epilogue = epi; a.nl = nl; a.pdl = m->use_pdl;
+    ++m->launches;
+    return gemv_launch(w, a, m->stream);
+}
+
+// final norm + head on one row of x (the reference runs the head as a B=1 matvec too, :1833-1837)
+int head_logits(Model* m, const float* xrow) {
+    return gemv(m, m->head, xrow, m->output_norm, m->logits, nullptr, EPI_STORE, 4);
+}
+
+// one token: everything through the matvec kernels; position and token id are read from device memory so that the
+// step can be captured once and replayed
+int body_decode(Model* m) {
+    const elb_config& c = m->cfg;
+    const int H = c.n_head, HKV = c.n_head_kv, KD = HKV * 128;
+    const float scale = 1.0f / std::sqrt(float(c.head_dim));
+    ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, 1, m->x, m->stream));
+    ++m->launches;
+    for (int l = 0; l < c.n_layer; ++l) {
+        Layer& L = m->layers[size_t(l)];
+        for (auto& s : L.qkv) ELB_TRY(gemv(m, s.w, m->x, L.attn_norm, m->qkv + s.col, nullptr, EPI_STORE, m->nl_qkv));
+        AttnDecodeArgs a{m->qkv, L.q_norm, L.k_norm, m->rope, m->pos_dev,
+                         m->kcache + size_t(l) * m->n_ctx * KD, m->vcache + size_t(l) * m->n_ctx * KD, m->att, m->attn_part,
+                         m->attn_counters, H, HKV, c.rope_dim, m->attn_split, c.eps, scale, m->use_pdl};
+        ELB_TRY(attn_decode_launch(a, m->stream));
+        ++m->launches;
+        ELB_TRY(gemv(m, L.wo, m->att, nullptr, m->x, m->x, EPI_ADD, m->nl_wo));
+        ELB_TRY(gemv(m, L.gu, m->x, L.ffn_norm, m->act, nullptr, EPI_SILU, m->nl_gu));
+        ELB_TRY(gemv(m, L.down, m->act, nullptr, m->x, m->x, EPI_ADD, m->nl_down));
+    }
+    return head_logits(m, m->x);
+}
+
+int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
+    std::memcpy(m->tokens_host, tokens, size_t(B) * sizeof(int32_t));
+    *m->pos_host = pos0;
+    ELB_CUDA(cudaMemcpyAsync(m->tokens_dev, m->tokens_host, size_t(B) * sizeof(int32_t), cudaMemcpyHostToDevice, m->stream));
+    ELB_CUDA(cudaMemcpyAsync(m->pos_dev, m->pos_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    ELB_CUDA(cudaEventRecord(m->ev0, m->stream));
+    m->last_rows = B;
+    if (B == 1) {
+        // the first single-token step runs eagerly (it also sets the kernels' launch attributes); the second one is
+        // captured, later ones replay the graph
+        if (m->use_graph && m->decode_calls++ > 0) {
+            if (!m->graph) {
+                cudaGraph_t g = nullptr;
+                ELB_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+                const int64_t before = m->launches;
+                const int rc = body_decode(m);
+                m->graph_launches_ = m->launches - before;
+                const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+                if (rc != ELB_OK) { if (g) cudaGraphDestroy(g); return rc; }
+                ELB_CUDA(e);
+                const cudaError_t ei = cudaGraphInstantiate(&m->graph, g, 0);
+                cudaGraphDestroy(g);
+                ELB_CUDA(ei);
+                m->launches = before;
+            }
+            ELB_CUDA(cudaGraphLaunch(m->graph, m->stream));
+            m->launches += m->graph_launches_;
+        } else {
+            ELB_TRY(body_decode(m));
+        }
+    } else {
+        ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, B, m->x, m->stream));
+        ++m->launches;
+        ELB_TRY(body_prefill(m, B, pos0));
+        if (logits) ELB_TRY(head_logits(m, m->x + size_t(B - 1) * m->cfg.n_embd));
+    }
+    ELB_CUDA(cudaEventRecord(m->ev1, m->stream));
+    if (logits)
+        ELB_CUDA(cudaMemcpyAsync(logits, m->logits, size_t(m->cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+    ELB_CUDA(cudaStreamSynchronize(m->stream));
+    float ms = 0.f;
+    ELB_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    m->last_ms += ms;
+    return ELB_OK;
+}
+
+}  // namespace
+
+int model_create(const elb_config* cfg, int n_ctx, int device, Model** out) {
+    if (!cfg || !out) return fail(ELB_ERR_INVALID, "model_create: null argument");
+    if (n_ctx <= 0) return fail(ELB_ERR_INVALID, "model_create: context length must be positive");
+    if (cfg->n_layer <= 0 || cfg->n_layer > 512 || cfg->n_embd <= 0 || cfg->n_head <= 0 || cfg->n_head_kv <= 0 ||
+        cfg->n_head % cfg->n_head_kv != 0 || cfg->n_ff <= 0 || cfg->n_vocab <= 0 || cfg->rope_dim <= 0 ||
+        cfg->rope_dim % 2 != 0 || cfg->rope_dim > cfg->head_dim)
+        return fail(ELB_ERR_INVALID, "model_create: invalid configuration");
+    if (cfg->head_dim != 128) return fail(ELB_ERR_UNSUPPORTED, "model_create: only head_dim = 128 is supported");
+    if (cfg->n_head / cfg->n_head_kv > 8) return fail(ELB_ERR_UNSUPPORTED, "model_create: at most 8 query heads per KV head");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) {
+        cudaGetLastError();
+        return fail(ELB_ERR_CUDA, "model_create: no such CUDA device");
+    }
+    auto* m = new Model;
+    m->cfg = *cfg;
+    m->n_ctx = n_ctx;
+    m->device = device;
+    m->max_batch = cfg->max_batch > 0 ? cfg->max_batch : 512;
+    m->pending.resize(size_t(3 + cfg->n_layer * 11));
+    m->layers.resize(size_t(cfg->n_layer));
+    m->use_graph = !env_on("ELB_NO_GRAPH");
+    m->use_pdl = !env_on("ELB_NO_PDL");
+    if (const char* v = std::getenv("ELB_NL3")) {  // bit mask like the reference's EL_NL3: 1 qkv, 2 wo, 4 gate/up, 8 down
+        const int mask = std::atoi(v);
+        m->nl_qkv = mask & 1 ? 3 : 4; m->nl_wo = mask & 2 ? 3 : 4; m->nl_gu = mask & 4 ? 3 : 4; m->nl_down = mask & 8 ? 3 : 4;
+    }
+    *out = m;
+    return ELB_OK;
+}
+
+int model_set_tensor(Model* m, int role, int layer, int type, int64_t rows, int64_t n, const void* bytes, size_t nbytes) {
+    if (!m || !bytes) return fail(ELB_ERR_INVALID, "set_tensor: null argument");
+    if (m->finalized) return fail(ELB_ERR_STATE, "set_tensor: model already finalized");
+    if (role < 0 || role > ELB_DOWN) return fail(ELB_ERR_INVALID, "set_tensor: unknown role");
+    if (role > ELB_OUTPUT_NORM && (layer < 0 || layer >= m->cfg.n_layer)) return fail(ELB_ERR_RANGE, "set_tensor: layer out of range");
+    m->pending[size_t(slot_of(m, role, layer))] = HostTensor{type, rows, n, static_cast<const uint8_t*>(bytes), nbytes};
+    return ELB_OK;
+}
+
+void model_destroy(Model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    if (m->stream) cudaStreamSynchronize(m->stream);
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    if (m->head && m->head != m->embd) weight_destroy(m->head);
+    weight_destroy(m->embd);
+    for (Layer& L : m->layers) {
+        for (auto& s : L.qkv) weight_destroy(s.w);
+        weight_destroy(L.wo); weight_destroy(L.gu); weight_destroy(L.down);
+        cudaFree(L.attn_norm); cudaFree(L.ffn_norm); cudaFree(L.q_norm); cudaFree(L.k_norm);
+    }
+    for (void* p : {(void*)m->output_norm, (void*)m->rope, (void*)m->kcache, (void*)m->vcache, (void*)m->x, (void*)m->qkv,
+                    (void*)m->att, (void*)m->act, (void*)m->logits, (void*)m->limbs, (void*)m->inv_scale, (void*)m->xsum,
+                    (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters})
+        cudaFree(p);
+    if (m->tokens_host) cudaFreeHost(m->tokens_host);
+    if (m->pos_host) cudaFreeHost(m->pos_host);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+int model_finalize(Model* m) {
+    if (!m) return fail(ELB_ERR_INVALID, "finalize: null model");
+    if (m->finalized) return fail(ELB_ERR_STATE, "finalize: called twice");
+    ELB_CUDA(cudaSetDevice(m->device));
+    const elb_config& c = m->cfg;
+    const int64_t E = c.n_embd, F = c.n_ff, QD = int64_t(c.n_head) * 128, KD = int64_t(c.n_head_kv) * 128, QKV = QD + 2 * KD;
+    const int64_t V = c.n_vocab, B = m->max_batch;
+    auto P = [&](int role, int layer) -> const HostTensor& { return m->pending[size_t(slot_of(m, role, layer))]; };
+
+    // shapes (read_tensors of the reference, src/model.cpp:66-103)
+    ELB_TRY(check_shape(P(ELB_TOK_EMBD, 0), V, E, "token_embd"));
+    ELB_TRY(check_shape(P(ELB_OUTPUT, 0), V, E, "output"));
+    for (int l = 0; l < c.n_layer; ++l) {
+        ELB_TRY(check_shape(P(ELB_WQ, l), QD, E, "attn_q"));
+        ELB_TRY(check_shape(P(ELB_WK, l), KD, E, "attn_k"));
+        ELB_TRY(check_shape(P(ELB_WV, l), KD, E, "attn_v"));
+        ELB_TRY(check_shape(P(ELB_WO, l), E, QD, "attn_output"));
+        ELB_TRY(check_shape(P(ELB_GATE, l), F, E, "ffn_gate"));
+        ELB_TRY(check_shape(P(ELB_UP, l), F, E, "ffn_up"));
+        ELB_TRY(check_shape(P(ELB_DOWN, l), E, F, "ffn_down"));
+    }
+
+    // device memory budget before anything is allocated (pre-flight check of the reference, :1578-1591)
+    const size_t kv_bytes = size_t(c.n_layer) * size_t(m->n_ctx) * size_t(KD) * sizeof(float);
+    const int64_t maxn = std::max({E, QD, F});
+    size_t need = 2 * kv_bytes + size_t(B) * size_t(E + QKV + QD + F) * 4 + size_t(V) * 4 + size_t(4) * B * maxn + size_t(B) * (maxn / 32 + 1) * 4;
+    for (const HostTensor& t : m->pending)
+        if (t.bytes && t.rows > 1) need += t.nbytes + (t.type != ELB_F16 && &t != &P(ELB_TOK_EMBD, 0) && &t != &P(ELB_OUTPUT, 0) ? size_t(t.rows) * t.n * 2 + size_t(t.rows) * (t.n / 32) * 4 : 0);
+    size_t free_b = 0, total_b = 0;
+    ELB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    if (need + (256ull << 20) > free_b) {
+        char msg[160];
+        std::snprintf(msg, sizeof msg, "not enough device memory: %.0f MB needed, %.0f MB free (lower n_ctx)", need / 1048576.0, free_b / 1048576.0);
+        return fail(ELB_ERR_MEMORY, msg);
+    }
+
+    ELB_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    ELB_CUDA(cudaEventCreate(&m->ev0));
+    ELB_CUDA(cudaEventCreate(&m->ev1));
+
+    const HostTensor& emb = P(ELB_TOK_EMBD, 0);
+    if (!emb.bytes) return fail(ELB_ERR_STATE, "model: token_embd missing");
+    ELB_TRY(weight_create(m->device, emb.type, emb.rows, emb.n, emb.bytes, emb.nbytes, 0, &m->embd));
+    ELB_TRY(gemv_prepare(m->embd));
+    const HostTensor& outw = P(ELB_OUTPUT, 0);
+    if (outw.bytes) {
+        ELB_TRY(weight_create(m->device, outw.type, outw.rows, outw.n, outw.bytes, outw.nbytes, 0, &m->head));
+        ELB_TRY(gemv_prepare(m->head));
+    } else {
+        m->head = m->embd;  // tied embeddings (src/model.cpp:73-74 of the reference)
+    }
+    m->weight_bytes += m->head->tiled_bytes;
+    ELB_TRY(upload_f32(P(ELB_OUTPUT_NORM, 0), &m->output_norm));
+    for (int l = 0; l < c.n_layer; ++l) {
+        Layer& L = m->layers[size_t(l)];
+        ELB_TRY(upload_f32(P(ELB_ATTN_NORM, l), &L.attn_norm));
+        ELB_TRY(upload_f32(P(ELB_FFN_NORM, l), &L.ffn_norm));
+        ELB_TRY(upload_f32(P(ELB_Q_NORM, l), &L.q_norm));
+        ELB_TRY(upload_f32(P(ELB_K_NORM, l), &L.k_norm));
+        ELB_TRY(upload_linear(m, {&P(ELB_WQ, l), &P(ELB_WK, l), &P(ELB_WV, l)}, ELB_W_PLANES, &L.qkv));
+        std::vector<Seg> one;
+        ELB_TRY(upload_linear(m, {&P(ELB_WO, l)}, ELB_W_PLANES, &one));
+        L.wo = one[0].w;
+        ELB_TRY(upload_pair(m, P(ELB_GATE, l), P(ELB_UP, l), &L.gu));
+        one.clear();
+        ELB_TRY(upload_linear(m, {&P(ELB_DOWN, l)}, ELB_W_PLANES, &one));
+        L.down = one[0].w;
+    }
+
+    // RoPE table: angle in double, rounded to float (src/model.cpp:105-109, 23-32; src/cuda/model_cuda.cu:1610-1619)
+    {
+        const int half = c.rope_dim / 2;
+        std::vector<float> cs(size_t(m->n_ctx) * half * 2);
+        std::vector<double> inv(static_cast<size_t>(half));
+        for (int i = 0; i < half; ++i) inv[size_t(i)] = std::pow(c.rope_base, -2.0 * i / c.rope_dim);
+        for (int p = 0; p < m->n_ctx; ++p)
+            for (int i = 0; i < half; ++i) {
+                const double th = p * inv[size_t(i)];
+                cs[(size_t(p) * half + i) * 2] = float(std::cos(th));
+                cs[(size_t(p) * half + i) * 2 + 1] = float(std::sin(th));
+            }
+        ELB_CUDA(cudaMalloc(&m->rope, cs.size() * 4));
+        ELB_CUDA(cudaMemcpy(m->rope, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+    }
+    ELB_CUDA(cudaMalloc(&m->kcache, kv_bytes));
+    ELB_CUDA(cudaMalloc(&m->vcache, kv_bytes));
+    ELB_CUDA(cudaMemset(m->kcache, 0, kv_bytes));
+    ELB_CUDA(cudaMemset(m->vcache, 0, kv_bytes));
+    ELB_CUDA(cudaMalloc(&m->x, size_t(B) * E * 4));
+    ELB_CUDA(cudaMalloc(&m->qkv, size_t(B) * QKV * 4));
+    ELB_CUDA(cudaMalloc(&m->att, size_t(B) * QD * 4));
+    ELB_CUDA(cudaMalloc(&m->act, size_t(B) * F * 4));
+    ELB_CUDA(cudaMalloc(&m->logits, size_t(V) * 4));
+    ELB_CUDA(cudaMalloc(&m->limbs, size_t(4) * B * maxn));
+    ELB_CUDA(cudaMalloc(&m->inv_scale, size_t(B) * 4));
+    ELB_CUDA(cudaMalloc(&m->xsum, size_t(B) * (maxn / 32 + 1) * 4));
+    ELB_CUDA(cudaMalloc(&m->tokens_dev, size_t(B) * sizeof(int32_t)));
+    ELB_CUDA(cudaMalloc(&m->pos_dev, sizeof(int)));
+    ELB_CUDA(cudaMallocHost(&m->tokens_host, size_t(B) * sizeof(int32_t)));
+    ELB_CUDA(cudaMallocHost(&m->pos_host, sizeof(int)));
+    // decode attention: a fixed number of key splits so that the launch shape does not depend on the position
+    DeviceInfo di;
+    ELB_TRY(device_info(m->device, &di));
+    m->attn_split = std::max(1, std::min(32, (di.sm_count + c.n_head_kv - 1) / c.n_head_kv));
+    if (const char* v = std::getenv("ELB_ATTN_SPLIT")) m->attn_split = std::max(1, std::atoi(v));
+    const int group = c.n_head / c.n_head_kv;
+    ELB_CUDA(cudaMalloc(&m->attn_part, size_t(c.n_head_kv) * m->attn_split * group * (128 + 2) * 4));
+    ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(c.n_head_kv) * sizeof(unsigned)));
+    ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(c.n_head_kv) * sizeof(unsigned)));
+    m->pending.clear();
+    m->pending.shrink_to_fit();
+    m->finalized = true;
+    return ELB_OK;
+}
+
+int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits) {
+    if (!m || !tokens) return fail(ELB_ERR_INVALID, "eval: null argument");
+    if (!m->finalized) return fail(ELB_ERR_STATE, "eval: model not finalized");
+    if (n <= 0) return fail(ELB_ERR_INVALID, "eval: empty token sequence");
+    if (pos0 < 0 || int64_t(pos0) + n > m->n_ctx) return fail(ELB_ERR_RANGE, "eval: context window full");
+    for (int i = 0; i < n; ++i)
+        if (tokens[i] < 0 || tokens[i] >= m->cfg.n_vocab) return fail(ELB_ERR_RANGE, "eval: token id out of range");
+    ELB_CUDA(cudaSetDevice(m->device));
+    m->last_ms = 0.f;
+    const int64_t before = m->launches;
+    for (int done = 0; done < n;) {
+        const int b = std::min(m->max_batch, n - done);
+        ELB_TRY(chunk(m, tokens + done, b, pos0 + done, done + b == n ? logits : nullptr));
+        done += b;
+    }
+    m->last_launches = m->launches - before;
+    return ELB_OK;
+}
+
+int model_stats(const Model* m, float* ms, int64_t* launches) {
+    if (!m) return fail(ELB_ERR_INVALID, "stats: null model");
+    if (ms) *ms = m->last_ms;
+    if (launches) *launches = m->last_launches;
+    return ELB_OK;
+}
+
+int model_hidden(Model* m, float* out) {
+    if (!m || !out || !m->finalized) return fail(ELB_ERR_STATE, "hidden: model not ready");
+    ELB_CUDA(cudaMemcpy(out, m->x + size_t(m->last_rows - 1) * m->cfg.n_embd, size_t(m->cfg.n_embd) * 4, cudaMemcpyDeviceToHost));
+    return ELB_OK;
+}
+
+size_t model_weight_bytes(const Model* m) { return m->weight_bytes; }
+size_t model_kv_bytes_per_token(const Model* m) { return size_t(2) * m->cfg.n_layer * m->cfg.n_head_kv * 128 * sizeof(float); }
+int model_device(const Model* m) { return m->device; }
+
+}  // namespace elb

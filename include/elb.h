@@ -1,0 +1,146 @@
+/* exactinfer forward pass for NVIDIA B200 (sm_100a) — C ABI of libelb.so.
+ *
+ * Plain pointers and sizes only. Every function returns an elb_status (0 = ok) unless noted; after a failure
+ * elb_last_error() describes it (thread-local string). Nothing here throws, allocates with a foreign allocator
+ * or falls back to the CPU: without a CUDA device every compute entry point fails with ELB_ERR_CUDA.
+ *
+ * Each entry point cites the interface of the reference project (burakcelik1061-star/exactinfer) that it stands
+ * in for, as path:line inside that project.
+ */
+#ifndef ELB_H
+#define ELB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    ELB_OK = 0,
+    ELB_ERR_CUDA = 1,         /* a CUDA call failed, or no usable device (std::runtime_error in the reference) */
+    ELB_ERR_INVALID = 2,      /* bad argument, e.g. n <= 0 (std::invalid_argument, src/cuda/model_cuda.cu:1649) */
+    ELB_ERR_RANGE = 3,        /* context full or token id out of range (std::out_of_range, :1650-1652) */
+    ELB_ERR_UNSUPPORTED = 4,  /* tensor type / shape the path does not cover (std::runtime_error, :1428,1542) */
+    ELB_ERR_MEMORY = 5,       /* not enough device memory (std::runtime_error, :1586-1590) */
+    ELB_ERR_STATE = 6         /* call order, e.g. eval before finalize */
+} elb_status;
+
+/* ggml tensor type ids, as stored in GGUF (src/gguf.h:22-25) */
+enum { ELB_F32 = 0, ELB_F16 = 1, ELB_Q8_0 = 8, ELB_Q4_K = 12, ELB_Q6_K = 14 };
+
+const char* elb_last_error(void);
+
+/* ---- device -------------------------------------------------------------------------------------------------
+ * el::cuda_available (src/model.h:56, src/cuda/model_cuda.cu:1894-1907): number of devices with compute
+ * capability 10.x; 0 with the reason in elb_last_error() when there is none. */
+int elb_device_count(void);
+/* Raw device / pinned-host buffers for callers that keep activations on the GPU (tests, microbenchmarks). */
+int elb_malloc(int device, size_t bytes, void** out);
+int elb_free(void* dptr);
+int elb_host_alloc(size_t bytes, void** out); /* pinned */
+int elb_host_free(void* hptr);
+int elb_memcpy_h2d(void* dst, const void* src, size_t bytes);
+int elb_memcpy_d2h(void* dst, const void* src, size_t bytes);
+int elb_device_sync(int device);
+
+/* ---- weights ------------------------------------------------------------------------------------------------
+ * One weight matrix W[rows][n] in a ggml block format, uploaded and re-laid out for the GPU kernels
+ * (upload_group, src/cuda/model_cuda.cu:1450-1506). `bytes` is the tensor exactly as it lies in the GGUF file
+ * (el::Tensor::data, src/gguf.h:27-36). Supported: F16, Q8_0, Q4_K, Q6_K (wtype_of, :1421-1431).
+ *
+ * flags: ELB_W_PLANES also builds the int8 digit planes the tensor-core (prefill) path reads;
+ *        ELB_W_PAIR interleaves two equally shaped matrices given back to back in `bytes` (gate then up) in
+ *        8-row groups, so that the SwiGLU epilogue finds gate[r] and up[r] in one thread (`rows` = rows of ONE
+ *        of them; the weight then has 2*rows rows). */
+typedef struct elb_weight elb_weight;
+enum { ELB_W_PLANES = 1, ELB_W_PAIR = 2 };
+int elb_weight_create(int device, int ggml_type, int64_t rows, int64_t n, const void* bytes, size_t nbytes, int flags,
+                      elb_weight** out);
+void elb_weight_destroy(elb_weight* w);
+int64_t elb_weight_rows(const elb_weight* w);
+int64_t elb_weight_cols(const elb_weight* w);
+size_t elb_weight_device_bytes(const elb_weight* w); /* bytes the decode path streams per matvec */
+
+/* ---- operators (src/ops.h:11-29). Pointers named d_* are device pointers, the others host pointers. ---------- */
+
+/* el::get_row (src/ops.h:20, src/ops.cpp:76-82) for `count` consecutive rows from row0, decoded on the device
+ * with the reference's fp32 operation order (src/quant.cpp:7-60): out[count][n], bit-exact. */
+int elb_get_rows(const elb_weight* w, int64_t row0, int64_t count, float* out);
+int elb_get_rows_dev(const elb_weight* w, int64_t row0, int64_t count, float* d_out);
+
+/* el::matvec (src/ops.h:23, src/ops.cpp:126-153): y[r] = sum_j W[r][j] * x[j]. Quantized types split x into
+ * `nl` (3 or 4) exact int8 limbs (k_split8, src/cuda/model_cuda.cu:701-729) and accumulate quant x limb products
+ * in int32; F16 weights use fp32 FMA. nl = 0 picks 4. */
+int elb_matvec(const elb_weight* w, const float* x, float* y, int nl);
+int elb_matvec_dev(const elb_weight* w, const float* d_x, float* d_y, int nl);
+
+/* Y[b][rows] = X[b][n] * W^T for b tokens (linear() with B > 1, src/cuda/model_cuda.cu:1706-1780): limb split once,
+ * then the int8 tensor-core GEMM over the digit planes (needs ELB_W_PLANES). */
+int elb_matmul(const elb_weight* w, const float* x, int64_t b, float* y, int nl);
+int elb_matmul_dev(const elb_weight* w, const float* d_x, int64_t b, float* d_y, int nl);
+
+/* el::rmsnorm (src/ops.h:26, src/ops.cpp:155-160) over `rows` rows of length n (sum of squares in double). */
+int elb_rmsnorm(float* out, const float* x, const float* w, int n, float eps, int rows);
+
+/* k_split8 (src/cuda/model_cuda.cu:701-729): limbs[nl][b][n] int8, inv_scale[b] = 2^-k. */
+int elb_split_limbs(int device, const float* x, int64_t b, int64_t n, int nl, int8_t* limbs, float* inv_scale);
+
+/* Exact int32 sums the matvec forms, for parity checks (src/cuda/model_cuda.cu:943-1012):
+ *   P[rows][n/sub][nl]  = sum over one sub-block (32 values; 16 for Q6_K) of limb * quant   (sub-block partials)
+ *   I[rows][n/blk][nl]  = sum over the sub-blocks of a super-block of scale * P             (blk 256; 32 for Q8_0)
+ *   J[rows][n/blk][nl]  = Q4_K only: sum of min * (sum of the limb over the sub-block); zero otherwise
+ * Any of P, I, J may be NULL. Computed by the same device code path as elb_matvec. */
+int elb_limb_sums(const elb_weight* w, const float* x, int nl, int32_t* P, int32_t* I, int32_t* J);
+
+/* ---- model (el::Backend, src/model.h:42-57) -------------------------------------------------------------------*/
+typedef struct {
+    int32_t n_layer, n_embd, n_ff, n_head, n_head_kv, head_dim, n_vocab, rope_dim; /* el::Config, src/model.h:17-23 */
+    double rope_base;
+    float eps;
+    int32_t max_batch; /* prompt chunk length; 0 = 512 (make_cuda_backend, src/cuda/model_cuda.cu:1912) */
+} elb_config;
+
+/* tensor roles, in the order of el::ModelTensors / el::LayerTensors (src/model.h:25-36) */
+enum {
+    ELB_TOK_EMBD = 0, ELB_OUTPUT = 1, ELB_OUTPUT_NORM = 2, ELB_ATTN_NORM = 3, ELB_FFN_NORM = 4, ELB_Q_NORM = 5,
+    ELB_K_NORM = 6, ELB_WQ = 7, ELB_WK = 8, ELB_WV = 9, ELB_WO = 10, ELB_GATE = 11, ELB_UP = 12, ELB_DOWN = 13
+};
+
+typedef struct elb_model elb_model;
+
+/* CudaModel constructor (src/cuda/model_cuda.cu:1539-1635), split so that the caller streams tensors in:
+ * create -> set_tensor for every tensor of el::ModelTensors (ELB_OUTPUT may be omitted: tied head,
+ * src/model.cpp:73-74) -> finalize (allocates the fp32 KV cache for n_ctx positions and the scratch buffers,
+ * builds the RoPE table from double-precision angles, checks device memory). head_dim must be 128. */
+int elb_model_create(const elb_config* cfg, int n_ctx, int device, elb_model** out);
+int elb_model_set_tensor(elb_model* m, int role, int layer, int ggml_type, int64_t rows, int64_t n, const void* bytes,
+                         size_t nbytes);
+int elb_model_finalize(elb_model* m);
+void elb_model_destroy(elb_model* m);
+
+/* Backend::eval (src/model.h:48-50; CudaModel::eval, src/cuda/model_cuda.cu:1648-1658): tokens[0..n) are processed
+ * at positions pos0..pos0+n-1 and written to the KV cache (only rows [pos0, pos0+n) are touched); when logits is
+ * not NULL the LAST token's n_vocab fp32 logits are written to that host buffer. Synchronous.
+ * n <= 0 -> ELB_ERR_INVALID; pos0 < 0, pos0+n > n_ctx or a token outside [0, n_vocab) -> ELB_ERR_RANGE. */
+int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits);
+
+/* Same step, measured: device time in milliseconds of the last elb_model_eval (CUDA events on the model's own
+ * stream, host<->device copies excluded), and the number of this library's kernels that call launched. */
+int elb_model_last_eval_stats(const elb_model* m, float* device_ms, int64_t* kernel_launches);
+/* Residual stream of the last evaluated token, E floats (for layer-level parity checks). */
+int elb_model_hidden(elb_model* m, float* out);
+size_t elb_model_weight_bytes(const elb_model* m); /* bytes one decode step streams from the weight tensors */
+size_t elb_model_kv_bytes_per_token(const elb_model* m);
+
+/* ---- timing helpers for microbenchmarks: run the device-pointer matvec `iters` times over `n_w` weights in
+ * rotation (so that the working set exceeds L2) and return the average device time per call in ms. */
+int elb_bench_matvec(elb_weight* const* ws, int n_w, const float* d_x, float* d_y, int nl, int iters, float* avg_ms);
+int elb_bench_matmul(elb_weight* const* ws, int n_w, const float* d_x, int64_t b, float* d_y, int nl, int iters,
+                     float* avg_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELB_H */
