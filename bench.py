@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the forward-pass hot path: Qwen3-4B-shaped Q4_K_M decode (and prefill) tok/s on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0). A step is one single-token decode step at batch 1 after a 512-token prompt
+(el bench --pp 512 --tg K of the reference, src/main.cpp:621-648, seeded synthetic weights, LCG token stream).
+  value      decode tok/s with tokens and weights resident on the device (CUDA events around K back-to-back steps)
+  e2e        the same K steps through Backend.eval: host token in, host logits out, copies inside the timed region
+  roofline   the dominant kernel (Q4_K matvec, 2560 x 9728, 4 limbs) timed alone over 24 weight copies in rotation
+  cpu_baseline  the reference's CPU path on the host cores, bounded sample (N=1, rank 0 only)
+--impl reference times only that CPU path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from exactinfer_b200 import synth  # noqa: E402
+
+PROMPT = 512
+SEED = 20251125
+MICRO_ROWS, MICRO_N = 2560, 9728
+MICRO_BYTES = MICRO_ROWS * (MICRO_N // 256) * 144  # 14 008 320 algorithmic bytes per matvec
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--workload", default="qwen3-4b-q4_k_m", choices=sorted(synth.SPECS))
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (debugging only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=20.0)
+    return ap.parse_args()
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.remove(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+def get_spec(args):
+    spec = synth.SPECS[args.workload]
+    if args.layers:
+        import dataclasses
+        spec = dataclasses.replace(spec, n_layer=args.layers)
+    return spec
+
+
+def model_tensors(spec):
+    t0 = time.time()
+    tens = list(synth.generate(spec, SEED))
+    return tens, time.time() - t0
+
+
+# ---------------------------------------------------------------- CPU baseline (the reference's CPU path)
+
+def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
+    """Decode tok/s of the reference CPU backend on the host cores, on a bounded sample: one warm-up token, then
+    single-token steps from position 1 until `seconds` have passed (at most max_steps). Uses the reference's own code
+    (oracle/_ref/libelref.so over a GGUF written to a temporary file) when that build is present, else the restated
+    oracle (bit-identical, same OpenMP structure)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+
+    toks = synth.lcg_tokens(max_steps + 1, spec.n_vocab)
+    n_ctx = max_steps + 2
+    tmp = None
+    if ol.have_ref():
+        kind = "reference"
+        tmp = tempfile.mkdtemp(prefix="elb_bench_")
+        path = os.path.join(tmp, "model.gguf")
+        synth.write_gguf(path, spec, tens)
+        model = ol.RefModel(path, n_ctx)
+        cores = ol.ref().ref_threads() if hasattr(ol.ref(), "ref_threads") else os.cpu_count()
+    else:
+        kind = "port"
+        model = ol.OracleModel(spec, tens, n_ctx)
+        cores = ol.oracle().orc_threads()
+    model.eval(toks[:1], 0)  # warm-up
+    t0 = time.perf_counter()
+    done = 0
+    while done < max_steps and (done < 2 or time.perf_counter() - t0 < seconds):
+        model.eval(toks[done + 1:done + 2], done + 1)
+        done += 1
+    dt = time.perf_counter() - t0
+    model.close()
+    if tmp:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+    return {"value": done / dt, "unit": "tok/s", "cores": int(cores), "kind": kind,
+            "sample": f"{done} single-token decode steps at positions 1..{done} of the same model (1 warm-up token; "
+                      f"context shorter than the GPU run's {PROMPT}+), {dt:.1f} s"}, done, dt
+
+
+def run_reference(args):
+    rank, local, world = dist_env()
+    if rank != 0:
+        return
+    spec = get_spec(args)
+    tens, _ = model_tensors(spec)
+    budget = 150.0
+    base, done, dt = cpu_decode_baseline(spec, tens, budget, max(2, args.steps))
+    out = {"impl": "reference", "metric": f"{spec.name} decode tok/s (batch 1)", "value": base["value"], "unit": "tok/s",
+           "n_gpus": args.gpus, "steps": done, "steps_requested": args.steps, "warmup": 1,
+           "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "f32", "data": "synthetic", "config": {"workload": f"{spec.name} tg (CPU path, token at a time)"},
+           "cpu_baseline": base,
+           "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out), flush=True)
+
+
+# ---------------------------------------------------------------- the dominant kernel alone (roofline)
+
+def microbench_matvec(e, device, iters=480, copies=24):
+    """Q4_K matvec 2560 x 9728 with a 4-limb N(0,1) activation, `copies` distinct weights in rotation (336 MB, larger
+    than the 126 MB L2) so that every launch streams its weight from HBM. Average device time per launch in ms."""
+    import ctypes as C
+    from exactinfer_b200 import capi
+    rng = np.random.default_rng(SEED + 1)
+    ws = [e.Weight(synth.Q4_K, MICRO_ROWS, MICRO_N, synth.rand_q4_k(rng, MICRO_ROWS, MICRO_N), device=device)
+          for _ in range(copies)]
+    x = e.DeviceBuffer.from_array(rng.normal(size=MICRO_N).astype(np.float32), device)
+    y = e.DeviceBuffer(MICRO_ROWS * 4, device)
+    arr = (C.c_void_p * copies)(*[w._h for w in ws])
+    ms = C.c_float()
+    capi.check(capi.lib().elb_bench_matvec(arr, copies, x.ptr, y.ptr, 4, iters, C.byref(ms)))
+    for w in ws:
+        w.close()
+    return ms.value
+
+
+# ---------------------------------------------------------------- our arm
+
+def pinned_array(e, n_floats):
+    import ctypes as C
+    from exactinfer_b200 import capi
+    p = C.c_void_p()
+    capi.check(capi.lib().elb_host_alloc(n_floats * 4, C.byref(p)))
+    return np.ctypeslib.as_array((C.c_float * n_floats).from_address(p.value)), p
+
+
+def run_ours(args):
+    rank, local, world = dist_env()
+    n_gpus = max(args.gpus, world)
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import exactinfer_b200 as e
+    ok, why = e.cuda_available()
+    if not ok:
+        raise SystemExit(f"bench: the CUDA path is unavailable ({why}); there is no CPU fallback")
+    K, W = args.steps, max(args.warmup, 3)
+    spec = get_spec(args)
+    tens, gen_s = model_tensors(spec)
+    t0 = time.time()
+    model = e.Backend(spec, tens, PROMPT + W + K + 1, device=local)
+    load_s = time.time() - t0
+    toks = synth.lcg_tokens(PROMPT + W + K, spec.n_vocab)
+    logits, _pin = pinned_array(e, spec.n_vocab)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- prefill pp512: one warm-up pass, then 3 timed passes (median); weights (GBs) exceed L2 between passes
+    model.eval(toks[:PROMPT], 0, out=logits)
+    pp_dev, pp_wall = [], []
+    for _ in range(3):
+        barrier()
+        t1 = time.perf_counter()
+        model.eval(toks[:PROMPT], 0, out=logits)
+        pp_wall.append(time.perf_counter() - t1)
+        pp_dev.append(model.last_eval_stats()[0] / 1000.0)
+    pp_launches = model.last_eval_stats()[1]
+    pp_dev_s, pp_wall_s = max_over_ranks(statistics.median(pp_dev)), max_over_ranks(statistics.median(pp_wall))
+
+    # ---- decode: W warm-up steps, then exactly K timed steps (device events inside the library, on its stream)
+    model.eval_steps(toks[PROMPT:PROMPT + W], PROMPT)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    dev_ms = model.eval_steps(toks[PROMPT + W:PROMPT + W + K], PROMPT + W)
+    launches = model.last_eval_stats()[1]
+    barrier()
+    dev_ms = max_over_ranks(dev_ms)
+
+    # ---- the same K steps end to end: host token in, host logits out (pinned), each call synchronous
+    barrier()
+    t1 = time.perf_counter()
+    for i in range(K):
+        p = PROMPT + W + i
+        model.eval(toks[p:p + 1], p, out=logits)
+    e2e_s = max_over_ranks(time.perf_counter() - t1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        model.close()
+        return
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    micro_ms = microbench_matvec(e, local) if spec.layout != "f16" else None
+    step_bytes = model.weight_bytes + model.kv_bytes_per_token * (PROMPT + W + K / 2.0)
+    tok_s = n_gpus * K / (dev_ms / 1000.0)
+    out = {
+        "metric": f"{spec.name} decode tok/s (batch 1, after pp{PROMPT})", "value": tok_s, "unit": "tok/s",
+        "n_gpus": n_gpus, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 limbs x quantized ints -> int32, fp32 scales",
+        "data": "synthetic",
+        "config": {"workload": f"{spec.name}: {spec.n_layer} layers, E{spec.n_embd} F{spec.n_ff} H{spec.n_head}/"
+                               f"{spec.n_head_kv} V{spec.n_vocab}, batch 1, pp{PROMPT} then tg{K}",
+                   "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} independent replicas",
+                   "l2": "inputs larger than L2: every step streams all weights (GBs) from HBM",
+                   "seed": SEED, "tokens": "reference LCG stream, seed 12345"},
+        "e2e": {"value": n_gpus * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8,
+                "d2h_bytes_per_step": spec.n_vocab * 4},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "prefill": {"value": n_gpus * PROMPT / pp_dev_s, "unit": "tok/s", "ms": pp_dev_s * 1000.0,
+                    "e2e_tok_s": n_gpus * PROMPT / pp_wall_s, "gpu_launches": int(pp_launches)},
+        "decode_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1000.0) / 1e9,
+                       "frac_of_measured_copy": step_bytes / (dev_ms / K / 1000.0) / 1e9 / hbm,
+                       "frac_of_8tbs": step_bytes / (dev_ms / K / 1000.0) / 1e9 / 8000.0},
+        "setup_s": {"generate": gen_s, "upload": load_s},
+    }
+    if micro_ms is not None:
+        ach = MICRO_BYTES / (micro_ms / 1000.0) / 1e9
+        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv<Q4_K> 2560x9728, 4 limbs", "achieved": ach, "peak": hbm,
+                           "unit": "GB/s", "frac": ach / hbm, "peak_kind": peak_kind, "frac_of_8tbs": ach / 8000.0,
+                           "us_per_launch": micro_ms * 1000.0, "traffic": None}
+    model.close()
+    if n_gpus == 1 and not args.no_cpu_baseline:
+        base, _, _ = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)
+        out["cpu_baseline"] = base
+    print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

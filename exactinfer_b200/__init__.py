@@ -178,6 +178,14 @@ class Backend:
                                    logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
+    def eval_steps(self, tokens, pos0: int) -> float:
+        """Single-token steps back to back, logits left on the device; returns the device time in ms."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        ms = C.c_float()
+        check(lib().elb_model_eval_steps(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), tokens.size, pos0,
+                                         C.byref(ms)))
+        return ms.value
+
     def last_eval_stats(self):
         ms, n = C.c_float(), C.c_int64()
         check(lib().elb_model_last_eval_stats(self._h, C.byref(ms), C.byref(n)))

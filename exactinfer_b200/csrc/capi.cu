@@ -254,6 +254,9 @@ void elb_model_destroy(elb_model* m) { model_destroy(M(m)); }
 int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits) {
     return model_eval(M(m), tokens, n, pos0, logits);
 }
+int elb_model_eval_steps(elb_model* m, const int32_t* tokens, int n, int pos0, float* device_ms) {
+    return model_eval_steps(M(m), tokens, n, pos0, device_ms);
+}
 int elb_model_last_eval_stats(const elb_model* m, float* device_ms, int64_t* kernel_launches) {
     return model_stats(M(m), device_ms, kernel_launches);
 }

@@ -219,6 +219,7 @@ int model_set_tensor(Model* m, int role, int layer, int type, int64_t rows, int6
 int model_finalize(Model* m);
 void model_destroy(Model* m);
 int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits);
+int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* device_ms);
 int model_stats(const Model* m, float* ms, int64_t* launches);
 int model_hidden(Model* m, float* out);
 size_t model_weight_bytes(const Model* m);

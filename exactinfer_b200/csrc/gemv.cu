@@ -11,6 +11,7 @@
 // where a row tile is shared by several CTAs, in a scratch buffer summed by the last CTA to arrive (fixed CTA order):
 // results are deterministic and need no floating-point atomics.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -41,30 +42,44 @@ template <> struct Unit<ELB_Q4_K> { uint4 h0, h1, q[4]; };
 template <> struct Unit<ELB_Q6_K> { uint32_t dd; uint4 s0, s1, ql[4]; uint2 qh[4]; };
 template <> struct Unit<ELB_Q8_0> { uint2 d0, d1; uint4 q[4]; };
 
+// A unit travels HBM -> shared memory with cp.async (a per-warp ring, so that several units per warp are in flight
+// without holding registers), then shared memory -> registers right before it is used. The image in shared memory
+// is byte for byte the unit in the tiled layout.
+__device__ __forceinline__ void issue_unit(uint8_t* slot, const uint8_t* src, int unit_bytes, int lane) {
+    const unsigned dst = unsigned(__cvta_generic_to_shared(slot));
+    for (int o = lane * 16; o < unit_bytes; o += 512)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src + o));
+}
+__device__ __forceinline__ void ring_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void ring_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint4 lds4(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint2 lds2(const uint8_t* p) { return *reinterpret_cast<const uint2*>(p); }
+
 __device__ __forceinline__ void load_unit(Unit<ELB_Q4_K>& u, const uint8_t* base, int lane) {
     const int g = lane >> 2;
-    u.h0 = ldg_stream(base + g * 32);
-    u.h1 = ldg_stream(base + g * 32 + 16);
+    u.h0 = lds4(base + g * 32);
+    u.h1 = lds4(base + g * 32 + 16);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) u.q[j] = ldg_stream(base + 256 + j * 512 + lane * 16);
+    for (int j = 0; j < 4; ++j) u.q[j] = lds4(base + 256 + j * 512 + lane * 16);
 }
 __device__ __forceinline__ void load_unit(Unit<ELB_Q6_K>& u, const uint8_t* base, int lane) {
     const int g = lane >> 2;
-    u.dd = __ldg(reinterpret_cast<const uint32_t*>(base + g * 4));
-    u.s0 = ldg_stream(base + 32 + g * 32);
-    u.s1 = ldg_stream(base + 32 + g * 32 + 16);
+    u.dd = *reinterpret_cast<const uint32_t*>(base + g * 4);
+    u.s0 = lds4(base + 32 + g * 32);
+    u.s1 = lds4(base + 32 + g * 32 + 16);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        u.ql[c] = ldg_stream(base + 288 + c * 512 + lane * 16);
-        u.qh[c] = ldg_stream2(base + 2336 + c * 256 + lane * 8);
+        u.ql[c] = lds4(base + 288 + c * 512 + lane * 16);
+        u.qh[c] = lds2(base + 2336 + c * 256 + lane * 8);
     }
 }
 __device__ __forceinline__ void load_unit(Unit<ELB_Q8_0>& u, const uint8_t* base, int lane) {
     const int g = lane >> 2;
-    u.d0 = ldg_stream2(base + g * 16);
-    u.d1 = ldg_stream2(base + g * 16 + 8);
+    u.d0 = lds2(base + g * 16);
+    u.d1 = lds2(base + g * 16 + 8);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) u.q[i] = ldg_stream(base + 128 + i * 512 + lane * 16);
+    for (int i = 0; i < 4; ++i) u.q[i] = lds4(base + 128 + i * 512 + lane * 16);
 }
 
 __device__ __forceinline__ uint32_t sel4(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
@@ -273,39 +288,105 @@ __device__ __forceinline__ double block_sum(double v, double* red, int tid) {
     return s;
 }
 
-// value the matvec multiplies: x itself, or RMSNorm(x) * w with the reference's operation order
-// (sum of squares in double, one float reciprocal, (x*inv)*w; src/ops.cpp:155-160 of the reference)
-__device__ __forceinline__ float pro_value(const GemvParams& p, int i, float inv) {
-    const float v = p.x[i];
-    return p.prologue == PRO_RMSNORM ? __fmul_rn(__fmul_rn(v, inv), p.norm_w[i]) : v;
+// four consecutive fixed-point values -> one packed word of each of the 4 limbs (k_split8 digit extraction)
+__device__ __forceinline__ void split4(const float4& f, int k, int8_t* lim, int n_pad, int idx) {
+    int v[4] = {__float2int_rn(ldexpf(f.x, k)), __float2int_rn(ldexpf(f.y, k)), __float2int_rn(ldexpf(f.z, k)),
+                __float2int_rn(ldexpf(f.w, k))};
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int a = l < 3 ? ((v[q] + 128) & 255) - 128 : v[q];
+            word |= uint32_t(a & 255) << (8 * q);
+            v[q] = (v[q] - a) >> 8;
+        }
+        *reinterpret_cast<uint32_t*>(lim + l * n_pad + idx) = word;
+    }
 }
 
-// Returns inv_scale = 2^-k. lim: [4][n_pad] int8. Limbs beyond nl come out zero because |X| < 2^(8 nl - 2).
+constexpr int PRO_V4 = 10;  // float4 per thread kept in registers: rows of up to 10240 values need one pass over x
+
+// x (or RMSNorm(x)*w) -> limbs in shared memory. Returns inv_scale = 2^-k. lim: [4][n_pad] int8; limbs beyond nl come
+// out zero because |X| < 2^(8 nl - 2). All loads of a pass are issued before the first use, so a pass costs about one
+// memory round trip.
 template <int TYPE>
 __device__ float prologue(const GemvParams& p, int8_t* lim, int n_pad, int8_t* sd, void* red) {
     const int tid = threadIdx.x, n = p.n;
-    float inv = 1.0f;
-    if (p.prologue == PRO_RMSNORM) {
-        double ss = 0.0;
-        for (int i = tid; i < n; i += GEMV_THREADS) { const double v = p.x[i]; ss += v * v; }
-        ss = block_sum(ss, static_cast<double*>(red), tid);
-        inv = float(1.0 / sqrt(ss / n + double(p.eps)));
-    }
-    float m = 0.f;
-    for (int i = tid; i < n; i += GEMV_THREADS) m = fmaxf(m, fabsf(pro_value(p, i, inv)));
-    m = block_max(m, static_cast<float*>(red), tid);
-    int e = 0;
-    if (m > 0.f) frexpf(m, &e);
-    const int k = m > 0.f ? 8 * p.nl - 2 - e : 0;
-    for (int i = tid; i < n; i += GEMV_THREADS) {
-        int v = __float2int_rn(ldexpf(pro_value(p, i, inv), k));
+    const bool norm = p.prologue == PRO_RMSNORM;
+    int k = 0;
+    if (n <= PRO_V4 * 4 * GEMV_THREADS) {
+        float4 v[PRO_V4];
 #pragma unroll
-        for (int l = 0; l < 3; ++l) {
-            const int a = ((v + 128) & 255) - 128;
-            lim[l * n_pad + i] = int8_t(a);
-            v = (v - a) >> 8;
+        for (int j = 0; j < PRO_V4; ++j) {
+            const int idx = (j * GEMV_THREADS + tid) * 4;
+            v[j] = idx < n ? *reinterpret_cast<const float4*>(p.x + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        lim[3 * n_pad + i] = int8_t(v);
+        if (norm) {  // sum of squares in double, one float reciprocal, (x*inv)*w (src/ops.cpp:155-160 of the reference)
+            float4 w[PRO_V4];
+#pragma unroll
+            for (int j = 0; j < PRO_V4; ++j) {
+                const int idx = (j * GEMV_THREADS + tid) * 4;
+                w[j] = idx < n ? *reinterpret_cast<const float4*>(p.norm_w + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            double ss = 0.0;
+#pragma unroll
+            for (int j = 0; j < PRO_V4; ++j)
+                ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
+            ss = block_sum(ss, static_cast<double*>(red), tid);
+            const float inv = float(1.0 / sqrt(ss / n + double(p.eps)));
+#pragma unroll
+            for (int j = 0; j < PRO_V4; ++j) {
+                v[j].x = __fmul_rn(__fmul_rn(v[j].x, inv), w[j].x);
+                v[j].y = __fmul_rn(__fmul_rn(v[j].y, inv), w[j].y);
+                v[j].z = __fmul_rn(__fmul_rn(v[j].z, inv), w[j].z);
+                v[j].w = __fmul_rn(__fmul_rn(v[j].w, inv), w[j].w);
+            }
+        }
+        float m = 0.f;
+#pragma unroll
+        for (int j = 0; j < PRO_V4; ++j)
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+        m = block_max(m, static_cast<float*>(red), tid);
+        int e = 0;
+        if (m > 0.f) frexpf(m, &e);
+        k = m > 0.f ? 8 * p.nl - 2 - e : 0;
+#pragma unroll
+        for (int j = 0; j < PRO_V4; ++j) {
+            const int idx = (j * GEMV_THREADS + tid) * 4;
+            if (idx < n) split4(v[j], k, lim, n_pad, idx);
+        }
+    } else {  // long rows: two passes, the second one served by L1
+        float inv = 1.0f;
+        if (norm) {
+            double ss = 0.0;
+            for (int i = tid; i < n; i += GEMV_THREADS) { const double v = p.x[i]; ss += v * v; }
+            ss = block_sum(ss, static_cast<double*>(red), tid);
+            inv = float(1.0 / sqrt(ss / n + double(p.eps)));
+        }
+        float m = 0.f;
+        for (int i = tid * 4; i < n; i += GEMV_THREADS * 4) {
+            float4 f = *reinterpret_cast<const float4*>(p.x + i);
+            if (norm) {
+                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + i);
+                f = make_float4(__fmul_rn(__fmul_rn(f.x, inv), w.x), __fmul_rn(__fmul_rn(f.y, inv), w.y),
+                                __fmul_rn(__fmul_rn(f.z, inv), w.z), __fmul_rn(__fmul_rn(f.w, inv), w.w));
+            }
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        }
+        m = block_max(m, static_cast<float*>(red), tid);
+        int e = 0;
+        if (m > 0.f) frexpf(m, &e);
+        k = m > 0.f ? 8 * p.nl - 2 - e : 0;
+        for (int i = tid * 4; i < n; i += GEMV_THREADS * 4) {
+            float4 f = *reinterpret_cast<const float4*>(p.x + i);
+            if (norm) {
+                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + i);
+                f = make_float4(__fmul_rn(__fmul_rn(f.x, inv), w.x), __fmul_rn(__fmul_rn(f.y, inv), w.y),
+                                __fmul_rn(__fmul_rn(f.z, inv), w.z), __fmul_rn(__fmul_rn(f.w, inv), w.w));
+            }
+            split4(f, k, lim, n_pad, i);
+        }
     }
     __syncthreads();
     if (TYPE == ELB_Q4_K || TYPE == ELB_Q6_K) {
@@ -350,7 +431,7 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, int64_t X, int g, 
 
 __host__ __device__ __forceinline__ int64_t range_lo(int64_t total, int64_t parts, int64_t i) { return total * i / parts; }
 
-template <int TYPE, bool DBG>
+template <int TYPE, bool DBG, int DEPTH>
 __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -360,6 +441,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
     int8_t* lim = reinterpret_cast<int8_t*>(smem);
     int8_t* sd = lim + 4 * n_pad;
     float* red = reinterpret_cast<float*>(sd + ((p.n / QK_K) * SD_PER_BLK + 15) / 16 * 16);  // [warps][slots][16]
+    uint8_t* ring = reinterpret_cast<uint8_t*>(red + GEMV_WARPS * p.slots * 16) + size_t(warp) * DEPTH * UNIT_BYTES;
     __shared__ double red8[GEMV_WARPS];
     __shared__ int s_last[2];
 
@@ -367,23 +449,37 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
     const int64_t cA = range_lo(U, G, c), cB = range_lo(U, G, c + 1);
     const int64_t wA = cA + range_lo(cB - cA, GEMV_WARPS, warp), wB = cA + range_lo(cB - cA, GEMV_WARPS, warp + 1);
 
-    // weights do not depend on the previous kernel: start streaming before waiting for it
-    Unit<TYPE> cur, nxt;
-    if (wA < wB) load_unit(cur, p.W + wA * UNIT_BYTES, lane);
+    // weights do not depend on the previous kernel: fill the ring before waiting for it. One commit group per unit,
+    // empty groups included, so that "all but the newest DEPTH-1 groups" always means "the unit about to be used".
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) {
+        if (wA + d < wB) issue_unit(ring + d * UNIT_BYTES, p.W + (wA + d) * UNIT_BYTES, UNIT_BYTES, lane);
+        ring_commit();
+    }
     pdl_launch_dependents();
     pdl_wait();
     const float inv_scale = prologue<TYPE>(p, lim, n_pad, sd, red8);
 
     Acc a{{0.f, 0.f}, {0.f, 0.f}};
-    int slot = 0;
+    int slot = 0, rs = 0;  // rs: ring slot of the unit in hand
     const float wt = t < 2 ? (t & 1 ? 65536.0f : 1.0f) : 0.0f;
     const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
     for (int64_t u = wA; u < wB; ++u) {
-        if (u + 1 < wB) load_unit(nxt, p.W + (u + 1) * UNIT_BYTES, lane);
+        {   // refill the slot that the previous iteration finished reading
+            const int fs = rs == 0 ? DEPTH - 1 : rs - 1;
+            if (u + DEPTH - 1 < wB) issue_unit(ring + fs * UNIT_BYTES, p.W + (u + DEPTH - 1) * UNIT_BYTES, UNIT_BYTES, lane);
+            ring_commit();
+        }
+        ring_wait<DEPTH - 1>();
+        __syncwarp();
+        Unit<TYPE> cur;
+        load_unit(cur, ring + rs * UNIT_BYTES, lane);
+        rs = rs + 1 == DEPTH ? 0 : rs + 1;
         const int64_t X = u / p.upt;
         const int b = int(u - X * p.upt);
         DbgOut dbg{p.dbgP, p.dbgI, p.dbgJ, 16 * X + g, p.rows, p.n / (TYPE == ELB_Q6_K ? 16 : 32), p.n / (TYPE == ELB_Q8_0 ? 32 : QK_K)};
         compute_unit<DBG>(cur, b, lim, n_pad, sd, lane, a, dbg);
+        __syncwarp();  // every lane has its registers before the slot is refilled
         if (u + 1 == wB || (u + 1) / p.upt != X) {  // tile finished for this warp: row sums over the 4 lanes of a row
             float v0 = a.acc[0] * wt - a.accm[0] * wtm, v1 = a.acc[1] * wt - a.accm[1] * wtm;
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
@@ -397,8 +493,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
             ++slot;
             a = Acc{{0.f, 0.f}, {0.f, 0.f}};
         }
-        cur = nxt;
     }
+    ring_wait<0>();
     __syncthreads();
     if (cA >= cB) return;
 
@@ -587,28 +683,46 @@ int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s) {
     const int nl = a.nl == 0 ? 4 : a.nl;
     if (nl < 2 || nl > 4) return fail(ELB_ERR_INVALID, "matvec: limb count must be 2, 3 or 4");
     const int64_t U = w->tiles * w->units_per_tile;
-    const int grid = int(std::min<int64_t>(U, w->max_grid));
+    // Grid: one CTA per row tile while the tiles fit in one resident wave (no tile is shared between CTAs then);
+    // otherwise, and for matrices with fewer tiles than SMs, equal contiguous unit ranges (tiles on CTA borders are
+    // finished through the scratch buffer).
+    static const int grid_override = [] { const char* v = std::getenv("ELB_GEMV_GRID"); return v ? std::atoi(v) : 0; }();
+    int64_t grid64 = w->tiles >= di.sm_count && w->tiles <= w->max_grid ? w->tiles
+                     : w->tiles < di.sm_count                            ? std::min<int64_t>(U, di.sm_count)
+                                                                         : std::min<int64_t>(U, w->max_grid);
+    if (grid_override > 0) grid64 = std::min<int64_t>({U, int64_t(grid_override), int64_t(w->max_grid)});
+    const int grid = int(grid64);
     const int64_t per_cta = (U + grid - 1) / grid, per_warp = (per_cta + GEMV_WARPS - 1) / GEMV_WARPS;
     const int slots = int((per_warp + w->units_per_tile - 1) / w->units_per_tile + 2);
     const int sd_per_blk = w->type == ELB_Q4_K ? 64 : w->type == ELB_Q6_K ? 128 : 0;
-    const size_t smem = size_t(4) * (w->n + LIMB_PAD) + (size_t(w->n / QK_K) * sd_per_blk + 15) / 16 * 16 +
-                        size_t(GEMV_WARPS) * slots * 16 * sizeof(float);
-    if (smem > di.smem_optin) return fail(ELB_ERR_UNSUPPORTED, "matvec: row too long for shared memory");
+    const size_t fixed = size_t(4) * (w->n + LIMB_PAD) + (size_t(w->n / QK_K) * sd_per_blk + 15) / 16 * 16 +
+                         size_t(GEMV_WARPS) * slots * 16 * sizeof(float);
+    // ring depth: as deep as two resident CTAs per SM allow (at most 4 units per warp), else one CTA per SM
+    const size_t per_depth = size_t(GEMV_WARPS) * w->unit_bytes, two_cta_budget = (di.smem_optin + 1024) / 2 - 1024;
+    static const int depth_override = [] { const char* v = std::getenv("ELB_GEMV_DEPTH"); return v ? std::atoi(v) : 0; }();
+    int depth = fixed < two_cta_budget ? int((two_cta_budget - fixed) / per_depth) : 0;
+    if (depth < 2) depth = fixed < di.smem_optin ? int((di.smem_optin - fixed) / per_depth) : 0;
+    if (depth < 2) return fail(ELB_ERR_UNSUPPORTED, "matvec: row too long for shared memory");
+    depth = std::min(depth, 4);
+    if (depth_override >= 2 && depth_override <= 4 && fixed + depth_override * per_depth <= di.smem_optin) depth = depth_override;
+    const bool dbg = a.dbgP || a.dbgI || a.dbgJ;
+    if (dbg) depth = 2;
+    const size_t smem = fixed + depth * per_depth;
     GemvParams p{w->tiled, w->tiles, w->units_per_tile, w->rows, int(w->n), a.x, a.norm_w, a.eps, a.y, a.resid,
                  w->part, w->counters, nl, a.prologue, a.epilogue, slots, a.dbgP, a.dbgI, a.dbgJ};
-    const bool dbg = a.dbgP || a.dbgI || a.dbgJ;
+#define ELB_GEMV_CASE(T)                                                                        \
+    case T:                                                                                     \
+        if (dbg) return launch(k_gemv<T, true, 2>, grid, smem, a.pdl, s, p);                     \
+        if (depth == 2) return launch(k_gemv<T, false, 2>, grid, smem, a.pdl, s, p);             \
+        if (depth == 3) return launch(k_gemv<T, false, 3>, grid, smem, a.pdl, s, p);             \
+        return launch(k_gemv<T, false, 4>, grid, smem, a.pdl, s, p);
     switch (w->type) {
-        case ELB_Q4_K:
-            return dbg ? launch(k_gemv<ELB_Q4_K, true>, grid, smem, a.pdl, s, p)
-                       : launch(k_gemv<ELB_Q4_K, false>, grid, smem, a.pdl, s, p);
-        case ELB_Q6_K:
-            return dbg ? launch(k_gemv<ELB_Q6_K, true>, grid, smem, a.pdl, s, p)
-                       : launch(k_gemv<ELB_Q6_K, false>, grid, smem, a.pdl, s, p);
-        case ELB_Q8_0:
-            return dbg ? launch(k_gemv<ELB_Q8_0, true>, grid, smem, a.pdl, s, p)
-                       : launch(k_gemv<ELB_Q8_0, false>, grid, smem, a.pdl, s, p);
+        ELB_GEMV_CASE(ELB_Q4_K)
+        ELB_GEMV_CASE(ELB_Q6_K)
+        ELB_GEMV_CASE(ELB_Q8_0)
         default: return fail(ELB_ERR_UNSUPPORTED, "matvec: unsupported weight type");
     }
+#undef ELB_GEMV_CASE
 }
 
 }  // namespace elb

@@ -216,6 +216,29 @@ int body_decode(Model* m) {
     return head_logits(m, m->x);
 }
 
+// Enqueue one single-token step on the model's stream (token id and position already on the device). The first
+// step runs eagerly (it also sets the kernels' launch attributes), the second is captured, later ones replay the graph.
+int enqueue_decode_step(Model* m) {
+    if (!m->use_graph || m->decode_calls++ == 0) return body_decode(m);
+    if (!m->graph) {
+        cudaGraph_t g = nullptr;
+        ELB_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        const int64_t before = m->launches;
+        const int rc = body_decode(m);
+        m->graph_launches_ = m->launches - before;
+        m->launches = before;
+        const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+        if (rc != ELB_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        ELB_CUDA(e);
+        const cudaError_t ei = cudaGraphInstantiate(&m->graph, g, 0);
+        cudaGraphDestroy(g);
+        ELB_CUDA(ei);
+    }
+    ELB_CUDA(cudaGraphLaunch(m->graph, m->stream));
+    m->launches += m->graph_launches_;
+    return ELB_OK;
+}
+
 int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
     std::memcpy(m->tokens_host, tokens, size_t(B) * sizeof(int32_t));
     *m->pos_host = pos0;
@@ -224,28 +247,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
     ELB_CUDA(cudaEventRecord(m->ev0, m->stream));
     m->last_rows = B;
     if (B == 1) {
-        // the first single-token step runs eagerly (it also sets the kernels' launch attributes); the second one is
-        // captured, later ones replay the graph
-        if (m->use_graph && m->decode_calls++ > 0) {
-            if (!m->graph) {
-                cudaGraph_t g = nullptr;
-                ELB_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-                const int64_t before = m->launches;
-                const int rc = body_decode(m);
-                m->graph_launches_ = m->launches - before;
-                const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
-                if (rc != ELB_OK) { if (g) cudaGraphDestroy(g); return rc; }
-                ELB_CUDA(e);
-                const cudaError_t ei = cudaGraphInstantiate(&m->graph, g, 0);
-                cudaGraphDestroy(g);
-                ELB_CUDA(ei);
-                m->launches = before;
-            }
-            ELB_CUDA(cudaGraphLaunch(m->graph, m->stream));
-            m->launches += m->graph_launches_;
-        } else {
-            ELB_TRY(body_decode(m));
-        }
+        ELB_TRY(enqueue_decode_step(m));
     } else {
         ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, B, m->x, m->stream));
         ++m->launches;
@@ -459,6 +461,39 @@ int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits) 
         done += b;
     }
     m->last_launches = m->launches - before;
+    return ELB_OK;
+}
+
+// n single-token steps at positions pos0.. enqueued back to back without reading logits back (the tg loop of the
+// reference's bench command, src/main.cpp:639, minus its per-token host round trip); device time of the whole run.
+int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* device_ms) {
+    if (!m || !tokens || !device_ms) return fail(ELB_ERR_INVALID, "eval_steps: null argument");
+    if (!m->finalized) return fail(ELB_ERR_STATE, "eval_steps: model not finalized");
+    if (n <= 0) return fail(ELB_ERR_INVALID, "eval_steps: empty token sequence");
+    if (pos0 < 0 || int64_t(pos0) + n > m->n_ctx) return fail(ELB_ERR_RANGE, "eval_steps: context window full");
+    for (int i = 0; i < n; ++i)
+        if (tokens[i] < 0 || tokens[i] >= m->cfg.n_vocab) return fail(ELB_ERR_RANGE, "eval_steps: token id out of range");
+    ELB_CUDA(cudaSetDevice(m->device));
+    int32_t* pin = nullptr;  // [n] tokens then [n] positions, pinned so that the copies stay asynchronous
+    ELB_CUDA(cudaMallocHost(&pin, size_t(2) * n * sizeof(int32_t)));
+    for (int i = 0; i < n; ++i) { pin[i] = tokens[i]; pin[n + i] = pos0 + i; }
+    const int64_t before = m->launches;
+    int rc = ELB_OK;
+    cudaEventRecord(m->ev0, m->stream);
+    for (int i = 0; i < n && rc == ELB_OK; ++i) {
+        cudaMemcpyAsync(m->tokens_dev, pin + i, sizeof(int32_t), cudaMemcpyHostToDevice, m->stream);
+        cudaMemcpyAsync(m->pos_dev, pin + n + i, sizeof(int), cudaMemcpyHostToDevice, m->stream);
+        rc = enqueue_decode_step(m);
+    }
+    cudaEventRecord(m->ev1, m->stream);
+    const cudaError_t e = cudaStreamSynchronize(m->stream);
+    cudaFreeHost(pin);
+    if (rc != ELB_OK) return rc;
+    ELB_CUDA(e);
+    ELB_CUDA(cudaEventElapsedTime(device_ms, m->ev0, m->ev1));
+    m->last_ms = *device_ms;
+    m->last_launches = m->launches - before;
+    m->last_rows = 1;
     return ELB_OK;
 }
 

@@ -126,6 +126,11 @@ void elb_model_destroy(elb_model* m);
  * n <= 0 -> ELB_ERR_INVALID; pos0 < 0, pos0+n > n_ctx or a token outside [0, n_vocab) -> ELB_ERR_RANGE. */
 int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits);
 
+/* n single-token steps at positions pos0.., enqueued back to back without reading logits back (the tg loop of the
+ * reference's bench command, src/main.cpp:639, without its per-token host round trip). device_ms receives the device
+ * time of the whole run (CUDA events on the model's stream). Same argument checks as elb_model_eval. */
+int elb_model_eval_steps(elb_model* m, const int32_t* tokens, int n, int pos0, float* device_ms);
+
 /* Same step, measured: device time in milliseconds of the last elb_model_eval (CUDA events on the model's own
  * stream, host<->device copies excluded), and the number of this library's kernels that call launched. */
 int elb_model_last_eval_stats(const elb_model* m, float* device_ms, int64_t* kernel_launches);

@@ -20,7 +20,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 import oracle_lib as ol  # noqa: E402
 from exactinfer_b200 import synth  # noqa: E402
 
-TINY = dict(name="tiny", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640)
+TINY = dict(name="tiny", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640, head_sigma=2e-5)
 
 
 def weights_digest(tensors):

@@ -1,0 +1,147 @@
+"""GPU parity of the whole forward pass (Backend.eval through the C ABI) against the CPU oracle's restated
+CpuModel on the same seeded synthetic weights: prompt chunk, then single-token steps (the captured decode graph).
+
+Bars (written here): max |delta logprob| <= 3e-5 over the generated tokens (double-precision log-softmax as in the
+reference's generate command), logits and the residual stream within 2e-4 of the oracle relative to their largest
+magnitude (errors of the order of fp32 rounding compound over the layers), and the golden logits of the reference's own
+CPU build within the same bar.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from exactinfer_b200 import synth
+
+pytestmark = pytest.mark.gpu
+LOGPROB_TOL = 3e-5
+REL_TOL = 2e-4
+
+
+@pytest.fixture(scope="module")
+def elb():
+    import exactinfer_b200 as e
+    ok, why = e.cuda_available()
+    assert ok, f"CUDA path unavailable: {why}"
+    return e
+
+
+def logprobs(logits):
+    return logits.astype(np.float64) - ol.logsumexp(logits)
+
+
+def rel(a, b):
+    return float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max() / max(np.abs(b).max(), 1e-30))
+
+
+def run_pair(elb, spec, seed, n_prompt, n_decode, max_batch=0):
+    tens = list(synth.generate(spec, seed))
+    n_ctx = n_prompt + n_decode + 1
+    gpu = elb.Backend(spec, tens, n_ctx, max_batch=max_batch)
+    cpu = ol.OracleModel(spec, tens, n_ctx)
+    toks = synth.lcg_tokens(n_prompt, spec.n_vocab)
+    lg, lc = gpu.eval(toks, 0), cpu.eval(toks, 0)
+    worst_lp, worst_rel = 0.0, rel(lg, lc)
+    assert rel(gpu.hidden(), cpu.hidden()) <= REL_TOL
+    pos = n_prompt
+    for _ in range(n_decode):
+        nxt = int(np.argmax(lc))  # teacher-forced on the oracle's greedy token
+        pg, pc = logprobs(lg), logprobs(lc)
+        worst_lp = max(worst_lp, abs(pg[nxt] - pc[nxt]))
+        top = np.argsort(lc)[-8:]
+        worst_lp = max(worst_lp, float(np.abs(pg[top] - pc[top]).max()))
+        lg, lc = gpu.eval([nxt], pos), cpu.eval([nxt], pos)
+        worst_rel = max(worst_rel, rel(lg, lc))
+        pos += 1
+    gpu.close()
+    cpu.close()
+    return worst_lp, worst_rel
+
+
+@pytest.mark.parametrize("layout", ("q4_k_m", "q8_0", "f16", "q6_k"))
+def test_small_model_prefill_and_decode(elb, layout):
+    spec = synth.Spec(name="small", n_layer=3, n_embd=512, n_ff=1024, n_head=8, n_head_kv=2, n_vocab=2048, layout=layout,
+                      head_sigma=2e-5)
+    lp, r = run_pair(elb, spec, seed=21, n_prompt=40, n_decode=6)
+    assert lp <= LOGPROB_TOL, lp
+    assert r <= REL_TOL, r
+
+
+def test_chunked_prompt_equals_oracle(elb):
+    """A prompt longer than the chunk length goes through several chunks (eval's internal chunking)."""
+    spec = synth.Spec(name="small", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640, layout="q4_k_m",
+                      head_sigma=2e-5)
+    lp, r = run_pair(elb, spec, seed=5, n_prompt=75, n_decode=3, max_batch=32)
+    assert lp <= LOGPROB_TOL and r <= REL_TOL, (lp, r)
+
+
+def test_wide_group_and_odd_shapes(elb):
+    """8 query heads per KV head (the 32B grouping) and a vocabulary that is not a multiple of 16."""
+    spec = synth.Spec(name="wide", n_layer=2, n_embd=1024, n_ff=768, n_head=8, n_head_kv=1, n_vocab=1003, layout="q4_k_m",
+                      head_sigma=2e-5)
+    lp, r = run_pair(elb, spec, seed=9, n_prompt=33, n_decode=4)
+    assert lp <= LOGPROB_TOL and r <= REL_TOL, (lp, r)
+
+
+@pytest.mark.parametrize("layout", ("f16", "q8_0", "q4_k_m"))
+def test_golden_logits_of_reference_build(elb, golden_dir, layout):
+    g = np.load(os.path.join(golden_dir, "tiny_model.npz"))
+    spec = synth.Spec(name="tiny", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640, layout=layout,
+                      head_sigma=2e-5)
+    m = elb.Backend(spec, list(synth.generate(spec, seed=11)), 32)
+    toks = g["tokens"]
+    outs = [m.eval(toks[:8], 0)]
+    for i in range(8, 12):
+        outs.append(m.eval(toks[i:i + 1], i))
+    want = g[f"{layout}_logits"]
+    for a, b in zip(outs, want):
+        assert rel(a, b) <= REL_TOL
+        assert np.abs(logprobs(a) - logprobs(b))[np.argsort(b)[-8:]].max() <= LOGPROB_TOL
+
+
+def test_decode_only_from_position_zero_and_prefix_rewrite(elb):
+    """Single-token evals from position 0, then re-evaluating a suffix (the serve loop's prefix reuse relies on eval
+    touching only the KV rows it is given)."""
+    spec = synth.Spec(name="small", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640, layout="q8_0")
+    tens = list(synth.generate(spec, 13))
+    gpu, cpu = elb.Backend(spec, tens, 16), ol.OracleModel(spec, tens, 16)
+    toks = synth.lcg_tokens(10, spec.n_vocab)
+    for i in range(6):
+        lg, lc = gpu.eval(toks[i:i + 1], i), cpu.eval(toks[i:i + 1], i)
+        assert rel(lg, lc) <= REL_TOL
+    # rewind to position 3 with other tokens: rows 3.. are overwritten, rows 0..2 are reused
+    lg, lc = gpu.eval(toks[6:10], 3), cpu.eval(toks[6:10], 3)
+    assert rel(lg, lc) <= REL_TOL
+    assert gpu.eval(toks[:2], 7, want_logits=False) is None
+
+
+def test_eval_argument_errors(elb):
+    spec = synth.Spec(name="small", n_layer=1, n_embd=256, n_ff=256, n_head=2, n_head_kv=1, n_vocab=64, layout="q8_0")
+    m = elb.Backend(spec, list(synth.generate(spec, 3)), 8)
+    with pytest.raises(ValueError):
+        m.eval(np.zeros(0, np.int32), 0)
+    with pytest.raises(IndexError):
+        m.eval([64], 0)
+    with pytest.raises(IndexError):
+        m.eval([-1], 0)
+    with pytest.raises(IndexError):
+        m.eval([1, 2, 3], 6)
+    with pytest.raises(IndexError):
+        m.eval([1], -1)
+    assert m.eval([1, 2, 3], 5).shape == (64,)
+    assert m.name() == "cuda-b200" and m.n_ctx() == 8 and m.cfg().n_vocab == 64
+
+
+def test_benchmark_distribution_within_logit_resolution(elb):
+    """With the benchmark's block-scale spread (1e-3 everywhere) logits reach 10^2..10^3, where one fp32 ulp is itself
+    3e-5..6e-5: there the log-probability error is bounded by the resolution of the logits, 3e-5 + 2 ulp(max |logit|)."""
+    spec = synth.Spec(name="small", n_layer=3, n_embd=512, n_ff=1024, n_head=8, n_head_kv=2, n_vocab=2048, layout="q4_k_m")
+    tens = list(synth.generate(spec, 21))
+    gpu, cpu = elb.Backend(spec, tens, 48), ol.OracleModel(spec, tens, 48)
+    toks = synth.lcg_tokens(40, spec.n_vocab)
+    lg, lc = gpu.eval(toks, 0), cpu.eval(toks, 0)
+    tol = LOGPROB_TOL + 2 * float(np.spacing(np.float32(np.abs(lc).max())))
+    top = np.argsort(lc)[-8:]
+    assert np.abs(logprobs(lg) - logprobs(lc))[top].max() <= tol
+    assert rel(lg, lc) <= REL_TOL

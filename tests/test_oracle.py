@@ -84,7 +84,7 @@ def _digest(tensors):
 def test_tiny_model_logits_match_golden(golden_dir, layout):
     g = np.load(os.path.join(golden_dir, "tiny_model.npz"))
     spec = synth.Spec(name="tiny", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640,
-                      layout=layout)
+                      layout=layout, head_sigma=2e-5)
     tens = list(synth.generate(spec, seed=11))
     assert _digest(tens) == bytes(g[f"{layout}_sha"]).decode(), "synthetic weight generator drifted"
     toks = g["tokens"]
