@@ -10,6 +10,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "split.cuh"
 
 namespace elb {
 
@@ -57,7 +58,7 @@ __device__ __forceinline__ void head_norm_rope(const float* src, const float* w,
 
 // ---------------------------------------------------------------- decode
 
-constexpr int AD_THREADS = 256, AD_KT = 32, AD_MAXG = 8, AD_LDK = D + 1;
+constexpr int AD_THREADS = 256, AD_KT = 32, AD_MAXG = 8, AD_LDK = D + 1, AD_MAXSPLIT = 32;
 
 struct AttnDecodeParams {
     const float* qkv;  // [QD + 2 KD] of this token, q and k not yet normalised
@@ -70,6 +71,7 @@ struct AttnDecodeParams {
     unsigned* counters;  // [HKV]
     int H, HKV, rope_dim, nsplit;
     float eps, scale;
+    PostOp post;
 };
 
 __global__ void __launch_bounds__(AD_THREADS) k_attn_decode(const AttnDecodeParams p) {
@@ -80,6 +82,7 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_decode(const AttnDecodePara
     __shared__ float Ps[AD_MAXG][AD_KT];
     __shared__ float corr_s[AD_MAXG], m_s[AD_MAXG], l_s[AD_MAXG];
     __shared__ int s_last;
+    __shared__ double red8[8];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.x, split = blockIdx.y, group = p.H / p.HKV, QD = p.H * D, KD = p.HKV * D;
     pdl_launch_dependents();
@@ -163,47 +166,58 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_decode(const AttnDecodePara
             const int h = oh + 2 * i;
             if (h < group) p.att[(kvh * group + h) * D + od] = acc[i] / l_s[h];
         }
-        return;
-    }
-    // partial result of this split: [group][D] accumulators, then m and l per head
-    float* mine = p.part + (size_t(kvh) * p.nsplit + split) * group * (D + 2);
+    } else {
+        // partial result of this split: [group][D] accumulators, then m and l per head
+        float* mine = p.part + (size_t(kvh) * p.nsplit + split) * group * (D + 2);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int h = oh + 2 * i;
-        if (h < group) mine[h * (D + 2) + od] = acc[i];
-    }
-    if (tid < group) {
-        mine[tid * (D + 2) + D] = m_s[tid];
-        mine[tid * (D + 2) + D + 1] = l_s[tid];
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned old = atomicAdd(&p.counters[kvh], 1u);
-        s_last = old == unsigned(p.nsplit - 1);
-        if (s_last) p.counters[kvh] = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const float* base = p.part + size_t(kvh) * p.nsplit * group * (D + 2);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int h = oh + 2 * i;
-        if (h >= group) continue;
-        float M = -INFINITY;
-        for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, __ldcg(base + (size_t(s) * group + h) * (D + 2) + D));
-        float L = 0.f, o = 0.f;
-        for (int s = 0; s < p.nsplit; ++s) {  // fixed split order
-            const float* ps = base + (size_t(s) * group + h) * (D + 2);
-            const float ms = __ldcg(ps + D);
-            if (ms == -INFINITY) continue;
-            const float w = expf(ms - M);
-            L = fmaf(__ldcg(ps + D + 1), w, L);
-            o = fmaf(__ldcg(ps + od), w, o);
+        for (int i = 0; i < 4; ++i) {
+            const int h = oh + 2 * i;
+            if (h < group) mine[h * (D + 2) + od] = acc[i];
         }
-        p.att[(kvh * group + h) * D + od] = o / L;
+        if (tid < group) {
+            mine[tid * (D + 2) + D] = m_s[tid];
+            mine[tid * (D + 2) + D + 1] = l_s[tid];
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned old = atomicAdd(&p.counters[kvh], 1u);
+            s_last = old == unsigned(p.nsplit - 1);
+            if (s_last) p.counters[kvh] = 0;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const float* base = p.part + size_t(kvh) * p.nsplit * group * (D + 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int h = oh + 2 * i;
+                if (h >= group) continue;
+                // all loads of a pass are issued before the first use (the split count is at most AD_MAXSPLIT)
+                float ms[AD_MAXSPLIT], ls[AD_MAXSPLIT], as[AD_MAXSPLIT];
+#pragma unroll
+                for (int s = 0; s < AD_MAXSPLIT; ++s) {
+                    const float* ps = base + (size_t(s < p.nsplit ? s : 0) * group + h) * (D + 2);
+                    ms[s] = s < p.nsplit ? __ldcg(ps + D) : -INFINITY;
+                    ls[s] = __ldcg(ps + D + 1);
+                    as[s] = __ldcg(ps + od);
+                }
+                float M = -INFINITY;
+#pragma unroll
+                for (int s = 0; s < AD_MAXSPLIT; ++s) M = fmaxf(M, ms[s]);
+                float L = 0.f, o = 0.f;
+#pragma unroll
+                for (int s = 0; s < AD_MAXSPLIT; ++s) {  // fixed split order
+                    if (ms[s] == -INFINITY) continue;
+                    const float w = expf(ms[s] - M);
+                    L = fmaf(ls[s], w, L);
+                    o = fmaf(as[s], w, o);
+                }
+                p.att[(kvh * group + h) * D + od] = o / L;
+            }
+        }
     }
+    post_op(p.post, gridDim.x * gridDim.y, &s_last, red8);
 }
 
 // ---------------------------------------------------------------- prompt chunk
@@ -333,8 +347,9 @@ __global__ void __launch_bounds__(256) k_rmsnorm_rows(float* out, const float* x
 
 int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s) {
     if (a.H % a.HKV || a.H / a.HKV > AD_MAXG) return fail(ELB_ERR_UNSUPPORTED, "attention: at most 8 query heads per KV head");
+    if (a.nsplit < 1 || a.nsplit > AD_MAXSPLIT) return fail(ELB_ERR_INVALID, "attention: split count out of range");
     AttnDecodeParams p{a.qkv, a.q_norm, a.k_norm, reinterpret_cast<const float2*>(a.rope), a.pos, a.kc, a.vc, a.att, a.part,
-                       a.counters, a.H, a.HKV, a.rope_dim, a.nsplit, a.eps, a.scale};
+                       a.counters, a.H, a.HKV, a.rope_dim, a.nsplit, a.eps, a.scale, a.post};
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.HKV, a.nsplit);
     cfg.blockDim = dim3(AD_THREADS);

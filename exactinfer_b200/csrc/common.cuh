@@ -78,6 +78,9 @@ struct Weight {
     float* part = nullptr;     // [grid][2][16]
     unsigned* counters = nullptr;  // [tiles]
     int max_grid = 0;
+    // activation limbs for the operator-level entry points (the model keeps its own): [4][n] int8, then 2^-k
+    int8_t* xlimbs = nullptr;
+    float* xinv = nullptr;
 };
 
 // ---------------------------------------------------------------- device helpers
@@ -152,6 +155,15 @@ __device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t 
                  : "r"(a0), "r"(a1), "r"(b0));
 }
 
+// x * 2^k as two exact multiplications by powers of two (|k| can exceed the exponent range of one float);
+// bit-identical to ldexpf(x, k) wherever the result is a normal float or zero, which covers every value that
+// survives the rounding to an integer
+struct Pow2 { float s1, s2; };
+__device__ __forceinline__ Pow2 make_pow2(int k) {
+    const int k1 = k >> 1, k2 = k - k1;
+    return Pow2{__int_as_float((k1 + 127) << 23), __int_as_float((k2 + 127) << 23)};
+}
+
 // programmatic dependent launch: let the next kernel of the stream start its prologue / wait for the previous one
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -174,17 +186,36 @@ int launch_gather_rows(const Weight* w, const int32_t* d_tokens, int count, floa
 // with the row sums.
 enum { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SILU = 2 };
-struct GemvArgs {
-    const float* x = nullptr;       // [n] input activation (device)
-    const float* norm_w = nullptr;  // [n] RMSNorm weight (PRO_RMSNORM)
+// What a producer kernel leaves for the next matvec once its whole output is written (run by its last CTA).
+struct PostOp {
+    int kind = 0;                   // 0: nothing; 1: limbs of src (of RMSNorm(src) * norm_w when norm_w is set)
+    const float* src = nullptr;     // the producer's fp32 output vector
+    int n = 0, nl = 4;
+    const float* norm_w = nullptr;
     float eps = 0.f;
-    float* y = nullptr;             // [rows] (EPI_SILU: [rows/2])
-    const float* resid = nullptr;   // EPI_ADD: y = resid + W x (may alias y)
-    int prologue = PRO_PLAIN, epilogue = EPI_STORE;
-    int nl = 4;
-    bool pdl = false;               // launch with programmatic stream serialization
+    int8_t* limbs = nullptr;        // [4][n]
+    float* inv_scale = nullptr;     // [1]
+    unsigned* done = nullptr;       // arrival counter of the producer's CTAs (zero between launches)
+};
+struct GemvArgs {
+    const int8_t* limbs = nullptr;     // quantized weights: pre-split activation [4][n] and its 2^-k (device)
+    const float* inv_scale = nullptr;
+    const float* x = nullptr;          // F16 weights: fp32 activation [n], optionally RMSNorm'ed in the kernel
+    const float* norm_w = nullptr;
+    float eps = 0.f;
+    int prologue = PRO_PLAIN;
+    float* y = nullptr;                // [rows] (EPI_SILU: [rows/2])
+    const float* resid = nullptr;      // EPI_ADD: y = resid + W x (may alias y)
+    int epilogue = EPI_STORE;
+    bool pdl = false;                  // launch with programmatic stream serialization
+    PostOp post;
     int32_t *dbgP = nullptr, *dbgI = nullptr, *dbgJ = nullptr;  // parity dumps
 };
+int gemv_prepare(Weight* w);  // allocates the split-K scratch (once per weight)
+int prep_limbs_launch(const float* x, int n, const float* norm_w, float eps, int nl, int8_t* limbs, float* inv_scale,
+                      bool pdl, cudaStream_t s);
+int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s);
+
 // linear.cu — several tokens at once
 int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const float* d_norm_w, float eps,
                  int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s);
@@ -198,6 +229,7 @@ struct AttnDecodeArgs {
     const float* qkv; const float *q_norm, *k_norm; const float* rope; const int* pos;
     float *kc, *vc, *att, *part; unsigned* counters;
     int H, HKV, rope_dim, nsplit; float eps, scale; bool pdl;
+    PostOp post;
 };
 int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s);
 int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_norm, const float* rope, int pos0, int B,
@@ -206,8 +238,6 @@ int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const flo
                         int pos0, int B, int H, int HKV, float scale, cudaStream_t s);
 int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s);
 
-int gemv_prepare(Weight* w);  // allocates the split-K scratch (once per weight)
-int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s);
 
 }  // namespace elb
 

@@ -14,6 +14,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "split.cuh"
 
 namespace elb {
 
@@ -24,15 +25,15 @@ struct GemvParams {
     const uint8_t* W;
     int64_t tiles, upt, rows;
     int n;
-    const float* x;
-    const float* norm_w;
-    float eps;
+    const int8_t* limbs;     // [4][n] pre-split activation (global)
+    const float* inv_scale;  // [1]
     float* y;
     const float* resid;
     float* part;
     unsigned* counters;
-    int nl, prologue, epilogue, slots;
+    int epilogue, slots;
     int32_t *dbgP, *dbgI, *dbgJ;
+    PostOp post;
 };
 
 // ---------------------------------------------------------------- units: registers of one lane
@@ -114,7 +115,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
 #pragma unroll
         for (int odd = 0; odd < 2; ++odd) {
             const int sub = 2 * j + odd;
-            const uint2 bf = *reinterpret_cast<const uint2*>(lcol + sub * 32);
+            const uint2 bf = __ldg(reinterpret_cast<const uint2*>(lcol + sub * 32));
             int C[4] = {0, 0, 0, 0};
             if (odd == 0)
                 mma_u8s8_k32(C, q.x & 0x0F0F0F0Fu, q.z & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu, bf.x, bf.y);
@@ -144,7 +145,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
     // min term: J[col] = sum over the 8 sub-blocks of m * (digit `col>>2` of the limb sum S of limb `col&3`)
     const uint32_t a0 = t == 0 ? mg[0] : t == 1 ? mg[1] : 0u, a1 = t == 0 ? mh[0] : t == 1 ? mh[1] : 0u;
-    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 8 + 4 * (t & 1));
+    const uint32_t b0 = __ldg(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 8 + 4 * (t & 1)));
     int J[4] = {0, 0, 0, 0};
     mma_u8s8_k16(J, a0, a1, b0);
     const float ng = h2f_bits(u.h0.x >> 16), nh = h2f_bits(u.h1.x >> 16);
@@ -186,7 +187,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
             const uint32_t w = sel4(ql, i);
             const uint32_t a0 = (w & 0x0F0F0F0Fu) | (((qh.x >> (2 * i)) & 0x03030303u) << 4);
             const uint32_t a1 = ((w >> 4) & 0x0F0F0F0Fu) | (((qh.y >> (2 * i)) & 0x03030303u) << 4);
-            const uint32_t bf = *reinterpret_cast<const uint32_t*>(lcol + s * 16);
+            const uint32_t bf = __ldg(reinterpret_cast<const uint32_t*>(lcol + s * 16));
             int C[4] = {0, 0, 0, 0};
             mma_u8s8_k16(C, a0, a1, bf);
             const int s0 = int(int8_t(sel4(u.s0, s >> 2) >> (8 * (s & 3)))), s1 = int(int8_t(sel4(u.s1, s >> 2) >> (8 * (s & 3))));
@@ -211,7 +212,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
     const float dg = h2f_bits(u.dd & 0xFFFFu), dh = h2f_bits(u.dd >> 16);
     a.acc[0] += dg * fmaf(float(I[1]), 256.0f, float(I[0]));
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
-    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 16 + 4 * t);
+    const uint32_t b0 = __ldg(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 16 + 4 * t));
     int J[4] = {0, 0, 0, 0};
     mma_s8s8_k16(J, sel4(u.s0, t), sel4(u.s1, t), b0);
     a.accm[0] += (32.0f * dg) * fmaf(float(J[1]), 256.0f, float(J[0]));
@@ -243,7 +244,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, con
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint4 q = u.q[i];
-        const uint2 bf = *reinterpret_cast<const uint2*>(lcol + i * 32);
+        const uint2 bf = __ldg(reinterpret_cast<const uint2*>(lcol + i * 32));
         int C[4] = {0, 0, 0, 0};
         mma_s8s8_k32(C, q.x, q.z, q.y, q.w, bf.x, bf.y);
         const uint32_t d0w = i < 2 ? u.d0.x : u.d0.y, d1w = i < 2 ? u.d1.x : u.d1.y;
@@ -267,146 +268,12 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, con
 
 // ---------------------------------------------------------------- prologue: x -> limbs (+ limb sums) in shared memory
 
-__device__ __forceinline__ float block_max(float v, float* red, int tid) {
-    v = warp_max(v);
-    if ((tid & 31) == 0) red[tid >> 5] = v;
-    __syncthreads();
-    float m = red[0];
-#pragma unroll
-    for (int i = 1; i < GEMV_WARPS; ++i) m = fmaxf(m, red[i]);
-    __syncthreads();
-    return m;
-}
-__device__ __forceinline__ double block_sum(double v, double* red, int tid) {
-    v = warp_sum(v);
-    if ((tid & 31) == 0) red[tid >> 5] = v;
-    __syncthreads();
-    double s = red[0];
-#pragma unroll
-    for (int i = 1; i < GEMV_WARPS; ++i) s += red[i];
-    __syncthreads();
-    return s;
-}
-
-// four consecutive fixed-point values -> one packed word of each of the 4 limbs (k_split8 digit extraction)
-__device__ __forceinline__ void split4(const float4& f, int k, int8_t* lim, int n_pad, int idx) {
-    int v[4] = {__float2int_rn(ldexpf(f.x, k)), __float2int_rn(ldexpf(f.y, k)), __float2int_rn(ldexpf(f.z, k)),
-                __float2int_rn(ldexpf(f.w, k))};
-#pragma unroll
-    for (int l = 0; l < 4; ++l) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int a = l < 3 ? ((v[q] + 128) & 255) - 128 : v[q];
-            word |= uint32_t(a & 255) << (8 * q);
-            v[q] = (v[q] - a) >> 8;
-        }
-        *reinterpret_cast<uint32_t*>(lim + l * n_pad + idx) = word;
-    }
-}
-
-constexpr int PRO_V4 = 10;  // float4 per thread kept in registers: rows of up to 10240 values need one pass over x
-
-// x (or RMSNorm(x)*w) -> limbs in shared memory. Returns inv_scale = 2^-k. lim: [4][n_pad] int8; limbs beyond nl come
-// out zero because |X| < 2^(8 nl - 2). All loads of a pass are issued before the first use, so a pass costs about one
-// memory round trip.
-template <int TYPE>
-__device__ float prologue(const GemvParams& p, int8_t* lim, int n_pad, int8_t* sd, void* red) {
-    const int tid = threadIdx.x, n = p.n;
-    const bool norm = p.prologue == PRO_RMSNORM;
-    int k = 0;
-    if (n <= PRO_V4 * 4 * GEMV_THREADS) {
-        float4 v[PRO_V4];
-#pragma unroll
-        for (int j = 0; j < PRO_V4; ++j) {
-            const int idx = (j * GEMV_THREADS + tid) * 4;
-            v[j] = idx < n ? *reinterpret_cast<const float4*>(p.x + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        if (norm) {  // sum of squares in double, one float reciprocal, (x*inv)*w (src/ops.cpp:155-160 of the reference)
-            float4 w[PRO_V4];
-#pragma unroll
-            for (int j = 0; j < PRO_V4; ++j) {
-                const int idx = (j * GEMV_THREADS + tid) * 4;
-                w[j] = idx < n ? *reinterpret_cast<const float4*>(p.norm_w + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-            double ss = 0.0;
-#pragma unroll
-            for (int j = 0; j < PRO_V4; ++j)
-                ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
-            ss = block_sum(ss, static_cast<double*>(red), tid);
-            const float inv = float(1.0 / sqrt(ss / n + double(p.eps)));
-#pragma unroll
-            for (int j = 0; j < PRO_V4; ++j) {
-                v[j].x = __fmul_rn(__fmul_rn(v[j].x, inv), w[j].x);
-                v[j].y = __fmul_rn(__fmul_rn(v[j].y, inv), w[j].y);
-                v[j].z = __fmul_rn(__fmul_rn(v[j].z, inv), w[j].z);
-                v[j].w = __fmul_rn(__fmul_rn(v[j].w, inv), w[j].w);
-            }
-        }
-        float m = 0.f;
-#pragma unroll
-        for (int j = 0; j < PRO_V4; ++j)
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
-        m = block_max(m, static_cast<float*>(red), tid);
-        int e = 0;
-        if (m > 0.f) frexpf(m, &e);
-        k = m > 0.f ? 8 * p.nl - 2 - e : 0;
-#pragma unroll
-        for (int j = 0; j < PRO_V4; ++j) {
-            const int idx = (j * GEMV_THREADS + tid) * 4;
-            if (idx < n) split4(v[j], k, lim, n_pad, idx);
-        }
-    } else {  // long rows: two passes, the second one served by L1
-        float inv = 1.0f;
-        if (norm) {
-            double ss = 0.0;
-            for (int i = tid; i < n; i += GEMV_THREADS) { const double v = p.x[i]; ss += v * v; }
-            ss = block_sum(ss, static_cast<double*>(red), tid);
-            inv = float(1.0 / sqrt(ss / n + double(p.eps)));
-        }
-        float m = 0.f;
-        for (int i = tid * 4; i < n; i += GEMV_THREADS * 4) {
-            float4 f = *reinterpret_cast<const float4*>(p.x + i);
-            if (norm) {
-                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + i);
-                f = make_float4(__fmul_rn(__fmul_rn(f.x, inv), w.x), __fmul_rn(__fmul_rn(f.y, inv), w.y),
-                                __fmul_rn(__fmul_rn(f.z, inv), w.z), __fmul_rn(__fmul_rn(f.w, inv), w.w));
-            }
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
-        }
-        m = block_max(m, static_cast<float*>(red), tid);
-        int e = 0;
-        if (m > 0.f) frexpf(m, &e);
-        k = m > 0.f ? 8 * p.nl - 2 - e : 0;
-        for (int i = tid * 4; i < n; i += GEMV_THREADS * 4) {
-            float4 f = *reinterpret_cast<const float4*>(p.x + i);
-            if (norm) {
-                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + i);
-                f = make_float4(__fmul_rn(__fmul_rn(f.x, inv), w.x), __fmul_rn(__fmul_rn(f.y, inv), w.y),
-                                __fmul_rn(__fmul_rn(f.z, inv), w.z), __fmul_rn(__fmul_rn(f.w, inv), w.w));
-            }
-            split4(f, k, lim, n_pad, i);
-        }
-    }
-    __syncthreads();
-    if (TYPE == ELB_Q4_K || TYPE == ELB_Q6_K) {
-        // limb sums over each sub-block, as two balanced base-256 digits: sd[blk][col = limb + 4*digit][sub]
-        constexpr int SUB = TYPE == ELB_Q4_K ? 32 : 16, SPB = QK_K / SUB;
-        const int total = n / SUB * 4;
-        for (int idx = tid; idx < total; idx += GEMV_THREADS) {
-            const int l = idx & 3, s = idx >> 2;
-            const int* w = reinterpret_cast<const int*>(lim + l * n_pad + s * SUB);
-            int S = 0;
-#pragma unroll
-            for (int q = 0; q < SUB / 4; ++q) S = __dp4a(w[q], 0x01010101, S);
-            const int lo = ((S + 128) & 255) - 128, hi = (S - lo) >> 8;
-            const int blk = s / SPB, si = s % SPB;
-            sd[(blk * 8 + l) * SPB + si] = int8_t(lo);
-            sd[(blk * 8 + 4 + l) * SPB + si] = int8_t(hi);
-        }
-        __syncthreads();
-    }
-    return ldexpf(1.0f, -k);
+// The split activation (limbs and their sub-block sums, layout in split.cuh) is read straight from global memory
+// through L1: every SM touches the same few tens of KB, so after a first sweep the B-fragments are L1 hits and no
+// shared memory, copy phase or block barrier stands between a warp and its first MMA. This warms L1 up.
+__device__ __forceinline__ void prefetch_act(const int8_t* act, int n) {
+    const int lines = int((act_bytes(n) + 127) / 128);
+    for (int i = threadIdx.x; i < lines; i += GEMV_THREADS) asm volatile("prefetch.global.L1 [%0];" ::"l"(act + size_t(i) * 128));
 }
 
 // ---------------------------------------------------------------- epilogue for rows g / g+8 of tile X
@@ -429,45 +296,49 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, int64_t X, int g, 
 
 // ---------------------------------------------------------------- the kernel
 
-__host__ __device__ __forceinline__ int64_t range_lo(int64_t total, int64_t parts, int64_t i) { return total * i / parts; }
+// start of part i when `total` items are cut into `parts` contiguous ranges (total * parts < 2^31, checked on the host)
+__host__ __device__ __forceinline__ int range_lo(int total, int parts, int i) { return int(unsigned(total) * unsigned(i) / unsigned(parts)); }
 
 template <int TYPE, bool DBG, int DEPTH>
 __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int n_pad = p.n + LIMB_PAD;
-    constexpr int SD_PER_BLK = TYPE == ELB_Q4_K ? 64 : TYPE == ELB_Q6_K ? 128 : 0;
+    const int n_pad = p.n, upt = int(p.upt);
     constexpr int UNIT_BYTES = TYPE == ELB_Q4_K ? Q4K_UNIT : TYPE == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT;
-    int8_t* lim = reinterpret_cast<int8_t*>(smem);
-    int8_t* sd = lim + 4 * n_pad;
-    float* red = reinterpret_cast<float*>(sd + ((p.n / QK_K) * SD_PER_BLK + 15) / 16 * 16);  // [warps][slots][16]
+    const int8_t* lim = p.limbs;
+    const int8_t* sd = p.limbs + (TYPE == ELB_Q6_K ? act_sd16_off(p.n) : act_sd32_off(p.n));
+    float* red = reinterpret_cast<float*>(smem);  // [warps][slots][16]
     uint8_t* ring = reinterpret_cast<uint8_t*>(red + GEMV_WARPS * p.slots * 16) + size_t(warp) * DEPTH * UNIT_BYTES;
     __shared__ double red8[GEMV_WARPS];
-    __shared__ int s_last[2];
+    __shared__ int s_last[2], s_wfirst[GEMV_WARPS], s_wlast[GEMV_WARPS];  // tiles touched by each warp
 
-    const int64_t U = p.tiles * p.upt, G = gridDim.x, c = blockIdx.x;
-    const int64_t cA = range_lo(U, G, c), cB = range_lo(U, G, c + 1);
-    const int64_t wA = cA + range_lo(cB - cA, GEMV_WARPS, warp), wB = cA + range_lo(cB - cA, GEMV_WARPS, warp + 1);
+    const int U = int(p.tiles) * upt, G = gridDim.x, c = blockIdx.x;
+    const int cA = range_lo(U, G, c), cB = range_lo(U, G, c + 1);
+    const int wA = cA + range_lo(cB - cA, GEMV_WARPS, warp), wB = cA + range_lo(cB - cA, GEMV_WARPS, warp + 1);
 
     // weights do not depend on the previous kernel: fill the ring before waiting for it. One commit group per unit,
     // empty groups included, so that "all but the newest DEPTH-1 groups" always means "the unit about to be used".
+    const uint8_t* src = p.W + size_t(wA) * UNIT_BYTES;
 #pragma unroll
     for (int d = 0; d < DEPTH - 1; ++d) {
-        if (wA + d < wB) issue_unit(ring + d * UNIT_BYTES, p.W + (wA + d) * UNIT_BYTES, UNIT_BYTES, lane);
+        if (wA + d < wB) issue_unit(ring + d * UNIT_BYTES, src + size_t(d) * UNIT_BYTES, UNIT_BYTES, lane);
         ring_commit();
     }
     pdl_launch_dependents();
     pdl_wait();
-    const float inv_scale = prologue<TYPE>(p, lim, n_pad, sd, red8);
+    prefetch_act(p.limbs, p.n);
+    const float inv_scale = __ldcg(p.inv_scale);
 
     Acc a{{0.f, 0.f}, {0.f, 0.f}};
-    int slot = 0, rs = 0;  // rs: ring slot of the unit in hand
+    int slot = 0, rs = 0;           // rs: ring slot of the unit in hand
+    int X = wA / upt, b = wA - X * upt;  // tile and block of the unit in hand
+    if (lane == 0) { s_wfirst[warp] = X; s_wlast[warp] = wB > wA ? (wB - 1) / upt : X - 1; }
     const float wt = t < 2 ? (t & 1 ? 65536.0f : 1.0f) : 0.0f;
     const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
-    for (int64_t u = wA; u < wB; ++u) {
+    for (int u = wA; u < wB; ++u) {
         {   // refill the slot that the previous iteration finished reading
             const int fs = rs == 0 ? DEPTH - 1 : rs - 1;
-            if (u + DEPTH - 1 < wB) issue_unit(ring + fs * UNIT_BYTES, p.W + (u + DEPTH - 1) * UNIT_BYTES, UNIT_BYTES, lane);
+            if (u + DEPTH - 1 < wB) issue_unit(ring + fs * UNIT_BYTES, src + size_t(u - wA + DEPTH - 1) * UNIT_BYTES, UNIT_BYTES, lane);
             ring_commit();
         }
         ring_wait<DEPTH - 1>();
@@ -475,12 +346,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
         Unit<TYPE> cur;
         load_unit(cur, ring + rs * UNIT_BYTES, lane);
         rs = rs + 1 == DEPTH ? 0 : rs + 1;
-        const int64_t X = u / p.upt;
-        const int b = int(u - X * p.upt);
-        DbgOut dbg{p.dbgP, p.dbgI, p.dbgJ, 16 * X + g, p.rows, p.n / (TYPE == ELB_Q6_K ? 16 : 32), p.n / (TYPE == ELB_Q8_0 ? 32 : QK_K)};
+        DbgOut dbg{p.dbgP, p.dbgI, p.dbgJ, int64_t(16) * X + g, p.rows, p.n / (TYPE == ELB_Q6_K ? 16 : 32), p.n / (TYPE == ELB_Q8_0 ? 32 : QK_K)};
         compute_unit<DBG>(cur, b, lim, n_pad, sd, lane, a, dbg);
         __syncwarp();  // every lane has its registers before the slot is refilled
-        if (u + 1 == wB || (u + 1) / p.upt != X) {  // tile finished for this warp: row sums over the 4 lanes of a row
+        if (++b == upt || u + 1 == wB) {  // tile finished for this warp: row sums over the 4 lanes of a row
             float v0 = a.acc[0] * wt - a.accm[0] * wtm, v1 = a.acc[1] * wt - a.accm[1] * wtm;
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
@@ -492,71 +361,66 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv(const GemvParams p) {
             }
             ++slot;
             a = Acc{{0.f, 0.f}, {0.f, 0.f}};
+            if (b == upt) { b = 0; ++X; }
         }
     }
     ring_wait<0>();
     __syncthreads();
-    if (cA >= cB) return;
 
     // CTA-level sums in warp order; complete tiles go out, shared tiles go to the scratch buffer
-    const int64_t Xf = cA / p.upt, Xl = (cB - 1) / p.upt;
-    const int ntl = int(Xl - Xf + 1);
+    const int Xf = cA / upt, Xl = (cB - 1) / upt, ntl = Xl - Xf + 1;
+    const bool part_first = Xf * upt < cA || (Xf + 1) * upt > cB;
+    const bool part_last = Xl != Xf && (Xl + 1) * upt > cB;
     for (int e = tid; e < ntl * 8; e += GEMV_THREADS) {
-        const int64_t X = Xf + e / 8;
-        const int gg = e % 8;
+        const int Xt = Xf + (e >> 3), gg = e & 7;
         float v0 = 0.f, v1 = 0.f;
+#pragma unroll
         for (int w = 0; w < GEMV_WARPS; ++w) {
-            const int64_t a0 = cA + range_lo(cB - cA, GEMV_WARPS, w), a1 = cA + range_lo(cB - cA, GEMV_WARPS, w + 1);
-            if (a0 >= a1) continue;
-            const int64_t f = a0 / p.upt, l = (a1 - 1) / p.upt;
-            if (X < f || X > l) continue;
-            v0 += red[(w * p.slots + int(X - f)) * 16 + gg];
-            v1 += red[(w * p.slots + int(X - f)) * 16 + gg + 8];
+            const int f = s_wfirst[w];
+            if (Xt < f || Xt > s_wlast[w]) continue;
+            v0 += red[(w * p.slots + (Xt - f)) * 16 + gg];
+            v1 += red[(w * p.slots + (Xt - f)) * 16 + gg + 8];
         }
-        const bool full = X * p.upt >= cA && (X + 1) * p.upt <= cB;
-        if (full) {
-            epilogue(p, X, gg, v0 * inv_scale, v1 * inv_scale);
+        const bool partial = (Xt == Xf && part_first) || (Xt == Xl && part_last);
+        if (!partial) {
+            epilogue(p, Xt, gg, v0 * inv_scale, v1 * inv_scale);
         } else {
-            float* dst = p.part + (c * 2 + (X == Xf ? 0 : 1)) * 16;
+            float* dst = p.part + (c * 2 + (Xt == Xf ? 0 : 1)) * 16;
             dst[gg] = v0;
             dst[gg + 8] = v1;
         }
     }
-    const bool part_first = Xf * p.upt < cA || (Xf + 1) * p.upt > cB;
-    const bool part_last = Xl != Xf && (Xl + 1) * p.upt > cB;
-    if (!part_first && !part_last) return;  // uniform over the CTA
+    if (part_first || part_last) {  // uniform over the CTA
     __threadfence();
     __syncthreads();
-    if (tid == 0) {
-        for (int i = 0; i < 2; ++i) {
-            s_last[i] = 0;
-            if (i == 0 ? !part_first : !part_last) continue;
-            const int64_t X = i == 0 ? Xf : Xl;
-            const int64_t c_lo = ((X * p.upt + 1) * G - 1) / U, c_hi = (((X + 1) * p.upt) * G - 1) / U;
-            const unsigned old = atomicAdd(&p.counters[X], 1u);
+    if (tid < 2) {
+        s_last[tid] = 0;
+        if (tid == 0 ? part_first : part_last) {
+            const int Xt = tid == 0 ? Xf : Xl;
+            const int c_lo = ((Xt * upt + 1) * G - 1) / U, c_hi = ((Xt + 1) * upt * G - 1) / U;
+            const unsigned old = atomicAdd(&p.counters[Xt], 1u);
             if (old == unsigned(c_hi - c_lo)) {
-                s_last[i] = 1;
-                p.counters[X] = 0;  // ready for the next launch; every other CTA has already arrived
+                s_last[tid] = 1;
+                p.counters[Xt] = 0;  // ready for the next launch; every other CTA has already arrived
             }
         }
     }
     __syncthreads();
-    for (int i = 0; i < 2; ++i) {
-        if (!s_last[i]) continue;
-        __threadfence();
-        if (tid < 8) {
-            const int64_t X = i == 0 ? Xf : Xl;
-            const int64_t c_lo = ((X * p.upt + 1) * G - 1) / U, c_hi = (((X + 1) * p.upt) * G - 1) / U;
-            float v0 = 0.f, v1 = 0.f;
-            for (int64_t cc = c_lo; cc <= c_hi; ++cc) {  // fixed CTA order
-                const int64_t first_tile = range_lo(U, G, cc) / p.upt;
-                const float* src = p.part + (cc * 2 + (X == first_tile ? 0 : 1)) * 16;
-                v0 += __ldcg(src + tid);
-                v1 += __ldcg(src + tid + 8);
-            }
-            epilogue(p, X, tid, v0 * inv_scale, v1 * inv_scale);
+    if (s_last[0] || s_last[1]) __threadfence();
+    if (tid < 16 && s_last[tid >> 3]) {
+        const int i = tid >> 3, gg = tid & 7, Xt = i == 0 ? Xf : Xl;
+        const int c_lo = ((Xt * upt + 1) * G - 1) / U, c_hi = ((Xt + 1) * upt * G - 1) / U;
+        float v0 = 0.f, v1 = 0.f;
+        for (int cc = c_lo; cc <= c_hi; ++cc) {  // fixed CTA order
+            const int first_tile = range_lo(U, G, cc) / upt;
+            const float* srcp = p.part + (cc * 2 + (Xt == first_tile ? 0 : 1)) * 16;
+            v0 += __ldcg(srcp + gg);
+            v1 += __ldcg(srcp + gg + 8);
         }
+        epilogue(p, Xt, gg, v0 * inv_scale, v1 * inv_scale);
     }
+    }
+    post_op(p.post, G, &s_last[0], red8);
 }
 
 // ---------------------------------------------------------------- F16 weights: fp32 FMA, two rows (g, g+8) per warp
@@ -571,12 +435,14 @@ struct GemvF16Params {
     float* y;
     const float* resid;
     int prologue, epilogue;
+    PostOp post;
 };
 
 __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_f16(const GemvF16Params p) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* xs = reinterpret_cast<float*>(smem);
     __shared__ double red8[GEMV_WARPS];
+    __shared__ int s_flag;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, n = p.n;
     pdl_launch_dependents();
     pdl_wait();
@@ -592,10 +458,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_f16(const GemvF16Param
         xs[i] = p.prologue == PRO_RMSNORM ? __fmul_rn(__fmul_rn(v, inv), p.norm_w[i]) : v;
     }
     __syncthreads();
-    const int64_t pairs = p.tiles * 8, GW = int64_t(gridDim.x) * GEMV_WARPS, wg = int64_t(blockIdx.x) * GEMV_WARPS + warp;
-    for (int64_t pr = range_lo(pairs, GW, wg); pr < range_lo(pairs, GW, wg + 1); ++pr) {
-        const int64_t X = pr / 8;
-        const int g = int(pr % 8);
+    const int pairs = int(p.tiles) * 8, GW = gridDim.x * GEMV_WARPS, wg = blockIdx.x * GEMV_WARPS + warp;
+    for (int pr = range_lo(pairs, GW, wg); pr < range_lo(pairs, GW, wg + 1); ++pr) {
+        const int64_t X = pr >> 3;
+        const int g = pr & 7;
         const __half* w0 = p.W + (16 * X + g) * n;
         const __half* w1 = w0 + 8 * int64_t(n);
         float s0 = 0.f, s1 = 0.f;
@@ -622,6 +488,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_f16(const GemvF16Param
             epilogue(q, X, g, s0, s1);
         }
     }
+    post_op(p.post, gridDim.x, &s_flag, red8);
+}
+
+// Stand-alone limb split of one vector (one block): the first matvec of a chain, and the operator-level entry points.
+__global__ void __launch_bounds__(SPLIT_THREADS) k_prep_limbs(const float* x, int n, const float* norm_w, float eps, int nl,
+                                                             int8_t* limbs, float* inv_scale) {
+    __shared__ double red8[SPLIT_WARPS];
+    pdl_launch_dependents();
+    pdl_wait();
+    block_split(x, n, norm_w, eps, nl, limbs, inv_scale, red8);
 }
 
 // ---------------------------------------------------------------- host side
@@ -634,6 +510,8 @@ int gemv_prepare(Weight* w) {
     ELB_CUDA(cudaMalloc(&w->part, size_t(w->max_grid) * 2 * 16 * sizeof(float)));
     ELB_CUDA(cudaMalloc(&w->counters, size_t(w->tiles) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(w->counters, 0, size_t(w->tiles) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&w->xlimbs, act_bytes(int(w->n))));
+    ELB_CUDA(cudaMalloc(&w->xinv, sizeof(float)));
     return ELB_OK;
 }
 
@@ -664,58 +542,75 @@ static int launch(K kernel, int grid, size_t smem, bool pdl, cudaStream_t s, con
     return ELB_OK;
 }
 
+int prep_limbs_launch(const float* x, int n, const float* norm_w, float eps, int nl, int8_t* limbs, float* inv_scale,
+                      bool pdl, cudaStream_t s) {
+    if (nl < 2 || nl > 4) return fail(ELB_ERR_INVALID, "split: limb count must be 2, 3 or 4");
+    if (n % 256) return fail(ELB_ERR_UNSUPPORTED, "split: vector length must be a multiple of 256");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(SPLIT_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    ELB_CUDA(cudaLaunchKernelEx(&cfg, k_prep_limbs, x, n, norm_w, eps, nl, limbs, inv_scale));
+    return ELB_OK;
+}
+
 int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s) {
-    if (!w || !a.x || !a.y) return fail(ELB_ERR_INVALID, "matvec: null argument");
+    if (!w || !a.y) return fail(ELB_ERR_INVALID, "matvec: null argument");
     if (a.epilogue == EPI_ADD && !a.resid) return fail(ELB_ERR_INVALID, "matvec: residual epilogue without residual");
     if (a.epilogue == EPI_SILU && !w->pair) return fail(ELB_ERR_INVALID, "matvec: SwiGLU epilogue needs a paired weight");
-    if (a.prologue == PRO_RMSNORM && !a.norm_w) return fail(ELB_ERR_INVALID, "matvec: RMSNorm prologue without weight");
+    if (a.post.kind && (!a.post.src || !a.post.limbs || !a.post.inv_scale || !a.post.done || a.post.n % 256))
+        return fail(ELB_ERR_INVALID, "matvec: incomplete post-op");
     DeviceInfo di;
     ELB_TRY(device_info(w->device, &di));
     if (w->type == ELB_F16) {
+        if (!a.x) return fail(ELB_ERR_INVALID, "matvec: F16 weights take the fp32 activation");
+        if (a.prologue == PRO_RMSNORM && !a.norm_w) return fail(ELB_ERR_INVALID, "matvec: RMSNorm prologue without weight");
         GemvF16Params p{reinterpret_cast<const __half*>(w->tiled), w->tiles, w->rows, int(w->n), a.x, a.norm_w, a.eps, a.y,
-                        a.resid, a.prologue, a.epilogue};
+                        a.resid, a.prologue, a.epilogue, a.post};
         const size_t smem = size_t(w->n) * sizeof(float);
         if (smem > di.smem_optin) return fail(ELB_ERR_UNSUPPORTED, "matvec: row too long for shared memory");
         const int grid = int(std::min<int64_t>((w->tiles * 8 + GEMV_WARPS - 1) / GEMV_WARPS, int64_t(di.sm_count) * 2));
         return launch(k_gemv_f16, grid, smem, a.pdl, s, p);
     }
+    if (!a.limbs || !a.inv_scale) return fail(ELB_ERR_INVALID, "matvec: quantized weights take the pre-split activation");
     if (!w->part) return fail(ELB_ERR_STATE, "matvec: weight scratch not prepared");
-    const int nl = a.nl == 0 ? 4 : a.nl;
-    if (nl < 2 || nl > 4) return fail(ELB_ERR_INVALID, "matvec: limb count must be 2, 3 or 4");
+    if (w->tiles * w->units_per_tile * int64_t(w->max_grid) >= (int64_t(1) << 31) || w->tiles * 8 * int64_t(w->max_grid) * GEMV_WARPS >= (int64_t(1) << 31))
+        return fail(ELB_ERR_UNSUPPORTED, "matvec: matrix too large for 32-bit unit indexing");
     const int64_t U = w->tiles * w->units_per_tile;
-    // Grid: one CTA per row tile while the tiles fit in one resident wave (no tile is shared between CTAs then);
-    // otherwise, and for matrices with fewer tiles than SMs, equal contiguous unit ranges (tiles on CTA borders are
-    // finished through the scratch buffer).
+    // Grid: equal contiguous unit ranges, one CTA per SM (tiles on CTA borders are finished through the scratch buffer).
     static const int grid_override = [] { const char* v = std::getenv("ELB_GEMV_GRID"); return v ? std::atoi(v) : 0; }();
-    int64_t grid64 = w->tiles >= di.sm_count && w->tiles <= w->max_grid ? w->tiles
-                     : w->tiles < di.sm_count                            ? std::min<int64_t>(U, di.sm_count)
-                                                                         : std::min<int64_t>(U, w->max_grid);
+    int64_t grid64 = std::min<int64_t>(U, di.sm_count);  // one CTA per SM: the next kernel's CTAs fit beside them
     if (grid_override > 0) grid64 = std::min<int64_t>({U, int64_t(grid_override), int64_t(w->max_grid)});
     const int grid = int(grid64);
     const int64_t per_cta = (U + grid - 1) / grid, per_warp = (per_cta + GEMV_WARPS - 1) / GEMV_WARPS;
     const int slots = int((per_warp + w->units_per_tile - 1) / w->units_per_tile + 2);
-    const int sd_per_blk = w->type == ELB_Q4_K ? 64 : w->type == ELB_Q6_K ? 128 : 0;
-    const size_t fixed = size_t(4) * (w->n + LIMB_PAD) + (size_t(w->n / QK_K) * sd_per_blk + 15) / 16 * 16 +
-                         size_t(GEMV_WARPS) * slots * 16 * sizeof(float);
+    const size_t fixed = size_t(GEMV_WARPS) * slots * 16 * sizeof(float);
     // ring depth: as deep as two resident CTAs per SM allow (at most 4 units per warp), else one CTA per SM
     const size_t per_depth = size_t(GEMV_WARPS) * w->unit_bytes, two_cta_budget = (di.smem_optin + 1024) / 2 - 1024;
     static const int depth_override = [] { const char* v = std::getenv("ELB_GEMV_DEPTH"); return v ? std::atoi(v) : 0; }();
     int depth = fixed < two_cta_budget ? int((two_cta_budget - fixed) / per_depth) : 0;
     if (depth < 2) depth = fixed < di.smem_optin ? int((di.smem_optin - fixed) / per_depth) : 0;
     if (depth < 2) return fail(ELB_ERR_UNSUPPORTED, "matvec: row too long for shared memory");
-    depth = std::min(depth, 4);
-    if (depth_override >= 2 && depth_override <= 4 && fixed + depth_override * per_depth <= di.smem_optin) depth = depth_override;
+    depth = std::min(depth, 6);
+    if (depth_override >= 2 && depth_override <= 6 && fixed + depth_override * per_depth <= di.smem_optin) depth = depth_override;
     const bool dbg = a.dbgP || a.dbgI || a.dbgJ;
     if (dbg) depth = 2;
+    if (depth == 5) depth = 4;
     const size_t smem = fixed + depth * per_depth;
-    GemvParams p{w->tiled, w->tiles, w->units_per_tile, w->rows, int(w->n), a.x, a.norm_w, a.eps, a.y, a.resid,
-                 w->part, w->counters, nl, a.prologue, a.epilogue, slots, a.dbgP, a.dbgI, a.dbgJ};
+    GemvParams p{w->tiled, w->tiles, w->units_per_tile, w->rows, int(w->n), a.limbs, a.inv_scale, a.y, a.resid,
+                 w->part, w->counters, a.epilogue, slots, a.dbgP, a.dbgI, a.dbgJ, a.post};
 #define ELB_GEMV_CASE(T)                                                                        \
     case T:                                                                                     \
         if (dbg) return launch(k_gemv<T, true, 2>, grid, smem, a.pdl, s, p);                     \
         if (depth == 2) return launch(k_gemv<T, false, 2>, grid, smem, a.pdl, s, p);             \
         if (depth == 3) return launch(k_gemv<T, false, 3>, grid, smem, a.pdl, s, p);             \
-        return launch(k_gemv<T, false, 4>, grid, smem, a.pdl, s, p);
+        if (depth <= 5) return launch(k_gemv<T, false, 4>, grid, smem, a.pdl, s, p);             \
+        return launch(k_gemv<T, false, 6>, grid, smem, a.pdl, s, p);
     switch (w->type) {
         ELB_GEMV_CASE(ELB_Q4_K)
         ELB_GEMV_CASE(ELB_Q6_K)

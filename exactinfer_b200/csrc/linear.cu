@@ -43,8 +43,9 @@ __global__ void __launch_bounds__(256) k_split_rows(const float* __restrict__ X,
     if (m > 0.f) frexpf(m, &e);
     const int k = m > 0.f ? 8 * nl - 2 - e : 0;
     int8_t* out = limbs + b * n;
+    const Pow2 sc = make_pow2(k);
     for (int i = tid; i < n; i += 256) {
-        int v = __float2int_rn(ldexpf(val(i), k));
+        int v = __float2int_rn(val(i) * sc.s1 * sc.s2);
 #pragma unroll
         for (int l = 0; l < 3; ++l) {
             const int a = ((v + 128) & 255) - 128;
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(256) k_split_rows(const float* __restrict__ X,
     if (xsum) {  // sum of the fixed-point values over each 32-slice, exact in int64, rounded once
         for (int c = tid; c < n / 32; c += 256) {
             long long s = 0;
-            for (int i = 0; i < 32; ++i) s += __float2int_rn(ldexpf(val(32 * c + i), k));
+            for (int i = 0; i < 32; ++i) s += __float2int_rn(val(32 * c + i) * sc.s1 * sc.s2);
             xsum[b * (n / 32) + c] = float(s);
         }
     }

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "split.cuh"
 
 namespace elb {
 
@@ -56,6 +57,9 @@ struct Model {
     int* pos_dev = nullptr;
     int32_t* tokens_host = nullptr;  // pinned
     int* pos_host = nullptr;         // pinned
+    int8_t* dlimbs[4] = {nullptr, nullptr, nullptr, nullptr};  // single-token limb buffers (see body_decode)
+    float* dinv = nullptr;   // [4] their 2^-k
+    unsigned* done = nullptr;  // [4] post-op arrival counters
     float* attn_part = nullptr;
     unsigned* attn_counters = nullptr;
     int attn_split = 1;
@@ -179,41 +183,81 @@ int body_prefill(Model* m, int B, int pos0) {
     return ELB_OK;
 }
 
-int gemv(Model* m, const Weight* w, const float* xin, const float* norm_w, float* y, const float* resid, int epi, int nl) {
+// Where the activation of a single-token matvec comes from: limbs left in `lim` by the producer's post-op (quantized
+// weights), or the fp32 vector itself, normalised inside the kernel (F16 weights).
+struct ActIn {
+    const int8_t* lim;
+    const float* inv_scale;
+    const float* x;
+    const float* norm_w;
+};
+
+int gemv(Model* m, const Weight* w, const ActIn& in, float* y, const float* resid, int epi, const PostOp& post) {
     GemvArgs a;
-    a.x = xin; a.norm_w = norm_w; a.eps = m->cfg.eps; a.y = y; a.resid = resid;
-    a.prologue = norm_w ? PRO_RMSNORM : PRO_PLAIN;
-    a.epilogue = epi; a.nl = nl; a.pdl = m->use_pdl;
+    a.limbs = in.lim; a.inv_scale = in.inv_scale;
+    a.x = in.x; a.norm_w = in.norm_w; a.eps = m->cfg.eps;
+    a.prologue = in.norm_w ? PRO_RMSNORM : PRO_PLAIN;
+    a.y = y; a.resid = resid; a.epilogue = epi; a.pdl = m->use_pdl; a.post = post;
     ++m->launches;
     return gemv_launch(w, a, m->stream);
 }
 
-// final norm + head on one row of x (the reference runs the head as a B=1 matvec too, :1833-1837)
+// post-op that leaves the limbs of `src` (optionally RMSNorm'ed) in slot `slot` of the model's limb buffers; none when
+// the consumer does not read limbs
+PostOp make_post(Model* m, bool wanted, const float* src, int n, const float* norm_w, int nl, int slot) {
+    PostOp po;
+    if (!wanted) return po;
+    po.kind = 1; po.src = src; po.n = n; po.nl = nl; po.norm_w = norm_w; po.eps = m->cfg.eps;
+    po.limbs = m->dlimbs[slot]; po.inv_scale = m->dinv + slot; po.done = m->done + slot;
+    return po;
+}
+
+// final norm + head on one row of x (the reference runs the head as a B=1 matvec too, :1833-1837); stand-alone split
 int head_logits(Model* m, const float* xrow) {
-    return gemv(m, m->head, xrow, m->output_norm, m->logits, nullptr, EPI_STORE, 4);
+    const int E = m->cfg.n_embd;
+    if (m->head->type != ELB_F16) {
+        ELB_TRY(prep_limbs_launch(xrow, E, m->output_norm, m->cfg.eps, 4, m->dlimbs[0], m->dinv, false, m->stream));
+        ++m->launches;
+    }
+    return gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, xrow, m->output_norm}, m->logits, nullptr, EPI_STORE, PostOp{});
 }
 
 // one token: everything through the matvec kernels; position and token id are read from device memory so that the
-// step can be captured once and replayed
+// step can be captured once and replayed. Limb buffers: 0 = input of qkv / head, 1 = input of wo, 2 = input of gate|up,
+// 3 = input of down; each is filled by the post-op of the kernel that produces the vector.
 int body_decode(Model* m) {
     const elb_config& c = m->cfg;
-    const int H = c.n_head, HKV = c.n_head_kv, KD = HKV * 128;
+    const int E = c.n_embd, F = c.n_ff, H = c.n_head, HKV = c.n_head_kv, QD = H * 128, KD = HKV * 128;
     const float scale = 1.0f / std::sqrt(float(c.head_dim));
+    auto quant = [](const Weight* w) { return w->type != ELB_F16; };
+    auto qkv_quant = [&](const Layer& L) { bool q = false; for (auto& s : L.qkv) q |= quant(s.w); return q; };
     ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, 1, m->x, m->stream));
     ++m->launches;
+    if (qkv_quant(m->layers[0])) {
+        ELB_TRY(prep_limbs_launch(m->x, E, m->layers[0].attn_norm, c.eps, m->nl_qkv, m->dlimbs[0], m->dinv, m->use_pdl, m->stream));
+        ++m->launches;
+    }
     for (int l = 0; l < c.n_layer; ++l) {
         Layer& L = m->layers[size_t(l)];
-        for (auto& s : L.qkv) ELB_TRY(gemv(m, s.w, m->x, L.attn_norm, m->qkv + s.col, nullptr, EPI_STORE, m->nl_qkv));
+        const bool last = l + 1 == c.n_layer;
+        for (auto& s : L.qkv)
+            ELB_TRY(gemv(m, s.w, ActIn{m->dlimbs[0], m->dinv, m->x, L.attn_norm}, m->qkv + s.col, nullptr, EPI_STORE, PostOp{}));
         AttnDecodeArgs a{m->qkv, L.q_norm, L.k_norm, m->rope, m->pos_dev,
                          m->kcache + size_t(l) * m->n_ctx * KD, m->vcache + size_t(l) * m->n_ctx * KD, m->att, m->attn_part,
-                         m->attn_counters, H, HKV, c.rope_dim, m->attn_split, c.eps, scale, m->use_pdl};
+                         m->attn_counters, H, HKV, c.rope_dim, m->attn_split, c.eps, scale, m->use_pdl,
+                         make_post(m, quant(L.wo), m->att, QD, nullptr, m->nl_wo, 1)};
         ELB_TRY(attn_decode_launch(a, m->stream));
         ++m->launches;
-        ELB_TRY(gemv(m, L.wo, m->att, nullptr, m->x, m->x, EPI_ADD, m->nl_wo));
-        ELB_TRY(gemv(m, L.gu, m->x, L.ffn_norm, m->act, nullptr, EPI_SILU, m->nl_gu));
-        ELB_TRY(gemv(m, L.down, m->act, nullptr, m->x, m->x, EPI_ADD, m->nl_down));
+        ELB_TRY(gemv(m, L.wo, ActIn{m->dlimbs[1], m->dinv + 1, m->att, nullptr}, m->x, m->x, EPI_ADD,
+                     make_post(m, quant(L.gu), m->x, E, L.ffn_norm, m->nl_gu, 2)));
+        ELB_TRY(gemv(m, L.gu, ActIn{m->dlimbs[2], m->dinv + 2, m->x, L.ffn_norm}, m->act, nullptr, EPI_SILU,
+                     make_post(m, quant(L.down), m->act, F, nullptr, m->nl_down, 3)));
+        const bool next_quant = last ? quant(m->head) : qkv_quant(m->layers[size_t(l) + 1]);
+        ELB_TRY(gemv(m, L.down, ActIn{m->dlimbs[3], m->dinv + 3, m->act, nullptr}, m->x, m->x, EPI_ADD,
+                     make_post(m, next_quant, m->x, E, last ? m->output_norm : m->layers[size_t(l) + 1].attn_norm,
+                               last ? 4 : m->nl_qkv, 0)));
     }
-    return head_logits(m, m->x);
+    return gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, m->x, m->output_norm}, m->logits, nullptr, EPI_STORE, PostOp{});
 }
 
 // Enqueue one single-token step on the model's stream (token id and position already on the device). The first
@@ -320,7 +364,8 @@ void model_destroy(Model* m) {
     }
     for (void* p : {(void*)m->output_norm, (void*)m->rope, (void*)m->kcache, (void*)m->vcache, (void*)m->x, (void*)m->qkv,
                     (void*)m->att, (void*)m->act, (void*)m->logits, (void*)m->limbs, (void*)m->inv_scale, (void*)m->xsum,
-                    (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters})
+                    (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
+                    (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
     if (m->tokens_host) cudaFreeHost(m->tokens_host);
     if (m->pos_host) cudaFreeHost(m->pos_host);
@@ -430,11 +475,18 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->pos_dev, sizeof(int)));
     ELB_CUDA(cudaMallocHost(&m->tokens_host, size_t(B) * sizeof(int32_t)));
     ELB_CUDA(cudaMallocHost(&m->pos_host, sizeof(int)));
+    {
+        const int64_t ns[4] = {E, QD, E, F};
+        for (int i = 0; i < 4; ++i) ELB_CUDA(cudaMalloc(&m->dlimbs[i], act_bytes(int(ns[i]))));
+        ELB_CUDA(cudaMalloc(&m->dinv, 4 * sizeof(float)));
+        ELB_CUDA(cudaMalloc(&m->done, 4 * sizeof(unsigned)));
+        ELB_CUDA(cudaMemset(m->done, 0, 4 * sizeof(unsigned)));
+    }
     // decode attention: a fixed number of key splits so that the launch shape does not depend on the position
     DeviceInfo di;
     ELB_TRY(device_info(m->device, &di));
     m->attn_split = std::max(1, std::min(32, (di.sm_count + c.n_head_kv - 1) / c.n_head_kv));
-    if (const char* v = std::getenv("ELB_ATTN_SPLIT")) m->attn_split = std::max(1, std::atoi(v));
+    if (const char* v = std::getenv("ELB_ATTN_SPLIT")) m->attn_split = std::max(1, std::min(32, std::atoi(v)));
     const int group = c.n_head / c.n_head_kv;
     ELB_CUDA(cudaMalloc(&m->attn_part, size_t(c.n_head_kv) * m->attn_split * group * (128 + 2) * 4));
     ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(c.n_head_kv) * sizeof(unsigned)));

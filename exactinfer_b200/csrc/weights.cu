@@ -175,7 +175,7 @@ int weight_create(int device, int type, int64_t rows_one, int64_t n, const void*
 void weight_destroy(Weight* w) {
     if (!w) return;
     cudaSetDevice(w->device);
-    cudaFree(w->tiled); cudaFree(w->planes); cudaFree(w->pl_d); cudaFree(w->pl_dm); cudaFree(w->part); cudaFree(w->counters);
+    cudaFree(w->tiled); cudaFree(w->planes); cudaFree(w->pl_d); cudaFree(w->pl_dm); cudaFree(w->part); cudaFree(w->counters); cudaFree(w->xlimbs); cudaFree(w->xinv);
     delete w;
 }
 
