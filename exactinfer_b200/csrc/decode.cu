@@ -1,0 +1,675 @@
+// One decode step (one token, batch 1) as ONE persistent cooperative kernel.
+//
+// At batch 1 every layer is a chain of five dependent steps (qkv matvec, attention, output projection, gate|up, down),
+// each a few microseconds of HBM traffic on this GPU: launched as separate kernels they are bound by launch and
+// dependency latency, not by bandwidth. Here one CTA per SM stays resident for the whole step and walks the chain with
+// grid-wide barriers between the steps:
+//   * every warp owns a fixed, contiguous share of the (row tile, k block) units of every weight matrix of the step, in
+//     execution order — one long "unit stream" — and keeps DEPTH-1 units of that stream in flight (cp.async into its
+//     ring in shared memory) no matter which phase the CTA is in: HBM keeps streaming through barriers, attention
+//     and activation conversion;
+//   * the activation of a matvec is converted to int8 limbs redundantly by every CTA (shared memory), from the fp32
+//     vector and a global maximum (atomicMax, order independent) or the per-tile sums of squares (RMSNorm) that the
+//     producing phase left: no serial single-CTA section;
+//   * row tiles that straddle two CTAs are finished by the last CTA to arrive, in fixed CTA order; sums of squares are
+//     kept per row tile and added in tile order: the step is deterministic.
+// Barrier waits are bounded: on timeout the kernel raises an error word, drains its copies and leaves.
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "split.cuh"
+#include "gemv_core.cuh"
+#include "layout.cuh"
+#include "decode.cuh"
+
+namespace elb {
+
+constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32, DK_DEPTH = 3;
+constexpr int DK_HD = 128, DK_KT = 32, DK_MAXG = 8, DK_MAXSPLIT = 32;
+constexpr unsigned DK_SPIN_LIMIT = 1u << 22;
+
+// ---------------------------------------------------------------- grid barrier (bounded)
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// All CTAs arrive, then leave together. `nb` counts this CTA's barriers. Returns false when the wait ran out (or an
+// earlier one did): the caller stops working, every later barrier returns at once.
+__device__ __forceinline__ bool grid_barrier(const DkParams& p, int& nb, int* s_dead) {
+    __syncthreads();
+    if (threadIdx.x == 0 && !*s_dead) {
+        __threadfence();
+        atomicAdd(p.bar, 1u);
+        const unsigned target = unsigned(++nb) * gridDim.x;
+        unsigned it = 0;
+        while (ld_acquire(p.bar) < target) {
+            if (++it > DK_SPIN_LIMIT) {
+                *s_dead = 1;
+                atomicExch(p.err, 1);
+                break;
+            }
+            if (it > 2048) __nanosleep(64);
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    return !*s_dead;
+}
+
+// ---------------------------------------------------------------- activation -> limbs in shared memory
+
+__device__ __forceinline__ float dk_block_max(float v, float* red, int tid) {
+    v = warp_max(v);
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    float m = red[0];
+#pragma unroll
+    for (int i = 1; i < DK_WARPS; ++i) m = fmaxf(m, red[i]);
+    __syncthreads();
+    return m;
+}
+__device__ __forceinline__ double dk_block_sum(double v, double* red, int tid) {
+    v = warp_sum(v);
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < DK_WARPS; ++i) s += red[i];  // fixed order
+    __syncthreads();
+    return s;
+}
+
+struct ActSmem {
+    int8_t* lim;   // [4][n_pad]
+    int8_t* sd32;  // [n/256][8][8]
+    int8_t* sd16;  // [n/256][8][16]
+    int n_pad;
+};
+
+// src: fp32 vector in global memory, written by other CTAs before the last barrier (read through L2).
+// norm_w != nullptr: RMSNorm with the reference's operation order (src/ops.cpp:155-160): the sum of squares is the
+// sum, in tile order, of the per-tile sums the producing phase left in ssq[n/16]. Otherwise max|src| is known
+// (amax_bits, the bit pattern of a non-negative float). Returns inv_scale = 2^-k.
+__device__ float convert_act(const float* src, int n, const float* norm_w, const double* ssq, float eps,
+                             const unsigned* amax_bits, int nl, const ActSmem& a, double* red) {
+    const int tid = threadIdx.x;
+    float inv = 1.0f, m = 0.f;
+    if (norm_w) {
+        double ss = 0.0;
+        for (int i = tid; i < n / 16; i += DK_THREADS) ss += __ldcg(ssq + i);
+        ss = dk_block_sum(ss, red, tid);
+        inv = float(1.0 / sqrt(ss / n + double(eps)));
+        for (int i = tid * 4; i < n; i += DK_THREADS * 4)
+            m = fmaxf(m, absmax4(norm4(__ldcg(reinterpret_cast<const float4*>(src + i)), inv,
+                                       __ldg(reinterpret_cast<const float4*>(norm_w + i)))));
+        m = dk_block_max(m, reinterpret_cast<float*>(red), tid);
+    } else {
+        m = __uint_as_float(__ldcg(amax_bits));
+    }
+    const int k = split_shift(m, nl);
+    const Pow2 sc = make_pow2(k);
+    for (int i = tid * 4; i < n; i += DK_THREADS * 4) {  // warp-uniform trip count: n is a multiple of 128
+        float4 f = __ldcg(reinterpret_cast<const float4*>(src + i));
+        if (norm_w) f = norm4(f, inv, __ldg(reinterpret_cast<const float4*>(norm_w + i)));
+        split4(f, sc, a.lim, a.n_pad, a.sd32, a.sd16, i, true);
+    }
+    __syncthreads();
+    return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
+}
+
+// ---------------------------------------------------------------- the unit stream of one warp
+
+// Matrices of the step in execution order: per layer qkv segments, wo, gate|up, down; then the head.
+__device__ __forceinline__ const DkMat& mat_at(const DkParams& p, int j) {
+    const int per = p.n_qkv + 3, l = j / per, i = j - l * per;
+    if (l >= p.n_layer) return p.head;
+    const DkLayer& L = p.layers[l];
+    return i < p.n_qkv ? L.qkv[i] : i == p.n_qkv ? L.wo : i == p.n_qkv + 1 ? L.gu : L.down;
+}
+
+// A matrix with fewer units than CTAs is shared by the first U CTAs only, so that every participating CTA owns work
+// (the arrival counts of shared tiles rely on it).
+struct WarpRange { int cA, cB, wA, wB, G; };
+__device__ __forceinline__ WarpRange warp_range(const DkMat& m, int warp) {
+    const int U = m.tiles * m.upt, G = min(int(gridDim.x), U), c = blockIdx.x;
+    WarpRange r;
+    r.G = G;
+    r.cA = c < G ? range_lo(U, G, c) : 0;
+    r.cB = c < G ? range_lo(U, G, c + 1) : 0;
+    r.wA = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp);
+    r.wB = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp + 1);
+    return r;
+}
+
+// Prefetch cursor: the next unit of this warp's stream that has not been requested yet.
+struct Cursor {
+    int j, n_mats, u, end, unit_bytes;
+    const uint8_t* W;
+};
+__device__ __forceinline__ void cursor_seek(const DkParams& p, Cursor& c, int warp) {  // first non-empty range from c.j on
+    while (c.j < c.n_mats) {
+        const DkMat& m = mat_at(p, c.j);
+        const WarpRange r = warp_range(m, warp);
+        if (r.wA < r.wB) {
+            c.u = r.wA; c.end = r.wB; c.W = m.W; c.unit_bytes = m.unit_bytes;
+            return;
+        }
+        ++c.j;
+    }
+}
+// request the cursor's unit into `slot` (if the stream has not ended) and move on; always one commit group
+__device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8_t* slot, int warp, int lane) {
+    if (c.j < c.n_mats) {
+        issue_unit(slot, c.W + size_t(c.u) * c.unit_bytes, c.unit_bytes, lane);
+        if (++c.u == c.end) {
+            ++c.j;
+            cursor_seek(p, c, warp);
+        }
+    }
+    ring_commit();
+}
+
+// ---------------------------------------------------------------- one matvec phase
+
+enum { DK_EPI_STORE = 0, DK_EPI_ADD_SSQ = 1, DK_EPI_SILU_AMAX = 2 };
+
+struct PhaseSmem {
+    uint8_t* ring;   // this warp's ring [DK_DEPTH][slot_bytes]
+    int slot_bytes;
+    ActSmem act;
+    float* red;      // [DK_WARPS][slots][16]
+    double* red8;    // [DK_WARPS]
+    float* sq;       // [tiles of this CTA + 2][16] squares / finished values
+    int* wfirst;     // [DK_WARPS]
+    int* wlast;      // [DK_WARPS]
+    int* flags;      // [4]: last-arriver flags (0,1), dead (2), block amax bits (3)
+};
+
+// finished rows g, g+8 of tile X: write them out; returns the values written (for the per-tile bookkeeping)
+__device__ __forceinline__ void dk_epilogue(int epi, const DkMat& m, float* y, int64_t X, int g, float v0, float v1,
+                                            float& o0, float& o1) {
+    const int64_t r0 = 16 * X + g, r1 = r0 + 8;
+    o0 = 0.f; o1 = 0.f;
+    if (epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
+        const int64_t o = 8 * X + g;
+        if (o < m.rows / 2) { o0 = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1); y[o] = o0; }
+        return;
+    }
+    if (epi == DK_EPI_ADD_SSQ) {
+        if (r0 < m.rows) { o0 = __ldcg(y + r0) + v0; y[r0] = o0; }  // through L2: another CTA may have written it
+        if (r1 < m.rows) { o1 = __ldcg(y + r1) + v1; y[r1] = o1; }
+        return;
+    }
+    if (r0 < m.rows) y[r0] = v0;
+    if (r1 < m.rows) y[r1] = v1;
+}
+
+// after a tile is finished by 8 consecutive threads (gg = 0..7, values o0 / o1): per-tile sum of squares in double, in
+// row order, or the block maximum; `slot` is this tile's row in s.sq
+__device__ __forceinline__ void dk_tile_stats(int epi, const DkParams& p, const PhaseSmem& s, int slot, int gg, float o0, float o1) {
+    if (epi == DK_EPI_ADD_SSQ) {
+        s.sq[slot * 16 + gg] = o0;
+        s.sq[slot * 16 + gg + 8] = o1;
+    } else if (epi == DK_EPI_SILU_AMAX) {
+        atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(fabsf(o0)));
+    }
+}
+
+template <int TYPE>
+__device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, int& rs, const PhaseSmem& s,
+                          int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3, upt = m.upt;
+    const int8_t* sd = TYPE == ELB_Q6_K ? s.act.sd16 : s.act.sd32;
+    Acc a{{0.f, 0.f}, {0.f, 0.f}};
+    int slot = 0;
+    int X = r.wA / upt, b = r.wA - X * upt;
+    if (lane == 0) { s.wfirst[warp] = X; s.wlast[warp] = r.wB > r.wA ? (r.wB - 1) / upt : X - 1; }
+    const float wt = t < 2 ? (t & 1 ? 65536.0f : 1.0f) : 0.0f;
+    const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
+    DbgOut dbg{nullptr, nullptr, nullptr, 0, 0, 0, 0};
+    for (int u = r.wA; u < r.wB; ++u) {
+        cursor_issue(p, pf, s.ring + (rs == 0 ? DK_DEPTH - 1 : rs - 1) * s.slot_bytes, warp, lane);
+        ring_wait<DK_DEPTH - 1>();
+        __syncwarp();
+        Unit<TYPE> cur;
+        load_unit(cur, s.ring + rs * s.slot_bytes, lane);
+        rs = rs + 1 == DK_DEPTH ? 0 : rs + 1;
+        compute_unit<false>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg);
+        __syncwarp();
+        if (++b == upt || u + 1 == r.wB) {
+            float v0 = a.acc[0] * wt - a.accm[0] * wtm, v1 = a.acc[1] * wt - a.accm[1] * wtm;
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            if (t == 0) {
+                s.red[(warp * p.slots + slot) * 16 + g] = v0;
+                s.red[(warp * p.slots + slot) * 16 + g + 8] = v1;
+            }
+            ++slot;
+            a = Acc{{0.f, 0.f}, {0.f, 0.f}};
+            if (b == upt) { b = 0; ++X; }
+        }
+    }
+}
+
+// y (+)= W * act for one matrix; the activation limbs are already in shared memory. Ends with every row of this
+// CTA's share written (tiles shared with a neighbour: by whichever CTA arrives last).
+__device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf, int& rs,
+                             const PhaseSmem& s, double* ssq_out, unsigned* amax_out) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
+    const WarpRange r = warp_range(m, warp);
+    if (tid == 0) s.flags[3] = 0;
+    __syncthreads();
+    switch (m.type) {
+        case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, rs, s, warp, lane); break;
+        case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, rs, s, warp, lane); break;
+        default: run_units<ELB_Q8_0>(p, m, r, pf, rs, s, warp, lane); break;
+    }
+    __syncthreads();
+    const int U = m.tiles * upt, G = r.G, c = blockIdx.x;
+    if (r.cA < r.cB) {
+        const int Xf = r.cA / upt, Xl = (r.cB - 1) / upt, ntl = Xl - Xf + 1;
+        const bool part_first = Xf * upt < r.cA || (Xf + 1) * upt > r.cB;
+        const bool part_last = Xl != Xf && (Xl + 1) * upt > r.cB;
+        for (int e = tid; e < ntl * 8; e += DK_THREADS) {
+            const int Xt = Xf + (e >> 3), gg = e & 7;
+            float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < DK_WARPS; ++w) {
+                const int f = s.wfirst[w];
+                if (Xt < f || Xt > s.wlast[w]) continue;
+                v0 += s.red[(w * p.slots + (Xt - f)) * 16 + gg];
+                v1 += s.red[(w * p.slots + (Xt - f)) * 16 + gg + 8];
+            }
+            const bool partial = (Xt == Xf && part_first) || (Xt == Xl && part_last);
+            if (!partial) {
+                float o0, o1;
+                dk_epilogue(epi, m, y, Xt, gg, v0 * inv_scale, v1 * inv_scale, o0, o1);
+                dk_tile_stats(epi, p, s, e >> 3, gg, o0, o1);
+            } else {
+                float* dst = m.part + (c * 2 + (Xt == Xf ? 0 : 1)) * 16;
+                dst[gg] = v0;
+                dst[gg + 8] = v1;
+            }
+        }
+        if (part_first || part_last) {  // uniform over the CTA
+            __threadfence();
+            __syncthreads();
+            if (tid < 2) {
+                s.flags[tid] = 0;
+                if (tid == 0 ? part_first : part_last) {
+                    const int Xt = tid == 0 ? Xf : Xl;
+                    const int c_lo = ((Xt * upt + 1) * G - 1) / U, c_hi = ((Xt + 1) * upt * G - 1) / U;
+                    const unsigned old = atomicAdd(&m.counters[Xt], 1u);
+                    if (old == unsigned(c_hi - c_lo)) {
+                        s.flags[tid] = 1;
+                        m.counters[Xt] = 0;
+                    }
+                }
+            }
+            __syncthreads();
+            if (s.flags[0] || s.flags[1]) __threadfence();
+            if (tid < 16 && s.flags[tid >> 3]) {
+                const int i = tid >> 3, gg = tid & 7, Xt = i == 0 ? Xf : Xl;
+                const int c_lo = ((Xt * upt + 1) * G - 1) / U, c_hi = ((Xt + 1) * upt * G - 1) / U;
+                float v0 = 0.f, v1 = 0.f;
+                for (int cc = c_lo; cc <= c_hi; ++cc) {  // fixed CTA order
+                    const int first_tile = range_lo(U, G, cc) / upt;
+                    const float* srcp = m.part + (cc * 2 + (Xt == first_tile ? 0 : 1)) * 16;
+                    v0 += __ldcg(srcp + gg);
+                    v1 += __ldcg(srcp + gg + 8);
+                }
+                float o0, o1;
+                dk_epilogue(epi, m, y, Xt, gg, v0 * inv_scale, v1 * inv_scale, o0, o1);
+                dk_tile_stats(epi, p, s, i == 0 ? 0 : ntl - 1, gg, o0, o1);
+            }
+        }
+        __syncthreads();
+        // per-tile sums of squares of the finished tiles, rows in order, in double (RMSNorm of the next phase)
+        if (epi == DK_EPI_ADD_SSQ) {
+            for (int e = tid; e < ntl; e += DK_THREADS) {
+                const int Xt = Xf + e;
+                const bool partial = (Xt == Xf && part_first) || (Xt == Xl && part_last);
+                if (partial && !s.flags[Xt == Xf ? 0 : 1]) continue;  // finished elsewhere
+                double ss = 0.0;
+                for (int q = 0; q < 16; ++q) { const double v = s.sq[e * 16 + q]; ss += v * v; }
+                ssq_out[Xt] = ss;
+            }
+        }
+    }
+    if (epi == DK_EPI_SILU_AMAX) {
+        __syncthreads();
+        if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
+    }
+}
+
+// ---------------------------------------------------------------- attention phase (one token)
+
+// RMSNorm over one 128-wide head followed by NEOX RoPE (src/ops.cpp:155-160, src/model.cpp:23-32 of the reference);
+// one warp per head, lane owns elements lane, lane+32, lane+64, lane+96.
+__device__ __forceinline__ void dk_head_norm_rope(const float* src, const float* w, const float2* cs, int rope_dim, float eps,
+                                                  float* dst, int lane) {
+    float v[4];
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[j] = __ldcg(src + lane + 32 * j);
+        ss += double(v[j]) * v[j];
+    }
+    ss = warp_sum(ss);
+    const float inv = float(1.0 / sqrt(ss / DK_HD + double(eps)));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __fmul_rn(__fmul_rn(v[j], inv), w[lane + 32 * j]);
+    __syncwarp();
+    const int half = rope_dim / 2;
+    for (int i = lane; i < half; i += 32) {
+        const float2 c = cs[i];
+        const float a = dst[i], b = dst[i + half];
+        dst[i] = __fsub_rn(__fmul_rn(a, c.x), __fmul_rn(b, c.y));
+        dst[i + half] = __fadd_rn(__fmul_rn(a, c.y), __fmul_rn(b, c.x));
+    }
+    __syncwarp();
+}
+
+struct AttnSmem {
+    float* qs;    // [DK_MAXG][128]
+    float* knew;  // [128]
+    float* vnew;  // [128]
+    float* Ks;    // [DK_KT][129]
+    float* Vs;    // [DK_KT][128]
+    float* Ps;    // [DK_MAXG][DK_KT]
+    float* corr;  // [DK_MAXG], then m [DK_MAXG], l [DK_MAXG]
+    int* flags;
+};
+
+// CTA c < HKV * nsplit works on KV head c / nsplit, key split c % nsplit: q/k norm + RoPE, KV append, flash decode
+// over its keys, partial results to the scratch buffer; the last split of a KV head to arrive combines them in split
+// order and writes att (and max|att|). Semantics: src/model.cpp:176-214 of the reference.
+__device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& s, unsigned* amax_out) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c = blockIdx.x;
+    if (c >= p.HKV * p.nsplit) return;
+    const int kvh = c / p.nsplit, split = c - kvh * p.nsplit, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
+    const int pos = *p.pos, T = pos + 1;
+    const float2* cs = reinterpret_cast<const float2*>(p.rope) + size_t(pos) * (p.rope_dim / 2);
+    float* m_s = s.corr + DK_MAXG;
+    float* l_s = s.corr + 2 * DK_MAXG;
+    for (int h = warp; h < group + 1; h += DK_WARPS) {
+        if (h < group) dk_head_norm_rope(p.qkv + (kvh * group + h) * DK_HD, L.q_norm, cs, p.rope_dim, p.eps, s.qs + h * DK_HD, lane);
+        else dk_head_norm_rope(p.qkv + QD + kvh * DK_HD, L.k_norm, cs, p.rope_dim, p.eps, s.knew, lane);
+    }
+    if (tid < DK_HD) s.vnew[tid] = __ldcg(p.qkv + QD + KD + kvh * DK_HD + tid);
+    if (tid < DK_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+    if (tid == 0) s.flags[3] = 0;
+    __syncthreads();
+    if (split == 0 && tid < DK_HD) {  // KV append (src/model.cpp:186-189): only row `pos` is written
+        L.kc[size_t(pos) * KD + kvh * DK_HD + tid] = s.knew[tid];
+        L.vc[size_t(pos) * KD + kvh * DK_HD + tid] = s.vnew[tid];
+    }
+    const int tiles = (T + DK_KT - 1) / DK_KT, per = (tiles + p.nsplit - 1) / p.nsplit;
+    const int t_begin = min(T, split * per * DK_KT), t_end = min(T, (split + 1) * per * DK_KT);
+    float acc[2] = {0.f, 0.f};  // outputs (head tid/128 + 4i, dim tid%128)
+    const int od = tid & (DK_HD - 1), oh = tid >> 7;
+    for (int t0 = t_begin; t0 < t_end; t0 += DK_KT) {
+        const int nk = min(DK_KT, t_end - t0);
+        __syncthreads();
+        for (int idx = tid; idx < DK_KT * (DK_HD / 4); idx += DK_THREADS) {
+            const int j = idx / (DK_HD / 4), cc = (idx % (DK_HD / 4)) * 4;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (j < nk) {
+                const int t = t0 + j;
+                if (t == pos) {  // the row this step appends: from shared memory, not from the cache
+                    kv = *reinterpret_cast<const float4*>(s.knew + cc);
+                    vv = *reinterpret_cast<const float4*>(s.vnew + cc);
+                } else {
+                    kv = *reinterpret_cast<const float4*>(L.kc + size_t(t) * KD + kvh * DK_HD + cc);
+                    vv = *reinterpret_cast<const float4*>(L.vc + size_t(t) * KD + kvh * DK_HD + cc);
+                }
+            }
+            float* kr = s.Ks + j * (DK_HD + 1) + cc;
+            kr[0] = kv.x; kr[1] = kv.y; kr[2] = kv.z; kr[3] = kv.w;
+            *reinterpret_cast<float4*>(s.Vs + j * DK_HD + cc) = vv;
+        }
+        __syncthreads();
+        if (warp < group) {  // scores: warp = head, lane = key; dimension order, multiply then add, as the CPU path does
+            float sc = -INFINITY;
+            if (lane < nk) {
+                float a = 0.f;
+                const float* q = s.qs + warp * DK_HD;
+                const float* kr = s.Ks + lane * (DK_HD + 1);
+#pragma unroll 8
+                for (int i = 0; i < DK_HD; ++i) a = __fadd_rn(a, __fmul_rn(q[i], kr[i]));
+                sc = __fmul_rn(a, p.scale);
+            }
+            const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(sc));
+            const float pj = lane < nk ? expf(sc - m_new) : 0.f;
+            const float sum = warp_sum(pj);
+            s.Ps[warp * DK_KT + lane] = pj;
+            if (lane == 0) {
+                const float cr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                s.corr[warp] = cr;
+                l_s[warp] = l_s[warp] * cr + sum;
+                m_s[warp] = m_new;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int h = oh + 4 * i;
+            if (h >= group) continue;
+            float a = acc[i] * s.corr[h];
+            for (int j = 0; j < nk; ++j) a = fmaf(s.Ps[h * DK_KT + j], s.Vs[j * DK_HD + od], a);
+            acc[i] = a;
+        }
+    }
+    __syncthreads();
+    float* mine = p.attn_part + (size_t(kvh) * p.nsplit + split) * group * (DK_HD + 2);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int h = oh + 4 * i;
+        if (h < group) mine[h * (DK_HD + 2) + od] = acc[i];
+    }
+    if (tid < group) {
+        mine[tid * (DK_HD + 2) + DK_HD] = m_s[tid];
+        mine[tid * (DK_HD + 2) + DK_HD + 1] = l_s[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned old = atomicAdd(&p.attn_counters[kvh], 1u);
+        s.flags[0] = old == unsigned(p.nsplit - 1);
+        if (s.flags[0]) p.attn_counters[kvh] = 0;
+    }
+    __syncthreads();
+    if (!s.flags[0]) return;
+    __threadfence();
+    const float* base = p.attn_part + size_t(kvh) * p.nsplit * group * (DK_HD + 2);
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int h = oh + 4 * i;
+        if (h >= group) continue;
+        float ms[DK_MAXSPLIT], ls[DK_MAXSPLIT], as[DK_MAXSPLIT];  // every load of the pass is issued before the first use
+#pragma unroll
+        for (int q = 0; q < DK_MAXSPLIT; ++q) {
+            const float* ps = base + (size_t(q < p.nsplit ? q : 0) * group + h) * (DK_HD + 2);
+            ms[q] = q < p.nsplit ? __ldcg(ps + DK_HD) : -INFINITY;
+            ls[q] = __ldcg(ps + DK_HD + 1);
+            as[q] = __ldcg(ps + od);
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < DK_MAXSPLIT; ++q) M = fmaxf(M, ms[q]);
+        float Lsum = 0.f, o = 0.f;
+#pragma unroll
+        for (int q = 0; q < DK_MAXSPLIT; ++q) {  // fixed split order
+            if (ms[q] == -INFINITY) continue;
+            const float w = expf(ms[q] - M);
+            Lsum = fmaf(ls[q], w, Lsum);
+            o = fmaf(as[q], w, o);
+        }
+        const float r = o / Lsum;
+        p.att[(kvh * group + h) * DK_HD + od] = r;
+        mx = fmaxf(mx, fabsf(r));
+    }
+    mx = warp_max(mx);
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
+    __syncthreads();
+    if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
+}
+
+// ---------------------------------------------------------------- the step
+
+constexpr int DK_SQ_TILES = 8;
+constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * (DK_HD + 1) + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
+
+__host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
+    const size_t act = size_t(4) * (n_max + 32) + size_t(n_max / 256) * 192, attn = size_t(DK_ATTN_FLOATS) * 4;
+    return ((act > attn ? act : attn) + 15) / 16 * 16;
+}
+__global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p, const int slot_bytes) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // shared memory: rings | scratch (limbs of the running matvec, or the attention tiles) | reduction buffers
+    uint8_t* scratch = smem + size_t(DK_WARPS) * DK_DEPTH * slot_bytes;
+    uint8_t* tail = scratch + dk_scratch_bytes(p.n_max);
+    PhaseSmem s;
+    s.ring = smem + size_t(warp) * DK_DEPTH * slot_bytes;
+    s.slot_bytes = slot_bytes;
+    s.act.lim = reinterpret_cast<int8_t*>(scratch);
+    s.red = reinterpret_cast<float*>(tail);
+    s.sq = s.red + DK_WARPS * p.slots * 16;
+    s.red8 = reinterpret_cast<double*>(s.sq + DK_SQ_TILES * 16);
+    s.wfirst = reinterpret_cast<int*>(s.red8 + DK_WARPS);
+    s.wlast = s.wfirst + DK_WARPS;
+    s.flags = s.wlast + DK_WARPS;
+    AttnSmem as;
+    as.qs = reinterpret_cast<float*>(scratch);
+    as.knew = as.qs + DK_MAXG * DK_HD;
+    as.vnew = as.knew + DK_HD;
+    as.Ks = as.vnew + DK_HD;
+    as.Vs = as.Ks + DK_KT * (DK_HD + 1);
+    as.Ps = as.Vs + DK_KT * DK_HD;
+    as.corr = as.Ps + DK_MAXG * DK_KT;
+    as.flags = s.flags;
+    auto act_for = [&](int n) {
+        ActSmem a;
+        a.lim = reinterpret_cast<int8_t*>(scratch);
+        a.n_pad = n + 32;
+        a.sd32 = a.lim + 4 * a.n_pad;
+        a.sd16 = a.sd32 + (n / 256) * 64;
+        return a;
+    };
+    if (tid == 0) s.flags[2] = 0;
+    __syncthreads();
+
+    // start the weight stream: DEPTH-1 units per warp in flight from here to the end of the step
+    Cursor pf;
+    pf.j = 0;
+    pf.n_mats = p.n_layer * (p.n_qkv + 3) + 1;
+    cursor_seek(p, pf, warp);
+#pragma unroll
+    for (int d = 0; d < DK_DEPTH - 1; ++d) cursor_issue(p, pf, s.ring + d * slot_bytes, warp, lane);
+    int rs = 0, nb = 0;
+    int* dead = &s.flags[2];
+
+    // token embedding (get_row, src/ops.cpp:76-82 of the reference): CTA c decodes row tiles c, c+G, ... of the row
+    {
+        const int64_t R = *p.token;
+        for (int Xt = blockIdx.x; Xt < p.E / 16; Xt += gridDim.x) {
+            if (tid < 16) {
+                const int k = Xt * 16 + tid;
+                const float v = p.embd_type == ELB_F16 ? __half2float(reinterpret_cast<const __half*>(p.embd)[R * p.E + k])
+                                                       : elem_value(p.embd_type, tiled_elem(p.embd_type, p.embd, p.E, R, k));
+                p.x[k] = v;
+                s.sq[tid] = v;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                double ss = 0.0;
+                for (int q = 0; q < 16; ++q) { const double v = s.sq[q]; ss += v * v; }
+                p.ssq[Xt] = ss;
+            }
+            __syncthreads();
+        }
+    }
+    bool ok = grid_barrier(p, nb, dead);
+
+    for (int l = 0; l < p.n_layer && ok; ++l) {
+        const DkLayer& L = p.layers[l];
+        unsigned* amax = p.amax + 2 * l;
+        {
+            s.act = act_for(p.E);
+            const float inv = convert_act(p.x, p.E, L.attn_norm, p.ssq, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
+            for (int i = 0; i < p.n_qkv; ++i)
+                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr, nullptr);
+        }
+        if (!(ok = grid_barrier(p, nb, dead))) break;
+        attn_phase(p, L, as, amax);
+        if (!(ok = grid_barrier(p, nb, dead))) break;
+        {
+            s.act = act_for(p.H * DK_HD);
+            const float inv = convert_act(p.att, p.H * DK_HD, nullptr, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
+            matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
+        }
+        if (!(ok = grid_barrier(p, nb, dead))) break;
+        {
+            s.act = act_for(p.E);
+            const float inv = convert_act(p.x, p.E, L.ffn_norm, p.ssq, p.eps, nullptr, p.nl_gu, s.act, s.red8);
+            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, nullptr, amax + 1);
+        }
+        if (!(ok = grid_barrier(p, nb, dead))) break;
+        {
+            s.act = act_for(p.F);
+            const float inv = convert_act(p.act, p.F, nullptr, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
+            matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
+        }
+        ok = grid_barrier(p, nb, dead);
+    }
+    if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference)
+        s.act = act_for(p.E);
+        const float inv = convert_act(p.x, p.E, p.output_norm, p.ssq, p.eps, nullptr, 4, s.act, s.red8);
+        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr, nullptr);
+    }
+    ring_wait<0>();
+}
+
+size_t decode_smem_bytes(const DkParams& p, int slot_bytes) {
+    return size_t(DK_WARPS) * DK_DEPTH * slot_bytes + dk_scratch_bytes(p.n_max) + size_t(DK_WARPS) * p.slots * 16 * 4 +
+           DK_SQ_TILES * 16 * 4 + DK_WARPS * 8 + 2 * DK_WARPS * 4 + 4 * 4 + 16;
+}
+
+int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s) {
+    const size_t smem = decode_smem_bytes(p, slot_bytes);
+    static thread_local size_t configured = 0;
+    if (configured < smem) {
+        ELB_CUDA(cudaFuncSetAttribute(k_decode_step, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        configured = smem;
+    }
+    void* args[] = {const_cast<DkParams*>(&p), const_cast<int*>(&slot_bytes)};
+    ELB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(k_decode_step), dim3(grid), dim3(DK_THREADS), args, smem, s));
+    return ELB_OK;
+}
+
+// can one CTA per SM of the step kernel be resident with this much shared memory?
+int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits) {
+    DeviceInfo di;
+    ELB_TRY(device_info(device, &di));
+    const size_t smem = decode_smem_bytes(p, slot_bytes);
+    *fits = false;
+    if (smem > di.smem_optin) return ELB_OK;
+    ELB_CUDA(cudaFuncSetAttribute(k_decode_step, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    int per_sm = 0;
+    ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, DK_THREADS, smem));
+    *fits = per_sm >= 1;
+    return ELB_OK;
+}
+
+int decode_threads() { return DK_THREADS; }
+int decode_warps() { return DK_WARPS; }
+
+}  // namespace elb

@@ -1,0 +1,55 @@
+// Parameters of the persistent decode kernel (decode.cu), filled by the model (model.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace elb {
+
+struct DkMat {  // one weight matrix of the step, in tiled layout
+    const uint8_t* W;
+    int type, unit_bytes, tiles, upt, rows, n;
+    float* part;         // split-K scratch [grid][2][16]
+    unsigned* counters;  // [tiles]
+};
+
+struct DkLayer {
+    DkMat qkv[3];
+    int qkv_col[3];
+    DkMat wo, gu, down;
+    const float *attn_norm, *ffn_norm, *q_norm, *k_norm;
+    float *kc, *vc;  // this layer's KV cache [n_ctx][KD]
+};
+
+struct DkParams {
+    const DkLayer* layers;  // device array [n_layer]
+    int n_layer, n_qkv;     // every layer has the same number of qkv segments
+    DkMat head;
+    const float* output_norm;
+    const uint8_t* embd;    // token embedding table, tiled layout
+    int embd_type;
+    int E, F, H, HKV, rope_dim, n_ctx, nsplit;
+    float eps, scale;
+    int nl_qkv, nl_wo, nl_gu, nl_down;
+    const int32_t* token;   // device scalars
+    const int* pos;
+    const float* rope;      // [n_ctx][rope_dim/2][2]
+    float *x, *qkv, *att, *act, *logits;
+    double* ssq;            // [E/16] per-tile sums of squares of x
+    unsigned* amax;         // [n_layer][2] bit patterns of max|att|, max|act| of each layer, zero at launch
+    float* attn_part;       // [HKV][nsplit][group][130]
+    unsigned* attn_counters;  // [HKV]
+    unsigned* bar;          // grid barrier counter, zero at launch
+    int* err;               // raised when a barrier wait ran out
+    int slots;              // row-tile slots per warp in the reduction buffer
+    int n_max;              // longest activation vector
+};
+
+// one token at the position / token id stored on the device; the caller zeroes bar and amax before the launch.
+// slot_bytes: size of one ring slot (the largest unit of the step's matrices); grid: one CTA per SM.
+int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s);
+int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits);
+size_t decode_smem_bytes(const DkParams& p, int slot_bytes);
+int decode_threads();
+int decode_warps();
+
+}  // namespace elb

@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "split.cuh"
+#include "decode.cuh"
 
 namespace elb {
 
@@ -70,6 +71,14 @@ struct Model {
     int64_t last_launches = 0, launches = 0, graph_launches_ = 0;
     int last_rows = 1, decode_calls = 0;
     size_t weight_bytes = 0;
+    // persistent decode kernel (quantized models whose step fits in shared memory)
+    bool use_mega = false;
+    DkParams dk{};
+    DkLayer* dk_layers = nullptr;
+    int dk_slot = 0, dk_grid = 0;
+    double* ssq = nullptr;
+    unsigned* sync_words = nullptr;  // [1 + 2 n_layer]: barrier counter, then max|att|, max|act| per layer
+    int* err_host = nullptr;         // pinned, mapped: raised by the kernel when a barrier wait runs out
 };
 
 namespace {
@@ -229,6 +238,11 @@ int body_decode(Model* m) {
     const elb_config& c = m->cfg;
     const int E = c.n_embd, F = c.n_ff, H = c.n_head, HKV = c.n_head_kv, QD = H * 128, KD = HKV * 128;
     const float scale = 1.0f / std::sqrt(float(c.head_dim));
+    if (m->use_mega) {
+        ELB_CUDA(cudaMemsetAsync(m->sync_words, 0, size_t(1 + 2 * c.n_layer) * sizeof(unsigned), m->stream));
+        ++m->launches;
+        return decode_step_launch(m->dk, m->dk_slot, m->dk_grid, m->stream);
+    }
     auto quant = [](const Weight* w) { return w->type != ELB_F16; };
     auto qkv_quant = [&](const Layer& L) { bool q = false; for (auto& s : L.qkv) q |= quant(s.w); return q; };
     ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, 1, m->x, m->stream));
@@ -302,6 +316,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
     if (logits)
         ELB_CUDA(cudaMemcpyAsync(logits, m->logits, size_t(m->cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
+    if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
     float ms = 0.f;
     ELB_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->last_ms += ms;
@@ -309,6 +324,82 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
 }
 
 }  // namespace
+
+// Fill the parameters of the persistent decode kernel; it is used when every weight is quantized and the step's
+// shared memory (rings + the longest activation's limbs) fits on one SM. ELB_NO_MEGA=1 keeps the kernel-per-op path.
+int setup_decode_kernel(Model* m) {
+    const elb_config& c = m->cfg;
+    if (env_on("ELB_NO_MEGA")) return ELB_OK;
+    auto mat = [](const Weight* w) {
+        return DkMat{w->tiled, w->type, w->unit_bytes, int(w->tiles), int(w->units_per_tile), int(w->rows), int(w->n), w->part, w->counters};
+    };
+    bool quant = m->head->type != ELB_F16 && m->embd->type != ELB_F32;
+    const size_t nq = m->layers[0].qkv.size();
+    for (const Layer& L : m->layers) {
+        quant = quant && L.qkv.size() == nq && L.wo->type != ELB_F16 && L.gu->type != ELB_F16 && L.down->type != ELB_F16;
+        for (auto& s : L.qkv) quant = quant && s.w->type != ELB_F16;
+    }
+    const int E = c.n_embd, F = c.n_ff, QD = c.n_head * 128, KD = c.n_head_kv * 128;
+    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256) return ELB_OK;
+    DeviceInfo di;
+    ELB_TRY(device_info(m->device, &di));
+    DkParams& p = m->dk;
+    p = DkParams{};
+    std::vector<DkLayer> hl(size_t(c.n_layer));
+    int slot = m->head->unit_bytes;
+    int64_t max_units_cta = (m->head->tiles * m->head->units_per_tile + di.sm_count - 1) / di.sm_count;
+    int slots = 0;
+    auto account = [&](const Weight* w) {
+        slot = std::max(slot, w->unit_bytes);
+        const int64_t per_cta = (w->tiles * w->units_per_tile + di.sm_count - 1) / di.sm_count;
+        const int64_t per_warp = (per_cta + decode_warps() - 1) / decode_warps();
+        slots = std::max(slots, int((per_warp + w->units_per_tile - 1) / w->units_per_tile + 2));
+        (void)max_units_cta;
+    };
+    account(m->head);
+    for (int l = 0; l < c.n_layer; ++l) {
+        const Layer& L = m->layers[size_t(l)];
+        DkLayer& d = hl[size_t(l)];
+        for (size_t i = 0; i < nq; ++i) { d.qkv[i] = mat(L.qkv[i].w); d.qkv_col[i] = int(L.qkv[i].col); account(L.qkv[i].w); }
+        d.wo = mat(L.wo); d.gu = mat(L.gu); d.down = mat(L.down);
+        account(L.wo); account(L.gu); account(L.down);
+        d.attn_norm = L.attn_norm; d.ffn_norm = L.ffn_norm; d.q_norm = L.q_norm; d.k_norm = L.k_norm;
+        d.kc = m->kcache + size_t(l) * m->n_ctx * KD;
+        d.vc = m->vcache + size_t(l) * m->n_ctx * KD;
+    }
+    ELB_CUDA(cudaMalloc(&m->dk_layers, hl.size() * sizeof(DkLayer)));
+    ELB_CUDA(cudaMemcpy(m->dk_layers, hl.data(), hl.size() * sizeof(DkLayer), cudaMemcpyHostToDevice));
+    ELB_CUDA(cudaMalloc(&m->ssq, size_t(E / 16) * sizeof(double)));
+    ELB_CUDA(cudaMalloc(&m->sync_words, size_t(1 + 2 * c.n_layer) * sizeof(unsigned)));
+    ELB_CUDA(cudaHostAlloc(&m->err_host, sizeof(int), cudaHostAllocMapped));
+    *m->err_host = 0;
+    int* err_dev = nullptr;
+    ELB_CUDA(cudaHostGetDevicePointer(&err_dev, m->err_host, 0));
+    p.layers = m->dk_layers; p.n_layer = c.n_layer; p.n_qkv = int(nq);
+    p.head = mat(m->head); p.output_norm = m->output_norm;
+    p.embd = m->embd->tiled; p.embd_type = m->embd->type;
+    p.E = E; p.F = F; p.H = c.n_head; p.HKV = c.n_head_kv; p.rope_dim = c.rope_dim; p.n_ctx = m->n_ctx;
+    p.nsplit = std::max(1, std::min({32, m->attn_split, di.sm_count / c.n_head_kv}));
+    p.eps = c.eps; p.scale = 1.0f / std::sqrt(float(c.head_dim));
+    p.nl_qkv = m->nl_qkv; p.nl_wo = m->nl_wo; p.nl_gu = m->nl_gu; p.nl_down = m->nl_down;
+    p.token = m->tokens_dev; p.pos = m->pos_dev; p.rope = m->rope;
+    p.x = m->x; p.qkv = m->qkv; p.att = m->att; p.act = m->act; p.logits = m->logits;
+    p.ssq = m->ssq; p.bar = m->sync_words; p.amax = m->sync_words + 1;
+    p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
+    p.err = err_dev; p.slots = slots; p.n_max = std::max({E, F, QD});
+    m->dk_slot = (slot + 15) / 16 * 16;
+    m->dk_grid = di.sm_count;
+    // 32-bit unit arithmetic in the kernel
+    for (int l = 0; l < c.n_layer; ++l)
+        for (const Weight* w : {m->layers[size_t(l)].wo, m->layers[size_t(l)].gu, m->layers[size_t(l)].down, m->head})
+            if (w->tiles * w->units_per_tile * int64_t(di.sm_count) >= (int64_t(1) << 31) || w->max_grid < di.sm_count) return ELB_OK;
+    bool fits = false;
+    ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+    int coop = 0;
+    ELB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
+    m->use_mega = fits && coop;
+    return ELB_OK;
+}
 
 int model_create(const elb_config* cfg, int n_ctx, int device, Model** out) {
     if (!cfg || !out) return fail(ELB_ERR_INVALID, "model_create: null argument");
@@ -367,6 +458,8 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
+    cudaFree(m->dk_layers); cudaFree(m->ssq); cudaFree(m->sync_words);
+    if (m->err_host) cudaFreeHost(m->err_host);
     if (m->tokens_host) cudaFreeHost(m->tokens_host);
     if (m->pos_host) cudaFreeHost(m->pos_host);
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -491,6 +584,7 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->attn_part, size_t(c.n_head_kv) * m->attn_split * group * (128 + 2) * 4));
     ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(c.n_head_kv) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(c.n_head_kv) * sizeof(unsigned)));
+    ELB_TRY(setup_decode_kernel(m));
     m->pending.clear();
     m->pending.shrink_to_fit();
     m->finalized = true;
@@ -542,6 +636,7 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
     cudaFreeHost(pin);
     if (rc != ELB_OK) return rc;
     ELB_CUDA(e);
+    if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
     ELB_CUDA(cudaEventElapsedTime(device_ms, m->ev0, m->ev1));
     m->last_ms = *device_ms;
     m->last_launches = m->launches - before;

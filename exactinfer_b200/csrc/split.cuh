@@ -38,12 +38,14 @@ __host__ __device__ __forceinline__ size_t act_bytes(int n) { return size_t(4) *
 __host__ __device__ __forceinline__ size_t act_sd32_off(int n) { return size_t(4) * n; }
 __host__ __device__ __forceinline__ size_t act_sd16_off(int n) { return size_t(4) * n + size_t(n / 256) * 64; }
 
-// Four consecutive fixed-point values (index idx, a multiple of 4) -> one packed word of each of the 4 limbs, plus the
+// Four consecutive fixed-point values (index idx, a multiple of 4) -> one packed word of each of the 4 limbs (rows of
+// `stride` bytes at lim), plus the
 // limb sums of the enclosing 16- and 32-wide sub-blocks (shuffles over the 4 / 8 neighbouring lanes, which hold the rest
 // of the sub-block: every lane of the warp must call this together). Balanced base-256 digits: adding 128 at every
 // byte position turns them into the ordinary base-256 digits of v + 0x80808080, so the four limbs of one value are the
 // bytes of (v + 0x80808080) ^ 0x80808080; a 4x4 byte transpose then groups them by limb.
-__device__ __forceinline__ void split4(const float4& f, const Pow2 sc, int8_t* out, int n, int idx, bool valid) {
+__device__ __forceinline__ void split4(const float4& f, const Pow2 sc, int8_t* lim, int stride, int8_t* sd32, int8_t* sd16,
+                                       int idx, bool valid) {
     const uint32_t a = (uint32_t(__float2int_rn(f.x * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t b = (uint32_t(__float2int_rn(f.y * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t c = (uint32_t(__float2int_rn(f.z * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
@@ -53,11 +55,9 @@ __device__ __forceinline__ void split4(const float4& f, const Pow2 sc, int8_t* o
     const uint32_t w[4] = {__byte_perm(ab01, cd01, 0x5410), __byte_perm(ab01, cd01, 0x7632),   // limb 0, limb 1
                            __byte_perm(ab23, cd23, 0x5410), __byte_perm(ab23, cd23, 0x7632)};  // limb 2, limb 3
     const int lane = threadIdx.x & 31;
-    int8_t* sd32 = out + act_sd32_off(n);
-    int8_t* sd16 = out + act_sd16_off(n);
 #pragma unroll
     for (int l = 0; l < 4; ++l) {
-        if (valid) *reinterpret_cast<uint32_t*>(out + size_t(l) * n + idx) = w[l];
+        if (valid) *reinterpret_cast<uint32_t*>(lim + size_t(l) * stride + idx) = w[l];
         int s = __dp4a(int(w[l]), 0x01010101, 0);
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);  // sum over 16 values (lanes 4j..4j+3)
@@ -125,7 +125,7 @@ __device__ __forceinline__ void block_split(const float* src, int n, const float
 #pragma unroll
         for (int j = 0; j < SPLIT_V4; ++j) {
             const int idx = (j * SPLIT_THREADS + tid) * 4;
-            if (j * SPLIT_THREADS * 4 < n) split4(v[j], sc, out, n, idx, idx < n);  // warp-uniform guard: n % 128 == 0
+            if (j * SPLIT_THREADS * 4 < n) split4(v[j], sc, out, n, out + act_sd32_off(n), out + act_sd16_off(n), idx, idx < n);  // warp-uniform guard: n % 128 == 0
         }
     } else {  // long vectors: passes over src, the later ones served by cache
         float inv = 1.0f;
@@ -148,7 +148,7 @@ __device__ __forceinline__ void block_split(const float* src, int n, const float
         for (int i = tid * 4; i < n; i += SPLIT_THREADS * 4) {
             float4 f = __ldcg(reinterpret_cast<const float4*>(src + i));
             if (norm_w) f = norm4(f, inv, __ldg(reinterpret_cast<const float4*>(norm_w + i)));
-            split4(f, sc, out, n, i, true);
+            split4(f, sc, out, n, out + act_sd32_off(n), out + act_sd16_off(n), i, true);
         }
     }
     if (tid == 0) *inv_scale = k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);  // 2^-k
