@@ -42,8 +42,7 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
 __device__ __forceinline__ bool grid_barrier(const DkParams& p, int& nb, int* s_dead) {
     __syncthreads();
     if (threadIdx.x == 0 && !*s_dead) {
-        __threadfence();
-        atomicAdd(p.bar, 1u);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");  // orders the CTA's writes before it
         const unsigned target = unsigned(++nb) * gridDim.x;
         unsigned it = 0;
         while (ld_acquire(p.bar) < target) {
@@ -96,26 +95,61 @@ struct ActSmem {
 // (amax_bits, the bit pattern of a non-negative float). Returns inv_scale = 2^-k.
 __device__ float convert_act(const float* src, int n, const float* norm_w, const double* ssq, float eps,
                              const unsigned* amax_bits, int nl, const ActSmem& a, double* red) {
+    constexpr int V4 = 5;  // float4 per thread kept in registers: one pass over vectors of up to 10240 values
     const int tid = threadIdx.x;
-    float inv = 1.0f, m = 0.f;
-    if (norm_w) {
-        double ss = 0.0;
-        for (int i = tid; i < n / 16; i += DK_THREADS) ss += __ldcg(ssq + i);
-        ss = dk_block_sum(ss, red, tid);
-        inv = float(1.0 / sqrt(ss / n + double(eps)));
-        for (int i = tid * 4; i < n; i += DK_THREADS * 4)
-            m = fmaxf(m, absmax4(norm4(__ldcg(reinterpret_cast<const float4*>(src + i)), inv,
-                                       __ldg(reinterpret_cast<const float4*>(norm_w + i)))));
-        m = dk_block_max(m, reinterpret_cast<float*>(red), tid);
+    int k;
+    if (n <= V4 * 4 * DK_THREADS) {
+        // every load of the phase (vector, norm weight, statistics) is issued before the first use: one round trip
+        float4 v[V4], w[V4];
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int idx = (j * DK_THREADS + tid) * 4;
+            v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(src + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[j] = norm_w && idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float m = 0.f;
+        if (norm_w) {
+            double ss = 0.0;
+            for (int i = tid; i < n / 16; i += DK_THREADS) ss += __ldcg(ssq + i);
+            ss = dk_block_sum(ss, red, tid);
+            const float inv = float(1.0 / sqrt(ss / n + double(eps)));
+#pragma unroll
+            for (int j = 0; j < V4; ++j) {
+                v[j] = norm4(v[j], inv, w[j]);
+                m = fmaxf(m, absmax4(v[j]));
+            }
+            m = dk_block_max(m, reinterpret_cast<float*>(red), tid);
+        } else {
+            m = __uint_as_float(__ldcg(amax_bits));
+        }
+        k = split_shift(m, nl);
+        const Pow2 sc = make_pow2(k);
+#pragma unroll
+        for (int j = 0; j < V4; ++j) {
+            const int idx = (j * DK_THREADS + tid) * 4;
+            if (j * DK_THREADS * 4 < n) split4(v[j], sc, a.lim, a.n_pad, a.sd32, a.sd16, idx, idx < n);  // warp-uniform
+        }
     } else {
-        m = __uint_as_float(__ldcg(amax_bits));
-    }
-    const int k = split_shift(m, nl);
-    const Pow2 sc = make_pow2(k);
-    for (int i = tid * 4; i < n; i += DK_THREADS * 4) {  // warp-uniform trip count: n is a multiple of 128
-        float4 f = __ldcg(reinterpret_cast<const float4*>(src + i));
-        if (norm_w) f = norm4(f, inv, __ldg(reinterpret_cast<const float4*>(norm_w + i)));
-        split4(f, sc, a.lim, a.n_pad, a.sd32, a.sd16, i, true);
+        float inv = 1.0f, m = 0.f;
+        if (norm_w) {
+            double ss = 0.0;
+            for (int i = tid; i < n / 16; i += DK_THREADS) ss += __ldcg(ssq + i);
+            ss = dk_block_sum(ss, red, tid);
+            inv = float(1.0 / sqrt(ss / n + double(eps)));
+            for (int i = tid * 4; i < n; i += DK_THREADS * 4)
+                m = fmaxf(m, absmax4(norm4(__ldcg(reinterpret_cast<const float4*>(src + i)), inv,
+                                           __ldg(reinterpret_cast<const float4*>(norm_w + i)))));
+            m = dk_block_max(m, reinterpret_cast<float*>(red), tid);
+        } else {
+            m = __uint_as_float(__ldcg(amax_bits));
+        }
+        k = split_shift(m, nl);
+        const Pow2 sc = make_pow2(k);
+        for (int i = tid * 4; i < n; i += DK_THREADS * 4) {  // warp-uniform trip count: n is a multiple of 128
+            float4 f = __ldcg(reinterpret_cast<const float4*>(src + i));
+            if (norm_w) f = norm4(f, inv, __ldg(reinterpret_cast<const float4*>(norm_w + i)));
+            split4(f, sc, a.lim, a.n_pad, a.sd32, a.sd16, i, true);
+        }
     }
     __syncthreads();
     return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
@@ -131,15 +165,14 @@ __device__ __forceinline__ const DkMat& mat_at(const DkParams& p, int j) {
     return i < p.n_qkv ? L.qkv[i] : i == p.n_qkv ? L.wo : i == p.n_qkv + 1 ? L.gu : L.down;
 }
 
-// A matrix with fewer units than CTAs is shared by the first U CTAs only, so that every participating CTA owns work
-// (the arrival counts of shared tiles rely on it).
-struct WarpRange { int cA, cB, wA, wB, G; };
+// Whole row tiles per CTA (no tile is shared between CTAs, so a phase ends without any cross-CTA reduction); a matrix
+// with fewer tiles than CTAs occupies the first CTAs only. Within the CTA the warps cut the units into equal ranges.
+struct WarpRange { int cA, cB, wA, wB; };
 __device__ __forceinline__ WarpRange warp_range(const DkMat& m, int warp) {
-    const int U = m.tiles * m.upt, G = min(int(gridDim.x), U), c = blockIdx.x;
+    const int G = min(int(gridDim.x), m.tiles), c = blockIdx.x;
     WarpRange r;
-    r.G = G;
-    r.cA = c < G ? range_lo(U, G, c) : 0;
-    r.cB = c < G ? range_lo(U, G, c + 1) : 0;
+    r.cA = c < G ? range_lo(m.tiles, G, c) * m.upt : 0;
+    r.cB = c < G ? range_lo(m.tiles, G, c + 1) * m.upt : 0;
     r.wA = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp);
     r.wB = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp + 1);
     return r;
@@ -271,12 +304,9 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
         default: run_units<ELB_Q8_0>(p, m, r, pf, rs, s, warp, lane); break;
     }
     __syncthreads();
-    const int U = m.tiles * upt, G = r.G, c = blockIdx.x;
     if (r.cA < r.cB) {
-        const int Xf = r.cA / upt, Xl = (r.cB - 1) / upt, ntl = Xl - Xf + 1;
-        const bool part_first = Xf * upt < r.cA || (Xf + 1) * upt > r.cB;
-        const bool part_last = Xl != Xf && (Xl + 1) * upt > r.cB;
-        for (int e = tid; e < ntl * 8; e += DK_THREADS) {
+        const int Xf = r.cA / upt, ntl = (r.cB - r.cA) / upt;
+        for (int e = tid; e < ntl * 8; e += DK_THREADS) {  // sums over the warps in warp order, then the epilogue
             const int Xt = Xf + (e >> 3), gg = e & 7;
             float v0 = 0.f, v1 = 0.f;
 #pragma unroll
@@ -286,59 +316,16 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
                 v0 += s.red[(w * p.slots + (Xt - f)) * 16 + gg];
                 v1 += s.red[(w * p.slots + (Xt - f)) * 16 + gg + 8];
             }
-            const bool partial = (Xt == Xf && part_first) || (Xt == Xl && part_last);
-            if (!partial) {
-                float o0, o1;
-                dk_epilogue(epi, m, y, Xt, gg, v0 * inv_scale, v1 * inv_scale, o0, o1);
-                dk_tile_stats(epi, p, s, e >> 3, gg, o0, o1);
-            } else {
-                float* dst = m.part + (c * 2 + (Xt == Xf ? 0 : 1)) * 16;
-                dst[gg] = v0;
-                dst[gg + 8] = v1;
-            }
+            float o0, o1;
+            dk_epilogue(epi, m, y, Xt, gg, v0 * inv_scale, v1 * inv_scale, o0, o1);
+            dk_tile_stats(epi, p, s, e >> 3, gg, o0, o1);
         }
-        if (part_first || part_last) {  // uniform over the CTA
-            __threadfence();
+        if (epi == DK_EPI_ADD_SSQ) {  // per-tile sums of squares, rows in order, in double (RMSNorm of the next phase)
             __syncthreads();
-            if (tid < 2) {
-                s.flags[tid] = 0;
-                if (tid == 0 ? part_first : part_last) {
-                    const int Xt = tid == 0 ? Xf : Xl;
-                    const int c_lo = ((Xt * upt + 1) * G - 1) / U, c_hi = ((Xt + 1) * upt * G - 1) / U;
-                    const unsigned old = atomicAdd(&m.counters[Xt], 1u);
-                    if (old == unsigned(c_hi - c_lo)) {
-                        s.flags[tid] = 1;
-                        m.counters[Xt] = 0;
-                    }
-                }
-            }
-            __syncthreads();
-            if (s.flags[0] || s.flags[1]) __threadfence();
-            if (tid < 16 && s.flags[tid >> 3]) {
-                const int i = tid >> 3, gg = tid & 7, Xt = i == 0 ? Xf : Xl;
-                const int c_lo = ((Xt * upt + 1) * G - 1) / U, c_hi = ((Xt + 1) * upt * G - 1) / U;
-                float v0 = 0.f, v1 = 0.f;
-                for (int cc = c_lo; cc <= c_hi; ++cc) {  // fixed CTA order
-                    const int first_tile = range_lo(U, G, cc) / upt;
-                    const float* srcp = m.part + (cc * 2 + (Xt == first_tile ? 0 : 1)) * 16;
-                    v0 += __ldcg(srcp + gg);
-                    v1 += __ldcg(srcp + gg + 8);
-                }
-                float o0, o1;
-                dk_epilogue(epi, m, y, Xt, gg, v0 * inv_scale, v1 * inv_scale, o0, o1);
-                dk_tile_stats(epi, p, s, i == 0 ? 0 : ntl - 1, gg, o0, o1);
-            }
-        }
-        __syncthreads();
-        // per-tile sums of squares of the finished tiles, rows in order, in double (RMSNorm of the next phase)
-        if (epi == DK_EPI_ADD_SSQ) {
             for (int e = tid; e < ntl; e += DK_THREADS) {
-                const int Xt = Xf + e;
-                const bool partial = (Xt == Xf && part_first) || (Xt == Xl && part_last);
-                if (partial && !s.flags[Xt == Xf ? 0 : 1]) continue;  // finished elsewhere
                 double ss = 0.0;
                 for (int q = 0; q < 16; ++q) { const double v = s.sq[e * 16 + q]; ss += v * v; }
-                ssq_out[Xt] = ss;
+                ssq_out[Xf + e] = ss;
             }
         }
     }
@@ -524,6 +511,14 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
 
 // ---------------------------------------------------------------- the step
 
+__device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.prof[l * 16 + ev] = t;
+    }
+}
+
 constexpr int DK_SQ_TILES = 8;
 constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * (DK_HD + 1) + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
 
@@ -602,33 +597,48 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     for (int l = 0; l < p.n_layer && ok; ++l) {
         const DkLayer& L = p.layers[l];
         unsigned* amax = p.amax + 2 * l;
+        dk_stamp(p, l, 0);
         {
             s.act = act_for(p.E);
             const float inv = convert_act(p.x, p.E, L.attn_norm, p.ssq, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
+            dk_stamp(p, l, 1);
             for (int i = 0; i < p.n_qkv; ++i)
                 matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr, nullptr);
         }
+        dk_stamp(p, l, 2);
         if (!(ok = grid_barrier(p, nb, dead))) break;
+        dk_stamp(p, l, 3);
         attn_phase(p, L, as, amax);
+        dk_stamp(p, l, 4);
         if (!(ok = grid_barrier(p, nb, dead))) break;
+        dk_stamp(p, l, 5);
         {
             s.act = act_for(p.H * DK_HD);
             const float inv = convert_act(p.att, p.H * DK_HD, nullptr, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
+            dk_stamp(p, l, 6);
             matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
         }
+        dk_stamp(p, l, 7);
         if (!(ok = grid_barrier(p, nb, dead))) break;
+        dk_stamp(p, l, 8);
         {
             s.act = act_for(p.E);
             const float inv = convert_act(p.x, p.E, L.ffn_norm, p.ssq, p.eps, nullptr, p.nl_gu, s.act, s.red8);
+            dk_stamp(p, l, 9);
             matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, nullptr, amax + 1);
         }
+        dk_stamp(p, l, 10);
         if (!(ok = grid_barrier(p, nb, dead))) break;
+        dk_stamp(p, l, 11);
         {
             s.act = act_for(p.F);
             const float inv = convert_act(p.act, p.F, nullptr, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
+            dk_stamp(p, l, 12);
             matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
         }
+        dk_stamp(p, l, 13);
         ok = grid_barrier(p, nb, dead);
+        dk_stamp(p, l, 14);
     }
     if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference)
         s.act = act_for(p.E);

@@ -42,6 +42,7 @@ struct DkParams {
     int* err;               // raised when a barrier wait ran out
     int slots;              // row-tile slots per warp in the reduction buffer
     int n_max;              // longest activation vector
+    unsigned long long* prof;  // diagnostics (ELB_DK_PROF=1): [n_layer][16] nanosecond stamps of CTA 0, else null
 };
 
 // one token at the position / token id stored on the device; the caller zeroes bar and amax before the launch.

@@ -340,7 +340,7 @@ int setup_decode_kernel(Model* m) {
         for (auto& s : L.qkv) quant = quant && s.w->type != ELB_F16;
     }
     const int E = c.n_embd, F = c.n_ff, QD = c.n_head * 128, KD = c.n_head_kv * 128;
-    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256) return ELB_OK;
+    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || (E / 16 + 147) / 148 > 8) return ELB_OK;
     DeviceInfo di;
     ELB_TRY(device_info(m->device, &di));
     DkParams& p = m->dk;
@@ -351,7 +351,7 @@ int setup_decode_kernel(Model* m) {
     int slots = 0;
     auto account = [&](const Weight* w) {
         slot = std::max(slot, w->unit_bytes);
-        const int64_t per_cta = (w->tiles * w->units_per_tile + di.sm_count - 1) / di.sm_count;
+        const int64_t per_cta = (w->tiles + di.sm_count - 1) / di.sm_count * w->units_per_tile;
         const int64_t per_warp = (per_cta + decode_warps() - 1) / decode_warps();
         slots = std::max(slots, int((per_warp + w->units_per_tile - 1) / w->units_per_tile + 2));
         (void)max_units_cta;
@@ -398,6 +398,10 @@ int setup_decode_kernel(Model* m) {
     int coop = 0;
     ELB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
     m->use_mega = fits && coop;
+    if (m->use_mega && env_on("ELB_DK_PROF")) {
+        ELB_CUDA(cudaMalloc(&p.prof, size_t(c.n_layer) * 16 * sizeof(unsigned long long)));
+        ELB_CUDA(cudaMemset(p.prof, 0, size_t(c.n_layer) * 16 * sizeof(unsigned long long)));
+    }
     return ELB_OK;
 }
 
@@ -640,6 +644,19 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
     ELB_CUDA(cudaEventElapsedTime(device_ms, m->ev0, m->ev1));
     m->last_ms = *device_ms;
     m->last_launches = m->launches - before;
+    if (m->use_mega && m->dk.prof) {  // diagnostics: phase times of the last step, CTA 0, averaged over the layers
+        std::vector<unsigned long long> t(size_t(m->cfg.n_layer) * 16);
+        cudaMemcpy(t.data(), m->dk.prof, t.size() * 8, cudaMemcpyDeviceToHost);
+        static const char* names[15] = {"", "convert qkv", "matvec qkv", "barrier", "attention", "barrier", "convert wo", "matvec wo", "barrier", "convert gu", "matvec gu", "barrier", "convert down", "matvec down", "barrier"};
+        double layer_total = 0;
+        for (int ev = 1; ev < 15; ++ev) {
+            double sum = 0;
+            for (int l = 0; l < m->cfg.n_layer; ++l) sum += double(t[size_t(l) * 16 + ev] - t[size_t(l) * 16 + ev - 1]);
+            std::fprintf(stderr, "[dk prof] %-13s %7.2f us\n", names[ev], sum / m->cfg.n_layer / 1000.0);
+            layer_total += sum / m->cfg.n_layer / 1000.0;
+        }
+        std::fprintf(stderr, "[dk prof] layer total   %7.2f us\n", layer_total);
+    }
     m->last_rows = 1;
     return ELB_OK;
 }
