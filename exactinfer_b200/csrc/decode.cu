@@ -155,6 +155,14 @@ __device__ float convert_act(const float* src, int n, const float* norm_w, const
     return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
 }
 
+__device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.prof[l * 32 + ev] = t;
+    }
+}
+
 // ---------------------------------------------------------------- the unit stream of one warp
 
 // Matrices of the step in execution order: per layer qkv segments, wo, gate|up, down; then the head.
@@ -206,6 +214,18 @@ __device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8
     ring_commit();
 }
 
+// Same walk, further ahead, into L2 only: the second cursor of a warp runs `l2_ahead` units (about one layer) in front
+// of its ring, so that HBM streams at an even rate through the phases that consume nothing (attention, conversion,
+// barriers) and the ring refills at L2 latency. One 128-byte line per lane.
+__device__ __forceinline__ void cursor_prefetch_l2(const DkParams& p, Cursor& c, int warp, int lane) {
+    if (c.j >= c.n_mats) return;
+    if (lane * 128 < c.unit_bytes) asm volatile("prefetch.global.L2 [%0];" ::"l"(c.W + size_t(c.u) * c.unit_bytes + lane * 128));
+    if (++c.u == c.end) {
+        ++c.j;
+        cursor_seek(p, c, warp);
+    }
+}
+
 // ---------------------------------------------------------------- one matvec phase
 
 enum { DK_EPI_STORE = 0, DK_EPI_ADD_SSQ = 1, DK_EPI_SILU_AMAX = 2 };
@@ -253,8 +273,8 @@ __device__ __forceinline__ void dk_tile_stats(int epi, const DkParams& p, const 
 }
 
 template <int TYPE>
-__device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, int& rs, const PhaseSmem& s,
-                          int warp, int lane) {
+__device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, Cursor& pl2, int& rs,
+                          const PhaseSmem& s, int warp, int lane) {
     const int g = lane >> 2, t = lane & 3, upt = m.upt;
     const int8_t* sd = TYPE == ELB_Q6_K ? s.act.sd16 : s.act.sd32;
     Acc a{{0.f, 0.f}, {0.f, 0.f}};
@@ -265,6 +285,7 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
     const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
     DbgOut dbg{nullptr, nullptr, nullptr, 0, 0, 0, 0};
     for (int u = r.wA; u < r.wB; ++u) {
+        cursor_prefetch_l2(p, pl2, warp, lane);
         cursor_issue(p, pf, s.ring + (rs == 0 ? DK_DEPTH - 1 : rs - 1) * s.slot_bytes, warp, lane);
         ring_wait<DK_DEPTH - 1>();
         __syncwarp();
@@ -292,18 +313,23 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
 
 // y (+)= W * act for one matrix; the activation limbs are already in shared memory. Ends with every row of this
 // CTA's share written (tiles shared with a neighbour: by whichever CTA arrives last).
-__device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf, int& rs,
-                             const PhaseSmem& s, double* ssq_out, unsigned* amax_out) {
+__device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf, Cursor& pl2,
+                             int& rs, const PhaseSmem& s, double* ssq_out, unsigned* amax_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
     const WarpRange r = warp_range(m, warp);
+    const int pl = epi == DK_EPI_SILU_AMAX ? int(amax_out - p.amax) / 2 : -1;
+    if (pl >= 0) dk_stamp(p, pl, 16);
     if (tid == 0) s.flags[3] = 0;
     __syncthreads();
+    if (pl >= 0) dk_stamp(p, pl, 17);
     switch (m.type) {
-        case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, rs, s, warp, lane); break;
-        case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, rs, s, warp, lane); break;
-        default: run_units<ELB_Q8_0>(p, m, r, pf, rs, s, warp, lane); break;
+        case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, pl2, rs, s, warp, lane); break;
+        case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, pl2, rs, s, warp, lane); break;
+        default: run_units<ELB_Q8_0>(p, m, r, pf, pl2, rs, s, warp, lane); break;
     }
+    if (pl >= 0) dk_stamp(p, pl, 18);
     __syncthreads();
+    if (pl >= 0) dk_stamp(p, pl, 19);
     if (r.cA < r.cB) {
         const int Xf = r.cA / upt, ntl = (r.cB - r.cA) / upt;
         for (int e = tid; e < ntl * 8; e += DK_THREADS) {  // sums over the warps in warp order, then the epilogue
@@ -329,6 +355,7 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
             }
         }
     }
+    if (pl >= 0) dk_stamp(p, pl, 20);
     if (epi == DK_EPI_SILU_AMAX) {
         __syncthreads();
         if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
@@ -511,14 +538,6 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
 
 // ---------------------------------------------------------------- the step
 
-__device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        p.prof[l * 16 + ev] = t;
-    }
-}
-
 constexpr int DK_SQ_TILES = 8;
 constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * (DK_HD + 1) + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
 
@@ -569,6 +588,8 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     cursor_seek(p, pf, warp);
 #pragma unroll
     for (int d = 0; d < DK_DEPTH - 1; ++d) cursor_issue(p, pf, s.ring + d * slot_bytes, warp, lane);
+    Cursor pl2 = pf;  // (pf has already moved DEPTH-1 units on; those lines are on their way anyway)
+    for (int i = 0; i < p.l2_ahead; ++i) cursor_prefetch_l2(p, pl2, warp, lane);
     int rs = 0, nb = 0;
     int* dead = &s.flags[2];
 
@@ -603,7 +624,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             const float inv = convert_act(p.x, p.E, L.attn_norm, p.ssq, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
             dk_stamp(p, l, 1);
             for (int i = 0; i < p.n_qkv; ++i)
-                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr, nullptr);
+                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, pl2, rs, s, nullptr, nullptr);
         }
         dk_stamp(p, l, 2);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -616,7 +637,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.H * DK_HD);
             const float inv = convert_act(p.att, p.H * DK_HD, nullptr, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
             dk_stamp(p, l, 6);
-            matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
+            matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, pl2, rs, s, p.ssq, nullptr);
         }
         dk_stamp(p, l, 7);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -625,7 +646,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.E);
             const float inv = convert_act(p.x, p.E, L.ffn_norm, p.ssq, p.eps, nullptr, p.nl_gu, s.act, s.red8);
             dk_stamp(p, l, 9);
-            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, nullptr, amax + 1);
+            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, pl2, rs, s, nullptr, amax + 1);
         }
         dk_stamp(p, l, 10);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -634,7 +655,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.F);
             const float inv = convert_act(p.act, p.F, nullptr, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
             dk_stamp(p, l, 12);
-            matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
+            matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, pl2, rs, s, p.ssq, nullptr);
         }
         dk_stamp(p, l, 13);
         ok = grid_barrier(p, nb, dead);
@@ -643,7 +664,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference)
         s.act = act_for(p.E);
         const float inv = convert_act(p.x, p.E, p.output_norm, p.ssq, p.eps, nullptr, 4, s.act, s.red8);
-        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr, nullptr);
+        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, pl2, rs, s, nullptr, nullptr);
     }
     ring_wait<0>();
 }

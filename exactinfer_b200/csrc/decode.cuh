@@ -42,6 +42,7 @@ struct DkParams {
     int* err;               // raised when a barrier wait ran out
     int slots;              // row-tile slots per warp in the reduction buffer
     int n_max;              // longest activation vector
+    int l2_ahead;           // units (per warp) that the L2 prefetch runs in front of the shared-memory ring
     unsigned long long* prof;  // diagnostics (ELB_DK_PROF=1): [n_layer][16] nanosecond stamps of CTA 0, else null
 };
 

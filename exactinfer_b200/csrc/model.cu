@@ -387,6 +387,14 @@ int setup_decode_kernel(Model* m) {
     p.ssq = m->ssq; p.bar = m->sync_words; p.amax = m->sync_words + 1;
     p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
     p.err = err_dev; p.slots = slots; p.n_max = std::max({E, F, QD});
+    {   // about one layer's worth of units per warp in front (a layer of the 4B shape is 58 MB; L2 holds 126 MB)
+        int64_t layer_units = 0;
+        const Layer& L0 = m->layers[0];
+        for (auto& sgm : L0.qkv) layer_units += sgm.w->tiles * sgm.w->units_per_tile;
+        for (const Weight* w : {L0.wo, L0.gu, L0.down}) layer_units += w->tiles * w->units_per_tile;
+        p.l2_ahead = int(std::max<int64_t>(2, layer_units / (int64_t(di.sm_count) * decode_warps())));
+        if (const char* v = std::getenv("ELB_DK_L2AHEAD")) p.l2_ahead = std::max(0, std::atoi(v));
+    }
     m->dk_slot = (slot + 15) / 16 * 16;
     m->dk_grid = di.sm_count;
     // 32-bit unit arithmetic in the kernel
@@ -399,8 +407,8 @@ int setup_decode_kernel(Model* m) {
     ELB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
     m->use_mega = fits && coop;
     if (m->use_mega && env_on("ELB_DK_PROF")) {
-        ELB_CUDA(cudaMalloc(&p.prof, size_t(c.n_layer) * 16 * sizeof(unsigned long long)));
-        ELB_CUDA(cudaMemset(p.prof, 0, size_t(c.n_layer) * 16 * sizeof(unsigned long long)));
+        ELB_CUDA(cudaMalloc(&p.prof, size_t(c.n_layer) * 32 * sizeof(unsigned long long)));
+        ELB_CUDA(cudaMemset(p.prof, 0, size_t(c.n_layer) * 32 * sizeof(unsigned long long)));
     }
     return ELB_OK;
 }
@@ -645,17 +653,22 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
     m->last_ms = *device_ms;
     m->last_launches = m->launches - before;
     if (m->use_mega && m->dk.prof) {  // diagnostics: phase times of the last step, CTA 0, averaged over the layers
-        std::vector<unsigned long long> t(size_t(m->cfg.n_layer) * 16);
+        std::vector<unsigned long long> t(size_t(m->cfg.n_layer) * 32);
         cudaMemcpy(t.data(), m->dk.prof, t.size() * 8, cudaMemcpyDeviceToHost);
         static const char* names[15] = {"", "convert qkv", "matvec qkv", "barrier", "attention", "barrier", "convert wo", "matvec wo", "barrier", "convert gu", "matvec gu", "barrier", "convert down", "matvec down", "barrier"};
         double layer_total = 0;
         for (int ev = 1; ev < 15; ++ev) {
             double sum = 0;
-            for (int l = 0; l < m->cfg.n_layer; ++l) sum += double(t[size_t(l) * 16 + ev] - t[size_t(l) * 16 + ev - 1]);
+            for (int l = 0; l < m->cfg.n_layer; ++l) sum += double(t[size_t(l) * 32 + ev] - t[size_t(l) * 32 + ev - 1]);
             std::fprintf(stderr, "[dk prof] %-13s %7.2f us\n", names[ev], sum / m->cfg.n_layer / 1000.0);
             layer_total += sum / m->cfg.n_layer / 1000.0;
         }
         std::fprintf(stderr, "[dk prof] layer total   %7.2f us\n", layer_total);
+        for (int ev = 17; ev <= 20; ++ev) {
+            double sum = 0;
+            for (int l = 0; l < m->cfg.n_layer; ++l) sum += double(t[size_t(l) * 32 + ev] - t[size_t(l) * 32 + ev - 1]);
+            std::fprintf(stderr, "[dk prof] gu inner %d    %7.2f us\n", ev, sum / m->cfg.n_layer / 1000.0);
+        }
     }
     m->last_rows = 1;
     return ELB_OK;
