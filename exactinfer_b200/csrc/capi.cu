@@ -158,6 +158,7 @@ static int matmul_dev_on(const Weight* w, const float* d_x, int64_t b, float* d_
     float* inv = reinterpret_cast<float*>(limbs + inv_off);
     float* xs = reinterpret_cast<float*>(limbs + xs_off);
     ELB_TRY(split_launch(d_x, w->n, b, int(w->n), nl == 0 ? 4 : nl, nullptr, 0.f, limbs, inv, xs, s));
+    if (gemm_tc_usable(w, int(b))) return gemm_tc_launch(w, limbs, inv, xs, int(b), nl == 0 ? 4 : nl, d_y, w->rows, nullptr, EPI_STORE, s);
     return gemm_planes_launch(w, limbs, inv, xs, int(b), d_y, w->rows, nullptr, EPI_STORE, s);
 }
 
@@ -167,7 +168,7 @@ int elb_matmul_dev(const elb_weight* w, const float* d_x, int64_t b, float* d_y,
     Dev scratch;
     ELB_TRY(matmul_dev_on(W(w), d_x, b, d_y, nl, nullptr, &scratch));
     ELB_CUDA(cudaStreamSynchronize(nullptr));
-    return ELB_OK;
+    return gemm_tc_check();
 }
 int elb_matmul(const elb_weight* w, const float* x, int64_t b, float* y, int nl) {
     if (!w || !x || !y) return fail(ELB_ERR_INVALID, "matmul: null argument");

@@ -1,0 +1,369 @@
+// Prompt-chunk linear layer on the 5th-generation tensor cores: Y[token][row] = sum_k W[row][k] * x[token][k] with
+// W = W0 + 256 W1 (int8 digit planes of the integer weight sc*q, built at upload) and x = 2^-k * sum_l a_l 256^l
+// (int8 limbs), every product exact in int32.
+//
+// One tcgen05 accumulator holds all digit products of equal weight 256^j: column (j, token) accumulates
+// W0 . a_j + W1 . a_(j-1), j = 0..NL. Both MMAs of a k-step read the limb tile from the same shared-memory buffer:
+// its rows are ordered (limb, token) with a block of T zero rows in front and behind, and the operand of the W1
+// product is simply the same buffer addressed T rows earlier. So a 128-row x T-token tile costs 2 MMAs of
+// M=128, N=(NL+1)T, K=32 per 32 k, one accumulator of (NL+1)T TMEM columns (two, for double buffering), and the limb
+// combination sum_j 256^j R_j is one Horner chain per (row, token) per 256-block in the epilogue, where the fp16
+// block scale d (and Q4_K's dmin*m term) is applied in fp32.
+//
+// Warp roles (192 threads): warps 0-3 epilogue (TMEM lanes = weight rows), warp 4 TMA producer, warp 5 MMA issuer and
+// TMEM owner. Operands arrive by TMA (no multicast) into a 3-stage ring of
+// 128-byte-swizzled K-major tiles; TMEM accumulators are double buffered so that the drain of one 256-block overlaps
+// the MMAs of the next. Every mbarrier wait is bounded: on timeout the kernel raises an error word and winds down.
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace elb {
+
+constexpr int TC_ROWS = 128, TC_KSTAGE = 128, TC_STAGES = 3, TC_THREADS = 192;
+constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
+
+// ---------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait; false when it ran out (the error word is raised by the caller)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t a = smem_u32(bar);
+    for (unsigned it = 0; it < TC_SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, int8 x int8 -> int32, issued by one thread
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the mbarrier gets one arrival when every MMA issued so far by this thread has completed
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 16 consecutive columns of this warp's 32 TMEM lanes -> 16 registers per thread (thread = lane = weight row)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle; 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= uint64_t((saddr & 0x3FFFF) >> 4);  // start address, 16-byte units
+    d |= uint64_t(1024 >> 4) << 32;         // stride between 8-row groups
+    d |= uint64_t(1) << 46;                 // descriptor version of this architecture
+    d |= uint64_t(2) << 61;                 // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor for kind::i8: int32 accumulator, signed 8-bit A and B, both K-major, M x N
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- the kernel
+
+struct TcParams {
+    const __half* pl_d;      // [rows16][n/256] block scale
+    const float* pl_dm;      // Q4_K: [rows16][n/32] fl(dmin*m); else null
+    const float* xsum;       // [B][n/32] sum of the fixed-point activation over each 32-slice
+    const float* inv_scale;  // [B] 2^-k
+    float* Y;
+    const float* resid;
+    int64_t rows16, rows, ldy;
+    int B, n, epilogue;
+    int* err;
+};
+
+template <int NL> struct TcShape {
+    static constexpr int T = NL == 4 ? 48 : 64;       // tokens per tile
+    static constexpr int N = (NL + 1) * T;            // accumulator columns: (digit weight j, token)
+    static constexpr int ZB = T * 128;                // one block of zero rows
+    static constexpr int LB = NL * T * 128;           // limb rows of one stage
+    static constexpr int A_BYTES = TC_ROWS * 128;     // one plane tile of one stage
+    static constexpr int LIMB_AREA = ZB + TC_STAGES * (LB + ZB);
+    static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + 1024;  // + barriers + alignment slack
+};
+
+template <int NL>
+__global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapW,
+                                                          const __grid_constant__ CUtensorMap mapX, const TcParams p) {
+    using S = TcShape<NL>;
+    constexpr int T = S::T, N = S::N;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* limb_area = smem;
+    uint8_t* a_area = smem + S::LIMB_AREA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(a_area + TC_STAGES * 2 * S::A_BYTES);
+    uint64_t* full = bars;                   // [TC_STAGES] TMA -> MMA
+    uint64_t* empty = bars + TC_STAGES;      // [TC_STAGES] MMA -> TMA
+    uint64_t* tfull = bars + 2 * TC_STAGES;  // [2] MMA -> epilogue
+    uint64_t* tempty = tfull + 2;            // [2] epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row0 = blockIdx.x * TC_ROWS, tok0 = blockIdx.y * T;
+    const int nk = p.n / TC_KSTAGE, nkb = p.n / 256;
+
+    // zero blocks in front of, between and behind the limb stages
+    for (int z = 0; z <= TC_STAGES; ++z) {
+        uint4* zp = reinterpret_cast<uint4*>(limb_area + z * (S::LB + S::ZB));
+        for (int i = tid; i < S::ZB / 16; i += TC_THREADS) zp[i] = make_uint4(0, 0, 0, 0);
+    }
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zero rows are read by the tensor core
+    if (warp == 5) tmem_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 4) {
+        if (lane == 0) {  // ---- TMA producer
+            for (int kt = 0; kt < nk && ok; ++kt) {
+                const int s = kt % TC_STAGES;
+                ok = mbar_wait(empty + s, ((kt / TC_STAGES) & 1) ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(full + s, 2 * S::A_BYTES + S::LB);
+                const int k0 = kt * TC_KSTAGE;
+                tma_load_3d(a_area + (s * 2 + 0) * S::A_BYTES, &mapW, k0, row0, 0, full + s);
+                tma_load_3d(a_area + (s * 2 + 1) * S::A_BYTES, &mapW, k0, row0, 1, full + s);
+                uint8_t* lb = limb_area + S::ZB + s * (S::LB + S::ZB);
+                for (int l = 0; l < NL; ++l) tma_load_3d(lb + l * S::ZB, &mapX, k0, tok0, l, full + s);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {  // ---- MMA issuer
+            constexpr uint32_t idesc = idesc_i8(TC_ROWS, N);
+            for (int kt = 0; kt < nk && ok; ++kt) {
+                const int s = kt % TC_STAGES, kb = kt >> 1, acc = kb & 1;
+                if ((kt & 1) == 0) {  // first half of a 256-block: its accumulator must have been drained
+                    ok = mbar_wait(tempty + acc, ((kb >> 1) & 1) ^ 1);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(full + s, (kt / TC_STAGES) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(a_area + (s * 2 + 0) * S::A_BYTES), a1 = a0 + S::A_BYTES;
+                const uint32_t b0 = smem_u32(limb_area + S::ZB + s * (S::LB + S::ZB)), b1 = b0 - S::ZB;
+                const uint32_t d = tmem_base + acc * 256;
+#pragma unroll
+                for (int ks = 0; ks < TC_KSTAGE / 32; ++ks) {
+                    mma_i8(d, smem_desc(a0 + ks * 32), smem_desc(b0 + ks * 32), idesc, ((kt & 1) | ks) != 0);
+                    mma_i8(d, smem_desc(a1 + ks * 32), smem_desc(b1 + ks * 32), idesc, 1);
+                }
+                mma_commit(empty + s);                    // the stage is free once these MMAs have read it
+                if (kt & 1) mma_commit(tfull + acc);      // the 256-block is complete
+            }
+        }
+    } else {  // ---- epilogue: warp w owns TMEM lanes 32w..32w+31 = weight rows row0 + 32w + lane
+        const int64_t R = row0 + warp * 32 + lane;
+        const bool row_ok = R < p.rows16;
+        const int nblk = p.n / 256, nsub = p.n / 32;
+        float accf[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) accf[t] = 0.f;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int acc = kb & 1;
+            ok = mbar_wait(tfull + acc, (kb >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const float d = row_ok ? __half2float(p.pl_d[R * nblk + kb]) : 0.f;
+            const uint32_t tbase = tmem_base + acc * 256 + (uint32_t(warp * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < T / 16; ++c) {
+                int v[NL + 1][16];
+#pragma unroll
+                for (int j = 0; j <= NL; ++j) tmem_ld16(tbase + j * T + c * 16, v[j]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    float f = float(v[NL][t]);
+#pragma unroll
+                    for (int j = NL - 1; j >= 0; --j) f = fmaf(f, 256.0f, float(v[j][t]));
+                    accf[c * 16 + t] = fmaf(d, f, accf[c * 16 + t]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty + acc);  // accumulator drained: the issuer may overwrite it
+            if (p.pl_dm) {  // Q4_K: minus sum over the 8 sub-blocks of fl(dmin*m) * sum(X)
+                float dm[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) dm[q] = row_ok ? __ldg(p.pl_dm + R * nsub + kb * 8 + q) : 0.f;
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const int tok = min(tok0 + t, p.B - 1);
+                    const float4 x0 = __ldg(reinterpret_cast<const float4*>(p.xsum + int64_t(tok) * nsub + kb * 8));
+                    const float4 x1 = __ldg(reinterpret_cast<const float4*>(p.xsum + int64_t(tok) * nsub + kb * 8 + 4));
+                    float s = dm[0] * x0.x;
+                    s = fmaf(dm[1], x0.y, s); s = fmaf(dm[2], x0.z, s); s = fmaf(dm[3], x0.w, s);
+                    s = fmaf(dm[4], x1.x, s); s = fmaf(dm[5], x1.y, s); s = fmaf(dm[6], x1.z, s); s = fmaf(dm[7], x1.w, s);
+                    accf[t] -= s;
+                }
+            }
+        }
+        if (ok) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const int tok = tok0 + t;
+                const bool tok_ok = tok < p.B;
+                const float y = accf[t] * (tok_ok ? __ldg(p.inv_scale + tok) : 0.f);
+                if (p.epilogue == EPI_SILU) {  // tile rows 0..7 gate, 8..15 up (16-row groups): partner is 8 lanes up
+                    const float up = __shfl_down_sync(0xffffffffu, y, 8);
+                    const int64_t o = R / 16 * 8 + (R & 7);
+                    if (tok_ok && (lane & 8) == 0 && o < p.rows / 2)
+                        p.Y[int64_t(tok) * p.ldy + o] = __fmul_rn(__fdiv_rn(y, 1.0f + expf(-y)), up);
+                } else if (tok_ok && R < p.rows) {
+                    const int64_t o = int64_t(tok) * p.ldy + R;
+                    p.Y[o] = p.epilogue == EPI_ADD ? p.resid[o] + y : y;
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(p.err, 2);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------- host side
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// int8 tensor [d2][d1][k] (k contiguous), box [1][box1][128], 128-byte swizzle, zero fill outside
+int make_map(CUtensorMap* map, const void* base, uint64_t k, uint64_t d1, uint64_t d2, uint32_t box1) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return fail(ELB_ERR_CUDA, "matmul: cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[3] = {k, d1, d2};
+    const cuuint64_t strides[2] = {k, k * d1};
+    const cuuint32_t box[3] = {128, box1, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ELB_ERR_CUDA, "matmul: tensor map encoding failed");
+    return ELB_OK;
+}
+
+int* error_word() {  // pinned, mapped: raised by a kernel whose bounded wait ran out
+    static int* host = [] {
+        int* p = nullptr;
+        if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return static_cast<int*>(nullptr);
+        *p = 0;
+        return p;
+    }();
+    return host;
+}
+
+}  // namespace
+
+bool gemm_tc_usable(const Weight* w, int B) {
+    static const bool off = [] { const char* v = std::getenv("ELB_NO_TC"); return v && v[0] == '1'; }();
+    return !off && w->planes && w->n_planes == 2 && w->n % 256 == 0 && w->n % 16 == 0 && B >= 16 && encode_fn() != nullptr;
+}
+
+int gemm_tc_check() {  // after a synchronize: did a tensor-core GEMM give up on a wait?
+    int* e = error_word();
+    if (e && *e) {
+        *e = 0;
+        return fail(ELB_ERR_CUDA, "matmul: a bounded wait in the tensor-core kernel ran out");
+    }
+    return ELB_OK;
+}
+
+int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B, int nl,
+                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s) {
+    if (!gemm_tc_usable(w, B)) return fail(ELB_ERR_STATE, "matmul: tensor-core path not usable for this weight");
+    if (epilogue == EPI_SILU && !w->pair) return fail(ELB_ERR_INVALID, "matmul: SwiGLU epilogue needs a paired weight");
+    int* err_host = error_word();
+    int* err_dev = nullptr;
+    if (!err_host || cudaHostGetDevicePointer(&err_dev, err_host, 0) != cudaSuccess) return fail(ELB_ERR_CUDA, "matmul: no error word");
+    const int64_t rows16 = w->tiles * 16;
+    CUtensorMap mapW, mapX;
+    const bool four = nl >= 4;
+    const int T = four ? TcShape<4>::T : TcShape<3>::T;
+    ELB_TRY(make_map(&mapW, w->planes, uint64_t(w->n), uint64_t(rows16), 2, TC_ROWS));
+    ELB_TRY(make_map(&mapX, d_limbs, uint64_t(w->n), uint64_t(B), 4, uint32_t(T)));
+    TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue, err_dev};
+    const dim3 grid(unsigned((rows16 + TC_ROWS - 1) / TC_ROWS), unsigned((B + T - 1) / T));
+    static thread_local bool configured = false;
+    if (!configured) {
+        ELB_CUDA(cudaFuncSetAttribute(k_gemm_tc<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<3>::SMEM));
+        ELB_CUDA(cudaFuncSetAttribute(k_gemm_tc<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<4>::SMEM));
+        configured = true;
+    }
+    if (four) k_gemm_tc<4><<<grid, TC_THREADS, TcShape<4>::SMEM, s>>>(mapW, mapX, p);
+    else k_gemm_tc<3><<<grid, TC_THREADS, TcShape<3>::SMEM, s>>>(mapW, mapX, p);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
+}  // namespace elb

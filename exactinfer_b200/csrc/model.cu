@@ -155,9 +155,10 @@ int check_shape(const HostTensor& t, int64_t rows, int64_t n, const char* what) 
 
 // ---- one linear layer over B tokens (linear() of the reference, :1706-1780), limbs already split when quantized
 int linear_tokens(Model* m, const Weight* w, const float* xin, int64_t ldx, const float* norm_w, int B, float* y,
-                  int64_t ldy, const float* resid, int epi) {
+                  int64_t ldy, const float* resid, int epi, int nl) {
     ++m->launches;
     if (w->type == ELB_F16) return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
+    if (gemm_tc_usable(w, B)) return gemm_tc_launch(w, m->limbs, m->inv_scale, m->xsum, B, nl, y, ldy, resid, epi, m->stream);
     return gemm_planes_launch(w, m->limbs, m->inv_scale, m->xsum, B, y, ldy, resid, epi, m->stream);
 }
 
@@ -178,16 +179,16 @@ int body_prefill(Model* m, int B, int pos0) {
         bool q = false;
         for (auto& s : L.qkv) q |= s.w->type != ELB_F16;
         ELB_TRY(split_tokens(m, m->x, E, E, m->nl_qkv, L.attn_norm, B, q));
-        for (auto& s : L.qkv) ELB_TRY(linear_tokens(m, s.w, m->x, E, L.attn_norm, B, m->qkv + s.col, QKV, nullptr, EPI_STORE));
+        for (auto& s : L.qkv) ELB_TRY(linear_tokens(m, s.w, m->x, E, L.attn_norm, B, m->qkv + s.col, QKV, nullptr, EPI_STORE, m->nl_qkv));
         ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, pos0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream));
         ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream));
         m->launches += 2;
         ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16));
-        ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, m->x, E, m->x, EPI_ADD));
+        ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, m->x, E, m->x, EPI_ADD, m->nl_wo));
         ELB_TRY(split_tokens(m, m->x, E, E, m->nl_gu, L.ffn_norm, B, L.gu->type != ELB_F16));
-        ELB_TRY(linear_tokens(m, L.gu, m->x, E, L.ffn_norm, B, m->act, F, nullptr, EPI_SILU));
+        ELB_TRY(linear_tokens(m, L.gu, m->x, E, L.ffn_norm, B, m->act, F, nullptr, EPI_SILU, m->nl_gu));
         ELB_TRY(split_tokens(m, m->act, F, F, m->nl_down, nullptr, B, L.down->type != ELB_F16));
-        ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, m->x, E, m->x, EPI_ADD));
+        ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, m->x, E, m->x, EPI_ADD, m->nl_down));
     }
     return ELB_OK;
 }
@@ -317,6 +318,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
         ELB_CUDA(cudaMemcpyAsync(logits, m->logits, size_t(m->cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
+    ELB_TRY(gemm_tc_check());
     float ms = 0.f;
     ELB_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->last_ms += ms;
@@ -392,7 +394,8 @@ int setup_decode_kernel(Model* m) {
         const Layer& L0 = m->layers[0];
         for (auto& sgm : L0.qkv) layer_units += sgm.w->tiles * sgm.w->units_per_tile;
         for (const Weight* w : {L0.wo, L0.gu, L0.down}) layer_units += w->tiles * w->units_per_tile;
-        p.l2_ahead = int(std::max<int64_t>(2, layer_units / (int64_t(di.sm_count) * decode_warps())));
+        (void)layer_units;
+        p.l2_ahead = 0;  // measured: the extra look-ahead did not pay on this kernel (ELB_DK_L2AHEAD to try again)
         if (const char* v = std::getenv("ELB_DK_L2AHEAD")) p.l2_ahead = std::max(0, std::atoi(v));
     }
     m->dk_slot = (slot + 15) / 16 * 16;
