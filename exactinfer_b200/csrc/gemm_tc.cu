@@ -10,8 +10,8 @@
 // combination sum_j 256^j R_j is one Horner chain per (row, token) per 256-block in the epilogue, where the fp16
 // block scale d (and Q4_K's dmin*m term) is applied in fp32.
 //
-// Warp roles (192 threads): warps 0-3 epilogue (TMEM lanes = weight rows), warp 4 TMA producer, warp 5 MMA issuer and
-// TMEM owner. Operands arrive by TMA (no multicast) into a 3-stage ring of
+// Warp roles (320 threads): warps 0-7 epilogue (warp w drains TMEM lanes 32(w%4).. = weight rows, for half w/4 of the
+// tile's tokens), warp 8 TMA producer, warp 9 MMA issuer and TMEM owner. Operands arrive by TMA (no multicast) into a 3-stage ring of
 // 128-byte-swizzled K-major tiles; TMEM accumulators are double buffered so that the drain of one 256-block overlaps
 // the MMAs of the next. Every mbarrier wait is bounded: on timeout the kernel raises an error word and winds down.
 #include <cuda.h>
@@ -23,7 +23,7 @@
 
 namespace elb {
 
-constexpr int TC_ROWS = 128, TC_KSTAGE = 128, TC_STAGES = 3, TC_THREADS = 192;
+constexpr int TC_ROWS = 128, TC_KSTAGE = 128, TC_STAGES = 3, TC_EPI_WARPS = 8, TC_THREADS = (TC_EPI_WARPS + 2) * 32;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -92,6 +92,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle; 8-row groups 1024 bytes apart.
@@ -119,6 +125,7 @@ struct TcParams {
     const float* resid;
     int64_t rows16, rows, ldy;
     int B, n, epilogue;
+    int row_tiles, tok_tiles;  // the grid walks row_tiles * tok_tiles output tiles, token tiles of one row tile adjacent
     int* err;
 };
 
@@ -129,7 +136,8 @@ template <int NL> struct TcShape {
     static constexpr int LB = NL * T * 128;           // limb rows of one stage
     static constexpr int A_BYTES = TC_ROWS * 128;     // one plane tile of one stage
     static constexpr int LIMB_AREA = ZB + TC_STAGES * (LB + ZB);
-    static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + 1024;  // + barriers + alignment slack
+    static constexpr int XS_BYTES = 2 * T * 8 * 4;    // sum(X) of the tile's tokens over the 8 sub-blocks of a block, x2
+    static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + XS_BYTES + 1024;  // + barriers + slack
 };
 
 template <int NL>
@@ -147,10 +155,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     uint64_t* tfull = bars + 2 * TC_STAGES;  // [2] MMA -> epilogue
     uint64_t* tempty = tfull + 2;            // [2] epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    float* xs_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [2][T][8]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row0 = blockIdx.x * TC_ROWS, tok0 = blockIdx.y * T;
-    const int nk = p.n / TC_KSTAGE, nkb = p.n / 256;
+    const int nk = p.n / TC_KSTAGE, nkb = p.n / 256, n_tiles = p.row_tiles * p.tok_tiles;
 
     // zero blocks in front of, between and behind the limb stages
     for (int z = 0; z <= TC_STAGES; ++z) {
@@ -159,22 +167,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     }
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, TC_EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zero rows are read by the tensor core
-    if (warp == 5) tmem_alloc(tmem_slot, 512);
+    if (warp == TC_EPI_WARPS + 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
-    if (warp == 4) {
+    if (warp == TC_EPI_WARPS) {
         if (lane == 0) {  // ---- TMA producer
-            for (int kt = 0; kt < nk && ok; ++kt) {
-                const int s = kt % TC_STAGES;
-                ok = mbar_wait(empty + s, ((kt / TC_STAGES) & 1) ^ 1);
+            int it = 0;  // stages filled so far, over all tiles of this CTA
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int row0 = tile / p.tok_tiles * TC_ROWS, tok0 = tile % p.tok_tiles * T;
+            for (int kt = 0; kt < nk && ok; ++kt, ++it) {
+                const int s = it % TC_STAGES;
+                ok = mbar_wait(empty + s, ((it / TC_STAGES) & 1) ^ 1);
                 if (!ok) break;
                 mbar_expect_tx(full + s, 2 * S::A_BYTES + S::LB);
                 const int k0 = kt * TC_KSTAGE;
@@ -183,17 +194,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 uint8_t* lb = limb_area + S::ZB + s * (S::LB + S::ZB);
                 for (int l = 0; l < NL; ++l) tma_load_3d(lb + l * S::ZB, &mapX, k0, tok0, l, full + s);
             }
+            }
         }
-    } else if (warp == 5) {
+    } else if (warp == TC_EPI_WARPS + 1) {
         if (lane == 0) {  // ---- MMA issuer
             constexpr uint32_t idesc = idesc_i8(TC_ROWS, N);
-            for (int kt = 0; kt < nk && ok; ++kt) {
-                const int s = kt % TC_STAGES, kb = kt >> 1, acc = kb & 1;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x)
+            for (int kt = 0; kt < nk && ok; ++kt, ++it) {
+                const int s = it % TC_STAGES, kb = it >> 1, acc = kb & 1;  // kb: 256-blocks issued so far (nk is even)
                 if ((kt & 1) == 0) {  // first half of a 256-block: its accumulator must have been drained
                     ok = mbar_wait(tempty + acc, ((kb >> 1) & 1) ^ 1);
                     if (!ok) break;
                 }
-                ok = mbar_wait(full + s, (kt / TC_STAGES) & 1);
+                ok = mbar_wait(full + s, (it / TC_STAGES) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a0 = smem_u32(a_area + (s * 2 + 0) * S::A_BYTES), a1 = a0 + S::A_BYTES;
@@ -208,57 +222,84 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 if (kt & 1) mma_commit(tfull + acc);      // the 256-block is complete
             }
         }
-    } else {  // ---- epilogue: warp w owns TMEM lanes 32w..32w+31 = weight rows row0 + 32w + lane
-        const int64_t R = row0 + warp * 32 + lane;
-        const bool row_ok = R < p.rows16;
+    } else {  // ---- epilogue: warp w drains TMEM lanes 32(w%4).. (weight rows) for tokens [th*TH, (th+1)*TH), th = w/4
+        constexpr int TH = T / 2;  // tokens per epilogue warp
+        const int q4 = warp & 3, th = warp >> 2;
         const int nblk = p.n / 256, nsub = p.n / 32;
-        float accf[T];
+        int kbt = 0;  // 256-blocks drained so far, over all tiles of this CTA
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int row0 = tile / p.tok_tiles * TC_ROWS, tok0 = tile % p.tok_tiles * T;
+        const int64_t R = row0 + q4 * 32 + lane;
+        const bool row_ok = R < p.rows16;
+        float accf[TH];
 #pragma unroll
-        for (int t = 0; t < T; ++t) accf[t] = 0.f;
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-            const int acc = kb & 1;
-            ok = mbar_wait(tfull + acc, (kb >> 1) & 1);
+        for (int t = 0; t < TH; ++t) accf[t] = 0.f;
+        // block scale and the dmin*m row of the first block; the next block's are fetched while this one is drained
+        float d = row_ok ? __half2float(p.pl_d[R * nblk]) : 0.f;
+        float4 dm0 = make_float4(0.f, 0.f, 0.f, 0.f), dm1 = dm0;
+        if (p.pl_dm && row_ok) {
+            dm0 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub));
+            dm1 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + 4));
+        }
+        for (int kb = 0; kb < nkb && ok; ++kb, ++kbt) {
+            const int acc = kbt & 1;
+            float d_next = 0.f;
+            float4 dn0 = make_float4(0.f, 0.f, 0.f, 0.f), dn1 = dn0;
+            if (kb + 1 < nkb && row_ok) {
+                d_next = __half2float(p.pl_d[R * nblk + kb + 1]);
+                if (p.pl_dm) {
+                    dn0 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + (kb + 1) * 8));
+                    dn1 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + (kb + 1) * 8 + 4));
+                }
+            }
+            if (p.pl_dm) {  // stage sum(X) of this block for the tile's tokens (all 8 epilogue warps, 2 floats each)
+                float* xb = xs_s + acc * (T * 8);
+                const int etid = warp * 32 + lane;  // 0..255
+                for (int i = etid; i < T * 8; i += TC_EPI_WARPS * 32) {
+                    const int tok = min(tok0 + (i >> 3), p.B - 1);
+                    xb[i] = __ldg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7));
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");  // epilogue warps only
+            }
+            ok = mbar_wait(tfull + acc, (kbt >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            const float d = row_ok ? __half2float(p.pl_d[R * nblk + kb]) : 0.f;
-            const uint32_t tbase = tmem_base + acc * 256 + (uint32_t(warp * 32) << 16);
+            const uint32_t tbase = tmem_base + acc * 256 + (uint32_t(q4 * 32) << 16) + th * TH;
+            {
+                int v[NL + 1][TH];  // every load of the drain is issued before the one wait
 #pragma unroll
-            for (int c = 0; c < T / 16; ++c) {
-                int v[NL + 1][16];
+                for (int c = 0; c < TH / 8; ++c)
 #pragma unroll
-                for (int j = 0; j <= NL; ++j) tmem_ld16(tbase + j * T + c * 16, v[j]);
+                    for (int j = 0; j <= NL; ++j) tmem_ld8(tbase + j * T + c * 8, *reinterpret_cast<int (*)[8]>(&v[j][c * 8]));
                 tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty + acc);  // accumulator in registers: the issuer may overwrite it
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
+                for (int t = 0; t < TH; ++t) {
                     float f = float(v[NL][t]);
 #pragma unroll
                     for (int j = NL - 1; j >= 0; --j) f = fmaf(f, 256.0f, float(v[j][t]));
-                    accf[c * 16 + t] = fmaf(d, f, accf[c * 16 + t]);
+                    accf[t] = fmaf(d, f, accf[t]);
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty + acc);  // accumulator drained: the issuer may overwrite it
             if (p.pl_dm) {  // Q4_K: minus sum over the 8 sub-blocks of fl(dmin*m) * sum(X)
-                float dm[8];
+                const float* xb = xs_s + acc * (T * 8) + th * TH * 8;
 #pragma unroll
-                for (int q = 0; q < 8; ++q) dm[q] = row_ok ? __ldg(p.pl_dm + R * nsub + kb * 8 + q) : 0.f;
-#pragma unroll
-                for (int t = 0; t < T; ++t) {
-                    const int tok = min(tok0 + t, p.B - 1);
-                    const float4 x0 = __ldg(reinterpret_cast<const float4*>(p.xsum + int64_t(tok) * nsub + kb * 8));
-                    const float4 x1 = __ldg(reinterpret_cast<const float4*>(p.xsum + int64_t(tok) * nsub + kb * 8 + 4));
-                    float s = dm[0] * x0.x;
-                    s = fmaf(dm[1], x0.y, s); s = fmaf(dm[2], x0.z, s); s = fmaf(dm[3], x0.w, s);
-                    s = fmaf(dm[4], x1.x, s); s = fmaf(dm[5], x1.y, s); s = fmaf(dm[6], x1.z, s); s = fmaf(dm[7], x1.w, s);
+                for (int t = 0; t < TH; ++t) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(xb + t * 8), x1 = *reinterpret_cast<const float4*>(xb + t * 8 + 4);
+                    float s = dm0.x * x0.x;
+                    s = fmaf(dm0.y, x0.y, s); s = fmaf(dm0.z, x0.z, s); s = fmaf(dm0.w, x0.w, s);
+                    s = fmaf(dm1.x, x1.x, s); s = fmaf(dm1.y, x1.y, s); s = fmaf(dm1.z, x1.z, s); s = fmaf(dm1.w, x1.w, s);
                     accf[t] -= s;
                 }
             }
+            d = d_next; dm0 = dn0; dm1 = dn1;
         }
         if (ok) {
 #pragma unroll
-            for (int t = 0; t < T; ++t) {
-                const int tok = tok0 + t;
+            for (int t = 0; t < TH; ++t) {
+                const int tok = tok0 + th * TH + t;
                 const bool tok_ok = tok < p.B;
                 const float y = accf[t] * (tok_ok ? __ldg(p.inv_scale + tok) : 0.f);
                 if (p.epilogue == EPI_SILU) {  // tile rows 0..7 gate, 8..15 up (16-row groups): partner is 8 lanes up
@@ -272,11 +313,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 }
             }
         }
+        }
     }
     if (!ok) atomicExch(p.err, 2);
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, 512);
+    if (warp == TC_EPI_WARPS + 1) tmem_dealloc(tmem_base, 512);
 }
 
 // ---------------------------------------------------------------- host side
@@ -352,8 +394,12 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
     const int T = four ? TcShape<4>::T : TcShape<3>::T;
     ELB_TRY(make_map(&mapW, w->planes, uint64_t(w->n), uint64_t(rows16), 2, TC_ROWS));
     ELB_TRY(make_map(&mapX, d_limbs, uint64_t(w->n), uint64_t(B), 4, uint32_t(T)));
-    TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue, err_dev};
-    const dim3 grid(unsigned((rows16 + TC_ROWS - 1) / TC_ROWS), unsigned((B + T - 1) / T));
+    const int row_tiles = int((rows16 + TC_ROWS - 1) / TC_ROWS), tok_tiles = (B + T - 1) / T;
+    TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
+               row_tiles, tok_tiles, err_dev};
+    DeviceInfo di;
+    ELB_TRY(device_info(w->device, &di));
+    const dim3 grid(unsigned(std::min(row_tiles * tok_tiles, di.sm_count)));  // persistent: one CTA per SM walks the tiles
     static thread_local bool configured = false;
     if (!configured) {
         ELB_CUDA(cudaFuncSetAttribute(k_gemm_tc<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<3>::SMEM));
