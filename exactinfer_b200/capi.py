@@ -43,6 +43,7 @@ SIGNATURES = {
     "elb_get_rows_dev": (C.c_int, [_vp, C.c_int64, C.c_int64, _vp]),
     "elb_matvec": (C.c_int, [_vp, _f32p, _f32p, C.c_int]),
     "elb_matvec_dev": (C.c_int, [_vp, _vp, _vp, C.c_int]),
+    "elb_matvec_static": (C.c_int, [_vp, _vp, _vp, C.c_int]),
     "elb_matmul": (C.c_int, [_vp, _f32p, C.c_int64, _f32p, C.c_int]),
     "elb_matmul_dev": (C.c_int, [_vp, _vp, C.c_int64, _vp, C.c_int]),
     "elb_rmsnorm": (C.c_int, [_f32p, _f32p, _f32p, C.c_int, C.c_float, C.c_int]),

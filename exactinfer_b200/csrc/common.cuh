@@ -215,6 +215,7 @@ int gemv_prepare(Weight* w);  // allocates the split-K scratch (once per weight)
 int prep_limbs_launch(const float* x, int n, const float* norm_w, float eps, int nl, int8_t* limbs, float* inv_scale,
                       bool pdl, cudaStream_t s);
 int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s);
+int matvec_static(const Weight* w, const float* d_x, float* d_y, int nl, cudaStream_t s);
 
 // linear.cu — several tokens at once
 int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const float* d_norm_w, float eps,

@@ -12,6 +12,7 @@
 // results are deterministic and need no floating-point atomics.
 #include <algorithm>
 #include <cstdlib>
+#include <string>
 
 #include "common.cuh"
 #include "split.cuh"
@@ -389,4 +390,84 @@ int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s) {
 #undef ELB_GEMV_CASE
 }
 
+// ---------------------------------------------------------------- matvec without any allocation
+//
+// Some hosts cannot call cudaMalloc where they need a matvec: a real-time or serving thread that must not take the
+// driver's allocation lock, code that runs after the process has handed all of its device memory to a pool it does not
+// control, or a caller that is inside a region where allocation is forbidden by its own rules. For them the working
+// memory of the matvec (the limb-split activation, the split-K partial sums and their arrival counters) lives in one
+// statically sized array in device memory instead of buffers allocated per weight.
+//
+// The array is part of the library image on every GPU that loads it (NOALLOC_BYTES, about 208 KB, until the process
+// exits). Every call uses the same array and leaves its contents behind: two calls that overlap on the GPU (different
+// streams, different threads) corrupt each other — issue them one after the other.
+constexpr int NOALLOC_MAX_N = 16384;        // longest activation vector
+constexpr int NOALLOC_MAX_TILES = 16384;    // row tiles of 16 rows: up to 262144 rows
+constexpr int NOALLOC_MAX_GRID = 512;       // CTAs whose partial sums fit
+constexpr size_t NOALLOC_ACT_OFF = 0;
+constexpr size_t NOALLOC_INV_OFF = (size_t(4) * NOALLOC_MAX_N + size_t(NOALLOC_MAX_N / 256) * 192 + 255) / 256 * 256;
+constexpr size_t NOALLOC_PART_OFF = NOALLOC_INV_OFF + 256;
+constexpr size_t NOALLOC_CNT_OFF = NOALLOC_PART_OFF + size_t(NOALLOC_MAX_GRID) * 2 * 16 * sizeof(float);
+constexpr size_t NOALLOC_BYTES = NOALLOC_CNT_OFF + size_t(NOALLOC_MAX_TILES) * sizeof(unsigned);
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+// Device address of the array on `device` (which must be current). In host code the array's name is only a handle for
+// the runtime, not an address a kernel could use, so the address is asked for once per device and remembered.
+static int noalloc_scratch(int device, unsigned char** out) {
+    static unsigned char* cache[64] = {};
+    if (device < 0 || device >= 64) return fail(ELB_ERR_INVALID, "matvec_static: device index out of range");
+    if (!cache[device]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(ELB_ERR_CUDA, std::string("matvec_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+        cache[device] = static_cast<unsigned char*>(p);
+    }
+    *out = cache[device];
+    return ELB_OK;
+}
+
+int matvec_static(const Weight* w, const float* d_x, float* d_y, int nl, cudaStream_t s) {
+    if (!w || !d_x || !d_y) return fail(ELB_ERR_INVALID, "matvec_static: null argument");
+    if (nl == 0) nl = 4;
+    ELB_CUDA(cudaSetDevice(w->device));
+    GemvArgs a;
+    a.x = d_x;
+    a.y = d_y;
+    if (w->type == ELB_F16) return gemv_launch(w, a, s);  // fp32 path: no working memory at all
+    if (w->n > NOALLOC_MAX_N)
+        return fail(ELB_ERR_UNSUPPORTED, "matvec_static: row length " + std::to_string(w->n) + " exceeds the static limit of " + std::to_string(NOALLOC_MAX_N));
+    if (w->tiles > NOALLOC_MAX_TILES)
+        return fail(ELB_ERR_UNSUPPORTED, "matvec_static: " + std::to_string(w->rows) + " rows exceed the static limit of " + std::to_string(NOALLOC_MAX_TILES * 16));
+    DeviceInfo di;
+    ELB_TRY(device_info(w->device, &di));
+    if (di.sm_count > NOALLOC_MAX_GRID) return fail(ELB_ERR_UNSUPPORTED, "matvec_static: more SMs than the static partial-sum area covers");
+    unsigned char* base = nullptr;
+    ELB_TRY(noalloc_scratch(w->device, &base));
+    int8_t* act = reinterpret_cast<int8_t*>(base + NOALLOC_ACT_OFF);
+    float* inv = reinterpret_cast<float*>(base + NOALLOC_INV_OFF);
+    // the arrival counters must start at zero whatever an earlier (possibly failed) call left behind
+    ELB_CUDA(cudaMemsetAsync(base + NOALLOC_CNT_OFF, 0, size_t(w->tiles) * sizeof(unsigned), s));
+    ELB_TRY(prep_limbs_launch(d_x, int(w->n), nullptr, 0.f, nl, act, inv, false, s));
+    Weight view = *w;  // same weight, working memory redirected to the static array (nothing is allocated or freed)
+    view.part = reinterpret_cast<float*>(base + NOALLOC_PART_OFF);
+    view.counters = reinterpret_cast<unsigned*>(base + NOALLOC_CNT_OFF);
+    view.max_grid = std::min(w->max_grid > 0 ? w->max_grid : NOALLOC_MAX_GRID, NOALLOC_MAX_GRID);
+    a.limbs = act;
+    a.inv_scale = inv;
+    return gemv_launch(&view, a, s);
+}
+
 }  // namespace elb
+
+// C entry point of the allocation-free matvec (declared in include/elb.h). It lives in this file because the static
+// array does: its device address is looked up here (cudaGetSymbolAddress, on the first call per device).
+extern "C" int elb_matvec_static(const elb_weight* w, const float* d_x, float* d_y, int nl) {
+    const elb::Weight* ww = reinterpret_cast<const elb::Weight*>(w);
+    const int rc = elb::matvec_static(ww, d_x, d_y, nl, nullptr);
+    if (rc != ELB_OK) return rc;
+    if (cudaStreamSynchronize(nullptr) != cudaSuccess) return elb::fail(ELB_ERR_CUDA, "matvec_static: kernel failed");
+    return ELB_OK;
+}
+

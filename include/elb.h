@@ -76,6 +76,18 @@ int elb_get_rows_dev(const elb_weight* w, int64_t row0, int64_t count, float* d_
 int elb_matvec(const elb_weight* w, const float* x, float* y, int nl);
 int elb_matvec_dev(const elb_weight* w, const float* d_x, float* d_y, int nl);
 
+/* The same matvec for callers that must not allocate: a serving or real-time thread that cannot take the driver's
+ * allocation lock, a host that has already given all device memory to a pool it does not control, or any code inside
+ * a section where allocation is ruled out. No counterpart in the reference project (its backend allocates freely).
+ * Pointers are device pointers. The call allocates and frees nothing (no cudaMalloc / cudaFree, no library
+ * allocator): its working memory — the limb-split activation, split-K partial sums, arrival counters — is one static
+ * array of about 208 KB that every GPU loading this library carries until the process exits.
+ * Limits: row length n <= 16384, at most 262144 rows; larger weights are refused with ELB_ERR_UNSUPPORTED and a
+ * message that names the limit. The first call on a device looks up the array's device address; make that first call
+ * outside any stream capture. All calls share the array and leave their data in it: calls that overlap on the GPU
+ * (several streams or threads) race — issue them one after another. Result: identical to elb_matvec_dev. */
+int elb_matvec_static(const elb_weight* w, const float* d_x, float* d_y, int nl);
+
 /* Y[b][rows] = X[b][n] * W^T for b tokens (linear() with B > 1, src/cuda/model_cuda.cu:1706-1780): limb split once,
  * then the int8 tensor-core GEMM over the digit planes (needs ELB_W_PLANES). */
 int elb_matmul(const elb_weight* w, const float* x, int64_t b, float* y, int nl);
