@@ -7,7 +7,9 @@ One JSON line on stdout (rank 0). A step is one single-token decode step at batc
 (el bench --pp 512 --tg K of the reference, src/main.cpp:621-648, seeded synthetic weights, LCG token stream).
   value      decode tok/s with tokens and weights resident on the device (CUDA events around K back-to-back steps)
   e2e        the same K steps through Backend.eval: host token in, host logits out, copies inside the timed region
-  roofline   the dominant kernel (Q4_K matvec, 2560 x 9728, 4 limbs) timed alone over 24 weight copies in rotation
+  roofline   the dominant kernel of the timed region: the persistent decode-step kernel (algorithmic bytes = all
+             weights once + the KV rows read), live CUDA-event time; roofline_gemv is the Q4_K matvec 2560 x 9728
+             (4 limbs) timed alone over 24 weight copies in rotation
   cpu_baseline  the reference's CPU path on the host cores, bounded sample (N=1, rank 0 only)
 --impl reference times only that CPU path.
 """
@@ -33,6 +35,34 @@ PROMPT = 512
 SEED = 20251125
 MICRO_ROWS, MICRO_N = 2560, 9728
 MICRO_BYTES = MICRO_ROWS * (MICRO_N // 256) * 144  # 14 008 320 algorithmic bytes per matvec
+INT8_PEAK_TOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+MICRO_TRAFFIC = 14_121_643  # profiles/k_gemv_q4_k_2560x9728_microbench.txt (mean of 3 launches)
+
+
+def decode_traffic(spec):
+    """DRAM bytes per k_decode_step launch, scaled per layer from the 4- and 8-layer ncu captures of the 4B shape
+    (profiles/k_decode_step_qwen3-4b-q4_k_m_4_and_8_layers.txt): 322.4 MB for head, embedding row and fixed part,
+    65.23 MB per layer at positions ~517. None for shapes that were not captured."""
+    if spec.name != "qwen3-4b-q4_k_m":
+        return None
+    return 322.4e6 + 65.23e6 * spec.n_layer
+
+
+def metric_name(spec):
+    return f"{spec.name} decode tok/s (batch 1, after pp{PROMPT}; prefill tok/s under \"prefill\")"
+
+
+def workload_name(spec, K):
+    return (f"{spec.name}: {spec.n_layer} layers, E{spec.n_embd} F{spec.n_ff} H{spec.n_head}/{spec.n_head_kv} "
+            f"V{spec.n_vocab}, batch 1, pp{PROMPT} then tg{K}")
+
+
+def spec_macs_per_token(spec):
+    """Multiply-accumulates of the linear layers for one token (head excluded: prefill computes it once per chunk)."""
+    qd, kd = spec.n_head * spec.head_dim, spec.n_head_kv * spec.head_dim
+    per_layer = spec.n_embd * (qd + 2 * kd) + qd * spec.n_embd + 3 * spec.n_embd * spec.n_ff
+    return float(spec.n_layer * per_layer)
 
 
 def parse_args():
@@ -174,10 +204,12 @@ def run_reference(args):
     tens, _ = model_tensors(spec)
     budget = 150.0
     base, done, dt = cpu_decode_baseline(spec, tens, budget, max(2, args.steps))
-    out = {"impl": "reference", "metric": f"{spec.name} decode tok/s (batch 1)", "value": base["value"], "unit": "tok/s",
+    out = {"impl": "reference", "metric": metric_name(spec), "value": base["value"], "unit": "tok/s",
            "n_gpus": args.gpus, "steps": done, "steps_requested": args.steps, "warmup": 1,
            "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-           "dtype": "f32", "data": "synthetic", "config": {"workload": f"{spec.name} tg (CPU path, token at a time)"},
+           "dtype": "f32", "data": "synthetic", "config": {"workload": workload_name(spec, args.steps),
+                      "sample": "CPU path, single-token steps from position 1 (no 512-token prompt: it alone would "
+                                "take minutes on the host), bounded to 150 s"},
            "cpu_baseline": base,
            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out), flush=True)
@@ -215,7 +247,9 @@ def pinned_array(e, n_floats):
 
 def run_ours(args):
     rank, local, world = dist_env()
-    n_gpus = max(args.gpus, world)
+    n_gpus = world  # one rank per GPU; started without a launcher, --gpus N > 1 still runs the single-GPU path
+    if args.gpus != world and rank == 0:
+        print(f"bench: --gpus {args.gpus} but WORLD_SIZE is {world}; running on {world} GPU(s)", file=sys.stderr)
     dist = None
     if world > 1:
         import torch
@@ -230,7 +264,12 @@ def run_ours(args):
     spec = get_spec(args)
     tens, gen_s = model_tensors(spec)
     t0 = time.time()
-    model = e.Backend(spec, tens, PROMPT + W + K + 1, device=local)
+    tp = None
+    if world > 1:  # tensor parallel: rank 0 makes the NCCL id of the library's own communicator, all ranks join it
+        box = [e.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        tp = (rank, world, box[0])
+    model = e.Backend(spec, tens, PROMPT + W + K + 1, device=local, tp=tp)
     load_s = time.time() - t0
     toks = synth.lcg_tokens(PROMPT + W + K, spec.n_vocab)
     logits, _pin = pinned_array(e, spec.n_vocab)
@@ -281,44 +320,66 @@ def run_ours(args):
 
     if rank != 0:
         model.close()
+        dist.barrier()
+        dist.destroy_process_group()
         return
     peaks, peak_kind = measured_peaks()
     hbm = float(peaks["hbm_gbs"])
     micro_ms = microbench_matvec(e, local) if spec.layout != "f16" else None
     step_bytes = model.weight_bytes + model.kv_bytes_per_token * (PROMPT + W + K / 2.0)
-    tok_s = n_gpus * K / (dev_ms / 1000.0)
+    tok_s = K / (dev_ms / 1000.0)  # one sequence: under tensor parallelism the ranks share every step
     out = {
-        "metric": f"{spec.name} decode tok/s (batch 1, after pp{PROMPT})", "value": tok_s, "unit": "tok/s",
+        "metric": metric_name(spec), "value": tok_s, "unit": "tok/s",
         "n_gpus": n_gpus, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8 limbs x quantized ints -> int32, fp32 scales",
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 limbs x quantized ints -> int32, fp32 scales",
         "data": "synthetic",
-        "config": {"workload": f"{spec.name}: {spec.n_layer} layers, E{spec.n_embd} F{spec.n_ff} H{spec.n_head}/"
-                               f"{spec.n_head_kv} V{spec.n_vocab}, batch 1, pp{PROMPT} then tg{K}",
-                   "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} independent replicas",
+        "config": {"workload": workload_name(spec, K),
+                   "parallelism": "single GPU" if world == 1 else
+                   f"tp{world}: heads and FFN columns cut over {world} GPUs, NCCL all-reduce after attn_output and "
+                   "ffn_down, all-gather of the logits",
                    "l2": "inputs larger than L2: every step streams all weights (GBs) from HBM",
                    "seed": SEED, "tokens": "reference LCG stream, seed 12345"},
-        "e2e": {"value": n_gpus * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8,
+        "e2e": {"value": K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": spec.n_vocab * 4},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "prefill": {"value": n_gpus * PROMPT / pp_dev_s, "unit": "tok/s", "ms": pp_dev_s * 1000.0,
-                    "e2e_tok_s": n_gpus * PROMPT / pp_wall_s, "gpu_launches": int(pp_launches)},
-        "decode_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1000.0) / 1e9,
+        "prefill": {"value": PROMPT / pp_dev_s, "unit": "tok/s", "ms": pp_dev_s * 1000.0,
+                    "e2e_tok_s": PROMPT / pp_wall_s, "gpu_launches": int(pp_launches)},
+        "decode_hbm": {"per": "GPU (rank 0's share of the weights and KV rows)", "bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1000.0) / 1e9,
                        "frac_of_measured_copy": step_bytes / (dev_ms / K / 1000.0) / 1e9 / hbm,
                        "frac_of_8tbs": step_bytes / (dev_ms / K / 1000.0) / 1e9 / 8000.0},
         "setup_s": {"generate": gen_s, "upload": load_s},
     }
+    # dominant kernel of the timed region: with one persistent launch per token it is the decode step itself
+    step_s = dev_ms / K / 1000.0
+    per_step = launches / float(K)
+    if per_step < 4:
+        ach = step_bytes / step_s / 1e9
+        out["roofline"] = {"bound": "hbm", "kernel": "k_decode_step (one persistent launch per token: every matvec, "
+                           "norm, RoPE, attention and SwiGLU of the step)", "achieved": ach, "peak": hbm, "unit": "GB/s",
+                           "frac": ach / hbm, "peak_kind": peak_kind, "frac_of_8tbs": ach / 8000.0,
+                           "bytes_per_launch": step_bytes, "us_per_launch": step_s * 1e6, "traffic": decode_traffic(spec)}
     if micro_ms is not None:
         ach = MICRO_BYTES / (micro_ms / 1000.0) / 1e9
-        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv<Q4_K> 2560x9728, 4 limbs", "achieved": ach, "peak": hbm,
-                           "unit": "GB/s", "frac": ach / hbm, "peak_kind": peak_kind, "frac_of_8tbs": ach / 8000.0,
-                           "us_per_launch": micro_ms * 1000.0, "traffic": None}
+        micro = {"bound": "hbm", "kernel": "k_gemv<Q4_K> 2560x9728, 4 limbs, alone (24 weight copies in rotation)",
+                 "achieved": ach, "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_kind": peak_kind,
+                 "frac_of_8tbs": ach / 8000.0, "bytes_per_launch": MICRO_BYTES, "us_per_launch": micro_ms * 1000.0,
+                 "traffic": MICRO_TRAFFIC}
+        out["roofline_gemv"] = micro
+        out.setdefault("roofline", micro)
+    ops = 2.0 * spec_macs_per_token(spec)
+    out["prefill"]["roofline"] = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 kind::i8) + attention + splits",
+                                  "achieved": ops * out["prefill"]["value"] / 1e12, "peak": INT8_PEAK_TOPS,
+                                  "unit": "TOP/s", "frac": ops * out["prefill"]["value"] / 1e12 / INT8_PEAK_TOPS,
+                                  "peak_kind": "nominal dense int8 (not in MEASURED_PEAKS.json)",
+                                  "note": "2*M*N*K counted once; the limb planes issue (NL+1)x that on the tensor pipe"}
     model.close()
     if n_gpus == 1 and not args.no_cpu_baseline:
         base, _, _ = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)
         out["cpu_baseline"] = base
     print(json.dumps(out), flush=True)
     if dist is not None:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -136,16 +136,58 @@ def split_limbs(x: np.ndarray, nl: int, device: int = 0):
     return limbs, inv
 
 
+def spec_config(spec: "synth.Spec", max_batch: int = 0) -> Config:
+    return Config(spec.n_layer, spec.n_embd, spec.n_ff, spec.n_head, spec.n_head_kv, spec.head_dim, spec.n_vocab,
+                  spec.head_dim, spec.rope_base, spec.eps, max_batch)
+
+
+def tp_unique_id() -> bytes:
+    """128-byte NCCL id for Backend(tp=...): make it on one rank, hand it to the others."""
+    buf = C.create_string_buffer(128)
+    check(lib().elb_tp_unique_id(buf))
+    return buf.raw
+
+
+def tp_dims(spec: "synth.Spec", rank: int, size: int) -> dict:
+    """This rank's share of the model: heads, FFN range [f0, f1), vocabulary rows [v0, v1). Host arithmetic only."""
+    cfg = spec_config(spec)
+    h, hkv = C.c_int(), C.c_int()
+    f0, f1, v0, v1 = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64()
+    check(lib().elb_tp_dims(C.byref(cfg), rank, size, C.byref(h), C.byref(hkv), C.byref(f0), C.byref(f1), C.byref(v0),
+                            C.byref(v1)))
+    return {"n_head": h.value, "n_head_kv": hkv.value, "f0": f0.value, "f1": f1.value, "v0": v0.value, "v1": v1.value}
+
+
+def tp_shard(spec: "synth.Spec", rank: int, size: int, role: str, t: int, rows: int, n: int, data: np.ndarray):
+    """Rank `rank`'s cut of one tensor of the whole model: (rows, n, bytes). Host arithmetic only."""
+    cfg = spec_config(spec)
+    data = np.ascontiguousarray(data, dtype=np.uint8).reshape(-1)
+    orows, on, nb = C.c_int64(), C.c_int64(), C.c_size_t()
+    rid = synth.ROLE_ID[role]
+    check(lib().elb_tp_shard_shape(C.byref(cfg), rank, size, rid, t, rows, n, C.byref(orows), C.byref(on), C.byref(nb)))
+    out = np.empty(nb.value, dtype=np.uint8)
+    check(lib().elb_tp_shard_copy(C.byref(cfg), rank, size, rid, t, rows, n, data.ctypes.data_as(C.c_void_p), data.nbytes,
+                                  out.ctypes.data_as(C.c_void_p), out.nbytes))
+    return orows.value, on.value, out
+
+
 class Backend:
     """el::Backend (src/model.h:42-51) on the CUDA library: cfg(), n_ctx(), name(), eval(tokens, pos0) -> logits."""
 
-    def __init__(self, spec: "synth.Spec", tensors, n_ctx: int, device: int = 0, max_batch: int = 0):
+    def __init__(self, spec: "synth.Spec", tensors, n_ctx: int, device: int = 0, max_batch: int = 0, tp=None):
+        """tp = (rank, size, id) makes this process rank `rank` of a tensor-parallel group of `size` GPUs; `id` is the
+        128-byte value of tp_unique_id() made on one rank and given to all. `tensors` are the whole model's on every
+        rank; eval must then be called by all ranks with the same arguments."""
         self.spec = spec
-        self._cfg = Config(spec.n_layer, spec.n_embd, spec.n_ff, spec.n_head, spec.n_head_kv, spec.head_dim, spec.n_vocab,
-                           spec.head_dim, spec.rope_base, spec.eps, max_batch)
+        self._cfg = spec_config(spec, max_batch)
         self._n_ctx = n_ctx
         h = C.c_void_p()
-        check(lib().elb_model_create(C.byref(self._cfg), n_ctx, device, C.byref(h)))
+        if tp is None or tp[1] == 1:
+            check(lib().elb_model_create(C.byref(self._cfg), n_ctx, device, C.byref(h)))
+        else:
+            rank, size, ident = tp
+            buf = C.create_string_buffer(bytes(ident), 128)
+            check(lib().elb_model_create_tp(C.byref(self._cfg), n_ctx, device, rank, size, buf, C.byref(h)))
         self._h = h
         try:
             keep = []

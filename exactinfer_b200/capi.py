@@ -23,6 +23,7 @@ class Config(C.Structure):
 
 _f32p, _i8p, _i32p = C.POINTER(C.c_float), C.POINTER(C.c_int8), C.POINTER(C.c_int32)
 _vp = C.c_void_p
+_i64p = C.POINTER(C.c_int64)
 
 SIGNATURES = {
     "elb_last_error": (C.c_char_p, []),
@@ -59,6 +60,14 @@ SIGNATURES = {
     "elb_model_hidden": (C.c_int, [_vp, _f32p]),
     "elb_model_weight_bytes": (C.c_size_t, [_vp]),
     "elb_model_kv_bytes_per_token": (C.c_size_t, [_vp]),
+    "elb_tp_dims": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), _i64p, _i64p,
+                              _i64p, _i64p]),
+    "elb_tp_shard_shape": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, _i64p,
+                                     _i64p, C.POINTER(C.c_size_t)]),
+    "elb_tp_shard_copy": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, _vp,
+                                    C.c_size_t, _vp, C.c_size_t]),
+    "elb_tp_unique_id": (C.c_int, [_vp]),
+    "elb_model_create_tp": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "elb_bench_matvec": (C.c_int, [C.POINTER(_vp), C.c_int, _vp, _vp, C.c_int, C.c_int, _f32p]),
     "elb_bench_matmul": (C.c_int, [C.POINTER(_vp), C.c_int, _vp, C.c_int64, _vp, C.c_int, C.c_int, _f32p]),
 }

@@ -256,6 +256,50 @@ int elb_model_create(const elb_config* cfg, int n_ctx, int device, elb_model** o
     *out = reinterpret_cast<elb_model*>(m);
     return ELB_OK;
 }
+int elb_model_create_tp(const elb_config* cfg, int n_ctx, int device, int tp_rank, int tp_size, const void* id128,
+                        elb_model** out) {
+    if (elb_device_count() == 0) return fail(ELB_ERR_CUDA, std::string("no usable CUDA device: ") + g_error);
+    Model* m = nullptr;
+    ELB_TRY(model_create_tp(cfg, n_ctx, device, tp_rank, tp_size, id128, &m));
+    *out = reinterpret_cast<elb_model*>(m);
+    return ELB_OK;
+}
+int elb_tp_unique_id(void* id128) { return tp_unique_id(id128); }
+int elb_tp_dims(const elb_config* cfg, int tp_rank, int tp_size, int* n_head, int* n_head_kv, int64_t* f0, int64_t* f1,
+                int64_t* v0, int64_t* v1) {
+    if (!cfg) return fail(ELB_ERR_INVALID, "tp_dims: null configuration");
+    TpDims d;
+    ELB_TRY(tp_dims(*cfg, tp_rank, tp_size, &d));
+    if (n_head) *n_head = d.H;
+    if (n_head_kv) *n_head_kv = d.HKV;
+    if (f0) *f0 = d.f0;
+    if (f1) *f1 = d.f1;
+    if (v0) *v0 = d.v0;
+    if (v1) *v1 = d.v1;
+    return ELB_OK;
+}
+int elb_tp_shard_shape(const elb_config* cfg, int tp_rank, int tp_size, int role, int ggml_type, int64_t rows, int64_t n,
+                       int64_t* out_rows, int64_t* out_n, size_t* out_nbytes) {
+    if (!cfg) return fail(ELB_ERR_INVALID, "tp_shard_shape: null configuration");
+    TpDims d;
+    TpShard s;
+    ELB_TRY(tp_dims(*cfg, tp_rank, tp_size, &d));
+    ELB_TRY(tp_shard_shape(*cfg, d, role, ggml_type, rows, n, &s));
+    if (out_rows) *out_rows = s.rows;
+    if (out_n) *out_n = s.n;
+    if (out_nbytes) *out_nbytes = s.nbytes;
+    return ELB_OK;
+}
+int elb_tp_shard_copy(const elb_config* cfg, int tp_rank, int tp_size, int role, int ggml_type, int64_t rows, int64_t n,
+                      const void* bytes, size_t nbytes, void* out, size_t out_nbytes) {
+    if (!cfg) return fail(ELB_ERR_INVALID, "tp_shard_copy: null configuration");
+    TpDims d;
+    TpShard s;
+    ELB_TRY(tp_dims(*cfg, tp_rank, tp_size, &d));
+    ELB_TRY(tp_shard_shape(*cfg, d, role, ggml_type, rows, n, &s));
+    if (out_nbytes < s.nbytes) return fail(ELB_ERR_INVALID, "tp_shard_copy: output buffer too small");
+    return tp_shard_copy(s, static_cast<const uint8_t*>(bytes), nbytes, static_cast<uint8_t*>(out));
+}
 int elb_model_set_tensor(elb_model* m, int role, int layer, int ggml_type, int64_t rows, int64_t n, const void* bytes,
                          size_t nbytes) {
     return model_set_tensor(M(m), role, layer, ggml_type, rows, n, bytes, nbytes);

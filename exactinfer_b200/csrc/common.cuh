@@ -67,6 +67,7 @@ struct Weight {
     int64_t units_per_tile = 0;
     int unit_bytes = 0;
     bool pair = false;     // gate|up interleaved in 8-row groups
+    bool view = false;     // rows of another weight: tiled memory is borrowed, not owned
     uint8_t* tiled = nullptr;  // tiled layout (quantized types) or plain row-major fp16 (F16)
     size_t tiled_bytes = 0;
     // digit planes for the tensor-core path: plane p holds digit p of the integer weight, row-major [rows16][n]
@@ -179,6 +180,9 @@ int device_info(int device, DeviceInfo* out);
 int weight_create(int device, int type, int64_t rows_one, int64_t n, const void* bytes, size_t nbytes, int flags,
                   Weight** out);
 void weight_destroy(Weight* w);
+// rows [row0, row0 + rows) of `base` as a weight of its own (row0 a multiple of 16; not for gate|up pairs); the tiled
+// memory stays owned by `base`, which must outlive the view. No digit planes.
+int weight_view_rows(const Weight* base, int64_t row0, int64_t rows, Weight** out);
 int get_rows_dev(const Weight* w, int64_t row0, int64_t count, float* d_out, cudaStream_t s);
 int launch_gather_rows(const Weight* w, const int32_t* d_tokens, int count, float* d_out, cudaStream_t s);
 
@@ -247,10 +251,36 @@ int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps,
 
 }  // namespace elb
 
+// tp.cu: tensor-parallel cut of the model's tensors (host arithmetic) and the NCCL communicator
+namespace elb {
+struct TpDims {
+    int rank = 0, size = 1;
+    int H = 0, HKV = 0;                  // heads of this rank
+    int64_t f0 = 0, f1 = 0;              // this rank's slice of the FFN dimension
+    int64_t v0 = 0, v1 = 0, vchunk = 0;  // this rank's vocabulary rows; vchunk = rows per rank in the gathered logits
+};
+struct TpShard {
+    int64_t row0 = 0, rows = 0, col0 = 0, n = 0;
+    int64_t row_bytes = 0, src_row_bytes = 0, src_col_off = 0;
+    size_t nbytes = 0;
+    bool contiguous = true;  // a row slice: the shard is one byte range of the source
+};
+int tp_dims(const elb_config& c, int rank, int size, TpDims* d);
+int tp_shard_shape(const elb_config& c, const TpDims& d, int role, int type, int64_t rows, int64_t n, TpShard* s);
+int tp_shard_copy(const TpShard& s, const uint8_t* src, size_t src_bytes, uint8_t* dst);
+struct TpComm;
+int tp_unique_id(void* id128);
+int tp_comm_create(int device, int rank, int size, const void* id128, TpComm** out);
+void tp_comm_destroy(TpComm* c);
+int tp_all_reduce(TpComm* c, const float* in, float* out, size_t count, cudaStream_t s);
+int tp_all_gather(TpComm* c, const float* in, float* out, size_t count_per_rank, cudaStream_t s);
+}  // namespace elb
+
 // model.cu
 namespace elb {
 struct Model;
 int model_create(const elb_config* cfg, int n_ctx, int device, Model** out);
+int model_create_tp(const elb_config* cfg, int n_ctx, int device, int rank, int size, const void* id128, Model** out);
 int model_set_tensor(Model* m, int role, int layer, int type, int64_t rows, int64_t n, const void* bytes, size_t nbytes);
 int model_finalize(Model* m);
 void model_destroy(Model* m);

@@ -79,6 +79,14 @@ struct Model {
     double* ssq = nullptr;
     unsigned* sync_words = nullptr;  // [1 + 2 n_layer]: barrier counter, then max|att|, max|act| per layer
     int* err_host = nullptr;         // pinned, mapped: raised by the kernel when a barrier wait runs out
+    // tensor parallelism (tp.size == 1: none). H, HKV, F are this rank's share of heads and of the FFN dimension.
+    TpDims tp{};
+    TpComm* comm = nullptr;
+    int H = 0, HKV = 0;
+    int64_t F = 0;
+    float* xr = nullptr;            // [max_batch][E] this rank's partial sums before the all-reduce
+    float* logits_local = nullptr;  // [vchunk] this rank's rows of the head
+    std::vector<std::vector<uint8_t>> shard_store;  // column cuts of wo / down, valid until finalize
 };
 
 namespace {
@@ -170,8 +178,14 @@ int split_tokens(Model* m, const float* xin, int64_t ldx, int n, int nl, const f
 
 int body_prefill(Model* m, int B, int pos0) {
     const elb_config& c = m->cfg;
-    const int E = c.n_embd, F = c.n_ff, H = c.n_head, HKV = c.n_head_kv, QD = H * 128, KD = HKV * 128, QKV = QD + 2 * KD;
+    const int E = c.n_embd, F = int(m->F), H = m->H, HKV = m->HKV, QD = H * 128, KD = HKV * 128, QKV = QD + 2 * KD;
     const float scale = 1.0f / std::sqrt(float(c.head_dim));
+    // row-parallel linears (wo, down): every rank writes its partial sums to xr (rank 0 adds the residual), the
+    // all-reduce leaves the new residual stream in x on every rank
+    const bool tp = m->tp.size > 1;
+    float* yo = tp ? m->xr : m->x;
+    const float* res = !tp || m->tp.rank == 0 ? m->x : nullptr;
+    const int epi_o = res ? EPI_ADD : EPI_STORE;
     for (int l = 0; l < c.n_layer; ++l) {
         Layer& L = m->layers[size_t(l)];
         float* kc = m->kcache + size_t(l) * m->n_ctx * KD;
@@ -184,11 +198,13 @@ int body_prefill(Model* m, int B, int pos0) {
         ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream));
         m->launches += 2;
         ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16));
-        ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, m->x, E, m->x, EPI_ADD, m->nl_wo));
+        ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, yo, E, res, epi_o, m->nl_wo));
+        if (tp) ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(B) * E, m->stream));
         ELB_TRY(split_tokens(m, m->x, E, E, m->nl_gu, L.ffn_norm, B, L.gu->type != ELB_F16));
         ELB_TRY(linear_tokens(m, L.gu, m->x, E, L.ffn_norm, B, m->act, F, nullptr, EPI_SILU, m->nl_gu));
         ELB_TRY(split_tokens(m, m->act, F, F, m->nl_down, nullptr, B, L.down->type != ELB_F16));
-        ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, m->x, E, m->x, EPI_ADD, m->nl_down));
+        ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, yo, E, res, epi_o, m->nl_down));
+        if (tp) ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(B) * E, m->stream));
     }
     return ELB_OK;
 }
@@ -222,6 +238,15 @@ PostOp make_post(Model* m, bool wanted, const float* src, int n, const float* no
     return po;
 }
 
+// the head on limbs already in slot 0 (or on xrow for F16 weights); under tensor parallelism every rank computes its
+// vocabulary rows and the all-gather assembles the logits on all of them
+int head_gemv(Model* m, const float* xrow) {
+    if (m->tp.size == 1)
+        return gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, xrow, m->output_norm}, m->logits, nullptr, EPI_STORE, PostOp{});
+    ELB_TRY(gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, xrow, m->output_norm}, m->logits_local, nullptr, EPI_STORE, PostOp{}));
+    return tp_all_gather(m->comm, m->logits_local, m->logits, size_t(m->tp.vchunk), m->stream);
+}
+
 // final norm + head on one row of x (the reference runs the head as a B=1 matvec too, :1833-1837); stand-alone split
 int head_logits(Model* m, const float* xrow) {
     const int E = m->cfg.n_embd;
@@ -229,7 +254,7 @@ int head_logits(Model* m, const float* xrow) {
         ELB_TRY(prep_limbs_launch(xrow, E, m->output_norm, m->cfg.eps, 4, m->dlimbs[0], m->dinv, false, m->stream));
         ++m->launches;
     }
-    return gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, xrow, m->output_norm}, m->logits, nullptr, EPI_STORE, PostOp{});
+    return head_gemv(m, xrow);
 }
 
 // one token: everything through the matvec kernels; position and token id are read from device memory so that the
@@ -237,8 +262,20 @@ int head_logits(Model* m, const float* xrow) {
 // 3 = input of down; each is filled by the post-op of the kernel that produces the vector.
 int body_decode(Model* m) {
     const elb_config& c = m->cfg;
-    const int E = c.n_embd, F = c.n_ff, H = c.n_head, HKV = c.n_head_kv, QD = H * 128, KD = HKV * 128;
+    const int E = c.n_embd, F = int(m->F), H = m->H, HKV = m->HKV, QD = H * 128, KD = HKV * 128;
     const float scale = 1.0f / std::sqrt(float(c.head_dim));
+    const bool tp = m->tp.size > 1;
+    float* yo = tp ? m->xr : m->x;
+    const float* res = !tp || m->tp.rank == 0 ? m->x : nullptr;
+    const int epi_o = res ? EPI_ADD : EPI_STORE;
+    // after a row-parallel matvec: all-reduce the partial sums into x, then split x for the next matvec (single GPU:
+    // that split is the matvec's own post-op)
+    auto reduce_then_split = [&](bool wanted, const float* norm_w, int nl, int slot) -> int {
+        ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(E), m->stream));
+        if (!wanted) return ELB_OK;
+        ++m->launches;
+        return prep_limbs_launch(m->x, E, norm_w, c.eps, nl, m->dlimbs[slot], m->dinv + slot, false, m->stream);
+    };
     if (m->use_mega) {
         ELB_CUDA(cudaMemsetAsync(m->sync_words, 0, size_t(1 + 2 * c.n_layer) * sizeof(unsigned), m->stream));
         ++m->launches;
@@ -263,16 +300,18 @@ int body_decode(Model* m) {
                          make_post(m, quant(L.wo), m->att, QD, nullptr, m->nl_wo, 1)};
         ELB_TRY(attn_decode_launch(a, m->stream));
         ++m->launches;
-        ELB_TRY(gemv(m, L.wo, ActIn{m->dlimbs[1], m->dinv + 1, m->att, nullptr}, m->x, m->x, EPI_ADD,
-                     make_post(m, quant(L.gu), m->x, E, L.ffn_norm, m->nl_gu, 2)));
+        ELB_TRY(gemv(m, L.wo, ActIn{m->dlimbs[1], m->dinv + 1, m->att, nullptr}, yo, res, epi_o,
+                     make_post(m, !tp && quant(L.gu), m->x, E, L.ffn_norm, m->nl_gu, 2)));
+        if (tp) ELB_TRY(reduce_then_split(quant(L.gu), L.ffn_norm, m->nl_gu, 2));
         ELB_TRY(gemv(m, L.gu, ActIn{m->dlimbs[2], m->dinv + 2, m->x, L.ffn_norm}, m->act, nullptr, EPI_SILU,
                      make_post(m, quant(L.down), m->act, F, nullptr, m->nl_down, 3)));
         const bool next_quant = last ? quant(m->head) : qkv_quant(m->layers[size_t(l) + 1]);
-        ELB_TRY(gemv(m, L.down, ActIn{m->dlimbs[3], m->dinv + 3, m->act, nullptr}, m->x, m->x, EPI_ADD,
-                     make_post(m, next_quant, m->x, E, last ? m->output_norm : m->layers[size_t(l) + 1].attn_norm,
-                               last ? 4 : m->nl_qkv, 0)));
+        const float* next_norm = last ? m->output_norm : m->layers[size_t(l) + 1].attn_norm;
+        ELB_TRY(gemv(m, L.down, ActIn{m->dlimbs[3], m->dinv + 3, m->act, nullptr}, yo, res, epi_o,
+                     make_post(m, !tp && next_quant, m->x, E, next_norm, last ? 4 : m->nl_qkv, 0)));
+        if (tp) ELB_TRY(reduce_then_split(next_quant, next_norm, last ? 4 : m->nl_qkv, 0));
     }
-    return gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, m->x, m->output_norm}, m->logits, nullptr, EPI_STORE, PostOp{});
+    return head_gemv(m, m->x);
 }
 
 // Enqueue one single-token step on the model's stream (token id and position already on the device). The first
@@ -331,7 +370,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
 // shared memory (rings + the longest activation's limbs) fits on one SM. ELB_NO_MEGA=1 keeps the kernel-per-op path.
 int setup_decode_kernel(Model* m) {
     const elb_config& c = m->cfg;
-    if (env_on("ELB_NO_MEGA")) return ELB_OK;
+    if (env_on("ELB_NO_MEGA") || m->tp.size > 1) return ELB_OK;  // the one-kernel step has no exchange between GPUs
     auto mat = [](const Weight* w) {
         return DkMat{w->tiled, w->type, w->unit_bytes, int(w->tiles), int(w->units_per_tile), int(w->rows), int(w->n), w->part, w->counters};
     };
@@ -417,7 +456,12 @@ int setup_decode_kernel(Model* m) {
 }
 
 int model_create(const elb_config* cfg, int n_ctx, int device, Model** out) {
+    return model_create_tp(cfg, n_ctx, device, 0, 1, nullptr, out);
+}
+
+int model_create_tp(const elb_config* cfg, int n_ctx, int device, int rank, int size, const void* id128, Model** out) {
     if (!cfg || !out) return fail(ELB_ERR_INVALID, "model_create: null argument");
+    if (size > 1 && !id128) return fail(ELB_ERR_INVALID, "model_create: tensor parallelism needs the communicator id");
     if (n_ctx <= 0) return fail(ELB_ERR_INVALID, "model_create: context length must be positive");
     if (cfg->n_layer <= 0 || cfg->n_layer > 512 || cfg->n_embd <= 0 || cfg->n_head <= 0 || cfg->n_head_kv <= 0 ||
         cfg->n_head % cfg->n_head_kv != 0 || cfg->n_ff <= 0 || cfg->n_vocab <= 0 || cfg->rope_dim <= 0 ||
@@ -430,10 +474,18 @@ int model_create(const elb_config* cfg, int n_ctx, int device, Model** out) {
         cudaGetLastError();
         return fail(ELB_ERR_CUDA, "model_create: no such CUDA device");
     }
+    TpDims tp;
+    ELB_TRY(tp_dims(*cfg, rank, size, &tp));
     auto* m = new Model;
     m->cfg = *cfg;
+    m->tp = tp;
+    m->H = tp.H; m->HKV = tp.HKV; m->F = tp.f1 - tp.f0;
     m->n_ctx = n_ctx;
     m->device = device;
+    if (size > 1) {
+        const int rc = tp_comm_create(device, rank, size, id128, &m->comm);
+        if (rc != ELB_OK) { delete m; return rc; }
+    }
     m->max_batch = cfg->max_batch > 0 ? cfg->max_batch : 512;
     m->pending.resize(size_t(3 + cfg->n_layer * 11));
     m->layers.resize(size_t(cfg->n_layer));
@@ -461,7 +513,7 @@ void model_destroy(Model* m) {
     cudaSetDevice(m->device);
     if (m->stream) cudaStreamSynchronize(m->stream);
     if (m->graph) cudaGraphExecDestroy(m->graph);
-    if (m->head && m->head != m->embd) weight_destroy(m->head);
+    if (m->head && m->head != m->embd) weight_destroy(m->head);  // also a row view of embd (tied head under TP)
     weight_destroy(m->embd);
     for (Layer& L : m->layers) {
         for (auto& s : L.qkv) weight_destroy(s.w);
@@ -474,6 +526,8 @@ void model_destroy(Model* m) {
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
     cudaFree(m->dk_layers); cudaFree(m->ssq); cudaFree(m->sync_words);
+    cudaFree(m->xr); cudaFree(m->logits_local);
+    tp_comm_destroy(m->comm);
     if (m->err_host) cudaFreeHost(m->err_host);
     if (m->tokens_host) cudaFreeHost(m->tokens_host);
     if (m->pos_host) cudaFreeHost(m->pos_host);
@@ -488,9 +542,10 @@ int model_finalize(Model* m) {
     if (m->finalized) return fail(ELB_ERR_STATE, "finalize: called twice");
     ELB_CUDA(cudaSetDevice(m->device));
     const elb_config& c = m->cfg;
-    const int64_t E = c.n_embd, F = c.n_ff, QD = int64_t(c.n_head) * 128, KD = int64_t(c.n_head_kv) * 128, QKV = QD + 2 * KD;
-    const int64_t V = c.n_vocab, B = m->max_batch;
+    const int64_t E = c.n_embd, V = c.n_vocab, B = m->max_batch;
     auto P = [&](int role, int layer) -> const HostTensor& { return m->pending[size_t(slot_of(m, role, layer))]; };
+    {   // global shapes, then (tensor parallel) every tensor is replaced by this rank's cut of it
+        const int64_t F = c.n_ff, QD = int64_t(c.n_head) * 128, KD = int64_t(c.n_head_kv) * 128;
 
     // shapes (read_tensors of the reference, src/model.cpp:66-103)
     ELB_TRY(check_shape(P(ELB_TOK_EMBD, 0), V, E, "token_embd"));
@@ -504,6 +559,27 @@ int model_finalize(Model* m) {
         ELB_TRY(check_shape(P(ELB_UP, l), F, E, "ffn_up"));
         ELB_TRY(check_shape(P(ELB_DOWN, l), E, F, "ffn_down"));
     }
+    }
+    if (m->tp.size > 1) {
+        for (int role = ELB_OUTPUT; role <= ELB_DOWN; ++role) {
+            if (role != ELB_OUTPUT && role < ELB_WQ) continue;
+            for (int l = 0; l < (role == ELB_OUTPUT ? 1 : c.n_layer); ++l) {
+                HostTensor& t = m->pending[size_t(slot_of(m, role, l))];
+                if (!t.bytes) continue;
+                TpShard sh;
+                ELB_TRY(tp_shard_shape(c, m->tp, role, t.type, t.rows, t.n, &sh));
+                if (sh.contiguous) {
+                    t.bytes += size_t(sh.row0) * size_t(sh.src_row_bytes);
+                } else {
+                    m->shard_store.emplace_back(sh.nbytes);
+                    ELB_TRY(tp_shard_copy(sh, t.bytes, t.nbytes, m->shard_store.back().data()));
+                    t.bytes = m->shard_store.back().data();
+                }
+                t.rows = sh.rows; t.n = sh.n; t.nbytes = sh.nbytes;
+            }
+        }
+    }
+    const int64_t F = m->F, QD = int64_t(m->H) * 128, KD = int64_t(m->HKV) * 128, QKV = QD + 2 * KD;
 
     // device memory budget before anything is allocated (pre-flight check of the reference, :1578-1591)
     const size_t kv_bytes = size_t(c.n_layer) * size_t(m->n_ctx) * size_t(KD) * sizeof(float);
@@ -530,6 +606,9 @@ int model_finalize(Model* m) {
     const HostTensor& outw = P(ELB_OUTPUT, 0);
     if (outw.bytes) {
         ELB_TRY(weight_create(m->device, outw.type, outw.rows, outw.n, outw.bytes, outw.nbytes, 0, &m->head));
+        ELB_TRY(gemv_prepare(m->head));
+    } else if (m->tp.size > 1) {
+        ELB_TRY(weight_view_rows(m->embd, m->tp.v0, m->tp.v1 - m->tp.v0, &m->head));  // this rank's rows of the tied table
         ELB_TRY(gemv_prepare(m->head));
     } else {
         m->head = m->embd;  // tied embeddings (src/model.cpp:73-74 of the reference)
@@ -575,7 +654,11 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->qkv, size_t(B) * QKV * 4));
     ELB_CUDA(cudaMalloc(&m->att, size_t(B) * QD * 4));
     ELB_CUDA(cudaMalloc(&m->act, size_t(B) * F * 4));
-    ELB_CUDA(cudaMalloc(&m->logits, size_t(V) * 4));
+    ELB_CUDA(cudaMalloc(&m->logits, size_t(std::max<int64_t>(V, m->tp.vchunk * m->tp.size)) * 4));
+    if (m->tp.size > 1) {
+        ELB_CUDA(cudaMalloc(&m->xr, size_t(B) * E * 4));
+        ELB_CUDA(cudaMalloc(&m->logits_local, size_t(m->tp.vchunk) * 4));
+    }
     ELB_CUDA(cudaMalloc(&m->limbs, size_t(4) * B * maxn));
     ELB_CUDA(cudaMalloc(&m->inv_scale, size_t(B) * 4));
     ELB_CUDA(cudaMalloc(&m->xsum, size_t(B) * (maxn / 32 + 1) * 4));
@@ -593,15 +676,17 @@ int model_finalize(Model* m) {
     // decode attention: a fixed number of key splits so that the launch shape does not depend on the position
     DeviceInfo di;
     ELB_TRY(device_info(m->device, &di));
-    m->attn_split = std::max(1, std::min(32, (di.sm_count + c.n_head_kv - 1) / c.n_head_kv));
+    m->attn_split = std::max(1, std::min(32, (di.sm_count + m->HKV - 1) / m->HKV));
     if (const char* v = std::getenv("ELB_ATTN_SPLIT")) m->attn_split = std::max(1, std::min(32, std::atoi(v)));
     const int group = c.n_head / c.n_head_kv;
-    ELB_CUDA(cudaMalloc(&m->attn_part, size_t(c.n_head_kv) * m->attn_split * group * (128 + 2) * 4));
-    ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(c.n_head_kv) * sizeof(unsigned)));
-    ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(c.n_head_kv) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&m->attn_part, size_t(m->HKV) * m->attn_split * group * (128 + 2) * 4));
+    ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(m->HKV) * sizeof(unsigned)));
+    ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(m->HKV) * sizeof(unsigned)));
     ELB_TRY(setup_decode_kernel(m));
     m->pending.clear();
     m->pending.shrink_to_fit();
+    m->shard_store.clear();
+    m->shard_store.shrink_to_fit();
     m->finalized = true;
     return ELB_OK;
 }
@@ -691,7 +776,7 @@ int model_hidden(Model* m, float* out) {
 }
 
 size_t model_weight_bytes(const Model* m) { return m->weight_bytes; }
-size_t model_kv_bytes_per_token(const Model* m) { return size_t(2) * m->cfg.n_layer * m->cfg.n_head_kv * 128 * sizeof(float); }
+size_t model_kv_bytes_per_token(const Model* m) { return size_t(2) * m->cfg.n_layer * m->HKV * 128 * sizeof(float); }
 int model_device(const Model* m) { return m->device; }
 
 }  // namespace elb

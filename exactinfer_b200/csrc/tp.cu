@@ -1,0 +1,186 @@
+// Tensor parallelism over the GPUs of one box: how each tensor of the model is cut for rank r of N (host code, no
+// device needed), and the NCCL communicator the forward pass calls for its two all-reduces per layer.
+// The reference runs on one GPU; the cut is the usual column/row split of its layer (CpuModel::forward,
+// src/model.cpp:157-234), which keeps every head and every SwiGLU element on one rank:
+//   attn_q/k/v   rows of whole heads      H/N query heads, HKV/N key-value heads per rank
+//   attn_output  columns of those heads   partial sums -> all-reduce
+//   ffn_gate/up  rows [f0, f1)            f0, f1 multiples of 256 (uneven when F/256 is not a multiple of N)
+//   ffn_down     columns [f0, f1)         partial sums -> all-reduce
+//   output head  rows [v0, v1)            whole 16-row tiles; logits are all-gathered
+//   norms, token embedding               replicated
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace elb {
+
+int tp_dims(const elb_config& c, int rank, int size, TpDims* d) {
+    if (size < 1 || rank < 0 || rank >= size) return fail(ELB_ERR_INVALID, "tensor parallel: rank outside [0, size)");
+    if (c.n_head_kv % size || c.n_head % size)
+        return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: the number of ranks must divide the KV and query head counts");
+    d->rank = rank; d->size = size;
+    d->H = c.n_head / size;
+    d->HKV = c.n_head_kv / size;
+    if (size > 1 && (int64_t(d->H) * c.head_dim) % 256)
+        return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: query heads per rank x head_dim must be a multiple of 256");
+    if (size > 1 && c.n_ff % 256) return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: n_ff must be a multiple of 256");
+    if (size == 1) {
+        d->f0 = 0; d->f1 = c.n_ff;
+    } else {
+        const int64_t nb = c.n_ff / 256;
+        if (nb < size) return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: fewer 256-blocks in n_ff than ranks");
+        d->f0 = nb * rank / size * 256;
+        d->f1 = nb * (rank + 1) / size * 256;
+    }
+    const int64_t tiles = (int64_t(c.n_vocab) + 15) / 16;
+    if (tiles < size) return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: vocabulary smaller than 16 rows per rank");
+    d->vchunk = (tiles + size - 1) / size * 16;
+    d->v0 = std::min<int64_t>(d->vchunk * rank, c.n_vocab);
+    d->v1 = std::min<int64_t>(d->vchunk * (rank + 1), c.n_vocab);
+    if (d->v1 <= d->v0) return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: a rank would own no vocabulary rows");
+    return ELB_OK;
+}
+
+namespace {
+
+// bytes of `cols` consecutive values of a row, starting at a multiple of the type's block; -1 when not block aligned
+int64_t col_bytes(int type, int64_t cols) {
+    switch (type) {
+        case ELB_F32: return cols * 4;
+        case ELB_F16: return cols * 2;
+        case ELB_Q8_0: return cols % QK8_0 ? -1 : cols / QK8_0 * Q8_0_BYTES;
+        case ELB_Q4_K: return cols % QK_K ? -1 : cols / QK_K * Q4_K_BYTES;
+        case ELB_Q6_K: return cols % QK_K ? -1 : cols / QK_K * Q6_K_BYTES;
+        default: return -1;
+    }
+}
+
+}  // namespace
+
+int tp_shard_shape(const elb_config& c, const TpDims& d, int role, int type, int64_t rows, int64_t n, TpShard* s) {
+    s->row0 = 0; s->rows = rows; s->col0 = 0; s->n = n;
+    const int64_t hd = c.head_dim;
+    switch (role) {
+        case ELB_WQ: s->row0 = int64_t(d.rank) * d.H * hd; s->rows = int64_t(d.H) * hd; break;
+        case ELB_WK:
+        case ELB_WV: s->row0 = int64_t(d.rank) * d.HKV * hd; s->rows = int64_t(d.HKV) * hd; break;
+        case ELB_WO: s->col0 = int64_t(d.rank) * d.H * hd; s->n = int64_t(d.H) * hd; break;
+        case ELB_GATE:
+        case ELB_UP: s->row0 = d.f0; s->rows = d.f1 - d.f0; break;
+        case ELB_DOWN: s->col0 = d.f0; s->n = d.f1 - d.f0; break;
+        case ELB_OUTPUT: s->row0 = d.v0; s->rows = d.v1 - d.v0; break;
+        default: break;  // norms and the token embedding are replicated
+    }
+    if (s->row0 + s->rows > rows || s->col0 + s->n > n) return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: tensor smaller than its shard");
+    const int64_t rb = col_bytes(type, s->n), full = col_bytes(type, n), off = col_bytes(type, s->col0);
+    if (rb < 0 || full < 0 || off < 0) return fail(ELB_ERR_UNSUPPORTED, "tensor parallel: column cut not on a block boundary of this type");
+    s->row_bytes = rb; s->src_row_bytes = full; s->src_col_off = off;
+    s->nbytes = size_t(rb) * size_t(s->rows);
+    s->contiguous = s->n == n;
+    return ELB_OK;
+}
+
+int tp_shard_copy(const TpShard& s, const uint8_t* src, size_t src_bytes, uint8_t* dst) {
+    if (!src || !dst) return fail(ELB_ERR_INVALID, "tensor parallel: null buffer");
+    if (size_t(s.src_row_bytes) * size_t(s.row0 + s.rows) > src_bytes) return fail(ELB_ERR_INVALID, "tensor parallel: source tensor too short");
+    for (int64_t r = 0; r < s.rows; ++r)
+        std::memcpy(dst + size_t(r) * s.row_bytes, src + size_t(s.row0 + r) * s.src_row_bytes + s.src_col_off, size_t(s.row_bytes));
+    return ELB_OK;
+}
+
+// ---------------------------------------------------------------- NCCL, resolved at run time
+// The library is found with dlopen so that single-GPU users need no NCCL: a process that already loaded one (PyTorch
+// brings its own) gets that copy, others the system's.
+namespace {
+
+struct Nccl {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    std::string why;
+};
+
+Nccl* nccl() {
+    static Nccl n;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
+            n.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+            if (n.handle) break;
+        }
+        if (!n.handle) { n.why = "NCCL not found (libnccl.so.2)"; return; }
+        auto sym = [&](const char* s) { void* p = dlsym(n.handle, s); if (!p) n.why = std::string("NCCL lacks ") + s; return p; };
+        n.GetUniqueId = reinterpret_cast<decltype(n.GetUniqueId)>(sym("ncclGetUniqueId"));
+        n.CommInitRank = reinterpret_cast<decltype(n.CommInitRank)>(sym("ncclCommInitRank"));
+        n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(sym("ncclCommDestroy"));
+        n.AllReduce = reinterpret_cast<decltype(n.AllReduce)>(sym("ncclAllReduce"));
+        n.AllGather = reinterpret_cast<decltype(n.AllGather)>(sym("ncclAllGather"));
+        n.GetErrorString = reinterpret_cast<decltype(n.GetErrorString)>(sym("ncclGetErrorString"));
+    });
+    return &n;
+}
+
+int nccl_fail(Nccl* n, ncclResult_t r, const char* what) {
+    return fail(ELB_ERR_CUDA, std::string(what) + ": " + (n->GetErrorString ? n->GetErrorString(r) : "NCCL error"));
+}
+
+}  // namespace
+
+struct TpComm {
+    ncclComm_t comm = nullptr;
+    int rank = 0, size = 1;
+};
+
+int tp_unique_id(void* id128) {
+    static_assert(sizeof(ncclUniqueId) == 128, "NCCL unique id is 128 bytes");
+    if (!id128) return fail(ELB_ERR_INVALID, "tp_unique_id: null buffer");
+    Nccl* n = nccl();
+    if (!n->why.empty()) return fail(ELB_ERR_UNSUPPORTED, n->why);
+    ncclUniqueId id;
+    const ncclResult_t r = n->GetUniqueId(&id);
+    if (r != ncclSuccess) return nccl_fail(n, r, "ncclGetUniqueId");
+    std::memcpy(id128, &id, 128);
+    return ELB_OK;
+}
+
+int tp_comm_create(int device, int rank, int size, const void* id128, TpComm** out) {
+    if (!id128 || !out) return fail(ELB_ERR_INVALID, "tp_comm_create: null argument");
+    Nccl* n = nccl();
+    if (!n->why.empty()) return fail(ELB_ERR_UNSUPPORTED, n->why);
+    ELB_CUDA(cudaSetDevice(device));
+    ncclUniqueId id;
+    std::memcpy(&id, id128, 128);
+    auto* c = new TpComm;
+    c->rank = rank; c->size = size;
+    const ncclResult_t r = n->CommInitRank(&c->comm, size, id, rank);
+    if (r != ncclSuccess) { delete c; return nccl_fail(n, r, "ncclCommInitRank"); }
+    *out = c;
+    return ELB_OK;
+}
+
+void tp_comm_destroy(TpComm* c) {
+    if (!c) return;
+    if (c->comm) nccl()->CommDestroy(c->comm);
+    delete c;
+}
+
+int tp_all_reduce(TpComm* c, const float* in, float* out, size_t count, cudaStream_t s) {
+    const ncclResult_t r = nccl()->AllReduce(in, out, count, ncclFloat, ncclSum, c->comm, s);
+    return r == ncclSuccess ? ELB_OK : nccl_fail(nccl(), r, "ncclAllReduce");
+}
+
+int tp_all_gather(TpComm* c, const float* in, float* out, size_t count_per_rank, cudaStream_t s) {
+    const ncclResult_t r = nccl()->AllGather(in, out, count_per_rank, ncclFloat, c->comm, s);
+    return r == ncclSuccess ? ELB_OK : nccl_fail(nccl(), r, "ncclAllGather");
+}
+
+}  // namespace elb

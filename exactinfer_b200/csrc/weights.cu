@@ -172,9 +172,24 @@ int weight_create(int device, int type, int64_t rows_one, int64_t n, const void*
     return ELB_OK;
 }
 
+int weight_view_rows(const Weight* base, int64_t row0, int64_t rows, Weight** out) {
+    if (!base || !out || rows <= 0 || row0 < 0 || row0 + rows > base->rows) return fail(ELB_ERR_INVALID, "weight_view_rows: bad range");
+    if (row0 % 16 || base->pair) return fail(ELB_ERR_UNSUPPORTED, "weight_view_rows: the first row must be a multiple of 16 of an unpaired weight");
+    auto* w = new Weight;
+    w->device = base->device; w->type = base->type; w->rows = rows; w->n = base->n; w->view = true;
+    w->tiles = (rows + 15) / 16;
+    w->units_per_tile = base->units_per_tile; w->unit_bytes = base->unit_bytes;
+    const size_t tile_bytes = base->type == ELB_F16 ? size_t(16) * base->n * 2 : size_t(base->units_per_tile) * base->unit_bytes;
+    w->tiled = base->tiled + size_t(row0 / 16) * tile_bytes;
+    w->tiled_bytes = size_t(w->tiles) * tile_bytes;
+    *out = w;
+    return ELB_OK;
+}
+
 void weight_destroy(Weight* w) {
     if (!w) return;
     cudaSetDevice(w->device);
+    if (w->view) w->tiled = nullptr;
     cudaFree(w->tiled); cudaFree(w->planes); cudaFree(w->pl_d); cudaFree(w->pl_dm); cudaFree(w->part); cudaFree(w->counters); cudaFree(w->xlimbs); cudaFree(w->xinv);
     delete w;
 }

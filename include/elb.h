@@ -151,6 +151,30 @@ int elb_model_hidden(elb_model* m, float* out);
 size_t elb_model_weight_bytes(const elb_model* m); /* bytes one decode step streams from the weight tensors */
 size_t elb_model_kv_bytes_per_token(const elb_model* m);
 
+/* ---- tensor parallelism over the GPUs of one box (one process per GPU). The reference is single-GPU; these calls have
+ * no counterpart there. The cut keeps whole heads and whole SwiGLU elements on a rank: attn_q/k/v and ffn_gate/up by
+ * rows, attn_output and ffn_down by columns (their partial sums are all-reduced over NCCL, one all-reduce per
+ * attention block and one per MLP block), the head by rows (logits are all-gathered); norms and the token embedding
+ * are replicated. tp_size must divide n_head and n_head_kv; n_ff is cut in multiples of 256, unevenly if need be.
+ *
+ * elb_tp_dims / elb_tp_shard_shape / elb_tp_shard_copy are host arithmetic and need no GPU: the share of rank
+ * tp_rank in the heads, the FFN range [f0, f1), the vocabulary rows [v0, v1), and the cut of one tensor (role as in
+ * elb_model_set_tensor) as shape, byte size and bytes. */
+int elb_tp_dims(const elb_config* cfg, int tp_rank, int tp_size, int* n_head, int* n_head_kv, int64_t* f0, int64_t* f1,
+                int64_t* v0, int64_t* v1);
+int elb_tp_shard_shape(const elb_config* cfg, int tp_rank, int tp_size, int role, int ggml_type, int64_t rows, int64_t n,
+                       int64_t* out_rows, int64_t* out_n, size_t* out_nbytes);
+int elb_tp_shard_copy(const elb_config* cfg, int tp_rank, int tp_size, int role, int ggml_type, int64_t rows, int64_t n,
+                      const void* bytes, size_t nbytes, void* out, size_t out_nbytes);
+/* 128-byte NCCL id: rank 0 makes one and hands it to the other ranks by any means it has (a file, a socket,
+ * torch.distributed); every rank passes it to elb_model_create_tp, which joins the communicator (collective call). */
+int elb_tp_unique_id(void* id128);
+/* Like elb_model_create for rank tp_rank of tp_size; cfg is the WHOLE model's configuration and elb_model_set_tensor
+ * still receives the whole tensors: elb_model_finalize uploads only this rank's cut. elb_model_eval must then be
+ * called by all ranks with the same arguments; every rank receives the full logits. */
+int elb_model_create_tp(const elb_config* cfg, int n_ctx, int device, int tp_rank, int tp_size, const void* id128,
+                        elb_model** out);
+
 /* ---- timing helpers for microbenchmarks: run the device-pointer matvec `iters` times over `n_w` weights in
  * rotation (so that the working set exceeds L2) and return the average device time per call in ms. */
 int elb_bench_matvec(elb_weight* const* ws, int n_w, const float* d_x, float* d_y, int nl, int iters, float* avg_ms);
