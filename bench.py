@@ -212,7 +212,7 @@ def run_reference(args):
                                 "take minutes on the host), bounded to 150 s"},
            "cpu_baseline": base,
            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(out), flush=True)
+    emit(json.dumps(out))
 
 
 # ---------------------------------------------------------------- the dominant kernel alone (roofline)
@@ -377,13 +377,22 @@ def run_ours(args):
     if n_gpus == 1 and not args.no_cpu_baseline:
         base, _, _ = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)
         out["cpu_baseline"] = base
-    print(json.dumps(out), flush=True)
+    emit(json.dumps(out))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 
 
+def emit(line: str):
+    os.write(REAL_STDOUT, (line + "\n").encode())
+
+
 if __name__ == "__main__":
+    # libraries (NCCL's version banner, for one) print to stdout: send file descriptor 1 to stderr for the whole run and
+    # keep the real one for the single JSON line
+    sys.stdout.flush()
+    REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)

@@ -274,6 +274,28 @@ int tp_comm_create(int device, int rank, int size, const void* id128, TpComm** o
 void tp_comm_destroy(TpComm* c);
 int tp_all_reduce(TpComm* c, const float* in, float* out, size_t count, cudaStream_t s);
 int tp_all_gather(TpComm* c, const float* in, float* out, size_t count_per_rank, cudaStream_t s);
+struct TpPeerBuf {
+    void* local = nullptr;
+    void* peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int size = 0;
+};
+int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok);
+void tp_peer_free(TpPeerBuf* b, int rank);
+
+// tp_reduce.cu: all-reduce of one activation vector through peer memory, fused with the limb split that follows it
+struct TpReduce {
+    TpPeerBuf buf;       // per rank: flags [2][8] words, then slots [2][size][n_max] floats
+    int rank = 0, size = 1, n_max = 0;
+    unsigned* seq = nullptr;  // device counter of reductions done
+    int* err_host = nullptr;  // pinned, mapped: raised when a peer did not arrive in time
+    int* err_dev = nullptr;
+};
+int tp_reduce_create(TpComm* c, int device, int rank, int size, int n_max, cudaStream_t s, TpReduce** out);  // *out null: unavailable
+void tp_reduce_destroy(TpReduce* r);
+// x[n] = sum over ranks (rank order) of their `part`; then, when limbs != null, the split of x (RMSNorm first when
+// norm_w != null) as prep_limbs_launch leaves it. Collective: every rank launches it with the same n.
+int tp_reduce_split_launch(TpReduce* r, const float* part, float* x, int n, const float* norm_w, float eps, int nl,
+                           int8_t* limbs, float* inv_scale, cudaStream_t s);
 }  // namespace elb
 
 // model.cu

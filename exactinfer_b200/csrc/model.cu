@@ -82,6 +82,7 @@ struct Model {
     // tensor parallelism (tp.size == 1: none). H, HKV, F are this rank's share of heads and of the FFN dimension.
     TpDims tp{};
     TpComm* comm = nullptr;
+    TpReduce* tpr = nullptr;  // single-token all-reduce through peer memory (null: NCCL)
     int H = 0, HKV = 0;
     int64_t F = 0;
     float* xr = nullptr;            // [max_batch][E] this rank's partial sums before the all-reduce
@@ -271,6 +272,11 @@ int body_decode(Model* m) {
     // after a row-parallel matvec: all-reduce the partial sums into x, then split x for the next matvec (single GPU:
     // that split is the matvec's own post-op)
     auto reduce_then_split = [&](bool wanted, const float* norm_w, int nl, int slot) -> int {
+        if (m->tpr) {  // one kernel: exchange through peer memory, sum, (norm +) split
+            ++m->launches;
+            return tp_reduce_split_launch(m->tpr, m->xr, m->x, E, norm_w, c.eps, nl, wanted ? m->dlimbs[slot] : nullptr,
+                                          m->dinv + slot, m->stream);
+        }
         ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(E), m->stream));
         if (!wanted) return ELB_OK;
         ++m->launches;
@@ -357,6 +363,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
         ELB_CUDA(cudaMemcpyAsync(logits, m->logits, size_t(m->cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
+    if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
     ELB_TRY(gemm_tc_check());
     float ms = 0.f;
     ELB_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
@@ -527,6 +534,7 @@ void model_destroy(Model* m) {
         cudaFree(p);
     cudaFree(m->dk_layers); cudaFree(m->ssq); cudaFree(m->sync_words);
     cudaFree(m->xr); cudaFree(m->logits_local);
+    tp_reduce_destroy(m->tpr);
     tp_comm_destroy(m->comm);
     if (m->err_host) cudaFreeHost(m->err_host);
     if (m->tokens_host) cudaFreeHost(m->tokens_host);
@@ -656,6 +664,7 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->act, size_t(B) * F * 4));
     ELB_CUDA(cudaMalloc(&m->logits, size_t(std::max<int64_t>(V, m->tp.vchunk * m->tp.size)) * 4));
     if (m->tp.size > 1) {
+        if (!env_on("ELB_TP_NCCL")) ELB_TRY(tp_reduce_create(m->comm, m->device, m->tp.rank, m->tp.size, int(E), m->stream, &m->tpr));
         ELB_CUDA(cudaMalloc(&m->xr, size_t(B) * E * 4));
         ELB_CUDA(cudaMalloc(&m->logits_local, size_t(m->tp.vchunk) * 4));
     }
@@ -737,6 +746,7 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
     if (rc != ELB_OK) return rc;
     ELB_CUDA(e);
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
+    if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
     ELB_CUDA(cudaEventElapsedTime(device_ms, m->ev0, m->ev1));
     m->last_ms = *device_ms;
     m->last_launches = m->launches - before;

@@ -93,6 +93,37 @@ __device__ __forceinline__ int split_shift(float m, int nl) {  // k = 8 nl - 2 -
 // One block of SPLIT_THREADS threads: the split vector `out` (layout above; limbs beyond nl come out zero because
 // |X| < 2^(8 nl - 2); n must be a multiple of 256) and *inv_scale = 2^-k. src is read through L2 (it may have been written by other CTAs of
 // the running kernel). red: 8 doubles of shared memory.
+// The split of a vector that the block already holds in registers: thread tid owns float4 number j * SPLIT_THREADS + tid
+// in v[j] (zero beyond n). Returns k.
+__device__ __forceinline__ int block_split_values(float4 (&v)[SPLIT_V4], int n, const float* norm_w, float eps, int nl,
+                                                  int8_t* out, double* red) {
+    const int tid = threadIdx.x;
+    if (norm_w) {
+        double ss = 0.0;
+#pragma unroll
+        for (int j = 0; j < SPLIT_V4; ++j)
+            ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
+        ss = block_sum(ss, red, tid);
+        const float inv = float(1.0 / sqrt(ss / n + double(eps)));
+#pragma unroll
+        for (int j = 0; j < SPLIT_V4; ++j) {
+            const int idx = (j * SPLIT_THREADS + tid) * 4;
+            if (idx < n) v[j] = norm4(v[j], inv, __ldg(reinterpret_cast<const float4*>(norm_w + idx)));
+        }
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < SPLIT_V4; ++j) m = fmaxf(m, absmax4(v[j]));
+    const int k = split_shift(block_max(m, reinterpret_cast<float*>(red), tid), nl);
+    const Pow2 sc = make_pow2(k);
+#pragma unroll
+    for (int j = 0; j < SPLIT_V4; ++j) {
+        const int idx = (j * SPLIT_THREADS + tid) * 4;
+        if (j * SPLIT_THREADS * 4 < n) split4(v[j], sc, out, n, out + act_sd32_off(n), out + act_sd16_off(n), idx, idx < n);  // warp-uniform guard: n % 128 == 0
+    }
+    return k;
+}
+
 __device__ __forceinline__ void block_split(const float* src, int n, const float* norm_w, float eps, int nl, int8_t* out,
                                             float* inv_scale, double* red) {
     const int tid = threadIdx.x;
@@ -104,29 +135,7 @@ __device__ __forceinline__ void block_split(const float* src, int n, const float
             const int idx = (j * SPLIT_THREADS + tid) * 4;
             v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(src + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (norm_w) {
-            double ss = 0.0;
-#pragma unroll
-            for (int j = 0; j < SPLIT_V4; ++j)
-                ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
-            ss = block_sum(ss, red, tid);
-            const float inv = float(1.0 / sqrt(ss / n + double(eps)));
-#pragma unroll
-            for (int j = 0; j < SPLIT_V4; ++j) {
-                const int idx = (j * SPLIT_THREADS + tid) * 4;
-                if (idx < n) v[j] = norm4(v[j], inv, __ldg(reinterpret_cast<const float4*>(norm_w + idx)));
-            }
-        }
-        float m = 0.f;
-#pragma unroll
-        for (int j = 0; j < SPLIT_V4; ++j) m = fmaxf(m, absmax4(v[j]));
-        k = split_shift(block_max(m, reinterpret_cast<float*>(red), tid), nl);
-        const Pow2 sc = make_pow2(k);
-#pragma unroll
-        for (int j = 0; j < SPLIT_V4; ++j) {
-            const int idx = (j * SPLIT_THREADS + tid) * 4;
-            if (j * SPLIT_THREADS * 4 < n) split4(v[j], sc, out, n, out + act_sd32_off(n), out + act_sd16_off(n), idx, idx < n);  // warp-uniform guard: n % 128 == 0
-        }
+        k = block_split_values(v, n, norm_w, eps, nl, out, red);
     } else {  // long vectors: passes over src, the later ones served by cache
         float inv = 1.0f;
         if (norm_w) {

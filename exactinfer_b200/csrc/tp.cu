@@ -14,6 +14,7 @@
 #include <algorithm>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -181,6 +182,72 @@ int tp_all_reduce(TpComm* c, const float* in, float* out, size_t count, cudaStre
 int tp_all_gather(TpComm* c, const float* in, float* out, size_t count_per_rank, cudaStream_t s) {
     const ncclResult_t r = nccl()->AllGather(in, out, count_per_rank, ncclFloat, c->comm, s);
     return r == ncclSuccess ? ELB_OK : nccl_fail(nccl(), r, "ncclAllGather");
+}
+
+
+// ---------------------------------------------------------------- peer-visible buffers (one process per GPU)
+// Every rank allocates `bytes` of device memory, zeroes it, and the ranks exchange CUDA IPC handles through the
+// communicator; peer[r] is rank r's buffer as mapped into this process (peer[rank] = the local one). `ok` comes back
+// false on every rank when any rank could not map a peer (the caller then keeps to NCCL).
+int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok) {
+    *ok = false;
+    *out = TpPeerBuf{};
+    if (!c || c->size < 2 || c->size > 8) return ELB_OK;
+    ELB_CUDA(cudaSetDevice(device));
+    out->size = c->size;
+    ELB_CUDA(cudaMalloc(&out->local, bytes));
+    ELB_CUDA(cudaMemset(out->local, 0, bytes));
+    cudaIpcMemHandle_t mine;
+    int good = cudaIpcGetMemHandle(&mine, out->local) == cudaSuccess ? 1 : 0;
+    if (!good) cudaGetLastError();
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle is 64 bytes");
+    uint8_t *d_send = nullptr, *d_recv = nullptr;
+    ELB_CUDA(cudaMalloc(&d_send, 64 + 4));
+    ELB_CUDA(cudaMalloc(&d_recv, size_t(68) * c->size));
+    uint8_t pack[68];
+    std::memcpy(pack, &mine, 64);
+    std::memcpy(pack + 64, &good, 4);
+    ELB_CUDA(cudaMemcpyAsync(d_send, pack, 68, cudaMemcpyHostToDevice, s));
+    ncclResult_t r = nccl()->AllGather(d_send, d_recv, 68, ncclInt8, c->comm, s);
+    if (r != ncclSuccess) return nccl_fail(nccl(), r, "ncclAllGather (peer handles)");
+    std::vector<uint8_t> all(size_t(68) * c->size);
+    ELB_CUDA(cudaMemcpyAsync(all.data(), d_recv, all.size(), cudaMemcpyDeviceToHost, s));
+    ELB_CUDA(cudaStreamSynchronize(s));
+    for (int p = 0; p < c->size; ++p) {
+        int g = 0;
+        std::memcpy(&g, all.data() + size_t(p) * 68 + 64, 4);
+        good &= g;
+    }
+    for (int p = 0; p < c->size && good; ++p) {
+        if (p == c->rank) { out->peer[p] = out->local; continue; }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, all.data() + size_t(p) * 68, 64);
+        if (cudaIpcOpenMemHandle(&out->peer[p], h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            out->peer[p] = nullptr;
+            good = 0;
+        }
+    }
+    // every rank must take the same path: agree on the outcome
+    float flag = good ? 0.f : 1.f, *d_flag = reinterpret_cast<float*>(d_send);
+    ELB_CUDA(cudaMemcpyAsync(d_flag, &flag, 4, cudaMemcpyHostToDevice, s));
+    r = nccl()->AllReduce(d_flag, d_flag, 1, ncclFloat, ncclSum, c->comm, s);
+    if (r != ncclSuccess) return nccl_fail(nccl(), r, "ncclAllReduce (peer mapping outcome)");
+    ELB_CUDA(cudaMemcpyAsync(&flag, d_flag, 4, cudaMemcpyDeviceToHost, s));
+    ELB_CUDA(cudaStreamSynchronize(s));
+    cudaFree(d_send);
+    cudaFree(d_recv);
+    *ok = flag == 0.f;
+    if (!*ok) tp_peer_free(out, c->rank);
+    return ELB_OK;
+}
+
+void tp_peer_free(TpPeerBuf* b, int rank) {
+    if (!b) return;
+    for (int p = 0; p < b->size; ++p)
+        if (p != rank && b->peer[p]) cudaIpcCloseMemHandle(b->peer[p]);
+    cudaFree(b->local);
+    *b = TpPeerBuf{};
 }
 
 }  // namespace elb

@@ -1,0 +1,165 @@
+// All-reduce of one activation vector across the tensor-parallel ranks through peer memory, fused with what follows it
+// in the decode chain: the new residual stream and its (RMSNorm +) limb split for the next matvec.
+//
+// A single-token all-reduce moves 10-20 KB: its cost is latency, not bandwidth. One kernel (one CTA) per rank:
+//   1. push: the rank's partial sums are stored into slot [parity][rank] of EVERY rank's buffer (plain peer stores
+//      over NVLink), then a system-scope release store raises flag [parity][rank] on every rank to the sequence number;
+//   2. wait (bounded) until all `size` local flags carry the sequence number;
+//   3. sum the slots in rank order - the same order and the same values on every rank, so all ranks hold bit-identical
+//      results - write x, and run the limb split on the values still in registers.
+// Two parities: a rank can be at most one reduction ahead of a peer (it needs the peer's flag of reduction s to
+// finish s), so slot [s & 1] is never overwritten while a peer still reads reduction s - 2... s.
+// The waits are bounded: a rank that never arrives raises the error word; the kernel still returns.
+#include "common.cuh"
+#include "split.cuh"
+
+namespace elb {
+
+namespace {
+
+constexpr unsigned TPR_SPIN_LIMIT = 1u << 24;  // x ~100 ns: about two seconds
+constexpr size_t TPR_FLAG_BYTES = 256;  // flag words [2 parities][8 ranks], padded
+
+struct TprParams {
+    float* slots[8];      // rank p's slot area as mapped here
+    unsigned* flags[8];   // rank p's flag words as mapped here
+    int rank, size, n_max, n;
+    const float* part;
+    float* x;
+    const float* norm_w;
+    float eps;
+    int nl;
+    int8_t* limbs;
+    float* inv_scale;
+    unsigned* seq;
+    int* err;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(SPLIT_THREADS) k_tp_reduce_split(const TprParams p) {
+    __shared__ double red8[SPLIT_WARPS];
+    __shared__ int s_dead;
+    const int tid = threadIdx.x;
+    const unsigned s = *p.seq, epoch = s + 1;
+    const int par = int(s & 1u);
+    if (tid == 0) s_dead = 0;
+    // 1. push this rank's partial sums to every other rank (its own stay in registers)
+    float4 mine[SPLIT_V4];
+#pragma unroll
+    for (int j = 0; j < SPLIT_V4; ++j) {
+        const int idx = (j * SPLIT_THREADS + tid) * 4;
+        mine[j] = idx < p.n ? __ldcg(reinterpret_cast<const float4*>(p.part + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const size_t my_slot = (size_t(par) * p.size + p.rank) * p.n_max;
+    for (int q = 0; q < p.size; ++q) {
+        const int peer = (p.rank + 1 + q) % p.size;  // spread the first stores over the links
+        if (peer == p.rank) continue;
+#pragma unroll
+        for (int j = 0; j < SPLIT_V4; ++j) {
+            const int idx = (j * SPLIT_THREADS + tid) * 4;
+            if (idx < p.n) *reinterpret_cast<float4*>(p.slots[peer] + my_slot + idx) = mine[j];
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.size && tid != p.rank) st_release_sys(p.flags[tid] + par * 8 + p.rank, epoch);
+    // 2. wait for every peer's flag on this rank
+    if (tid < p.size && tid != p.rank) {
+        const unsigned* f = p.flags[p.rank] + par * 8 + tid;
+        unsigned it = 0;
+        while (ld_acquire_sys(f) != epoch) {
+            if (++it > TPR_SPIN_LIMIT) {
+                s_dead = 1;
+                atomicExch(p.err, 1);
+                break;
+            }
+            if (it > 64) __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    // 3. sum in rank order, write x, split
+    float4 v[SPLIT_V4];
+#pragma unroll
+    for (int j = 0; j < SPLIT_V4; ++j) v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!s_dead) {
+        for (int r = 0; r < p.size; ++r) {
+            const float* src = p.slots[p.rank] + (size_t(par) * p.size + r) * p.n_max;
+#pragma unroll
+            for (int j = 0; j < SPLIT_V4; ++j) {
+                const int idx = (j * SPLIT_THREADS + tid) * 4;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (idx < p.n) a = r == p.rank ? mine[j] : __ldcg(reinterpret_cast<const float4*>(src + idx));
+                if (r == 0) v[j] = a;
+                else { v[j].x += a.x; v[j].y += a.y; v[j].z += a.z; v[j].w += a.w; }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < SPLIT_V4; ++j) {
+            const int idx = (j * SPLIT_THREADS + tid) * 4;
+            if (idx < p.n) *reinterpret_cast<float4*>(p.x + idx) = v[j];
+        }
+    }
+    if (p.limbs) {
+        const int k = block_split_values(v, p.n, p.norm_w, p.eps, p.nl, p.limbs, red8);
+        if (tid == 0) *p.inv_scale = k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
+    }
+    if (tid == 0) *p.seq = epoch;
+}
+
+}  // namespace
+
+int tp_reduce_create(TpComm* c, int device, int rank, int size, int n_max, cudaStream_t s, TpReduce** out) {
+    *out = nullptr;
+    if (size < 2 || size > 8 || n_max > SPLIT_V4 * 4 * SPLIT_THREADS || n_max % 4) return ELB_OK;
+    auto* r = new TpReduce;
+    r->rank = rank; r->size = size; r->n_max = n_max;
+    bool ok = false;
+    const size_t bytes = TPR_FLAG_BYTES + size_t(2) * size * n_max * sizeof(float);
+    const int rc = tp_peer_alloc(c, device, bytes, s, &r->buf, &ok);
+    if (rc != ELB_OK || !ok) { delete r; return rc; }
+    if (cudaMalloc(&r->seq, sizeof(unsigned)) != cudaSuccess || cudaMemset(r->seq, 0, sizeof(unsigned)) != cudaSuccess ||
+        cudaHostAlloc(&r->err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+        cudaGetLastError();
+        tp_reduce_destroy(r);
+        return fail(ELB_ERR_MEMORY, "tp_reduce: out of memory");
+    }
+    *r->err_host = 0;
+    ELB_CUDA(cudaHostGetDevicePointer(&r->err_dev, r->err_host, 0));
+    *out = r;
+    return ELB_OK;
+}
+
+void tp_reduce_destroy(TpReduce* r) {
+    if (!r) return;
+    tp_peer_free(&r->buf, r->rank);
+    cudaFree(r->seq);
+    if (r->err_host) cudaFreeHost(r->err_host);
+    delete r;
+}
+
+int tp_reduce_split_launch(TpReduce* r, const float* part, float* x, int n, const float* norm_w, float eps, int nl,
+                           int8_t* limbs, float* inv_scale, cudaStream_t s) {
+    if (!r || !part || !x || n <= 0 || n > r->n_max || n % 4) return fail(ELB_ERR_INVALID, "tp_reduce: bad argument");
+    if (limbs && (n % 256 || !inv_scale)) return fail(ELB_ERR_INVALID, "tp_reduce: the split needs a multiple of 256 values");
+    TprParams p{};
+    for (int q = 0; q < r->size; ++q) {
+        p.flags[q] = reinterpret_cast<unsigned*>(r->buf.peer[q]);
+        p.slots[q] = reinterpret_cast<float*>(static_cast<uint8_t*>(r->buf.peer[q]) + TPR_FLAG_BYTES);
+    }
+    p.rank = r->rank; p.size = r->size; p.n_max = r->n_max; p.n = n;
+    p.part = part; p.x = x; p.norm_w = norm_w; p.eps = eps; p.nl = nl; p.limbs = limbs; p.inv_scale = inv_scale;
+    p.seq = r->seq; p.err = r->err_dev;
+    k_tp_reduce_split<<<1, SPLIT_THREADS, 0, s>>>(p);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
+}  // namespace elb
