@@ -58,6 +58,10 @@ def workload_name(spec, K):
             f"V{spec.n_vocab}, batch 1, pp{PROMPT} then tg{K}")
 
 
+def big_model(spec):
+    return spec_macs_per_token(spec) > 8e9
+
+
 def spec_macs_per_token(spec):
     """Multiply-accumulates of the linear layers for one token (head excluded: prefill computes it once per chunk)."""
     qd, kd = spec.n_head * spec.head_dim, spec.n_head_kv * spec.head_dim
@@ -152,7 +156,9 @@ def get_spec(args):
 
 def model_tensors(spec):
     t0 = time.time()
-    tens = list(synth.generate(spec, SEED))
+    # models above ~8 GB reuse the random blocks of layers 0 and 1 for the later layers of the same parity (types and
+    # shapes unchanged, every layer still has its own copy in HBM): host generation time only
+    tens = list(synth.generate(spec, SEED, share_layers=big_model(spec)))
     return tens, time.time() - t0
 
 
@@ -338,7 +344,9 @@ def run_ours(args):
                    f"tp{world}: heads and FFN columns cut over {world} GPUs, NCCL all-reduce after attn_output and "
                    "ffn_down, all-gather of the logits",
                    "l2": "inputs larger than L2: every step streams all weights (GBs) from HBM",
-                   "seed": SEED, "tokens": "reference LCG stream, seed 12345"},
+                   "seed": SEED, "tokens": "reference LCG stream, seed 12345",
+                   "weights": "two sets of random blocks shared by the layers of equal parity" if big_model(spec)
+                   else "every layer drawn separately"},
         "e2e": {"value": K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": spec.n_vocab * 4},
         "gpu_launches": int(launches),

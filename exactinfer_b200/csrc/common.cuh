@@ -131,29 +131,33 @@ __device__ __forceinline__ uint2 ldg_stream2(const void* p) {
 }
 
 // mma.sync m16n8k32 / m16n8k16, A unsigned or signed 8-bit, B signed 8-bit, int32 accumulate (exact)
-__device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                             uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+// Integer tensor-core products of one warp, C = A * B with a zero accumulator (the callers scale every product before
+// they add it up, so there is nothing to accumulate into; passing the zeros as inputs spares four moves per MMA).
+#define ELB_MMA_K32(NAME, TA)                                                                                          \
+    __device__ __forceinline__ void NAME(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, \
+                                         uint32_t b1) {                                                               \
+        asm("mma.sync.aligned.m16n8k32.row.col.s32." TA ".s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};" \
+            : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])                                                          \
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));                                           \
+    }
+#define ELB_MMA_K16(NAME, TA)                                                                                \
+    __device__ __forceinline__ void NAME(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {              \
+        asm("mma.sync.aligned.m16n8k16.row.col.s32." TA ".s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};" \
+            : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])                                                \
+            : "r"(a0), "r"(a1), "r"(b0), "r"(0));                                                            \
+    }
+ELB_MMA_K32(mma_u8s8_k32, "u8")
+ELB_MMA_K32(mma_s8s8_k32, "s8")
+ELB_MMA_K16(mma_u8s8_k16, "u8")
+ELB_MMA_K16(mma_s8s8_k16, "s8")
+#undef ELB_MMA_K32
+#undef ELB_MMA_K16
+// accumulating form: c += A * B
+__device__ __forceinline__ void mma_s8s8_k32_acc(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_s8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                             uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(b0));
-}
-__device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(b0));
 }
 
 // x * 2^k as two exact multiplications by powers of two (|k| can exceed the exponent range of one float);

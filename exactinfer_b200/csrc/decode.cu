@@ -37,15 +37,16 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     return v;
 }
 
-// All CTAs arrive, then leave together. `nb` counts this CTA's barriers. Returns false when the wait ran out (or an
+// All CTAs arrive, then leave together. `target` is the arrival count that completes this CTA's next barrier (the
+// counter is never reset: a launch starts from launches * barriers per launch * CTAs). Returns false when the wait ran out (or an
 // earlier one did): the caller stops working, every later barrier returns at once.
-__device__ __forceinline__ bool grid_barrier(const DkParams& p, int& nb, int* s_dead) {
+__device__ __forceinline__ bool grid_barrier(const DkParams& p, unsigned& target, int* s_dead) {
     __syncthreads();
     if (threadIdx.x == 0 && !*s_dead) {
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");  // orders the CTA's writes before it
-        const unsigned target = unsigned(++nb) * gridDim.x;
+        target += gridDim.x;
         unsigned it = 0;
-        while (ld_acquire(p.bar) < target) {
+        while (int(ld_acquire(p.bar) - target) < 0) {
             if (++it > DK_SPIN_LIMIT) {
                 *s_dead = 1;
                 atomicExch(p.err, 1);
@@ -214,18 +215,6 @@ __device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8
     ring_commit();
 }
 
-// Same walk, further ahead, into L2 only: the second cursor of a warp runs `l2_ahead` units (about one layer) in front
-// of its ring, so that HBM streams at an even rate through the phases that consume nothing (attention, conversion,
-// barriers) and the ring refills at L2 latency. One 128-byte line per lane.
-__device__ __forceinline__ void cursor_prefetch_l2(const DkParams& p, Cursor& c, int warp, int lane) {
-    if (c.j >= c.n_mats) return;
-    if (lane * 128 < c.unit_bytes) asm volatile("prefetch.global.L2 [%0];" ::"l"(c.W + size_t(c.u) * c.unit_bytes + lane * 128));
-    if (++c.u == c.end) {
-        ++c.j;
-        cursor_seek(p, c, warp);
-    }
-}
-
 // ---------------------------------------------------------------- one matvec phase
 
 enum { DK_EPI_STORE = 0, DK_EPI_ADD_SSQ = 1, DK_EPI_SILU_AMAX = 2 };
@@ -273,7 +262,7 @@ __device__ __forceinline__ void dk_tile_stats(int epi, const DkParams& p, const 
 }
 
 template <int TYPE>
-__device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, Cursor& pl2, int& rs,
+__device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, int& rs,
                           const PhaseSmem& s, int warp, int lane) {
     const int g = lane >> 2, t = lane & 3, upt = m.upt;
     const int8_t* sd = TYPE == ELB_Q6_K ? s.act.sd16 : s.act.sd32;
@@ -285,7 +274,6 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
     const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
     DbgOut dbg{nullptr, nullptr, nullptr, 0, 0, 0, 0};
     for (int u = r.wA; u < r.wB; ++u) {
-        cursor_prefetch_l2(p, pl2, warp, lane);
         cursor_issue(p, pf, s.ring + (rs == 0 ? DK_DEPTH - 1 : rs - 1) * s.slot_bytes, warp, lane);
         ring_wait<DK_DEPTH - 1>();
         __syncwarp();
@@ -313,19 +301,19 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
 
 // y (+)= W * act for one matrix; the activation limbs are already in shared memory. Ends with every row of this
 // CTA's share written (tiles shared with a neighbour: by whichever CTA arrives last).
-__device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf, Cursor& pl2,
+__device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf,
                              int& rs, const PhaseSmem& s, double* ssq_out, unsigned* amax_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
     const WarpRange r = warp_range(m, warp);
-    const int pl = epi == DK_EPI_SILU_AMAX ? int(amax_out - p.amax) / 2 : -1;
+    const int pl = epi == DK_EPI_SILU_AMAX ? (int(amax_out - p.amax) / 2) % p.n_layer : -1;
     if (pl >= 0) dk_stamp(p, pl, 16);
     if (tid == 0) s.flags[3] = 0;
     __syncthreads();
     if (pl >= 0) dk_stamp(p, pl, 17);
     switch (m.type) {
-        case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, pl2, rs, s, warp, lane); break;
-        case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, pl2, rs, s, warp, lane); break;
-        default: run_units<ELB_Q8_0>(p, m, r, pf, pl2, rs, s, warp, lane); break;
+        case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, rs, s, warp, lane); break;
+        case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, rs, s, warp, lane); break;
+        default: run_units<ELB_Q8_0>(p, m, r, pf, rs, s, warp, lane); break;
     }
     if (pl >= 0) dk_stamp(p, pl, 18);
     __syncthreads();
@@ -408,7 +396,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c = blockIdx.x;
     if (c >= p.HKV * p.nsplit) return;
     const int kvh = c / p.nsplit, split = c - kvh * p.nsplit, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
-    const int pos = *p.pos, T = pos + 1;
+    const int pos = p.pos[p.ctl[0]], T = pos + 1;
     const float2* cs = reinterpret_cast<const float2*>(p.rope) + size_t(pos) * (p.rope_dim / 2);
     float* m_s = s.corr + DK_MAXG;
     float* l_s = s.corr + 2 * DK_MAXG;
@@ -588,14 +576,17 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     cursor_seek(p, pf, warp);
 #pragma unroll
     for (int d = 0; d < DK_DEPTH - 1; ++d) cursor_issue(p, pf, s.ring + d * slot_bytes, warp, lane);
-    Cursor pl2 = pf;  // (pf has already moved DEPTH-1 units on; those lines are on their way anyway)
-    for (int i = 0; i < p.l2_ahead; ++i) cursor_prefetch_l2(p, pl2, warp, lane);
-    int rs = 0, nb = 0;
+    int rs = 0;
     int* dead = &s.flags[2];
+    const unsigned step = p.ctl[0], epoch = p.ctl[2];
+    unsigned nb = epoch * unsigned(1 + 5 * p.n_layer) * gridDim.x;  // arrivals before this launch
+    unsigned* const amax_base = p.amax + (epoch & 1u) * 2 * p.n_layer;
+    if (blockIdx.x == 0)  // the other half of the amax slots: untouched by this launch, zero for the next one
+        for (int i = tid; i < 2 * p.n_layer; i += DK_THREADS) p.amax[((epoch + 1) & 1u) * 2 * p.n_layer + i] = 0u;
 
     // token embedding (get_row, src/ops.cpp:76-82 of the reference): CTA c decodes row tiles c, c+G, ... of the row
     {
-        const int64_t R = *p.token;
+        const int64_t R = p.token[step];
         for (int Xt = blockIdx.x; Xt < p.E / 16; Xt += gridDim.x) {
             if (tid < 16) {
                 const int k = Xt * 16 + tid;
@@ -617,14 +608,14 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
 
     for (int l = 0; l < p.n_layer && ok; ++l) {
         const DkLayer& L = p.layers[l];
-        unsigned* amax = p.amax + 2 * l;
+        unsigned* amax = amax_base + 2 * l;
         dk_stamp(p, l, 0);
         {
             s.act = act_for(p.E);
             const float inv = convert_act(p.x, p.E, L.attn_norm, p.ssq, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
             dk_stamp(p, l, 1);
             for (int i = 0; i < p.n_qkv; ++i)
-                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, pl2, rs, s, nullptr, nullptr);
+                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr, nullptr);
         }
         dk_stamp(p, l, 2);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -637,7 +628,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.H * DK_HD);
             const float inv = convert_act(p.att, p.H * DK_HD, nullptr, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
             dk_stamp(p, l, 6);
-            matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, pl2, rs, s, p.ssq, nullptr);
+            matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
         }
         dk_stamp(p, l, 7);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -646,7 +637,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.E);
             const float inv = convert_act(p.x, p.E, L.ffn_norm, p.ssq, p.eps, nullptr, p.nl_gu, s.act, s.red8);
             dk_stamp(p, l, 9);
-            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, pl2, rs, s, nullptr, amax + 1);
+            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, nullptr, amax + 1);
         }
         dk_stamp(p, l, 10);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -655,7 +646,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.F);
             const float inv = convert_act(p.act, p.F, nullptr, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
             dk_stamp(p, l, 12);
-            matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, pl2, rs, s, p.ssq, nullptr);
+            matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
         }
         dk_stamp(p, l, 13);
         ok = grid_barrier(p, nb, dead);
@@ -664,9 +655,13 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference)
         s.act = act_for(p.E);
         const float inv = convert_act(p.x, p.E, p.output_norm, p.ssq, p.eps, nullptr, 4, s.act, s.red8);
-        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, pl2, rs, s, nullptr, nullptr);
+        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr, nullptr);
     }
     ring_wait<0>();
+    if (blockIdx.x == 0 && tid == 0) {  // every CTA read ctl before its first barrier: safe to move on
+        p.ctl[2] = epoch + 1;
+        if (p.ctl[1]) p.ctl[0] = step + 1;
+    }
 }
 
 size_t decode_smem_bytes(const DkParams& p, int slot_bytes) {

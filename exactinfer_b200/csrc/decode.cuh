@@ -30,23 +30,25 @@ struct DkParams {
     int E, F, H, HKV, rope_dim, n_ctx, nsplit;
     float eps, scale;
     int nl_qkv, nl_wo, nl_gu, nl_down;
-    const int32_t* token;   // device scalars
+    const int32_t* token;   // device arrays: token id and position of step i of the running batch of steps
     const int* pos;
+    unsigned* ctl;          // [0] index of the step to run, [1] non-zero: the kernel moves the index on when it ends,
+                            // [2] launches so far (barrier targets and the parity of the amax slots derive from it)
     const float* rope;      // [n_ctx][rope_dim/2][2]
     float *x, *qkv, *att, *act, *logits;
     double* ssq;            // [E/16] per-tile sums of squares of x
-    unsigned* amax;         // [n_layer][2] bit patterns of max|att|, max|act| of each layer, zero at launch
+    unsigned* amax;         // [2][n_layer][2] bit patterns of max|att|, max|act| of each layer; launch e uses half e & 1
+                            // (zero when it starts) and zeroes the other half for launch e + 1
     float* attn_part;       // [HKV][nsplit][group][130]
     unsigned* attn_counters;  // [HKV]
-    unsigned* bar;          // grid barrier counter, zero at launch
+    unsigned* bar;          // grid barrier counter: counts arrivals for ever (compared modulo 2^32)
     int* err;               // raised when a barrier wait ran out
     int slots;              // row-tile slots per warp in the reduction buffer
     int n_max;              // longest activation vector
-    int l2_ahead;           // units (per warp) that the L2 prefetch runs in front of the shared-memory ring
     unsigned long long* prof;  // diagnostics (ELB_DK_PROF=1): [n_layer][16] nanosecond stamps of CTA 0, else null
 };
 
-// one token at the position / token id stored on the device; the caller zeroes bar and amax before the launch.
+// one token at the position / token id stored on the device (step ctl[0] of the arrays); nothing to reset between launches.
 // slot_bytes: size of one ring slot (the largest unit of the step's matrices); grid: one CTA per SM.
 int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s);
 int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits);

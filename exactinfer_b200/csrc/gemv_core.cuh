@@ -65,6 +65,13 @@ __device__ __forceinline__ void load_unit(Unit<ELB_Q8_0>& u, const uint8_t* base
 // activation fragments: plain loads (the compiler picks LDS or LDG from the pointer; global ones hit L1)
 template <class T> __device__ __forceinline__ T ld_act(const T* p) { return *p; }
 
+// prmt.b32 in its default mode: selector nibble k < 8 copies byte k of {a, b}; 8 + k fills the byte with byte k's sign
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t sel4(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 // Accumulators of one lane for the tile in progress: rows g (index 0) and g+8 (index 1).
@@ -90,7 +97,9 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
     const uint32_t sh[2] = {u.h1.y & 0x3F3F3F3Fu, (u.h1.w & 0x0F0F0F0Fu) | ((u.h1.y >> 2) & 0x30303030u)};
     const uint32_t mg[2] = {u.h0.z & 0x3F3F3F3Fu, ((u.h0.w >> 4) & 0x0F0F0F0Fu) | ((u.h0.z >> 2) & 0x30303030u)};
     const uint32_t mh[2] = {u.h1.z & 0x3F3F3F3Fu, ((u.h1.w >> 4) & 0x0F0F0F0Fu) | ((u.h1.z >> 2) & 0x30303030u)};
-    int I[4] = {0, 0, 0, 0};
+    // even sub-blocks: low nibbles; odd sub-blocks: the high nibbles stay where they are (16 q, still a u8), their
+    // products are accumulated apart and divided by 16 once per block (exact: every term is a multiple of 16)
+    int I[4] = {0, 0, 0, 0}, I16[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint4 q = u.q[j];
@@ -98,37 +107,38 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
         for (int odd = 0; odd < 2; ++odd) {
             const int sub = 2 * j + odd;
             const uint2 bf = ld_act(reinterpret_cast<const uint2*>(lcol + sub * 32));
-            int C[4] = {0, 0, 0, 0};
-            if (odd == 0)
-                mma_u8s8_k32(C, q.x & 0x0F0F0F0Fu, q.z & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu, bf.x, bf.y);
-            else
-                mma_u8s8_k32(C, (q.x >> 4) & 0x0F0F0F0Fu, (q.z >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu,
-                             (q.w >> 4) & 0x0F0F0F0Fu, bf.x, bf.y);
-            const int s0 = (sg[sub >> 2] >> (8 * (sub & 3))) & 0xFF, s1 = (sh[sub >> 2] >> (8 * (sub & 3))) & 0xFF;
-            I[0] += s0 * C[0];
-            I[1] += s0 * C[1];
-            I[2] += s1 * C[2];
-            I[3] += s1 * C[3];
+            const uint32_t mask = odd ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+            int C[4];
+            mma_u8s8_k32(C, q.x & mask, q.z & mask, q.y & mask, q.w & mask, bf.x, bf.y);
+            const int s0 = int(__byte_perm(sg[sub >> 2], 0u, 0x4440 + (sub & 3))), s1 = int(__byte_perm(sh[sub >> 2], 0u, 0x4440 + (sub & 3)));
+            if (odd) {
+                I16[0] += s0 * C[0]; I16[1] += s0 * C[1]; I16[2] += s1 * C[2]; I16[3] += s1 * C[3];
+            } else {
+                I[0] += s0 * C[0]; I[1] += s0 * C[1]; I[2] += s1 * C[2]; I[3] += s1 * C[3];
+            }
             if (DBG && dbg.P && t < 2) {
+                const int sh4 = odd ? 4 : 0;
                 const int64_t s = int64_t(b) * 8 + sub;
                 if (dbg.row_g < dbg.rows) {
-                    dbg.P[(dbg.row_g * dbg.nsub + s) * 4 + 2 * t] = C[0];
-                    dbg.P[(dbg.row_g * dbg.nsub + s) * 4 + 2 * t + 1] = C[1];
+                    dbg.P[(dbg.row_g * dbg.nsub + s) * 4 + 2 * t] = C[0] >> sh4;
+                    dbg.P[(dbg.row_g * dbg.nsub + s) * 4 + 2 * t + 1] = C[1] >> sh4;
                 }
                 if (dbg.row_g + 8 < dbg.rows) {
-                    dbg.P[((dbg.row_g + 8) * dbg.nsub + s) * 4 + 2 * t] = C[2];
-                    dbg.P[((dbg.row_g + 8) * dbg.nsub + s) * 4 + 2 * t + 1] = C[3];
+                    dbg.P[((dbg.row_g + 8) * dbg.nsub + s) * 4 + 2 * t] = C[2] >> sh4;
+                    dbg.P[((dbg.row_g + 8) * dbg.nsub + s) * 4 + 2 * t + 1] = C[3] >> sh4;
                 }
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) I[i] += I16[i] >> 4;
     const float dg = h2f_bits(u.h0.x & 0xFFFFu), dh = h2f_bits(u.h1.x & 0xFFFFu);
     a.acc[0] += dg * fmaf(float(I[1]), 256.0f, float(I[0]));
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
     // min term: J[col] = sum over the 8 sub-blocks of m * (digit `col>>2` of the limb sum S of limb `col&3`)
     const uint32_t a0 = t == 0 ? mg[0] : t == 1 ? mg[1] : 0u, a1 = t == 0 ? mh[0] : t == 1 ? mh[1] : 0u;
     const uint32_t b0 = ld_act(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 8 + 4 * (t & 1)));
-    int J[4] = {0, 0, 0, 0};
+    int J[4];
     mma_u8s8_k16(J, a0, a1, b0);
     const float ng = h2f_bits(u.h0.x >> 16), nh = h2f_bits(u.h1.x >> 16);
     a.accm[0] += ng * fmaf(float(J[1]), 256.0f, float(J[0]));
@@ -167,12 +177,17 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
         for (int i = 0; i < 4; ++i) {
             const int s = 4 * c + i;
             const uint32_t w = sel4(ql, i);
-            const uint32_t a0 = (w & 0x0F0F0F0Fu) | (((qh.x >> (2 * i)) & 0x03030303u) << 4);
-            const uint32_t a1 = ((w >> 4) & 0x0F0F0F0Fu) | (((qh.y >> (2 * i)) & 0x03030303u) << 4);
+            // the two high bits of each q6 moved to bits 4-5 of its byte with one shift and one mask
+            const uint32_t hx = (i < 2 ? qh.x << (4 - 2 * i) : qh.x >> (2 * i - 4)) & 0x30303030u;
+            const uint32_t hy = (i < 2 ? qh.y << (4 - 2 * i) : qh.y >> (2 * i - 4)) & 0x30303030u;
+            const uint32_t a0 = (w & 0x0F0F0F0Fu) | hx;
+            const uint32_t a1 = ((w >> 4) & 0x0F0F0F0Fu) | hy;
             const uint32_t bf = ld_act(reinterpret_cast<const uint32_t*>(lcol + s * 16));
-            int C[4] = {0, 0, 0, 0};
+            int C[4];
             mma_u8s8_k16(C, a0, a1, bf);
-            const int s0 = int(int8_t(sel4(u.s0, s >> 2) >> (8 * (s & 3)))), s1 = int(int8_t(sel4(u.s1, s >> 2) >> (8 * (s & 3))));
+            // int8 scale of sub-block s, sign-extended by the byte permute (selector 8+k replicates byte k's sign)
+            const uint32_t sel = 0x8880u + 0x1111u * (s & 3);
+            const int s0 = int(prmt(sel4(u.s0, s >> 2), 0u, sel)), s1 = int(prmt(sel4(u.s1, s >> 2), 0u, sel));
             I[0] += s0 * C[0];
             I[1] += s0 * C[1];
             I[2] += s1 * C[2];
@@ -195,7 +210,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
     a.acc[0] += dg * fmaf(float(I[1]), 256.0f, float(I[0]));
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
     const uint32_t b0 = ld_act(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 16 + 4 * t));
-    int J[4] = {0, 0, 0, 0};
+    int J[4];
     mma_s8s8_k16(J, sel4(u.s0, t), sel4(u.s1, t), b0);
     a.accm[0] += (32.0f * dg) * fmaf(float(J[1]), 256.0f, float(J[0]));
     a.accm[1] += (32.0f * dh) * fmaf(float(J[3]), 256.0f, float(J[2]));
@@ -227,7 +242,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, con
     for (int i = 0; i < 4; ++i) {
         const uint4 q = u.q[i];
         const uint2 bf = ld_act(reinterpret_cast<const uint2*>(lcol + i * 32));
-        int C[4] = {0, 0, 0, 0};
+        int C[4];
         mma_s8s8_k32(C, q.x, q.z, q.y, q.w, bf.x, bf.y);
         const uint32_t d0w = i < 2 ? u.d0.x : u.d0.y, d1w = i < 2 ? u.d1.x : u.d1.y;
         const float dg = h2f_bits((d0w >> (16 * (i & 1))) & 0xFFFFu), dh = h2f_bits((d1w >> (16 * (i & 1))) & 0xFFFFu);

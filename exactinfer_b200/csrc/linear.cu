@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
                     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bb), b1 = *reinterpret_cast<const uint32_t*>(bb + 16);
 #pragma unroll
                     for (int pl = 0; pl < NPL; ++pl)
-                        mma_s8s8_k32(acc[pl][nf][l], af[pl][0], af[pl][1], af[pl][2], af[pl][3], b0, b1);
+                        mma_s8s8_k32_acc(acc[pl][nf][l], af[pl][0], af[pl][1], af[pl][2], af[pl][3], b0, b1);
                 }
             const int kdone = kt * GM_K + (ks + 1) * 32;
             if (kdone % p.blk == 0) drain(kdone / p.blk - 1);

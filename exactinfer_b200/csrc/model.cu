@@ -77,7 +77,8 @@ struct Model {
     DkLayer* dk_layers = nullptr;
     int dk_slot = 0, dk_grid = 0;
     double* ssq = nullptr;
-    unsigned* sync_words = nullptr;  // [1 + 2 n_layer]: barrier counter, then max|att|, max|act| per layer
+    unsigned* sync_words = nullptr;  // barrier counter, step index, advance flag, launch count, then 2 x [n_layer][2] amax slots
+    int* pos_steps = nullptr;        // positions of a batch of single-token steps (persistent kernel)
     int* err_host = nullptr;         // pinned, mapped: raised by the kernel when a barrier wait runs out
     // tensor parallelism (tp.size == 1: none). H, HKV, F are this rank's share of heads and of the FFN dimension.
     TpDims tp{};
@@ -283,7 +284,6 @@ int body_decode(Model* m) {
         return prep_limbs_launch(m->x, E, norm_w, c.eps, nl, m->dlimbs[slot], m->dinv + slot, false, m->stream);
     };
     if (m->use_mega) {
-        ELB_CUDA(cudaMemsetAsync(m->sync_words, 0, size_t(1 + 2 * c.n_layer) * sizeof(unsigned), m->stream));
         ++m->launches;
         return decode_step_launch(m->dk, m->dk_slot, m->dk_grid, m->stream);
     }
@@ -347,7 +347,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
     std::memcpy(m->tokens_host, tokens, size_t(B) * sizeof(int32_t));
     *m->pos_host = pos0;
     ELB_CUDA(cudaMemcpyAsync(m->tokens_dev, m->tokens_host, size_t(B) * sizeof(int32_t), cudaMemcpyHostToDevice, m->stream));
-    ELB_CUDA(cudaMemcpyAsync(m->pos_dev, m->pos_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    ELB_CUDA(cudaMemcpyAsync(m->use_mega && B == 1 ? m->pos_steps : m->pos_dev, m->pos_host, sizeof(int), cudaMemcpyHostToDevice, m->stream));
     ELB_CUDA(cudaEventRecord(m->ev0, m->stream));
     m->last_rows = B;
     if (B == 1) {
@@ -418,7 +418,9 @@ int setup_decode_kernel(Model* m) {
     ELB_CUDA(cudaMalloc(&m->dk_layers, hl.size() * sizeof(DkLayer)));
     ELB_CUDA(cudaMemcpy(m->dk_layers, hl.data(), hl.size() * sizeof(DkLayer), cudaMemcpyHostToDevice));
     ELB_CUDA(cudaMalloc(&m->ssq, size_t(E / 16) * sizeof(double)));
-    ELB_CUDA(cudaMalloc(&m->sync_words, size_t(1 + 2 * c.n_layer) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&m->sync_words, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
+    ELB_CUDA(cudaMemset(m->sync_words, 0, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&m->pos_steps, size_t(m->max_batch) * sizeof(int)));
     ELB_CUDA(cudaHostAlloc(&m->err_host, sizeof(int), cudaHostAllocMapped));
     *m->err_host = 0;
     int* err_dev = nullptr;
@@ -430,20 +432,11 @@ int setup_decode_kernel(Model* m) {
     p.nsplit = std::max(1, std::min({32, m->attn_split, di.sm_count / c.n_head_kv}));
     p.eps = c.eps; p.scale = 1.0f / std::sqrt(float(c.head_dim));
     p.nl_qkv = m->nl_qkv; p.nl_wo = m->nl_wo; p.nl_gu = m->nl_gu; p.nl_down = m->nl_down;
-    p.token = m->tokens_dev; p.pos = m->pos_dev; p.rope = m->rope;
+    p.token = m->tokens_dev; p.pos = m->pos_steps; p.rope = m->rope;
     p.x = m->x; p.qkv = m->qkv; p.att = m->att; p.act = m->act; p.logits = m->logits;
-    p.ssq = m->ssq; p.bar = m->sync_words; p.amax = m->sync_words + 1;
+    p.ssq = m->ssq; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
     p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
     p.err = err_dev; p.slots = slots; p.n_max = std::max({E, F, QD});
-    {   // about one layer's worth of units per warp in front (a layer of the 4B shape is 58 MB; L2 holds 126 MB)
-        int64_t layer_units = 0;
-        const Layer& L0 = m->layers[0];
-        for (auto& sgm : L0.qkv) layer_units += sgm.w->tiles * sgm.w->units_per_tile;
-        for (const Weight* w : {L0.wo, L0.gu, L0.down}) layer_units += w->tiles * w->units_per_tile;
-        (void)layer_units;
-        p.l2_ahead = 0;  // measured: the extra look-ahead did not pay on this kernel (ELB_DK_L2AHEAD to try again)
-        if (const char* v = std::getenv("ELB_DK_L2AHEAD")) p.l2_ahead = std::max(0, std::atoi(v));
-    }
     m->dk_slot = (slot + 15) / 16 * 16;
     m->dk_grid = di.sm_count;
     // 32-bit unit arithmetic in the kernel
@@ -532,7 +525,7 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->dk_layers); cudaFree(m->ssq); cudaFree(m->sync_words);
+    cudaFree(m->dk_layers); cudaFree(m->ssq); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     tp_reduce_destroy(m->tpr);
     tp_comm_destroy(m->comm);
@@ -729,16 +722,30 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
     for (int i = 0; i < n; ++i)
         if (tokens[i] < 0 || tokens[i] >= m->cfg.n_vocab) return fail(ELB_ERR_RANGE, "eval_steps: token id out of range");
     ELB_CUDA(cudaSetDevice(m->device));
-    int32_t* pin = nullptr;  // [n] tokens then [n] positions, pinned so that the copies stay asynchronous
-    ELB_CUDA(cudaMallocHost(&pin, size_t(2) * n * sizeof(int32_t)));
+    int32_t* pin = nullptr;  // [n] tokens, [n] positions, then the control words; pinned so that the copies stay asynchronous
+    ELB_CUDA(cudaMallocHost(&pin, (size_t(2) * n + 4) * sizeof(int32_t)));
     for (int i = 0; i < n; ++i) { pin[i] = tokens[i]; pin[n + i] = pos0 + i; }
+    int32_t* ctl = pin + 2 * n;
+    ctl[0] = 0; ctl[1] = 1; ctl[2] = 0; ctl[3] = 0;  // {index 0, advance} to start a batch, {index 0, stay} to end it
     const int64_t before = m->launches;
     int rc = ELB_OK;
     cudaEventRecord(m->ev0, m->stream);
-    for (int i = 0; i < n && rc == ELB_OK; ++i) {
-        cudaMemcpyAsync(m->tokens_dev, pin + i, sizeof(int32_t), cudaMemcpyHostToDevice, m->stream);
-        cudaMemcpyAsync(m->pos_dev, pin + n + i, sizeof(int), cudaMemcpyHostToDevice, m->stream);
-        rc = enqueue_decode_step(m);
+    if (m->use_mega) {
+        // the persistent kernel walks the token / position arrays by itself: one upload per batch of steps
+        for (int done = 0; done < n && rc == ELB_OK; done += m->max_batch) {
+            const int b = std::min(m->max_batch, n - done);
+            cudaMemcpyAsync(m->tokens_dev, pin + done, size_t(b) * sizeof(int32_t), cudaMemcpyHostToDevice, m->stream);
+            cudaMemcpyAsync(m->pos_steps, pin + n + done, size_t(b) * sizeof(int), cudaMemcpyHostToDevice, m->stream);
+            cudaMemcpyAsync(m->dk.ctl, ctl, 2 * sizeof(unsigned), cudaMemcpyHostToDevice, m->stream);
+            for (int i = 0; i < b && rc == ELB_OK; ++i) rc = enqueue_decode_step(m);
+        }
+        cudaMemcpyAsync(m->dk.ctl, ctl + 2, 2 * sizeof(unsigned), cudaMemcpyHostToDevice, m->stream);
+    } else {
+        for (int i = 0; i < n && rc == ELB_OK; ++i) {
+            cudaMemcpyAsync(m->tokens_dev, pin + i, sizeof(int32_t), cudaMemcpyHostToDevice, m->stream);
+            cudaMemcpyAsync(m->pos_dev, pin + n + i, sizeof(int), cudaMemcpyHostToDevice, m->stream);
+            rc = enqueue_decode_step(m);
+        }
     }
     cudaEventRecord(m->ev1, m->stream);
     const cudaError_t e = cudaStreamSynchronize(m->stream);
