@@ -11,8 +11,10 @@
 //   * the activation of a matvec is converted to int8 limbs redundantly by every CTA (shared memory), from the fp32
 //     vector and a global maximum (atomicMax, order independent) or the per-tile sums of squares (RMSNorm) that the
 //     producing phase left: no serial single-CTA section;
-//   * row tiles that straddle two CTAs are finished by the last CTA to arrive, in fixed CTA order; sums of squares are
-//     kept per row tile and added in tile order: the step is deterministic.
+//   * no phase ends with an exchange between CTAs: q, k, v and gate|up are cut in whole row tiles; attn_output and
+//     ffn_down, which have few row tiles and long rows, are cut in equal unit ranges, a row tile then has at most two
+//     contributing CTAs, each leaves its partial sums in a buffer of its own and the next conversion adds residual +
+//     first + second in that order on every CTA: the step is deterministic.
 // Barrier waits are bounded: on timeout the kernel raises an error word, drains its copies and leaves.
 #include <algorithm>
 #include <cstdlib>
@@ -90,28 +92,49 @@ struct ActSmem {
     int n_pad;
 };
 
-// src: fp32 vector in global memory, written by other CTAs before the last barrier (read through L2).
-// norm_w != nullptr: RMSNorm with the reference's operation order (src/ops.cpp:155-160): the sum of squares is the
-// sum, in tile order, of the per-tile sums the producing phase left in ssq[n/16]. Otherwise max|src| is known
-// (amax_bits, the bit pattern of a non-negative float). Returns inv_scale = 2^-k.
-__device__ float convert_act(const float* src, int n, const float* norm_w, const double* ssq, float eps,
+// Activation of the next matvec -> limbs in shared memory, by every CTA for itself. Two sources:
+//  * resid != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): the vector is
+//    resid.x + resid.p0 + resid.p1 (the row-parallel matvec before it left partial sums, see DK_EPI_PART), added in
+//    that order by every CTA alike; CTA c also stores its slice of the sum to resid.out, the residual stream of the next
+//    conversion. RMSNorm with the reference's operation order (src/ops.cpp:155-160), sum of squares in double.
+//  * otherwise src with max|src| known (amax_bits, the bit pattern of a non-negative float).
+// All of it read through L2 (written by other CTAs before the last barrier). Returns inv_scale = 2^-k.
+struct Resid { const float *x, *p0, *p1; float* out; };
+
+__device__ float convert_act(const float* src, const Resid* resid, int n, const float* norm_w, float eps,
                              const unsigned* amax_bits, int nl, const ActSmem& a, double* red) {
     constexpr int V4 = 5;  // float4 per thread kept in registers: one pass over vectors of up to 10240 values
     const int tid = threadIdx.x;
     int k;
     if (n <= V4 * 4 * DK_THREADS) {
-        // every load of the phase (vector, norm weight, statistics) is issued before the first use: one round trip
+        // every load of the phase (vector, partial sums, norm weight) is issued before the first use: one round trip
         float4 v[V4], w[V4];
 #pragma unroll
         for (int j = 0; j < V4; ++j) {
             const int idx = (j * DK_THREADS + tid) * 4;
-            v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(src + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            w[j] = norm_w && idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (resid) {
+                const float4 x = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->x + idx)) : z;
+                const float4 p0 = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->p0 + idx)) : z;
+                const float4 p1 = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->p1 + idx)) : z;
+                v[j] = make_float4(__fadd_rn(__fadd_rn(x.x, p0.x), p1.x), __fadd_rn(__fadd_rn(x.y, p0.y), p1.y),
+                                   __fadd_rn(__fadd_rn(x.z, p0.z), p1.z), __fadd_rn(__fadd_rn(x.w, p0.w), p1.w));
+            } else {
+                v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(src + idx)) : z;
+            }
+            w[j] = norm_w && idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : z;
         }
         float m = 0.f;
-        if (norm_w) {
+        if (resid) {
+            // this CTA's slice of the new residual stream (whole float4s; every CTA holds the same values)
+            const int q4 = n / 4, lo = range_lo(q4, gridDim.x, blockIdx.x), hi = range_lo(q4, gridDim.x, blockIdx.x + 1);
             double ss = 0.0;
-            for (int i = tid; i < n / 16; i += DK_THREADS) ss += __ldcg(ssq + i);
+#pragma unroll
+            for (int j = 0; j < V4; ++j) {
+                const int i4 = j * DK_THREADS + tid;
+                if (i4 >= lo && i4 < hi) *reinterpret_cast<float4*>(resid->out + i4 * 4) = v[j];
+                ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
+            }
             ss = dk_block_sum(ss, red, tid);
             const float inv = float(1.0 / sqrt(ss / n + double(eps)));
 #pragma unroll
@@ -130,27 +153,12 @@ __device__ float convert_act(const float* src, int n, const float* norm_w, const
             const int idx = (j * DK_THREADS + tid) * 4;
             if (j * DK_THREADS * 4 < n) split4(v[j], sc, a.lim, a.n_pad, a.sd32, a.sd16, idx, idx < n);  // warp-uniform
         }
-    } else {
-        float inv = 1.0f, m = 0.f;
-        if (norm_w) {
-            double ss = 0.0;
-            for (int i = tid; i < n / 16; i += DK_THREADS) ss += __ldcg(ssq + i);
-            ss = dk_block_sum(ss, red, tid);
-            inv = float(1.0 / sqrt(ss / n + double(eps)));
-            for (int i = tid * 4; i < n; i += DK_THREADS * 4)
-                m = fmaxf(m, absmax4(norm4(__ldcg(reinterpret_cast<const float4*>(src + i)), inv,
-                                           __ldg(reinterpret_cast<const float4*>(norm_w + i)))));
-            m = dk_block_max(m, reinterpret_cast<float*>(red), tid);
-        } else {
-            m = __uint_as_float(__ldcg(amax_bits));
-        }
+    } else {  // longer vectors (no residual stream is that long: the host keeps such shapes off this kernel)
+        const float m = __uint_as_float(__ldcg(amax_bits));
         k = split_shift(m, nl);
         const Pow2 sc = make_pow2(k);
-        for (int i = tid * 4; i < n; i += DK_THREADS * 4) {  // warp-uniform trip count: n is a multiple of 128
-            float4 f = __ldcg(reinterpret_cast<const float4*>(src + i));
-            if (norm_w) f = norm4(f, inv, __ldg(reinterpret_cast<const float4*>(norm_w + i)));
-            split4(f, sc, a.lim, a.n_pad, a.sd32, a.sd16, i, true);
-        }
+        for (int i = tid * 4; i < n; i += DK_THREADS * 4)  // warp-uniform trip count: n is a multiple of 128
+            split4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, a.lim, a.n_pad, a.sd32, a.sd16, i, true);
     }
     __syncthreads();
     return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
@@ -174,14 +182,23 @@ __device__ __forceinline__ const DkMat& mat_at(const DkParams& p, int j) {
     return i < p.n_qkv ? L.qkv[i] : i == p.n_qkv ? L.wo : i == p.n_qkv + 1 ? L.gu : L.down;
 }
 
-// Whole row tiles per CTA (no tile is shared between CTAs, so a phase ends without any cross-CTA reduction); a matrix
-// with fewer tiles than CTAs occupies the first CTAs only. Within the CTA the warps cut the units into equal ranges.
+// The CTA's share of a matrix as a range of units [cA, cB), cut into equal ranges for its warps [wA, wB).
+// Whole tiles of the matrix's group by default (no tile is shared between CTAs: the phase ends without any exchange;
+// a group with fewer tiles than CTAs occupies the first CTAs only); equal unit ranges for a balanced matrix.
 struct WarpRange { int cA, cB, wA, wB; };
 __device__ __forceinline__ WarpRange warp_range(const DkMat& m, int warp) {
-    const int G = min(int(gridDim.x), m.tiles), c = blockIdx.x;
+    const int c = blockIdx.x;
     WarpRange r;
-    r.cA = c < G ? range_lo(m.tiles, G, c) * m.upt : 0;
-    r.cB = c < G ? range_lo(m.tiles, G, c + 1) * m.upt : 0;
+    if (m.balanced) {
+        const int U = m.tiles * m.upt;
+        r.cA = range_lo(U, gridDim.x, c);
+        r.cB = range_lo(U, gridDim.x, c + 1);
+    } else {
+        const int G = min(int(gridDim.x), m.group_tiles);
+        const int gA = c < G ? range_lo(m.group_tiles, G, c) : 0, gB = c < G ? range_lo(m.group_tiles, G, c + 1) : 0;
+        r.cA = min(max(gA - m.group_off, 0), m.tiles) * m.upt;
+        r.cB = min(max(gB - m.group_off, 0), m.tiles) * m.upt;
+    }
     r.wA = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp);
     r.wB = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp + 1);
     return r;
@@ -217,7 +234,7 @@ __device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8
 
 // ---------------------------------------------------------------- one matvec phase
 
-enum { DK_EPI_STORE = 0, DK_EPI_ADD_SSQ = 1, DK_EPI_SILU_AMAX = 2 };
+enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU_AMAX = 2 };
 
 struct PhaseSmem {
     uint8_t* ring;   // this warp's ring [DK_DEPTH][slot_bytes]
@@ -225,41 +242,10 @@ struct PhaseSmem {
     ActSmem act;
     float* red;      // [DK_WARPS][slots][16]
     double* red8;    // [DK_WARPS]
-    float* sq;       // [tiles of this CTA + 2][16] squares / finished values
     int* wfirst;     // [DK_WARPS]
     int* wlast;      // [DK_WARPS]
-    int* flags;      // [4]: last-arriver flags (0,1), dead (2), block amax bits (3)
+    int* flags;      // [4]: dead (2), block amax bits (3)
 };
-
-// finished rows g, g+8 of tile X: write them out; returns the values written (for the per-tile bookkeeping)
-__device__ __forceinline__ void dk_epilogue(int epi, const DkMat& m, float* y, int64_t X, int g, float v0, float v1,
-                                            float& o0, float& o1) {
-    const int64_t r0 = 16 * X + g, r1 = r0 + 8;
-    o0 = 0.f; o1 = 0.f;
-    if (epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
-        const int64_t o = 8 * X + g;
-        if (o < m.rows / 2) { o0 = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1); y[o] = o0; }
-        return;
-    }
-    if (epi == DK_EPI_ADD_SSQ) {
-        if (r0 < m.rows) { o0 = __ldcg(y + r0) + v0; y[r0] = o0; }  // through L2: another CTA may have written it
-        if (r1 < m.rows) { o1 = __ldcg(y + r1) + v1; y[r1] = o1; }
-        return;
-    }
-    if (r0 < m.rows) y[r0] = v0;
-    if (r1 < m.rows) y[r1] = v1;
-}
-
-// after a tile is finished by 8 consecutive threads (gg = 0..7, values o0 / o1): per-tile sum of squares in double, in
-// row order, or the block maximum; `slot` is this tile's row in s.sq
-__device__ __forceinline__ void dk_tile_stats(int epi, const DkParams& p, const PhaseSmem& s, int slot, int gg, float o0, float o1) {
-    if (epi == DK_EPI_ADD_SSQ) {
-        s.sq[slot * 16 + gg] = o0;
-        s.sq[slot * 16 + gg + 8] = o1;
-    } else if (epi == DK_EPI_SILU_AMAX) {
-        atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(fabsf(o0)));
-    }
-}
 
 template <int TYPE>
 __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, int& rs,
@@ -299,27 +285,27 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
     }
 }
 
-// y (+)= W * act for one matrix; the activation limbs are already in shared memory. Ends with every row of this
-// CTA's share written (tiles shared with a neighbour: by whichever CTA arrives last).
+// y = W * act for one matrix; the activation limbs are already in shared memory. Ends with this CTA's share written:
+//   DK_EPI_STORE      y[row] = sum                       (whole tiles)
+//   DK_EPI_SILU_AMAX  y[o] = silu(gate) * up, max|y|      (whole tiles of a gate|up pair)
+//   DK_EPI_PART       partial sums of a balanced matrix: the CTA that holds a tile's first unit writes part0[row], the
+//                     one that holds its last unit (when it is another CTA) part1[row]; a CTA that holds the whole tile
+//                     writes zeros to part1. The consumer adds x + part0 + part1 (convert_act).
 __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf,
-                             int& rs, const PhaseSmem& s, double* ssq_out, unsigned* amax_out) {
+                             int& rs, const PhaseSmem& s, unsigned* amax_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
     const WarpRange r = warp_range(m, warp);
-    const int pl = epi == DK_EPI_SILU_AMAX ? (int(amax_out - p.amax) / 2) % p.n_layer : -1;
-    if (pl >= 0) dk_stamp(p, pl, 16);
     if (tid == 0) s.flags[3] = 0;
-    __syncthreads();
-    if (pl >= 0) dk_stamp(p, pl, 17);
+    __syncthreads();  // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v)
     switch (m.type) {
         case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, rs, s, warp, lane); break;
         case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, rs, s, warp, lane); break;
         default: run_units<ELB_Q8_0>(p, m, r, pf, rs, s, warp, lane); break;
     }
-    if (pl >= 0) dk_stamp(p, pl, 18);
     __syncthreads();
-    if (pl >= 0) dk_stamp(p, pl, 19);
     if (r.cA < r.cB) {
-        const int Xf = r.cA / upt, ntl = (r.cB - r.cA) / upt;
+        const int Xf = r.cA / upt, ntl = (r.cB - 1) / upt - Xf + 1;
+        float mx = 0.f;
         for (int e = tid; e < ntl * 8; e += DK_THREADS) {  // sums over the warps in warp order, then the epilogue
             const int Xt = Xf + (e >> 3), gg = e & 7;
             float v0 = 0.f, v1 = 0.f;
@@ -330,20 +316,35 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
                 v0 += s.red[(w * p.slots + (Xt - f)) * 16 + gg];
                 v1 += s.red[(w * p.slots + (Xt - f)) * 16 + gg + 8];
             }
-            float o0, o1;
-            dk_epilogue(epi, m, y, Xt, gg, v0 * inv_scale, v1 * inv_scale, o0, o1);
-            dk_tile_stats(epi, p, s, e >> 3, gg, o0, o1);
-        }
-        if (epi == DK_EPI_ADD_SSQ) {  // per-tile sums of squares, rows in order, in double (RMSNorm of the next phase)
-            __syncthreads();
-            for (int e = tid; e < ntl; e += DK_THREADS) {
-                double ss = 0.0;
-                for (int q = 0; q < 16; ++q) { const double v = s.sq[e * 16 + q]; ss += v * v; }
-                ssq_out[Xf + e] = ss;
+            v0 *= inv_scale;
+            v1 *= inv_scale;
+            const int64_t r0 = 16 * int64_t(Xt) + gg, r1 = r0 + 8;
+            if (epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
+                const int64_t o = 8 * int64_t(Xt) + gg;
+                if (o < m.rows / 2) {
+                    const float act = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
+                    y[o] = act;
+                    mx = fmaxf(mx, fabsf(act));
+                }
+            } else if (epi == DK_EPI_PART) {
+                const bool first = r.cA <= Xt * upt, last = r.cB >= (Xt + 1) * upt;
+                float* dst = first ? y : y + p.E;  // y = part0, part1 follows it
+                if (r0 < m.rows) dst[r0] = v0;
+                if (r1 < m.rows) dst[r1] = v1;
+                if (first && last) {
+                    if (r0 < m.rows) y[p.E + r0] = 0.f;
+                    if (r1 < m.rows) y[p.E + r1] = 0.f;
+                }
+            } else {
+                if (r0 < m.rows) y[r0] = v0;
+                if (r1 < m.rows) y[r1] = v1;
             }
         }
+        if (epi == DK_EPI_SILU_AMAX) {
+            mx = warp_max(mx);
+            if (lane == 0) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
+        }
     }
-    if (pl >= 0) dk_stamp(p, pl, 20);
     if (epi == DK_EPI_SILU_AMAX) {
         __syncthreads();
         if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
@@ -526,7 +527,6 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
 
 // ---------------------------------------------------------------- the step
 
-constexpr int DK_SQ_TILES = 8;
 constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * (DK_HD + 1) + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
 
 __host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
@@ -544,8 +544,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     s.slot_bytes = slot_bytes;
     s.act.lim = reinterpret_cast<int8_t*>(scratch);
     s.red = reinterpret_cast<float*>(tail);
-    s.sq = s.red + DK_WARPS * p.slots * 16;
-    s.red8 = reinterpret_cast<double*>(s.sq + DK_SQ_TILES * 16);
+    s.red8 = reinterpret_cast<double*>(s.red + DK_WARPS * p.slots * 16);
     s.wfirst = reinterpret_cast<int*>(s.red8 + DK_WARPS);
     s.wlast = s.wfirst + DK_WARPS;
     s.flags = s.wlast + DK_WARPS;
@@ -584,27 +583,25 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     if (blockIdx.x == 0)  // the other half of the amax slots: untouched by this launch, zero for the next one
         for (int i = tid; i < 2 * p.n_layer; i += DK_THREADS) p.amax[((epoch + 1) & 1u) * 2 * p.n_layer + i] = 0u;
 
-    // token embedding (get_row, src/ops.cpp:76-82 of the reference): CTA c decodes row tiles c, c+G, ... of the row
+    // token embedding (get_row, src/ops.cpp:76-82 of the reference): the CTAs decode slices of the row into the first
+    // residual buffer and clear the partial sums that the first conversion adds
     {
         const int64_t R = p.token[step];
-        for (int Xt = blockIdx.x; Xt < p.E / 16; Xt += gridDim.x) {
-            if (tid < 16) {
-                const int k = Xt * 16 + tid;
-                const float v = p.embd_type == ELB_F16 ? __half2float(reinterpret_cast<const __half*>(p.embd)[R * p.E + k])
-                                                       : elem_value(p.embd_type, tiled_elem(p.embd_type, p.embd, p.E, R, k));
-                p.x[k] = v;
-                s.sq[tid] = v;
-            }
-            __syncthreads();
-            if (tid == 0) {
-                double ss = 0.0;
-                for (int q = 0; q < 16; ++q) { const double v = s.sq[q]; ss += v * v; }
-                p.ssq[Xt] = ss;
-            }
-            __syncthreads();
+        const int lo = range_lo(p.E, gridDim.x, blockIdx.x), hi = range_lo(p.E, gridDim.x, blockIdx.x + 1);
+        for (int k = lo + tid; k < hi; k += DK_THREADS) {
+            p.xbuf[k] = p.embd_type == ELB_F16 ? __half2float(reinterpret_cast<const __half*>(p.embd)[R * p.E + k])
+                                               : elem_value(p.embd_type, tiled_elem(p.embd_type, p.embd, p.E, R, k));
+            p.part[k] = 0.f;
+            p.part[p.E + k] = 0.f;
         }
     }
     bool ok = grid_barrier(p, nb, dead);
+    int cur = 0;  // which half of xbuf holds the residual stream (without the pending partial sums)
+    auto resid_step = [&](float* out) {
+        Resid r{p.xbuf + cur * p.E, p.part, p.part + p.E, out ? out : p.xbuf + (cur ^ 1) * p.E};
+        cur ^= 1;
+        return r;
+    };
 
     for (int l = 0; l < p.n_layer && ok; ++l) {
         const DkLayer& L = p.layers[l];
@@ -612,10 +609,11 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         dk_stamp(p, l, 0);
         {
             s.act = act_for(p.E);
-            const float inv = convert_act(p.x, p.E, L.attn_norm, p.ssq, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
+            const Resid rs_ = resid_step(nullptr);
+            const float inv = convert_act(nullptr, &rs_, p.E, L.attn_norm, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
             dk_stamp(p, l, 1);
             for (int i = 0; i < p.n_qkv; ++i)
-                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr, nullptr);
+                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr);
         }
         dk_stamp(p, l, 2);
         if (!(ok = grid_barrier(p, nb, dead))) break;
@@ -626,36 +624,38 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         dk_stamp(p, l, 5);
         {
             s.act = act_for(p.H * DK_HD);
-            const float inv = convert_act(p.att, p.H * DK_HD, nullptr, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
+            const float inv = convert_act(p.att, nullptr, p.H * DK_HD, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
             dk_stamp(p, l, 6);
-            matvec_phase(p, L.wo, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
+            matvec_phase(p, L.wo, DK_EPI_PART, p.part, inv, pf, rs, s, nullptr);
         }
         dk_stamp(p, l, 7);
         if (!(ok = grid_barrier(p, nb, dead))) break;
         dk_stamp(p, l, 8);
         {
             s.act = act_for(p.E);
-            const float inv = convert_act(p.x, p.E, L.ffn_norm, p.ssq, p.eps, nullptr, p.nl_gu, s.act, s.red8);
+            const Resid rs_ = resid_step(nullptr);
+            const float inv = convert_act(nullptr, &rs_, p.E, L.ffn_norm, p.eps, nullptr, p.nl_gu, s.act, s.red8);
             dk_stamp(p, l, 9);
-            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, nullptr, amax + 1);
+            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, amax + 1);
         }
         dk_stamp(p, l, 10);
         if (!(ok = grid_barrier(p, nb, dead))) break;
         dk_stamp(p, l, 11);
         {
             s.act = act_for(p.F);
-            const float inv = convert_act(p.act, p.F, nullptr, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
+            const float inv = convert_act(p.act, nullptr, p.F, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
             dk_stamp(p, l, 12);
-            matvec_phase(p, L.down, DK_EPI_ADD_SSQ, p.x, inv, pf, rs, s, p.ssq, nullptr);
+            matvec_phase(p, L.down, DK_EPI_PART, p.part, inv, pf, rs, s, nullptr);
         }
         dk_stamp(p, l, 13);
         ok = grid_barrier(p, nb, dead);
         dk_stamp(p, l, 14);
     }
-    if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference)
+    if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference); the last residual stream goes to p.x
         s.act = act_for(p.E);
-        const float inv = convert_act(p.x, p.E, p.output_norm, p.ssq, p.eps, nullptr, 4, s.act, s.red8);
-        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr, nullptr);
+        const Resid rs_ = resid_step(p.x);
+        const float inv = convert_act(nullptr, &rs_, p.E, p.output_norm, p.eps, nullptr, 4, s.act, s.red8);
+        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr);
     }
     ring_wait<0>();
     if (blockIdx.x == 0 && tid == 0) {  // every CTA read ctl before its first barrier: safe to move on
@@ -666,7 +666,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
 
 size_t decode_smem_bytes(const DkParams& p, int slot_bytes) {
     return size_t(DK_WARPS) * DK_DEPTH * slot_bytes + dk_scratch_bytes(p.n_max) + size_t(DK_WARPS) * p.slots * 16 * 4 +
-           DK_SQ_TILES * 16 * 4 + DK_WARPS * 8 + 2 * DK_WARPS * 4 + 4 * 4 + 16;
+           DK_WARPS * 8 + 2 * DK_WARPS * 4 + 4 * 4 + 16;
 }
 
 int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s) {

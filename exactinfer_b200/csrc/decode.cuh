@@ -8,8 +8,11 @@ namespace elb {
 struct DkMat {  // one weight matrix of the step, in tiled layout
     const uint8_t* W;
     int type, unit_bytes, tiles, upt, rows, n;
-    float* part;         // split-K scratch [grid][2][16]
-    unsigned* counters;  // [tiles]
+    // How the CTAs share the matrix. group_tiles / group_off: the matrix is tiles [group_off, group_off + tiles) of a
+    // group of matrices that run in one phase (q, k, v) and the CTAs cut the group's tiles, whole tiles each.
+    // balanced: the CTAs cut the (tile, k block) units into equal ranges instead; a tile then has up to two
+    // contributors, which leave their partial sums in two buffers for the consumer to add (wo, down).
+    int group_tiles, group_off, balanced;
 };
 
 struct DkLayer {
@@ -36,7 +39,8 @@ struct DkParams {
                             // [2] launches so far (barrier targets and the parity of the amax slots derive from it)
     const float* rope;      // [n_ctx][rope_dim/2][2]
     float *x, *qkv, *att, *act, *logits;
-    double* ssq;            // [E/16] per-tile sums of squares of x
+    float* xbuf;            // [2][E] residual stream, alternating: a conversion reads one and writes the other
+    float* part;            // [2][E] partial sums of the last row-parallel matvec (wo, down), added by the next conversion
     unsigned* amax;         // [2][n_layer][2] bit patterns of max|att|, max|act| of each layer; launch e uses half e & 1
                             // (zero when it starts) and zeroes the other half for launch e + 1
     float* attn_part;       // [HKV][nsplit][group][130]

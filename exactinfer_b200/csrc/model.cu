@@ -76,7 +76,7 @@ struct Model {
     DkParams dk{};
     DkLayer* dk_layers = nullptr;
     int dk_slot = 0, dk_grid = 0;
-    double* ssq = nullptr;
+    float* xbuf = nullptr;  // persistent kernel: residual stream [2][E], then partial sums [2][E]
     unsigned* sync_words = nullptr;  // barrier counter, step index, advance flag, launch count, then 2 x [n_layer][2] amax slots
     int* pos_steps = nullptr;        // positions of a batch of single-token steps (persistent kernel)
     int* err_host = nullptr;         // pinned, mapped: raised by the kernel when a barrier wait runs out
@@ -378,8 +378,18 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
 int setup_decode_kernel(Model* m) {
     const elb_config& c = m->cfg;
     if (env_on("ELB_NO_MEGA") || m->tp.size > 1) return ELB_OK;  // the one-kernel step has no exchange between GPUs
-    auto mat = [](const Weight* w) {
-        return DkMat{w->tiled, w->type, w->unit_bytes, int(w->tiles), int(w->units_per_tile), int(w->rows), int(w->n), w->part, w->counters};
+    DeviceInfo di;
+    ELB_TRY(device_info(m->device, &di));
+    auto mat = [](const Weight* w) {  // alone in its phase, whole tiles per CTA
+        return DkMat{w->tiled, w->type, w->unit_bytes, int(w->tiles), int(w->units_per_tile), int(w->rows), int(w->n),
+                     int(w->tiles), 0, 0};
+    };
+    // row-parallel matrices (few row tiles, long rows): equal unit ranges, when every CTA's range is at least one tile
+    // long, so that no tile has more than two contributors
+    auto mat_balanced = [&](const Weight* w) {
+        DkMat d = mat(w);
+        d.balanced = w->tiles * w->units_per_tile / di.sm_count >= w->units_per_tile ? 1 : 0;
+        return d;
     };
     bool quant = m->head->type != ELB_F16 && m->embd->type != ELB_F32;
     const size_t nq = m->layers[0].qkv.size();
@@ -388,9 +398,7 @@ int setup_decode_kernel(Model* m) {
         for (auto& s : L.qkv) quant = quant && s.w->type != ELB_F16;
     }
     const int E = c.n_embd, F = c.n_ff, QD = c.n_head * 128, KD = c.n_head_kv * 128;
-    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || (E / 16 + 147) / 148 > 8) return ELB_OK;
-    DeviceInfo di;
-    ELB_TRY(device_info(m->device, &di));
+    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 5 * 4 * decode_threads()) return ELB_OK;
     DkParams& p = m->dk;
     p = DkParams{};
     std::vector<DkLayer> hl(size_t(c.n_layer));
@@ -408,8 +416,17 @@ int setup_decode_kernel(Model* m) {
     for (int l = 0; l < c.n_layer; ++l) {
         const Layer& L = m->layers[size_t(l)];
         DkLayer& d = hl[size_t(l)];
-        for (size_t i = 0; i < nq; ++i) { d.qkv[i] = mat(L.qkv[i].w); d.qkv_col[i] = int(L.qkv[i].col); account(L.qkv[i].w); }
-        d.wo = mat(L.wo); d.gu = mat(L.gu); d.down = mat(L.down);
+        int group = 0;
+        for (size_t i = 0; i < nq; ++i) group += int(L.qkv[i].w->tiles);
+        for (size_t i = 0, off = 0; i < nq; ++i) {  // q, k, v share one phase: the CTAs cut the tiles of all three together
+            d.qkv[i] = mat(L.qkv[i].w);
+            d.qkv[i].group_tiles = group;
+            d.qkv[i].group_off = int(off);
+            off += size_t(L.qkv[i].w->tiles);
+            d.qkv_col[i] = int(L.qkv[i].col);
+            account(L.qkv[i].w);
+        }
+        d.wo = mat_balanced(L.wo); d.gu = mat(L.gu); d.down = mat_balanced(L.down);
         account(L.wo); account(L.gu); account(L.down);
         d.attn_norm = L.attn_norm; d.ffn_norm = L.ffn_norm; d.q_norm = L.q_norm; d.k_norm = L.k_norm;
         d.kc = m->kcache + size_t(l) * m->n_ctx * KD;
@@ -417,7 +434,7 @@ int setup_decode_kernel(Model* m) {
     }
     ELB_CUDA(cudaMalloc(&m->dk_layers, hl.size() * sizeof(DkLayer)));
     ELB_CUDA(cudaMemcpy(m->dk_layers, hl.data(), hl.size() * sizeof(DkLayer), cudaMemcpyHostToDevice));
-    ELB_CUDA(cudaMalloc(&m->ssq, size_t(E / 16) * sizeof(double)));
+    ELB_CUDA(cudaMalloc(&m->xbuf, size_t(4) * E * sizeof(float)));  // residual stream [2][E], partial sums [2][E]
     ELB_CUDA(cudaMalloc(&m->sync_words, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->sync_words, 0, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->pos_steps, size_t(m->max_batch) * sizeof(int)));
@@ -434,7 +451,7 @@ int setup_decode_kernel(Model* m) {
     p.nl_qkv = m->nl_qkv; p.nl_wo = m->nl_wo; p.nl_gu = m->nl_gu; p.nl_down = m->nl_down;
     p.token = m->tokens_dev; p.pos = m->pos_steps; p.rope = m->rope;
     p.x = m->x; p.qkv = m->qkv; p.att = m->att; p.act = m->act; p.logits = m->logits;
-    p.ssq = m->ssq; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
+    p.xbuf = m->xbuf; p.part = m->xbuf + 2 * E; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
     p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
     p.err = err_dev; p.slots = slots; p.n_max = std::max({E, F, QD});
     m->dk_slot = (slot + 15) / 16 * 16;
@@ -525,7 +542,7 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->dk_layers); cudaFree(m->ssq); cudaFree(m->sync_words); cudaFree(m->pos_steps);
+    cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     tp_reduce_destroy(m->tpr);
     tp_comm_destroy(m->comm);
