@@ -28,7 +28,7 @@
 namespace elb {
 
 constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32, DK_DEPTH = 3;
-constexpr int DK_HD = 128, DK_KT = 32, DK_MAXG = 8, DK_MAXSPLIT = 32;
+constexpr int DK_HD = 128, DK_KT = 48, DK_KS = DK_HD + 4, DK_MAXG = 8, DK_MAXSPLIT = 32;  // DK_KS: row stride of the K tile (float4 reads without bank conflicts)
 constexpr unsigned DK_SPIN_LIMIT = 1u << 22;
 
 // ---------------------------------------------------------------- grid barrier (bounded)
@@ -383,21 +383,38 @@ struct AttnSmem {
     float* qs;    // [DK_MAXG][128]
     float* knew;  // [128]
     float* vnew;  // [128]
-    float* Ks;    // [DK_KT][129]
+    float* Ks;    // [DK_KT][DK_KS]
     float* Vs;    // [DK_KT][128]
     float* Ps;    // [DK_MAXG][DK_KT]
     float* corr;  // [DK_MAXG], then m [DK_MAXG], l [DK_MAXG]
     int* flags;
 };
 
+// K and V rows t0 .. t0+nk-1 of one KV head -> shared memory with cp.async (row `pos`, which this step appends, is
+// filled in from shared memory by the caller). One commit group.
+__device__ __forceinline__ void attn_fetch_kv(const DkLayer& L, const AttnSmem& s, int KD, int kvh, int t0, int nk, int pos) {
+    const unsigned ks = unsigned(__cvta_generic_to_shared(s.Ks)), vs = unsigned(__cvta_generic_to_shared(s.Vs));
+    for (int idx = threadIdx.x; idx < nk * (DK_HD / 4); idx += DK_THREADS) {
+        const int j = idx / (DK_HD / 4), cc = (idx % (DK_HD / 4)) * 4, t = t0 + j;
+        if (t == pos) continue;
+        const size_t off = size_t(t) * KD + kvh * DK_HD + cc;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks + unsigned(j * DK_KS + cc) * 4u), "l"(L.kc + off));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs + unsigned(j * DK_HD + cc) * 4u), "l"(L.vc + off));
+    }
+    ring_commit();
+}
+
 // CTA c < HKV * nsplit works on KV head c / nsplit, key split c % nsplit: q/k norm + RoPE, KV append, flash decode
-// over its keys, partial results to the scratch buffer; the last split of a KV head to arrive combines them in split
-// order and writes att (and max|att|). Semantics: src/model.cpp:176-214 of the reference.
+// over its keys (DK_KT at a time, fetched while the heads are normalised), partial results to the scratch buffer; the
+// last split of a KV head to arrive combines them in split order and writes att (and max|att|).
+// Semantics: src/model.cpp:176-214 of the reference.
 __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& s, unsigned* amax_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c = blockIdx.x;
     if (c >= p.HKV * p.nsplit) return;
     const int kvh = c / p.nsplit, split = c - kvh * p.nsplit, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
     const int pos = p.pos[p.ctl[0]], T = pos + 1;
+    const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);  // equal key ranges
+    attn_fetch_kv(L, s, KD, kvh, t_begin, min(DK_KT, t_end - t_begin), pos);
     const float2* cs = reinterpret_cast<const float2*>(p.rope) + size_t(pos) * (p.rope_dim / 2);
     float* m_s = s.corr + DK_MAXG;
     float* l_s = s.corr + 2 * DK_MAXG;
@@ -405,7 +422,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
         if (h < group) dk_head_norm_rope(p.qkv + (kvh * group + h) * DK_HD, L.q_norm, cs, p.rope_dim, p.eps, s.qs + h * DK_HD, lane);
         else dk_head_norm_rope(p.qkv + QD + kvh * DK_HD, L.k_norm, cs, p.rope_dim, p.eps, s.knew, lane);
     }
-    if (tid < DK_HD) s.vnew[tid] = __ldcg(p.qkv + QD + KD + kvh * DK_HD + tid);
+    if (tid >= DK_THREADS - DK_HD) s.vnew[tid - (DK_THREADS - DK_HD)] = __ldcg(p.qkv + QD + KD + kvh * DK_HD + tid - (DK_THREADS - DK_HD));
     if (tid < DK_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
     if (tid == 0) s.flags[3] = 0;
     __syncthreads();
@@ -413,45 +430,57 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
         L.kc[size_t(pos) * KD + kvh * DK_HD + tid] = s.knew[tid];
         L.vc[size_t(pos) * KD + kvh * DK_HD + tid] = s.vnew[tid];
     }
-    const int tiles = (T + DK_KT - 1) / DK_KT, per = (tiles + p.nsplit - 1) / p.nsplit;
-    const int t_begin = min(T, split * per * DK_KT), t_end = min(T, (split + 1) * per * DK_KT);
     float acc[2] = {0.f, 0.f};  // outputs (head tid/128 + 4i, dim tid%128)
     const int od = tid & (DK_HD - 1), oh = tid >> 7;
     for (int t0 = t_begin; t0 < t_end; t0 += DK_KT) {
         const int nk = min(DK_KT, t_end - t0);
+        if (t0 != t_begin) {
+            __syncthreads();  // the previous tile has been consumed
+            attn_fetch_kv(L, s, KD, kvh, t0, nk, pos);
+        }
+        if (pos >= t0 && pos < t0 + nk && tid < DK_HD) {  // the row this step appends: from shared memory, not from the cache
+            s.Ks[(pos - t0) * DK_KS + tid] = s.knew[tid];
+            s.Vs[(pos - t0) * DK_HD + tid] = s.vnew[tid];
+        }
+        ring_wait<0>();
         __syncthreads();
-        for (int idx = tid; idx < DK_KT * (DK_HD / 4); idx += DK_THREADS) {
-            const int j = idx / (DK_HD / 4), cc = (idx % (DK_HD / 4)) * 4;
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+        // scores: warp = (head, 32-key slot), lane = key; dimension order, multiply then add, as the CPU path does
+        for (int w = warp; w < group * ((nk + 31) / 32); w += DK_WARPS) {
+            const int h = w % group, j = (w / group) * 32 + lane;
             if (j < nk) {
-                const int t = t0 + j;
-                if (t == pos) {  // the row this step appends: from shared memory, not from the cache
-                    kv = *reinterpret_cast<const float4*>(s.knew + cc);
-                    vv = *reinterpret_cast<const float4*>(s.vnew + cc);
-                } else {
-                    kv = *reinterpret_cast<const float4*>(L.kc + size_t(t) * KD + kvh * DK_HD + cc);
-                    vv = *reinterpret_cast<const float4*>(L.vc + size_t(t) * KD + kvh * DK_HD + cc);
+                float a = 0.f;
+                const float4* q = reinterpret_cast<const float4*>(s.qs + h * DK_HD);
+                const float4* kr = reinterpret_cast<const float4*>(s.Ks + j * DK_KS);
+#pragma unroll 8
+                for (int i = 0; i < DK_HD / 4; ++i) {
+                    const float4 qv = q[i], kv = kr[i];
+                    a = __fadd_rn(a, __fmul_rn(qv.x, kv.x));
+                    a = __fadd_rn(a, __fmul_rn(qv.y, kv.y));
+                    a = __fadd_rn(a, __fmul_rn(qv.z, kv.z));
+                    a = __fadd_rn(a, __fmul_rn(qv.w, kv.w));
                 }
+                s.Ps[h * DK_KT + j] = __fmul_rn(a, p.scale);
             }
-            float* kr = s.Ks + j * (DK_HD + 1) + cc;
-            kr[0] = kv.x; kr[1] = kv.y; kr[2] = kv.z; kr[3] = kv.w;
-            *reinterpret_cast<float4*>(s.Vs + j * DK_HD + cc) = vv;
         }
         __syncthreads();
-        if (warp < group) {  // scores: warp = head, lane = key; dimension order, multiply then add, as the CPU path does
-            float sc = -INFINITY;
-            if (lane < nk) {
-                float a = 0.f;
-                const float* q = s.qs + warp * DK_HD;
-                const float* kr = s.Ks + lane * (DK_HD + 1);
-#pragma unroll 8
-                for (int i = 0; i < DK_HD; ++i) a = __fadd_rn(a, __fmul_rn(q[i], kr[i]));
-                sc = __fmul_rn(a, p.scale);
+        if (warp < group) {  // softmax bookkeeping of head `warp` over the tile
+            float sc[(DK_KT + 31) / 32], mx = -INFINITY;
+#pragma unroll
+            for (int q = 0; q < (DK_KT + 31) / 32; ++q) {
+                const int j = q * 32 + lane;
+                sc[q] = j < nk ? s.Ps[warp * DK_KT + j] : -INFINITY;
+                mx = fmaxf(mx, sc[q]);
             }
-            const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(sc));
-            const float pj = lane < nk ? expf(sc - m_new) : 0.f;
-            const float sum = warp_sum(pj);
-            s.Ps[warp * DK_KT + lane] = pj;
+            const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(mx));
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < (DK_KT + 31) / 32; ++q) {
+                const int j = q * 32 + lane;
+                const float pj = j < nk ? expf(sc[q] - m_new) : 0.f;
+                if (j < nk) s.Ps[warp * DK_KT + j] = pj;
+                sum += pj;
+            }
+            sum = warp_sum(sum);
             if (lane == 0) {
                 const float cr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
                 s.corr[warp] = cr;
@@ -465,6 +494,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
             const int h = oh + 4 * i;
             if (h >= group) continue;
             float a = acc[i] * s.corr[h];
+#pragma unroll 8
             for (int j = 0; j < nk; ++j) a = fmaf(s.Ps[h * DK_KT + j], s.Vs[j * DK_HD + od], a);
             acc[i] = a;
         }
@@ -527,7 +557,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
 
 // ---------------------------------------------------------------- the step
 
-constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * (DK_HD + 1) + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
+constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * DK_KS + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
 
 __host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
     const size_t act = size_t(4) * (n_max + 32) + size_t(n_max / 256) * 192, attn = size_t(DK_ATTN_FLOATS) * 4;
@@ -553,7 +583,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     as.knew = as.qs + DK_MAXG * DK_HD;
     as.vnew = as.knew + DK_HD;
     as.Ks = as.vnew + DK_HD;
-    as.Vs = as.Ks + DK_KT * (DK_HD + 1);
+    as.Vs = as.Ks + DK_KT * DK_KS;
     as.Ps = as.Vs + DK_KT * DK_HD;
     as.corr = as.Ps + DK_MAXG * DK_KT;
     as.flags = s.flags;
