@@ -92,6 +92,53 @@ struct ActSmem {
     int n_pad;
 };
 
+// Four consecutive values (index idx, a multiple of 4) -> one packed word of each of the 4 limbs (split4 of split.cuh
+// without the sub-block sums, which limb_sums adds in a pass of its own).
+__device__ __forceinline__ void limbs4(const float4& f, const Pow2 sc, int8_t* lim, int stride, int idx) {
+    const uint32_t a = (uint32_t(__float2int_rn(f.x * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
+    const uint32_t b = (uint32_t(__float2int_rn(f.y * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
+    const uint32_t c = (uint32_t(__float2int_rn(f.z * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
+    const uint32_t d = (uint32_t(__float2int_rn(f.w * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
+    const uint32_t ab01 = __byte_perm(a, b, 0x5140), ab23 = __byte_perm(a, b, 0x7362);  // a0 b0 a1 b1 | a2 b2 a3 b3
+    const uint32_t cd01 = __byte_perm(c, d, 0x5140), cd23 = __byte_perm(c, d, 0x7362);
+    *reinterpret_cast<uint32_t*>(lim + idx) = __byte_perm(ab01, cd01, 0x5410);
+    *reinterpret_cast<uint32_t*>(lim + stride + idx) = __byte_perm(ab01, cd01, 0x7632);
+    *reinterpret_cast<uint32_t*>(lim + 2 * stride + idx) = __byte_perm(ab23, cd23, 0x5410);
+    *reinterpret_cast<uint32_t*>(lim + 3 * stride + idx) = __byte_perm(ab23, cd23, 0x7632);
+}
+
+// Sums of each limb over the 32-wide (sd_mask & 1: Q4_K's min term) and 16-wide (sd_mask & 2: Q6_K's offset) sub-blocks,
+// as two balanced base-256 digits, in the layout the matvec's extra MMA reads (split.cuh). One thread per sum, from
+// the limbs in shared memory.
+__device__ __forceinline__ void limb_sums(const ActSmem& a, int n, int sd_mask) {
+    if (sd_mask & 1) {
+        for (int e = threadIdx.x; e < n / 8; e += DK_THREADS) {  // n/32 sub-blocks x 4 limbs
+            const int S = e >> 2, l = e & 3;
+            const uint4* src = reinterpret_cast<const uint4*>(a.lim + l * a.n_pad + S * 32);
+            const uint4 x = src[0], y = src[1];
+            int sum = __dp4a(int(x.x), 0x01010101, 0);
+            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
+            sum = __dp4a(int(y.x), 0x01010101, sum); sum = __dp4a(int(y.y), 0x01010101, sum);
+            sum = __dp4a(int(y.z), 0x01010101, sum); sum = __dp4a(int(y.w), 0x01010101, sum);
+            const int lo = ((sum + 128) & 255) - 128, blk = S >> 3, si = S & 7;
+            a.sd32[(blk * 8 + l) * 8 + si] = int8_t(lo);
+            a.sd32[(blk * 8 + 4 + l) * 8 + si] = int8_t((sum - lo) >> 8);
+        }
+    }
+    if (sd_mask & 2) {
+        for (int e = threadIdx.x; e < n / 4; e += DK_THREADS) {  // n/16 sub-blocks x 4 limbs
+            const int S = e >> 2, l = e & 3;
+            const uint4 x = *reinterpret_cast<const uint4*>(a.lim + l * a.n_pad + S * 16);
+            int sum = __dp4a(int(x.x), 0x01010101, 0);
+            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
+            const int lo = ((sum + 128) & 255) - 128, blk = S >> 4, si = S & 15;
+            a.sd16[(blk * 8 + l) * 16 + si] = int8_t(lo);
+            a.sd16[(blk * 8 + 4 + l) * 16 + si] = int8_t((sum - lo) >> 8);
+        }
+    }
+}
+__device__ __forceinline__ int sd_need(const DkMat& m) { return m.type == ELB_Q4_K ? 1 : m.type == ELB_Q6_K ? 2 : 0; }
+
 // Activation of the next matvec -> limbs in shared memory, by every CTA for itself. Two sources:
 //  * resid != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): the vector is
 //    resid.x + resid.p0 + resid.p1 (the row-parallel matvec before it left partial sums, see DK_EPI_PART), added in
@@ -102,7 +149,7 @@ struct ActSmem {
 struct Resid { const float *x, *p0, *p1; float* out; };
 
 __device__ float convert_act(const float* src, const Resid* resid, int n, const float* norm_w, float eps,
-                             const unsigned* amax_bits, int nl, const ActSmem& a, double* red) {
+                             const unsigned* amax_bits, int nl, const ActSmem& a, double* red, int sd_mask) {
     constexpr int V4 = 5;  // float4 per thread kept in registers: one pass over vectors of up to 10240 values
     const int tid = threadIdx.x;
     int k;
@@ -151,15 +198,17 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
 #pragma unroll
         for (int j = 0; j < V4; ++j) {
             const int idx = (j * DK_THREADS + tid) * 4;
-            if (j * DK_THREADS * 4 < n) split4(v[j], sc, a.lim, a.n_pad, a.sd32, a.sd16, idx, idx < n);  // warp-uniform
+            if (idx < n) limbs4(v[j], sc, a.lim, a.n_pad, idx);
         }
     } else {  // longer vectors (no residual stream is that long: the host keeps such shapes off this kernel)
         const float m = __uint_as_float(__ldcg(amax_bits));
         k = split_shift(m, nl);
         const Pow2 sc = make_pow2(k);
-        for (int i = tid * 4; i < n; i += DK_THREADS * 4)  // warp-uniform trip count: n is a multiple of 128
-            split4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, a.lim, a.n_pad, a.sd32, a.sd16, i, true);
+        for (int i = tid * 4; i < n; i += DK_THREADS * 4)
+            limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, a.lim, a.n_pad, i);
     }
+    __syncthreads();
+    limb_sums(a, n, sd_mask);
     __syncthreads();
     return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
 }
@@ -640,7 +689,9 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         {
             s.act = act_for(p.E);
             const Resid rs_ = resid_step(nullptr);
-            const float inv = convert_act(nullptr, &rs_, p.E, L.attn_norm, p.eps, nullptr, p.nl_qkv, s.act, s.red8);
+            int need = 0;
+            for (int i = 0; i < p.n_qkv; ++i) need |= sd_need(L.qkv[i]);
+            const float inv = convert_act(nullptr, &rs_, p.E, L.attn_norm, p.eps, nullptr, p.nl_qkv, s.act, s.red8, need);
             dk_stamp(p, l, 1);
             for (int i = 0; i < p.n_qkv; ++i)
                 matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr);
@@ -654,7 +705,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         dk_stamp(p, l, 5);
         {
             s.act = act_for(p.H * DK_HD);
-            const float inv = convert_act(p.att, nullptr, p.H * DK_HD, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8);
+            const float inv = convert_act(p.att, nullptr, p.H * DK_HD, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8, sd_need(L.wo));
             dk_stamp(p, l, 6);
             matvec_phase(p, L.wo, DK_EPI_PART, p.part, inv, pf, rs, s, nullptr);
         }
@@ -664,7 +715,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         {
             s.act = act_for(p.E);
             const Resid rs_ = resid_step(nullptr);
-            const float inv = convert_act(nullptr, &rs_, p.E, L.ffn_norm, p.eps, nullptr, p.nl_gu, s.act, s.red8);
+            const float inv = convert_act(nullptr, &rs_, p.E, L.ffn_norm, p.eps, nullptr, p.nl_gu, s.act, s.red8, sd_need(L.gu));
             dk_stamp(p, l, 9);
             matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, amax + 1);
         }
@@ -673,7 +724,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         dk_stamp(p, l, 11);
         {
             s.act = act_for(p.F);
-            const float inv = convert_act(p.act, nullptr, p.F, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8);
+            const float inv = convert_act(p.act, nullptr, p.F, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8, sd_need(L.down));
             dk_stamp(p, l, 12);
             matvec_phase(p, L.down, DK_EPI_PART, p.part, inv, pf, rs, s, nullptr);
         }
@@ -684,7 +735,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference); the last residual stream goes to p.x
         s.act = act_for(p.E);
         const Resid rs_ = resid_step(p.x);
-        const float inv = convert_act(nullptr, &rs_, p.E, p.output_norm, p.eps, nullptr, 4, s.act, s.red8);
+        const float inv = convert_act(nullptr, &rs_, p.E, p.output_norm, p.eps, nullptr, 4, s.act, s.red8, sd_need(p.head));
         matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr);
     }
     ring_wait<0>();

@@ -786,11 +786,6 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
             layer_total += sum / m->cfg.n_layer / 1000.0;
         }
         std::fprintf(stderr, "[dk prof] layer total   %7.2f us\n", layer_total);
-        for (int ev = 17; ev <= 20; ++ev) {
-            double sum = 0;
-            for (int l = 0; l < m->cfg.n_layer; ++l) sum += double(t[size_t(l) * 32 + ev] - t[size_t(l) * 32 + ev - 1]);
-            std::fprintf(stderr, "[dk prof] gu inner %d    %7.2f us\n", ev, sum / m->cfg.n_layer / 1000.0);
-        }
     }
     m->last_rows = 1;
     return ELB_OK;
