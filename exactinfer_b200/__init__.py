@@ -136,9 +136,9 @@ def split_limbs(x: np.ndarray, nl: int, device: int = 0):
     return limbs, inv
 
 
-def spec_config(spec: "synth.Spec", max_batch: int = 0) -> Config:
+def spec_config(spec: "synth.Spec", max_batch: int = 0, n_seq: int = 0) -> Config:
     return Config(spec.n_layer, spec.n_embd, spec.n_ff, spec.n_head, spec.n_head_kv, spec.head_dim, spec.n_vocab,
-                  spec.head_dim, spec.rope_base, spec.eps, max_batch)
+                  spec.head_dim, spec.rope_base, spec.eps, max_batch, n_seq)
 
 
 def tp_unique_id() -> bytes:
@@ -174,12 +174,13 @@ def tp_shard(spec: "synth.Spec", rank: int, size: int, role: str, t: int, rows: 
 class Backend:
     """el::Backend (src/model.h:42-51) on the CUDA library: cfg(), n_ctx(), name(), eval(tokens, pos0) -> logits."""
 
-    def __init__(self, spec: "synth.Spec", tensors, n_ctx: int, device: int = 0, max_batch: int = 0, tp=None):
+    def __init__(self, spec: "synth.Spec", tensors, n_ctx: int, device: int = 0, max_batch: int = 0, tp=None,
+                 n_seq: int = 0):
         """tp = (rank, size, id) makes this process rank `rank` of a tensor-parallel group of `size` GPUs; `id` is the
         128-byte value of tp_unique_id() made on one rank and given to all. `tensors` are the whole model's on every
         rank; eval must then be called by all ranks with the same arguments."""
         self.spec = spec
-        self._cfg = spec_config(spec, max_batch)
+        self._cfg = spec_config(spec, max_batch, n_seq)
         self._n_ctx = n_ctx
         h = C.c_void_p()
         if tp is None or tp[1] == 1:
@@ -219,6 +220,22 @@ class Backend:
         check(lib().elb_model_eval(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), tokens.size, pos0,
                                    logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
+
+    def eval_batch(self, tokens, seq, pos, want=None, want_logits: bool = True):
+        """Rows of several sequences in one pass: row i is tokens[i] at position pos[i] of sequence seq[i] (n_seq given at
+        construction). Returns one row of logits per wanted row (want: boolean mask, default all rows), or None."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        seq = np.ascontiguousarray(seq, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        n = tokens.size
+        w = None if want is None else np.ascontiguousarray(want, dtype=np.uint8)
+        n_out = n if w is None else int(np.count_nonzero(w))
+        out = np.empty((n_out, self.spec.n_vocab), dtype=np.float32) if want_logits else None
+        i32 = C.POINTER(C.c_int32)
+        check(lib().elb_model_eval_batch(self._h, n, tokens.ctypes.data_as(i32), seq.ctypes.data_as(i32), pos.ctypes.data_as(i32),
+                                         w.ctypes.data_as(C.c_void_p) if w is not None else None,
+                                         out.ctypes.data_as(C.c_void_p) if want_logits else None))
+        return out
 
     def eval_steps(self, tokens, pos0: int) -> float:
         """Single-token steps back to back, logits left on the device; returns the device time in ms."""

@@ -18,7 +18,7 @@ class Config(C.Structure):
     """elb_config (mirrors el::Config of the reference, src/model.h:17-23)"""
     _fields_ = [("n_layer", C.c_int32), ("n_embd", C.c_int32), ("n_ff", C.c_int32), ("n_head", C.c_int32),
                 ("n_head_kv", C.c_int32), ("head_dim", C.c_int32), ("n_vocab", C.c_int32), ("rope_dim", C.c_int32),
-                ("rope_base", C.c_double), ("eps", C.c_float), ("max_batch", C.c_int32)]
+                ("rope_base", C.c_double), ("eps", C.c_float), ("max_batch", C.c_int32), ("n_seq", C.c_int32)]
 
 
 _f32p, _i8p, _i32p = C.POINTER(C.c_float), C.POINTER(C.c_int8), C.POINTER(C.c_int32)
@@ -55,6 +55,7 @@ SIGNATURES = {
     "elb_model_finalize": (C.c_int, [_vp]),
     "elb_model_destroy": (None, [_vp]),
     "elb_model_eval": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, _vp]),
+    "elb_model_eval_batch": (C.c_int, [_vp, C.c_int, _i32p, _i32p, _i32p, _vp, _vp]),
     "elb_model_eval_steps": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, _f32p]),
     "elb_model_last_eval_stats": (C.c_int, [_vp, _f32p, C.POINTER(C.c_int64)]),
     "elb_model_hidden": (C.c_int, [_vp, _f32p]),

@@ -8,6 +8,7 @@
 // Semantics follow CpuModel::forward of the reference (src/model.cpp:176-214): scale = 1/sqrt(float(D)), scores
 // accumulated in dimension order without FMA contraction, max-subtracted softmax.
 #include <cmath>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "split.cuh"
@@ -224,11 +225,15 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_decode(const AttnDecodePara
 
 // grid (B, H + 2 HKV), one warp per (token, head). q heads: norm + rope in place. k heads: norm + rope in place and
 // store to the cache row pos0 + b. v heads: store.
+// posv / seqv (both or neither): row b sits at position posv[b] of sequence seqv[b], whose cache starts seq_stride
+// floats after kc / vc; without them row b sits at position pos0 + b of the cache at kc / vc.
 __global__ void __launch_bounds__(32) k_qkv_post(float* qkv, int64_t ld, const float* q_norm, const float* k_norm,
                                                  const float2* rope, int pos0, float* kc, float* vc, int H, int HKV,
-                                                 int rope_dim, float eps) {
+                                                 int rope_dim, float eps, const int* posv, const int* seqv,
+                                                 size_t seq_stride) {
     const int b = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x, QD = H * D, KD = HKV * D;
-    const int pos = pos0 + b;
+    const int pos = posv ? posv[b] : pos0 + b;
+    if (seqv) { kc += size_t(seqv[b]) * seq_stride; vc += size_t(seqv[b]) * seq_stride; }
     float* row = qkv + int64_t(b) * ld;
     const float2* cs = rope + size_t(pos) * (rope_dim / 2);
     if (hd < H) {
@@ -326,6 +331,277 @@ __global__ void __launch_bounds__(AP_THREADS) k_attn_prefill(const float* __rest
     }
 }
 
+// Prompt chunk, all query heads of one KV head together: a CTA holds 64 query rows (group heads x 64/group tokens), so
+// every K/V tile is loaded once for the whole group, and each thread keeps a 4-row x 2-key block of scores and a
+// 4-row x 8-dim block of outputs in registers. Same arithmetic as k_attn_prefill: scores in dimension order, multiply
+// then add, online softmax over 32-key tiles, causal. grid (HKV, ceil(B / (64/group))).
+constexpr int AG_ROWS = 64, AG_K = 32, AG_LD = D + 4, AG_THREADS = 256, AG_LDP = AG_K + 1;
+constexpr size_t AG_SMEM = size_t(AG_ROWS * AG_LD + AG_K * AG_LD + AG_K * D + AG_ROWS * AG_LDP) * sizeof(float);
+
+__global__ void __launch_bounds__(AG_THREADS) k_attn_prefill_gqa(const float* __restrict__ qkv, int64_t ld,
+                                                                 const float* __restrict__ kc, const float* __restrict__ vc,
+                                                                 float* __restrict__ att, int64_t ld_att, int pos0, int B,
+                                                                 int H, int HKV, float scale) {
+    extern __shared__ __align__(16) float sm[];
+    float* Qs = sm;                        // [64][AG_LD]
+    float* Ks = Qs + AG_ROWS * AG_LD;      // [32][AG_LD]
+    float* Vs = Ks + AG_K * AG_LD;         // [32][D]
+    float* Ps = Vs + AG_K * D;             // [64][33]
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int kvh = blockIdx.x, group = H / HKV, TQ = AG_ROWS / group, q0 = blockIdx.y * TQ, KD = HKV * D;
+    const int nq = min(TQ, B - q0);
+    for (int idx = tid; idx < AG_ROWS * (D / 4); idx += AG_THREADS) {  // row r = head * TQ + token
+        const int r = idx / (D / 4), c = (idx % (D / 4)) * 4, h = r / TQ, t = r - h * TQ;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < nq) v = *reinterpret_cast<const float4*>(qkv + int64_t(q0 + t) * ld + (kvh * group + h) * D + c);
+        *reinterpret_cast<float4*>(Qs + r * AG_LD + c) = v;
+    }
+    int last[4];  // last key each of this thread's rows may see
+    float m[4], l[4], acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i, t = r % TQ;
+        last[i] = t < nq ? pos0 + q0 + t : -1;
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
+    }
+    const int T = pos0 + q0 + nq;  // keys needed by the tile
+    for (int t0 = 0; t0 < T; t0 += AG_K) {
+        __syncthreads();
+        for (int idx = tid; idx < AG_K * (D / 4); idx += AG_THREADS) {
+            const int j = idx / (D / 4), c = (idx % (D / 4)) * 4;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (t0 + j < T) {
+                kv = *reinterpret_cast<const float4*>(kc + size_t(t0 + j) * KD + kvh * D + c);
+                vv = *reinterpret_cast<const float4*>(vc + size_t(t0 + j) * KD + kvh * D + c);
+            }
+            *reinterpret_cast<float4*>(Ks + j * AG_LD + c) = kv;
+            *reinterpret_cast<float4*>(Vs + j * D + c) = vv;
+        }
+        __syncthreads();
+        float sc[4][2];  // rows ty*4+i, keys tx and tx+16
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i][0] = sc[i][1] = 0.f;
+#pragma unroll 4
+        for (int d4 = 0; d4 < D / 4; ++d4) {
+            float4 q[4], k[2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[i] = *reinterpret_cast<const float4*>(Qs + (ty * 4 + i) * AG_LD + d4 * 4);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) k[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * AG_LD + d4 * 4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    float a = sc[i][j];
+                    a = __fadd_rn(a, __fmul_rn(q[i].x, k[j].x));
+                    a = __fadd_rn(a, __fmul_rn(q[i].y, k[j].y));
+                    a = __fadd_rn(a, __fmul_rn(q[i].z, k[j].z));
+                    a = __fadd_rn(a, __fmul_rn(q[i].w, k[j].w));
+                    sc[i][j] = a;
+                }
+        }
+        float corr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                sc[i][j] = t0 + tx + 16 * j <= last[i] ? __fmul_rn(sc[i][j], scale) : -INFINITY;
+                mx = fmaxf(mx, sc[i][j]);
+            }
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(m[i], mx);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float pj = sc[i][j] == -INFINITY ? 0.f : expf(sc[i][j] - m_new);
+                Ps[(ty * 4 + i) * AG_LDP + tx + 16 * j] = pj;
+                sum += pj;
+            }
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            corr[i] = m[i] == -INFINITY ? 0.f : expf(m[i] - m_new);
+            l[i] = l[i] * corr[i] + sum;
+            m[i] = m_new;
+        }
+        __syncwarp();  // a row's 16 threads are half a warp
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[i][c] *= corr[i];
+        const int nk = min(AG_K, T - t0);
+        for (int j = 0; j < nk; ++j) {  // outputs: dims tx*4..+3 and 64+tx*4..+3
+            const float4 v0 = *reinterpret_cast<const float4*>(Vs + j * D + tx * 4);
+            const float4 v1 = *reinterpret_cast<const float4*>(Vs + j * D + 64 + tx * 4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float pj = Ps[(ty * 4 + i) * AG_LDP + j];
+                acc[i][0] = fmaf(pj, v0.x, acc[i][0]); acc[i][1] = fmaf(pj, v0.y, acc[i][1]);
+                acc[i][2] = fmaf(pj, v0.z, acc[i][2]); acc[i][3] = fmaf(pj, v0.w, acc[i][3]);
+                acc[i][4] = fmaf(pj, v1.x, acc[i][4]); acc[i][5] = fmaf(pj, v1.y, acc[i][5]);
+                acc[i][6] = fmaf(pj, v1.z, acc[i][6]); acc[i][7] = fmaf(pj, v1.w, acc[i][7]);
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i, h = r / TQ, t = r - h * TQ;
+        if (t >= nq) continue;
+        const float inv = 1.0f / l[i];
+        float* o = att + int64_t(q0 + t) * ld_att + (kvh * group + h) * D;
+        *reinterpret_cast<float4*>(o + tx * 4) = make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+        *reinterpret_cast<float4*>(o + 64 + tx * 4) = make_float4(acc[i][4] * inv, acc[i][5] * inv, acc[i][6] * inv, acc[i][7] * inv);
+    }
+}
+
+// ---------------------------------------------------------------- rows of several sequences
+
+// Row b of the batch is one token of sequence seqv[b] at position posv[b]; its q heads are normalised and rotated and
+// its K/V row is in the cache already (k_qkv_post). Grid (B, HKV, nsplit): all q heads of a KV group share one pass
+// over keys 0..posv[b] of that sequence; key splits meet in `part` and the last split to arrive adds them in split order.
+// The same arithmetic as k_attn_decode (src/model.cpp:191-214 of the reference).
+struct AttnRowsParams {
+    const float* qkv;
+    int64_t ld;
+    const float *kc, *vc;  // this layer's cache of sequence 0; sequence s starts seq_stride floats later
+    size_t seq_stride;
+    const int *posv, *seqv;
+    float* att;
+    int64_t ld_att;
+    float* part;         // [B][HKV][nsplit][group][D + 2]
+    unsigned* counters;  // [B][HKV]
+    int H, HKV, nsplit;
+    float scale;
+};
+
+__global__ void __launch_bounds__(AD_THREADS) k_attn_rows(const AttnRowsParams p) {
+    __shared__ float qs[AD_MAXG][D];
+    __shared__ float Ks[AD_KT][AD_LDK];
+    __shared__ float Vs[AD_KT][D];
+    __shared__ float Ps[AD_MAXG][AD_KT];
+    __shared__ float corr_s[AD_MAXG], m_s[AD_MAXG], l_s[AD_MAXG];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, group = p.H / p.HKV, KD = p.HKV * D;
+    const int T = p.posv[b] + 1;
+    const float* kc = p.kc + size_t(p.seqv[b]) * p.seq_stride;
+    const float* vc = p.vc + size_t(p.seqv[b]) * p.seq_stride;
+    for (int idx = tid; idx < group * D; idx += AD_THREADS) qs[idx / D][idx % D] = p.qkv[int64_t(b) * p.ld + (kvh * group) * D + idx];
+    if (tid < AD_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+    const int tiles = (T + AD_KT - 1) / AD_KT, per = (tiles + p.nsplit - 1) / p.nsplit;
+    const int t_begin = min(T, split * per * AD_KT), t_end = min(T, (split + 1) * per * AD_KT);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // outputs (head tid/128 + 2i, dim tid%128)
+    const int od = tid & (D - 1), oh = tid >> 7;
+    for (int t0 = t_begin; t0 < t_end; t0 += AD_KT) {
+        const int nk = min(AD_KT, t_end - t0);
+        __syncthreads();
+        for (int idx = tid; idx < AD_KT * (D / 4); idx += AD_THREADS) {
+            const int j = idx / (D / 4), c = (idx % (D / 4)) * 4;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (j < nk) {
+                kv = *reinterpret_cast<const float4*>(kc + size_t(t0 + j) * KD + kvh * D + c);
+                vv = *reinterpret_cast<const float4*>(vc + size_t(t0 + j) * KD + kvh * D + c);
+            }
+            Ks[j][c] = kv.x; Ks[j][c + 1] = kv.y; Ks[j][c + 2] = kv.z; Ks[j][c + 3] = kv.w;
+            *reinterpret_cast<float4*>(&Vs[j][c]) = vv;
+        }
+        __syncthreads();
+        if (warp < group) {  // scores: warp = head, lane = key; dimension order, multiply then add, as the CPU path does
+            float sc = -INFINITY;
+            if (lane < nk) {
+                float a = 0.f;
+#pragma unroll 8
+                for (int i = 0; i < D; ++i) a = __fadd_rn(a, __fmul_rn(qs[warp][i], Ks[lane][i]));
+                sc = __fmul_rn(a, p.scale);
+            }
+            const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(sc));
+            const float pj = lane < nk ? expf(sc - m_new) : 0.f;
+            const float sum = warp_sum(pj);
+            Ps[warp][lane] = pj;
+            if (lane == 0) {
+                const float c = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                corr_s[warp] = c;
+                l_s[warp] = l_s[warp] * c + sum;
+                m_s[warp] = m_new;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = oh + 2 * i;
+            if (h >= group) continue;
+            float a = acc[i] * corr_s[h];
+            for (int j = 0; j < nk; ++j) a = fmaf(Ps[h][j], Vs[j][od], a);
+            acc[i] = a;
+        }
+    }
+    __syncthreads();
+    float* out = p.att + int64_t(b) * p.ld_att;
+    if (p.nsplit == 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = oh + 2 * i;
+            if (h < group) out[(kvh * group + h) * D + od] = acc[i] / l_s[h];
+        }
+        return;
+    }
+    float* base = p.part + (size_t(b) * p.HKV + kvh) * p.nsplit * group * (D + 2);
+    float* mine = base + size_t(split) * group * (D + 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int h = oh + 2 * i;
+        if (h < group) mine[h * (D + 2) + od] = acc[i];
+    }
+    if (tid < group) {
+        mine[tid * (D + 2) + D] = m_s[tid];
+        mine[tid * (D + 2) + D + 1] = l_s[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* cnt = p.counters + size_t(b) * p.HKV + kvh;
+        const unsigned old = atomicAdd(cnt, 1u);
+        s_last = old == unsigned(p.nsplit - 1);
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int h = oh + 2 * i;
+        if (h >= group) continue;
+        float M = -INFINITY;
+        for (int q = 0; q < p.nsplit; ++q) M = fmaxf(M, __ldcg(base + (size_t(q) * group + h) * (D + 2) + D));
+        float L = 0.f, o = 0.f;
+        for (int q = 0; q < p.nsplit; ++q) {  // fixed split order
+            const float* ps = base + (size_t(q) * group + h) * (D + 2);
+            const float mq = __ldcg(ps + D);
+            if (mq == -INFINITY) continue;
+            const float w = expf(mq - M);
+            L = fmaf(__ldcg(ps + D + 1), w, L);
+            o = fmaf(__ldcg(ps + od), w, o);
+        }
+        out[(kvh * group + h) * D + od] = o / L;
+    }
+}
+
+int attn_rows_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, size_t seq_stride, const int* posv,
+                     const int* seqv, float* att, int64_t ld_att, float* part, unsigned* counters, int B, int H, int HKV,
+                     int nsplit, float scale, cudaStream_t s) {
+    if (H % HKV || H / HKV > AD_MAXG) return fail(ELB_ERR_UNSUPPORTED, "attention: at most 8 query heads per KV head");
+    if (nsplit < 1 || nsplit > AD_MAXSPLIT) return fail(ELB_ERR_INVALID, "attention: split count out of range");
+    AttnRowsParams p{qkv, ld, kc, vc, seq_stride, posv, seqv, att, ld_att, part, counters, H, HKV, nsplit, scale};
+    k_attn_rows<<<dim3(B, HKV, nsplit), AD_THREADS, 0, s>>>(p);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
 // ---------------------------------------------------------------- RMSNorm over rows (el::rmsnorm, src/ops.cpp:155-160)
 __global__ void __launch_bounds__(256) k_rmsnorm_rows(float* out, const float* x, const float* w, int n, float eps) {
     __shared__ double red8[8];
@@ -364,9 +640,10 @@ int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s) {
 }
 
 int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_norm, const float* rope, int pos0, int B,
-                    float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s) {
+                    float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s, const int* posv,
+                    const int* seqv, size_t seq_stride) {
     k_qkv_post<<<dim3(B, H + 2 * HKV), 32, 0, s>>>(qkv, ld, q_norm, k_norm, reinterpret_cast<const float2*>(rope), pos0, kc,
-                                                   vc, H, HKV, rope_dim, eps);
+                                                   vc, H, HKV, rope_dim, eps, posv, seqv, seq_stride);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }
@@ -376,7 +653,17 @@ int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const flo
     static thread_local bool configured = false;
     if (!configured) {
         ELB_CUDA(cudaFuncSetAttribute(k_attn_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AP_SMEM)));
+        ELB_CUDA(cudaFuncSetAttribute(k_attn_prefill_gqa, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AG_SMEM)));
         configured = true;
+    }
+    const int group = H / HKV;
+    static const bool old_kernel = [] { const char* v = std::getenv("ELB_ATTN_SIMPLE"); return v && v[0] == '1'; }();
+    if (!old_kernel && H % HKV == 0 && AG_ROWS % group == 0 && ld % 4 == 0 && ld_att % 4 == 0) {
+        const int TQ = AG_ROWS / group;
+        k_attn_prefill_gqa<<<dim3(HKV, (B + TQ - 1) / TQ), AG_THREADS, AG_SMEM, s>>>(qkv, ld, kc, vc, att, ld_att, pos0, B, H,
+                                                                                   HKV, scale);
+        ELB_CUDA(cudaGetLastError());
+        return ELB_OK;
     }
     k_attn_prefill<<<dim3(H, (B + AP_Q - 1) / AP_Q), AP_THREADS, AP_SMEM, s>>>(qkv, ld, kc, vc, att, ld_att, pos0, B, H, HKV,
                                                                              scale);

@@ -247,7 +247,12 @@ struct AttnDecodeArgs {
 };
 int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s);
 int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_norm, const float* rope, int pos0, int B,
-                    float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s);
+                    float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s,
+                    const int* posv = nullptr, const int* seqv = nullptr, size_t seq_stride = 0);
+// rows of several sequences (row b: position posv[b] of sequence seqv[b]); part [B][HKV][nsplit][group][130], counters [B][HKV]
+int attn_rows_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, size_t seq_stride, const int* posv,
+                     const int* seqv, float* att, int64_t ld_att, float* part, unsigned* counters, int B, int H, int HKV,
+                     int nsplit, float scale, cudaStream_t s);
 int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
                         int pos0, int B, int H, int HKV, float scale, cudaStream_t s);
 int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s);
@@ -312,6 +317,8 @@ int model_finalize(Model* m);
 void model_destroy(Model* m);
 int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits);
 int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* device_ms);
+int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
+                     float* logits);
 int model_stats(const Model* m, float* ms, int64_t* launches);
 int model_hidden(Model* m, float* out);
 size_t model_weight_bytes(const Model* m);

@@ -23,7 +23,8 @@
 
 namespace elb {
 
-constexpr int TC_ROWS = 128, TC_KSTAGE = 128, TC_STAGES = 3, TC_EPI_WARPS = 8, TC_THREADS = (TC_EPI_WARPS + 2) * 32;
+constexpr int TC_ROWS = 128, TC_KSTAGE = 128, TC_STAGES = 3, TC_EPI_WARPS = 16, TC_THREADS = (TC_EPI_WARPS + 2) * 32;
+constexpr int TC_TOK_PARTS = TC_EPI_WARPS / 4;  // epilogue warps per TMEM lane quarter: each takes a share of the tile's tokens
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -91,6 +92,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, int (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -223,7 +230,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             }
         }
     } else {  // ---- epilogue: warp w drains TMEM lanes 32(w%4).. (weight rows) for tokens [th*TH, (th+1)*TH), th = w/4
-        constexpr int TH = T / 2;  // tokens per epilogue warp
+        constexpr int TH = T / TC_TOK_PARTS;  // tokens per epilogue warp
+        static_assert(TH % 4 == 0, "token share of an epilogue warp is loaded four columns at a time");
+        constexpr int XPT = (T * 8 + TC_EPI_WARPS * 32 - 1) / (TC_EPI_WARPS * 32);  // sum(X) values staged per thread
+        const int etid = warp * 32 + lane;
         const int q4 = warp & 3, th = warp >> 2;
         const int nblk = p.n / 256, nsub = p.n / 32;
         int kbt = 0;  // 256-blocks drained so far, over all tiles of this CTA
@@ -241,6 +251,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             dm0 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub));
             dm1 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + 4));
         }
+        // sum(X) of a block for the tile's tokens is staged through shared memory by all epilogue warps; the values of
+        // the next block are fetched while this one is drained
+        float xreg[XPT];
+        auto fetch_xsum = [&](int kb) {
+#pragma unroll
+            for (int q = 0; q < XPT; ++q) {
+                const int i = etid + q * TC_EPI_WARPS * 32;
+                const int tok = min(tok0 + (i >> 3), p.B - 1);
+                xreg[q] = i < T * 8 ? __ldg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7)) : 0.f;
+            }
+        };
+        if (p.pl_dm) fetch_xsum(0);
         for (int kb = 0; kb < nkb && ok; ++kb, ++kbt) {
             const int acc = kbt & 1;
             float d_next = 0.f;
@@ -252,13 +274,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                     dn1 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + (kb + 1) * 8 + 4));
                 }
             }
-            if (p.pl_dm) {  // stage sum(X) of this block for the tile's tokens (all 8 epilogue warps, 2 floats each)
+            if (p.pl_dm) {
                 float* xb = xs_s + acc * (T * 8);
-                const int etid = warp * 32 + lane;  // 0..255
-                for (int i = etid; i < T * 8; i += TC_EPI_WARPS * 32) {
-                    const int tok = min(tok0 + (i >> 3), p.B - 1);
-                    xb[i] = __ldg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7));
+#pragma unroll
+                for (int q = 0; q < XPT; ++q) {
+                    const int i = etid + q * TC_EPI_WARPS * 32;
+                    if (i < T * 8) xb[i] = xreg[q];
                 }
+                if (kb + 1 < nkb) fetch_xsum(kb + 1);
                 asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");  // epilogue warps only
             }
             ok = mbar_wait(tfull + acc, (kbt >> 1) & 1);
@@ -268,9 +291,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             {
                 int v[NL + 1][TH];  // every load of the drain is issued before the one wait
 #pragma unroll
-                for (int c = 0; c < TH / 8; ++c)
+                for (int c = 0; c < TH / 4; ++c)
 #pragma unroll
-                    for (int j = 0; j <= NL; ++j) tmem_ld8(tbase + j * T + c * 8, *reinterpret_cast<int (*)[8]>(&v[j][c * 8]));
+                    for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + c * 4, *reinterpret_cast<int (*)[4]>(&v[j][c * 4]));
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();

@@ -41,7 +41,7 @@ bool env_on(const char* name) {
 
 struct Model {
     elb_config cfg{};
-    int n_ctx = 0, device = 0, max_batch = 512;
+    int n_ctx = 0, device = 0, max_batch = 512, n_seq = 1;
     bool finalized = false;
     std::vector<HostTensor> pending;  // [3 + n_layer * 11], valid until finalize
     cudaStream_t stream = nullptr;
@@ -86,6 +86,12 @@ struct Model {
     TpReduce* tpr = nullptr;  // single-token all-reduce through peer memory (null: NCCL)
     int H = 0, HKV = 0;
     int64_t F = 0;
+    // several sequences (n_seq > 1): rows of a batch carry their own sequence and position
+    int *seq_dev = nullptr, *posv_dev = nullptr;   // [max_batch]
+    float* logits_rows = nullptr;                  // [n_seq][n_vocab] logits of the wanted rows of a batch
+    float* rows_part = nullptr;                    // attention partial results of a batch
+    unsigned* rows_counters = nullptr;
+    int rows_split = 1;
     float* xr = nullptr;            // [max_batch][E] this rank's partial sums before the all-reduce
     float* logits_local = nullptr;  // [vchunk] this rank's rows of the head
     std::vector<std::vector<uint8_t>> shard_store;  // column cuts of wo / down, valid until finalize
@@ -178,7 +184,8 @@ int split_tokens(Model* m, const float* xin, int64_t ldx, int n, int nl, const f
     return split_launch(xin, ldx, B, n, nl, norm_w, m->cfg.eps, m->limbs, m->inv_scale, m->xsum, m->stream);
 }
 
-int body_prefill(Model* m, int B, int pos0) {
+// Rows of one sequence at consecutive positions (seq0, pos0 + b), or (mixed) row b at posv_dev[b] of sequence seq_dev[b].
+int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
     const elb_config& c = m->cfg;
     const int E = c.n_embd, F = int(m->F), H = m->H, HKV = m->HKV, QD = H * 128, KD = HKV * 128, QKV = QD + 2 * KD;
     const float scale = 1.0f / std::sqrt(float(c.head_dim));
@@ -190,14 +197,22 @@ int body_prefill(Model* m, int B, int pos0) {
     const int epi_o = res ? EPI_ADD : EPI_STORE;
     for (int l = 0; l < c.n_layer; ++l) {
         Layer& L = m->layers[size_t(l)];
-        float* kc = m->kcache + size_t(l) * m->n_ctx * KD;
-        float* vc = m->vcache + size_t(l) * m->n_ctx * KD;
+        const size_t seq_stride = size_t(m->n_ctx) * KD;
+        float* kc = m->kcache + (size_t(l) * m->n_seq + (mixed ? 0 : seq0)) * seq_stride;
+        float* vc = m->vcache + (size_t(l) * m->n_seq + (mixed ? 0 : seq0)) * seq_stride;
         bool q = false;
         for (auto& s : L.qkv) q |= s.w->type != ELB_F16;
         ELB_TRY(split_tokens(m, m->x, E, E, m->nl_qkv, L.attn_norm, B, q));
         for (auto& s : L.qkv) ELB_TRY(linear_tokens(m, s.w, m->x, E, L.attn_norm, B, m->qkv + s.col, QKV, nullptr, EPI_STORE, m->nl_qkv));
-        ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, pos0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream));
-        ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream));
+        if (mixed) {
+            ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, 0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream,
+                                    m->posv_dev, m->seq_dev, seq_stride));
+            ELB_TRY(attn_rows_launch(m->qkv, QKV, kc, vc, seq_stride, m->posv_dev, m->seq_dev, m->att, QD, m->rows_part,
+                                     m->rows_counters, B, H, HKV, m->rows_split, scale, m->stream));
+        } else {
+            ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, pos0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream));
+            ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream));
+        }
         m->launches += 2;
         ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16));
         ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, yo, E, res, epi_o, m->nl_wo));
@@ -301,7 +316,7 @@ int body_decode(Model* m) {
         for (auto& s : L.qkv)
             ELB_TRY(gemv(m, s.w, ActIn{m->dlimbs[0], m->dinv, m->x, L.attn_norm}, m->qkv + s.col, nullptr, EPI_STORE, PostOp{}));
         AttnDecodeArgs a{m->qkv, L.q_norm, L.k_norm, m->rope, m->pos_dev,
-                         m->kcache + size_t(l) * m->n_ctx * KD, m->vcache + size_t(l) * m->n_ctx * KD, m->att, m->attn_part,
+                         m->kcache + size_t(l) * m->n_seq * m->n_ctx * KD, m->vcache + size_t(l) * m->n_seq * m->n_ctx * KD, m->att, m->attn_part,
                          m->attn_counters, H, HKV, c.rope_dim, m->attn_split, c.eps, scale, m->use_pdl,
                          make_post(m, quant(L.wo), m->att, QD, nullptr, m->nl_wo, 1)};
         ELB_TRY(attn_decode_launch(a, m->stream));
@@ -429,8 +444,8 @@ int setup_decode_kernel(Model* m) {
         d.wo = mat_balanced(L.wo); d.gu = mat(L.gu); d.down = mat_balanced(L.down);
         account(L.wo); account(L.gu); account(L.down);
         d.attn_norm = L.attn_norm; d.ffn_norm = L.ffn_norm; d.q_norm = L.q_norm; d.k_norm = L.k_norm;
-        d.kc = m->kcache + size_t(l) * m->n_ctx * KD;
-        d.vc = m->vcache + size_t(l) * m->n_ctx * KD;
+        d.kc = m->kcache + size_t(l) * m->n_seq * m->n_ctx * KD;  // sequence 0
+        d.vc = m->vcache + size_t(l) * m->n_seq * m->n_ctx * KD;
     }
     ELB_CUDA(cudaMalloc(&m->dk_layers, hl.size() * sizeof(DkLayer)));
     ELB_CUDA(cudaMemcpy(m->dk_layers, hl.data(), hl.size() * sizeof(DkLayer), cudaMemcpyHostToDevice));
@@ -504,6 +519,7 @@ int model_create_tp(const elb_config* cfg, int n_ctx, int device, int rank, int 
         if (rc != ELB_OK) { delete m; return rc; }
     }
     m->max_batch = cfg->max_batch > 0 ? cfg->max_batch : 512;
+    m->n_seq = cfg->n_seq > 0 ? cfg->n_seq : 1;
     m->pending.resize(size_t(3 + cfg->n_layer * 11));
     m->layers.resize(size_t(cfg->n_layer));
     m->use_graph = !env_on("ELB_NO_GRAPH");
@@ -544,6 +560,7 @@ void model_destroy(Model* m) {
         cudaFree(p);
     cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
+    cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);
     tp_comm_destroy(m->comm);
     if (m->err_host) cudaFreeHost(m->err_host);
@@ -600,7 +617,7 @@ int model_finalize(Model* m) {
     const int64_t F = m->F, QD = int64_t(m->H) * 128, KD = int64_t(m->HKV) * 128, QKV = QD + 2 * KD;
 
     // device memory budget before anything is allocated (pre-flight check of the reference, :1578-1591)
-    const size_t kv_bytes = size_t(c.n_layer) * size_t(m->n_ctx) * size_t(KD) * sizeof(float);
+    const size_t kv_bytes = size_t(c.n_layer) * size_t(m->n_seq) * size_t(m->n_ctx) * size_t(KD) * sizeof(float);
     const int64_t maxn = std::max({E, QD, F});
     size_t need = 2 * kv_bytes + size_t(B) * size_t(E + QKV + QD + F) * 4 + size_t(V) * 4 + size_t(4) * B * maxn + size_t(B) * (maxn / 32 + 1) * 4;
     for (const HostTensor& t : m->pending)
@@ -619,11 +636,14 @@ int model_finalize(Model* m) {
 
     const HostTensor& emb = P(ELB_TOK_EMBD, 0);
     if (!emb.bytes) return fail(ELB_ERR_STATE, "model: token_embd missing");
-    ELB_TRY(weight_create(m->device, emb.type, emb.rows, emb.n, emb.bytes, emb.nbytes, 0, &m->embd));
+    // with several sequences the head runs as a matrix product over the rows of a batch: digit planes for it too
+    const int head_flags = m->n_seq > 1 && m->tp.size == 1 ? ELB_W_PLANES : 0;
+    const bool tied = !P(ELB_OUTPUT, 0).bytes;
+    ELB_TRY(weight_create(m->device, emb.type, emb.rows, emb.n, emb.bytes, emb.nbytes, tied ? head_flags : 0, &m->embd));
     ELB_TRY(gemv_prepare(m->embd));
     const HostTensor& outw = P(ELB_OUTPUT, 0);
     if (outw.bytes) {
-        ELB_TRY(weight_create(m->device, outw.type, outw.rows, outw.n, outw.bytes, outw.nbytes, 0, &m->head));
+        ELB_TRY(weight_create(m->device, outw.type, outw.rows, outw.n, outw.bytes, outw.nbytes, head_flags, &m->head));
         ELB_TRY(gemv_prepare(m->head));
     } else if (m->tp.size > 1) {
         ELB_TRY(weight_view_rows(m->embd, m->tp.v0, m->tp.v1 - m->tp.v0, &m->head));  // this rank's rows of the tied table
@@ -683,6 +703,19 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->xsum, size_t(B) * (maxn / 32 + 1) * 4));
     ELB_CUDA(cudaMalloc(&m->tokens_dev, size_t(B) * sizeof(int32_t)));
     ELB_CUDA(cudaMalloc(&m->pos_dev, sizeof(int)));
+    if (m->n_seq > 1) {
+        DeviceInfo dinfo;
+        ELB_TRY(device_info(m->device, &dinfo));
+        ELB_CUDA(cudaMalloc(&m->seq_dev, size_t(B) * sizeof(int)));
+        ELB_CUDA(cudaMalloc(&m->posv_dev, size_t(B) * sizeof(int)));
+        ELB_CUDA(cudaMalloc(&m->logits_rows, size_t(m->n_seq) * V * sizeof(float)));
+        // key splits of the batched attention: enough CTAs for two per SM when one row per sequence is in the batch
+        m->rows_split = int(std::max<int64_t>(1, std::min<int64_t>(8, (2 * dinfo.sm_count + int64_t(m->n_seq) * m->HKV - 1) / (int64_t(m->n_seq) * m->HKV))));
+        const int group = c.n_head / c.n_head_kv;
+        ELB_CUDA(cudaMalloc(&m->rows_part, size_t(B) * m->HKV * m->rows_split * group * (128 + 2) * sizeof(float)));
+        ELB_CUDA(cudaMalloc(&m->rows_counters, size_t(B) * m->HKV * sizeof(unsigned)));
+        ELB_CUDA(cudaMemset(m->rows_counters, 0, size_t(B) * m->HKV * sizeof(unsigned)));
+    }
     ELB_CUDA(cudaMallocHost(&m->tokens_host, size_t(B) * sizeof(int32_t)));
     ELB_CUDA(cudaMallocHost(&m->pos_host, sizeof(int)));
     {
@@ -725,6 +758,82 @@ int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits) 
         ELB_TRY(chunk(m, tokens + done, b, pos0 + done, done + b == n ? logits : nullptr));
         done += b;
     }
+    m->last_launches = m->launches - before;
+    return ELB_OK;
+}
+
+// Rows of several sequences in one pass: the prompt-chunk path with per-row sequence and position (body_prefill, mixed)
+// or, when all rows belong to one sequence at consecutive positions, exactly the prompt-chunk path on that sequence's
+// cache. The head runs over the wanted rows only.
+int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
+                     float* logits) {
+    if (!m || !tokens || !seq || !pos) return fail(ELB_ERR_INVALID, "eval_batch: null argument");
+    if (!m->finalized) return fail(ELB_ERR_STATE, "eval_batch: model not finalized");
+    if (n <= 0) return fail(ELB_ERR_INVALID, "eval_batch: empty batch");
+    if (n > m->max_batch) return fail(ELB_ERR_RANGE, "eval_batch: more rows than max_batch");
+    bool uniform = true;
+    std::vector<int> rows;  // wanted rows
+    for (int i = 0; i < n; ++i) {
+        if (tokens[i] < 0 || tokens[i] >= m->cfg.n_vocab) return fail(ELB_ERR_RANGE, "eval_batch: token id out of range");
+        if (seq[i] < 0 || seq[i] >= m->n_seq) return fail(ELB_ERR_RANGE, "eval_batch: sequence index out of range");
+        if (pos[i] < 0 || pos[i] >= m->n_ctx) return fail(ELB_ERR_RANGE, "eval_batch: context window full");
+        uniform = uniform && seq[i] == seq[0] && pos[i] == pos[0] + i;
+        if (logits && (!want || want[i])) rows.push_back(i);
+    }
+    for (int i = 0; i < n; ++i)  // rows of one sequence: increasing, consecutive positions
+        for (int j = i + 1; j < n; ++j)
+            if (seq[j] == seq[i]) {
+                if (pos[j] != pos[i] + 1) return fail(ELB_ERR_INVALID, "eval_batch: rows of a sequence must be at consecutive positions");
+                break;
+            }
+    if (!uniform && m->n_seq == 1) return fail(ELB_ERR_INVALID, "eval_batch: one sequence needs consecutive positions");
+    if (int(rows.size()) > m->n_seq) return fail(ELB_ERR_UNSUPPORTED, "eval_batch: more wanted rows than sequences");
+    if (m->tp.size > 1 && rows.size() > 1) return fail(ELB_ERR_UNSUPPORTED, "eval_batch: one wanted row under tensor parallelism");
+    ELB_CUDA(cudaSetDevice(m->device));
+    const int E = m->cfg.n_embd;
+    const int64_t V = m->cfg.n_vocab, before = m->launches;
+    std::memcpy(m->tokens_host, tokens, size_t(n) * sizeof(int32_t));
+    ELB_CUDA(cudaMemcpyAsync(m->tokens_dev, m->tokens_host, size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice, m->stream));
+    if (!uniform) {
+        // (pageable source: the copies are staged by the runtime before the call returns)
+        ELB_CUDA(cudaMemcpyAsync(m->seq_dev, seq, size_t(n) * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+        ELB_CUDA(cudaMemcpyAsync(m->posv_dev, pos, size_t(n) * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    }
+    ELB_CUDA(cudaEventRecord(m->ev0, m->stream));
+    ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, n, m->x, m->stream));
+    ++m->launches;
+    ELB_TRY(body_prefill(m, n, pos[0], seq[0], !uniform));
+    m->last_rows = n;
+    float* out_dev = nullptr;
+    if (rows.size() == 1) {
+        ELB_TRY(head_logits(m, m->x + size_t(rows[0]) * E));
+        out_dev = m->logits;
+    } else if (rows.size() > 1) {
+        float* xh = m->x;
+        if (int(rows.size()) != n) {  // compact the wanted rows (act is free after the last layer)
+            xh = m->act;
+            for (size_t r = 0; r < rows.size(); ++r)
+                ELB_CUDA(cudaMemcpyAsync(xh + r * E, m->x + size_t(rows[r]) * E, size_t(E) * sizeof(float), cudaMemcpyDeviceToDevice, m->stream));
+        }
+        const int R = int(rows.size());
+        if (m->head->type != ELB_F16 && !m->head->planes) {  // no digit planes: row by row
+            for (int r = 0; r < R; ++r) {
+                ELB_TRY(prep_limbs_launch(xh + size_t(r) * E, E, m->output_norm, m->cfg.eps, 4, m->dlimbs[0], m->dinv, false, m->stream));
+                ++m->launches;
+                ELB_TRY(gemv(m, m->head, ActIn{m->dlimbs[0], m->dinv, xh + size_t(r) * E, m->output_norm}, m->logits_rows + size_t(r) * V,
+                             nullptr, EPI_STORE, PostOp{}));
+            }
+        } else {
+            ELB_TRY(split_tokens(m, xh, E, E, 4, m->output_norm, R, m->head->type != ELB_F16));
+            ELB_TRY(linear_tokens(m, m->head, xh, E, m->output_norm, R, m->logits_rows, V, nullptr, EPI_STORE, 4));
+        }
+        out_dev = m->logits_rows;
+    }
+    ELB_CUDA(cudaEventRecord(m->ev1, m->stream));
+    if (out_dev) ELB_CUDA(cudaMemcpyAsync(logits, out_dev, rows.size() * size_t(V) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+    ELB_CUDA(cudaStreamSynchronize(m->stream));
+    ELB_TRY(gemm_tc_check());
+    ELB_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
     m->last_launches = m->launches - before;
     return ELB_OK;
 }

@@ -112,6 +112,8 @@ typedef struct {
     double rope_base;
     float eps;
     int32_t max_batch; /* prompt chunk length; 0 = 512 (make_cuda_backend, src/cuda/model_cuda.cu:1912) */
+    int32_t n_seq;     /* sequences that share the model, each with its own n_ctx rows of KV cache; 0 = 1 (the reference
+                          keeps one sequence per process) */
 } elb_config;
 
 /* tensor roles, in the order of el::ModelTensors / el::LayerTensors (src/model.h:25-36) */
@@ -137,6 +139,17 @@ void elb_model_destroy(elb_model* m);
  * not NULL the LAST token's n_vocab fp32 logits are written to that host buffer. Synchronous.
  * n <= 0 -> ELB_ERR_INVALID; pos0 < 0, pos0+n > n_ctx or a token outside [0, n_vocab) -> ELB_ERR_RANGE. */
 int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits);
+
+/* Rows of several sequences in one pass (no counterpart in the reference, which serves one sequence at a time:
+ * src/main.cpp:499-505 keeps a single `cached` prefix). Row i is token tokens[i] at position pos[i] of sequence seq[i]
+ * (0 <= seq[i] < n_seq); the rows of one sequence must come in increasing, consecutive positions, continuing what that
+ * sequence has cached, exactly as elb_model_eval requires of its tokens. Each row attends to positions 0..pos[i] of its
+ * own sequence; only the KV rows (seq[i], pos[i]) are written. n <= max_batch. When logits is not NULL it receives one
+ * row of n_vocab floats for every row i with want[i] != 0, in row order (want == NULL: every row); at most n_seq rows
+ * may be wanted. A prompt goes in as rows of one sequence (want only the last), a batched decode step as one row per
+ * sequence. elb_model_eval(tokens, n, pos0) is the same as rows (seq 0, pos0 + i) with only the last row wanted. */
+int elb_model_eval_batch(elb_model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos,
+                         const uint8_t* want, float* logits);
 
 /* n single-token steps at positions pos0.., enqueued back to back without reading logits back (the tg loop of the
  * reference's bench command, src/main.cpp:639, without its per-token host round trip). device_ms receives the device
