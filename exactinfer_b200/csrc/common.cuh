@@ -290,6 +290,7 @@ struct TpPeerBuf {
 };
 int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok);
 void tp_peer_free(TpPeerBuf* b, int rank);
+int tp_agree(TpComm* c, bool mine, cudaStream_t s, bool* all);
 
 // tp_reduce.cu: all-reduce of one activation vector through peer memory, fused with the limb split that follows it
 struct TpReduce {

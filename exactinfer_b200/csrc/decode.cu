@@ -30,6 +30,7 @@ namespace elb {
 constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32, DK_DEPTH = 3;
 constexpr int DK_HD = 128, DK_KT = 48, DK_KS = DK_HD + 4, DK_MAXG = 8, DK_MAXSPLIT = 32;  // DK_KS: row stride of the K tile (float4 reads without bank conflicts)
 constexpr unsigned DK_SPIN_LIMIT = 1u << 22;
+constexpr unsigned DK_XSPIN_LIMIT = 1u << 24;  // waits on another GPU (x ~100 ns: about two seconds)
 
 // ---------------------------------------------------------------- grid barrier (bounded)
 
@@ -55,6 +56,63 @@ __device__ __forceinline__ bool grid_barrier(const DkParams& p, unsigned& target
                 break;
             }
             if (it > 2048) __nanosleep(64);
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    return !*s_dead;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Barrier over the CTAs of ALL tensor-parallel ranks: exchange number x (counted from the first launch, the same on
+// every rank) is complete when every rank's CTAs have arrived. CTA 0 waits for the local arrivals, raises this rank's
+// flag of set x & 1 on every peer (system-scope release: the partial sums the local CTAs stored to the peers, each
+// followed by a system fence, are visible before it), waits for the peers' flags, then releases the local CTAs through
+// a local word. One rank: the grid barrier. All waits bounded.
+__device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& target, unsigned x, int* s_dead) {
+    if (p.tp_size == 1) return grid_barrier(p, target, s_dead);
+    __syncthreads();
+    if (threadIdx.x == 0 && !*s_dead) {
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");
+        target += gridDim.x;
+        unsigned it = 0;
+        bool dead = false;
+        if (blockIdx.x == 0) {
+            while (!dead && int(ld_acquire(p.bar) - target) < 0)
+                if (++it > DK_SPIN_LIMIT) dead = true; else if (it > 2048) __nanosleep(64);
+            const int set = int(x & 1u);
+            unsigned* mine = nullptr;  // this rank's flag words
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (q >= p.tp_size) break;
+                if (q == p.tp_rank) mine = p.flag_peer[q];
+                else if (!dead) st_release_sys(p.flag_peer[q] + set * 8 + p.tp_rank, x + 1);
+            }
+            for (int q = 0; q < p.tp_size && !dead; ++q) {
+                if (q == p.tp_rank) continue;
+                it = 0;
+                while (!dead && ld_acquire_sys(mine + set * 8 + q) != x + 1)
+                    if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 64) __nanosleep(100);
+            }
+            if (!dead) st_release_gpu(p.xctl + 1, x + 1);
+        } else {
+            while (!dead && int(ld_acquire(p.xctl + 1) - (x + 1)) < 0)
+                if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 2048) __nanosleep(100);
+        }
+        if (dead) {
+            *s_dead = 1;
+            atomicExch(p.err, 1);
         }
         __threadfence();
     }
@@ -141,12 +199,17 @@ __device__ __forceinline__ int sd_need(const DkMat& m) { return m.type == ELB_Q4
 
 // Activation of the next matvec -> limbs in shared memory, by every CTA for itself. Two sources:
 //  * resid != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): the vector is
-//    resid.x + resid.p0 + resid.p1 (the row-parallel matvec before it left partial sums, see DK_EPI_PART), added in
-//    that order by every CTA alike; CTA c also stores its slice of the sum to resid.out, the residual stream of the next
-//    conversion. RMSNorm with the reference's operation order (src/ops.cpp:155-160), sum of squares in double.
+//    resid.x + the resid.np vectors at resid.parts (the row-parallel matvec before it left partial sums, two per
+//    tensor-parallel rank, see DK_EPI_PART), added in that order by every CTA of every rank alike; CTA c also stores
+//    its slice of the sum to resid.out, the residual stream of the next conversion. RMSNorm with the reference's operation order (src/ops.cpp:155-160), sum of squares in double.
 //  * otherwise src with max|src| known (amax_bits, the bit pattern of a non-negative float).
 // All of it read through L2 (written by other CTAs before the last barrier). Returns inv_scale = 2^-k.
-struct Resid { const float *x, *p0, *p1; float* out; };
+struct Resid {
+    const float* x;
+    const float* parts;  // np vectors of E floats, added in order; np = 0: none
+    int np;
+    float* out;
+};
 
 __device__ float convert_act(const float* src, const Resid* resid, int n, const float* norm_w, float eps,
                              const unsigned* amax_bits, int nl, const ActSmem& a, double* red, int sd_mask) {
@@ -161,15 +224,30 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
             const int idx = (j * DK_THREADS + tid) * 4;
             const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
             if (resid) {
-                const float4 x = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->x + idx)) : z;
-                const float4 p0 = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->p0 + idx)) : z;
-                const float4 p1 = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->p1 + idx)) : z;
-                v[j] = make_float4(__fadd_rn(__fadd_rn(x.x, p0.x), p1.x), __fadd_rn(__fadd_rn(x.y, p0.y), p1.y),
-                                   __fadd_rn(__fadd_rn(x.z, p0.z), p1.z), __fadd_rn(__fadd_rn(x.w, p0.w), p1.w));
+                v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->x + idx)) : z;
             } else {
                 v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(src + idx)) : z;
             }
             w[j] = norm_w && idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : z;
+        }
+        if (resid) {  // + the partial sums, vector by vector (two at a time in flight), in the same order everywhere
+            for (int q = 0; q < resid->np; q += 2) {
+                float4 a[V4], b[V4];
+#pragma unroll
+                for (int j = 0; j < V4; ++j) {
+                    const int idx = (j * DK_THREADS + tid) * 4;
+                    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                    a[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q) * n + idx)) : z;
+                    b[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q + 1) * n + idx)) : z;
+                }
+#pragma unroll
+                for (int j = 0; j < V4; ++j) {
+                    v[j].x = __fadd_rn(__fadd_rn(v[j].x, a[j].x), b[j].x);
+                    v[j].y = __fadd_rn(__fadd_rn(v[j].y, a[j].y), b[j].y);
+                    v[j].z = __fadd_rn(__fadd_rn(v[j].z, a[j].z), b[j].z);
+                    v[j].w = __fadd_rn(__fadd_rn(v[j].w, a[j].w), b[j].w);
+                }
+            }
         }
         float m = 0.f;
         if (resid) {
@@ -283,7 +361,7 @@ __device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8
 
 // ---------------------------------------------------------------- one matvec phase
 
-enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU_AMAX = 2 };
+enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU_AMAX = 2, DK_EPI_LOGITS = 3 };
 
 struct PhaseSmem {
     uint8_t* ring;   // this warp's ring [DK_DEPTH][slot_bytes]
@@ -337,11 +415,13 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
 // y = W * act for one matrix; the activation limbs are already in shared memory. Ends with this CTA's share written:
 //   DK_EPI_STORE      y[row] = sum                       (whole tiles)
 //   DK_EPI_SILU_AMAX  y[o] = silu(gate) * up, max|y|      (whole tiles of a gate|up pair)
-//   DK_EPI_PART       partial sums of a balanced matrix: the CTA that holds a tile's first unit writes part0[row], the
-//                     one that holds its last unit (when it is another CTA) part1[row]; a CTA that holds the whole tile
-//                     writes zeros to part1. The consumer adds x + part0 + part1 (convert_act).
+//   DK_EPI_PART       partial sums of a balanced matrix: the CTA that holds a tile's first unit writes vector 0, the
+//                     one that holds its last unit (when it is another CTA) vector 1 of this rank's pair in set `xset`;
+//                     a CTA that holds the whole tile writes zeros to vector 1. Stored on every tensor-parallel rank;
+//                     the consumer adds residual + all the vectors (convert_act).
+//   DK_EPI_LOGITS     y[v0 + row] = sum on every tensor-parallel rank (this rank's vocabulary rows of the head)
 __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf,
-                             int& rs, const PhaseSmem& s, unsigned* amax_out) {
+                             int& rs, const PhaseSmem& s, unsigned* amax_out, int xset = 0) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
     const WarpRange r = warp_range(m, warp);
     if (tid == 0) s.flags[3] = 0;
@@ -377,13 +457,28 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
                 }
             } else if (epi == DK_EPI_PART) {
                 const bool first = r.cA <= Xt * upt, last = r.cB >= (Xt + 1) * upt;
-                float* dst = first ? y : y + p.E;  // y = part0, part1 follows it
-                if (r0 < m.rows) dst[r0] = v0;
-                if (r1 < m.rows) dst[r1] = v1;
-                if (first && last) {
-                    if (r0 < m.rows) y[p.E + r0] = 0.f;
-                    if (r1 < m.rows) y[p.E + r1] = 0.f;
+                const size_t pair = (size_t(xset) * p.tp_size + p.tp_rank) * 2 * p.E;  // this rank's two vectors of the set
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {  // constant indices into the parameter arrays
+                    if (q >= p.tp_size) break;
+                    float* base = p.part_peer[q] + pair;
+                    float* dst = first ? base : base + p.E;
+                    if (r0 < m.rows) dst[r0] = v0;
+                    if (r1 < m.rows) dst[r1] = v1;
+                    if (first && last) {
+                        if (r0 < m.rows) base[p.E + r0] = 0.f;
+                        if (r1 < m.rows) base[p.E + r1] = 0.f;
+                    }
                 }
+                if (p.tp_size > 1) __threadfence_system();  // on the peers before this CTA arrives at the exchange barrier
+            } else if (epi == DK_EPI_LOGITS) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    if (q >= p.tp_size) break;
+                    if (r0 < m.rows) p.logits_peer[q][p.v0 + r0] = v0;
+                    if (r1 < m.rows) p.logits_peer[q][p.v0 + r1] = v1;
+                }
+                if (p.tp_size > 1) __threadfence_system();
             } else {
                 if (r0 < m.rows) y[r0] = v0;
                 if (r1 < m.rows) y[r1] = v1;
@@ -657,7 +752,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     int rs = 0;
     int* dead = &s.flags[2];
     const unsigned step = p.ctl[0], epoch = p.ctl[2];
-    unsigned nb = epoch * unsigned(1 + 5 * p.n_layer) * gridDim.x;  // arrivals before this launch
+    unsigned nb = epoch * unsigned(1 + 5 * p.n_layer + (p.tp_size > 1 ? 1 : 0)) * gridDim.x;  // arrivals before this launch
     unsigned* const amax_base = p.amax + (epoch & 1u) * 2 * p.n_layer;
     if (blockIdx.x == 0)  // the other half of the amax slots: untouched by this launch, zero for the next one
         for (int i = tid; i < 2 * p.n_layer; i += DK_THREADS) p.amax[((epoch + 1) & 1u) * 2 * p.n_layer + i] = 0u;
@@ -670,14 +765,20 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         for (int k = lo + tid; k < hi; k += DK_THREADS) {
             p.xbuf[k] = p.embd_type == ELB_F16 ? __half2float(reinterpret_cast<const __half*>(p.embd)[R * p.E + k])
                                                : elem_value(p.embd_type, tiled_elem(p.embd_type, p.embd, p.E, R, k));
-            p.part[k] = 0.f;
-            p.part[p.E + k] = 0.f;
         }
     }
     bool ok = grid_barrier(p, nb, dead);
     int cur = 0;  // which half of xbuf holds the residual stream (without the pending partial sums)
+    // exchanges (row-parallel matvec -> all ranks) are numbered from the first launch; number x uses set x & 1
+    unsigned xn = epoch * unsigned(2 * p.n_layer + 1);
+    float* my_part = nullptr;  // this rank's copy of the partial-sum sets
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+        if (q == p.tp_rank) my_part = p.part_peer[q];
+    int pending = -1;  // set whose partial sums the next residual conversion adds (-1: none yet in this launch)
     auto resid_step = [&](float* out) {
-        Resid r{p.xbuf + cur * p.E, p.part, p.part + p.E, out ? out : p.xbuf + (cur ^ 1) * p.E};
+        Resid r{p.xbuf + cur * p.E, pending < 0 ? nullptr : my_part + size_t(pending) * p.tp_size * 2 * p.E,
+                pending < 0 ? 0 : 2 * p.tp_size, out ? out : p.xbuf + (cur ^ 1) * p.E};
         cur ^= 1;
         return r;
     };
@@ -707,10 +808,12 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.H * DK_HD);
             const float inv = convert_act(p.att, nullptr, p.H * DK_HD, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8, sd_need(L.wo));
             dk_stamp(p, l, 6);
-            matvec_phase(p, L.wo, DK_EPI_PART, p.part, inv, pf, rs, s, nullptr);
+            matvec_phase(p, L.wo, DK_EPI_PART, nullptr, inv, pf, rs, s, nullptr, int(xn & 1u));
         }
         dk_stamp(p, l, 7);
-        if (!(ok = grid_barrier(p, nb, dead))) break;
+        if (!(ok = exchange_barrier(p, nb, xn, dead))) break;
+        pending = int(xn & 1u);
+        ++xn;
         dk_stamp(p, l, 8);
         {
             s.act = act_for(p.E);
@@ -726,17 +829,20 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(p.F);
             const float inv = convert_act(p.act, nullptr, p.F, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8, sd_need(L.down));
             dk_stamp(p, l, 12);
-            matvec_phase(p, L.down, DK_EPI_PART, p.part, inv, pf, rs, s, nullptr);
+            matvec_phase(p, L.down, DK_EPI_PART, nullptr, inv, pf, rs, s, nullptr, int(xn & 1u));
         }
         dk_stamp(p, l, 13);
-        ok = grid_barrier(p, nb, dead);
+        ok = exchange_barrier(p, nb, xn, dead);
+        pending = int(xn & 1u);
+        ++xn;
         dk_stamp(p, l, 14);
     }
     if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference); the last residual stream goes to p.x
         s.act = act_for(p.E);
         const Resid rs_ = resid_step(p.x);
         const float inv = convert_act(nullptr, &rs_, p.E, p.output_norm, p.eps, nullptr, 4, s.act, s.red8, sd_need(p.head));
-        matvec_phase(p, p.head, DK_EPI_STORE, p.logits, inv, pf, rs, s, nullptr);
+        matvec_phase(p, p.head, DK_EPI_LOGITS, nullptr, inv, pf, rs, s, nullptr);
+        if (p.tp_size > 1) exchange_barrier(p, nb, xn, dead);  // every rank's rows are in place on every rank
     }
     ring_wait<0>();
     if (blockIdx.x == 0 && tid == 0) {  // every CTA read ctl before its first barrier: safe to move on

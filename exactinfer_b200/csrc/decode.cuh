@@ -40,7 +40,17 @@ struct DkParams {
     const float* rope;      // [n_ctx][rope_dim/2][2]
     float *x, *qkv, *att, *act, *logits;
     float* xbuf;            // [2][E] residual stream, alternating: a conversion reads one and writes the other
-    float* part;            // [2][E] partial sums of the last row-parallel matvec (wo, down), added by the next conversion
+    // Partial sums of the row-parallel matvecs (attn_output, ffn_down), added by the next conversion. Two sets, used in
+    // turn by successive exchanges; a set holds, for every tensor-parallel rank, two vectors of E floats (the two
+    // contributors a row tile can have on that rank). part_peer[q] is rank q's copy as mapped into this process (peer
+    // memory; part_peer[tp_rank] is the local one): every rank stores its partial sums into its slot on ALL ranks, and
+    // after the exchange barrier every rank adds the same 2 * tp_size vectors in the same order.
+    int tp_rank, tp_size;   // 1 rank: a single GPU, the exchange barrier is the grid barrier
+    float* part_peer[8];    // [2 sets][tp_size][2][E]
+    unsigned* flag_peer[8]; // rank q's arrival flags [2 sets][8 ranks]
+    float* logits_peer[8];  // rank q's logits [n_vocab padded]: every rank stores its vocabulary rows on all ranks
+    int v0;                 // first vocabulary row of this rank
+    unsigned* xctl;         // local words: [0] exchanges so far, [1] release word of the exchange barrier
     unsigned* amax;         // [2][n_layer][2] bit patterns of max|att|, max|act| of each layer; launch e uses half e & 1
                             // (zero when it starts) and zeroes the other half for launch e + 1
     float* attn_part;       // [HKV][nsplit][group][130]

@@ -76,7 +76,10 @@ struct Model {
     DkParams dk{};
     DkLayer* dk_layers = nullptr;
     int dk_slot = 0, dk_grid = 0;
-    float* xbuf = nullptr;  // persistent kernel: residual stream [2][E], then partial sums [2][E]
+    float* xbuf = nullptr;  // persistent kernel: residual stream [2][E]
+    TpPeerBuf xarea;        // persistent kernel: flags, partial sums and logits, visible to all tensor-parallel ranks
+    unsigned* xctl = nullptr;
+    float* logits_step = nullptr;  // where a single-token step leaves its logits (m->logits unless the persistent kernel runs)
     unsigned* sync_words = nullptr;  // barrier counter, step index, advance flag, launch count, then 2 x [n_layer][2] amax slots
     int* pos_steps = nullptr;        // positions of a batch of single-token steps (persistent kernel)
     int* err_host = nullptr;         // pinned, mapped: raised by the kernel when a barrier wait runs out
@@ -375,7 +378,8 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
     }
     ELB_CUDA(cudaEventRecord(m->ev1, m->stream));
     if (logits)
-        ELB_CUDA(cudaMemcpyAsync(logits, m->logits, size_t(m->cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+        ELB_CUDA(cudaMemcpyAsync(logits, B == 1 && m->use_mega ? m->logits_step : m->logits, size_t(m->cfg.n_vocab) * sizeof(float),
+                                 cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
     if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
@@ -392,7 +396,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
 // shared memory (rings + the longest activation's limbs) fits on one SM. ELB_NO_MEGA=1 keeps the kernel-per-op path.
 int setup_decode_kernel(Model* m) {
     const elb_config& c = m->cfg;
-    if (env_on("ELB_NO_MEGA") || m->tp.size > 1) return ELB_OK;  // the one-kernel step has no exchange between GPUs
+    if (env_on("ELB_NO_MEGA") || (m->tp.size > 1 && env_on("ELB_TP_NO_MEGA"))) return ELB_OK;
     DeviceInfo di;
     ELB_TRY(device_info(m->device, &di));
     auto mat = [](const Weight* w) {  // alone in its phase, whole tiles per CTA
@@ -412,7 +416,14 @@ int setup_decode_kernel(Model* m) {
         quant = quant && L.qkv.size() == nq && L.wo->type != ELB_F16 && L.gu->type != ELB_F16 && L.down->type != ELB_F16;
         for (auto& s : L.qkv) quant = quant && s.w->type != ELB_F16;
     }
-    const int E = c.n_embd, F = c.n_ff, QD = c.n_head * 128, KD = c.n_head_kv * 128;
+    // this rank's dimensions; the longest FFN cut of any rank sizes the shared memory, so that all ranks decide alike
+    int Fmax = int(m->F);
+    for (int r = 0; r < m->tp.size; ++r) {
+        TpDims d;
+        ELB_TRY(tp_dims(c, r, m->tp.size, &d));
+        Fmax = std::max(Fmax, int(d.f1 - d.f0));
+    }
+    const int E = c.n_embd, F = int(m->F), QD = m->H * 128, KD = m->HKV * 128;
     if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 5 * 4 * decode_threads()) return ELB_OK;
     DkParams& p = m->dk;
     p = DkParams{};
@@ -449,7 +460,23 @@ int setup_decode_kernel(Model* m) {
     }
     ELB_CUDA(cudaMalloc(&m->dk_layers, hl.size() * sizeof(DkLayer)));
     ELB_CUDA(cudaMemcpy(m->dk_layers, hl.data(), hl.size() * sizeof(DkLayer), cudaMemcpyHostToDevice));
-    ELB_CUDA(cudaMalloc(&m->xbuf, size_t(4) * E * sizeof(float)));  // residual stream [2][E], partial sums [2][E]
+    ELB_CUDA(cudaMalloc(&m->xbuf, size_t(2) * E * sizeof(float)));  // residual stream [2][E]
+    // exchange area: flags, partial sums [2 sets][ranks][2][E], logits; mapped into every rank under tensor parallelism
+    const int N = m->tp.size;
+    const size_t part_floats = size_t(2) * N * 2 * E, logit_floats = size_t(std::max<int64_t>(c.n_vocab, m->tp.vchunk * N));
+    const size_t xbytes = 256 + (part_floats + logit_floats) * sizeof(float);
+    if (N > 1) {
+        bool mapped = false;
+        ELB_TRY(tp_peer_alloc(m->comm, m->device, xbytes, m->stream, &m->xarea, &mapped));
+        if (!mapped) return ELB_OK;  // no peer mapping: the kernel-per-op path with NCCL stays
+    } else {
+        ELB_CUDA(cudaMalloc(&m->xarea.local, xbytes));
+        ELB_CUDA(cudaMemset(m->xarea.local, 0, xbytes));
+        m->xarea.peer[0] = m->xarea.local;
+        m->xarea.size = 1;
+    }
+    ELB_CUDA(cudaMalloc(&m->xctl, 2 * sizeof(unsigned)));
+    ELB_CUDA(cudaMemset(m->xctl, 0, 2 * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->sync_words, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->sync_words, 0, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->pos_steps, size_t(m->max_batch) * sizeof(int)));
@@ -460,26 +487,38 @@ int setup_decode_kernel(Model* m) {
     p.layers = m->dk_layers; p.n_layer = c.n_layer; p.n_qkv = int(nq);
     p.head = mat(m->head); p.output_norm = m->output_norm;
     p.embd = m->embd->tiled; p.embd_type = m->embd->type;
-    p.E = E; p.F = F; p.H = c.n_head; p.HKV = c.n_head_kv; p.rope_dim = c.rope_dim; p.n_ctx = m->n_ctx;
-    p.nsplit = std::max(1, std::min({32, m->attn_split, di.sm_count / c.n_head_kv}));
+    p.E = E; p.F = F; p.H = m->H; p.HKV = m->HKV; p.rope_dim = c.rope_dim; p.n_ctx = m->n_ctx;
+    p.nsplit = std::max(1, std::min({32, m->attn_split, di.sm_count / m->HKV}));
+    p.tp_rank = m->tp.rank; p.tp_size = N; p.v0 = int(m->tp.v0); p.xctl = m->xctl;
+    for (int q = 0; q < N; ++q) {
+        uint8_t* base = static_cast<uint8_t*>(m->xarea.peer[q]);
+        p.flag_peer[q] = reinterpret_cast<unsigned*>(base);
+        p.part_peer[q] = reinterpret_cast<float*>(base + 256);
+        p.logits_peer[q] = p.part_peer[q] + part_floats;
+    }
     p.eps = c.eps; p.scale = 1.0f / std::sqrt(float(c.head_dim));
     p.nl_qkv = m->nl_qkv; p.nl_wo = m->nl_wo; p.nl_gu = m->nl_gu; p.nl_down = m->nl_down;
     p.token = m->tokens_dev; p.pos = m->pos_steps; p.rope = m->rope;
     p.x = m->x; p.qkv = m->qkv; p.att = m->att; p.act = m->act; p.logits = m->logits;
-    p.xbuf = m->xbuf; p.part = m->xbuf + 2 * E; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
+    p.xbuf = m->xbuf; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
     p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
-    p.err = err_dev; p.slots = slots; p.n_max = std::max({E, F, QD});
+    p.err = err_dev; p.slots = slots; p.n_max = std::max({E, Fmax, QD});
     m->dk_slot = (slot + 15) / 16 * 16;
     m->dk_grid = di.sm_count;
     // 32-bit unit arithmetic in the kernel
+    bool small = true;
     for (int l = 0; l < c.n_layer; ++l)
         for (const Weight* w : {m->layers[size_t(l)].wo, m->layers[size_t(l)].gu, m->layers[size_t(l)].down, m->head})
-            if (w->tiles * w->units_per_tile * int64_t(di.sm_count) >= (int64_t(1) << 31) || w->max_grid < di.sm_count) return ELB_OK;
+            if (w->tiles * w->units_per_tile * int64_t(di.sm_count) >= (int64_t(1) << 31) || w->max_grid < di.sm_count) small = false;
     bool fits = false;
     ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+    fits = fits && small;
     int coop = 0;
     ELB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
-    m->use_mega = fits && coop;
+    bool all = false;  // under tensor parallelism every rank must take the same path: its kernels wait for the peers'
+    ELB_TRY(tp_agree(m->comm, fits && coop, m->stream, &all));
+    m->use_mega = all;
+    if (m->use_mega) m->logits_step = p.logits_peer[m->tp.rank];  // the kernel leaves the logits in the exchange area
     if (m->use_mega && env_on("ELB_DK_PROF")) {
         ELB_CUDA(cudaMalloc(&p.prof, size_t(c.n_layer) * 32 * sizeof(unsigned long long)));
         ELB_CUDA(cudaMemset(p.prof, 0, size_t(c.n_layer) * 32 * sizeof(unsigned long long)));
@@ -558,7 +597,8 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->sync_words); cudaFree(m->pos_steps);
+    cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl);
+    if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);

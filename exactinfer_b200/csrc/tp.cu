@@ -242,6 +242,22 @@ int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf
     return ELB_OK;
 }
 
+// true on every rank only when `mine` is true on every rank (collective; one rank: its own answer)
+int tp_agree(TpComm* c, bool mine, cudaStream_t s, bool* all) {
+    *all = mine;
+    if (!c || c->size < 2) return ELB_OK;
+    float flag = mine ? 0.f : 1.f, *d_flag = nullptr;
+    ELB_CUDA(cudaMalloc(&d_flag, sizeof(float)));
+    ELB_CUDA(cudaMemcpyAsync(d_flag, &flag, sizeof(float), cudaMemcpyHostToDevice, s));
+    const ncclResult_t r = nccl()->AllReduce(d_flag, d_flag, 1, ncclFloat, ncclSum, c->comm, s);
+    if (r != ncclSuccess) { cudaFree(d_flag); return nccl_fail(nccl(), r, "ncclAllReduce (agreement)"); }
+    ELB_CUDA(cudaMemcpyAsync(&flag, d_flag, sizeof(float), cudaMemcpyDeviceToHost, s));
+    ELB_CUDA(cudaStreamSynchronize(s));
+    cudaFree(d_flag);
+    *all = flag == 0.f;
+    return ELB_OK;
+}
+
 void tp_peer_free(TpPeerBuf* b, int rank) {
     if (!b) return;
     for (int p = 0; p < b->size; ++p)
