@@ -341,8 +341,9 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": workload_name(spec, K),
                    "parallelism": "single GPU" if world == 1 else
-                   f"tp{world}: heads and FFN columns cut over {world} GPUs, NCCL all-reduce after attn_output and "
-                   "ffn_down, all-gather of the logits",
+                   f"tp{world}: heads and FFN columns cut over {world} GPUs; decode: one persistent kernel per rank, partial "
+                   "sums of attn_output and ffn_down and the logits rows exchanged through peer memory (kernel-per-op with "
+                   "a peer-memory all-reduce when the step does not fit the kernel); prompt chunks: NCCL all-reduce",
                    "l2": "inputs larger than L2: every step streams all weights (GBs) from HBM",
                    "seed": SEED, "tokens": "reference LCG stream, seed 12345",
                    "weights": "two sets of random blocks shared by the layers of equal parity" if big_model(spec)

@@ -76,39 +76,33 @@ __device__ __forceinline__ void st_release_gpu(unsigned* p, unsigned v) {
 }
 
 // Barrier over the CTAs of ALL tensor-parallel ranks: exchange number x (counted from the first launch, the same on
-// every rank) is complete when every rank's CTAs have arrived. CTA 0 waits for the local arrivals, raises this rank's
-// flag of set x & 1 on every peer (system-scope release: the partial sums the local CTAs stored to the peers, each
-// followed by a system fence, are visible before it), waits for the peers' flags, then releases the local CTAs through
-// a local word. One rank: the grid barrier. All waits bounded.
+// every rank) is complete when every rank's CTAs have arrived. Every CTA waits for the local arrivals; CTA 0 then raises
+// this rank's flag of set x & 1 on every peer (system-scope release: the partial sums the local CTAs stored to the
+// peers, each followed by a system fence, are visible before it); every CTA waits for the peers' flags in its own
+// rank's flag words. One rank: the grid barrier. All waits bounded.
 __device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& target, unsigned x, int* s_dead) {
     if (p.tp_size == 1) return grid_barrier(p, target, s_dead);
     __syncthreads();
     if (threadIdx.x == 0 && !*s_dead) {
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");
         target += gridDim.x;
+        const int set = int(x & 1u);
         unsigned it = 0;
         bool dead = false;
-        if (blockIdx.x == 0) {
-            while (!dead && int(ld_acquire(p.bar) - target) < 0)
-                if (++it > DK_SPIN_LIMIT) dead = true; else if (it > 2048) __nanosleep(64);
-            const int set = int(x & 1u);
-            unsigned* mine = nullptr;  // this rank's flag words
+        while (!dead && int(ld_acquire(p.bar) - target) < 0)  // the local CTAs
+            if (++it > DK_SPIN_LIMIT) dead = true; else if (it > 2048) __nanosleep(64);
+        unsigned* mine = nullptr;  // this rank's flag words
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                if (q >= p.tp_size) break;
-                if (q == p.tp_rank) mine = p.flag_peer[q];
-                else if (!dead) st_release_sys(p.flag_peer[q] + set * 8 + p.tp_rank, x + 1);
-            }
-            for (int q = 0; q < p.tp_size && !dead; ++q) {
-                if (q == p.tp_rank) continue;
-                it = 0;
-                while (!dead && ld_acquire_sys(mine + set * 8 + q) != x + 1)
-                    if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 64) __nanosleep(100);
-            }
-            if (!dead) st_release_gpu(p.xctl + 1, x + 1);
-        } else {
-            while (!dead && int(ld_acquire(p.xctl + 1) - (x + 1)) < 0)
-                if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 2048) __nanosleep(100);
+        for (int q = 0; q < 8; ++q) {  // constant indices into the parameter arrays
+            if (q >= p.tp_size) break;
+            if (q == p.tp_rank) mine = p.flag_peer[q];
+            else if (!dead && blockIdx.x == 0) st_release_sys(p.flag_peer[q] + set * 8 + p.tp_rank, x + 1);
+        }
+        for (int q = 0; q < p.tp_size && !dead; ++q) {  // every CTA watches the peers' flags itself: no second hop
+            if (q == p.tp_rank) continue;
+            it = 0;
+            while (!dead && ld_acquire_sys(mine + set * 8 + q) != x + 1)
+                if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 256) __nanosleep(100);
         }
         if (dead) {
             *s_dead = 1;
