@@ -11,10 +11,93 @@ namespace elb {
 
 // ---------------------------------------------------------------- limb split (k_split8 of the reference)
 
+// One block per row. The row stays in registers (float4 j * 256 + tid of the row, up to SR_V4 * 1024 values); longer
+// rows take the general kernel below.
+constexpr int SR_V4 = 10;
+
 __global__ void __launch_bounds__(256) k_split_rows(const float* __restrict__ X, int64_t ldx, int n, int nl,
                                                     const float* __restrict__ norm_w, float eps, int8_t* __restrict__ limbs,
                                                     int64_t limb_stride, float* __restrict__ inv_scale,
                                                     float* __restrict__ xsum) {
+    __shared__ double red8[8];
+    __shared__ float redf[8];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int64_t b = blockIdx.x;
+    const float* x = X + b * ldx;
+    float4 v[SR_V4];
+#pragma unroll
+    for (int j = 0; j < SR_V4; ++j) {
+        const int idx = (j * 256 + tid) * 4;
+        v[j] = idx < n ? *reinterpret_cast<const float4*>(x + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (norm_w) {
+        double ss = 0.0;
+#pragma unroll
+        for (int j = 0; j < SR_V4; ++j)
+            ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
+        ss = warp_sum(ss);
+        if (lane == 0) red8[tid >> 5] = ss;
+        __syncthreads();
+        ss = 0.0;
+        for (int i = 0; i < 8; ++i) ss += red8[i];
+        const float inv = float(1.0 / sqrt(ss / n + double(eps)));
+#pragma unroll
+        for (int j = 0; j < SR_V4; ++j) {
+            const int idx = (j * 256 + tid) * 4;
+            if (idx < n) {
+                const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w + idx));
+                v[j] = make_float4(__fmul_rn(__fmul_rn(v[j].x, inv), w.x), __fmul_rn(__fmul_rn(v[j].y, inv), w.y),
+                                   __fmul_rn(__fmul_rn(v[j].z, inv), w.z), __fmul_rn(__fmul_rn(v[j].w, inv), w.w));
+            }
+        }
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < SR_V4; ++j) m = fmaxf(m, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+    m = warp_max(m);
+    if (lane == 0) redf[tid >> 5] = m;
+    __syncthreads();
+    m = redf[0];
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, redf[i]);
+    int e = 0;
+    if (m > 0.f) frexpf(m, &e);
+    const int k = m > 0.f ? 8 * nl - 2 - e : 0;
+    int8_t* out = limbs + b * n;
+    const Pow2 sc = make_pow2(k);
+#pragma unroll
+    for (int j = 0; j < SR_V4; ++j) {
+        if (j * 1024 >= n) break;  // warp-uniform: n is a multiple of 32, so a warp's 128 values are all inside or all outside
+        const int idx = (j * 256 + tid) * 4;
+        const bool valid = idx < n;
+        const int i0 = __float2int_rn(v[j].x * sc.s1 * sc.s2), i1 = __float2int_rn(v[j].y * sc.s1 * sc.s2);
+        const int i2 = __float2int_rn(v[j].z * sc.s1 * sc.s2), i3 = __float2int_rn(v[j].w * sc.s1 * sc.s2);
+        // balanced digits of one value = bytes of (v + 0x80808080) ^ 0x80808080; a 4x4 byte transpose groups them by limb
+        const uint32_t a = (uint32_t(i0) + 0x80808080u) ^ 0x80808080u, bb = (uint32_t(i1) + 0x80808080u) ^ 0x80808080u;
+        const uint32_t c = (uint32_t(i2) + 0x80808080u) ^ 0x80808080u, d = (uint32_t(i3) + 0x80808080u) ^ 0x80808080u;
+        const uint32_t ab01 = __byte_perm(a, bb, 0x5140), ab23 = __byte_perm(a, bb, 0x7362);
+        const uint32_t cd01 = __byte_perm(c, d, 0x5140), cd23 = __byte_perm(c, d, 0x7362);
+        if (valid) {
+            *reinterpret_cast<uint32_t*>(out + idx) = __byte_perm(ab01, cd01, 0x5410);
+            *reinterpret_cast<uint32_t*>(out + limb_stride + idx) = __byte_perm(ab01, cd01, 0x7632);
+            *reinterpret_cast<uint32_t*>(out + 2 * limb_stride + idx) = __byte_perm(ab23, cd23, 0x5410);
+            *reinterpret_cast<uint32_t*>(out + 3 * limb_stride + idx) = __byte_perm(ab23, cd23, 0x7632);
+        }
+        if (xsum) {  // sum of the fixed-point values over each 32-slice (8 lanes), exact in 64 bits, rounded once
+            long long sum = (long long)i0 + i1 + i2 + i3;
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            if (valid && (lane & 7) == 0) xsum[b * (n / 32) + (idx >> 5)] = float(sum);
+        }
+    }
+    if (tid == 0) inv_scale[b] = ldexpf(1.0f, -k);
+}
+
+// rows longer than SR_V4 * 1024 values: passes over global memory
+__global__ void __launch_bounds__(256) k_split_rows_long(const float* __restrict__ X, int64_t ldx, int n, int nl,
+                                                         const float* __restrict__ norm_w, float eps, int8_t* __restrict__ limbs,
+                                                         int64_t limb_stride, float* __restrict__ inv_scale,
+                                                         float* __restrict__ xsum) {
     __shared__ double red8[8];
     __shared__ float redf[8];
     const int tid = threadIdx.x;
@@ -67,7 +150,10 @@ __global__ void __launch_bounds__(256) k_split_rows(const float* __restrict__ X,
 int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const float* d_norm_w, float eps,
                  int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s) {
     if (nl < 2 || nl > 4) return fail(ELB_ERR_INVALID, "split: limb count must be 2, 3 or 4");
-    k_split_rows<<<unsigned(b), 256, 0, s>>>(d_x, ldx, n, nl, d_norm_w, eps, d_limbs, b * int64_t(n), d_inv_scale, d_xsum);
+    const bool fast = n <= SR_V4 * 1024 && n % 32 == 0 && ldx % 4 == 0 && (b * int64_t(n)) % 4 == 0 &&
+                      reinterpret_cast<uintptr_t>(d_x) % 16 == 0 && (!d_norm_w || reinterpret_cast<uintptr_t>(d_norm_w) % 16 == 0);
+    if (fast) k_split_rows<<<unsigned(b), 256, 0, s>>>(d_x, ldx, n, nl, d_norm_w, eps, d_limbs, b * int64_t(n), d_inv_scale, d_xsum);
+    else k_split_rows_long<<<unsigned(b), 256, 0, s>>>(d_x, ldx, n, nl, d_norm_w, eps, d_limbs, b * int64_t(n), d_inv_scale, d_xsum);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }
