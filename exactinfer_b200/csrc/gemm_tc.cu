@@ -123,6 +123,10 @@ __host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
 
 // ---------------------------------------------------------------- the kernel
 
+// diagnostics (ELB_TC_PROF=1): clock cycles the MMA issuer of CTA 0 spent waiting for a drained accumulator, waiting for
+// operands, and in total, summed over launches
+__device__ unsigned long long g_tc_prof[12];
+
 struct TcParams {
     const __half* pl_d;      // [rows16][n/256] block scale
     const float* pl_dm;      // Q4_K: [rows16][n/32] fl(dmin*m); else null
@@ -134,6 +138,7 @@ struct TcParams {
     int B, n, epilogue;
     int row_tiles, tok_tiles;  // the grid walks row_tiles * tok_tiles output tiles, token tiles of one row tile adjacent
     int* err;
+    int prof;
 };
 
 template <int NL> struct TcShape {
@@ -144,7 +149,8 @@ template <int NL> struct TcShape {
     static constexpr int A_BYTES = TC_ROWS * 128;     // one plane tile of one stage
     static constexpr int LIMB_AREA = ZB + TC_STAGES * (LB + ZB);
     static constexpr int XS_BYTES = 2 * T * 8 * 4;    // sum(X) of the tile's tokens over the 8 sub-blocks of a block, x2
-    static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + XS_BYTES + 1024;  // + barriers + slack
+    static constexpr int SC_BYTES = 2 * TC_ROWS * 9 * 4;  // fl(dmin*m) [8] and d of the tile's rows for one block, x2
+    static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + XS_BYTES + SC_BYTES + 1024;  // + barriers + slack
 };
 
 template <int NL>
@@ -163,6 +169,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     uint64_t* tempty = tfull + 2;            // [2] epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     float* xs_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [2][T][8]
+    float* dm_s = xs_s + 2 * T * 8;            // [2][TC_ROWS][8]
+    float* d_s = dm_s + 2 * TC_ROWS * 8;       // [2][TC_ROWS]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nk = p.n / TC_KSTAGE, nkb = p.n / 256, n_tiles = p.row_tiles * p.tok_tiles;
@@ -207,15 +215,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
         if (lane == 0) {  // ---- MMA issuer
             constexpr uint32_t idesc = idesc_i8(TC_ROWS, N);
             int it = 0;
+            long long w_acc = 0, w_ops = 0;
+            const long long t_start = clock64();
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x)
             for (int kt = 0; kt < nk && ok; ++kt, ++it) {
                 const int s = it % TC_STAGES, kb = it >> 1, acc = kb & 1;  // kb: 256-blocks issued so far (nk is even)
+                long long t0 = clock64();
                 if ((kt & 1) == 0) {  // first half of a 256-block: its accumulator must have been drained
                     ok = mbar_wait(tempty + acc, ((kb >> 1) & 1) ^ 1);
                     if (!ok) break;
                 }
+                long long t1 = clock64();
                 ok = mbar_wait(full + s, (it / TC_STAGES) & 1);
                 if (!ok) break;
+                w_acc += t1 - t0;
+                w_ops += clock64() - t1;
                 tc_fence_after();
                 const uint32_t a0 = smem_u32(a_area + (s * 2 + 0) * S::A_BYTES), a1 = a0 + S::A_BYTES;
                 const uint32_t b0 = smem_u32(limb_area + S::ZB + s * (S::LB + S::ZB)), b1 = b0 - S::ZB;
@@ -228,96 +242,111 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 mma_commit(empty + s);                    // the stage is free once these MMAs have read it
                 if (kt & 1) mma_commit(tfull + acc);      // the 256-block is complete
             }
+            if (p.prof && blockIdx.x == 0) {
+                atomicAdd(&g_tc_prof[0], (unsigned long long)w_acc);
+                atomicAdd(&g_tc_prof[1], (unsigned long long)w_ops);
+                atomicAdd(&g_tc_prof[2], (unsigned long long)(clock64() - t_start));
+                atomicAdd(&g_tc_prof[3], 1ull);
+            }
         }
     } else {  // ---- epilogue: warp w drains TMEM lanes 32(w%4).. (weight rows) for tokens [th*TH, (th+1)*TH), th = w/4
         constexpr int TH = T / TC_TOK_PARTS;  // tokens per epilogue warp
         static_assert(TH % 4 == 0, "token share of an epilogue warp is loaded four columns at a time");
         constexpr int XPT = (T * 8 + TC_EPI_WARPS * 32 - 1) / (TC_EPI_WARPS * 32);  // sum(X) values staged per thread
+        static_assert(TC_EPI_WARPS * 32 >= 3 * TC_ROWS, "one scale value per staging thread");
         const int etid = warp * 32 + lane;
-        const int q4 = warp & 3, th = warp >> 2;
+        const int q4 = warp & 3, th = warp >> 2, my_row = q4 * 32 + lane;
         const int nblk = p.n / 256, nsub = p.n / 32;
         int kbt = 0;  // 256-blocks drained so far, over all tiles of this CTA
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const int row0 = tile / p.tok_tiles * TC_ROWS, tok0 = tile % p.tok_tiles * T;
-        const int64_t R = row0 + q4 * 32 + lane;
-        const bool row_ok = R < p.rows16;
+        const int64_t R = row0 + my_row;
         float accf[TH];
 #pragma unroll
         for (int t = 0; t < TH; ++t) accf[t] = 0.f;
-        // block scale and the dmin*m row of the first block; the next block's are fetched while this one is drained
-        float d = row_ok ? __half2float(p.pl_d[R * nblk]) : 0.f;
-        float4 dm0 = make_float4(0.f, 0.f, 0.f, 0.f), dm1 = dm0;
-        if (p.pl_dm && row_ok) {
-            dm0 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub));
-            dm1 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + 4));
-        }
-        // sum(X) of a block for the tile's tokens is staged through shared memory by all epilogue warps; the values of
-        // the next block are fetched while this one is drained
+        // Per 256-block the epilogue needs the block scale d and (Q4_K) the eight fl(dmin*m) of every row of the tile and
+        // sum(X) over the eight 32-slices of every token of the tile. Thread = weight row would make those loads one
+        // cache line per lane; instead all epilogue threads fetch them together (two threads per row for dmin*m, one
+        // per row for d, the rest sum(X)), one block ahead, and pass them on through shared memory.
         float xreg[XPT];
-        auto fetch_xsum = [&](int kb) {
+        float4 screg = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto fetch = [&](int kb) {
 #pragma unroll
             for (int q = 0; q < XPT; ++q) {
                 const int i = etid + q * TC_EPI_WARPS * 32;
                 const int tok = min(tok0 + (i >> 3), p.B - 1);
-                xreg[q] = i < T * 8 ? __ldg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7)) : 0.f;
+                xreg[q] = p.pl_dm && i < T * 8 ? __ldg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7)) : 0.f;
+            }
+            if (etid < 2 * TC_ROWS) {
+                const int64_t r = row0 + (etid >> 1);
+                screg = p.pl_dm && r < p.rows16 ? __ldg(reinterpret_cast<const float4*>(p.pl_dm + r * nsub + kb * 8 + 4 * (etid & 1)))
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+            } else if (etid < 3 * TC_ROWS) {
+                const int64_t r = row0 + etid - 2 * TC_ROWS;
+                screg.x = r < p.rows16 ? __half2float(p.pl_d[r * nblk + kb]) : 0.f;
             }
         };
-        if (p.pl_dm) fetch_xsum(0);
+        fetch(0);
         for (int kb = 0; kb < nkb && ok; ++kb, ++kbt) {
             const int acc = kbt & 1;
-            float d_next = 0.f;
-            float4 dn0 = make_float4(0.f, 0.f, 0.f, 0.f), dn1 = dn0;
-            if (kb + 1 < nkb && row_ok) {
-                d_next = __half2float(p.pl_d[R * nblk + kb + 1]);
-                if (p.pl_dm) {
-                    dn0 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + (kb + 1) * 8));
-                    dn1 = __ldg(reinterpret_cast<const float4*>(p.pl_dm + R * nsub + (kb + 1) * 8 + 4));
-                }
-            }
-            if (p.pl_dm) {
-                float* xb = xs_s + acc * (T * 8);
+            float* xb = xs_s + acc * (T * 8);
+            float* dmb = dm_s + acc * (TC_ROWS * 8);
+            float* db = d_s + acc * TC_ROWS;
 #pragma unroll
-                for (int q = 0; q < XPT; ++q) {
-                    const int i = etid + q * TC_EPI_WARPS * 32;
-                    if (i < T * 8) xb[i] = xreg[q];
-                }
-                if (kb + 1 < nkb) fetch_xsum(kb + 1);
-                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");  // epilogue warps only
+            for (int q = 0; q < XPT; ++q) {
+                const int i = etid + q * TC_EPI_WARPS * 32;
+                if (i < T * 8) xb[i] = xreg[q];
             }
+            if (etid < 2 * TC_ROWS) *reinterpret_cast<float4*>(dmb + etid * 4) = screg;
+            else if (etid < 3 * TC_ROWS) db[etid - 2 * TC_ROWS] = screg.x;
+            if (kb + 1 < nkb) fetch(kb + 1);
+            asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");  // epilogue warps only
+            // Q4_K: minus sum over the 8 sub-blocks of fl(dmin*m) * sum(X). It does not need the accumulator: it runs
+            // while the tensor core is still working on this block.
+            if (p.pl_dm) {
+                const float4 dm0 = *reinterpret_cast<const float4*>(dmb + my_row * 8), dm1 = *reinterpret_cast<const float4*>(dmb + my_row * 8 + 4);
+                const float* xt = xb + th * TH * 8;
+#pragma unroll
+                for (int t = 0; t < TH; t += 2) {
+                    const float4 xa0 = *reinterpret_cast<const float4*>(xt + t * 8), xa1 = *reinterpret_cast<const float4*>(xt + t * 8 + 4);
+                    const float4 xc0 = *reinterpret_cast<const float4*>(xt + t * 8 + 8), xc1 = *reinterpret_cast<const float4*>(xt + t * 8 + 12);
+                    float sa = dm0.x * xa0.x, sc = dm0.x * xc0.x;
+                    sa = fmaf(dm0.y, xa0.y, sa); sc = fmaf(dm0.y, xc0.y, sc);
+                    sa = fmaf(dm0.z, xa0.z, sa); sc = fmaf(dm0.z, xc0.z, sc);
+                    sa = fmaf(dm0.w, xa0.w, sa); sc = fmaf(dm0.w, xc0.w, sc);
+                    sa = fmaf(dm1.x, xa1.x, sa); sc = fmaf(dm1.x, xc1.x, sc);
+                    sa = fmaf(dm1.y, xa1.y, sa); sc = fmaf(dm1.y, xc1.y, sc);
+                    sa = fmaf(dm1.z, xa1.z, sa); sc = fmaf(dm1.z, xc1.z, sc);
+                    sa = fmaf(dm1.w, xa1.w, sa); sc = fmaf(dm1.w, xc1.w, sc);
+                    accf[t] -= sa;
+                    accf[t + 1] -= sc;
+                }
+            }
+            const float d = db[my_row];
             ok = mbar_wait(tfull + acc, (kbt >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const uint32_t tbase = tmem_base + acc * 256 + (uint32_t(q4 * 32) << 16) + th * TH;
-            {
-                int v[NL + 1][TH];  // every load of the drain is issued before the one wait
+            int v[NL + 1][TH];  // every load of the drain is issued before the one wait
 #pragma unroll
-                for (int c = 0; c < TH / 4; ++c)
+            for (int c = 0; c < TH / 4; ++c)
 #pragma unroll
-                    for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + c * 4, *reinterpret_cast<int (*)[4]>(&v[j][c * 4]));
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty + acc);  // accumulator in registers: the issuer may overwrite it
+                for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + c * 4, *reinterpret_cast<int (*)[4]>(&v[j][c * 4]));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty + acc);  // accumulator in registers: the issuer may overwrite it
+            // sum_j 256^j v_j with few int->float conversions: neighbouring columns are joined in int32 first
+            // (|v_j| < 2^23, so v_j + 256 v_{j+1} fits), as the reference joins its limb pairs (I0 = P0 + 256 P1,
+            // src/cuda/model_cuda.cu:962-994); the top column of four limbs is small enough for the exact
+            // add-a-constant conversion
 #pragma unroll
-                for (int t = 0; t < TH; ++t) {
-                    float f = float(v[NL][t]);
-#pragma unroll
-                    for (int j = NL - 1; j >= 0; --j) f = fmaf(f, 256.0f, float(v[j][t]));
-                    accf[t] = fmaf(d, f, accf[t]);
-                }
+            for (int t = 0; t < TH; ++t) {
+                const int i01 = v[0][t] + (v[1][t] << 8), i23 = v[2][t] + (v[3][t] << 8);
+                float f = NL == 4 ? fmaf(i2f_small(v[4][t]), 65536.0f, float(i23)) : float(i23);
+                f = fmaf(f, 65536.0f, float(i01));
+                accf[t] = fmaf(d, f, accf[t]);
             }
-            if (p.pl_dm) {  // Q4_K: minus sum over the 8 sub-blocks of fl(dmin*m) * sum(X)
-                const float* xb = xs_s + acc * (T * 8) + th * TH * 8;
-#pragma unroll
-                for (int t = 0; t < TH; ++t) {
-                    const float4 x0 = *reinterpret_cast<const float4*>(xb + t * 8), x1 = *reinterpret_cast<const float4*>(xb + t * 8 + 4);
-                    float s = dm0.x * x0.x;
-                    s = fmaf(dm0.y, x0.y, s); s = fmaf(dm0.z, x0.z, s); s = fmaf(dm0.w, x0.w, s);
-                    s = fmaf(dm1.x, x1.x, s); s = fmaf(dm1.y, x1.y, s); s = fmaf(dm1.z, x1.z, s); s = fmaf(dm1.w, x1.w, s);
-                    accf[t] -= s;
-                }
-            }
-            d = d_next; dm0 = dn0; dm1 = dn1;
         }
         if (ok) {
 #pragma unroll
@@ -390,12 +419,23 @@ int* error_word() {  // pinned, mapped: raised by a kernel whose bounded wait ra
 
 }  // namespace
 
+static bool tc_prof_on() {
+    static const bool on = [] { const char* v = std::getenv("ELB_TC_PROF"); return v && v[0] == '1'; }();
+    return on;
+}
+
 bool gemm_tc_usable(const Weight* w, int B) {
     static const bool off = [] { const char* v = std::getenv("ELB_NO_TC"); return v && v[0] == '1'; }();
     return !off && w->planes && w->n_planes == 2 && w->n % 256 == 0 && w->n % 16 == 0 && B >= 16 && encode_fn() != nullptr;
 }
 
 int gemm_tc_check() {  // after a synchronize: did a tensor-core GEMM give up on a wait?
+    if (tc_prof_on()) {
+        unsigned long long h[12] = {};
+        if (cudaMemcpyFromSymbol(h, g_tc_prof, sizeof h) == cudaSuccess && h[3])
+            std::fprintf(stderr, "[tc prof] launches %llu: MMA issuer of CTA 0 waited %.1f%% for accumulators, %.1f%% for operands\n", h[3],
+                         100.0 * double(h[0]) / double(h[2]), 100.0 * double(h[1]) / double(h[2]));
+    }
     int* e = error_word();
     if (e && *e) {
         *e = 0;
@@ -419,7 +459,7 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
     ELB_TRY(make_map(&mapX, d_limbs, uint64_t(w->n), uint64_t(B), 4, uint32_t(T)));
     const int row_tiles = int((rows16 + TC_ROWS - 1) / TC_ROWS), tok_tiles = (B + T - 1) / T;
     TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
-               row_tiles, tok_tiles, err_dev};
+               row_tiles, tok_tiles, err_dev, tc_prof_on() ? 1 : 0};
     DeviceInfo di;
     ELB_TRY(device_info(w->device, &di));
     const dim3 grid(unsigned(std::min(row_tiles * tok_tiles, di.sm_count)));  // persistent: one CTA per SM walks the tiles
