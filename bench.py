@@ -37,16 +37,16 @@ MICRO_ROWS, MICRO_N = 2560, 9728
 MICRO_BYTES = MICRO_ROWS * (MICRO_N // 256) * 144  # 14 008 320 algorithmic bytes per matvec
 INT8_PEAK_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-MICRO_TRAFFIC = 14_121_643  # profiles/k_gemv_q4_k_2560x9728_microbench.txt (mean of 3 launches)
+MICRO_TRAFFIC = 14_121_301  # profiles/k_gemv_q4_k_2560x9728_microbench.txt (mean of 3 launches)
 
 
 def decode_traffic(spec):
     """DRAM bytes per k_decode_step launch, scaled per layer from the 4- and 8-layer ncu captures of the 4B shape
-    (profiles/k_decode_step_qwen3-4b-q4_k_m_4_and_8_layers.txt): 322.4 MB for head, embedding row and fixed part,
-    65.23 MB per layer at positions ~517. None for shapes that were not captured."""
+    (profiles/k_decode_step_qwen3-4b-q4_k_m_4_and_8_layers.txt): 321.7 MB for head, embedding row and fixed part,
+    65.1 MB per layer at positions ~517. None for shapes that were not captured."""
     if spec.name != "qwen3-4b-q4_k_m":
         return None
-    return 322.4e6 + 65.23e6 * spec.n_layer
+    return 321.7e6 + 65.1e6 * spec.n_layer
 
 
 def metric_name(spec):
