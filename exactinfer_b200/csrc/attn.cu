@@ -7,6 +7,7 @@
 //   k_attn_prefill  prompt chunk: causal tiled attention, 32 queries of one head per CTA, online softmax.
 // Semantics follow CpuModel::forward of the reference (src/model.cpp:176-214): scale = 1/sqrt(float(D)), scores
 // accumulated in dimension order without FMA contraction, max-subtracted softmax.
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 
@@ -334,21 +335,40 @@ __global__ void __launch_bounds__(AP_THREADS) k_attn_prefill(const float* __rest
 // Prompt chunk, all query heads of one KV head together: a CTA holds 64 query rows (group heads x 64/group tokens), so
 // every K/V tile is loaded once for the whole group, and each thread keeps a 4-row x 2-key block of scores and a
 // 4-row x 8-dim block of outputs in registers. Same arithmetic as k_attn_prefill: scores in dimension order, multiply
-// then add, online softmax over 32-key tiles, causal. grid (HKV, ceil(B / (64/group))).
-constexpr int AG_ROWS = 64, AG_K = 32, AG_LD = D + 4, AG_THREADS = 256, AG_LDP = AG_K + 1;
+// then add, online softmax over 32-key tiles, causal.
+// The keys of a query tile are cut into chunks of `kchunk` key tiles, one CTA per (query tile, chunk): late query tiles
+// see many more keys than early ones, and without the cut the longest tile alone sets the kernel's duration. A query
+// tile with one chunk writes its output directly; otherwise every chunk leaves (acc, m, l) in `part` and the last
+// chunk to arrive adds them in chunk order (deterministic). grid (HKV, number of (query tile, chunk) items).
+constexpr int AG_ROWS = 64, AG_K = 32, AG_LD = D + 4, AG_THREADS = 256, AG_LDP = AG_K + 1, AG_MAXCHUNK = 8;
 constexpr size_t AG_SMEM = size_t(AG_ROWS * AG_LD + AG_K * AG_LD + AG_K * D + AG_ROWS * AG_LDP) * sizeof(float);
+constexpr int AG_PART = AG_ROWS * (D + 2);  // floats per partial result
+
+__host__ __device__ __forceinline__ int ag_chunks(int pos0, int B, int TQ, int i, int kchunk) {  // chunks of query tile i
+    const int T = pos0 + min(B, (i + 1) * TQ);
+    return ((T + AG_K - 1) / AG_K + kchunk - 1) / kchunk;
+}
 
 __global__ void __launch_bounds__(AG_THREADS) k_attn_prefill_gqa(const float* __restrict__ qkv, int64_t ld,
                                                                  const float* __restrict__ kc, const float* __restrict__ vc,
                                                                  float* __restrict__ att, int64_t ld_att, int pos0, int B,
-                                                                 int H, int HKV, float scale) {
+                                                                 int H, int HKV, float scale, int kchunk, float* part,
+                                                                 unsigned* counters) {
     extern __shared__ __align__(16) float sm[];
     float* Qs = sm;                        // [64][AG_LD]
     float* Ks = Qs + AG_ROWS * AG_LD;      // [32][AG_LD]
     float* Vs = Ks + AG_K * AG_LD;         // [32][D]
     float* Ps = Vs + AG_K * D;             // [64][33]
+    __shared__ int s_last;
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-    const int kvh = blockIdx.x, group = H / HKV, TQ = AG_ROWS / group, q0 = blockIdx.y * TQ, KD = HKV * D;
+    const int kvh = blockIdx.x, group = H / HKV, TQ = AG_ROWS / group, KD = HKV * D, n_qt = (B + TQ - 1) / TQ;
+    int qt = 0, chunk = int(blockIdx.y), n_chunks = ag_chunks(pos0, B, TQ, 0, kchunk);  // item -> (query tile, chunk)
+    while (chunk >= n_chunks && qt + 1 < n_qt) {
+        chunk -= n_chunks;
+        ++qt;
+        n_chunks = ag_chunks(pos0, B, TQ, qt, kchunk);
+    }
+    const int q0 = qt * TQ;
     const int nq = min(TQ, B - q0);
     for (int idx = tid; idx < AG_ROWS * (D / 4); idx += AG_THREADS) {  // row r = head * TQ + token
         const int r = idx / (D / 4), c = (idx % (D / 4)) * 4, h = r / TQ, t = r - h * TQ;
@@ -367,8 +387,8 @@ __global__ void __launch_bounds__(AG_THREADS) k_attn_prefill_gqa(const float* __
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
     }
-    const int T = pos0 + q0 + nq;  // keys needed by the tile
-    for (int t0 = 0; t0 < T; t0 += AG_K) {
+    const int T = min(pos0 + q0 + nq, (chunk + 1) * kchunk * AG_K);  // keys of this chunk: [chunk * kchunk * 32, T)
+    for (int t0 = chunk * kchunk * AG_K; t0 < T; t0 += AG_K) {
         __syncthreads();
         for (int idx = tid; idx < AG_K * (D / 4); idx += AG_THREADS) {
             const int j = idx / (D / 4), c = (idx % (D / 4)) * 4;
@@ -447,6 +467,53 @@ __global__ void __launch_bounds__(AG_THREADS) k_attn_prefill_gqa(const float* __
             }
         }
         __syncwarp();
+    }
+    if (n_chunks > 1) {  // leave this chunk's result; the last chunk of the query tile to arrive adds them all
+        float* base = part + (size_t(kvh) * n_qt + qt) * AG_MAXCHUNK * AG_PART;
+        float* mine = base + size_t(chunk) * AG_PART;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float* o = mine + (ty * 4 + i) * (D + 2);
+            *reinterpret_cast<float2*>(o + tx * 4) = make_float2(acc[i][0], acc[i][1]);  // rows of D + 2 floats: 8-byte aligned
+            *reinterpret_cast<float2*>(o + tx * 4 + 2) = make_float2(acc[i][2], acc[i][3]);
+            *reinterpret_cast<float2*>(o + 64 + tx * 4) = make_float2(acc[i][4], acc[i][5]);
+            *reinterpret_cast<float2*>(o + 64 + tx * 4 + 2) = make_float2(acc[i][6], acc[i][7]);
+            if (tx == 0) { o[D] = m[i]; o[D + 1] = l[i]; }
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            unsigned* cnt = counters + size_t(kvh) * n_qt + qt;
+            const unsigned old = atomicAdd(cnt, 1u);
+            s_last = old == unsigned(n_chunks - 1);
+            if (s_last) *cnt = 0;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = ty * 4 + i;
+            float M = -INFINITY;
+            for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, __ldcg(base + size_t(c) * AG_PART + r * (D + 2) + D));
+            float L = 0.f;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) acc[i][c8] = 0.f;
+            for (int c = 0; c < n_chunks; ++c) {  // fixed chunk order
+                const float* ps = base + size_t(c) * AG_PART + r * (D + 2);
+                const float mc = __ldcg(ps + D);
+                if (mc == -INFINITY) continue;
+                const float w = expf(mc - M);
+                L = fmaf(__ldcg(ps + D + 1), w, L);
+                const float2 a0 = __ldcg(reinterpret_cast<const float2*>(ps + tx * 4)), a1 = __ldcg(reinterpret_cast<const float2*>(ps + tx * 4 + 2));
+                const float2 b0 = __ldcg(reinterpret_cast<const float2*>(ps + 64 + tx * 4)), b1 = __ldcg(reinterpret_cast<const float2*>(ps + 64 + tx * 4 + 2));
+                acc[i][0] = fmaf(a0.x, w, acc[i][0]); acc[i][1] = fmaf(a0.y, w, acc[i][1]);
+                acc[i][2] = fmaf(a1.x, w, acc[i][2]); acc[i][3] = fmaf(a1.y, w, acc[i][3]);
+                acc[i][4] = fmaf(b0.x, w, acc[i][4]); acc[i][5] = fmaf(b0.y, w, acc[i][5]);
+                acc[i][6] = fmaf(b1.x, w, acc[i][6]); acc[i][7] = fmaf(b1.y, w, acc[i][7]);
+            }
+            l[i] = L;
+        }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -648,8 +715,17 @@ int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_
     return ELB_OK;
 }
 
+size_t attn_prefill_scratch_floats(int max_batch, int H, int HKV) {  // partial results of the chunked prompt attention
+    const int group = std::max(1, H / HKV), TQ = AG_ROWS % group == 0 ? AG_ROWS / group : AG_ROWS;
+    return size_t(HKV) * size_t((max_batch + TQ - 1) / TQ) * AG_MAXCHUNK * AG_PART;
+}
+size_t attn_prefill_counters(int max_batch, int H, int HKV) {
+    const int group = std::max(1, H / HKV), TQ = AG_ROWS % group == 0 ? AG_ROWS / group : AG_ROWS;
+    return size_t(HKV) * size_t((max_batch + TQ - 1) / TQ);
+}
+
 int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
-                        int pos0, int B, int H, int HKV, float scale, cudaStream_t s) {
+                        int pos0, int B, int H, int HKV, float scale, cudaStream_t s, float* part, unsigned* counters) {
     static thread_local bool configured = false;
     if (!configured) {
         ELB_CUDA(cudaFuncSetAttribute(k_attn_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AP_SMEM)));
@@ -659,9 +735,15 @@ int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const flo
     const int group = H / HKV;
     static const bool old_kernel = [] { const char* v = std::getenv("ELB_ATTN_SIMPLE"); return v && v[0] == '1'; }();
     if (!old_kernel && H % HKV == 0 && AG_ROWS % group == 0 && ld % 4 == 0 && ld_att % 4 == 0) {
-        const int TQ = AG_ROWS / group;
-        k_attn_prefill_gqa<<<dim3(HKV, (B + TQ - 1) / TQ), AG_THREADS, AG_SMEM, s>>>(qkv, ld, kc, vc, att, ld_att, pos0, B, H,
-                                                                                   HKV, scale);
+        const int TQ = AG_ROWS / group, n_qt = (B + TQ - 1) / TQ;
+        // chunks of 4 key tiles (128 keys), longer when the context is long enough to need more than AG_MAXCHUNK of them;
+        // without scratch memory one chunk per query tile
+        const int tiles_max = (pos0 + B + AG_K - 1) / AG_K;
+        const int kchunk = part && counters ? std::max(4, (tiles_max + AG_MAXCHUNK - 1) / AG_MAXCHUNK) : tiles_max;
+        int items = 0;
+        for (int i = 0; i < n_qt; ++i) items += ag_chunks(pos0, B, TQ, i, kchunk);
+        k_attn_prefill_gqa<<<dim3(HKV, items), AG_THREADS, AG_SMEM, s>>>(qkv, ld, kc, vc, att, ld_att, pos0, B, H, HKV, scale,
+                                                                         kchunk, part, counters);
         ELB_CUDA(cudaGetLastError());
         return ELB_OK;
     }

@@ -254,7 +254,10 @@ int attn_rows_launch(const float* qkv, int64_t ld, const float* kc, const float*
                      const int* seqv, float* att, int64_t ld_att, float* part, unsigned* counters, int B, int H, int HKV,
                      int nsplit, float scale, cudaStream_t s);
 int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
-                        int pos0, int B, int H, int HKV, float scale, cudaStream_t s);
+                        int pos0, int B, int H, int HKV, float scale, cudaStream_t s, float* part = nullptr,
+                        unsigned* counters = nullptr);
+size_t attn_prefill_scratch_floats(int max_batch, int H, int HKV);  // `part` of attn_prefill_launch
+size_t attn_prefill_counters(int max_batch, int H, int HKV);        // `counters` (zero before the first launch)
 int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s);
 
 

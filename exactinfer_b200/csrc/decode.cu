@@ -298,7 +298,7 @@ __device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
 // Matrices of the step in execution order: per layer qkv segments, wo, gate|up, down; then the head.
 __device__ __forceinline__ const DkMat& mat_at(const DkParams& p, int j) {
     const int per = p.n_qkv + 3, l = j / per, i = j - l * per;
-    if (l >= p.n_layer) return p.head;
+    if (l >= p.n_layer) return p.layers[p.n_layer].wo;  // the head
     const DkLayer& L = p.layers[l];
     return i < p.n_qkv ? L.qkv[i] : i == p.n_qkv ? L.wo : i == p.n_qkv + 1 ? L.gu : L.down;
 }
@@ -777,66 +777,56 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         return r;
     };
 
-    for (int l = 0; l < p.n_layer && ok; ++l) {
+    // The step as ONE loop over its matvec stages - per layer q|k|v (0), attn_output (1), gate|up (2), ffn_down (3),
+    // then the head (4) - so that the conversion, the matvec and the attention code exist once in the kernel: unrolled
+    // per stage the code outgrows the instruction cache and the warps stall on instruction fetch.
+    const int n_stages = 4 * p.n_layer + 1;
+    for (int stage = 0; stage < n_stages && ok; ++stage) {
+        const bool head = stage + 1 == n_stages;
+        const int l = head ? p.n_layer : stage >> 2, k = head ? 4 : stage & 3;  // layers[n_layer].wo is the head
         const DkLayer& L = p.layers[l];
-        unsigned* amax = amax_base + 2 * l;
-        dk_stamp(p, l, 0);
-        {
-            s.act = act_for(p.E);
-            const Resid rs_ = resid_step(nullptr);
-            int need = 0;
-            for (int i = 0; i < p.n_qkv; ++i) need |= sd_need(L.qkv[i]);
-            const float inv = convert_act(nullptr, &rs_, p.E, L.attn_norm, p.eps, nullptr, p.nl_qkv, s.act, s.red8, need);
-            dk_stamp(p, l, 1);
-            for (int i = 0; i < p.n_qkv; ++i)
-                matvec_phase(p, L.qkv[i], DK_EPI_STORE, p.qkv + L.qkv_col[i], inv, pf, rs, s, nullptr);
+        unsigned* amax = amax_base + 2 * (head ? 0 : l);
+        if (k == 0) dk_stamp(p, l, 0);
+        if (k == 1) {  // attention sits between q|k|v and attn_output
+            attn_phase(p, L, as, amax);
+            dk_stamp(p, l, 4);
+            if (!(ok = grid_barrier(p, nb, dead))) break;
+            dk_stamp(p, l, 5);
         }
-        dk_stamp(p, l, 2);
-        if (!(ok = grid_barrier(p, nb, dead))) break;
-        dk_stamp(p, l, 3);
-        attn_phase(p, L, as, amax);
-        dk_stamp(p, l, 4);
-        if (!(ok = grid_barrier(p, nb, dead))) break;
-        dk_stamp(p, l, 5);
-        {
-            s.act = act_for(p.H * DK_HD);
-            const float inv = convert_act(p.att, nullptr, p.H * DK_HD, nullptr, p.eps, amax, p.nl_wo, s.act, s.red8, sd_need(L.wo));
-            dk_stamp(p, l, 6);
-            matvec_phase(p, L.wo, DK_EPI_PART, nullptr, inv, pf, rs, s, nullptr, int(xn & 1u));
+        // the stage's activation: where it comes from, how it is normalised, which matrices consume it
+        const float *src = nullptr, *norm_w = nullptr;
+        const unsigned* amax_in = nullptr;
+        unsigned* amax_out = nullptr;
+        const DkMat* mats = &L.wo;
+        float* y = nullptr;
+        int n = p.E, nl = 4, nm = 1, epi = DK_EPI_PART;
+        bool resid = true;
+        switch (k) {
+            case 0: norm_w = L.attn_norm; nl = p.nl_qkv; mats = L.qkv; nm = p.n_qkv; epi = DK_EPI_STORE; y = p.qkv; break;
+            case 1: resid = false; src = p.att; n = p.H * DK_HD; amax_in = amax; nl = p.nl_wo; break;
+            case 2: norm_w = L.ffn_norm; nl = p.nl_gu; mats = &L.gu; epi = DK_EPI_SILU_AMAX; y = p.act; amax_out = amax + 1; break;
+            case 3: resid = false; src = p.act; n = p.F; amax_in = amax + 1; nl = p.nl_down; mats = &L.down; break;
+            default: norm_w = p.output_norm; epi = DK_EPI_LOGITS; break;
         }
-        dk_stamp(p, l, 7);
-        if (!(ok = exchange_barrier(p, nb, xn, dead))) break;
-        pending = int(xn & 1u);
-        ++xn;
-        dk_stamp(p, l, 8);
-        {
-            s.act = act_for(p.E);
-            const Resid rs_ = resid_step(nullptr);
-            const float inv = convert_act(nullptr, &rs_, p.E, L.ffn_norm, p.eps, nullptr, p.nl_gu, s.act, s.red8, sd_need(L.gu));
-            dk_stamp(p, l, 9);
-            matvec_phase(p, L.gu, DK_EPI_SILU_AMAX, p.act, inv, pf, rs, s, amax + 1);
+        int need = 0;
+        for (int i = 0; i < nm; ++i) need |= sd_need(mats[i]);
+        s.act = act_for(n);
+        Resid rsd{nullptr, nullptr, 0, nullptr};
+        if (resid) rsd = resid_step(head ? p.x : nullptr);  // the last residual stream goes to p.x
+        const float inv = convert_act(src, resid ? &rsd : nullptr, n, norm_w, p.eps, amax_in, nl, s.act, s.red8, need);
+        const int sb = k == 0 ? 0 : 3 * k + 2;  // profile stamps of the stage: conversion, matvec, barrier
+        if (!head) dk_stamp(p, l, sb + 1);
+        for (int i = 0; i < nm; ++i)
+            matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u));
+        if (!head) dk_stamp(p, l, sb + 2);
+        if (k == 1 || k == 3 || (head && p.tp_size > 1)) {  // row-parallel matvecs and the logits meet all ranks
+            ok = exchange_barrier(p, nb, xn, dead);
+            pending = int(xn & 1u);
+            ++xn;
+        } else if (!head) {
+            ok = grid_barrier(p, nb, dead);
         }
-        dk_stamp(p, l, 10);
-        if (!(ok = grid_barrier(p, nb, dead))) break;
-        dk_stamp(p, l, 11);
-        {
-            s.act = act_for(p.F);
-            const float inv = convert_act(p.act, nullptr, p.F, nullptr, p.eps, amax + 1, p.nl_down, s.act, s.red8, sd_need(L.down));
-            dk_stamp(p, l, 12);
-            matvec_phase(p, L.down, DK_EPI_PART, nullptr, inv, pf, rs, s, nullptr, int(xn & 1u));
-        }
-        dk_stamp(p, l, 13);
-        ok = exchange_barrier(p, nb, xn, dead);
-        pending = int(xn & 1u);
-        ++xn;
-        dk_stamp(p, l, 14);
-    }
-    if (ok) {  // final norm + head (src/model.cpp:229-232 of the reference); the last residual stream goes to p.x
-        s.act = act_for(p.E);
-        const Resid rs_ = resid_step(p.x);
-        const float inv = convert_act(nullptr, &rs_, p.E, p.output_norm, p.eps, nullptr, 4, s.act, s.red8, sd_need(p.head));
-        matvec_phase(p, p.head, DK_EPI_LOGITS, nullptr, inv, pf, rs, s, nullptr);
-        if (p.tp_size > 1) exchange_barrier(p, nb, xn, dead);  // every rank's rows are in place on every rank
+        if (!head) dk_stamp(p, l, sb + 3);
     }
     ring_wait<0>();
     if (blockIdx.x == 0 && tid == 0) {  // every CTA read ctl before its first barrier: safe to move on

@@ -24,9 +24,8 @@ struct DkLayer {
 };
 
 struct DkParams {
-    const DkLayer* layers;  // device array [n_layer]
+    const DkLayer* layers;  // device array [n_layer + 1]; the extra element's `wo` is the head
     int n_layer, n_qkv;     // every layer has the same number of qkv segments
-    DkMat head;
     const float* output_norm;
     const uint8_t* embd;    // token embedding table, tiled layout
     int embd_type;

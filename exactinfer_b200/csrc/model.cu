@@ -95,6 +95,8 @@ struct Model {
     float* rows_part = nullptr;                    // attention partial results of a batch
     unsigned* rows_counters = nullptr;
     int rows_split = 1;
+    float* ap_part = nullptr;        // partial results of the chunked prompt attention
+    unsigned* ap_counters = nullptr;
     float* xr = nullptr;            // [max_batch][E] this rank's partial sums before the all-reduce
     float* logits_local = nullptr;  // [vchunk] this rank's rows of the head
     std::vector<std::vector<uint8_t>> shard_store;  // column cuts of wo / down, valid until finalize
@@ -214,7 +216,7 @@ int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
                                      m->rows_counters, B, H, HKV, m->rows_split, scale, m->stream));
         } else {
             ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, pos0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream));
-            ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream));
+            ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream, m->ap_part, m->ap_counters));
         }
         m->launches += 2;
         ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16));
@@ -427,7 +429,8 @@ int setup_decode_kernel(Model* m) {
     if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 5 * 4 * decode_threads()) return ELB_OK;
     DkParams& p = m->dk;
     p = DkParams{};
-    std::vector<DkLayer> hl(size_t(c.n_layer));
+    std::vector<DkLayer> hl(size_t(c.n_layer) + 1);  // + one element whose `wo` is the head
+    hl[size_t(c.n_layer)].wo = mat(m->head);
     int slot = m->head->unit_bytes;
     int64_t max_units_cta = (m->head->tiles * m->head->units_per_tile + di.sm_count - 1) / di.sm_count;
     int slots = 0;
@@ -485,7 +488,7 @@ int setup_decode_kernel(Model* m) {
     int* err_dev = nullptr;
     ELB_CUDA(cudaHostGetDevicePointer(&err_dev, m->err_host, 0));
     p.layers = m->dk_layers; p.n_layer = c.n_layer; p.n_qkv = int(nq);
-    p.head = mat(m->head); p.output_norm = m->output_norm;
+    p.output_norm = m->output_norm;
     p.embd = m->embd->tiled; p.embd_type = m->embd->type;
     p.E = E; p.F = F; p.H = m->H; p.HKV = m->HKV; p.rope_dim = c.rope_dim; p.n_ctx = m->n_ctx;
     p.nsplit = std::max(1, std::min({32, m->attn_split, di.sm_count / m->HKV}));
@@ -600,6 +603,7 @@ void model_destroy(Model* m) {
     cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
+    cudaFree(m->ap_part); cudaFree(m->ap_counters);
     cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);
     tp_comm_destroy(m->comm);
@@ -774,6 +778,9 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->attn_part, size_t(m->HKV) * m->attn_split * group * (128 + 2) * 4));
     ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(m->HKV) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&m->ap_part, attn_prefill_scratch_floats(m->max_batch, m->H, m->HKV) * sizeof(float)));
+    ELB_CUDA(cudaMalloc(&m->ap_counters, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
+    ELB_CUDA(cudaMemset(m->ap_counters, 0, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
     ELB_TRY(setup_decode_kernel(m));
     m->pending.clear();
     m->pending.shrink_to_fit();
