@@ -285,6 +285,45 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
     return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
 }
 
+// The FFN activation when its limbs do not fit in shared memory: the CTAs convert 256-value blocks of it (equal
+// ranges) into global memory - limbs [4][n_pad], then the sub-block sums, the layout of ActSmem - and meet at a grid
+// barrier; ffn_down then reads the limbs through L2. max|src| is known (amax_bits). Returns inv_scale = 2^-k.
+__device__ float convert_act_global(const float* src, int n, const unsigned* amax_bits, int nl, const ActSmem& g, int sd_mask) {
+    const int tid = threadIdx.x, nb = n / 256;
+    const int b0 = range_lo(nb, gridDim.x, blockIdx.x), b1 = range_lo(nb, gridDim.x, blockIdx.x + 1);
+    const int k = split_shift(__uint_as_float(__ldcg(amax_bits)), nl);
+    const Pow2 sc = make_pow2(k);
+    for (int i = b0 * 256 + tid * 4; i < b1 * 256; i += DK_THREADS * 4)
+        limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, g.lim, g.n_pad, i);
+    __syncthreads();  // this CTA's limbs are visible to its own threads
+    if (sd_mask & 1) {
+        for (int e = b0 * 32 + tid; e < b1 * 32; e += DK_THREADS) {  // 8 sub-blocks x 4 limbs per block
+            const int S = e >> 2, l = e & 3;
+            const uint4* q = reinterpret_cast<const uint4*>(g.lim + l * g.n_pad + S * 32);
+            const uint4 x = __ldcg(q), y = __ldcg(q + 1);  // through L2: the addresses are reused every layer
+            int sum = __dp4a(int(x.x), 0x01010101, 0);
+            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
+            sum = __dp4a(int(y.x), 0x01010101, sum); sum = __dp4a(int(y.y), 0x01010101, sum);
+            sum = __dp4a(int(y.z), 0x01010101, sum); sum = __dp4a(int(y.w), 0x01010101, sum);
+            const int lo = ((sum + 128) & 255) - 128, blk = S >> 3, si = S & 7;
+            g.sd32[(blk * 8 + l) * 8 + si] = int8_t(lo);
+            g.sd32[(blk * 8 + 4 + l) * 8 + si] = int8_t((sum - lo) >> 8);
+        }
+    }
+    if (sd_mask & 2) {
+        for (int e = b0 * 64 + tid; e < b1 * 64; e += DK_THREADS) {  // 16 sub-blocks x 4 limbs per block
+            const int S = e >> 2, l = e & 3;
+            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(g.lim + l * g.n_pad + S * 16));
+            int sum = __dp4a(int(x.x), 0x01010101, 0);
+            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
+            const int lo = ((sum + 128) & 255) - 128, blk = S >> 4, si = S & 15;
+            g.sd16[(blk * 8 + l) * 16 + si] = int8_t(lo);
+            g.sd16[(blk * 8 + 4 + l) * 16 + si] = int8_t((sum - lo) >> 8);
+        }
+    }
+    return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
+}
+
 __device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
     if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
@@ -368,7 +407,7 @@ struct PhaseSmem {
     int* flags;      // [4]: dead (2), block amax bits (3)
 };
 
-template <int TYPE>
+template <int TYPE, bool CG>
 __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, int& rs,
                           const PhaseSmem& s, int warp, int lane) {
     const int g = lane >> 2, t = lane & 3, upt = m.upt;
@@ -387,7 +426,7 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
         Unit<TYPE> cur;
         load_unit(cur, s.ring + rs * s.slot_bytes, lane);
         rs = rs + 1 == DK_DEPTH ? 0 : rs + 1;
-        compute_unit<false>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg);
+        compute_unit<false, CG>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg);
         __syncwarp();
         if (++b == upt || u + 1 == r.wB) {
             float v0 = a.acc[0] * wt - a.accm[0] * wtm, v1 = a.acc[1] * wt - a.accm[1] * wtm;
@@ -415,15 +454,23 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
 //                     the consumer adds residual + all the vectors (convert_act).
 //   DK_EPI_LOGITS     y[v0 + row] = sum on every tensor-parallel rank (this rank's vocabulary rows of the head)
 __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf,
-                             int& rs, const PhaseSmem& s, unsigned* amax_out, int xset = 0) {
+                             int& rs, const PhaseSmem& s, unsigned* amax_out, int xset = 0, bool gact = false) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
     const WarpRange r = warp_range(m, warp);
     if (tid == 0) s.flags[3] = 0;
     __syncthreads();  // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v)
-    switch (m.type) {
-        case ELB_Q4_K: run_units<ELB_Q4_K>(p, m, r, pf, rs, s, warp, lane); break;
-        case ELB_Q6_K: run_units<ELB_Q6_K>(p, m, r, pf, rs, s, warp, lane); break;
-        default: run_units<ELB_Q8_0>(p, m, r, pf, rs, s, warp, lane); break;
+    if (gact) {  // activation limbs in global memory (written by other CTAs before the last barrier): L2 loads
+        switch (m.type) {
+            case ELB_Q4_K: run_units<ELB_Q4_K, true>(p, m, r, pf, rs, s, warp, lane); break;
+            case ELB_Q6_K: run_units<ELB_Q6_K, true>(p, m, r, pf, rs, s, warp, lane); break;
+            default: run_units<ELB_Q8_0, true>(p, m, r, pf, rs, s, warp, lane); break;
+        }
+    } else {
+        switch (m.type) {
+            case ELB_Q4_K: run_units<ELB_Q4_K, false>(p, m, r, pf, rs, s, warp, lane); break;
+            case ELB_Q6_K: run_units<ELB_Q6_K, false>(p, m, r, pf, rs, s, warp, lane); break;
+            default: run_units<ELB_Q8_0, false>(p, m, r, pf, rs, s, warp, lane); break;
+        }
     }
     __syncthreads();
     if (r.cA < r.cB) {
@@ -746,7 +793,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     int rs = 0;
     int* dead = &s.flags[2];
     const unsigned step = p.ctl[0], epoch = p.ctl[2];
-    unsigned nb = epoch * unsigned(1 + 5 * p.n_layer + (p.tp_size > 1 ? 1 : 0)) * gridDim.x;  // arrivals before this launch
+    unsigned nb = epoch * unsigned(1 + (5 + (p.act_global ? 1 : 0)) * p.n_layer + (p.tp_size > 1 ? 1 : 0)) * gridDim.x;  // arrivals before this launch
     unsigned* const amax_base = p.amax + (epoch & 1u) * 2 * p.n_layer;
     if (blockIdx.x == 0)  // the other half of the amax slots: untouched by this launch, zero for the next one
         for (int i = tid; i < 2 * p.n_layer; i += DK_THREADS) p.amax[((epoch + 1) & 1u) * 2 * p.n_layer + i] = 0u;
@@ -810,14 +857,27 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         }
         int need = 0;
         for (int i = 0; i < nm; ++i) need |= sd_need(mats[i]);
-        s.act = act_for(n);
-        Resid rsd{nullptr, nullptr, 0, nullptr};
-        if (resid) rsd = resid_step(head ? p.x : nullptr);  // the last residual stream goes to p.x
-        const float inv = convert_act(src, resid ? &rsd : nullptr, n, norm_w, p.eps, amax_in, nl, s.act, s.red8, need);
+        const bool gact = k == 3 && p.act_global;
+        float inv;
+        if (gact) {
+            ActSmem g;
+            g.lim = p.gact;
+            g.n_pad = n + 32;
+            g.sd32 = g.lim + 4 * g.n_pad;
+            g.sd16 = g.sd32 + (n / 256) * 64;
+            s.act = g;
+            inv = convert_act_global(src, n, amax_in, nl, g, need);
+            if (!(ok = grid_barrier(p, nb, dead))) break;
+        } else {
+            s.act = act_for(n);
+            Resid rsd{nullptr, nullptr, 0, nullptr};
+            if (resid) rsd = resid_step(head ? p.x : nullptr);  // the last residual stream goes to p.x
+            inv = convert_act(src, resid ? &rsd : nullptr, n, norm_w, p.eps, amax_in, nl, s.act, s.red8, need);
+        }
         const int sb = k == 0 ? 0 : 3 * k + 2;  // profile stamps of the stage: conversion, matvec, barrier
         if (!head) dk_stamp(p, l, sb + 1);
         for (int i = 0; i < nm; ++i)
-            matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u));
+            matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u), gact);
         if (!head) dk_stamp(p, l, sb + 2);
         if (k == 1 || k == 3 || (head && p.tp_size > 1)) {  // row-parallel matvecs and the logits meet all ranks
             ok = exchange_barrier(p, nb, xn, dead);

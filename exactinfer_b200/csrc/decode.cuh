@@ -38,6 +38,8 @@ struct DkParams {
                             // [2] launches so far (barrier targets and the parity of the amax slots derive from it)
     const float* rope;      // [n_ctx][rope_dim/2][2]
     float *x, *qkv, *att, *act, *logits;
+    int8_t* gact;           // limbs + sub-block sums of the FFN activation in global memory, used when they do not fit in
+    int act_global;         // shared memory next to the rings (long n_ff): then set, and ffn_down reads them through L2
     float* xbuf;            // [2][E] residual stream, alternating: a conversion reads one and writes the other
     // Partial sums of the row-parallel matvecs (attn_output, ffn_down), added by the next conversion. Two sets, used in
     // turn by successive exchanges; a set holds, for every tensor-parallel rank, two vectors of E floats (the two

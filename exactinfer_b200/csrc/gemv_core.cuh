@@ -63,7 +63,11 @@ __device__ __forceinline__ void load_unit(Unit<ELB_Q8_0>& u, const uint8_t* base
 }
 
 // activation fragments: plain loads (the compiler picks LDS or LDG from the pointer; global ones hit L1)
-template <class T> __device__ __forceinline__ T ld_act(const T* p) { return *p; }
+// CG: through L2 only, for limbs in global memory that other CTAs of the SAME kernel wrote (L1 is not coherent)
+template <bool CG, class T> __device__ __forceinline__ T ld_act(const T* p) {
+    if constexpr (CG) return __ldcg(p);
+    else return *p;
+}
 
 // prmt.b32 in its default mode: selector nibble k < 8 copies byte k of {a, b}; 8 + k fills the byte with byte k's sign
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -87,7 +91,7 @@ struct DbgOut {
 };
 
 // ---- Q4_K: one 256-block of 16 rows
-template <bool DBG>
+template <bool DBG, bool CG = false>
 __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, const int8_t* lim, int n_pad,
                                              const int8_t* sd, int lane, Acc& a, const DbgOut& dbg) {
     const int g = lane >> 2, t = lane & 3;
@@ -106,7 +110,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
 #pragma unroll
         for (int odd = 0; odd < 2; ++odd) {
             const int sub = 2 * j + odd;
-            const uint2 bf = ld_act(reinterpret_cast<const uint2*>(lcol + sub * 32));
+            const uint2 bf = ld_act<CG>(reinterpret_cast<const uint2*>(lcol + sub * 32));
             const uint32_t mask = odd ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
             int C[4];
             mma_u8s8_k32(C, q.x & mask, q.z & mask, q.y & mask, q.w & mask, bf.x, bf.y);
@@ -137,7 +141,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
     // min term: J[col] = sum over the 8 sub-blocks of m * (digit `col>>2` of the limb sum S of limb `col&3`)
     const uint32_t a0 = t == 0 ? mg[0] : t == 1 ? mg[1] : 0u, a1 = t == 0 ? mh[0] : t == 1 ? mh[1] : 0u;
-    const uint32_t b0 = ld_act(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 8 + 4 * (t & 1)));
+    const uint32_t b0 = ld_act<CG>(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 8 + 4 * (t & 1)));
     int J[4];
     mma_u8s8_k16(J, a0, a1, b0);
     const float ng = h2f_bits(u.h0.x >> 16), nh = h2f_bits(u.h1.x >> 16);
@@ -163,7 +167,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
 
 // ---- Q6_K: one 256-block of 16 rows; sub-blocks of 16 with int8 scales; q6 is fed unsigned (0..63) and the
 // offset -32 * sum sc*S comes from one extra MMA over the limb sums S of the 16-wide sub-blocks.
-template <bool DBG>
+template <bool DBG, bool CG = false>
 __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, const int8_t* lim, int n_pad,
                                              const int8_t* sd, int lane, Acc& a, const DbgOut& dbg) {
     const int g = lane >> 2, t = lane & 3;
@@ -182,7 +186,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
             const uint32_t hy = (i < 2 ? qh.y << (4 - 2 * i) : qh.y >> (2 * i - 4)) & 0x30303030u;
             const uint32_t a0 = (w & 0x0F0F0F0Fu) | hx;
             const uint32_t a1 = ((w >> 4) & 0x0F0F0F0Fu) | hy;
-            const uint32_t bf = ld_act(reinterpret_cast<const uint32_t*>(lcol + s * 16));
+            const uint32_t bf = ld_act<CG>(reinterpret_cast<const uint32_t*>(lcol + s * 16));
             int C[4];
             mma_u8s8_k16(C, a0, a1, bf);
             // int8 scale of sub-block s, sign-extended by the byte permute (selector 8+k replicates byte k's sign)
@@ -209,7 +213,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
     const float dg = h2f_bits(u.dd & 0xFFFFu), dh = h2f_bits(u.dd >> 16);
     a.acc[0] += dg * fmaf(float(I[1]), 256.0f, float(I[0]));
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
-    const uint32_t b0 = ld_act(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 16 + 4 * t));
+    const uint32_t b0 = ld_act<CG>(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 16 + 4 * t));
     int J[4];
     mma_s8s8_k16(J, sel4(u.s0, t), sel4(u.s1, t), b0);
     a.accm[0] += (32.0f * dg) * fmaf(float(J[1]), 256.0f, float(J[0]));
@@ -233,7 +237,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
 }
 
 // ---- Q8_0: four 32-blocks of 16 rows; fp16 scale per block, so fp32 after every MMA
-template <bool DBG>
+template <bool DBG, bool CG = false>
 __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, const int8_t* lim, int n_pad,
                                              const int8_t*, int lane, Acc& a, const DbgOut& dbg) {
     const int g = lane >> 2, t = lane & 3;
@@ -241,7 +245,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, con
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint4 q = u.q[i];
-        const uint2 bf = ld_act(reinterpret_cast<const uint2*>(lcol + i * 32));
+        const uint2 bf = ld_act<CG>(reinterpret_cast<const uint2*>(lcol + i * 32));
         int C[4];
         mma_s8s8_k32(C, q.x, q.z, q.y, q.w, bf.x, bf.y);
         const uint32_t d0w = i < 2 ? u.d0.x : u.d0.y, d1w = i < 2 ? u.d1.x : u.d1.y;

@@ -79,6 +79,7 @@ struct Model {
     float* xbuf = nullptr;  // persistent kernel: residual stream [2][E]
     TpPeerBuf xarea;        // persistent kernel: flags, partial sums and logits, visible to all tensor-parallel ranks
     unsigned* xctl = nullptr;
+    int8_t* gact = nullptr;  // persistent kernel: limbs of the FFN activation when they do not fit in shared memory
     float* logits_step = nullptr;  // where a single-token step leaves its logits (m->logits unless the persistent kernel runs)
     unsigned* sync_words = nullptr;  // barrier counter, step index, advance flag, launch count, then 2 x [n_layer][2] amax slots
     int* pos_steps = nullptr;        // positions of a batch of single-token steps (persistent kernel)
@@ -515,6 +516,17 @@ int setup_decode_kernel(Model* m) {
             if (w->tiles * w->units_per_tile * int64_t(di.sm_count) >= (int64_t(1) << 31) || w->max_grid < di.sm_count) small = false;
     bool fits = false;
     ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+    if ((!fits || env_on("ELB_DK_GACT")) && Fmax > std::max(E, QD)) {  // (the variable forces the mode, for tests)
+        // the limbs of the FFN activation do not fit next to the rings: keep them in global memory (one more grid barrier
+        // per layer, ffn_down reads them through L2); every rank decides from the longest FFN cut, so all decide alike
+        p.act_global = 1;
+        p.n_max = std::max(E, QD);
+        ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+        if (fits) {
+            ELB_CUDA(cudaMalloc(&m->gact, act_bytes(Fmax) + 4 * 32));
+            p.gact = m->gact;
+        }
+    }
     fits = fits && small;
     int coop = 0;
     ELB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
@@ -600,7 +612,7 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl);
+    cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     cudaFree(m->ap_part); cudaFree(m->ap_counters);

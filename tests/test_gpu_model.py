@@ -145,3 +145,13 @@ def test_benchmark_distribution_within_logit_resolution(elb):
     top = np.argsort(lc)[-8:]
     assert np.abs(logprobs(lg) - logprobs(lc))[top].max() <= tol
     assert rel(lg, lc) <= REL_TOL
+
+
+def test_ffn_activation_in_global_memory(elb, monkeypatch):
+    """Shapes whose FFN activation does not fit in shared memory next to the weight rings keep its limbs in global
+    memory (one more grid barrier per layer); forced here on a small model."""
+    monkeypatch.setenv("ELB_DK_GACT", "1")
+    spec = synth.Spec(name="small", n_layer=3, n_embd=512, n_ff=1536, n_head=8, n_head_kv=2, n_vocab=2048, layout="q4_k_m",
+                      head_sigma=2e-5)
+    lp, r = run_pair(elb, spec, seed=23, n_prompt=24, n_decode=6)
+    assert lp <= LOGPROB_TOL and r <= REL_TOL, (lp, r)
