@@ -227,12 +227,13 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
         if (resid) {  // + the partial sums, vector by vector (two at a time in flight), in the same order everywhere
             for (int q = 0; q < resid->np; q += 2) {
                 float4 a[V4], b[V4];
+                const bool two = q + 1 < resid->np;  // (x + a) + 0 = x + a exactly: an odd count needs no second path
 #pragma unroll
                 for (int j = 0; j < V4; ++j) {
                     const int idx = (j * DK_THREADS + tid) * 4;
                     const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
                     a[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q) * n + idx)) : z;
-                    b[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q + 1) * n + idx)) : z;
+                    b[j] = idx < n && two ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q + 1) * n + idx)) : z;
                 }
 #pragma unroll
                 for (int j = 0; j < V4; ++j) {
@@ -498,7 +499,7 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
                 }
             } else if (epi == DK_EPI_PART) {
                 const bool first = r.cA <= Xt * upt, last = r.cB >= (Xt + 1) * upt;
-                const size_t pair = (size_t(xset) * p.tp_size + p.tp_rank) * 2 * p.E;  // this rank's two vectors of the set
+                const size_t pair = (size_t(xset) * p.tp_size + p.tp_rank) * p.pv * p.E;  // this rank's vectors of the set
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {  // constant indices into the parameter arrays
                     if (q >= p.tp_size) break;
@@ -506,7 +507,7 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
                     float* dst = first ? base : base + p.E;
                     if (r0 < m.rows) dst[r0] = v0;
                     if (r1 < m.rows) dst[r1] = v1;
-                    if (first && last) {
+                    if (first && last && p.pv == 2) {
                         if (r0 < m.rows) base[p.E + r0] = 0.f;
                         if (r1 < m.rows) base[p.E + r1] = 0.f;
                     }
@@ -818,8 +819,8 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         if (q == p.tp_rank) my_part = p.part_peer[q];
     int pending = -1;  // set whose partial sums the next residual conversion adds (-1: none yet in this launch)
     auto resid_step = [&](float* out) {
-        Resid r{p.xbuf + cur * p.E, pending < 0 ? nullptr : my_part + size_t(pending) * p.tp_size * 2 * p.E,
-                pending < 0 ? 0 : 2 * p.tp_size, out ? out : p.xbuf + (cur ^ 1) * p.E};
+        Resid r{p.xbuf + cur * p.E, pending < 0 ? nullptr : my_part + size_t(pending) * p.tp_size * p.pv * p.E,
+                pending < 0 ? 0 : p.pv * p.tp_size, out ? out : p.xbuf + (cur ^ 1) * p.E};
         cur ^= 1;
         return r;
     };

@@ -47,7 +47,8 @@ struct DkParams {
     // memory; part_peer[tp_rank] is the local one): every rank stores its partial sums into its slot on ALL ranks, and
     // after the exchange barrier every rank adds the same 2 * tp_size vectors in the same order.
     int tp_rank, tp_size;   // 1 rank: a single GPU, the exchange barrier is the grid barrier
-    float* part_peer[8];    // [2 sets][tp_size][2][E]
+    int pv;                 // vectors per rank in a set: 2 (a row tile can have two contributing CTAs) or 1 (whole tiles per CTA)
+    float* part_peer[8];    // [2 sets][tp_size][pv][E]
     unsigned* flag_peer[8]; // rank q's arrival flags [2 sets][8 ranks]
     float* logits_peer[8];  // rank q's logits [n_vocab padded]: every rank stores its vocabulary rows on all ranks
     int v0;                 // first vocabulary row of this rank
