@@ -358,7 +358,7 @@ def run_ours(args):
                        "frac_of_measured_copy": step_bytes / (dev_ms / K / 1000.0) / 1e9 / hbm,
                        "frac_of_8tbs": step_bytes / (dev_ms / K / 1000.0) / 1e9 / 8000.0},
         "setup_s": {"generate": gen_s, "upload": load_s},
-        "reference_published": {"note": "the reference's own figures for this metric, on other hardware and real weights; "
+        "reference_published": None if spec.name != "qwen3-4b-q4_k_m" else {"note": "the reference's own figures for this metric, on other hardware and real weights; "
                                         "nothing is published for B200, hence vs_baseline null",
                                 "hardware": "RTX 2060 (docs/performance.md:18 of the reference)",
                                 "decode_tok_s": [76, 81], "prefill_tok_s": [1100, 1140]},

@@ -129,6 +129,8 @@ typedef struct elb_model elb_model;
  * src/model.cpp:73-74) -> finalize (allocates the fp32 KV cache for n_ctx positions and the scratch buffers,
  * builds the RoPE table from double-precision angles, checks device memory). head_dim must be 128. */
 int elb_model_create(const elb_config* cfg, int n_ctx, int device, elb_model** out);
+/* The library keeps `bytes` by reference until elb_model_finalize returns (the reference's loader hands out pointers
+ * into its file mapping the same way, src/gguf.cpp): the caller must keep them valid until then, and may free them after. */
 int elb_model_set_tensor(elb_model* m, int role, int layer, int ggml_type, int64_t rows, int64_t n, const void* bytes,
                          size_t nbytes);
 int elb_model_finalize(elb_model* m);
