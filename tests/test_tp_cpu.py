@@ -70,3 +70,27 @@ def test_column_cut_copies_whole_blocks():
         rows, n, b = e.tp_shard(spec, r, 2, "ffn_down", synth.Q4_K, 256, 512, w)
         assert (rows, n) == (256, 256)
         assert np.array_equal(b.reshape(256, 144), raw[:, r, :])
+
+
+@pytest.mark.parametrize("layout,t", [("f16", synth.F16), ("q8_0", synth.Q8_0), ("q6_k", synth.Q6_K)])
+def test_cuts_reassemble_the_tensor(layout, t):
+    """Row cuts concatenated, and column cuts interleaved row by row, give back the whole tensor for every type."""
+    spec = synth.Spec("cut", n_layer=1, n_embd=256, n_ff=768, n_head=4, n_head_kv=2, n_vocab=100, layout=layout)
+    rng = np.random.default_rng(11)
+    F, E = spec.n_ff, spec.n_embd
+    gate = synth.rand_weight(rng, t, F, E)   # row cut
+    down = synth.rand_weight(rng, t, E, F)   # column cut
+    gate_b = np.ascontiguousarray(gate).reshape(F, -1)
+    down_b = np.ascontiguousarray(down).reshape(E, -1)
+    rows, cols = [], []
+    for r in range(2):
+        n_r, n_c, b = e.tp_shard(spec, r, 2, "ffn_gate", t, F, E, gate)
+        assert n_c == E
+        rows.append(b.reshape(n_r, -1))
+        n_r, n_c, b = e.tp_shard(spec, r, 2, "ffn_down", t, E, F, down)
+        assert n_r == E
+        cols.append(b.reshape(E, -1))
+    assert np.array_equal(np.concatenate(rows, axis=0), gate_b)
+    assert np.array_equal(np.concatenate(cols, axis=1), down_b)
+    d0, d1 = e.tp_dims(spec, 0, 2), e.tp_dims(spec, 1, 2)
+    assert (d0["f1"] - d0["f0"], d1["f1"] - d1["f0"]) == (256, 512)  # three 256-blocks cut 1 + 2
