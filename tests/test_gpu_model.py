@@ -155,3 +155,35 @@ def test_ffn_activation_in_global_memory(elb, monkeypatch):
                       head_sigma=2e-5)
     lp, r = run_pair(elb, spec, seed=23, n_prompt=24, n_decode=6)
     assert lp <= LOGPROB_TOL and r <= REL_TOL, (lp, r)
+
+
+def test_long_context(elb):
+    """A prompt of several chunks deep into the context (the chunked prompt attention cuts the keys of a query tile into
+    up to eight chunks) and a single-token step whose key splits take more than one pass over their keys. On this
+    sequence the reference's fp32 CPU path is itself ~1.6e-5 (relative) away from a float64 evaluation, so the bars
+    are taken against float64: the CUDA path may be at most as far from it as the CPU path (with a factor 1.5 of slack),
+    or within the usual bars."""
+    from f64_model import f64_logits
+    spec = synth.Spec(name="long", n_layer=1, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=300, layout="q4_k_m",
+                      head_sigma=2e-5)
+    tens = list(synth.generate(spec, 9))
+    n = 2500
+    toks = list(synth.lcg_tokens(n, spec.n_vocab))
+    gpu = elb.Backend(spec, tens, n + 2)
+    cpu = ol.OracleModel(spec, tens, n + 2)
+    for step in range(2):  # the prompt, then one more token
+        if step == 0:
+            lg, lc = gpu.eval(toks, 0), cpu.eval(toks, 0)
+        else:
+            toks.append(int(np.argmax(lc)))
+            lg, lc = gpu.eval(toks[-1:], n), cpu.eval(toks[-1:], n)
+        exact = f64_logits(spec, tens, np.asarray(toks))
+        lp_exact = exact - (np.log(np.sum(np.exp(exact - exact.max()))) + exact.max())
+        top = np.argsort(exact)[-8:]
+        e_gpu, e_cpu = rel(lg, exact), rel(lc, exact)
+        d_gpu = float(np.abs(logprobs(lg)[top] - lp_exact[top]).max())
+        d_cpu = float(np.abs(logprobs(lc)[top] - lp_exact[top]).max())
+        assert e_gpu <= max(REL_TOL, 1.5 * e_cpu), (step, e_gpu, e_cpu)
+        assert d_gpu <= max(LOGPROB_TOL, 1.5 * d_cpu), (step, d_gpu, d_cpu)
+    gpu.close()
+    cpu.close()
