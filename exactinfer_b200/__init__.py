@@ -221,6 +221,15 @@ class Backend:
                                    logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
+    def eval_top(self, tokens, pos0: int, k: int = 1):
+        """eval with the logits reduced on the device: (ids[k], logits[k], log-sum-exp) of the last token, ids ordered by
+        (logit descending, id ascending); logprob of ids[i] = logits[i] - lse."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        ids, vals, lse = np.empty(k, np.int32), np.empty(k, np.float32), C.c_double()
+        check(lib().elb_model_eval_top(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), tokens.size, pos0, k,
+                                       ids.ctypes.data_as(C.POINTER(C.c_int32)), capi.fptr(vals), C.byref(lse)))
+        return ids, vals, lse.value
+
     def eval_batch(self, tokens, seq, pos, want=None, want_logits: bool = True):
         """Rows of several sequences in one pass: row i is tokens[i] at position pos[i] of sequence seq[i] (n_seq given at
         construction). Returns one row of logits per wanted row (want: boolean mask, default all rows), or None."""

@@ -686,6 +686,72 @@ __global__ void __launch_bounds__(256) k_rmsnorm_rows(float* out, const float* x
     for (int i = tid; i < n; i += 256) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
 }
 
+// ---------------------------------------------------------------- logits post-processing
+// What the reference's generate loop does on the host with the n_vocab logits of every token (src/main.cpp:309-320):
+// log-sum-exp in double precision and the k best tokens ordered by (logit descending, id ascending). One block.
+__global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ logits, int n, int k, uint8_t* __restrict__ out) {
+    __shared__ double red_d[32];
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    __shared__ float s_val;
+    __shared__ int s_idx;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += 1024) mx = fmaxf(mx, logits[i]);
+    mx = warp_max(mx);
+    if (lane == 0) red_f[warp] = mx;
+    __syncthreads();
+    mx = red_f[0];
+    for (int w = 1; w < 32; ++w) mx = fmaxf(mx, red_f[w]);
+    double sum = 0.0;
+    for (int i = tid; i < n; i += 1024) sum += exp(double(logits[i]) - double(mx));
+    sum = warp_sum(sum);
+    if (lane == 0) red_d[warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 32; ++w) t += red_d[w];  // fixed order
+        *reinterpret_cast<double*>(out) = double(mx) + log(t);
+    }
+    int32_t* ids = reinterpret_cast<int32_t*>(out + 8);
+    float* vals = reinterpret_cast<float*>(out + 8 + 4 * TOP_MAXK);
+    float pv = INFINITY;  // the previous pick: candidates come strictly after it in the order
+    int pi = -1;
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = tid; i < n; i += 1024) {
+            const float v = logits[i];
+            const bool after = v < pv || (v == pv && i > pi);
+            if (after && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        __syncthreads();  // red_f / red_i free
+        if (lane == 0) { red_f[warp] = bv; red_i[warp] = bi; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 0; w < 32; ++w)
+                if (red_f[w] > bv || (red_f[w] == bv && red_i[w] < bi)) { bv = red_f[w]; bi = red_i[w]; }
+            s_val = bv; s_idx = bi;
+            ids[r] = bi; vals[r] = bv;
+        }
+        __syncthreads();
+        pv = s_val; pi = s_idx;
+    }
+}
+
+int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s) {
+    if (!logits || !out || n < 1 || k < 1 || k > TOP_MAXK || k > n) return fail(ELB_ERR_INVALID, "logits_top: bad argument");
+    k_logits_top<<<1, 1024, 0, s>>>(logits, n, k, out);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
 // ---------------------------------------------------------------- host side
 
 int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s) {

@@ -309,6 +309,10 @@ void elb_model_destroy(elb_model* m) { model_destroy(M(m)); }
 int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits) {
     return model_eval(M(m), tokens, n, pos0, logits);
 }
+int elb_model_eval_top(elb_model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* top_logits,
+                       double* lse) {
+    return model_eval_top(M(m), tokens, n, pos0, k, ids, top_logits, lse);
+}
 int elb_model_eval_batch(elb_model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos,
                          const uint8_t* want, float* logits) {
     return model_eval_batch(M(m), n, tokens, seq, pos, want, logits);

@@ -259,6 +259,11 @@ int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const flo
 size_t attn_prefill_scratch_floats(int max_batch, int H, int HKV);  // `part` of attn_prefill_launch
 size_t attn_prefill_counters(int max_batch, int H, int HKV);        // `counters` (zero before the first launch)
 int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s);
+// log-sum-exp (double) and the k best entries by (value descending, index ascending) of logits[n]; out: double lse, then
+// TOP_MAXK int32 ids, then TOP_MAXK floats
+constexpr int TOP_MAXK = 64;
+constexpr size_t TOP_BYTES = 8 + size_t(TOP_MAXK) * 8;
+int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s);
 
 
 }  // namespace elb
@@ -321,6 +326,7 @@ int model_finalize(Model* m);
 void model_destroy(Model* m);
 int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits);
 int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* device_ms);
+int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* vals, double* lse);
 int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
                      float* logits);
 int model_stats(const Model* m, float* ms, int64_t* launches);

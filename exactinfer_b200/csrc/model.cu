@@ -96,6 +96,8 @@ struct Model {
     float* rows_part = nullptr;                    // attention partial results of a batch
     unsigned* rows_counters = nullptr;
     int rows_split = 1;
+    uint8_t* top_dev = nullptr;      // device-side logits post-processing: lse, ids, logits
+    uint8_t* top_host = nullptr;     // pinned
     float* ap_part = nullptr;        // partial results of the chunked prompt attention
     unsigned* ap_counters = nullptr;
     float* xr = nullptr;            // [max_batch][E] this rank's partial sums before the all-reduce
@@ -364,7 +366,10 @@ int enqueue_decode_step(Model* m) {
     return ELB_OK;
 }
 
-int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
+// `top`: instead of copying the logits out, reduce them on the device to the k best tokens and the log-sum-exp
+struct TopOut { int k; int32_t* ids; float* vals; double* lse; };
+
+int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits, const TopOut* top = nullptr) {
     std::memcpy(m->tokens_host, tokens, size_t(B) * sizeof(int32_t));
     *m->pos_host = pos0;
     ELB_CUDA(cudaMemcpyAsync(m->tokens_dev, m->tokens_host, size_t(B) * sizeof(int32_t), cudaMemcpyHostToDevice, m->stream));
@@ -377,13 +382,24 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits) {
         ELB_TRY(launch_gather_rows(m->embd, m->tokens_dev, B, m->x, m->stream));
         ++m->launches;
         ELB_TRY(body_prefill(m, B, pos0));
-        if (logits) ELB_TRY(head_logits(m, m->x + size_t(B - 1) * m->cfg.n_embd));
+        if (logits || top) ELB_TRY(head_logits(m, m->x + size_t(B - 1) * m->cfg.n_embd));
+    }
+    const float* dev_logits = B == 1 && m->use_mega ? m->logits_step : m->logits;
+    if (top) {
+        ELB_TRY(logits_top_launch(dev_logits, m->cfg.n_vocab, top->k, m->top_dev, m->stream));
+        ++m->launches;
     }
     ELB_CUDA(cudaEventRecord(m->ev1, m->stream));
     if (logits)
-        ELB_CUDA(cudaMemcpyAsync(logits, B == 1 && m->use_mega ? m->logits_step : m->logits, size_t(m->cfg.n_vocab) * sizeof(float),
-                                 cudaMemcpyDeviceToHost, m->stream));
+        ELB_CUDA(cudaMemcpyAsync(logits, dev_logits, size_t(m->cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+    if (top) ELB_CUDA(cudaMemcpyAsync(m->top_host, m->top_dev, TOP_BYTES, cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
+    if (top) {  // layout of the result: lse (double), then k ids, then k logits
+        const uint8_t* r = m->top_host;
+        std::memcpy(top->lse, r, sizeof(double));
+        std::memcpy(top->ids, r + 8, size_t(top->k) * sizeof(int32_t));
+        std::memcpy(top->vals, r + 8 + 4 * TOP_MAXK, size_t(top->k) * sizeof(float));
+    }
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
     if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
     ELB_TRY(gemm_tc_check());
@@ -616,7 +632,8 @@ void model_destroy(Model* m) {
     cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
-    cudaFree(m->ap_part); cudaFree(m->ap_counters);
+    cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev);
+    if (m->top_host) cudaFreeHost(m->top_host);
     cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);
     tp_comm_destroy(m->comm);
@@ -791,6 +808,8 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->attn_part, size_t(m->HKV) * m->attn_split * group * (128 + 2) * 4));
     ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(m->HKV) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&m->top_dev, TOP_BYTES));
+    ELB_CUDA(cudaMallocHost(&m->top_host, TOP_BYTES));
     ELB_CUDA(cudaMalloc(&m->ap_part, attn_prefill_scratch_floats(m->max_batch, m->H, m->HKV) * sizeof(float)));
     ELB_CUDA(cudaMalloc(&m->ap_counters, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->ap_counters, 0, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
@@ -803,7 +822,19 @@ int model_finalize(Model* m) {
     return ELB_OK;
 }
 
-int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits) {
+namespace { struct TopOut; }
+int model_eval_impl(Model* m, const int32_t* tokens, int n, int pos0, float* logits, const TopOut* top);
+
+int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* vals, double* lse) {
+    if (!ids || !vals || !lse) return fail(ELB_ERR_INVALID, "eval_top: null argument");
+    if (k < 1 || k > TOP_MAXK || (m && k > m->cfg.n_vocab)) return fail(ELB_ERR_INVALID, "eval_top: k must be between 1 and 64 (and at most n_vocab)");
+    const TopOut top{k, ids, vals, lse};
+    return model_eval_impl(m, tokens, n, pos0, nullptr, &top);
+}
+
+int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits) { return model_eval_impl(m, tokens, n, pos0, logits, nullptr); }
+
+int model_eval_impl(Model* m, const int32_t* tokens, int n, int pos0, float* logits, const TopOut* top) {
     if (!m || !tokens) return fail(ELB_ERR_INVALID, "eval: null argument");
     if (!m->finalized) return fail(ELB_ERR_STATE, "eval: model not finalized");
     if (n <= 0) return fail(ELB_ERR_INVALID, "eval: empty token sequence");
@@ -815,7 +846,8 @@ int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits) 
     const int64_t before = m->launches;
     for (int done = 0; done < n;) {
         const int b = std::min(m->max_batch, n - done);
-        ELB_TRY(chunk(m, tokens + done, b, pos0 + done, done + b == n ? logits : nullptr));
+        const bool last = done + b == n;
+        ELB_TRY(chunk(m, tokens + done, b, pos0 + done, last ? logits : nullptr, last ? top : nullptr));
         done += b;
     }
     m->last_launches = m->launches - before;

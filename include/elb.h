@@ -142,6 +142,14 @@ void elb_model_destroy(elb_model* m);
  * n <= 0 -> ELB_ERR_INVALID; pos0 < 0, pos0+n > n_ctx or a token outside [0, n_vocab) -> ELB_ERR_RANGE. */
 int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits);
 
+/* elb_model_eval with the logits reduced on the device to what a sampler of the reference's kind needs
+ * (src/main.cpp:309-320 computes this on the host from all n_vocab floats of every token): the log-sum-exp of the last
+ * token's logits in double precision, and the k best tokens ordered by (logit descending, id ascending) with their
+ * logits, so that logprob = top_logits[i] - *lse. 1 <= k <= 64. Only 8 + 8k bytes cross to the host. No counterpart in
+ * the reference's backend interface. */
+int elb_model_eval_top(elb_model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* top_logits,
+                       double* lse);
+
 /* Rows of several sequences in one pass (no counterpart in the reference, which serves one sequence at a time:
  * src/main.cpp:499-505 keeps a single `cached` prefix). Row i is token tokens[i] at position pos[i] of sequence seq[i]
  * (0 <= seq[i] < n_seq); the rows of one sequence must come in increasing, consecutive positions, continuing what that

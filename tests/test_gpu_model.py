@@ -187,3 +187,25 @@ def test_long_context(elb):
         assert d_gpu <= max(LOGPROB_TOL, 1.5 * d_cpu), (step, d_gpu, d_cpu)
     gpu.close()
     cpu.close()
+
+
+def test_device_side_top_and_logsumexp(elb):
+    """elb_model_eval_top: the k best tokens by (logit descending, id ascending) and the double-precision log-sum-exp,
+    computed on the device, equal what the host computes from the full logits of the same evaluation."""
+    spec = synth.Spec(name="small", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=3001, layout="q4_k_m",
+                      head_sigma=2e-5)
+    tens = list(synth.generate(spec, 4))
+    gpu = elb.Backend(spec, tens, 40)
+    toks = synth.lcg_tokens(12, spec.n_vocab)
+    full = gpu.eval(toks, 0)
+    for k, (t, pos) in ((5, (toks, 0)), (1, ([7], 12)), (64, ([9], 13))):  # prompt chunk, then single-token steps
+        if len(t) == 1:
+            full = gpu.eval(t, pos)
+        ids, vals, lse = gpu.eval_top(t, pos, k)  # the same tokens at the same positions again: same logits
+        order = np.lexsort((np.arange(spec.n_vocab), -full.astype(np.float64)))[:k]
+        assert np.array_equal(ids, order)
+        assert np.array_equal(vals, full[order])
+        assert abs(lse - ol.logsumexp(full)) <= 1e-12 * max(1.0, abs(lse))
+    with pytest.raises(ValueError):
+        gpu.eval_top([1], 14, 65)
+    gpu.close()
