@@ -6,6 +6,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -202,6 +203,21 @@ class Backend:
             self.close()
             raise
         self._logits_host = None
+
+    @classmethod
+    def from_gguf(cls, path: str, n_ctx: int, device: int = 0, max_batch: int = 0, n_seq: int = 0):
+        """The model of a GGUF file, read and uploaded by the library itself (elb_model_load_gguf)."""
+        h = C.c_void_p()
+        check(lib().elb_model_load_gguf(os.fsencode(path), n_ctx, device, max_batch, n_seq, C.byref(h)))
+        self = cls.__new__(cls)
+        self._h, self._n_ctx, self._logits_host = h, n_ctx, None
+        self._cfg = Config()
+        check(lib().elb_model_config(h, C.byref(self._cfg)))
+        c = self._cfg
+        self.spec = synth.Spec(name=os.path.basename(path), n_layer=c.n_layer, n_embd=c.n_embd, n_ff=c.n_ff, n_head=c.n_head,
+                               n_head_kv=c.n_head_kv, n_vocab=c.n_vocab, layout="gguf", head_dim=c.head_dim,
+                               rope_base=c.rope_base, eps=c.eps)
+        return self
 
     def cfg(self):
         return self._cfg

@@ -53,6 +53,8 @@ SIGNATURES = {
     "elb_model_create": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.POINTER(_vp)]),
     "elb_model_set_tensor": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, _vp, C.c_size_t]),
     "elb_model_finalize": (C.c_int, [_vp]),
+    "elb_model_load_gguf": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
+    "elb_model_config": (C.c_int, [_vp, C.POINTER(Config)]),
     "elb_model_destroy": (None, [_vp]),
     "elb_model_eval": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, _vp]),
     "elb_model_eval_top": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, C.c_int, _i32p, _f32p, C.POINTER(C.c_double)]),

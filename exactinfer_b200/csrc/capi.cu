@@ -305,6 +305,14 @@ int elb_model_set_tensor(elb_model* m, int role, int layer, int ggml_type, int64
     return model_set_tensor(M(m), role, layer, ggml_type, rows, n, bytes, nbytes);
 }
 int elb_model_finalize(elb_model* m) { return model_finalize(M(m)); }
+int elb_model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, elb_model** out) {
+    if (!out) return fail(ELB_ERR_INVALID, "load_gguf: null argument");
+    Model* m = nullptr;
+    ELB_TRY(model_load_gguf(path, n_ctx, device, max_batch, n_seq, &m));  // the file is checked before any device is touched
+    *out = reinterpret_cast<elb_model*>(m);
+    return ELB_OK;
+}
+int elb_model_config(const elb_model* m, elb_config* out) { return model_config(M(m), out); }
 void elb_model_destroy(elb_model* m) { model_destroy(M(m)); }
 int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* logits) {
     return model_eval(M(m), tokens, n, pos0, logits);

@@ -1005,6 +1005,11 @@ int model_hidden(Model* m, float* out) {
     return ELB_OK;
 }
 
+int model_config(const Model* m, elb_config* out) {
+    if (!m || !out) return fail(ELB_ERR_INVALID, "config: null argument");
+    *out = m->cfg;
+    return ELB_OK;
+}
 size_t model_weight_bytes(const Model* m) { return m->weight_bytes; }
 size_t model_kv_bytes_per_token(const Model* m) { return size_t(2) * m->cfg.n_layer * m->HKV * 128 * sizeof(float); }
 int model_device(const Model* m) { return m->device; }

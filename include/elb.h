@@ -135,6 +135,16 @@ int elb_model_set_tensor(elb_model* m, int role, int layer, int ggml_type, int64
                          size_t nbytes);
 int elb_model_finalize(elb_model* m);
 void elb_model_destroy(elb_model* m);
+/* The same constructor straight from a GGUF file (versions 2 and 3): what Gguf::open + read_config + read_tensors +
+ * make_cuda_backend do together in the reference (src/gguf.cpp:204-258, src/model.cpp:38-103,
+ * src/cuda/model_cuda.cu:1900-1913). The file is mapped, its metadata gives the configuration (same keys and
+ * defaults), every tensor is handed over from the mapping and the model is finalized; the mapping is released before
+ * the call returns. Rejected as in the reference: architectures other than qwen3, RoPE scaling, bias tensors,
+ * key_length != value_length, tensor types other than F32 / F16 / Q8_0 / Q4_K / Q6_K. max_batch and n_seq as in
+ * elb_config (0 = defaults). */
+int elb_model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, elb_model** out);
+/* The configuration a model was created with (n_vocab and the rest, e.g. after elb_model_load_gguf). */
+int elb_model_config(const elb_model* m, elb_config* out);
 
 /* Backend::eval (src/model.h:48-50; CudaModel::eval, src/cuda/model_cuda.cu:1648-1658): tokens[0..n) are processed
  * at positions pos0..pos0+n-1 and written to the KV cache (only rows [pos0, pos0+n) are touched); when logits is

@@ -1,0 +1,50 @@
+"""elb_model_load_gguf checks the file before it touches a device: the rejections of the reference's loader
+(src/gguf.cpp, read_config / read_tensors in src/model.cpp:38-103) are testable without a GPU."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import exactinfer_b200 as e
+from exactinfer_b200 import synth
+
+
+def tiny(tmp_path):
+    spec = synth.Spec(name="tiny", n_layer=1, n_embd=256, n_ff=256, n_head=2, n_head_kv=2, n_vocab=64, layout="q8_0")
+    path = os.path.join(tmp_path, "m.gguf")
+    synth.write_gguf(path, spec, list(synth.generate(spec, 1)))
+    return path
+
+
+def test_missing_file(tmp_path):
+    with pytest.raises(ValueError, match="cannot open"):
+        e.Backend.from_gguf(os.path.join(tmp_path, "nope.gguf"), 8)
+
+
+def test_not_a_gguf_file(tmp_path):
+    p = os.path.join(tmp_path, "x.gguf")
+    open(p, "wb").write(b"GGML" + bytes(64))
+    with pytest.raises(ValueError, match="not a GGUF"):
+        e.Backend.from_gguf(p, 8)
+    open(p, "wb").write(b"GGUF" + struct.pack("<I", 1) + bytes(64))
+    with pytest.raises(e.ElbError, match="version"):
+        e.Backend.from_gguf(p, 8)
+
+
+def test_truncated_directory(tmp_path):
+    path = tiny(tmp_path)
+    data = open(path, "rb").read()
+    cut = os.path.join(tmp_path, "cut.gguf")
+    open(cut, "wb").write(data[:200])
+    with pytest.raises(ValueError, match="damaged|missing|past the end"):
+        e.Backend.from_gguf(cut, 8)
+
+
+def test_other_architecture_rejected(tmp_path):
+    path = tiny(tmp_path)
+    data = open(path, "rb").read().replace(b"qwen3", b"qwen9")  # same length: offsets stay valid
+    bad = os.path.join(tmp_path, "arch.gguf")
+    open(bad, "wb").write(data)
+    with pytest.raises(e.ElbError, match="architecture"):
+        e.Backend.from_gguf(bad, 8)

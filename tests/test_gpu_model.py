@@ -209,3 +209,23 @@ def test_device_side_top_and_logsumexp(elb):
     with pytest.raises(ValueError):
         gpu.eval_top([1], 14, 65)
     gpu.close()
+
+
+@pytest.mark.parametrize("layout", ("q4_k_m", "f16"))
+def test_model_loaded_from_gguf_equals_tensor_fed_model(elb, layout, tmp_path):
+    """elb_model_load_gguf (file mapped and parsed by the library) gives bit-identical logits to the model built from the
+    same tensors through elb_model_set_tensor, and reports the file's configuration."""
+    spec = synth.Spec(name="small", n_layer=2, n_embd=256, n_ff=512, n_head=4, n_head_kv=2, n_vocab=640, layout=layout,
+                      head_sigma=2e-5)
+    tens = list(synth.generate(spec, 6))
+    path = os.path.join(tmp_path, "model.gguf")
+    synth.write_gguf(path, spec, tens)
+    a = elb.Backend(spec, tens, 32)
+    b = elb.Backend.from_gguf(path, 32)
+    c = b.cfg()
+    assert (c.n_layer, c.n_embd, c.n_ff, c.n_head, c.n_head_kv, c.n_vocab, c.head_dim) == (2, 256, 512, 4, 2, 640, 128)
+    toks = synth.lcg_tokens(9, spec.n_vocab)
+    assert np.array_equal(a.eval(toks, 0), b.eval(toks, 0))
+    assert np.array_equal(a.eval([5], 9), b.eval([5], 9))
+    a.close()
+    b.close()
