@@ -237,13 +237,23 @@ class Backend:
                                    logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
-    def eval_top(self, tokens, pos0: int, k: int = 1):
+    def eval_top(self, tokens, pos0: int, k: int = 1, allowed=None):
         """eval with the logits reduced on the device: (ids[k], logits[k], log-sum-exp) of the last token, ids ordered by
-        (logit descending, id ascending); logprob of ids[i] = logits[i] - lse."""
+        (logit descending, id ascending); logprob of ids[i] = logits[i] - lse. allowed: boolean mask over the vocabulary
+        (constrained decoding): only allowed tokens are picked, the log-sum-exp still covers all."""
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)
         ids, vals, lse = np.empty(k, np.int32), np.empty(k, np.float32), C.c_double()
-        check(lib().elb_model_eval_top(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), tokens.size, pos0, k,
-                                       ids.ctypes.data_as(C.POINTER(C.c_int32)), capi.fptr(vals), C.byref(lse)))
+        i32 = C.POINTER(C.c_int32)
+        if allowed is None:
+            check(lib().elb_model_eval_top(self._h, tokens.ctypes.data_as(i32), tokens.size, pos0, k, ids.ctypes.data_as(i32),
+                                           capi.fptr(vals), C.byref(lse)))
+        else:
+            bits = np.packbits(np.asarray(allowed, dtype=bool), bitorder="little")
+            words = np.zeros((self.spec.n_vocab + 31) // 32 * 4, np.uint8)
+            words[:bits.size] = bits
+            check(lib().elb_model_eval_top_masked(self._h, tokens.ctypes.data_as(i32), tokens.size, pos0, k,
+                                                  words.ctypes.data_as(C.c_void_p), ids.ctypes.data_as(i32), capi.fptr(vals),
+                                                  C.byref(lse)))
         return ids, vals, lse.value
 
     def eval_batch(self, tokens, seq, pos, want=None, want_logits: bool = True):

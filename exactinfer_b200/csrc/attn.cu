@@ -689,7 +689,9 @@ __global__ void __launch_bounds__(256) k_rmsnorm_rows(float* out, const float* x
 // ---------------------------------------------------------------- logits post-processing
 // What the reference's generate loop does on the host with the n_vocab logits of every token (src/main.cpp:309-320):
 // log-sum-exp in double precision and the k best tokens ordered by (logit descending, id ascending). One block.
-__global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ logits, int n, int k, uint8_t* __restrict__ out) {
+// allowed != nullptr: bit i of the array says whether token i may be picked (the log-sum-exp still covers all tokens).
+__global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ logits, int n, int k, uint8_t* __restrict__ out,
+                                                     const uint32_t* __restrict__ allowed) {
     __shared__ double red_d[32];
     __shared__ float red_f[32];
     __shared__ int red_i[32];
@@ -722,7 +724,7 @@ __global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ l
         int bi = 0x7fffffff;
         for (int i = tid; i < n; i += 1024) {
             const float v = logits[i];
-            const bool after = v < pv || (v == pv && i > pi);
+            const bool after = (v < pv || (v == pv && i > pi)) && (!allowed || ((allowed[i >> 5] >> (i & 31)) & 1u));
             if (after && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
         }
 #pragma unroll
@@ -738,16 +740,17 @@ __global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ l
             for (int w = 0; w < 32; ++w)
                 if (red_f[w] > bv || (red_f[w] == bv && red_i[w] < bi)) { bv = red_f[w]; bi = red_i[w]; }
             s_val = bv; s_idx = bi;
-            ids[r] = bi; vals[r] = bv;
+            ids[r] = bi == 0x7fffffff ? -1 : bi;  // fewer than k tokens allowed: -1 from here on
+            vals[r] = bv;
         }
         __syncthreads();
         pv = s_val; pi = s_idx;
     }
 }
 
-int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s) {
+int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s, const uint32_t* d_allowed) {
     if (!logits || !out || n < 1 || k < 1 || k > TOP_MAXK || k > n) return fail(ELB_ERR_INVALID, "logits_top: bad argument");
-    k_logits_top<<<1, 1024, 0, s>>>(logits, n, k, out);
+    k_logits_top<<<1, 1024, 0, s>>>(logits, n, k, out, d_allowed);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }

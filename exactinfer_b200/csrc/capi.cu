@@ -321,6 +321,11 @@ int elb_model_eval_top(elb_model* m, const int32_t* tokens, int n, int pos0, int
                        double* lse) {
     return model_eval_top(M(m), tokens, n, pos0, k, ids, top_logits, lse);
 }
+int elb_model_eval_top_masked(elb_model* m, const int32_t* tokens, int n, int pos0, int k, const uint32_t* allowed,
+                              int32_t* ids, float* top_logits, double* lse) {
+    if (!allowed) return fail(ELB_ERR_INVALID, "eval_top_masked: null mask");
+    return model_eval_top(M(m), tokens, n, pos0, k, ids, top_logits, lse, allowed);
+}
 int elb_model_eval_batch(elb_model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos,
                          const uint8_t* want, float* logits) {
     return model_eval_batch(M(m), n, tokens, seq, pos, want, logits);

@@ -263,7 +263,7 @@ int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps,
 // TOP_MAXK int32 ids, then TOP_MAXK floats
 constexpr int TOP_MAXK = 64;
 constexpr size_t TOP_BYTES = 8 + size_t(TOP_MAXK) * 8;
-int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s);
+int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s, const uint32_t* d_allowed = nullptr);
 
 
 }  // namespace elb
@@ -328,7 +328,8 @@ int model_config(const Model* m, elb_config* out);
 void model_destroy(Model* m);
 int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits);
 int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* device_ms);
-int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* vals, double* lse);
+int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* vals, double* lse,
+                   const uint32_t* allowed = nullptr);
 int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
                      float* logits);
 int model_stats(const Model* m, float* ms, int64_t* launches);

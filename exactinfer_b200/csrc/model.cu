@@ -98,6 +98,7 @@ struct Model {
     int rows_split = 1;
     uint8_t* top_dev = nullptr;      // device-side logits post-processing: lse, ids, logits
     uint8_t* top_host = nullptr;     // pinned
+    uint32_t* mask_dev = nullptr;    // allowed-token bits of a constrained pick
     float* ap_part = nullptr;        // partial results of the chunked prompt attention
     unsigned* ap_counters = nullptr;
     float* xr = nullptr;            // [max_batch][E] this rank's partial sums before the all-reduce
@@ -367,7 +368,7 @@ int enqueue_decode_step(Model* m) {
 }
 
 // `top`: instead of copying the logits out, reduce them on the device to the k best tokens and the log-sum-exp
-struct TopOut { int k; int32_t* ids; float* vals; double* lse; };
+struct TopOut { int k; int32_t* ids; float* vals; double* lse; const uint32_t* allowed; };
 
 int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits, const TopOut* top = nullptr) {
     std::memcpy(m->tokens_host, tokens, size_t(B) * sizeof(int32_t));
@@ -386,7 +387,9 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits, const
     }
     const float* dev_logits = B == 1 && m->use_mega ? m->logits_step : m->logits;
     if (top) {
-        ELB_TRY(logits_top_launch(dev_logits, m->cfg.n_vocab, top->k, m->top_dev, m->stream));
+        if (top->allowed)  // (pageable source: staged by the runtime before the call returns)
+            ELB_CUDA(cudaMemcpyAsync(m->mask_dev, top->allowed, size_t((m->cfg.n_vocab + 31) / 32) * 4, cudaMemcpyHostToDevice, m->stream));
+        ELB_TRY(logits_top_launch(dev_logits, m->cfg.n_vocab, top->k, m->top_dev, m->stream, top->allowed ? m->mask_dev : nullptr));
         ++m->launches;
     }
     ELB_CUDA(cudaEventRecord(m->ev1, m->stream));
@@ -632,7 +635,7 @@ void model_destroy(Model* m) {
     cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
-    cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev);
+    cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev); cudaFree(m->mask_dev);
     if (m->top_host) cudaFreeHost(m->top_host);
     cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);
@@ -810,6 +813,7 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->top_dev, TOP_BYTES));
     ELB_CUDA(cudaMallocHost(&m->top_host, TOP_BYTES));
+    ELB_CUDA(cudaMalloc(&m->mask_dev, size_t((V + 31) / 32) * 4));
     ELB_CUDA(cudaMalloc(&m->ap_part, attn_prefill_scratch_floats(m->max_batch, m->H, m->HKV) * sizeof(float)));
     ELB_CUDA(cudaMalloc(&m->ap_counters, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->ap_counters, 0, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
@@ -825,10 +829,11 @@ int model_finalize(Model* m) {
 namespace { struct TopOut; }
 int model_eval_impl(Model* m, const int32_t* tokens, int n, int pos0, float* logits, const TopOut* top);
 
-int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* vals, double* lse) {
+int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* vals, double* lse,
+                   const uint32_t* allowed) {
     if (!ids || !vals || !lse) return fail(ELB_ERR_INVALID, "eval_top: null argument");
     if (k < 1 || k > TOP_MAXK || (m && k > m->cfg.n_vocab)) return fail(ELB_ERR_INVALID, "eval_top: k must be between 1 and 64 (and at most n_vocab)");
-    const TopOut top{k, ids, vals, lse};
+    const TopOut top{k, ids, vals, lse, allowed};
     return model_eval_impl(m, tokens, n, pos0, nullptr, &top);
 }
 

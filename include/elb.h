@@ -159,6 +159,12 @@ int elb_model_eval(elb_model* m, const int32_t* tokens, int n, int pos0, float* 
  * the reference's backend interface. */
 int elb_model_eval_top(elb_model* m, const int32_t* tokens, int n, int pos0, int k, int32_t* ids, float* top_logits,
                        double* lse);
+/* The same with a token mask, for constrained decoding (the reference's matcher walks the host copy of the logits in rank
+ * order until it finds an allowed token, src/main.cpp:232-246, src/constrain.h:51-56): bit i of allowed[(n_vocab+31)/32]
+ * says whether token i may be picked; the k best ALLOWED tokens come back (ids -1 when fewer are allowed), the
+ * log-sum-exp still covers the whole vocabulary, so top_logits[i] - *lse is the token's true log-probability. */
+int elb_model_eval_top_masked(elb_model* m, const int32_t* tokens, int n, int pos0, int k, const uint32_t* allowed,
+                              int32_t* ids, float* top_logits, double* lse);
 
 /* Rows of several sequences in one pass (no counterpart in the reference, which serves one sequence at a time:
  * src/main.cpp:499-505 keeps a single `cached` prefix). Row i is token tokens[i] at position pos[i] of sequence seq[i]

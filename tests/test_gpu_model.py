@@ -206,8 +206,20 @@ def test_device_side_top_and_logsumexp(elb):
         assert np.array_equal(ids, order)
         assert np.array_equal(vals, full[order])
         assert abs(lse - ol.logsumexp(full)) <= 1e-12 * max(1.0, abs(lse))
+    # constrained pick: only every third token allowed; the log-sum-exp is still over all tokens
+    full = gpu.eval([3], 14)
+    allowed = np.arange(spec.n_vocab) % 3 == 1
+    ids, vals, lse = gpu.eval_top([3], 14, 4, allowed=allowed)
+    cand = np.where(allowed)[0]
+    order = cand[np.lexsort((cand, -full[cand].astype(np.float64)))[:4]]
+    assert np.array_equal(ids, order) and np.array_equal(vals, full[order])
+    assert abs(lse - ol.logsumexp(full)) <= 1e-12 * max(1.0, abs(lse))
+    only = np.zeros(spec.n_vocab, bool)
+    only[[17, 2999]] = True
+    ids, vals, _ = gpu.eval_top([3], 14, 3, allowed=only)  # fewer allowed than asked for
+    assert set(ids[:2]) == {17, 2999} and ids[2] == -1
     with pytest.raises(ValueError):
-        gpu.eval_top([1], 14, 65)
+        gpu.eval_top([1], 15, 65)
     gpu.close()
 
 
