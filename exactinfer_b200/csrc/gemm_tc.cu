@@ -127,6 +127,7 @@ __host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
 // operands, and in total, summed over launches
 __device__ unsigned long long g_tc_prof[12];
 
+
 struct TcParams {
     const __half* pl_d;      // [rows16][n/256] block scale
     const float* pl_dm;      // Q4_K: [rows16][n/32] fl(dmin*m); else null
@@ -136,10 +137,51 @@ struct TcParams {
     const float* resid;
     int64_t rows16, rows, ldy;
     int B, n, epilogue;
-    int row_tiles, tok_tiles;  // the grid walks row_tiles * tok_tiles output tiles, token tiles of one row tile adjacent
+    int row_tiles, tok_tiles;  // row_tiles * tok_tiles output tiles, token tiles of one row tile adjacent
+    int waves;                 // whole tiles per CTA: CTA c computes tiles c, c + grid, ... (waves of them)
+    int per;                   // the tiles behind the whole waves are cut in (tile, 256-block) units, `per` per CTA:
+                               // CTA c owns units [c * per, (c + 1) * per) of them
+    float* scratch;            // [grid][T][TC_ROWS] partial sums of a tile piece that does not hold the tile's first block
+    unsigned* flags;           // [grid] launch number once the CTA's scratch is written
+    unsigned* ctl;             // {launches completed, CTAs of this launch that are done}: kept by the kernel itself, so a
+                               // launch replayed from a graph numbers itself like any other
     int* err;
     int prof;
 };
+
+// A grid of one CTA per SM walks the output tiles in whole waves; the tiles that do not fill a wave would leave most
+// SMs idle for a whole tile's time, so they are cut by (tile, 256-block) units instead: every CTA gets the same number
+// of consecutive units, a tile is shared by the CTA that holds its first blocks and one or more CTAs after it. Those
+// leave their partial sums (fp32, after the block scales) in `scratch` and the CTA with the first blocks adds them in
+// CTA order and writes the tile. The shared tiles come first: a CTA's share of them is at most two pieces, the piece
+// without a tile's first blocks first, so nobody waits long, and the whole tiles after them keep neighbouring CTAs on
+// neighbouring tiles (the weight tile of a row is fetched from HBM once for all its token tiles).
+struct Piece { int tile, kb0, kb1; };
+// Piece i of this CTA: 0 and 1 are its share of the shared tiles (a share is no longer than a tile, so it touches at
+// most two), 2 + w is its tile of whole wave w. False when the CTA has no such piece. Everything is recomputed from
+// the launch parameters, so that the walk costs the three roles one register.
+__device__ __forceinline__ bool piece_at(const int i, const int per, const int waves, const int n_tiles, const int nkb, Piece& pc) {
+    const int tile0 = waves * int(gridDim.x);  // the shared tiles follow the whole waves
+    if (i >= 2) {
+        pc.tile = int(blockIdx.x) + (i - 2) * int(gridDim.x);
+        pc.kb0 = 0;
+        pc.kb1 = nkb;
+        return pc.tile < n_tiles;  // (the last wave may be a partial one when nothing is shared: ELB_TC_NO_SPLIT)
+    }
+    const int units = max(n_tiles - tile0, 0) * nkb;
+    const int u0 = min(int(blockIdx.x) * per, units), u1 = min(u0 + per, units);
+    const int tl = u0 / nkb, k0 = u0 - tl * nkb, k1 = min(nkb, k0 + (u1 - u0));
+    if (i == 0) {
+        pc.tile = tile0 + tl;
+        pc.kb0 = k0;
+        pc.kb1 = k1;
+        return u0 < u1;
+    }
+    pc.tile = tile0 + tl + 1;
+    pc.kb0 = 0;
+    pc.kb1 = u1 - (tl + 1) * nkb;
+    return pc.kb1 > 0;
+}
 
 template <int NL> struct TcShape {
     static constexpr int T = NL == 4 ? 48 : 64;       // tokens per tile
@@ -173,7 +215,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     float* d_s = dm_s + 2 * TC_ROWS * 8;       // [2][TC_ROWS]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nk = p.n / TC_KSTAGE, nkb = p.n / 256, n_tiles = p.row_tiles * p.tok_tiles;
+    const int nkb = p.n / 256, n_tiles = p.row_tiles * p.tok_tiles;
+    int* s_fail = reinterpret_cast<int*>(tmem_slot + 1);
+    unsigned* s_seq = reinterpret_cast<unsigned*>(tmem_slot + 2);
+    if (tid == 0) {
+        *s_fail = 0;
+        // the count moves only when every CTA of a launch is done, hence after every CTA of it has read it
+        *s_seq = *reinterpret_cast<volatile unsigned*>(p.ctl) + 1;
+    }
 
     // zero blocks in front of, between and behind the limb stages
     for (int z = 0; z <= TC_STAGES; ++z) {
@@ -195,10 +244,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
 
     if (warp == TC_EPI_WARPS) {
         if (lane == 0) {  // ---- TMA producer
-            int it = 0;  // stages filled so far, over all tiles of this CTA
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int row0 = tile / p.tok_tiles * TC_ROWS, tok0 = tile % p.tok_tiles * T;
-            for (int kt = 0; kt < nk && ok; ++kt, ++it) {
+            int it = 0;  // stages filled so far, over all pieces of this CTA
+            Piece pc;
+            for (int pi = 0; pi < 2 + p.waves && ok; ++pi) {
+            if (!piece_at(pi, p.per, p.waves, n_tiles, nkb, pc)) continue;
+            const int row0 = pc.tile / p.tok_tiles * TC_ROWS, tok0 = pc.tile % p.tok_tiles * T;
+            for (int kt = 2 * pc.kb0; kt < 2 * pc.kb1 && ok; ++kt, ++it) {
                 const int s = it % TC_STAGES;
                 ok = mbar_wait(empty + s, ((it / TC_STAGES) & 1) ^ 1);
                 if (!ok) break;
@@ -217,8 +268,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             int it = 0;
             long long w_acc = 0, w_ops = 0;
             const long long t_start = clock64();
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x)
-            for (int kt = 0; kt < nk && ok; ++kt, ++it) {
+            Piece pc;
+            for (int pi = 0; pi < 2 + p.waves && ok; ++pi)
+            for (int kt = piece_at(pi, p.per, p.waves, n_tiles, nkb, pc) ? 2 * pc.kb0 : 2 * pc.kb1; kt < 2 * pc.kb1 && ok; ++kt, ++it) {
                 const int s = it % TC_STAGES, kb = it >> 1, acc = kb & 1;  // kb: 256-blocks issued so far (nk is even)
                 long long t0 = clock64();
                 if ((kt & 1) == 0) {  // first half of a 256-block: its accumulator must have been drained
@@ -258,8 +310,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
         const int q4 = warp & 3, th = warp >> 2, my_row = q4 * 32 + lane;
         const int nblk = p.n / 256, nsub = p.n / 32;
         int kbt = 0;  // 256-blocks drained so far, over all tiles of this CTA
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int row0 = tile / p.tok_tiles * TC_ROWS, tok0 = tile % p.tok_tiles * T;
+        Piece pc;
+        for (int pi = 0; pi < 2 + p.waves && ok; ++pi) {
+        if (!piece_at(pi, p.per, p.waves, n_tiles, nkb, pc)) continue;
+        const int row0 = pc.tile / p.tok_tiles * TC_ROWS, tok0 = pc.tile % p.tok_tiles * T;
         const int64_t R = row0 + my_row;
         float accf[TH];
 #pragma unroll
@@ -286,8 +340,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 screg.x = r < p.rows16 ? __half2float(p.pl_d[r * nblk + kb]) : 0.f;
             }
         };
-        fetch(0);
-        for (int kb = 0; kb < nkb && ok; ++kb, ++kbt) {
+        const bool is_tail = pc.kb0 > 0, is_open = pc.kb0 == 0 && pc.kb1 < nkb;
+        const int kb_end = pc.kb1;
+        fetch(pc.kb0);
+        for (int kb = pc.kb0; kb < kb_end && ok; ++kb, ++kbt) {
             const int acc = kbt & 1;
             float* xb = xs_s + acc * (T * 8);
             float* dmb = dm_s + acc * (TC_ROWS * 8);
@@ -299,7 +355,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             }
             if (etid < 2 * TC_ROWS) *reinterpret_cast<float4*>(dmb + etid * 4) = screg;
             else if (etid < 3 * TC_ROWS) db[etid - 2 * TC_ROWS] = screg.x;
-            if (kb + 1 < nkb) fetch(kb + 1);
+            if (kb + 1 < kb_end) fetch(kb + 1);
             asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");  // epilogue warps only
             // Q4_K: minus sum over the 8 sub-blocks of fl(dmin*m) * sum(X). It does not need the accumulator: it runs
             // while the tensor core is still working on this block.
@@ -327,25 +383,85 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t tbase = tmem_base + acc * 256 + (uint32_t(q4 * 32) << 16) + th * TH;
-            int v[NL + 1][TH];  // every load of the drain is issued before the one wait
-#pragma unroll
-            for (int c = 0; c < TH / 4; ++c)
-#pragma unroll
-                for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + c * 4, *reinterpret_cast<int (*)[4]>(&v[j][c * 4]));
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty + acc);  // accumulator in registers: the issuer may overwrite it
             // sum_j 256^j v_j with few int->float conversions: neighbouring columns are joined in int32 first
             // (|v_j| < 2^23, so v_j + 256 v_{j+1} fits), as the reference joins its limb pairs (I0 = P0 + 256 P1,
             // src/cuda/model_cuda.cu:962-994); the top column of four limbs is small enough for the exact
             // add-a-constant conversion
+            auto join = [&](const int(&w)[NL + 1][4], const int t0) {
 #pragma unroll
-            for (int t = 0; t < TH; ++t) {
-                const int i01 = v[0][t] + (v[1][t] << 8), i23 = v[2][t] + (v[3][t] << 8);
-                float f = NL == 4 ? fmaf(i2f_small(v[4][t]), 65536.0f, float(i23)) : float(i23);
-                f = fmaf(f, 65536.0f, float(i01));
-                accf[t] = fmaf(d, f, accf[t]);
+                for (int t = 0; t < 4; ++t) {
+                    const int i01 = w[0][t] + (w[1][t] << 8), i23 = w[2][t] + (w[3][t] << 8);
+                    float f = NL == 4 ? fmaf(i2f_small(w[NL][t]), 65536.0f, float(i23)) : float(i23);
+                    f = fmaf(f, 65536.0f, float(i01));
+                    accf[t0 + t] = fmaf(d, f, accf[t0 + t]);
+                }
+            };
+            auto release = [&]() {  // accumulator in registers: the issuer may overwrite it
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty + acc);
+            };
+            if constexpr (TH <= 12) {  // every load of the drain is issued before the one wait
+                int v[TH / 4][NL + 1][4];
+#pragma unroll
+                for (int c = 0; c < TH / 4; ++c)
+#pragma unroll
+                    for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + c * 4, v[c][j]);
+                tmem_ld_wait();
+                release();
+#pragma unroll
+                for (int c = 0; c < TH / 4; ++c) join(v[c], c * 4);
+            } else {
+                // Sixteen tokens of four columns would not leave room in the 96 registers a thread of this kernel can
+                // have: the drain goes four tokens at a time, two such chunks in flight (the loads of chunk c + 1 are
+                // issued before chunk c is worked on, so their latency is covered).
+                int v[2][NL + 1][4];
+#pragma unroll
+                for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T, v[0][j]);
+#pragma unroll
+                for (int c = 0; c < TH / 4; ++c) {
+                    tmem_ld_wait();
+                    if (c + 1 < TH / 4) {
+#pragma unroll
+                        for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + (c + 1) * 4, v[(c + 1) & 1][j]);
+                    } else {
+                        release();
+                    }
+                    join(v[c & 1], c * 4);
+                }
+            }
+        }
+        if (ok && is_tail) {  // not the tile's first blocks: leave the partial sums to the CTA that holds them
+            float* sl = p.scratch + (size_t(blockIdx.x) * T + th * TH) * TC_ROWS + my_row;  // a warp stores 32 neighbours
+#pragma unroll
+            for (int t = 0; t < TH; ++t) sl[t * TC_ROWS] = accf[t];
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+            if (etid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.flags + blockIdx.x), "r"(*s_seq) : "memory");
+            continue;
+        }
+        if (ok && is_open) {  // the tile's first blocks but not its last: add the pieces of the CTAs after this one
+            const int c_last = ((pc.tile - p.waves * int(gridDim.x) + 1) * nkb - 1) / p.per;
+            for (int c2 = int(blockIdx.x) + 1; c2 <= c_last; ++c2) {
+                if (etid == 0) {
+                    const unsigned seq = *s_seq;
+                    unsigned seen = 0, it2 = 0;
+                    do {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.flags + c2) : "memory");
+                    } while (seen != seq && ++it2 < TC_SPIN_LIMIT);
+                    if (seen != seq) *s_fail = 1;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+                if (*s_fail) { ok = false; break; }
+                const float* sl = p.scratch + (size_t(c2) * T + th * TH) * TC_ROWS + my_row;
+#pragma unroll
+                for (int t = 0; t < TH; t += 4) {  // four loads in flight
+                    float part[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) part[j] = __ldcg(sl + (t + j) * TC_ROWS);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) accf[t + j] += part[j];
+                }
             }
         }
         if (ok) {
@@ -371,6 +487,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (warp == TC_EPI_WARPS + 1) tmem_dealloc(tmem_base, 512);
+    if (tid == 0) {  // the last CTA to finish closes the launch
+        __threadfence();
+        if (atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1) {
+            p.ctl[1] = 0;
+            __threadfence();
+            atomicAdd(p.ctl, 1u);
+        }
+    }
 }
 
 // ---------------------------------------------------------------- host side
@@ -458,11 +582,30 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
     ELB_TRY(make_map(&mapW, w->planes, uint64_t(w->n), uint64_t(rows16), 2, TC_ROWS));
     ELB_TRY(make_map(&mapX, d_limbs, uint64_t(w->n), uint64_t(B), 4, uint32_t(T)));
     const int row_tiles = int((rows16 + TC_ROWS - 1) / TC_ROWS), tok_tiles = (B + T - 1) / T;
-    TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
-               row_tiles, tok_tiles, err_dev, tc_prof_on() ? 1 : 0};
     DeviceInfo di;
     ELB_TRY(device_info(w->device, &di));
-    const dim3 grid(unsigned(std::min(row_tiles * tok_tiles, di.sm_count)));  // persistent: one CTA per SM walks the tiles
+    const int64_t n_tiles = int64_t(row_tiles) * tok_tiles, nkb = w->n / 256;
+    if (n_tiles * nkb >= (int64_t(1) << 31)) return fail(ELB_ERR_UNSUPPORTED, "matmul: too many tiles for 32-bit arithmetic");
+    // persistent, one CTA per SM: whole waves of tiles, then the rest in equal shares of (tile, 256-block) units
+    static const bool no_split = [] { const char* v = std::getenv("ELB_TC_NO_SPLIT"); return v && v[0] == '1'; }();
+    const int waves = int(no_split ? (n_tiles + di.sm_count - 1) / di.sm_count : n_tiles / di.sm_count);
+    const int64_t units = std::max<int64_t>(n_tiles - int64_t(waves) * di.sm_count, 0) * nkb;
+    const int grid_n = waves > 0 ? int(std::min<int64_t>(n_tiles, di.sm_count)) : int(std::min<int64_t>(units, di.sm_count));
+    const int per = int((units + grid_n - 1) / grid_n);
+    // scratch of the shared tiles and the launch counter, once per device
+    static thread_local float* scratch[64] = {};
+    static thread_local unsigned* flags[64] = {};
+    static thread_local unsigned* ctl[64] = {};
+    if (!scratch[w->device]) {
+        ELB_CUDA(cudaMalloc(&scratch[w->device], size_t(di.sm_count) * TC_ROWS * 64 * sizeof(float)));
+        ELB_CUDA(cudaMalloc(&flags[w->device], size_t(di.sm_count) * sizeof(unsigned)));
+        ELB_CUDA(cudaMemset(flags[w->device], 0, size_t(di.sm_count) * sizeof(unsigned)));
+        ELB_CUDA(cudaMalloc(&ctl[w->device], 2 * sizeof(unsigned)));
+        ELB_CUDA(cudaMemset(ctl[w->device], 0, 2 * sizeof(unsigned)));
+    }
+    TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
+               row_tiles, tok_tiles, waves, per, scratch[w->device], flags[w->device], ctl[w->device], err_dev, tc_prof_on() ? 1 : 0};
+    const dim3 grid{unsigned(grid_n)};
     static thread_local bool configured = false;
     if (!configured) {
         ELB_CUDA(cudaFuncSetAttribute(k_gemm_tc<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<3>::SMEM));

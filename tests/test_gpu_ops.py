@@ -131,6 +131,22 @@ def test_matmul_matches_oracle(elb, t, b):
         check_matvec(y[i], wb, t, rows, n, x[i])
 
 
+@pytest.mark.parametrize("t,nl,b", ((synth.Q4_K, 4, 560), (synth.Q6_K, 3, 530)))
+def test_matmul_whole_waves_and_shared_tiles(elb, t, nl, b):
+    """More output tiles than SMs: the tensor-core kernel computes whole waves of tiles, cuts the remaining tiles by
+    256-blocks over all CTAs and adds the partial sums of a shared tile in a fixed order (twice the same bits)."""
+    rng = np.random.default_rng(b)
+    rows, n = 1700, 768  # 14 row tiles x 12 (48 tokens) or 9 (64 tokens) token tiles of 3 blocks each
+    wb = synth.rand_weight(rng, t, rows, n)
+    x = rng.normal(size=(b, n)).astype(np.float32)
+    x[5] *= 1e4
+    w = elb.Weight(t, rows, n, wb, planes=True)
+    y = w.matmul(x, nl)
+    for i in [5] + list(range(0, b, 37)) + [b - 1]:
+        check_matvec(y[i], wb, t, rows, n, x[i])
+    assert np.array_equal(bits(y), bits(w.matmul(x, nl))), "matmul must be deterministic"
+
+
 def test_rmsnorm_matches_oracle(elb):
     rng = np.random.default_rng(8)
     for n in (128, 2560):
