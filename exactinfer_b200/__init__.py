@@ -205,10 +205,16 @@ class Backend:
         self._logits_host = None
 
     @classmethod
-    def from_gguf(cls, path: str, n_ctx: int, device: int = 0, max_batch: int = 0, n_seq: int = 0):
-        """The model of a GGUF file, read and uploaded by the library itself (elb_model_load_gguf)."""
+    def from_gguf(cls, path: str, n_ctx: int, device: int = 0, max_batch: int = 0, n_seq: int = 0, tp=None):
+        """The model of a GGUF file, read and uploaded by the library itself (elb_model_load_gguf); tp = (rank, size,
+        id) makes this process one rank of a tensor-parallel group that loads the same file (elb_model_load_gguf_tp)."""
         h = C.c_void_p()
-        check(lib().elb_model_load_gguf(os.fsencode(path), n_ctx, device, max_batch, n_seq, C.byref(h)))
+        if tp is None:
+            check(lib().elb_model_load_gguf(os.fsencode(path), n_ctx, device, max_batch, n_seq, C.byref(h)))
+        else:
+            rank, size, ident = tp
+            buf = C.create_string_buffer(bytes(ident), 128)
+            check(lib().elb_model_load_gguf_tp(os.fsencode(path), n_ctx, device, max_batch, n_seq, rank, size, buf, C.byref(h)))
         self = cls.__new__(cls)
         self._h, self._n_ctx, self._logits_host = h, n_ctx, None
         self._cfg = Config()

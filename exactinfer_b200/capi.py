@@ -73,6 +73,7 @@ SIGNATURES = {
                                     C.c_size_t, _vp, C.c_size_t]),
     "elb_tp_unique_id": (C.c_int, [_vp]),
     "elb_model_create_tp": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
+    "elb_model_load_gguf_tp": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "elb_bench_matvec": (C.c_int, [C.POINTER(_vp), C.c_int, _vp, _vp, C.c_int, C.c_int, _f32p]),
     "elb_bench_matmul": (C.c_int, [C.POINTER(_vp), C.c_int, _vp, C.c_int64, _vp, C.c_int, C.c_int, _f32p]),
 }

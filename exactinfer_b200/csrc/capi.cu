@@ -308,7 +308,15 @@ int elb_model_finalize(elb_model* m) { return model_finalize(M(m)); }
 int elb_model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, elb_model** out) {
     if (!out) return fail(ELB_ERR_INVALID, "load_gguf: null argument");
     Model* m = nullptr;
-    ELB_TRY(model_load_gguf(path, n_ctx, device, max_batch, n_seq, &m));  // the file is checked before any device is touched
+    ELB_TRY(model_load_gguf(path, n_ctx, device, max_batch, n_seq, 0, 1, nullptr, &m));  // the file is checked before any device is touched
+    *out = reinterpret_cast<elb_model*>(m);
+    return ELB_OK;
+}
+int elb_model_load_gguf_tp(const char* path, int n_ctx, int device, int max_batch, int n_seq, int tp_rank, int tp_size,
+                           const void* id128, elb_model** out) {
+    if (!out) return fail(ELB_ERR_INVALID, "load_gguf: null argument");
+    Model* m = nullptr;
+    ELB_TRY(model_load_gguf(path, n_ctx, device, max_batch, n_seq, tp_rank, tp_size, id128, &m));
     *out = reinterpret_cast<elb_model*>(m);
     return ELB_OK;
 }

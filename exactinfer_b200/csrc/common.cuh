@@ -323,7 +323,8 @@ int model_create(const elb_config* cfg, int n_ctx, int device, Model** out);
 int model_create_tp(const elb_config* cfg, int n_ctx, int device, int rank, int size, const void* id128, Model** out);
 int model_set_tensor(Model* m, int role, int layer, int type, int64_t rows, int64_t n, const void* bytes, size_t nbytes);
 int model_finalize(Model* m);
-int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, Model** out);  // gguf_load.cu
+int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, int tp_rank, int tp_size,
+                    const void* id128, Model** out);  // gguf_load.cu
 int model_config(const Model* m, elb_config* out);
 void model_destroy(Model* m);
 int model_eval(Model* m, const int32_t* tokens, int n, int pos0, float* logits);

@@ -120,7 +120,8 @@ struct Mapping {
 
 }  // namespace
 
-int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, Model** out) {
+int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int n_seq, int tp_rank, int tp_size,
+                    const void* id128, Model** out) {
     if (!path || !out) return fail(ELB_ERR_INVALID, "load_gguf: null argument");
     Mapping map;
     map.fd = open(path, O_RDONLY);
@@ -196,7 +197,9 @@ int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int 
     cfg.n_vocab = int(emb->ne[1]);
 
     Model* m = nullptr;
-    ELB_TRY(model_create(&cfg, n_ctx, device, &m));
+    // under tensor parallelism every rank maps the whole file; model_set_tensor keeps this rank's cut of each tensor,
+    // so only those pages of the mapping are read for the column-parallel matrices
+    ELB_TRY(model_create_tp(&cfg, n_ctx, device, tp_rank, tp_size, id128, &m));
     auto give = [&](const std::string& name, int role, int layer, bool required) -> int {
         const TensorInfo* t = find(name);
         if (!t) return required ? fail(ELB_ERR_INVALID, "load_gguf: tensor " + name + " is missing") : ELB_OK;

@@ -213,6 +213,11 @@ int elb_tp_unique_id(void* id128);
  * called by all ranks with the same arguments; every rank receives the full logits. */
 int elb_model_create_tp(const elb_config* cfg, int n_ctx, int device, int tp_rank, int tp_size, const void* id128,
                         elb_model** out);
+/* elb_model_load_gguf for one rank of a tensor-parallel group: every rank maps the same file and uploads its own cut
+ * of each tensor (the per-rank slicing that upload_group / upload_lin, src/cuda/model_cuda.cu:1450-1528, would need for
+ * a sharded model; the reference has no such path). Collective like elb_model_create_tp. */
+int elb_model_load_gguf_tp(const char* path, int n_ctx, int device, int max_batch, int n_seq, int tp_rank, int tp_size,
+                           const void* id128, elb_model** out);
 
 /* ---- timing helpers for microbenchmarks: run the device-pointer matvec `iters` times over `n_w` weights in
  * rotation (so that the working set exceeds L2) and return the average device time per call in ms. */

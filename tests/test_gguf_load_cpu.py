@@ -32,6 +32,14 @@ def test_not_a_gguf_file(tmp_path):
         e.Backend.from_gguf(p, 8)
 
 
+def test_tensor_parallel_load_checks_the_file_first(tmp_path):
+    """elb_model_load_gguf_tp: the same checks before any device or communicator is touched."""
+    p = os.path.join(tmp_path, "x.gguf")
+    open(p, "wb").write(b"GGML" + bytes(64))
+    with pytest.raises(ValueError, match="not a GGUF"):
+        e.Backend.from_gguf(p, 8, tp=(1, 2, bytes(128)))
+
+
 def test_truncated_directory(tmp_path):
     path = tiny(tmp_path)
     data = open(path, "rb").read()

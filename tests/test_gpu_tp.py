@@ -18,14 +18,14 @@ def device_count():
     return capi.lib().elb_device_count() if ok else 0
 
 
-@pytest.mark.parametrize("layout", ("q4_k_m", "q8_0", "f16"))
-def test_two_ranks_match_oracle(layout):
+@pytest.mark.parametrize("layout,source", (("q4_k_m", ""), ("q8_0", ""), ("f16", ""), ("q4_k_m", "gguf")))
+def test_two_ranks_match_oracle(layout, source):
     if device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     with tempfile.TemporaryDirectory() as tmp:
         idf = os.path.join(tmp, "nccl_id")
-        procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_gpu_worker.py"), str(r), "2", idf, layout],
+        procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_gpu_worker.py"), str(r), "2", idf, layout, source],
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
         outs = []
         for p in procs:

@@ -1,6 +1,6 @@
 """One rank of the 2-GPU tensor-parallel parity check (started by test_gpu_tp.py): Backend(tp=...) on GPU `rank`, a prompt
 chunk then single-token steps, every rank compares the gathered logits with the CPU oracle's whole-model result.
-usage: tp_gpu_worker.py RANK SIZE ID_FILE LAYOUT"""
+usage: tp_gpu_worker.py RANK SIZE ID_FILE LAYOUT [gguf]   (gguf: every rank loads the same GGUF file itself)"""
 import os
 import sys
 import time
@@ -38,7 +38,19 @@ def main():
                       layout=layout, head_sigma=2e-5)
     tens = list(synth.generate(spec, 33))
     n_prompt, n_decode = 40, 5
-    gpu = e.Backend(spec, tens, n_prompt + n_decode + 1, device=rank, tp=(rank, size, ident))
+    if len(sys.argv) > 5 and sys.argv[5] == "gguf":  # the library maps the file and uploads this rank's cuts
+        path = id_file + ".gguf"
+        if rank == 0:
+            synth.write_gguf(path + ".tmp", spec, tens)
+            os.replace(path + ".tmp", path)
+        t0 = time.time()
+        while not os.path.exists(path):
+            if time.time() - t0 > 120:
+                raise SystemExit("rank 0 never wrote the model file")
+            time.sleep(0.05)
+        gpu = e.Backend.from_gguf(path, n_prompt + n_decode + 1, device=rank, tp=(rank, size, ident))
+    else:
+        gpu = e.Backend(spec, tens, n_prompt + n_decode + 1, device=rank, tp=(rank, size, ident))
     cpu = ol.OracleModel(spec, tens, n_prompt + n_decode + 1)
     toks = synth.lcg_tokens(n_prompt, spec.n_vocab)
 
