@@ -82,6 +82,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
+    ap.add_argument("--gemm-micro", action="store_true",
+                    help="only time the prompt-chunk GEMM on the five linear shapes of the 4B model at 512 tokens")
     return ap.parse_args()
 
 
@@ -242,6 +244,32 @@ def microbench_matvec(e, device, iters=480, copies=24):
     for w in ws:
         w.close()
     return ms.value
+
+
+def microbench_gemm(args):
+    """The limb GEMM (split of the 512 fp32 rows + k_gemm_tc) on the linear shapes of the Qwen3-4B layer with the limb
+    counts the model uses, 4 weight copies in rotation, best of 3 runs of 40 launches; one JSON line."""
+    import ctypes as C
+    import exactinfer_b200 as e
+    from exactinfer_b200 import capi
+    shapes = (("q", 4096, 2560, 4), ("k", 1024, 2560, 4), ("attn_output", 2560, 4096, 3), ("gate|up", 19456, 2560, 3),
+              ("ffn_down", 2560, 9728, 4))
+    rng = np.random.default_rng(SEED + 2)
+    out = {"metric": "k_gemm_tc microbenchmark, Q4_K, 512 tokens (limb split included)", "unit": "us", "shapes": {}}
+    for name, rows, n, nl in shapes:
+        base = synth.rand_q4_k(rng, rows, n)
+        ws = [e.Weight(synth.Q4_K, rows, n, base, planes=True) for _ in range(4)]
+        x = e.DeviceBuffer.from_array(rng.normal(size=(PROMPT, n)).astype(np.float32))
+        y = e.DeviceBuffer(rows * PROMPT * 4)
+        arr = (C.c_void_p * 4)(*[w._h for w in ws])
+        ms, best = C.c_float(), 1e9
+        for _ in range(3):
+            capi.check(capi.lib().elb_bench_matmul(arr, 4, x.ptr, PROMPT, y.ptr, nl, 40, C.byref(ms)))
+            best = min(best, ms.value)
+        out["shapes"][f"{name} {rows}x{n} nl{nl}"] = {"us": best * 1e3, "tops_single_count": 2.0 * rows * n * PROMPT / best / 1e9}
+        for w in ws:
+            w.close()
+    emit(json.dumps(out))
 
 
 # ---------------------------------------------------------------- our arm
@@ -412,7 +440,9 @@ if __name__ == "__main__":
     REAL_STDOUT = os.dup(1)
     os.dup2(2, 1)
     a = parse_args()
-    if a.impl == "reference":
+    if a.gemm_micro:
+        microbench_gemm(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

@@ -183,8 +183,13 @@ __device__ __forceinline__ bool piece_at(const int i, const int per, const int w
     return pc.kb1 > 0;
 }
 
-template <int NL> struct TcShape {
-    static constexpr int T = NL == 4 ? 48 : 64;       // tokens per tile
+// Tokens per tile. The accumulator has (NL + 1) * T columns, twice (double buffering) in the 512 TMEM columns: at most 64
+// tokens for three limbs, 48 for four. Small batches (decode steps of several sequences) take narrower tiles, so that
+// the tensor core and the epilogue do not work on columns that hold no token.
+constexpr int tc_wide(int nl) { return nl == 4 ? 48 : 64; }
+
+template <int NL, int TT> struct TcShape {
+    static constexpr int T = TT;                      // tokens per tile
     static constexpr int N = (NL + 1) * T;            // accumulator columns: (digit weight j, token)
     static constexpr int ZB = T * 128;                // one block of zero rows
     static constexpr int LB = NL * T * 128;           // limb rows of one stage
@@ -195,10 +200,10 @@ template <int NL> struct TcShape {
     static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + XS_BYTES + SC_BYTES + 1024;  // + barriers + slack
 };
 
-template <int NL>
+template <int NL, int TT>
 __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapW,
                                                           const __grid_constant__ CUtensorMap mapX, const TcParams p) {
-    using S = TcShape<NL>;
+    using S = TcShape<NL, TT>;
     constexpr int T = S::T, N = S::N;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -442,25 +447,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
         }
         if (ok && is_open) {  // the tile's first blocks but not its last: add the pieces of the CTAs after this one
             const int c_last = ((pc.tile - p.waves * int(gridDim.x) + 1) * nkb - 1) / p.per;
-            for (int c2 = int(blockIdx.x) + 1; c2 <= c_last; ++c2) {
-                if (etid == 0) {
-                    const unsigned seq = *s_seq;
+            // the pieces finish at about the same time: the lanes of one warp wait for one flag each, then everybody
+            // fetches the pieces, a few of them in flight at once, and adds them in CTA order
+            if (warp == 0) {
+                const unsigned seq = *s_seq;
+                for (int c2 = int(blockIdx.x) + 1 + lane; c2 <= c_last; c2 += 32) {
                     unsigned seen = 0, it2 = 0;
                     do {
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.flags + c2) : "memory");
                     } while (seen != seq && ++it2 < TC_SPIN_LIMIT);
                     if (seen != seq) *s_fail = 1;
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
-                if (*s_fail) { ok = false; break; }
-                const float* sl = p.scratch + (size_t(c2) * T + th * TH) * TC_ROWS + my_row;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+            if (*s_fail) ok = false;
+            constexpr int G = TH >= 16 ? 1 : 16 / TH;  // pieces fetched together
+            for (int c2 = int(blockIdx.x) + 1; c2 <= c_last && ok; c2 += G) {
+                float part[G][TH >= 16 ? 4 : TH];
 #pragma unroll
-                for (int t = 0; t < TH; t += 4) {  // four loads in flight
-                    float part[4];
+                for (int t0 = 0; t0 < TH; t0 += 4 * (TH >= 16 ? 1 : TH / 4)) {
+                    constexpr int W = TH >= 16 ? 4 : TH;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) part[j] = __ldcg(sl + (t + j) * TC_ROWS);
+                    for (int q = 0; q < G; ++q) {
+                        const int cq = min(c2 + q, c_last);  // (a piece past the last one is read again and not added)
+                        const float* sl = p.scratch + (size_t(cq) * T + th * TH + t0) * TC_ROWS + my_row;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) accf[t + j] += part[j];
+                        for (int j = 0; j < W; ++j) part[q][j] = __ldcg(sl + j * TC_ROWS);
+                    }
+#pragma unroll
+                    for (int q = 0; q < G; ++q)
+                        if (c2 + q <= c_last) {
+#pragma unroll
+                            for (int j = 0; j < W; ++j) accf[t0 + j] += part[q][j];
+                        }
                 }
             }
         }
@@ -578,7 +597,9 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
     const int64_t rows16 = w->tiles * 16;
     CUtensorMap mapW, mapX;
     const bool four = nl >= 4;
-    const int T = four ? TcShape<4>::T : TcShape<3>::T;
+    // tokens per tile: the widest tile for prompt chunks; 16 or 32 when that covers the batch (or wastes less of it)
+    const int wide = tc_wide(four ? 4 : 3);
+    const int T = B <= 16 ? 16 : B <= 32 ? 32 : B <= 64 && (B + 31) / 32 * 32 < (B + wide - 1) / wide * wide ? 32 : wide;
     ELB_TRY(make_map(&mapW, w->planes, uint64_t(w->n), uint64_t(rows16), 2, TC_ROWS));
     ELB_TRY(make_map(&mapX, d_limbs, uint64_t(w->n), uint64_t(B), 4, uint32_t(T)));
     const int row_tiles = int((rows16 + TC_ROWS - 1) / TC_ROWS), tok_tiles = (B + T - 1) / T;
@@ -606,14 +627,19 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
     TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
                row_tiles, tok_tiles, waves, per, scratch[w->device], flags[w->device], ctl[w->device], err_dev, tc_prof_on() ? 1 : 0};
     const dim3 grid{unsigned(grid_n)};
-    static thread_local bool configured = false;
-    if (!configured) {
-        ELB_CUDA(cudaFuncSetAttribute(k_gemm_tc<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<3>::SMEM));
-        ELB_CUDA(cudaFuncSetAttribute(k_gemm_tc<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcShape<4>::SMEM));
-        configured = true;
-    }
-    if (four) k_gemm_tc<4><<<grid, TC_THREADS, TcShape<4>::SMEM, s>>>(mapW, mapX, p);
-    else k_gemm_tc<3><<<grid, TC_THREADS, TcShape<3>::SMEM, s>>>(mapW, mapX, p);
+    static thread_local unsigned configured = 0;  // one bit per instantiation
+    auto launch = [&](auto kernel, int smem, unsigned bit) -> int {
+        if (!(configured & bit)) {
+            ELB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            configured |= bit;
+        }
+        kernel<<<grid, TC_THREADS, size_t(smem), s>>>(mapW, mapX, p);
+        return ELB_OK;
+    };
+#define ELB_TC_CASE(NL_, T_) \
+    if ((four ? 4 : 3) == NL_ && T == T_) ELB_TRY(launch(k_gemm_tc<NL_, T_>, TcShape<NL_, T_>::SMEM, 1u << ((NL_ - 3) * 8 + T_ / 16)));
+    ELB_TC_CASE(3, 16) ELB_TC_CASE(3, 32) ELB_TC_CASE(3, 64) ELB_TC_CASE(4, 16) ELB_TC_CASE(4, 32) ELB_TC_CASE(4, 48)
+#undef ELB_TC_CASE
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }

@@ -118,7 +118,7 @@ def test_matvec_edge_inputs(elb):
 
 
 @pytest.mark.parametrize("t", QTYPES + (synth.F16,))
-@pytest.mark.parametrize("b", (2, 33, 70))
+@pytest.mark.parametrize("b", (2, 16, 24, 33, 64, 70))  # 16, 24, 64: the narrow token tiles of the tensor-core kernel
 def test_matmul_matches_oracle(elb, t, b):
     rng = np.random.default_rng(b + t)
     rows, n = 200, 1024
@@ -129,6 +129,10 @@ def test_matmul_matches_oracle(elb, t, b):
     y = w.matmul(x, 4)
     for i in range(b):
         check_matvec(y[i], wb, t, rows, n, x[i])
+    if t != synth.F16 and b in (16, 24):
+        y3 = w.matmul(x, 3)
+        for i in range(0, b, 5):
+            check_matvec(y3[i], wb, t, rows, n, x[i])
 
 
 @pytest.mark.parametrize("t,nl,b", ((synth.Q4_K, 4, 560), (synth.Q6_K, 3, 530)))
