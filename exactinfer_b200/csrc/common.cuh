@@ -226,14 +226,16 @@ int gemv_launch(const Weight* w, const GemvArgs& a, cudaStream_t s);
 int matvec_static(const Weight* w, const float* d_x, float* d_y, int nl, cudaStream_t s);
 
 // linear.cu — several tokens at once
+// pdl: launch with programmatic stream serialization (the kernel sets itself up while its predecessor still runs and
+// waits for it before it touches global memory)
 int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const float* d_norm_w, float eps,
-                 int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s);
+                 int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s, bool pdl = false);
 int gemm_planes_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B,
                        float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
 // gemm_tc.cu — tcgen05 path for the two-plane weights (Q4_K, Q6_K)
 bool gemm_tc_usable(const Weight* w, int B);
 int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B, int nl,
-                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
+                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl = false);
 int gemm_tc_check();
 int gemm_f16_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, float* d_y,
                     int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);

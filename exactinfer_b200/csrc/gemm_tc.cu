@@ -223,11 +223,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     const int nkb = p.n / 256, n_tiles = p.row_tiles * p.tok_tiles;
     int* s_fail = reinterpret_cast<int*>(tmem_slot + 1);
     unsigned* s_seq = reinterpret_cast<unsigned*>(tmem_slot + 2);
-    if (tid == 0) {
-        *s_fail = 0;
-        // the count moves only when every CTA of a launch is done, hence after every CTA of it has read it
-        *s_seq = *reinterpret_cast<volatile unsigned*>(p.ctl) + 1;
-    }
+    pdl_launch_dependents();  // the next kernel of the stream may set itself up while this one works
 
     // zero blocks in front of, between and behind the limb stages
     for (int z = 0; z <= TC_STAGES; ++z) {
@@ -241,6 +237,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zero rows are read by the tensor core
     if (warp == TC_EPI_WARPS + 1) tmem_alloc(tmem_slot, 512);
+    // Launched with programmatic stream serialization this kernel starts while its predecessor still runs: everything
+    // above touched shared memory only. From here on it reads what earlier kernels wrote (limbs, sums, the residual, the
+    // launch counter) and writes what they may still read.
+    pdl_wait();
+    if (tid == 0) {
+        *s_fail = 0;
+        // the count moves only when every CTA of a launch is done, hence after every CTA of it has read it
+        *s_seq = *reinterpret_cast<volatile unsigned*>(p.ctl) + 1;
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             for (int q = 0; q < XPT; ++q) {
                 const int i = etid + q * TC_EPI_WARPS * 32;
                 const int tok = min(tok0 + (i >> 3), p.B - 1);
-                xreg[q] = p.pl_dm && i < T * 8 ? __ldg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7)) : 0.f;
+                xreg[q] = p.pl_dm && i < T * 8 ? __ldcg(p.xsum + int64_t(tok) * nsub + kb * 8 + (i & 7)) : 0.f;
             }
             if (etid < 2 * TC_ROWS) {
                 const int64_t r = row0 + (etid >> 1);
@@ -488,7 +493,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             for (int t = 0; t < TH; ++t) {
                 const int tok = tok0 + th * TH + t;
                 const bool tok_ok = tok < p.B;
-                const float y = accf[t] * (tok_ok ? __ldg(p.inv_scale + tok) : 0.f);
+                const float y = accf[t] * (tok_ok ? __ldcg(p.inv_scale + tok) : 0.f);
                 if (p.epilogue == EPI_SILU) {  // tile rows 0..7 gate, 8..15 up (16-row groups): partner is 8 lanes up
                     const float up = __shfl_down_sync(0xffffffffu, y, 8);
                     const int64_t o = R / 16 * 8 + (R & 7);
@@ -588,7 +593,7 @@ int gemm_tc_check() {  // after a synchronize: did a tensor-core GEMM give up on
 }
 
 int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B, int nl,
-                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s) {
+                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl) {
     if (!gemm_tc_usable(w, B)) return fail(ELB_ERR_STATE, "matmul: tensor-core path not usable for this weight");
     if (epilogue == EPI_SILU && !w->pair) return fail(ELB_ERR_INVALID, "matmul: SwiGLU epilogue needs a paired weight");
     int* err_host = error_word();
@@ -633,7 +638,17 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
             ELB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             configured |= bit;
         }
-        kernel<<<grid, TC_THREADS, size_t(smem), s>>>(mapW, mapX, p);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = size_t(smem);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        ELB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mapW, mapX, p));
         return ELB_OK;
     };
 #define ELB_TC_CASE(NL_, T_) \

@@ -24,11 +24,13 @@ __global__ void __launch_bounds__(256) k_split_rows(const float* __restrict__ X,
     const int tid = threadIdx.x, lane = tid & 31;
     const int64_t b = blockIdx.x;
     const float* x = X + b * ldx;
+    pdl_launch_dependents();
+    pdl_wait();  // the rows come from the kernel before this one
     float4 v[SR_V4];
 #pragma unroll
     for (int j = 0; j < SR_V4; ++j) {
         const int idx = (j * 256 + tid) * 4;
-        v[j] = idx < n ? *reinterpret_cast<const float4*>(x + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(x + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (norm_w) {
         double ss = 0.0;
@@ -100,13 +102,15 @@ __global__ void __launch_bounds__(256) k_split_rows_long(const float* __restrict
                                                          float* __restrict__ xsum) {
     __shared__ double red8[8];
     __shared__ float redf[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int64_t b = blockIdx.x;
     const float* x = X + b * ldx;
     float inv = 1.0f;
     if (norm_w) {
         double ss = 0.0;
-        for (int i = tid; i < n; i += 256) { const double v = x[i]; ss += v * v; }
+        for (int i = tid; i < n; i += 256) { const double v = __ldcg(x + i); ss += v * v; }
         ss = warp_sum(ss);
         if ((tid & 31) == 0) red8[tid >> 5] = ss;
         __syncthreads();
@@ -114,7 +118,7 @@ __global__ void __launch_bounds__(256) k_split_rows_long(const float* __restrict
         for (int i = 0; i < 8; ++i) ss += red8[i];
         inv = float(1.0 / sqrt(ss / n + double(eps)));
     }
-    auto val = [&](int i) { return norm_w ? __fmul_rn(__fmul_rn(x[i], inv), norm_w[i]) : x[i]; };
+    auto val = [&](int i) { return norm_w ? __fmul_rn(__fmul_rn(__ldcg(x + i), inv), norm_w[i]) : __ldcg(x + i); };
     float m = 0.f;
     for (int i = tid; i < n; i += 256) m = fmaxf(m, fabsf(val(i)));
     m = warp_max(m);
@@ -148,13 +152,22 @@ __global__ void __launch_bounds__(256) k_split_rows_long(const float* __restrict
 }
 
 int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const float* d_norm_w, float eps,
-                 int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s) {
+                 int8_t* d_limbs, float* d_inv_scale, float* d_xsum, cudaStream_t s, bool pdl) {
     if (nl < 2 || nl > 4) return fail(ELB_ERR_INVALID, "split: limb count must be 2, 3 or 4");
     const bool fast = n <= SR_V4 * 1024 && n % 32 == 0 && ldx % 4 == 0 && (b * int64_t(n)) % 4 == 0 &&
                       reinterpret_cast<uintptr_t>(d_x) % 16 == 0 && (!d_norm_w || reinterpret_cast<uintptr_t>(d_norm_w) % 16 == 0);
-    if (fast) k_split_rows<<<unsigned(b), 256, 0, s>>>(d_x, ldx, n, nl, d_norm_w, eps, d_limbs, b * int64_t(n), d_inv_scale, d_xsum);
-    else k_split_rows_long<<<unsigned(b), 256, 0, s>>>(d_x, ldx, n, nl, d_norm_w, eps, d_limbs, b * int64_t(n), d_inv_scale, d_xsum);
-    ELB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(b));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    const int64_t limb_stride = b * int64_t(n);
+    if (fast) ELB_CUDA(cudaLaunchKernelEx(&cfg, k_split_rows, d_x, ldx, n, nl, d_norm_w, eps, d_limbs, limb_stride, d_inv_scale, d_xsum));
+    else ELB_CUDA(cudaLaunchKernelEx(&cfg, k_split_rows_long, d_x, ldx, n, nl, d_norm_w, eps, d_limbs, limb_stride, d_inv_scale, d_xsum));
     return ELB_OK;
 }
 

@@ -183,14 +183,14 @@ int linear_tokens(Model* m, const Weight* w, const float* xin, int64_t ldx, cons
                   int64_t ldy, const float* resid, int epi, int nl) {
     ++m->launches;
     if (w->type == ELB_F16) return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
-    if (gemm_tc_usable(w, B)) return gemm_tc_launch(w, m->limbs, m->inv_scale, m->xsum, B, nl, y, ldy, resid, epi, m->stream);
+    if (gemm_tc_usable(w, B)) return gemm_tc_launch(w, m->limbs, m->inv_scale, m->xsum, B, nl, y, ldy, resid, epi, m->stream, m->use_pdl);
     return gemm_planes_launch(w, m->limbs, m->inv_scale, m->xsum, B, y, ldy, resid, epi, m->stream);
 }
 
 int split_tokens(Model* m, const float* xin, int64_t ldx, int n, int nl, const float* norm_w, int B, bool any_quant) {
     if (!any_quant) return ELB_OK;
     ++m->launches;
-    return split_launch(xin, ldx, B, n, nl, norm_w, m->cfg.eps, m->limbs, m->inv_scale, m->xsum, m->stream);
+    return split_launch(xin, ldx, B, n, nl, norm_w, m->cfg.eps, m->limbs, m->inv_scale, m->xsum, m->stream, m->use_pdl);
 }
 
 // Rows of one sequence at consecutive positions (seq0, pos0 + b), or (mixed) row b at posv_dev[b] of sequence seq_dev[b].
