@@ -224,12 +224,15 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
         cp_async_commit();
     };
 
-    int acc[NPL][4][4][4];  // [plane][token frag][limb][C reg]
-    float yacc[4][4];       // [token frag][C reg]
+    // One plane = Q8_0: a scale per 32 values, so every MMA (K = 32) is complete by itself and goes straight into the fp32
+    // sums; the integer accumulators exist only for the types with a scale per 256.
+    constexpr bool Q8 = NPL == 1;
+    int acc[Q8 ? 1 : NPL][Q8 ? 1 : 4][4][4];  // [plane][token frag][limb][C reg]
+    float yacc[4][4];                         // [token frag][C reg]
 #pragma unroll
-    for (int a = 0; a < NPL; ++a)
+    for (int a = 0; a < (Q8 ? 1 : NPL); ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
+        for (int b = 0; b < (Q8 ? 1 : 4); ++b)
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -242,6 +245,7 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
     const int64_t rg = row0 + warp * 16 + g;  // this lane's rows: rg and rg + 8
     // drain: integer sums -> fp32 with the block scale; `kb` = index of the scale block just finished
     auto drain = [&](int kb) {
+        if constexpr (Q8) return;
         const int nblk = p.n / p.blk;
         const float d0 = rg < p.rows16 ? __half2float(p.pl_d[rg * nblk + kb]) : 0.f;
         const float d1 = rg + 8 < p.rows16 ? __half2float(p.pl_d[(rg + 8) * nblk + kb]) : 0.f;
@@ -252,11 +256,11 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
                 float f = 0.f;
 #pragma unroll
                 for (int l = 3; l >= 0; --l) {
-                    int v = acc[0][nf][l][e];
-                    if (NPL == 2) v += 256 * acc[NPL - 1][nf][l][e];
+                    int v = acc[0][Q8 ? 0 : nf][l][e];
+                    if (NPL == 2) v += 256 * acc[NPL - 1][Q8 ? 0 : nf][l][e];
                     f = fmaf(f, 256.0f, float(v));
 #pragma unroll
-                    for (int a = 0; a < NPL; ++a) acc[a][nf][l][e] = 0;
+                    for (int a = 0; a < NPL; ++a) acc[a][Q8 ? 0 : nf][l][e] = 0;
                 }
                 yacc[nf][e] = fmaf(e < 2 ? d0 : d1, f, yacc[nf][e]);
             }
@@ -290,6 +294,39 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
         __syncthreads();
         const int8_t* ws = reinterpret_cast<const int8_t*>(smem) + (kt & 1) * STAGE;
         const int8_t* as = ws + W_STAGE;
+        if constexpr (Q8) {
+            // the four block scales of this stage of both rows of the lane: one 8-byte load each
+            const int nblk = p.n / 32;
+            uint2 dr0 = make_uint2(0u, 0u), dr1 = dr0;
+            if (rg < p.rows16) dr0 = __ldg(reinterpret_cast<const uint2*>(p.pl_d + rg * nblk + kt * (GM_K / 32)));
+            if (rg + 8 < p.rows16) dr1 = __ldg(reinterpret_cast<const uint2*>(p.pl_d + (rg + 8) * nblk + kt * (GM_K / 32)));
+            const __half2 h0a = *reinterpret_cast<const __half2*>(&dr0.x), h0b = *reinterpret_cast<const __half2*>(&dr0.y);
+            const __half2 h1a = *reinterpret_cast<const __half2*>(&dr1.x), h1b = *reinterpret_cast<const __half2*>(&dr1.y);
+            const float d0s[4] = {__low2float(h0a), __high2float(h0a), __low2float(h0b), __high2float(h0b)};
+            const float d1s[4] = {__low2float(h1a), __high2float(h1a), __low2float(h1b), __high2float(h1b)};
+#pragma unroll
+            for (int ks = 0; ks < GM_K / 32; ++ks) {
+                const int8_t* base = ws + (warp * 16 + g) * GM_LD + ks * 32 + 4 * t;
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(base), a1 = *reinterpret_cast<const uint32_t*>(base + 8 * GM_LD);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(base + 16), a3 = *reinterpret_cast<const uint32_t*>(base + 8 * GM_LD + 16);
+#pragma unroll
+                for (int nf = 0; nf < 4; ++nf) {
+                    int c[4][4];
+#pragma unroll
+                    for (int l = 0; l < 4; ++l) {
+                        const int8_t* bb = as + (l * GM_TOK + nf * 8 + g) * GM_LD + ks * 32 + 4 * t;
+                        mma_s8s8_k32(c[l], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(bb), *reinterpret_cast<const uint32_t*>(bb + 16));
+                    }
+                    // sum_l 256^l P_l: neighbouring limbs joined in int32 (|P_l| < 2^19), then d * that into the fp32 sum
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i01 = c[0][e] + (c[1][e] << 8), i23 = c[2][e] + (c[3][e] << 8);
+                        const float f = fmaf(float(i23), 65536.0f, float(i01));
+                        yacc[nf][e] = fmaf(e < 2 ? d0s[ks] : d1s[ks], f, yacc[nf][e]);
+                    }
+                }
+            }
+        } else {
 #pragma unroll
         for (int ks = 0; ks < GM_K / 32; ++ks) {
             uint32_t af[NPL][4];
@@ -313,6 +350,7 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
                 }
             const int kdone = kt * GM_K + (ks + 1) * 32;
             if (kdone % p.blk == 0) drain(kdone / p.blk - 1);
+        }
         }
         __syncthreads();
     }
