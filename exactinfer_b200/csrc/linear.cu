@@ -224,15 +224,12 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
         cp_async_commit();
     };
 
-    // One plane = Q8_0: a scale per 32 values, so every MMA (K = 32) is complete by itself and goes straight into the fp32
-    // sums; the integer accumulators exist only for the types with a scale per 256.
-    constexpr bool Q8 = NPL == 1;
-    int acc[Q8 ? 1 : NPL][Q8 ? 1 : 4][4][4];  // [plane][token frag][limb][C reg]
-    float yacc[4][4];                         // [token frag][C reg]
+    int acc[NPL][4][4][4];  // [plane][token frag][limb][C reg]
+    float yacc[4][4];       // [token frag][C reg]
 #pragma unroll
-    for (int a = 0; a < (Q8 ? 1 : NPL); ++a)
+    for (int a = 0; a < NPL; ++a)
 #pragma unroll
-        for (int b = 0; b < (Q8 ? 1 : 4); ++b)
+        for (int b = 0; b < 4; ++b)
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -245,7 +242,6 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
     const int64_t rg = row0 + warp * 16 + g;  // this lane's rows: rg and rg + 8
     // drain: integer sums -> fp32 with the block scale; `kb` = index of the scale block just finished
     auto drain = [&](int kb) {
-        if constexpr (Q8) return;
         const int nblk = p.n / p.blk;
         const float d0 = rg < p.rows16 ? __half2float(p.pl_d[rg * nblk + kb]) : 0.f;
         const float d1 = rg + 8 < p.rows16 ? __half2float(p.pl_d[(rg + 8) * nblk + kb]) : 0.f;
@@ -256,11 +252,11 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
                 float f = 0.f;
 #pragma unroll
                 for (int l = 3; l >= 0; --l) {
-                    int v = acc[0][Q8 ? 0 : nf][l][e];
-                    if (NPL == 2) v += 256 * acc[NPL - 1][Q8 ? 0 : nf][l][e];
+                    int v = acc[0][nf][l][e];
+                    if (NPL == 2) v += 256 * acc[NPL - 1][nf][l][e];
                     f = fmaf(f, 256.0f, float(v));
 #pragma unroll
-                    for (int a = 0; a < NPL; ++a) acc[a][Q8 ? 0 : nf][l][e] = 0;
+                    for (int a = 0; a < NPL; ++a) acc[a][nf][l][e] = 0;
                 }
                 yacc[nf][e] = fmaf(e < 2 ? d0 : d1, f, yacc[nf][e]);
             }
@@ -294,39 +290,6 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
         __syncthreads();
         const int8_t* ws = reinterpret_cast<const int8_t*>(smem) + (kt & 1) * STAGE;
         const int8_t* as = ws + W_STAGE;
-        if constexpr (Q8) {
-            // the four block scales of this stage of both rows of the lane: one 8-byte load each
-            const int nblk = p.n / 32;
-            uint2 dr0 = make_uint2(0u, 0u), dr1 = dr0;
-            if (rg < p.rows16) dr0 = __ldg(reinterpret_cast<const uint2*>(p.pl_d + rg * nblk + kt * (GM_K / 32)));
-            if (rg + 8 < p.rows16) dr1 = __ldg(reinterpret_cast<const uint2*>(p.pl_d + (rg + 8) * nblk + kt * (GM_K / 32)));
-            const __half2 h0a = *reinterpret_cast<const __half2*>(&dr0.x), h0b = *reinterpret_cast<const __half2*>(&dr0.y);
-            const __half2 h1a = *reinterpret_cast<const __half2*>(&dr1.x), h1b = *reinterpret_cast<const __half2*>(&dr1.y);
-            const float d0s[4] = {__low2float(h0a), __high2float(h0a), __low2float(h0b), __high2float(h0b)};
-            const float d1s[4] = {__low2float(h1a), __high2float(h1a), __low2float(h1b), __high2float(h1b)};
-#pragma unroll
-            for (int ks = 0; ks < GM_K / 32; ++ks) {
-                const int8_t* base = ws + (warp * 16 + g) * GM_LD + ks * 32 + 4 * t;
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(base), a1 = *reinterpret_cast<const uint32_t*>(base + 8 * GM_LD);
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(base + 16), a3 = *reinterpret_cast<const uint32_t*>(base + 8 * GM_LD + 16);
-#pragma unroll
-                for (int nf = 0; nf < 4; ++nf) {
-                    int c[4][4];
-#pragma unroll
-                    for (int l = 0; l < 4; ++l) {
-                        const int8_t* bb = as + (l * GM_TOK + nf * 8 + g) * GM_LD + ks * 32 + 4 * t;
-                        mma_s8s8_k32(c[l], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(bb), *reinterpret_cast<const uint32_t*>(bb + 16));
-                    }
-                    // sum_l 256^l P_l: neighbouring limbs joined in int32 (|P_l| < 2^19), then d * that into the fp32 sum
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i01 = c[0][e] + (c[1][e] << 8), i23 = c[2][e] + (c[3][e] << 8);
-                        const float f = fmaf(float(i23), 65536.0f, float(i01));
-                        yacc[nf][e] = fmaf(e < 2 ? d0s[ks] : d1s[ks], f, yacc[nf][e]);
-                    }
-                }
-            }
-        } else {
 #pragma unroll
         for (int ks = 0; ks < GM_K / 32; ++ks) {
             uint32_t af[NPL][4];
@@ -351,7 +314,6 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
             const int kdone = kt * GM_K + (ks + 1) * 32;
             if (kdone % p.blk == 0) drain(kdone / p.blk - 1);
         }
-        }
         __syncthreads();
     }
 
@@ -375,6 +337,127 @@ __global__ void __launch_bounds__(GM_THREADS) k_gemm_planes(const GemmParams p) 
         }
 }
 
+// Q8_0: one digit plane and a scale per 32 values, so every MMA (K = 32) is complete by itself: its four int32 results
+// per limb are joined (limb pairs in int32, |P_l| < 2^19) and go straight into the fp32 sums with the block scale,
+// acc += d * Horner_256(P_l) per 32 values as the reference does (src/cuda/model_cuda.cu:968-973). A warp owns RF
+// fragments of 16 rows, so every limb fragment fetched from shared memory feeds RF MMAs.
+template <int RF>
+__global__ void __launch_bounds__(GM_THREADS) k_gemm_q8(const GemmParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int ROWS = GM_ROWS * RF, W_STAGE = ROWS * GM_LD, A_STAGE = 4 * GM_TOK * GM_LD, STAGE = W_STAGE + A_STAGE;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int64_t row0 = int64_t(blockIdx.x) * ROWS;
+    const int tok0 = blockIdx.y * GM_TOK;
+    const int nk = p.n / GM_K, nblk = p.n / 32;
+
+    auto load_stage = [&](int st, int kt) {
+        int8_t* ws = reinterpret_cast<int8_t*>(smem) + st * STAGE;
+        int8_t* as = ws + W_STAGE;
+        const int k0 = kt * GM_K;
+        for (int idx = tid; idx < ROWS * (GM_K / 16); idx += GM_THREADS) {
+            const int r = idx / (GM_K / 16), c = idx % (GM_K / 16);
+            const bool ok = row0 + r < p.rows16;
+            cp_async16(ws + r * GM_LD + c * 16, p.planes + (ok ? row0 + r : 0) * p.n + k0 + c * 16, ok);
+        }
+        for (int idx = tid; idx < 4 * GM_TOK * (GM_K / 16); idx += GM_THREADS) {
+            const int l = idx / (GM_TOK * (GM_K / 16)), r = (idx / (GM_K / 16)) % GM_TOK, c = idx % (GM_K / 16);
+            const bool ok = tok0 + r < p.B;
+            cp_async16(as + (l * GM_TOK + r) * GM_LD + c * 16,
+                       p.limbs + (int64_t(l) * p.B + (ok ? tok0 + r : 0)) * p.n + k0 + c * 16, ok);
+        }
+        cp_async_commit();
+    };
+
+    float yacc[RF][4][4];  // [row fragment][token fragment][C reg]
+#pragma unroll
+    for (int a = 0; a < RF; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int d = 0; d < 4; ++d) yacc[a][b][d] = 0.f;
+    const int64_t rg0 = row0 + warp * 16 * RF + g;  // this lane's rows: rg0 + 16 rf and 8 more
+
+    load_stage(0, 0);
+    for (int kt = 0; kt < nk; ++kt) {
+        if (kt + 1 < nk) {
+            load_stage((kt + 1) & 1, kt + 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        // the four block scales of this stage for the lane's rows: one 8-byte load per row
+        float ds[RF][2][4];
+#pragma unroll
+        for (int rf = 0; rf < RF; ++rf)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int64_t r = rg0 + 16 * rf + 8 * h;
+                uint2 raw = make_uint2(0u, 0u);
+                if (r < p.rows16) raw = __ldg(reinterpret_cast<const uint2*>(p.pl_d + r * nblk + kt * (GM_K / 32)));
+                const __half2 lo = *reinterpret_cast<const __half2*>(&raw.x), hi = *reinterpret_cast<const __half2*>(&raw.y);
+                ds[rf][h][0] = __low2float(lo); ds[rf][h][1] = __high2float(lo);
+                ds[rf][h][2] = __low2float(hi); ds[rf][h][3] = __high2float(hi);
+            }
+        __syncthreads();
+        const int8_t* ws = reinterpret_cast<const int8_t*>(smem) + (kt & 1) * STAGE;
+        const int8_t* as = ws + W_STAGE;
+#pragma unroll
+        for (int ks = 0; ks < GM_K / 32; ++ks) {
+            uint32_t af[RF][4];
+#pragma unroll
+            for (int rf = 0; rf < RF; ++rf) {
+                const int8_t* base = ws + (warp * 16 * RF + rf * 16 + g) * GM_LD + ks * 32 + 4 * t;
+                af[rf][0] = *reinterpret_cast<const uint32_t*>(base);
+                af[rf][1] = *reinterpret_cast<const uint32_t*>(base + 8 * GM_LD);
+                af[rf][2] = *reinterpret_cast<const uint32_t*>(base + 16);
+                af[rf][3] = *reinterpret_cast<const uint32_t*>(base + 8 * GM_LD + 16);
+            }
+#pragma unroll
+            for (int nf = 0; nf < 4; ++nf) {
+                int c[RF][4][4];
+#pragma unroll
+                for (int l = 0; l < 4; ++l) {
+                    const int8_t* bb = as + (l * GM_TOK + nf * 8 + g) * GM_LD + ks * 32 + 4 * t;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bb), b1 = *reinterpret_cast<const uint32_t*>(bb + 16);
+#pragma unroll
+                    for (int rf = 0; rf < RF; ++rf) mma_s8s8_k32(c[rf][l], af[rf][0], af[rf][1], af[rf][2], af[rf][3], b0, b1);
+                }
+#pragma unroll
+                for (int rf = 0; rf < RF; ++rf)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i01 = c[rf][0][e] + (c[rf][1][e] << 8), i23 = c[rf][2][e] + (c[rf][3][e] << 8);
+                        const float f = fmaf(float(i23), 65536.0f, float(i01));
+                        yacc[rf][nf][e] = fmaf(ds[rf][e >> 1][ks], f, yacc[rf][nf][e]);
+                    }
+            }
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int rf = 0; rf < RF; ++rf)
+#pragma unroll
+        for (int nf = 0; nf < 4; ++nf)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tok0 + nf * 8 + 2 * t + e;
+                if (tok >= p.B) continue;
+                const int64_t rg = rg0 + 16 * rf;
+                const float is = p.inv_scale[tok];
+                const float v0 = yacc[rf][nf][e] * is, v1 = yacc[rf][nf][2 + e] * is;  // rows rg, rg+8
+                if (p.epilogue == EPI_SILU) {
+                    const int64_t o = rg / 16 * 8 + rg % 16;  // rg % 16 = g < 8: gate row; rg+8: the matching up row
+                    if (o < p.rows / 2) p.Y[int64_t(tok) * p.ldy + o] = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
+                } else {
+                    float* y = p.Y + int64_t(tok) * p.ldy;
+                    const float* r = p.epilogue == EPI_ADD ? p.resid + int64_t(tok) * p.ldy : nullptr;
+                    if (rg < p.rows) y[rg] = r ? r[rg] + v0 : v0;
+                    if (rg + 8 < p.rows) y[rg + 8] = r ? r[rg + 8] + v1 : v1;
+                }
+            }
+}
+
 int gemm_planes_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B,
                        float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s) {
     if (!w->planes) return fail(ELB_ERR_STATE, "matmul: weight was created without ELB_W_PLANES");
@@ -382,16 +465,29 @@ int gemm_planes_launch(const Weight* w, const int8_t* d_limbs, const float* d_in
     if (epilogue == EPI_SILU && !w->pair) return fail(ELB_ERR_INVALID, "matmul: SwiGLU epilogue needs a paired weight");
     GemmParams p{w->planes, w->pl_d, w->pl_dm, d_limbs, d_inv_scale, d_xsum, d_y, d_resid, w->tiles * 16, w->rows, ldy,
                  B, int(w->n), w->n_planes, w->type == ELB_Q8_0 ? 32 : 256, epilogue};
-    const dim3 grid(unsigned((w->tiles * 16 + GM_ROWS - 1) / GM_ROWS), unsigned((B + GM_TOK - 1) / GM_TOK));
-    const size_t smem = 2 * size_t(w->n_planes * GM_ROWS + 4 * GM_TOK) * GM_LD;
+    const int64_t rows16 = w->tiles * 16;
+    const unsigned tok_tiles = unsigned((B + GM_TOK - 1) / GM_TOK);
     static thread_local bool configured = false;
     if (!configured) {
-        ELB_CUDA(cudaFuncSetAttribute(k_gemm_planes<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (1 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
+        ELB_CUDA(cudaFuncSetAttribute(k_gemm_q8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (1 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
+        ELB_CUDA(cudaFuncSetAttribute(k_gemm_q8<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (2 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
         ELB_CUDA(cudaFuncSetAttribute(k_gemm_planes<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (2 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
         configured = true;
     }
-    if (w->n_planes == 1) k_gemm_planes<1><<<grid, GM_THREADS, smem, s>>>(p);
-    else k_gemm_planes<2><<<grid, GM_THREADS, smem, s>>>(p);
+    if (w->n_planes == 1) {  // Q8_0: 128-row tiles when that still leaves a few CTAs for every SM
+        DeviceInfo di;
+        ELB_TRY(device_info(w->device, &di));
+        const int64_t tiles128 = (rows16 + 2 * GM_ROWS - 1) / (2 * GM_ROWS);
+        if (tiles128 * tok_tiles >= 3 * int64_t(di.sm_count)) {
+            k_gemm_q8<2><<<dim3(unsigned(tiles128), tok_tiles), GM_THREADS, 2 * size_t(2 * GM_ROWS + 4 * GM_TOK) * GM_LD, s>>>(p);
+        } else {
+            k_gemm_q8<1><<<dim3(unsigned((rows16 + GM_ROWS - 1) / GM_ROWS), tok_tiles), GM_THREADS,
+                           2 * size_t(GM_ROWS + 4 * GM_TOK) * GM_LD, s>>>(p);
+        }
+    } else {
+        k_gemm_planes<2><<<dim3(unsigned((rows16 + GM_ROWS - 1) / GM_ROWS), tok_tiles), GM_THREADS,
+                             2 * size_t(2 * GM_ROWS + 4 * GM_TOK) * GM_LD, s>>>(p);
+    }
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }
