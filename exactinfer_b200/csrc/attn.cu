@@ -546,11 +546,19 @@ struct AttnRowsParams {
     float scale;
 };
 
+// Key / value tiles arrive by cp.async, the next tile while the current one is worked on: a CTA streams its whole key
+// range (a sequence's context when there are enough rows to fill the GPU without a key split), so the bytes in flight
+// per SM, not the arithmetic, set the pace.
+constexpr int AR_LDK = D + 4;  // key row stride: 16-byte aligned rows, conflict-free 128-bit reads (lane = key)
+constexpr int AR_KT = 24;       // keys per tile: two tiles of K and V are 50 KB, four CTAs per SM
+constexpr size_t AR_SMEM = size_t(2) * AR_KT * (AR_LDK + D) * sizeof(float);
+
 __global__ void __launch_bounds__(AD_THREADS) k_attn_rows(const AttnRowsParams p) {
-    __shared__ float qs[AD_MAXG][D];
-    __shared__ float Ks[AD_KT][AD_LDK];
-    __shared__ float Vs[AD_KT][D];
-    __shared__ float Ps[AD_MAXG][AD_KT];
+    extern __shared__ __align__(16) float ar_tiles[];
+    float* Ks = ar_tiles;                    // [2][AR_KT][AR_LDK]
+    float* Vs = Ks + 2 * AR_KT * AR_LDK;     // [2][AR_KT][D]
+    __shared__ __align__(16) float qs[AD_MAXG][D];
+    __shared__ float Ps[AD_MAXG][32];  // (a warp writes all 32 lanes)
     __shared__ float corr_s[AD_MAXG], m_s[AD_MAXG], l_s[AD_MAXG];
     __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -560,30 +568,48 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_rows(const AttnRowsParams p
     const float* vc = p.vc + size_t(p.seqv[b]) * p.seq_stride;
     for (int idx = tid; idx < group * D; idx += AD_THREADS) qs[idx / D][idx % D] = p.qkv[int64_t(b) * p.ld + (kvh * group) * D + idx];
     if (tid < AD_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
-    const int tiles = (T + AD_KT - 1) / AD_KT, per = (tiles + p.nsplit - 1) / p.nsplit;
-    const int t_begin = min(T, split * per * AD_KT), t_end = min(T, (split + 1) * per * AD_KT);
+    const int tiles = (T + AR_KT - 1) / AR_KT, per = (tiles + p.nsplit - 1) / p.nsplit;
+    const int t_begin = min(T, split * per * AR_KT), t_end = min(T, (split + 1) * per * AR_KT);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};  // outputs (head tid/128 + 2i, dim tid%128)
     const int od = tid & (D - 1), oh = tid >> 7;
-    for (int t0 = t_begin; t0 < t_end; t0 += AD_KT) {
-        const int nk = min(AD_KT, t_end - t0);
-        __syncthreads();
-        for (int idx = tid; idx < AD_KT * (D / 4); idx += AD_THREADS) {
+    auto fetch = [&](int buf, int t0, int nk) {
+        const unsigned ks = unsigned(__cvta_generic_to_shared(Ks + buf * AR_KT * AR_LDK));
+        const unsigned vs = unsigned(__cvta_generic_to_shared(Vs + buf * AR_KT * D));
+        for (int idx = tid; idx < nk * (D / 4); idx += AD_THREADS) {
             const int j = idx / (D / 4), c = (idx % (D / 4)) * 4;
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
-            if (j < nk) {
-                kv = *reinterpret_cast<const float4*>(kc + size_t(t0 + j) * KD + kvh * D + c);
-                vv = *reinterpret_cast<const float4*>(vc + size_t(t0 + j) * KD + kvh * D + c);
-            }
-            Ks[j][c] = kv.x; Ks[j][c + 1] = kv.y; Ks[j][c + 2] = kv.z; Ks[j][c + 3] = kv.w;
-            *reinterpret_cast<float4*>(&Vs[j][c]) = vv;
+            const size_t off = size_t(t0 + j) * KD + kvh * D + c;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks + unsigned(j * AR_LDK + c) * 4u), "l"(kc + off));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs + unsigned(j * D + c) * 4u), "l"(vc + off));
+        }
+        asm volatile("cp.async.commit_group;");
+    };
+    if (t_begin < t_end) fetch(0, t_begin, min(AR_KT, t_end - t_begin));
+    int buf = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += AR_KT, buf ^= 1) {
+        const int nk = min(AR_KT, t_end - t0);
+        if (t0 + AR_KT < t_end) {  // the other buffer was released by the barrier that ended the previous tile
+            fetch(buf ^ 1, t0 + AR_KT, min(AR_KT, t_end - t0 - AR_KT));
+            asm volatile("cp.async.wait_group 1;");
+        } else {
+            asm volatile("cp.async.wait_group 0;");
         }
         __syncthreads();
+        const float* Kb = Ks + buf * AR_KT * AR_LDK;
+        const float* Vb = Vs + buf * AR_KT * D;
         if (warp < group) {  // scores: warp = head, lane = key; dimension order, multiply then add, as the CPU path does
             float sc = -INFINITY;
             if (lane < nk) {
                 float a = 0.f;
+                const float4* q = reinterpret_cast<const float4*>(qs[warp]);
+                const float4* kr = reinterpret_cast<const float4*>(Kb + lane * AR_LDK);
 #pragma unroll 8
-                for (int i = 0; i < D; ++i) a = __fadd_rn(a, __fmul_rn(qs[warp][i], Ks[lane][i]));
+                for (int i = 0; i < D / 4; ++i) {
+                    const float4 qv = q[i], kv = kr[i];
+                    a = __fadd_rn(a, __fmul_rn(qv.x, kv.x));
+                    a = __fadd_rn(a, __fmul_rn(qv.y, kv.y));
+                    a = __fadd_rn(a, __fmul_rn(qv.z, kv.z));
+                    a = __fadd_rn(a, __fmul_rn(qv.w, kv.w));
+                }
                 sc = __fmul_rn(a, p.scale);
             }
             const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(sc));
@@ -603,9 +629,10 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_rows(const AttnRowsParams p
             const int h = oh + 2 * i;
             if (h >= group) continue;
             float a = acc[i] * corr_s[h];
-            for (int j = 0; j < nk; ++j) a = fmaf(Ps[h][j], Vs[j][od], a);
+            for (int j = 0; j < nk; ++j) a = fmaf(Ps[h][j], Vb[j * D + od], a);
             acc[i] = a;
         }
+        __syncthreads();  // the tile and Ps are free again
     }
     __syncthreads();
     float* out = p.att + int64_t(b) * p.ld_att;
@@ -664,7 +691,12 @@ int attn_rows_launch(const float* qkv, int64_t ld, const float* kc, const float*
     if (H % HKV || H / HKV > AD_MAXG) return fail(ELB_ERR_UNSUPPORTED, "attention: at most 8 query heads per KV head");
     if (nsplit < 1 || nsplit > AD_MAXSPLIT) return fail(ELB_ERR_INVALID, "attention: split count out of range");
     AttnRowsParams p{qkv, ld, kc, vc, seq_stride, posv, seqv, att, ld_att, part, counters, H, HKV, nsplit, scale};
-    k_attn_rows<<<dim3(B, HKV, nsplit), AD_THREADS, 0, s>>>(p);
+    static thread_local bool configured = false;
+    if (!configured) {
+        ELB_CUDA(cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AR_SMEM)));
+        configured = true;
+    }
+    k_attn_rows<<<dim3(B, HKV, nsplit), AD_THREADS, AR_SMEM, s>>>(p);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }
