@@ -411,16 +411,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty + acc);
             };
-            if constexpr (TH <= 12) {  // every load of the drain is issued before the one wait
-                int v[TH / 4][NL + 1][4];
+            if constexpr (TH <= 12) {  // every load of the drain is issued before the one wait, eight columns at a time
+                int v[NL + 1][TH];
 #pragma unroll
-                for (int c = 0; c < TH / 4; ++c)
-#pragma unroll
-                    for (int j = 0; j <= NL; ++j) tmem_ld4(tbase + j * T + c * 4, v[c][j]);
+                for (int j = 0; j <= NL; ++j) {
+                    if constexpr (TH >= 8) {
+                        tmem_ld8(tbase + j * T, *reinterpret_cast<int(*)[8]>(&v[j][0]));
+                        if constexpr (TH == 12) tmem_ld4(tbase + j * T + 8, *reinterpret_cast<int(*)[4]>(&v[j][8]));
+                    } else {
+                        tmem_ld4(tbase + j * T, *reinterpret_cast<int(*)[4]>(&v[j][0]));
+                    }
+                }
                 tmem_ld_wait();
                 release();
 #pragma unroll
-                for (int c = 0; c < TH / 4; ++c) join(v[c], c * 4);
+                for (int t = 0; t < TH; ++t) {
+                    const int i01 = v[0][t] + (v[1][t] << 8), i23 = v[2][t] + (v[3][t] << 8);
+                    float f = NL == 4 ? fmaf(i2f_small(v[NL][t]), 65536.0f, float(i23)) : float(i23);
+                    f = fmaf(f, 65536.0f, float(i01));
+                    accf[t] = fmaf(d, f, accf[t]);
+                }
             } else {
                 // Sixteen tokens of four columns would not leave room in the 96 registers a thread of this kernel can
                 // have: the drain goes four tokens at a time, two such chunks in flight (the loads of chunk c + 1 are
