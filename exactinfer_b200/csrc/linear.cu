@@ -164,7 +164,9 @@ int split_launch(const float* d_x, int64_t ldx, int64_t b, int n, int nl, const 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    // (rows too long for registers take several passes over global memory: launched early, that kernel ran slower -
+    // 4.6 % of the 32B prompt time - so only the one-pass kernel is)
+    cfg.numAttrs = pdl && fast ? 1 : 0;
     const int64_t limb_stride = b * int64_t(n);
     if (fast) ELB_CUDA(cudaLaunchKernelEx(&cfg, k_split_rows, d_x, ldx, n, nl, d_norm_w, eps, d_limbs, limb_stride, d_inv_scale, d_xsum));
     else ELB_CUDA(cudaLaunchKernelEx(&cfg, k_split_rows_long, d_x, ldx, n, nl, d_norm_w, eps, d_limbs, limb_stride, d_inv_scale, d_xsum));
