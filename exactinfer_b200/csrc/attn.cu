@@ -629,7 +629,12 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_rows(const AttnRowsParams p
             const int h = oh + 2 * i;
             if (h >= group) continue;
             float a = acc[i] * corr_s[h];
-            for (int j = 0; j < nk; ++j) a = fmaf(Ps[h][j], Vb[j * D + od], a);
+            if (nk == AR_KT) {  // a whole tile: fixed trip count, the loads run ahead of the additions
+#pragma unroll
+                for (int j = 0; j < AR_KT; ++j) a = fmaf(Ps[h][j], Vb[j * D + od], a);
+            } else {
+                for (int j = 0; j < nk; ++j) a = fmaf(Ps[h][j], Vb[j * D + od], a);
+            }
             acc[i] = a;
         }
         __syncthreads();  // the tile and Ps are free again
