@@ -116,6 +116,8 @@ __device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& ta
 
 // ---------------------------------------------------------------- activation -> limbs in shared memory
 
+// Block-wide maximum and sum of the conversion. No barrier behind the reads: the two use different buffers, and a
+// buffer is written again only in the next conversion, several CTA barriers later.
 __device__ __forceinline__ float dk_block_max(float v, float* red, int tid) {
     v = warp_max(v);
     if ((tid & 31) == 0) red[tid >> 5] = v;
@@ -123,7 +125,6 @@ __device__ __forceinline__ float dk_block_max(float v, float* red, int tid) {
     float m = red[0];
 #pragma unroll
     for (int i = 1; i < DK_WARPS; ++i) m = fmaxf(m, red[i]);
-    __syncthreads();
     return m;
 }
 __device__ __forceinline__ double dk_block_sum(double v, double* red, int tid) {
@@ -133,7 +134,6 @@ __device__ __forceinline__ double dk_block_sum(double v, double* red, int tid) {
     double s = 0.0;
 #pragma unroll
     for (int i = 0; i < DK_WARPS; ++i) s += red[i];  // fixed order
-    __syncthreads();
     return s;
 }
 
@@ -206,7 +206,7 @@ struct Resid {
 };
 
 __device__ float convert_act(const float* src, const Resid* resid, int n, const float* norm_w, float eps,
-                             const unsigned* amax_bits, int nl, const ActSmem& a, double* red, int sd_mask) {
+                             const unsigned* amax_bits, int nl, const ActSmem& a, double* red, float* redf, int sd_mask) {
     constexpr int V4 = 5;  // float4 per thread kept in registers: one pass over vectors of up to 10240 values
     const int tid = threadIdx.x;
     int k;
@@ -262,7 +262,7 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
                 v[j] = norm4(v[j], inv, w[j]);
                 m = fmaxf(m, absmax4(v[j]));
             }
-            m = dk_block_max(m, reinterpret_cast<float*>(red), tid);
+            m = dk_block_max(m, redf, tid);
         } else {
             m = __uint_as_float(__ldcg(amax_bits));
         }
@@ -455,11 +455,14 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
 //                     the consumer adds residual + all the vectors (convert_act).
 //   DK_EPI_LOGITS     y[v0 + row] = sum on every tensor-parallel rank (this rank's vocabulary rows of the head)
 __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf,
-                             int& rs, const PhaseSmem& s, unsigned* amax_out, int xset = 0, bool gact = false) {
+                             int& rs, const PhaseSmem& s, unsigned* amax_out, int xset = 0, bool gact = false,
+                             bool after_matrix = true) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
     const WarpRange r = warp_range(m, warp);
     if (tid == 0) s.flags[3] = 0;
-    __syncthreads();  // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v)
+    // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v); the first matrix
+    // comes straight from the conversion, which ends with a CTA barrier
+    if (after_matrix) __syncthreads();
     if (gact) {  // activation limbs in global memory (written by other CTAs before the last barrier): L2 loads
         switch (m.type) {
             case ELB_Q4_K: run_units<ELB_Q4_K, true>(p, m, r, pf, rs, s, warp, lane); break;
@@ -873,12 +876,12 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
             s.act = act_for(n);
             Resid rsd{nullptr, nullptr, 0, nullptr};
             if (resid) rsd = resid_step(head ? p.x : nullptr);  // the last residual stream goes to p.x
-            inv = convert_act(src, resid ? &rsd : nullptr, n, norm_w, p.eps, amax_in, nl, s.act, s.red8, need);
+            inv = convert_act(src, resid ? &rsd : nullptr, n, norm_w, p.eps, amax_in, nl, s.act, s.red8, s.red, need);
         }
         const int sb = k == 0 ? 0 : 3 * k + 2;  // profile stamps of the stage: conversion, matvec, barrier
         if (!head) dk_stamp(p, l, sb + 1);
         for (int i = 0; i < nm; ++i)
-            matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u), gact);
+            matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u), gact, i > 0);
         if (!head) dk_stamp(p, l, sb + 2);
         if (k == 1 || k == 3 || (head && p.tp_size > 1)) {  // row-parallel matvecs and the logits meet all ranks
             ok = exchange_barrier(p, nb, xn, dead);
