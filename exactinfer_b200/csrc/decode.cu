@@ -593,6 +593,18 @@ __device__ __forceinline__ void attn_fetch_kv(const DkLayer& L, const AttnSmem& 
     ring_commit();
 }
 
+// The first key / value tile of this CTA's attention part does not depend on the token in flight (its own row comes
+// from shared memory): it is requested as soon as the q|k|v matvec has released the scratch area, so that it travels
+// while the CTAs meet at the barrier in front of the attention.
+__device__ __forceinline__ void attn_prefetch(const DkParams& p, const DkLayer& L, const AttnSmem& s) {
+    const int c = blockIdx.x;
+    if (c >= p.HKV * p.nsplit) return;
+    const int kvh = c / p.nsplit, split = c - kvh * p.nsplit;
+    const int pos = p.pos[p.ctl[0]], T = pos + 1;
+    const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);
+    attn_fetch_kv(L, s, p.HKV * DK_HD, kvh, t_begin, min(DK_KT, t_end - t_begin), pos);
+}
+
 // CTA c < HKV * nsplit works on KV head c / nsplit, key split c % nsplit: q/k norm + RoPE, KV append, flash decode
 // over its keys (DK_KT at a time, fetched while the heads are normalised), partial results to the scratch buffer; the
 // last split of a KV head to arrive combines them in split order and writes att (and max|att|).
@@ -603,7 +615,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
     const int kvh = c / p.nsplit, split = c - kvh * p.nsplit, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
     const int pos = p.pos[p.ctl[0]], T = pos + 1;
     const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);  // equal key ranges
-    attn_fetch_kv(L, s, KD, kvh, t_begin, min(DK_KT, t_end - t_begin), pos);
+    // (the first tile was requested by attn_prefetch before the barrier)
     const float2* cs = reinterpret_cast<const float2*>(p.rope) + size_t(pos) * (p.rope_dim / 2);
     float* m_s = s.corr + DK_MAXG;
     float* l_s = s.corr + 2 * DK_MAXG;
@@ -883,6 +895,7 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         for (int i = 0; i < nm; ++i)
             matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u), gact, i > 0);
         if (!head) dk_stamp(p, l, sb + 2);
+        if (k == 0) attn_prefetch(p, L, as);
         if (k == 1 || k == 3 || (head && p.tp_size > 1)) {  // row-parallel matvecs and the logits meet all ranks
             ok = exchange_barrier(p, nb, xn, dead);
             pending = int(xn & 1u);
