@@ -711,10 +711,12 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
         mine[tid * (DK_HD + 2) + DK_HD] = m_s[tid];
         mine[tid * (DK_HD + 2) + DK_HD + 1] = l_s[tid];
     }
-    __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned old = atomicAdd(&p.attn_counters[kvh], 1u);
+        // release: the CTA's partial results (ordered before this thread by the barrier) are visible to whoever reads
+        // the count; acquire: the last arriver sees everybody else's
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.attn_counters + kvh) : "memory");
         s.flags[0] = old == unsigned(p.nsplit - 1);
         if (s.flags[0]) p.attn_counters[kvh] = 0;
     }
