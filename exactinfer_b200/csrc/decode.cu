@@ -57,7 +57,8 @@ __device__ __forceinline__ bool grid_barrier(const DkParams& p, unsigned& target
             }
             if (it > 2048) __nanosleep(64);
         }
-        __threadfence();
+        // (no fence here: the acquire load that saw the last arrival synchronises with every CTA's release, and the
+        // CTA barrier below carries that to the other threads)
     }
     __syncthreads();
     return !*s_dead;
