@@ -723,7 +723,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
     }
     __syncthreads();
     if (!s.flags[0]) return;
-    __threadfence();
+    // (thread 0's acquire and the barrier above order the other parts' results before the L2 loads below)
     const float* base = p.attn_part + size_t(kvh) * p.nsplit * group * (DK_HD + 2);
     float mx = 0.f;
 #pragma unroll
