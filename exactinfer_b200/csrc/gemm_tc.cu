@@ -454,7 +454,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             float* sl = p.scratch + (size_t(blockIdx.x) * T + th * TH) * TC_ROWS + my_row;  // a warp stores 32 neighbours
 #pragma unroll
             for (int t = 0; t < TH; ++t) sl[t * TC_ROWS] = accf[t];
-            __threadfence();
+            // (no fence per thread: the barrier orders the stores before thread 0, whose release store publishes them)
             asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
             if (etid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.flags + blockIdx.x), "r"(*s_seq) : "memory");
             continue;
@@ -524,11 +524,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (warp == TC_EPI_WARPS + 1) tmem_dealloc(tmem_base, 512);
-    if (tid == 0) {  // the last CTA to finish closes the launch
-        __threadfence();
+    if (tid == 0) {  // the last CTA to finish closes the launch (both words are read by the next launch only)
         if (atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1) {
             p.ctl[1] = 0;
-            __threadfence();
             atomicAdd(p.ctl, 1u);
         }
     }
