@@ -152,6 +152,17 @@ def layer_shapes(s: Spec) -> dict:
             "ffn_down": (s.n_embd, s.n_ff)}
 
 
+def decode_weight_bytes(spec: Spec) -> int:
+    """Quantized weight bytes a single-token step has to read once: every matrix of every layer plus the head (the
+    tied embedding table when there is no output tensor); norm vectors and the one embedding row are left out. This is
+    the algorithmic traffic of decode before the KV rows are added."""
+    total = spec.n_vocab * row_bytes(spec.weight_type("output" if not spec.tied else "token_embd", -1), spec.n_embd)
+    for l in range(spec.n_layer):
+        for role, (rows, n) in layer_shapes(spec).items():
+            total += rows * row_bytes(spec.weight_type(role, l), n)
+    return total
+
+
 def generate(spec: Spec, seed: int, share_layers: bool = False):
     """Yield (role, layer, ggml_type, rows, n, bytes) for every tensor of the model (layer = -1 for globals).
 
