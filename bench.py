@@ -169,6 +169,31 @@ def model_tensors(spec):
 
 # ---------------------------------------------------------------- CPU baseline (the reference's CPU path)
 
+def physical_cores() -> int:
+    """Physical cores this process may run on: distinct (package, core) pairs of /proc/cpuinfo among the CPUs of the
+    affinity mask; the size of the mask when that cannot be read."""
+    try:
+        allowed = os.sched_getaffinity(0)
+    except AttributeError:
+        allowed = set(range(os.cpu_count() or 1))
+    try:
+        cores, cpu, pkg = set(), None, 0
+        for line in open("/proc/cpuinfo"):
+            k, _, v = line.partition(":")
+            k, v = k.strip(), v.strip()
+            if k == "processor":
+                cpu, pkg = int(v), 0
+            elif k == "physical id":
+                pkg = int(v)
+            elif k == "core id" and cpu in allowed:
+                cores.add((pkg, int(v)))
+        if cores:
+            return len(cores)
+    except (OSError, ValueError):
+        pass
+    return max(1, len(allowed))
+
+
 def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
     """Decode tok/s of the reference CPU backend on the host cores, on a bounded sample: one warm-up token, then
     single-token steps from position 1 until `seconds` have passed (at most max_steps). Uses the reference's own code
@@ -180,15 +205,19 @@ def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
     toks = synth.lcg_tokens(max_steps + 1, spec.n_vocab)
     n_ctx = max_steps + 2
     tmp = None
+    want = physical_cores()
     if ol.have_ref():
         kind = "reference"
         tmp = tempfile.mkdtemp(prefix="elb_bench_")
         path = os.path.join(tmp, "model.gguf")
         synth.write_gguf(path, spec, tens)
+        # the thread count is set explicitly (a launcher such as torch.distributed.run exports OMP_NUM_THREADS=1)
+        ol.ref().ref_set_threads(want)
         model = ol.RefModel(path, n_ctx)
-        cores = ol.ref().ref_threads() if hasattr(ol.ref(), "ref_threads") else os.cpu_count()
+        cores = ol.ref().ref_threads()
     else:
         kind = "port"
+        ol.oracle().orc_set_threads(want)
         model = ol.OracleModel(spec, tens, n_ctx)
         cores = ol.oracle().orc_threads()
     model.eval(toks[:1], 0)  # warm-up
@@ -202,7 +231,7 @@ def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
     if tmp:
         import shutil
         shutil.rmtree(tmp, ignore_errors=True)
-    return {"value": done / dt, "unit": "tok/s", "cores": int(cores), "kind": kind,
+    return {"value": done / dt, "unit": "tok/s", "cores": int(cores), "physical_cores": int(want), "kind": kind,
             "sample": f"{done} single-token decode steps at positions 1..{done} of the same model (1 warm-up token; "
                       f"context shorter than the GPU run's {PROMPT}+), {dt:.1f} s"}, done, dt
 

@@ -696,11 +696,7 @@ int attn_rows_launch(const float* qkv, int64_t ld, const float* kc, const float*
     if (H % HKV || H / HKV > AD_MAXG) return fail(ELB_ERR_UNSUPPORTED, "attention: at most 8 query heads per KV head");
     if (nsplit < 1 || nsplit > AD_MAXSPLIT) return fail(ELB_ERR_INVALID, "attention: split count out of range");
     AttnRowsParams p{qkv, ld, kc, vc, seq_stride, posv, seqv, att, ld_att, part, counters, H, HKV, nsplit, scale};
-    static thread_local bool configured = false;
-    if (!configured) {
-        ELB_CUDA(cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AR_SMEM)));
-        configured = true;
-    }
+    ELB_TRY(ensure_dyn_smem((const void*)k_attn_rows, AR_SMEM));
     k_attn_rows<<<dim3(B, HKV, nsplit), AD_THREADS, AR_SMEM, s>>>(p);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
@@ -832,12 +828,8 @@ size_t attn_prefill_counters(int max_batch, int H, int HKV) {
 
 int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
                         int pos0, int B, int H, int HKV, float scale, cudaStream_t s, float* part, unsigned* counters) {
-    static thread_local bool configured = false;
-    if (!configured) {
-        ELB_CUDA(cudaFuncSetAttribute(k_attn_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AP_SMEM)));
-        ELB_CUDA(cudaFuncSetAttribute(k_attn_prefill_gqa, cudaFuncAttributeMaxDynamicSharedMemorySize, int(AG_SMEM)));
-        configured = true;
-    }
+    ELB_TRY(ensure_dyn_smem((const void*)k_attn_prefill, AP_SMEM));
+    ELB_TRY(ensure_dyn_smem((const void*)k_attn_prefill_gqa, AG_SMEM));
     const int group = H / HKV;
     static const bool old_kernel = [] { const char* v = std::getenv("ELB_ATTN_SIMPLE"); return v && v[0] == '1'; }();
     if (!old_kernel && H % HKV == 0 && AG_ROWS % group == 0 && ld % 4 == 0 && ld_att % 4 == 0) {

@@ -74,6 +74,12 @@ int elb_host_alloc(size_t bytes, void** out) { ELB_CUDA(cudaMallocHost(out, std:
 int elb_host_free(void* p) { ELB_CUDA(cudaFreeHost(p)); return ELB_OK; }
 int elb_memcpy_h2d(void* dst, const void* src, size_t bytes) { ELB_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice)); return ELB_OK; }
 int elb_memcpy_d2h(void* dst, const void* src, size_t bytes) { ELB_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost)); return ELB_OK; }
+int elb_device_mem_info(int device, size_t* free_bytes, size_t* total_bytes) {
+    if (!free_bytes || !total_bytes) return fail(ELB_ERR_INVALID, "elb_device_mem_info: null argument");
+    ELB_CUDA(cudaSetDevice(device));
+    ELB_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+    return ELB_OK;
+}
 int elb_device_sync(int device) {
     ELB_CUDA(cudaSetDevice(device));
     ELB_CUDA(cudaDeviceSynchronize());

@@ -179,6 +179,9 @@ struct DeviceInfo {
     size_t smem_optin = 0;
 };
 int device_info(int device, DeviceInfo* out);
+// Raise a kernel's dynamic shared memory limit to at least `smem` bytes on the CURRENT device. The attribute is kept per
+// device by the runtime, so what has been set is remembered per (kernel, device): any thread, any device, any order.
+int ensure_dyn_smem(const void* kernel, size_t smem);
 
 // weights.cu
 int weight_create(int device, int type, int64_t rows_one, int64_t n, const void* bytes, size_t nbytes, int flags,

@@ -922,11 +922,7 @@ size_t decode_smem_bytes(const DkParams& p, int slot_bytes) {
 
 int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s) {
     const size_t smem = decode_smem_bytes(p, slot_bytes);
-    static thread_local size_t configured = 0;
-    if (configured < smem) {
-        ELB_CUDA(cudaFuncSetAttribute(k_decode_step, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        configured = smem;
-    }
+    ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(k_decode_step), smem));
     void* args[] = {const_cast<DkParams*>(&p), const_cast<int*>(&slot_bytes)};
     ELB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(k_decode_step), dim3(grid), dim3(DK_THREADS), args, smem, s));
     return ELB_OK;
@@ -939,7 +935,7 @@ int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits) 
     const size_t smem = decode_smem_bytes(p, slot_bytes);
     *fits = false;
     if (smem > di.smem_optin) return ELB_OK;
-    ELB_CUDA(cudaFuncSetAttribute(k_decode_step, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(k_decode_step), smem));
     int per_sm = 0;
     ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, DK_THREADS, smem));
     *fits = per_sm >= 1;

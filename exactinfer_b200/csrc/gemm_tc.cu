@@ -643,12 +643,8 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
     TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
                row_tiles, tok_tiles, waves, per, scratch[w->device], flags[w->device], ctl[w->device], err_dev, tc_prof_on() ? 1 : 0};
     const dim3 grid{unsigned(grid_n)};
-    static thread_local unsigned configured = 0;  // one bit per instantiation
-    auto launch = [&](auto kernel, int smem, unsigned bit) -> int {
-        if (!(configured & bit)) {
-            ELB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            configured |= bit;
-        }
+    auto launch = [&](auto kernel, int smem) -> int {
+        ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(kernel), size_t(smem)));
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(TC_THREADS);
@@ -663,7 +659,7 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
         return ELB_OK;
     };
 #define ELB_TC_CASE(NL_, T_) \
-    if ((four ? 4 : 3) == NL_ && T == T_) ELB_TRY(launch(k_gemm_tc<NL_, T_>, TcShape<NL_, T_>::SMEM, 1u << ((NL_ - 3) * 8 + T_ / 16)));
+    if ((four ? 4 : 3) == NL_ && T == T_) ELB_TRY(launch(k_gemm_tc<NL_, T_>, TcShape<NL_, T_>::SMEM));
     ELB_TC_CASE(3, 16) ELB_TC_CASE(3, 32) ELB_TC_CASE(3, 64) ELB_TC_CASE(4, 16) ELB_TC_CASE(4, 32) ELB_TC_CASE(4, 48)
 #undef ELB_TC_CASE
     ELB_CUDA(cudaGetLastError());

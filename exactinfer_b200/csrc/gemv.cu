@@ -14,6 +14,8 @@
 #include <cstdlib>
 #include <string>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "split.cuh"
 #include "gemv_core.cuh"
@@ -287,17 +289,8 @@ int gemv_prepare(Weight* w) {
 
 template <typename K, typename P>
 static int launch(K kernel, int grid, size_t smem, bool pdl, cudaStream_t s, const P& params) {
-    static thread_local const void* configured[16] = {};
-    static thread_local size_t configured_smem[16] = {};
-    // raise the dynamic shared memory limit once per kernel (and again if a larger row length shows up)
-    int slot = -1;
-    for (int i = 0; i < 16; ++i)
-        if (configured[i] == (const void*)kernel || !configured[i]) { slot = i; break; }
-    if (slot >= 0 && (configured[slot] != (const void*)kernel || configured_smem[slot] < smem)) {
-        ELB_CUDA(cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        configured[slot] = (const void*)kernel;
-        configured_smem[slot] = smem;
-    }
+    // raise the dynamic shared memory limit once per kernel and device (and again if a larger row length shows up)
+    ELB_TRY(ensure_dyn_smem((const void*)kernel, smem));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GEMV_THREADS);
@@ -416,7 +409,9 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
 // the runtime, not an address a kernel could use, so the address is asked for once per device and remembered.
 static int noalloc_scratch(int device, unsigned char** out) {
     static unsigned char* cache[64] = {};
+    static std::mutex mu;  // serving threads may make their first calls at the same time
     if (device < 0 || device >= 64) return fail(ELB_ERR_INVALID, "matvec_static: device index out of range");
+    std::lock_guard<std::mutex> lock(mu);
     if (!cache[device]) {
         void* p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);

@@ -98,6 +98,7 @@ bool read_value(Cursor8& c, uint32_t type, const std::string& key, Meta* m) {
 }
 
 int64_t tensor_bytes(uint32_t type, uint64_t n, uint64_t rows) {
+    if (n > (uint64_t(1) << 31) || rows > (uint64_t(1) << 31)) return -1;  // n * rows * 4 stays far below 2^63
     switch (type) {
         case ELB_F32: return int64_t(n * rows * 4);
         case ELB_F16: return int64_t(n * rows * 2);
@@ -196,6 +197,44 @@ int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int 
     if (!emb || emb->ne.size() != 2 || emb->ne[0] != uint64_t(cfg.n_embd)) return fail(ELB_ERR_INVALID, "load_gguf: token_embd.weight missing or of the wrong shape");
     cfg.n_vocab = int(emb->ne[1]);
 
+    // Every tensor of the model is looked up, sized and bounds-checked before a device or a communicator is touched
+    // (expect_shape of the reference, src/model.cpp:76,92-95: the norm vectors have E, the head norms head_dim values).
+    if (cfg.n_layer <= 0 || cfg.n_layer > 512 || cfg.n_embd <= 0 || cfg.n_ff <= 0 || cfg.n_head <= 0 || cfg.n_head_kv <= 0 || cfg.head_dim <= 0)
+        return fail(ELB_ERR_INVALID, "load_gguf: implausible model dimensions");
+    auto vet = [&](const std::string& name, bool required, uint64_t want_n, uint64_t want_rows) -> int {
+        const TensorInfo* t = find(name);
+        if (!t) return required ? fail(ELB_ERR_INVALID, "load_gguf: tensor " + name + " is missing") : ELB_OK;
+        const uint64_t n = t->ne.empty() ? 0 : t->ne[0], rows = t->ne.size() > 1 ? t->ne[1] : 1;
+        if (t->ne.size() > 2 || n == 0) return fail(ELB_ERR_UNSUPPORTED, "load_gguf: unexpected rank of " + name);
+        if (n != want_n || rows != want_rows) return fail(ELB_ERR_UNSUPPORTED, "load_gguf: unexpected shape of " + name);
+        const int64_t bytes = tensor_bytes(t->type, n, rows);
+        if (bytes < 0) return fail(ELB_ERR_UNSUPPORTED, "load_gguf: tensor type of " + name + " is not supported (F32, F16, Q8_0, Q4_K, Q6_K)");
+        if (data0 > map.size || t->offset > map.size - data0 || uint64_t(bytes) > map.size - data0 - t->offset)
+            return fail(ELB_ERR_INVALID, "load_gguf: tensor " + name + " runs past the end of the file");
+        return ELB_OK;
+    };
+    {
+        const uint64_t E = uint64_t(cfg.n_embd), V = uint64_t(cfg.n_vocab), F = uint64_t(cfg.n_ff), D = uint64_t(cfg.head_dim);
+        const uint64_t QD = uint64_t(cfg.n_head) * D, KD = uint64_t(cfg.n_head_kv) * D;
+        ELB_TRY(vet("token_embd.weight", true, E, V));
+        ELB_TRY(vet("output.weight", false, E, V));
+        ELB_TRY(vet("output_norm.weight", true, E, 1));
+        for (int l = 0; l < cfg.n_layer; ++l) {
+            const std::string b = "blk." + std::to_string(l) + ".";
+            ELB_TRY(vet(b + "attn_norm.weight", true, E, 1));
+            ELB_TRY(vet(b + "ffn_norm.weight", true, E, 1));
+            ELB_TRY(vet(b + "attn_q_norm.weight", true, D, 1));
+            ELB_TRY(vet(b + "attn_k_norm.weight", true, D, 1));
+            ELB_TRY(vet(b + "attn_q.weight", true, E, QD));
+            ELB_TRY(vet(b + "attn_k.weight", true, E, KD));
+            ELB_TRY(vet(b + "attn_v.weight", true, E, KD));
+            ELB_TRY(vet(b + "attn_output.weight", true, QD, E));
+            ELB_TRY(vet(b + "ffn_gate.weight", true, E, F));
+            ELB_TRY(vet(b + "ffn_up.weight", true, E, F));
+            ELB_TRY(vet(b + "ffn_down.weight", true, F, E));
+        }
+    }
+
     Model* m = nullptr;
     // under tensor parallelism every rank maps the whole file; model_set_tensor keeps this rank's cut of each tensor,
     // so only those pages of the mapping are read for the column-parallel matrices
@@ -207,7 +246,9 @@ int model_load_gguf(const char* path, int n_ctx, int device, int max_batch, int 
         if (t->ne.size() > 2 || n == 0) return fail(ELB_ERR_UNSUPPORTED, "load_gguf: unexpected rank of " + name);
         const int64_t bytes = tensor_bytes(t->type, n, rows);
         if (bytes < 0) return fail(ELB_ERR_UNSUPPORTED, "load_gguf: tensor type of " + name + " is not supported (F32, F16, Q8_0, Q4_K, Q6_K)");
-        if (data0 + t->offset + uint64_t(bytes) > map.size) return fail(ELB_ERR_INVALID, "load_gguf: tensor " + name + " runs past the end of the file");
+        // (compared without forming data0 + offset + bytes: the offset comes from the file and may be close to 2^64)
+        if (data0 > map.size || t->offset > map.size - data0 || uint64_t(bytes) > map.size - data0 - t->offset)
+            return fail(ELB_ERR_INVALID, "load_gguf: tensor " + name + " runs past the end of the file");
         return model_set_tensor(m, role, layer, int(t->type), int64_t(rows), int64_t(n), base + data0 + t->offset, size_t(bytes));
     };
     int rc = give("token_embd.weight", ELB_TOK_EMBD, 0, true);

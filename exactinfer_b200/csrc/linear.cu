@@ -469,13 +469,9 @@ int gemm_planes_launch(const Weight* w, const int8_t* d_limbs, const float* d_in
                  B, int(w->n), w->n_planes, w->type == ELB_Q8_0 ? 32 : 256, epilogue};
     const int64_t rows16 = w->tiles * 16;
     const unsigned tok_tiles = unsigned((B + GM_TOK - 1) / GM_TOK);
-    static thread_local bool configured = false;
-    if (!configured) {
-        ELB_CUDA(cudaFuncSetAttribute(k_gemm_q8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (1 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
-        ELB_CUDA(cudaFuncSetAttribute(k_gemm_q8<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (2 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
-        ELB_CUDA(cudaFuncSetAttribute(k_gemm_planes<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(2 * (2 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
-        configured = true;
-    }
+    ELB_TRY(ensure_dyn_smem((const void*)k_gemm_q8<1>, size_t(2 * (1 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
+    ELB_TRY(ensure_dyn_smem((const void*)k_gemm_q8<2>, size_t(2 * (2 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
+    ELB_TRY(ensure_dyn_smem((const void*)k_gemm_planes<2>, size_t(2 * (2 * GM_ROWS + 4 * GM_TOK) * GM_LD)));
     if (w->n_planes == 1) {  // Q8_0: 128-row tiles when that still leaves a few CTAs for every SM
         DeviceInfo di;
         ELB_TRY(device_info(w->device, &di));

@@ -112,6 +112,9 @@ int64_t slot_of(const Model* m, int role, int layer) { return role <= ELB_OUTPUT
 
 int upload_f32(const HostTensor& t, float** out) {
     if (!t.bytes) return fail(ELB_ERR_STATE, "model: a norm tensor is missing");
+    if (t.type != ELB_F32 && t.type != ELB_F16) return fail(ELB_ERR_UNSUPPORTED, "model: norm weights must be F32 or F16");
+    if (t.rows <= 0 || t.n <= 0 || t.nbytes != size_t(t.rows) * size_t(t.n) * (t.type == ELB_F32 ? 4 : 2))
+        return fail(ELB_ERR_INVALID, "model: a norm tensor's byte count does not match its shape");
     std::vector<float> v(size_t(t.rows * t.n));
     if (t.type == ELB_F32) {
         std::memcpy(v.data(), t.bytes, v.size() * 4);
@@ -670,6 +673,19 @@ int model_finalize(Model* m) {
         ELB_TRY(check_shape(P(ELB_GATE, l), F, E, "ffn_gate"));
         ELB_TRY(check_shape(P(ELB_UP, l), F, E, "ffn_up"));
         ELB_TRY(check_shape(P(ELB_DOWN, l), E, F, "ffn_down"));
+    }
+    // norm vectors (expect_shape {E} / {head_dim} of the reference, src/model.cpp:76,92-95): the kernels read E or
+    // head_dim floats from them whatever the caller said their length was
+    auto check_vec = [&](const HostTensor& t, int64_t len, const char* what) -> int {
+        if (t.bytes && t.rows * t.n != len) return fail(ELB_ERR_UNSUPPORTED, std::string("model: unexpected shape of ") + what);
+        return ELB_OK;
+    };
+    ELB_TRY(check_vec(P(ELB_OUTPUT_NORM, 0), E, "output_norm"));
+    for (int l = 0; l < c.n_layer; ++l) {
+        ELB_TRY(check_vec(P(ELB_ATTN_NORM, l), E, "attn_norm"));
+        ELB_TRY(check_vec(P(ELB_FFN_NORM, l), E, "ffn_norm"));
+        ELB_TRY(check_vec(P(ELB_Q_NORM, l), c.head_dim, "attn_q_norm"));
+        ELB_TRY(check_vec(P(ELB_K_NORM, l), c.head_dim, "attn_k_norm"));
     }
     }
     if (m->tp.size > 1) {

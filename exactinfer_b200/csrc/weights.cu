@@ -2,6 +2,10 @@
 // tensor-core path, and the row decoders (embedding gather / parity checks) that read the tiled layout back.
 #include <vector>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "common.cuh"
 #include "layout.cuh"
 
@@ -91,6 +95,19 @@ int device_info(int device, DeviceInfo* out) {
         cache[device].sm_count = sms;
     }
     *out = cache[device];
+    return ELB_OK;
+}
+
+int ensure_dyn_smem(const void* kernel, size_t smem) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, size_t> done;
+    int device = 0;
+    ELB_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = done[{kernel, device}];
+    if (have >= smem && have > 0) return ELB_OK;
+    ELB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    have = smem;
     return ELB_OK;
 }
 

@@ -44,6 +44,9 @@ int elb_host_free(void* hptr);
 int elb_memcpy_h2d(void* dst, const void* src, size_t bytes);
 int elb_memcpy_d2h(void* dst, const void* src, size_t bytes);
 int elb_device_sync(int device);
+/* Free and total device memory in bytes (cudaMemGetInfo; the reference's pre-flight check reads the same figures,
+ * src/cuda/model_cuda.cu:1578-1591). */
+int elb_device_mem_info(int device, size_t* free_bytes, size_t* total_bytes);
 
 /* ---- weights ------------------------------------------------------------------------------------------------
  * One weight matrix W[rows][n] in a ggml block format, uploaded and re-laid out for the GPU kernels

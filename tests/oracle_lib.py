@@ -85,6 +85,7 @@ def ref():
         L.ref_model_eval.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _f32p]
         L.ref_model_close.argtypes = [C.c_void_p]
         L.ref_set_threads.argtypes = [C.c_int]
+        L.ref_threads.restype = C.c_int
         _ref = L
     return _ref
 
