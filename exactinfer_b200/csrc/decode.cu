@@ -4,10 +4,12 @@
 // each a few microseconds of HBM traffic on this GPU: launched as separate kernels they are bound by launch and
 // dependency latency, not by bandwidth. Here one CTA per SM stays resident for the whole step and walks the chain with
 // grid-wide barriers between the steps:
-//   * every warp owns a fixed, contiguous share of the (row tile, k block) units of every weight matrix of the step, in
-//     execution order — one long "unit stream" — and keeps DEPTH-1 units of that stream in flight (cp.async into its
-//     ring in shared memory) no matter which phase the CTA is in: HBM keeps streaming through barriers, attention
-//     and activation conversion;
+//   * every working warp owns a fixed, contiguous share of the (row tile, k block) units of every weight matrix of the
+//     step, in execution order — one long "unit stream" — and a seventeenth warp, which does nothing else, keeps every
+//     working warp's ring in shared memory as full as it gets (a byte ring: units of different block formats lie back
+//     to back; every unit is one bulk copy that reports to an mbarrier), no matter which phase the CTA is in: HBM
+//     keeps streaming through barriers, attention and activation conversion, and the working warps spend no
+//     instruction on requesting data;
 //   * the activation of a matvec is converted to int8 limbs redundantly by every CTA (shared memory), from the fp32
 //     vector and a global maximum (atomicMax, order independent) or the per-tile sums of squares (RMSNorm) that the
 //     producing phase left: no serial single-CTA section;
@@ -27,10 +29,25 @@
 
 namespace elb {
 
-constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32, DK_DEPTH = 3;
+constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32;  // the working warps; the CTA has one more warp, the producer
+// The CTA is launched with one more warpgroup (four warps, the unit in which registers can be handed over): its first
+// warp is the producer, the other three leave at once. Registers per thread: the compiler sizes the kernel for
+// 65536 / 640 = 96; the extra warpgroup then shrinks to DK_REGS_PRODUCER and the working warps grow to DK_REGS_WORKER.
+// The working warps can only take what the extra warpgroup has given back (registers the CTA never held are not in
+// its pool, and a warp asking for more than the pool holds waits for ever): 4 * 32 * (96 - 32) = 8192 registers released,
+// 16 * 32 * (112 - 96) = 8192 taken.
+constexpr int DK_CTA_THREADS = DK_THREADS + 128;
+constexpr int DK_REGS_LAUNCH = 96, DK_REGS_WORKER = 112, DK_REGS_PRODUCER = 32;
+static_assert(4 * 32 * (DK_REGS_LAUNCH - DK_REGS_PRODUCER) >= DK_THREADS * (DK_REGS_WORKER - DK_REGS_LAUNCH),
+              "the working warps would wait for registers that nobody releases");
+constexpr unsigned DK_MBAR_LIMIT = 1u << 17;  // tries of one wait for a weight unit (each try blocks for a while in hardware)
+constexpr int DK_NBAR = 8;  // mbarriers per warp = most units a warp can have requested and not yet consumed
 constexpr int DK_HD = 128, DK_KT = 48, DK_KS = DK_HD + 4, DK_MAXG = 8, DK_MAXSPLIT = 32;  // DK_KS: row stride of the K tile (float4 reads without bank conflicts)
 constexpr unsigned DK_SPIN_LIMIT = 1u << 22;
 constexpr unsigned DK_XSPIN_LIMIT = 1u << 24;  // waits on another GPU (x ~100 ns: about two seconds)
+
+// CTA barrier of the working warps (the producer warp runs on its own): a named barrier over DK_THREADS threads
+__device__ __forceinline__ void dk_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DK_THREADS) : "memory"); }
 
 // ---------------------------------------------------------------- grid barrier (bounded)
 
@@ -44,7 +61,7 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
 // counter is never reset: a launch starts from launches * barriers per launch * CTAs). Returns false when the wait ran out (or an
 // earlier one did): the caller stops working, every later barrier returns at once.
 __device__ __forceinline__ bool grid_barrier(const DkParams& p, unsigned& target, int* s_dead) {
-    __syncthreads();
+    dk_sync();
     if (threadIdx.x == 0 && !*s_dead) {
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");  // orders the CTA's writes before it
         target += gridDim.x;
@@ -60,7 +77,7 @@ __device__ __forceinline__ bool grid_barrier(const DkParams& p, unsigned& target
         // (no fence here: the acquire load that saw the last arrival synchronises with every CTA's release, and the
         // CTA barrier below carries that to the other threads)
     }
-    __syncthreads();
+    dk_sync();
     return !*s_dead;
 }
 
@@ -83,7 +100,7 @@ __device__ __forceinline__ void st_release_gpu(unsigned* p, unsigned v) {
 // rank's flag words. One rank: the grid barrier. All waits bounded.
 __device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& target, unsigned x, int* s_dead) {
     if (p.tp_size == 1) return grid_barrier(p, target, s_dead);
-    __syncthreads();
+    dk_sync();
     if (threadIdx.x == 0 && !*s_dead) {
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");
         target += gridDim.x;
@@ -111,7 +128,7 @@ __device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& ta
         }
         __threadfence();
     }
-    __syncthreads();
+    dk_sync();
     return !*s_dead;
 }
 
@@ -122,7 +139,7 @@ __device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& ta
 __device__ __forceinline__ float dk_block_max(float v, float* red, int tid) {
     v = warp_max(v);
     if ((tid & 31) == 0) red[tid >> 5] = v;
-    __syncthreads();
+    dk_sync();
     float m = red[0];
 #pragma unroll
     for (int i = 1; i < DK_WARPS; ++i) m = fmaxf(m, red[i]);
@@ -131,7 +148,7 @@ __device__ __forceinline__ float dk_block_max(float v, float* red, int tid) {
 __device__ __forceinline__ double dk_block_sum(double v, double* red, int tid) {
     v = warp_sum(v);
     if ((tid & 31) == 0) red[tid >> 5] = v;
-    __syncthreads();
+    dk_sync();
     double s = 0.0;
 #pragma unroll
     for (int i = 0; i < DK_WARPS; ++i) s += red[i];  // fixed order
@@ -190,7 +207,8 @@ __device__ __forceinline__ void limb_sums(const ActSmem& a, int n, int sd_mask) 
         }
     }
 }
-__device__ __forceinline__ int sd_need(const DkMat& m) { return m.type == ELB_Q4_K ? 1 : m.type == ELB_Q6_K ? 2 : 0; }
+__device__ __forceinline__ int sd_need(int type) { return type == ELB_Q4_K ? 1 : type == ELB_Q6_K ? 2 : 0; }
+__device__ __forceinline__ int unit_bytes_of(int type) { return type == ELB_Q4_K ? Q4K_UNIT : type == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT; }
 
 // Activation of the next matvec -> limbs in shared memory, by every CTA for itself. Two sources:
 //  * resid != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): the vector is
@@ -281,9 +299,9 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
         for (int i = tid * 4; i < n; i += DK_THREADS * 4)
             limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, a.lim, a.n_pad, i);
     }
-    __syncthreads();
+    dk_sync();
     limb_sums(a, n, sd_mask);
-    __syncthreads();
+    dk_sync();
     return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
 }
 
@@ -297,7 +315,7 @@ __device__ float convert_act_global(const float* src, int n, const unsigned* ama
     const Pow2 sc = make_pow2(k);
     for (int i = b0 * 256 + tid * 4; i < b1 * 256; i += DK_THREADS * 4)
         limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, g.lim, g.n_pad, i);
-    __syncthreads();  // this CTA's limbs are visible to its own threads
+    dk_sync();  // this CTA's limbs are visible to its own threads
     if (sd_mask & 1) {
         for (int e = b0 * 32 + tid; e < b1 * 32; e += DK_THREADS) {  // 8 sub-blocks x 4 limbs per block
             const int S = e >> 2, l = e & 3;
@@ -336,19 +354,16 @@ __device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
 
 // ---------------------------------------------------------------- the unit stream of one warp
 
-// Matrices of the step in execution order: per layer qkv segments, wo, gate|up, down; then the head.
-__device__ __forceinline__ const DkMat& mat_at(const DkParams& p, int j) {
-    const int per = p.n_qkv + 3, l = j / per, i = j - l * per;
-    if (l >= p.n_layer) return p.layers[p.n_layer].wo;  // the head
-    const DkLayer& L = p.layers[l];
-    return i < p.n_qkv ? L.qkv[i] : i == p.n_qkv ? L.wo : i == p.n_qkv + 1 ? L.gu : L.down;
-}
+// Matrices of the step in execution order: per layer qkv segments, wo, gate|up, down; then the head. Matrix `i` of
+// layer `l` (l == n_layer, i == 0: the head). Every layer has the same shapes, so the way a matrix is shared between
+// CTAs and warps depends only on its kind.
+__device__ __forceinline__ int kind_li(const DkParams& p, int l, int i) { return l >= p.n_layer ? 6 : i < p.n_qkv ? i : 3 + i - p.n_qkv; }
 
 // The CTA's share of a matrix as a range of units [cA, cB), cut into equal ranges for its warps [wA, wB).
 // Whole tiles of the matrix's group by default (no tile is shared between CTAs: the phase ends without any exchange;
 // a group with fewer tiles than CTAs occupies the first CTAs only); equal unit ranges for a balanced matrix.
 struct WarpRange { int cA, cB, wA, wB; };
-__device__ __forceinline__ WarpRange warp_range(const DkMat& m, int warp) {
+__device__ __forceinline__ WarpRange warp_range(const DkKind& m, int warp) {
     const int c = blockIdx.x;
     WarpRange r;
     if (m.balanced) {
@@ -366,32 +381,162 @@ __device__ __forceinline__ WarpRange warp_range(const DkMat& m, int warp) {
     return r;
 }
 
+// The shares of a warp (and of its CTA) in the matrices of every kind are computed once, when the kernel starts, and
+// kept in shared memory: sched[warp][kind] = {wA, wB}, cta[kind] = {cA, cB}.
+struct Sched {
+    const int2* warp;  // this warp's [DK_KINDS]
+    const int2* cta;   // [DK_KINDS]
+};
+
 // Prefetch cursor: the next unit of this warp's stream that has not been requested yet.
 struct Cursor {
-    int j, n_mats, u, end, unit_bytes;
+    int l, i, u, end, unit_bytes;  // matrix i of layer l (l > n_layer: the stream has ended)
     const uint8_t* W;
 };
-__device__ __forceinline__ void cursor_seek(const DkParams& p, Cursor& c, int warp) {  // first non-empty range from c.j on
-    while (c.j < c.n_mats) {
-        const DkMat& m = mat_at(p, c.j);
-        const WarpRange r = warp_range(m, warp);
-        if (r.wA < r.wB) {
-            c.u = r.wA; c.end = r.wB; c.W = m.W; c.unit_bytes = m.unit_bytes;
+__device__ __forceinline__ bool cursor_live(const DkParams& p, const Cursor& c) { return c.l <= p.n_layer; }
+__device__ __forceinline__ void cursor_next_matrix(const DkParams& p, Cursor& c) {
+    if (c.l >= p.n_layer || ++c.i == p.n_qkv + 3) { c.i = 0; ++c.l; }
+}
+__device__ __forceinline__ void cursor_seek(const DkParams& p, Cursor& c, const Sched& sc) {  // first non-empty range from (l, i) on
+    while (cursor_live(p, c)) {
+        const int2 r = sc.warp[kind_li(p, c.l, c.i)];
+        if (r.x < r.y) {
+            c.u = r.x; c.end = r.y; c.W = p.W[c.l][c.i]; c.unit_bytes = unit_bytes_of(p.wtype[c.l][c.i]);
             return;
         }
-        ++c.j;
+        cursor_next_matrix(p, c);
     }
 }
-// request the cursor's unit into `slot` (if the stream has not ended) and move on; always one commit group
-__device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8_t* slot, int warp, int lane) {
-    if (c.j < c.n_mats) {
-        issue_unit(slot, c.W + size_t(c.u) * c.unit_bytes, c.unit_bytes, lane);
-        if (++c.u == c.end) {
-            ++c.j;
-            cursor_seek(p, c, warp);
+
+// The ring of one working warp: `bytes` bytes of shared memory that the units of the warp's stream pass through in
+// order. A unit is requested with one bulk copy (global -> shared, completion counted in bytes on an mbarrier) by the
+// producer warp (its lane w serves working warp w) and consumed by the working warp; its place is given up when the
+// arithmetic on it is done. Units are placed back to back; one that would cross the end of the ring starts at offset 0
+// instead and the bytes left over count as used until the consumer has passed them too (consumer and producer walk the
+// same sequence of unit sizes, so both take the same decisions). Unit number q of the warp (counted from the start of
+// the kernel) reports to mbarrier q % DK_NBAR, whose phase for it has parity (q / DK_NBAR) & 1; the ring is at most
+// DK_NBAR of the smallest units long, so no more than DK_NBAR units are ever on request. The consumer tells the producer
+// how far it has come through one word of shared memory: the number of bytes it has given up since the kernel started.
+struct RingShared {       // in shared memory, one set for the CTA
+    unsigned freed[DK_WARPS];    // bytes given up by working warp w so far (gaps included)
+    unsigned issued[DK_WARPS];   // units requested for warp w in all, written when the producer ends
+    int producer_done;
+};
+struct Ring {             // consumer side, in registers of the working warp
+    uint32_t base;        // shared-memory addresses (32 bit) of the ring's first byte and of its first mbarrier
+    uint32_t bars;
+    int bytes;
+    int c_off;            // offset of the next unit to consume (before the wrap rule is applied)
+    unsigned c_seq;       // units given up so far
+    unsigned freed;       // bytes given up so far
+    unsigned* freed_out;  // where the producer reads it
+};
+
+__device__ __forceinline__ uint32_t dk_smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ const uint8_t* dk_smem_ptr(uint32_t a) { return static_cast<const uint8_t*>(__cvta_shared_to_generic(size_t(a))); }
+
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// The producer warp: lane w < DK_WARPS walks the stream of working warp w and requests its units as room appears in that
+// warp's ring. All lanes run in step, so the bookkeeping is paid once for the sixteen rings. Ends when every stream
+// has been requested to its end, when the step is given up (dead flag), or when nothing has moved for too long.
+__device__ void producer_warp(const DkParams& p, const uint32_t ring0, const int ring_bytes, const uint32_t bars0,
+                              const int2* sched_all, RingShared* rs, const int* s_dead, const int lane) {
+    const bool mine = lane < DK_WARPS;
+    const Sched sc{sched_all + (mine ? lane : 0) * DK_KINDS, nullptr};
+    Cursor c;
+    c.l = 0;
+    c.i = 0;
+    c.u = c.end = c.unit_bytes = 0;
+    c.W = nullptr;
+    if (mine) cursor_seek(p, c, sc);
+    else c.l = p.n_layer + 1;
+    const uint32_t base = ring0 + uint32_t(lane * ring_bytes), bars = bars0 + uint32_t(lane * DK_NBAR) * 8u;
+    unsigned issued = 0, seq = 0, idle = 0;
+    int off = 0;
+    const volatile unsigned* freed = rs->freed + (mine ? lane : 0);
+    while (true) {
+        const bool live = cursor_live(p, c);
+        if (!__any_sync(0xffffffffu, live)) break;
+        bool did = false;
+        if (live) {
+            const int ub = c.unit_bytes;
+            const bool wrap = off + ub > ring_bytes;
+            const int need = wrap ? ring_bytes - off + ub : ub;
+            if (int(issued - *freed) + need <= ring_bytes) {
+                if (wrap) off = 0;
+                const uint32_t bar = bars + (seq % DK_NBAR) * 8u;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(ub) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(base + uint32_t(off)), "l"(c.W + size_t(c.u) * ub), "r"(ub), "r"(bar)
+                             : "memory");
+                issued += unsigned(need);
+                off += ub;
+                ++seq;
+                did = true;
+                if (++c.u == c.end) {
+                    cursor_next_matrix(p, c);
+                    cursor_seek(p, c, sc);
+                }
+            }
+        }
+        if (__any_sync(0xffffffffu, did)) {
+            idle = 0;
+        } else {
+            if (*reinterpret_cast<const volatile int*>(s_dead) || ++idle > DK_SPIN_LIMIT) break;
+            __nanosleep(40);
         }
     }
-    ring_commit();
+    if (mine) rs->issued[lane] = seq;
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&rs->producer_done) = 1;
+    }
+}
+
+// Wait (bounded) until the oldest requested unit, of `ub` bytes, has arrived; returns where it lies. On timeout the
+// dead flag and the error word are raised and the caller goes on with whatever the ring holds: the next grid barrier
+// ends the step.
+__device__ __forceinline__ uint32_t ring_front(const DkParams& p, Ring& r, int ub, int* s_dead) {
+    if (r.c_off + ub > r.bytes) {  // the producer skipped the end of the ring for this unit
+        r.freed += unsigned(r.bytes - r.c_off);
+        r.c_off = 0;
+    }
+    const uint32_t bar = r.bars + (r.c_seq % DK_NBAR) * 8u, parity = (r.c_seq / DK_NBAR) & 1u;
+    bool done = false;
+    for (unsigned it = 0; it < DK_MBAR_LIMIT && !done; ++it) done = mbar_try(bar, parity);
+    if (!done && !*s_dead) {
+        *s_dead = 1;
+        atomicExch(p.err, 1);
+    }
+    return r.base + uint32_t(r.c_off);
+}
+// The unit at the front has been used up by every lane (the caller has synchronised the warp): its bytes are free again.
+__device__ __forceinline__ void ring_pop(Ring& r, int ub, int lane) {
+    r.c_off += ub;
+    r.freed += unsigned(ub);
+    ++r.c_seq;
+    if (lane == 0) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(dk_smem_u32(r.freed_out)), "r"(r.freed) : "memory");
+}
+// Before the kernel ends: the producer must have stopped and every copy it requested must have landed (bounded waits).
+__device__ __forceinline__ void ring_drain(Ring& r, const RingShared* rs, int warp) {
+    unsigned it = 0;
+    while (!*reinterpret_cast<const volatile int*>(&rs->producer_done) && ++it < DK_SPIN_LIMIT) __nanosleep(100);
+    const unsigned end = *reinterpret_cast<const volatile unsigned*>(&rs->issued[warp]);
+    for (; r.c_seq != end; ++r.c_seq) {
+        const uint32_t bar = r.bars + (r.c_seq % DK_NBAR) * 8u, parity = (r.c_seq / DK_NBAR) & 1u;
+        bool done = false;
+        for (unsigned j = 0; j < DK_MBAR_LIMIT && !done; ++j) done = mbar_try(bar, parity);
+    }
 }
 
 // ---------------------------------------------------------------- one matvec phase
@@ -399,8 +544,7 @@ __device__ __forceinline__ void cursor_issue(const DkParams& p, Cursor& c, uint8
 enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU_AMAX = 2, DK_EPI_LOGITS = 3 };
 
 struct PhaseSmem {
-    uint8_t* ring;   // this warp's ring [DK_DEPTH][slot_bytes]
-    int slot_bytes;
+    Sched sched;
     ActSmem act;
     float* red;      // [DK_WARPS][slots][16]
     double* red8;    // [DK_WARPS]
@@ -410,9 +554,10 @@ struct PhaseSmem {
 };
 
 template <int TYPE, bool CG>
-__device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r, Cursor& pf, int& rs,
+__device__ void run_units(const DkParams& p, const int upt, const WarpRange& r, Ring& rg,
                           const PhaseSmem& s, int warp, int lane) {
-    const int g = lane >> 2, t = lane & 3, upt = m.upt;
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int UB = TYPE == ELB_Q4_K ? Q4K_UNIT : TYPE == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT;
     const int8_t* sd = TYPE == ELB_Q6_K ? s.act.sd16 : s.act.sd32;
     Acc a{{0.f, 0.f}, {0.f, 0.f}};
     int slot = 0;
@@ -421,15 +566,23 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
     const float wt = t < 2 ? (t & 1 ? 65536.0f : 1.0f) : 0.0f;
     const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
     DbgOut dbg{nullptr, nullptr, nullptr, 0, 0, 0, 0};
+#ifdef ELB_DK_UNITPROF  // diagnostics build: where warp 0 of CTA 0 spends its clocks inside the unit loop
+    const bool prof = p.prof && blockIdx.x == 0 && warp == 0;
+    long long tp = 0, tw = 0, tc = 0, te = 0, t0 = 0, t1 = 0;
+#define ELB_TICK(acc) if (prof) { t1 = clock64(); acc += t1 - t0; t0 = t1; }
+    if (prof) t0 = clock64();
+#else
+#define ELB_TICK(acc)
+#endif
     for (int u = r.wA; u < r.wB; ++u) {
-        cursor_issue(p, pf, s.ring + (rs == 0 ? DK_DEPTH - 1 : rs - 1) * s.slot_bytes, warp, lane);
-        ring_wait<DK_DEPTH - 1>();
-        __syncwarp();
         Unit<TYPE> cur;
-        load_unit(cur, s.ring + rs * s.slot_bytes, lane);
-        rs = rs + 1 == DK_DEPTH ? 0 : rs + 1;
+        const uint32_t src = ring_front(p, rg, UB, &s.flags[2]);
+        ELB_TICK(tw)
+        load_unit(cur, dk_smem_ptr(src), lane);
         compute_unit<false, CG>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg);
-        __syncwarp();
+        __syncwarp();  // every lane has its fragments of the unit in registers and has used them
+        ring_pop(rg, UB, lane);
+        ELB_TICK(tc)
         if (++b == upt || u + 1 == r.wB) {
             float v0 = a.acc[0] * wt - a.accm[0] * wtm, v1 = a.acc[1] * wt - a.accm[1] * wtm;
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
@@ -444,7 +597,18 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
             a = Acc{{0.f, 0.f}, {0.f, 0.f}};
             if (b == upt) { b = 0; ++X; }
         }
+        ELB_TICK(te)
     }
+#ifdef ELB_DK_UNITPROF
+    if (prof && lane == 0) {
+        atomicAdd(p.prof + 16, (unsigned long long)tp);
+        atomicAdd(p.prof + 17, (unsigned long long)tw);
+        atomicAdd(p.prof + 18, (unsigned long long)tc);
+        atomicAdd(p.prof + 19, (unsigned long long)te);
+        atomicAdd(p.prof + 20, (unsigned long long)(r.wB - r.wA));
+    }
+#endif
+#undef ELB_TICK
 }
 
 // y = W * act for one matrix; the activation limbs are already in shared memory. Ends with this CTA's share written:
@@ -455,29 +619,30 @@ __device__ void run_units(const DkParams& p, const DkMat& m, const WarpRange& r,
 //                     a CTA that holds the whole tile writes zeros to vector 1. Stored on every tensor-parallel rank;
 //                     the consumer adds residual + all the vectors (convert_act).
 //   DK_EPI_LOGITS     y[v0 + row] = sum on every tensor-parallel rank (this rank's vocabulary rows of the head)
-__device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* y, float inv_scale, Cursor& pf,
-                             int& rs, const PhaseSmem& s, unsigned* amax_out, int xset = 0, bool gact = false,
+__device__ void matvec_phase(const DkParams& p, const int type, const int kind, int epi, float* y, float inv_scale, Ring& rg,
+                             const PhaseSmem& s, unsigned* amax_out, int xset = 0, bool gact = false,
                              bool after_matrix = true) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = m.upt;
-    const WarpRange r = warp_range(m, warp);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = p.kind[kind].upt, rows = p.kind[kind].rows;
+    const int2 rc = s.sched.cta[kind], rw = s.sched.warp[kind];
+    const WarpRange r{rc.x, rc.y, rw.x, rw.y};
     if (tid == 0) s.flags[3] = 0;
     // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v); the first matrix
     // comes straight from the conversion, which ends with a CTA barrier
-    if (after_matrix) __syncthreads();
+    if (after_matrix) dk_sync();
     if (gact) {  // activation limbs in global memory (written by other CTAs before the last barrier): L2 loads
-        switch (m.type) {
-            case ELB_Q4_K: run_units<ELB_Q4_K, true>(p, m, r, pf, rs, s, warp, lane); break;
-            case ELB_Q6_K: run_units<ELB_Q6_K, true>(p, m, r, pf, rs, s, warp, lane); break;
-            default: run_units<ELB_Q8_0, true>(p, m, r, pf, rs, s, warp, lane); break;
+        switch (type) {
+            case ELB_Q4_K: run_units<ELB_Q4_K, true>(p, upt, r, rg, s, warp, lane); break;
+            case ELB_Q6_K: run_units<ELB_Q6_K, true>(p, upt, r, rg, s, warp, lane); break;
+            default: run_units<ELB_Q8_0, true>(p, upt, r, rg, s, warp, lane); break;
         }
     } else {
-        switch (m.type) {
-            case ELB_Q4_K: run_units<ELB_Q4_K, false>(p, m, r, pf, rs, s, warp, lane); break;
-            case ELB_Q6_K: run_units<ELB_Q6_K, false>(p, m, r, pf, rs, s, warp, lane); break;
-            default: run_units<ELB_Q8_0, false>(p, m, r, pf, rs, s, warp, lane); break;
+        switch (type) {
+            case ELB_Q4_K: run_units<ELB_Q4_K, false>(p, upt, r, rg, s, warp, lane); break;
+            case ELB_Q6_K: run_units<ELB_Q6_K, false>(p, upt, r, rg, s, warp, lane); break;
+            default: run_units<ELB_Q8_0, false>(p, upt, r, rg, s, warp, lane); break;
         }
     }
-    __syncthreads();
+    dk_sync();
     if (r.cA < r.cB) {
         const int Xf = r.cA / upt, ntl = (r.cB - 1) / upt - Xf + 1;
         float mx = 0.f;
@@ -496,7 +661,7 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
             const int64_t r0 = 16 * int64_t(Xt) + gg, r1 = r0 + 8;
             if (epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
                 const int64_t o = 8 * int64_t(Xt) + gg;
-                if (o < m.rows / 2) {
+                if (o < rows / 2) {
                     const float act = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
                     y[o] = act;
                     mx = fmaxf(mx, fabsf(act));
@@ -509,11 +674,11 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
                     if (q >= p.tp_size) break;
                     float* base = p.part_peer[q] + pair;
                     float* dst = first ? base : base + p.E;
-                    if (r0 < m.rows) dst[r0] = v0;
-                    if (r1 < m.rows) dst[r1] = v1;
+                    if (r0 < rows) dst[r0] = v0;
+                    if (r1 < rows) dst[r1] = v1;
                     if (first && last && p.pv == 2) {
-                        if (r0 < m.rows) base[p.E + r0] = 0.f;
-                        if (r1 < m.rows) base[p.E + r1] = 0.f;
+                        if (r0 < rows) base[p.E + r0] = 0.f;
+                        if (r1 < rows) base[p.E + r1] = 0.f;
                     }
                 }
                 if (p.tp_size > 1) __threadfence_system();  // on the peers before this CTA arrives at the exchange barrier
@@ -521,13 +686,13 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     if (q >= p.tp_size) break;
-                    if (r0 < m.rows) p.logits_peer[q][p.v0 + r0] = v0;
-                    if (r1 < m.rows) p.logits_peer[q][p.v0 + r1] = v1;
+                    if (r0 < rows) p.logits_peer[q][p.v0 + r0] = v0;
+                    if (r1 < rows) p.logits_peer[q][p.v0 + r1] = v1;
                 }
                 if (p.tp_size > 1) __threadfence_system();
             } else {
-                if (r0 < m.rows) y[r0] = v0;
-                if (r1 < m.rows) y[r1] = v1;
+                if (r0 < rows) y[r0] = v0;
+                if (r1 < rows) y[r1] = v1;
             }
         }
         if (epi == DK_EPI_SILU_AMAX) {
@@ -536,7 +701,7 @@ __device__ void matvec_phase(const DkParams& p, const DkMat& m, int epi, float* 
         }
     }
     if (epi == DK_EPI_SILU_AMAX) {
-        __syncthreads();
+        dk_sync();
         if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
     }
 }
@@ -582,14 +747,14 @@ struct AttnSmem {
 
 // K and V rows t0 .. t0+nk-1 of one KV head -> shared memory with cp.async (row `pos`, which this step appends, is
 // filled in from shared memory by the caller). One commit group.
-__device__ __forceinline__ void attn_fetch_kv(const DkLayer& L, const AttnSmem& s, int KD, int kvh, int t0, int nk, int pos) {
+__device__ __forceinline__ void attn_fetch_kv(const float* kc, const float* vc, const AttnSmem& s, int KD, int kvh, int t0, int nk, int pos) {
     const unsigned ks = unsigned(__cvta_generic_to_shared(s.Ks)), vs = unsigned(__cvta_generic_to_shared(s.Vs));
     for (int idx = threadIdx.x; idx < nk * (DK_HD / 4); idx += DK_THREADS) {
         const int j = idx / (DK_HD / 4), cc = (idx % (DK_HD / 4)) * 4, t = t0 + j;
         if (t == pos) continue;
         const size_t off = size_t(t) * KD + kvh * DK_HD + cc;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks + unsigned(j * DK_KS + cc) * 4u), "l"(L.kc + off));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs + unsigned(j * DK_HD + cc) * 4u), "l"(L.vc + off));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks + unsigned(j * DK_KS + cc) * 4u), "l"(kc + off));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs + unsigned(j * DK_HD + cc) * 4u), "l"(vc + off));
     }
     ring_commit();
 }
@@ -597,55 +762,59 @@ __device__ __forceinline__ void attn_fetch_kv(const DkLayer& L, const AttnSmem& 
 // The first key / value tile of this CTA's attention part does not depend on the token in flight (its own row comes
 // from shared memory): it is requested as soon as the q|k|v matvec has released the scratch area, so that it travels
 // while the CTAs meet at the barrier in front of the attention.
-__device__ __forceinline__ void attn_prefetch(const DkParams& p, const DkLayer& L, const AttnSmem& s) {
+__device__ __forceinline__ void attn_prefetch(const DkParams& p, const int l, const AttnSmem& s) {
     const int c = blockIdx.x;
     if (c >= p.HKV * p.nsplit) return;
     const int kvh = c / p.nsplit, split = c - kvh * p.nsplit;
     const int pos = p.pos[p.ctl[0]], T = pos + 1;
     const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);
-    attn_fetch_kv(L, s, p.HKV * DK_HD, kvh, t_begin, min(DK_KT, t_end - t_begin), pos);
+    attn_fetch_kv(p.kc + size_t(l) * p.kv_stride, p.vc + size_t(l) * p.kv_stride, s, p.HKV * DK_HD, kvh, t_begin, min(DK_KT, t_end - t_begin), pos);
 }
 
 // CTA c < HKV * nsplit works on KV head c / nsplit, key split c % nsplit: q/k norm + RoPE, KV append, flash decode
 // over its keys (DK_KT at a time, fetched while the heads are normalised), partial results to the scratch buffer; the
 // last split of a KV head to arrive combines them in split order and writes att (and max|att|).
 // Semantics: src/model.cpp:176-214 of the reference.
-__device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& s, unsigned* amax_out) {
+__device__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, unsigned* amax_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c = blockIdx.x;
     if (c >= p.HKV * p.nsplit) return;
     const int kvh = c / p.nsplit, split = c - kvh * p.nsplit, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
     const int pos = p.pos[p.ctl[0]], T = pos + 1;
+    float* const kc = p.kc + size_t(l) * p.kv_stride;
+    float* const vc = p.vc + size_t(l) * p.kv_stride;
+    const float* const q_norm = p.norms + size_t(l) * p.norm_stride + 2 * p.E;
+    const float* const k_norm = q_norm + DK_HD;
     const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);  // equal key ranges
     // (the first tile was requested by attn_prefetch before the barrier)
     const float2* cs = reinterpret_cast<const float2*>(p.rope) + size_t(pos) * (p.rope_dim / 2);
     float* m_s = s.corr + DK_MAXG;
     float* l_s = s.corr + 2 * DK_MAXG;
     for (int h = warp; h < group + 1; h += DK_WARPS) {
-        if (h < group) dk_head_norm_rope(p.qkv + (kvh * group + h) * DK_HD, L.q_norm, cs, p.rope_dim, p.eps, s.qs + h * DK_HD, lane);
-        else dk_head_norm_rope(p.qkv + QD + kvh * DK_HD, L.k_norm, cs, p.rope_dim, p.eps, s.knew, lane);
+        if (h < group) dk_head_norm_rope(p.qkv + (kvh * group + h) * DK_HD, q_norm, cs, p.rope_dim, p.eps, s.qs + h * DK_HD, lane);
+        else dk_head_norm_rope(p.qkv + QD + kvh * DK_HD, k_norm, cs, p.rope_dim, p.eps, s.knew, lane);
     }
     if (tid >= DK_THREADS - DK_HD) s.vnew[tid - (DK_THREADS - DK_HD)] = __ldcg(p.qkv + QD + KD + kvh * DK_HD + tid - (DK_THREADS - DK_HD));
     if (tid < DK_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
     if (tid == 0) s.flags[3] = 0;
-    __syncthreads();
+    dk_sync();
     if (split == 0 && tid < DK_HD) {  // KV append (src/model.cpp:186-189): only row `pos` is written
-        L.kc[size_t(pos) * KD + kvh * DK_HD + tid] = s.knew[tid];
-        L.vc[size_t(pos) * KD + kvh * DK_HD + tid] = s.vnew[tid];
+        kc[size_t(pos) * KD + kvh * DK_HD + tid] = s.knew[tid];
+        vc[size_t(pos) * KD + kvh * DK_HD + tid] = s.vnew[tid];
     }
     float acc[2] = {0.f, 0.f};  // outputs (head tid/128 + 4i, dim tid%128)
     const int od = tid & (DK_HD - 1), oh = tid >> 7;
     for (int t0 = t_begin; t0 < t_end; t0 += DK_KT) {
         const int nk = min(DK_KT, t_end - t0);
         if (t0 != t_begin) {
-            __syncthreads();  // the previous tile has been consumed
-            attn_fetch_kv(L, s, KD, kvh, t0, nk, pos);
+            dk_sync();  // the previous tile has been consumed
+            attn_fetch_kv(kc, vc, s, KD, kvh, t0, nk, pos);
         }
         if (pos >= t0 && pos < t0 + nk && tid < DK_HD) {  // the row this step appends: from shared memory, not from the cache
             s.Ks[(pos - t0) * DK_KS + tid] = s.knew[tid];
             s.Vs[(pos - t0) * DK_HD + tid] = s.vnew[tid];
         }
         ring_wait<0>();
-        __syncthreads();
+        dk_sync();
         // scores: warp = (head, 32-key slot), lane = key; dimension order, multiply then add, as the CPU path does
         for (int w = warp; w < group * ((nk + 31) / 32); w += DK_WARPS) {
             const int h = w % group, j = (w / group) * 32 + lane;
@@ -664,7 +833,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
                 s.Ps[h * DK_KT + j] = __fmul_rn(a, p.scale);
             }
         }
-        __syncthreads();
+        dk_sync();
         if (warp < group) {  // softmax bookkeeping of head `warp` over the tile
             float sc[(DK_KT + 31) / 32], mx = -INFINITY;
 #pragma unroll
@@ -690,7 +859,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
                 m_s[warp] = m_new;
             }
         }
-        __syncthreads();
+        dk_sync();
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int h = oh + 4 * i;
@@ -701,7 +870,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
             acc[i] = a;
         }
     }
-    __syncthreads();
+    dk_sync();
     float* mine = p.attn_part + (size_t(kvh) * p.nsplit + split) * group * (DK_HD + 2);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -712,7 +881,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
         mine[tid * (DK_HD + 2) + DK_HD] = m_s[tid];
         mine[tid * (DK_HD + 2) + DK_HD + 1] = l_s[tid];
     }
-    __syncthreads();
+    dk_sync();
     if (tid == 0) {
         // release: the CTA's partial results (ordered before this thread by the barrier) are visible to whoever reads
         // the count; acquire: the last arriver sees everybody else's
@@ -721,7 +890,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
         s.flags[0] = old == unsigned(p.nsplit - 1);
         if (s.flags[0]) p.attn_counters[kvh] = 0;
     }
-    __syncthreads();
+    dk_sync();
     if (!s.flags[0]) return;
     // (thread 0's acquire and the barrier above order the other parts' results before the L2 loads below)
     const float* base = p.attn_part + size_t(kvh) * p.nsplit * group * (DK_HD + 2);
@@ -755,7 +924,7 @@ __device__ void attn_phase(const DkParams& p, const DkLayer& L, const AttnSmem& 
     }
     mx = warp_max(mx);
     if (lane == 0) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
-    __syncthreads();
+    dk_sync();
     if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
 }
 
@@ -767,21 +936,32 @@ __host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
     const size_t act = size_t(4) * (n_max + 32) + size_t(n_max / 256) * 192, attn = size_t(DK_ATTN_FLOATS) * 4;
     return ((act > attn ? act : attn) + 15) / 16 * 16;
 }
-__global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p, const int slot_bytes) {
-    extern __shared__ __align__(16) uint8_t smem[];
+__global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_constant__ DkParams p, const int ring_bytes) {
+    extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // shared memory: rings | scratch (limbs of the running matvec, or the attention tiles) | reduction buffers
-    uint8_t* scratch = smem + size_t(DK_WARPS) * DK_DEPTH * slot_bytes;
+    // shared memory: rings | scratch (limbs of the running matvec, or the attention tiles) | reduction buffers | mbarriers
+    uint8_t* scratch = smem + size_t(DK_WARPS) * ring_bytes;
     uint8_t* tail = scratch + dk_scratch_bytes(p.n_max);
     PhaseSmem s;
-    s.ring = smem + size_t(warp) * DK_DEPTH * slot_bytes;
-    s.slot_bytes = slot_bytes;
     s.act.lim = reinterpret_cast<int8_t*>(scratch);
     s.red = reinterpret_cast<float*>(tail);
     s.red8 = reinterpret_cast<double*>(s.red + DK_WARPS * p.slots * 16);
     s.wfirst = reinterpret_cast<int*>(s.red8 + DK_WARPS);
     s.wlast = s.wfirst + DK_WARPS;
     s.flags = s.wlast + DK_WARPS;
+    Ring rg;
+    rg.base = dk_smem_u32(smem) + uint32_t(warp * ring_bytes);
+    uint64_t* bars0 = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(s.flags + 4) + 7) & ~uintptr_t(7));
+    rg.bars = dk_smem_u32(bars0 + warp * DK_NBAR);
+    int2* sched_w = reinterpret_cast<int2*>(bars0 + DK_WARPS * DK_NBAR);  // [DK_WARPS][DK_KINDS]
+    int2* sched_c = sched_w + DK_WARPS * DK_KINDS;                         // [DK_KINDS]
+    RingShared* rshared = reinterpret_cast<RingShared*>(sched_c + DK_KINDS);
+    s.sched.warp = sched_w + (warp < DK_WARPS ? warp : 0) * DK_KINDS;
+    s.sched.cta = sched_c;
+    rg.bytes = ring_bytes;
+    rg.c_off = 0;
+    rg.c_seq = rg.freed = 0u;
+    rg.freed_out = rshared->freed + (warp < DK_WARPS ? warp : 0);
     AttnSmem as;
     as.qs = reinterpret_cast<float*>(scratch);
     as.knew = as.qs + DK_MAXG * DK_HD;
@@ -799,17 +979,30 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         a.sd16 = a.sd32 + (n / 256) * 64;
         return a;
     };
-    if (tid == 0) s.flags[2] = 0;
-    __syncthreads();
+    if (tid == 0) { s.flags[2] = 0; rshared->producer_done = 0; }
+    if (tid < DK_WARPS) { rshared->freed[tid] = 0u; rshared->issued[tid] = 0u; }
+    if (warp < DK_WARPS && lane < DK_KINDS) {  // this warp's share of every kind of matrix (kinds the model does not have: empty)
+        const int kind = lane;
+        const bool have = kind >= 3 || kind < p.n_qkv;
+        WarpRange r{0, 0, 0, 0};
+        if (have) r = warp_range(p.kind[kind], warp);
+        sched_w[warp * DK_KINDS + kind] = make_int2(r.wA, r.wB);
+        if (warp == 0) sched_c[kind] = make_int2(r.cA, r.cB);
+    }
+    if (warp < DK_WARPS && lane == 0) {
+        for (int i = 0; i < DK_NBAR; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(rg.bars + i * 8u), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();  // the only barrier of all twenty warps
 
-    // start the weight stream: DEPTH-1 units per warp in flight from here to the end of the step
-    Cursor pf;
-    pf.j = 0;
-    pf.n_mats = p.n_layer * (p.n_qkv + 3) + 1;
-    cursor_seek(p, pf, warp);
-#pragma unroll
-    for (int d = 0; d < DK_DEPTH - 1; ++d) cursor_issue(p, pf, s.ring + d * slot_bytes, warp, lane);
-    int rs = 0;
+    // the weight stream starts here: from now to the end of the step the producer warp keeps every ring as full as it gets
+    if (warp >= DK_WARPS) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DK_REGS_PRODUCER));
+        if (warp == DK_WARPS) producer_warp(p, dk_smem_u32(smem), ring_bytes, dk_smem_u32(bars0), sched_w, rshared, &s.flags[2], lane);
+        return;
+    }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DK_REGS_WORKER));
     int* dead = &s.flags[2];
     const unsigned step = p.ctl[0], epoch = p.ctl[2];
     unsigned nb = epoch * unsigned(1 + (5 + (p.act_global ? 1 : 0)) * p.n_layer + (p.tp_size > 1 ? 1 : 0)) * gridDim.x;  // arrivals before this launch
@@ -849,12 +1042,12 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
     const int n_stages = 4 * p.n_layer + 1;
     for (int stage = 0; stage < n_stages && ok; ++stage) {
         const bool head = stage + 1 == n_stages;
-        const int l = head ? p.n_layer : stage >> 2, k = head ? 4 : stage & 3;  // layers[n_layer].wo is the head
-        const DkLayer& L = p.layers[l];
+        const int l = head ? p.n_layer : stage >> 2, k = head ? 4 : stage & 3;
+        const float* const layer_norms = p.norms + size_t(l) * p.norm_stride;  // (not read for the head)
         unsigned* amax = amax_base + 2 * (head ? 0 : l);
         if (k == 0) dk_stamp(p, l, 0);
         if (k == 1) {  // attention sits between q|k|v and attn_output
-            attn_phase(p, L, as, amax);
+            attn_phase(p, l, as, amax);
             dk_stamp(p, l, 4);
             if (!(ok = grid_barrier(p, nb, dead))) break;
             dk_stamp(p, l, 5);
@@ -863,19 +1056,19 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         const float *src = nullptr, *norm_w = nullptr;
         const unsigned* amax_in = nullptr;
         unsigned* amax_out = nullptr;
-        const DkMat* mats = &L.wo;
         float* y = nullptr;
         int n = p.E, nl = 4, nm = 1, epi = DK_EPI_PART;
+        int i0 = p.n_qkv, kind0 = 3;  // the stage's first matrix: index within the layer, kind
         bool resid = true;
         switch (k) {
-            case 0: norm_w = L.attn_norm; nl = p.nl_qkv; mats = L.qkv; nm = p.n_qkv; epi = DK_EPI_STORE; y = p.qkv; break;
+            case 0: norm_w = layer_norms; nl = p.nl_qkv; i0 = 0; kind0 = 0; nm = p.n_qkv; epi = DK_EPI_STORE; y = p.qkv; break;
             case 1: resid = false; src = p.att; n = p.H * DK_HD; amax_in = amax; nl = p.nl_wo; break;
-            case 2: norm_w = L.ffn_norm; nl = p.nl_gu; mats = &L.gu; epi = DK_EPI_SILU_AMAX; y = p.act; amax_out = amax + 1; break;
-            case 3: resid = false; src = p.act; n = p.F; amax_in = amax + 1; nl = p.nl_down; mats = &L.down; break;
-            default: norm_w = p.output_norm; epi = DK_EPI_LOGITS; break;
+            case 2: norm_w = layer_norms + p.E; nl = p.nl_gu; i0 = p.n_qkv + 1; kind0 = 4; epi = DK_EPI_SILU_AMAX; y = p.act; amax_out = amax + 1; break;
+            case 3: resid = false; src = p.act; n = p.F; amax_in = amax + 1; nl = p.nl_down; i0 = p.n_qkv + 2; kind0 = 5; break;
+            default: norm_w = p.output_norm; epi = DK_EPI_LOGITS; i0 = 0; kind0 = 6; break;
         }
         int need = 0;
-        for (int i = 0; i < nm; ++i) need |= sd_need(mats[i]);
+        for (int i = 0; i < nm; ++i) need |= sd_need(p.wtype[l][i0 + i]);
         const bool gact = k == 3 && p.act_global;
         float inv;
         if (gact) {
@@ -896,9 +1089,9 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         const int sb = k == 0 ? 0 : 3 * k + 2;  // profile stamps of the stage: conversion, matvec, barrier
         if (!head) dk_stamp(p, l, sb + 1);
         for (int i = 0; i < nm; ++i)
-            matvec_phase(p, mats[i], epi, k == 0 ? y + L.qkv_col[i] : y, inv, pf, rs, s, amax_out, int(xn & 1u), gact, i > 0);
+            matvec_phase(p, p.wtype[l][i0 + i], kind0 + i, epi, k == 0 ? y + p.qkv_col[i] : y, inv, rg, s, amax_out, int(xn & 1u), gact, i > 0);
         if (!head) dk_stamp(p, l, sb + 2);
-        if (k == 0) attn_prefetch(p, L, as);
+        if (k == 0) attn_prefetch(p, l, as);
         if (k == 1 || k == 3 || (head && p.tp_size > 1)) {  // row-parallel matvecs and the logits meet all ranks
             ok = exchange_barrier(p, nb, xn, dead);
             pending = int(xn & 1u);
@@ -908,23 +1101,37 @@ __global__ void __launch_bounds__(DK_THREADS, 1) k_decode_step(const DkParams p,
         }
         if (!head) dk_stamp(p, l, sb + 3);
     }
-    ring_wait<0>();
+    ring_drain(rg, rshared, warp);  // (nothing is left in flight after a whole step; after a timeout the copies still land here)
     if (blockIdx.x == 0 && tid == 0) {  // every CTA read ctl before its first barrier: safe to move on
         p.ctl[2] = epoch + 1;
         if (p.ctl[1]) p.ctl[0] = step + 1;
     }
 }
 
-size_t decode_smem_bytes(const DkParams& p, int slot_bytes) {
-    return size_t(DK_WARPS) * DK_DEPTH * slot_bytes + dk_scratch_bytes(p.n_max) + size_t(DK_WARPS) * p.slots * 16 * 4 +
-           DK_WARPS * 8 + 2 * DK_WARPS * 4 + 4 * 4 + 16;
+// everything but the rings
+static size_t decode_fixed_smem(const DkParams& p) {
+    return dk_scratch_bytes(p.n_max) + size_t(DK_WARPS) * p.slots * 16 * 4 + DK_WARPS * 8 + 2 * DK_WARPS * 4 + 4 * 4 + 16 +
+           size_t(DK_WARPS) * DK_NBAR * 8 + size_t(DK_WARPS + 1) * DK_KINDS * 8 + sizeof(RingShared);
+}
+size_t decode_smem_bytes(const DkParams& p, int ring_bytes) { return size_t(DK_WARPS) * ring_bytes + decode_fixed_smem(p); }
+
+// Bytes per warp ring when the kernel takes all the shared memory a CTA can have (a multiple of 128), capped so that a
+// warp cannot have more than DK_NBAR of the smallest units on request; 0 when not even two of the largest units fit.
+int decode_ring_bytes(const DkParams& p, int max_unit, int min_unit, int device) {
+    DeviceInfo di;
+    if (device_info(device, &di) != ELB_OK) return 0;
+    const size_t fixed = decode_fixed_smem(p);
+    if (di.smem_optin < fixed + size_t(DK_WARPS) * 2 * max_unit) return 0;
+    size_t per = (di.smem_optin - fixed) / DK_WARPS / 128 * 128;
+    per = std::min(per, size_t(DK_NBAR) * min_unit / 128 * 128);
+    return per >= size_t(2) * max_unit ? int(per) : 0;
 }
 
 int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s) {
     const size_t smem = decode_smem_bytes(p, slot_bytes);
     ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(k_decode_step), smem));
     void* args[] = {const_cast<DkParams*>(&p), const_cast<int*>(&slot_bytes)};
-    ELB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(k_decode_step), dim3(grid), dim3(DK_THREADS), args, smem, s));
+    ELB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(k_decode_step), dim3(grid), dim3(DK_CTA_THREADS), args, smem, s));
     return ELB_OK;
 }
 
@@ -937,7 +1144,7 @@ int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits) 
     if (smem > di.smem_optin) return ELB_OK;
     ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(k_decode_step), smem));
     int per_sm = 0;
-    ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, DK_THREADS, smem));
+    ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, DK_CTA_THREADS, smem));
     *fits = per_sm >= 1;
     return ELB_OK;
 }

@@ -5,27 +5,32 @@
 
 namespace elb {
 
-struct DkMat {  // one weight matrix of the step, in tiled layout
-    const uint8_t* W;
-    int type, unit_bytes, tiles, upt, rows, n;
+// Everything the kernel needs to know about the step's matrices travels in its parameter block (constant memory, no
+// pointer chasing through global memory on the way to a weight): the shape of each KIND of matrix, which is the same in
+// every layer, and per layer only the base pointer and block format of each of its matrices.
+constexpr int DK_MAX_LAYERS = 96;  // layers a model may have to run on this kernel
+constexpr int DK_KINDS = 7;        // 0..2 qkv segment, 3 attn_output, 4 gate|up, 5 ffn_down, 6 head
+constexpr int DK_LAYER_MATS = 6;   // matrices of a layer in execution order: n_qkv segments, attn_output, gate|up, ffn_down
+
+struct DkKind {  // one kind of weight matrix, in tiled layout
+    int tiles, upt, rows, n;
     // How the CTAs share the matrix. group_tiles / group_off: the matrix is tiles [group_off, group_off + tiles) of a
     // group of matrices that run in one phase (q, k, v) and the CTAs cut the group's tiles, whole tiles each.
     // balanced: the CTAs cut the (tile, k block) units into equal ranges instead; a tile then has up to two
     // contributors, which leave their partial sums in two buffers for the consumer to add (wo, down).
-    int group_tiles, group_off, balanced;
-};
-
-struct DkLayer {
-    DkMat qkv[3];
-    int qkv_col[3];
-    DkMat wo, gu, down;
-    const float *attn_norm, *ffn_norm, *q_norm, *k_norm;
-    float *kc, *vc;  // this layer's KV cache [n_ctx][KD]
+    int group_tiles, group_off, balanced, pad;
 };
 
 struct DkParams {
-    const DkLayer* layers;  // device array [n_layer + 1]; the extra element's `wo` is the head
+    DkKind kind[DK_KINDS];
+    const uint8_t* W[DK_MAX_LAYERS + 1][DK_LAYER_MATS];  // [layer][matrix in execution order]; [n_layer][0] is the head
+    uint8_t wtype[DK_MAX_LAYERS + 1][8];                 // their block formats (ggml type ids)
     int n_layer, n_qkv;     // every layer has the same number of qkv segments
+    int qkv_col[3];         // first output column of each qkv segment
+    const float* norms;     // per layer norm_stride floats: attn_norm [E], ffn_norm [E], q_norm [128], k_norm [128]
+    int norm_stride;
+    float *kc, *vc;         // KV cache of layer 0 (sequence 0) [n_ctx][KD]; layer l lies l * kv_stride floats further
+    size_t kv_stride;
     const float* output_norm;
     const uint8_t* embd;    // token embedding table, tiled layout
     int embd_type;
@@ -65,10 +70,11 @@ struct DkParams {
 };
 
 // one token at the position / token id stored on the device (step ctl[0] of the arrays); nothing to reset between launches.
-// slot_bytes: size of one ring slot (the largest unit of the step's matrices); grid: one CTA per SM.
-int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s);
-int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits);
-size_t decode_smem_bytes(const DkParams& p, int slot_bytes);
+// ring_bytes: size of one warp's ring of weight units in shared memory (decode_ring_bytes); grid: one CTA per SM.
+int decode_step_launch(const DkParams& p, int ring_bytes, int grid, cudaStream_t s);
+int decode_step_fits(const DkParams& p, int ring_bytes, int device, bool* fits);
+size_t decode_smem_bytes(const DkParams& p, int ring_bytes);
+int decode_ring_bytes(const DkParams& p, int max_unit, int min_unit, int device);
 int decode_threads();
 int decode_warps();
 

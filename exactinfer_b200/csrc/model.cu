@@ -74,8 +74,8 @@ struct Model {
     // persistent decode kernel (quantized models whose step fits in shared memory)
     bool use_mega = false;
     DkParams dk{};
-    DkLayer* dk_layers = nullptr;
-    int dk_slot = 0, dk_grid = 0;
+    float* norm_arena = nullptr;  // the norm vectors of all layers, layer after layer: attn_norm [E], ffn_norm [E], q_norm, k_norm [head_dim]
+    int dk_slot = 0, dk_grid = 0;  // dk_slot: bytes of one warp's ring of weight units
     float* xbuf = nullptr;  // persistent kernel: residual stream [2][E]
     TpPeerBuf xarea;        // persistent kernel: flags, partial sums and logits, visible to all tensor-parallel ranks
     unsigned* xctl = nullptr;
@@ -110,7 +110,8 @@ namespace {
 
 int64_t slot_of(const Model* m, int role, int layer) { return role <= ELB_OUTPUT_NORM ? role : 3 + int64_t(layer) * 11 + (role - 3); }
 
-int upload_f32(const HostTensor& t, float** out) {
+// dst: device memory for the vector (null: *out is allocated)
+int upload_f32(const HostTensor& t, float** out, float* dst = nullptr) {
     if (!t.bytes) return fail(ELB_ERR_STATE, "model: a norm tensor is missing");
     if (t.type != ELB_F32 && t.type != ELB_F16) return fail(ELB_ERR_UNSUPPORTED, "model: norm weights must be F32 or F16");
     if (t.rows <= 0 || t.n <= 0 || t.nbytes != size_t(t.rows) * size_t(t.n) * (t.type == ELB_F32 ? 4 : 2))
@@ -124,7 +125,8 @@ int upload_f32(const HostTensor& t, float** out) {
     } else {
         return fail(ELB_ERR_UNSUPPORTED, "model: norm weights must be F32 or F16");
     }
-    ELB_CUDA(cudaMalloc(out, v.size() * 4));
+    if (dst) *out = dst;
+    else ELB_CUDA(cudaMalloc(out, v.size() * 4));
     ELB_CUDA(cudaMemcpy(*out, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
     return ELB_OK;
 }
@@ -424,16 +426,18 @@ int setup_decode_kernel(Model* m) {
     if (env_on("ELB_NO_MEGA") || (m->tp.size > 1 && env_on("ELB_TP_NO_MEGA"))) return ELB_OK;
     DeviceInfo di;
     ELB_TRY(device_info(m->device, &di));
-    auto mat = [](const Weight* w) {  // alone in its phase, whole tiles per CTA
-        return DkMat{w->tiled, w->type, w->unit_bytes, int(w->tiles), int(w->units_per_tile), int(w->rows), int(w->n),
-                     int(w->tiles), 0, 0};
+    auto kind_of = [](const Weight* w) {  // alone in its phase, whole tiles per CTA
+        return DkKind{int(w->tiles), int(w->units_per_tile), int(w->rows), int(w->n), int(w->tiles), 0, 0, 0};
     };
     // row-parallel matrices (few row tiles, long rows): equal unit ranges, when every CTA's range is at least one tile
     // long, so that no tile has more than two contributors
-    auto mat_balanced = [&](const Weight* w) {
-        DkMat d = mat(w);
+    auto kind_balanced = [&](const Weight* w) {
+        DkKind d = kind_of(w);
         d.balanced = w->tiles * w->units_per_tile / di.sm_count >= w->units_per_tile ? 1 : 0;
         return d;
+    };
+    auto same_shape = [](const Weight* a, const Weight* b) {
+        return a->tiles == b->tiles && a->units_per_tile == b->units_per_tile && a->rows == b->rows && a->n == b->n;
     };
     bool quant = m->head->type != ELB_F16 && m->embd->type != ELB_F32;
     const size_t nq = m->layers[0].qkv.size();
@@ -449,43 +453,58 @@ int setup_decode_kernel(Model* m) {
         Fmax = std::max(Fmax, int(d.f1 - d.f0));
     }
     const int E = c.n_embd, F = int(m->F), QD = m->H * 128, KD = m->HKV * 128;
-    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 5 * 4 * decode_threads()) return ELB_OK;
+    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 5 * 4 * decode_threads() || c.n_layer > DK_MAX_LAYERS) return ELB_OK;
+    // the kernel takes the shape of each kind of matrix from layer 0: every layer must repeat it (block formats may differ)
+    for (const Layer& L : m->layers) {
+        const Layer& L0 = m->layers[0];
+        bool same = same_shape(L.wo, L0.wo) && same_shape(L.gu, L0.gu) && same_shape(L.down, L0.down);
+        for (size_t i = 0; i < nq; ++i) same = same && same_shape(L.qkv[i].w, L0.qkv[i].w) && L.qkv[i].col == L0.qkv[i].col;
+        if (!same) return ELB_OK;
+    }
     DkParams& p = m->dk;
     p = DkParams{};
-    std::vector<DkLayer> hl(size_t(c.n_layer) + 1);  // + one element whose `wo` is the head
-    hl[size_t(c.n_layer)].wo = mat(m->head);
-    int slot = m->head->unit_bytes;
-    int64_t max_units_cta = (m->head->tiles * m->head->units_per_tile + di.sm_count - 1) / di.sm_count;
+    p.kind[6] = kind_of(m->head);
+    p.W[c.n_layer][0] = m->head->tiled;
+    p.wtype[c.n_layer][0] = uint8_t(m->head->type);
+    int unit_max = m->head->unit_bytes, unit_min = m->head->unit_bytes;  // largest and smallest unit of the step
     int slots = 0;
     auto account = [&](const Weight* w) {
-        slot = std::max(slot, w->unit_bytes);
+        unit_max = std::max(unit_max, w->unit_bytes);
+        unit_min = std::min(unit_min, w->unit_bytes);
         const int64_t per_cta = (w->tiles + di.sm_count - 1) / di.sm_count * w->units_per_tile;
         const int64_t per_warp = (per_cta + decode_warps() - 1) / decode_warps();
         slots = std::max(slots, int((per_warp + w->units_per_tile - 1) / w->units_per_tile + 2));
-        (void)max_units_cta;
     };
     account(m->head);
     for (int l = 0; l < c.n_layer; ++l) {
         const Layer& L = m->layers[size_t(l)];
-        DkLayer& d = hl[size_t(l)];
         int group = 0;
         for (size_t i = 0; i < nq; ++i) group += int(L.qkv[i].w->tiles);
         for (size_t i = 0, off = 0; i < nq; ++i) {  // q, k, v share one phase: the CTAs cut the tiles of all three together
-            d.qkv[i] = mat(L.qkv[i].w);
-            d.qkv[i].group_tiles = group;
-            d.qkv[i].group_off = int(off);
+            if (l == 0) {
+                p.kind[i] = kind_of(L.qkv[i].w);
+                p.kind[i].group_tiles = group;
+                p.kind[i].group_off = int(off);
+                p.qkv_col[i] = int(L.qkv[i].col);
+            }
             off += size_t(L.qkv[i].w->tiles);
-            d.qkv_col[i] = int(L.qkv[i].col);
+            p.W[l][i] = L.qkv[i].w->tiled;
+            p.wtype[l][i] = uint8_t(L.qkv[i].w->type);
             account(L.qkv[i].w);
         }
-        d.wo = mat_balanced(L.wo); d.gu = mat(L.gu); d.down = mat_balanced(L.down);
-        account(L.wo); account(L.gu); account(L.down);
-        d.attn_norm = L.attn_norm; d.ffn_norm = L.ffn_norm; d.q_norm = L.q_norm; d.k_norm = L.k_norm;
-        d.kc = m->kcache + size_t(l) * m->n_seq * m->n_ctx * KD;  // sequence 0
-        d.vc = m->vcache + size_t(l) * m->n_seq * m->n_ctx * KD;
+        if (l == 0) { p.kind[3] = kind_balanced(L.wo); p.kind[4] = kind_of(L.gu); p.kind[5] = kind_balanced(L.down); }
+        const Weight* rest[3] = {L.wo, L.gu, L.down};
+        for (int i = 0; i < 3; ++i) {
+            p.W[l][nq + i] = rest[i]->tiled;
+            p.wtype[l][nq + i] = uint8_t(rest[i]->type);
+            account(rest[i]);
+        }
     }
-    ELB_CUDA(cudaMalloc(&m->dk_layers, hl.size() * sizeof(DkLayer)));
-    ELB_CUDA(cudaMemcpy(m->dk_layers, hl.data(), hl.size() * sizeof(DkLayer), cudaMemcpyHostToDevice));
+    p.norms = m->norm_arena;
+    p.norm_stride = int(2 * E + 2 * c.head_dim);
+    p.kc = m->kcache;  // sequence 0
+    p.vc = m->vcache;
+    p.kv_stride = size_t(m->n_seq) * m->n_ctx * KD;
     ELB_CUDA(cudaMalloc(&m->xbuf, size_t(2) * E * sizeof(float)));  // residual stream [2][E]
     // exchange area: flags, partial sums [2 sets][ranks][2][E], logits; mapped into every rank under tensor parallelism
     const int N = m->tp.size;
@@ -511,7 +530,7 @@ int setup_decode_kernel(Model* m) {
     *m->err_host = 0;
     int* err_dev = nullptr;
     ELB_CUDA(cudaHostGetDevicePointer(&err_dev, m->err_host, 0));
-    p.layers = m->dk_layers; p.n_layer = c.n_layer; p.n_qkv = int(nq);
+    p.n_layer = c.n_layer; p.n_qkv = int(nq);
     p.output_norm = m->output_norm;
     p.embd = m->embd->tiled; p.embd_type = m->embd->type;
     p.E = E; p.F = F; p.H = m->H; p.HKV = m->HKV; p.rope_dim = c.rope_dim; p.n_ctx = m->n_ctx;
@@ -530,21 +549,32 @@ int setup_decode_kernel(Model* m) {
     p.xbuf = m->xbuf; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
     p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
     p.err = err_dev; p.slots = slots; p.n_max = std::max({E, Fmax, QD});
-    m->dk_slot = (slot + 15) / 16 * 16;
     m->dk_grid = di.sm_count;
     // 32-bit unit arithmetic in the kernel
     bool small = true;
     for (int l = 0; l < c.n_layer; ++l)
         for (const Weight* w : {m->layers[size_t(l)].wo, m->layers[size_t(l)].gu, m->layers[size_t(l)].down, m->head})
             if (w->tiles * w->units_per_tile * int64_t(di.sm_count) >= (int64_t(1) << 31) || w->max_grid < di.sm_count) small = false;
+    // The rings of the warps take whatever shared memory the activation limbs and the reduction buffers leave; a ring
+    // shorter than ELB_DK_MIN_RING bytes (default: three of the largest units) would leave the weight stream too little
+    // run-ahead, and the long FFN activation then goes to global memory instead.
     bool fits = false;
-    ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+    int min_ring = 3 * unit_max;
+    if (const char* v = std::getenv("ELB_DK_MIN_RING")) min_ring = std::max(2 * unit_max, std::atoi(v));
+    auto try_fit = [&]() -> int {
+        m->dk_slot = decode_ring_bytes(p, unit_max, unit_min, m->device);
+        if (const char* v = std::getenv("ELB_DK_RING")) m->dk_slot = std::min(m->dk_slot, std::max(2 * unit_max, std::atoi(v) / 128 * 128));  // (experiments)
+        fits = false;
+        if (m->dk_slot >= min_ring) ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+        return ELB_OK;
+    };
+    ELB_TRY(try_fit());
     if ((!fits || env_on("ELB_DK_GACT")) && Fmax > std::max(E, QD)) {  // (the variable forces the mode, for tests)
         // the limbs of the FFN activation do not fit next to the rings: keep them in global memory (one more grid barrier
         // per layer, ffn_down reads them through L2); every rank decides from the longest FFN cut, so all decide alike
         p.act_global = 1;
         p.n_max = std::max(E, QD);
-        ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
+        ELB_TRY(try_fit());
         if (fits) {
             ELB_CUDA(cudaMalloc(&m->gact, act_bytes(Fmax) + 4 * 32));
             p.gact = m->gact;
@@ -628,14 +658,14 @@ void model_destroy(Model* m) {
     for (Layer& L : m->layers) {
         for (auto& s : L.qkv) weight_destroy(s.w);
         weight_destroy(L.wo); weight_destroy(L.gu); weight_destroy(L.down);
-        cudaFree(L.attn_norm); cudaFree(L.ffn_norm); cudaFree(L.q_norm); cudaFree(L.k_norm);
     }
+    cudaFree(m->norm_arena);
     for (void* p : {(void*)m->output_norm, (void*)m->rope, (void*)m->kcache, (void*)m->vcache, (void*)m->x, (void*)m->qkv,
                     (void*)m->att, (void*)m->act, (void*)m->logits, (void*)m->limbs, (void*)m->inv_scale, (void*)m->xsum,
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->dk_layers); cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact);
+    cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev); cudaFree(m->mask_dev);
@@ -746,12 +776,16 @@ int model_finalize(Model* m) {
     }
     m->weight_bytes += m->head->tiled_bytes;
     ELB_TRY(upload_f32(P(ELB_OUTPUT_NORM, 0), &m->output_norm));
+    // the norm vectors of all layers in one piece of memory at a fixed stride: kernels address layer l by arithmetic
+    const size_t norm_stride = size_t(2) * E + 2 * size_t(c.head_dim);
+    ELB_CUDA(cudaMalloc(&m->norm_arena, size_t(c.n_layer) * norm_stride * sizeof(float)));
     for (int l = 0; l < c.n_layer; ++l) {
         Layer& L = m->layers[size_t(l)];
-        ELB_TRY(upload_f32(P(ELB_ATTN_NORM, l), &L.attn_norm));
-        ELB_TRY(upload_f32(P(ELB_FFN_NORM, l), &L.ffn_norm));
-        ELB_TRY(upload_f32(P(ELB_Q_NORM, l), &L.q_norm));
-        ELB_TRY(upload_f32(P(ELB_K_NORM, l), &L.k_norm));
+        float* base = m->norm_arena + size_t(l) * norm_stride;
+        ELB_TRY(upload_f32(P(ELB_ATTN_NORM, l), &L.attn_norm, base));
+        ELB_TRY(upload_f32(P(ELB_FFN_NORM, l), &L.ffn_norm, base + E));
+        ELB_TRY(upload_f32(P(ELB_Q_NORM, l), &L.q_norm, base + 2 * E));
+        ELB_TRY(upload_f32(P(ELB_K_NORM, l), &L.k_norm, base + 2 * E + c.head_dim));
         ELB_TRY(upload_linear(m, {&P(ELB_WQ, l), &P(ELB_WK, l), &P(ELB_WV, l)}, ELB_W_PLANES, &L.qkv));
         std::vector<Seg> one;
         ELB_TRY(upload_linear(m, {&P(ELB_WO, l)}, ELB_W_PLANES, &one));
@@ -1008,6 +1042,12 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
             layer_total += sum / m->cfg.n_layer / 1000.0;
         }
         std::fprintf(stderr, "[dk prof] layer total   %7.2f us\n", layer_total);
+        if (t[20])  // a build with -DELB_DK_UNITPROF: clocks of warp 0 of CTA 0 per unit, all launches so far
+            std::fprintf(stderr, "[dk prof] warp 0, clocks per unit: requests %.0f, waiting for the unit %.0f, arithmetic %.0f, row-tile ends %.0f (%llu units)\n",
+                         double(t[16]) / double(t[20]), double(t[17]) / double(t[20]), double(t[18]) / double(t[20]), double(t[19]) / double(t[20]), t[20]);
+        if (t[23]) std::fprintf(stderr, "[dk prof] per request: issue %.0f clocks, bookkeeping and next-matrix lookup %.0f (%llu requests)\n",
+                                double(t[21]) / double(t[23]), double(t[22]) / double(t[23]), t[23]);
+
     }
     m->last_rows = 1;
     return ELB_OK;
