@@ -5,18 +5,22 @@
 // dependency latency, not by bandwidth. Here one CTA per SM stays resident for the whole step and walks the chain with
 // grid-wide barriers between the steps:
 //   * every working warp owns a fixed, contiguous share of the (row tile, k block) units of every weight matrix of the
-//     step, in execution order — one long "unit stream" — and a seventeenth warp, which does nothing else, keeps every
+//     step, in execution order — one long "unit stream" — and one more warp, which does nothing else, keeps every
 //     working warp's ring in shared memory as full as it gets (a byte ring: units of different block formats lie back
 //     to back; every unit is one bulk copy that reports to an mbarrier), no matter which phase the CTA is in: HBM
 //     keeps streaming through barriers, attention and activation conversion, and the working warps spend no
 //     instruction on requesting data;
 //   * the activation of a matvec is converted to int8 limbs redundantly by every CTA (shared memory), from the fp32
-//     vector and a global maximum (atomicMax, order independent) or the per-tile sums of squares (RMSNorm) that the
-//     producing phase left: no serial single-CTA section;
+//     vector and a global maximum (atomicMax, order independent) or the sums that the producing phase left: no serial
+//     single-CTA section;
 //   * no phase ends with an exchange between CTAs: q, k, v and gate|up are cut in whole row tiles; attn_output and
-//     ffn_down, which have few row tiles and long rows, are cut in equal unit ranges, a row tile then has at most two
-//     contributing CTAs, each leaves its partial sums in a buffer of its own and the next conversion adds residual +
-//     first + second in that order on every CTA: the step is deterministic.
+//     ffn_down, which have few row tiles and long rows, are cut in equal unit ranges instead, a row tile then has at most
+//     two contributing CTAs: the one with the tile's first blocks adds the residual stream to its partial sums, the other
+//     leaves its partial sums in a second buffer, and the next conversion adds the two on every CTA: deterministic;
+//   * everything a phase needs to find its data (matrix shapes, base pointers, block formats) lies in the kernel's
+//     parameter block, and the code is kept small (loops are rolled, the phases are functions): a kernel of this length
+//     runs every piece of its code once per layer, so it is bound by instruction fetch as soon as it outgrows the
+//     instruction cache.
 // Barrier waits are bounded: on timeout the kernel raises an error word, drains its copies and leaves.
 #include <algorithm>
 #include <cstdlib>
@@ -29,7 +33,7 @@
 
 namespace elb {
 
-constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32;  // the working warps; the CTA has one more warp, the producer
+constexpr int DK_THREADS = 512, DK_WARPS = DK_THREADS / 32;  // the working warps
 // The CTA is launched with one more warpgroup (four warps, the unit in which registers can be handed over): its first
 // warp is the producer, the other three leave at once. Registers per thread: the compiler sizes the kernel for
 // 65536 / 640 = 96; the extra warpgroup then shrinks to DK_REGS_PRODUCER and the working warps grow to DK_REGS_WORKER.
@@ -40,11 +44,13 @@ constexpr int DK_CTA_THREADS = DK_THREADS + 128;
 constexpr int DK_REGS_LAUNCH = 96, DK_REGS_WORKER = 112, DK_REGS_PRODUCER = 32;
 static_assert(4 * 32 * (DK_REGS_LAUNCH - DK_REGS_PRODUCER) >= DK_THREADS * (DK_REGS_WORKER - DK_REGS_LAUNCH),
               "the working warps would wait for registers that nobody releases");
-constexpr unsigned DK_MBAR_LIMIT = 1u << 17;  // tries of one wait for a weight unit (each try blocks for a while in hardware)
 constexpr int DK_NBAR = 8;  // mbarriers per warp = most units a warp can have requested and not yet consumed
-constexpr int DK_HD = 128, DK_KT = 48, DK_KS = DK_HD + 4, DK_MAXG = 8, DK_MAXSPLIT = 32;  // DK_KS: row stride of the K tile (float4 reads without bank conflicts)
+constexpr int DK_HD = 128, DK_KT = 40, DK_KS = DK_HD + 4, DK_MAXG = 8;  // DK_KS: row stride of the K tile (float4 reads without bank conflicts)
+constexpr int DK_MAXSPLIT = 18;         // key splits of one KV head (their partial results are staged in the K/V tile area)
+constexpr int DK_PS = DK_HD + 4;        // floats per (split, head) of the attention's partial results: 128 outputs, m, l, padding
 constexpr unsigned DK_SPIN_LIMIT = 1u << 22;
 constexpr unsigned DK_XSPIN_LIMIT = 1u << 24;  // waits on another GPU (x ~100 ns: about two seconds)
+constexpr unsigned DK_MBAR_LIMIT = 1u << 17;   // tries of one wait for a weight unit (each try blocks for a while in hardware)
 
 // CTA barrier of the working warps (the producer warp runs on its own): a named barrier over DK_THREADS threads
 __device__ __forceinline__ void dk_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DK_THREADS) : "memory"); }
@@ -56,31 +62,6 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-
-// All CTAs arrive, then leave together. `target` is the arrival count that completes this CTA's next barrier (the
-// counter is never reset: a launch starts from launches * barriers per launch * CTAs). Returns false when the wait ran out (or an
-// earlier one did): the caller stops working, every later barrier returns at once.
-__device__ __forceinline__ bool grid_barrier(const DkParams& p, unsigned& target, int* s_dead) {
-    dk_sync();
-    if (threadIdx.x == 0 && !*s_dead) {
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");  // orders the CTA's writes before it
-        target += gridDim.x;
-        unsigned it = 0;
-        while (int(ld_acquire(p.bar) - target) < 0) {
-            if (++it > DK_SPIN_LIMIT) {
-                *s_dead = 1;
-                atomicExch(p.err, 1);
-                break;
-            }
-            if (it > 2048) __nanosleep(64);
-        }
-        // (no fence here: the acquire load that saw the last arrival synchronises with every CTA's release, and the
-        // CTA barrier below carries that to the other threads)
-    }
-    dk_sync();
-    return !*s_dead;
-}
-
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -89,44 +70,43 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_release_gpu(unsigned* p, unsigned v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
-// Barrier over the CTAs of ALL tensor-parallel ranks: exchange number x (counted from the first launch, the same on
-// every rank) is complete when every rank's CTAs have arrived. Every CTA waits for the local arrivals; CTA 0 then raises
-// this rank's flag of set x & 1 on every peer (system-scope release: the partial sums the local CTAs stored to the
-// peers, each followed by a system fence, are visible before it); every CTA waits for the peers' flags in its own
-// rank's flag words. One rank: the grid barrier. All waits bounded.
-__device__ __forceinline__ bool exchange_barrier(const DkParams& p, unsigned& target, unsigned x, int* s_dead) {
-    if (p.tp_size == 1) return grid_barrier(p, target, s_dead);
+// All CTAs arrive, then leave together. `target` is the arrival count that completes this CTA's next barrier (the
+// counter is never reset: a launch starts from launches * barriers per launch * CTAs). Returns false when the wait ran
+// out (or an earlier one did): the caller stops working, every later barrier returns at once.
+// peers: the barrier covers the CTAs of ALL tensor-parallel ranks: exchange number x (counted from the first launch,
+// the same on every rank) is complete when every rank's CTAs have arrived. Every CTA waits for the local arrivals; CTA 0
+// then raises this rank's flag of set x & 1 on every peer (system-scope release); every CTA waits for the peers' flags
+// in its own rank's flag words. What a CTA stored to its peers before the barrier is fenced once, by its arriving thread.
+__device__ __noinline__ bool grid_barrier(const DkParams& p, unsigned& target, int* s_dead, bool peers = false, unsigned x = 0) {
     dk_sync();
     if (threadIdx.x == 0 && !*s_dead) {
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");
+        if (peers) __threadfence_system();  // the CTA's peer stores (ordered before this thread by the CTA barrier)
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");  // orders the CTA's writes before it
         target += gridDim.x;
-        const int set = int(x & 1u);
         unsigned it = 0;
         bool dead = false;
-        while (!dead && int(ld_acquire(p.bar) - target) < 0)  // the local CTAs
+        while (!dead && int(ld_acquire(p.bar) - target) < 0)
             if (++it > DK_SPIN_LIMIT) dead = true; else if (it > 2048) __nanosleep(64);
-        unsigned* mine = nullptr;  // this rank's flag words
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {  // constant indices into the parameter arrays
-            if (q >= p.tp_size) break;
-            if (q == p.tp_rank) mine = p.flag_peer[q];
-            else if (!dead && blockIdx.x == 0) st_release_sys(p.flag_peer[q] + set * 8 + p.tp_rank, x + 1);
-        }
-        for (int q = 0; q < p.tp_size && !dead; ++q) {  // every CTA watches the peers' flags itself: no second hop
-            if (q == p.tp_rank) continue;
-            it = 0;
-            while (!dead && ld_acquire_sys(mine + set * 8 + q) != x + 1)
-                if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 256) __nanosleep(100);
+        // (no fence here: the acquire load that saw the last arrival synchronises with every CTA's release, and the
+        // CTA barrier below carries that to the other threads)
+        if (peers) {
+            const int set = int(x & 1u);
+            unsigned* mine = p.flag_peer[p.tp_rank];
+            if (blockIdx.x == 0 && !dead)
+                for (int q = 0; q < p.tp_size; ++q)
+                    if (q != p.tp_rank) st_release_sys(p.flag_peer[q] + set * 8 + p.tp_rank, x + 1);
+            for (int q = 0; q < p.tp_size && !dead; ++q) {  // every CTA watches the peers' flags itself: no second hop
+                if (q == p.tp_rank) continue;
+                it = 0;
+                while (!dead && ld_acquire_sys(mine + set * 8 + q) != x + 1)
+                    if (++it > DK_XSPIN_LIMIT) dead = true; else if (it > 256) __nanosleep(100);
+            }
         }
         if (dead) {
             *s_dead = 1;
             atomicExch(p.err, 1);
         }
-        __threadfence();
     }
     dk_sync();
     return !*s_dead;
@@ -161,9 +141,17 @@ struct ActSmem {
     int8_t* sd16;  // [n/256][8][16]
     int n_pad;
 };
+__device__ __forceinline__ ActSmem act_at(int8_t* base, int n) {
+    ActSmem a;
+    a.lim = base;
+    a.n_pad = n + 32;
+    a.sd32 = a.lim + 4 * a.n_pad;
+    a.sd16 = a.sd32 + (n / 256) * 64;
+    return a;
+}
 
 // Four consecutive values (index idx, a multiple of 4) -> one packed word of each of the 4 limbs (split4 of split.cuh
-// without the sub-block sums, which limb_sums adds in a pass of its own).
+// without the sub-block sums, which limb_sums_w adds in a pass of its own).
 __device__ __forceinline__ void limbs4(const float4& f, const Pow2 sc, int8_t* lim, int stride, int idx) {
     const uint32_t a = (uint32_t(__float2int_rn(f.x * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t b = (uint32_t(__float2int_rn(f.y * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
@@ -177,101 +165,80 @@ __device__ __forceinline__ void limbs4(const float4& f, const Pow2 sc, int8_t* l
     *reinterpret_cast<uint32_t*>(lim + 3 * stride + idx) = __byte_perm(ab23, cd23, 0x7632);
 }
 
-// Sums of each limb over the 32-wide (sd_mask & 1: Q4_K's min term) and 16-wide (sd_mask & 2: Q6_K's offset) sub-blocks,
-// as two balanced base-256 digits, in the layout the matvec's extra MMA reads (split.cuh). One thread per sum, from
-// the limbs in shared memory.
-__device__ __forceinline__ void limb_sums(const ActSmem& a, int n, int sd_mask) {
-    if (sd_mask & 1) {
-        for (int e = threadIdx.x; e < n / 8; e += DK_THREADS) {  // n/32 sub-blocks x 4 limbs
-            const int S = e >> 2, l = e & 3;
-            const uint4* src = reinterpret_cast<const uint4*>(a.lim + l * a.n_pad + S * 32);
-            const uint4 x = src[0], y = src[1];
-            int sum = __dp4a(int(x.x), 0x01010101, 0);
-            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
-            sum = __dp4a(int(y.x), 0x01010101, sum); sum = __dp4a(int(y.y), 0x01010101, sum);
-            sum = __dp4a(int(y.z), 0x01010101, sum); sum = __dp4a(int(y.w), 0x01010101, sum);
-            const int lo = ((sum + 128) & 255) - 128, blk = S >> 3, si = S & 7;
-            a.sd32[(blk * 8 + l) * 8 + si] = int8_t(lo);
-            a.sd32[(blk * 8 + 4 + l) * 8 + si] = int8_t((sum - lo) >> 8);
+// Sums of each limb over the sub-blocks [s0, s1) of width W (32: Q4_K's min term, 16: Q6_K's offset), as two balanced
+// base-256 digits, in the layout the matvec's extra MMA reads (split.cuh). One thread per (sub-block, limb). The limbs
+// are read with plain loads (shared memory) or through L2 (CG: global memory written by this CTA's own threads).
+template <int W, bool CG>
+__device__ __forceinline__ void limb_sums_w(const ActSmem& a, int s0, int s1) {
+    int8_t* sd = W == 32 ? a.sd32 : a.sd16;
+    constexpr int PER = 256 / W;  // sub-blocks per 256-block
+#pragma unroll 1
+    for (int e = s0 * 4 + threadIdx.x; e < s1 * 4; e += DK_THREADS) {
+        const int S = e >> 2, l = e & 3;
+        const uint4* src = reinterpret_cast<const uint4*>(a.lim + l * a.n_pad + S * W);
+        int sum = 0;
+#pragma unroll
+        for (int q = 0; q < W / 16; ++q) {
+            const uint4 x = CG ? __ldcg(src + q) : src[q];
+            sum = __dp4a(int(x.x), 0x01010101, sum);
+            sum = __dp4a(int(x.y), 0x01010101, sum);
+            sum = __dp4a(int(x.z), 0x01010101, sum);
+            sum = __dp4a(int(x.w), 0x01010101, sum);
         }
-    }
-    if (sd_mask & 2) {
-        for (int e = threadIdx.x; e < n / 4; e += DK_THREADS) {  // n/16 sub-blocks x 4 limbs
-            const int S = e >> 2, l = e & 3;
-            const uint4 x = *reinterpret_cast<const uint4*>(a.lim + l * a.n_pad + S * 16);
-            int sum = __dp4a(int(x.x), 0x01010101, 0);
-            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
-            const int lo = ((sum + 128) & 255) - 128, blk = S >> 4, si = S & 15;
-            a.sd16[(blk * 8 + l) * 16 + si] = int8_t(lo);
-            a.sd16[(blk * 8 + 4 + l) * 16 + si] = int8_t((sum - lo) >> 8);
-        }
+        const int lo = ((sum + 128) & 255) - 128, blk = S / PER, si = S % PER;
+        sd[(blk * 8 + l) * PER + si] = int8_t(lo);
+        sd[(blk * 8 + 4 + l) * PER + si] = int8_t((sum - lo) >> 8);
     }
 }
 __device__ __forceinline__ int sd_need(int type) { return type == ELB_Q4_K ? 1 : type == ELB_Q6_K ? 2 : 0; }
 __device__ __forceinline__ int unit_bytes_of(int type) { return type == ELB_Q4_K ? Q4K_UNIT : type == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT; }
 
-// Activation of the next matvec -> limbs in shared memory, by every CTA for itself. Two sources:
-//  * resid != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): the vector is
-//    resid.x + the resid.np vectors at resid.parts (the row-parallel matvec before it left partial sums, two per
-//    tensor-parallel rank, see DK_EPI_PART), added in that order by every CTA of every rank alike; CTA c also stores
-//    its slice of the sum to resid.out, the residual stream of the next conversion. RMSNorm with the reference's operation order (src/ops.cpp:155-160), sum of squares in double.
-//  * otherwise src with max|src| known (amax_bits, the bit pattern of a non-negative float).
-// All of it read through L2 (written by other CTAs before the last barrier). Returns inv_scale = 2^-k.
-struct Resid {
-    const float* x;
-    const float* parts;  // np vectors of E floats, added in order; np = 0: none
-    int np;
-    float* out;
-};
+__device__ __forceinline__ float pow2_neg(int k) { return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k); }
 
-__device__ float convert_act(const float* src, const Resid* resid, int n, const float* norm_w, float eps,
-                             const unsigned* amax_bits, int nl, const ActSmem& a, double* red, float* redf, int sd_mask) {
+// Activation of the next matvec -> limbs in shared memory, by every CTA for itself: the vector is A (+ B when B is
+// not null: the two buffers of partial sums a row-parallel matvec left, the first of which already holds the residual
+// stream), read through L2 (written by other CTAs before the last barrier).
+//  * norm_w != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): RMSNorm with the
+//    reference's operation order (src/ops.cpp:155-160), sum of squares in double; CTA c also stores its slice of A + B
+//    to `out` (when not null), the residual stream the next row-parallel matvec adds to.
+//  * otherwise max|A| is known (amax_bits, the bit pattern of a non-negative float).
+// Returns inv_scale = 2^-k.
+__device__ __noinline__ float convert_act(const float* A, const float* B, float* out, int n, const float* norm_w, float eps,
+                                          const unsigned* amax_bits, int nl, const ActSmem a, double* red, float* redf, int sd_mask) {
     constexpr int V4 = 5;  // float4 per thread kept in registers: one pass over vectors of up to 10240 values
     const int tid = threadIdx.x;
     int k;
     if (n <= V4 * 4 * DK_THREADS) {
-        // every load of the phase (vector, partial sums, norm weight) is issued before the first use: one round trip
+        // every load of the phase (vectors, norm weight) is issued before the first use: one round trip
         float4 v[V4], w[V4];
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < V4; ++j) {
             const int idx = (j * DK_THREADS + tid) * 4;
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (resid) {
-                v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->x + idx)) : z;
-            } else {
-                v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(src + idx)) : z;
-            }
-            w[j] = norm_w && idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : z;
+            v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(A + idx)) : z;
+            w[j] = idx < n && B ? __ldcg(reinterpret_cast<const float4*>(B + idx)) : z;
         }
-        if (resid) {  // + the partial sums, vector by vector (two at a time in flight), in the same order everywhere
-            for (int q = 0; q < resid->np; q += 2) {
-                float4 a[V4], b[V4];
-                const bool two = q + 1 < resid->np;  // (x + a) + 0 = x + a exactly: an odd count needs no second path
+        if (B) {
 #pragma unroll
-                for (int j = 0; j < V4; ++j) {
-                    const int idx = (j * DK_THREADS + tid) * 4;
-                    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-                    a[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q) * n + idx)) : z;
-                    b[j] = idx < n && two ? __ldcg(reinterpret_cast<const float4*>(resid->parts + size_t(q + 1) * n + idx)) : z;
-                }
-#pragma unroll
-                for (int j = 0; j < V4; ++j) {
-                    v[j].x = __fadd_rn(__fadd_rn(v[j].x, a[j].x), b[j].x);
-                    v[j].y = __fadd_rn(__fadd_rn(v[j].y, a[j].y), b[j].y);
-                    v[j].z = __fadd_rn(__fadd_rn(v[j].z, a[j].z), b[j].z);
-                    v[j].w = __fadd_rn(__fadd_rn(v[j].w, a[j].w), b[j].w);
-                }
+            for (int j = 0; j < V4; ++j) {
+                v[j].x = __fadd_rn(v[j].x, w[j].x); v[j].y = __fadd_rn(v[j].y, w[j].y);
+                v[j].z = __fadd_rn(v[j].z, w[j].z); v[j].w = __fadd_rn(v[j].w, w[j].w);
             }
         }
         float m = 0.f;
-        if (resid) {
+        if (norm_w) {
+#pragma unroll
+            for (int j = 0; j < V4; ++j) {
+                const int idx = (j * DK_THREADS + tid) * 4;
+                w[j] = idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : z;
+            }
             // this CTA's slice of the new residual stream (whole float4s; every CTA holds the same values)
-            const int q4 = n / 4, lo = range_lo(q4, gridDim.x, blockIdx.x), hi = range_lo(q4, gridDim.x, blockIdx.x + 1);
+            const int q4 = n / 4, lo = out ? range_lo(q4, gridDim.x, blockIdx.x) : 0, hi = out ? range_lo(q4, gridDim.x, blockIdx.x + 1) : 0;
             double ss = 0.0;
 #pragma unroll
             for (int j = 0; j < V4; ++j) {
                 const int i4 = j * DK_THREADS + tid;
-                if (i4 >= lo && i4 < hi) *reinterpret_cast<float4*>(resid->out + i4 * 4) = v[j];
+                if (i4 >= lo && i4 < hi) *reinterpret_cast<float4*>(out + i4 * 4) = v[j];
                 ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
             }
             ss = dk_block_sum(ss, red, tid);
@@ -293,55 +260,53 @@ __device__ float convert_act(const float* src, const Resid* resid, int n, const 
             if (idx < n) limbs4(v[j], sc, a.lim, a.n_pad, idx);
         }
     } else {  // longer vectors (no residual stream is that long: the host keeps such shapes off this kernel)
-        const float m = __uint_as_float(__ldcg(amax_bits));
-        k = split_shift(m, nl);
+        k = split_shift(__uint_as_float(__ldcg(amax_bits)), nl);
         const Pow2 sc = make_pow2(k);
+#pragma unroll 2
         for (int i = tid * 4; i < n; i += DK_THREADS * 4)
-            limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, a.lim, a.n_pad, i);
+            limbs4(__ldcg(reinterpret_cast<const float4*>(A + i)), sc, a.lim, a.n_pad, i);
     }
     dk_sync();
-    limb_sums(a, n, sd_mask);
+    if (sd_mask & 1) limb_sums_w<32, false>(a, 0, n / 32);
+    if (sd_mask & 2) limb_sums_w<16, false>(a, 0, n / 16);
     dk_sync();
-    return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
+    return pow2_neg(k);
 }
 
 // The FFN activation when its limbs do not fit in shared memory: the CTAs convert 256-value blocks of it (equal
 // ranges) into global memory - limbs [4][n_pad], then the sub-block sums, the layout of ActSmem - and meet at a grid
 // barrier; ffn_down then reads the limbs through L2. max|src| is known (amax_bits). Returns inv_scale = 2^-k.
-__device__ float convert_act_global(const float* src, int n, const unsigned* amax_bits, int nl, const ActSmem& g, int sd_mask) {
+__device__ __noinline__ float convert_act_global(const float* src, int n, const unsigned* amax_bits, int nl, const ActSmem g, int sd_mask) {
     const int tid = threadIdx.x, nb = n / 256;
     const int b0 = range_lo(nb, gridDim.x, blockIdx.x), b1 = range_lo(nb, gridDim.x, blockIdx.x + 1);
     const int k = split_shift(__uint_as_float(__ldcg(amax_bits)), nl);
     const Pow2 sc = make_pow2(k);
+#pragma unroll 1
     for (int i = b0 * 256 + tid * 4; i < b1 * 256; i += DK_THREADS * 4)
         limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, g.lim, g.n_pad, i);
-    dk_sync();  // this CTA's limbs are visible to its own threads
-    if (sd_mask & 1) {
-        for (int e = b0 * 32 + tid; e < b1 * 32; e += DK_THREADS) {  // 8 sub-blocks x 4 limbs per block
-            const int S = e >> 2, l = e & 3;
-            const uint4* q = reinterpret_cast<const uint4*>(g.lim + l * g.n_pad + S * 32);
-            const uint4 x = __ldcg(q), y = __ldcg(q + 1);  // through L2: the addresses are reused every layer
-            int sum = __dp4a(int(x.x), 0x01010101, 0);
-            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
-            sum = __dp4a(int(y.x), 0x01010101, sum); sum = __dp4a(int(y.y), 0x01010101, sum);
-            sum = __dp4a(int(y.z), 0x01010101, sum); sum = __dp4a(int(y.w), 0x01010101, sum);
-            const int lo = ((sum + 128) & 255) - 128, blk = S >> 3, si = S & 7;
-            g.sd32[(blk * 8 + l) * 8 + si] = int8_t(lo);
-            g.sd32[(blk * 8 + 4 + l) * 8 + si] = int8_t((sum - lo) >> 8);
+    dk_sync();  // this CTA's limbs are visible to its own threads (read back through L2: the addresses are reused every layer)
+    if (sd_mask & 1) limb_sums_w<32, true>(g, b0 * 8, b1 * 8);
+    if (sd_mask & 2) limb_sums_w<16, true>(g, b0 * 16, b1 * 16);
+    return pow2_neg(k);
+}
+
+// Tensor parallelism: after an exchange every rank holds, in its own copy of the set, the two partial-sum vectors of
+// every rank (rank 0's first one carries the residual stream). CTA c adds its slice of them in rank order — the same
+// order on every rank, so the residual stream stays bit-identical everywhere — and stores it to `out`; the CTAs then
+// meet at a grid barrier and the conversion reads `out` alone.
+__device__ __noinline__ void reduce_ranks(const DkParams& p, const float* set, float* out) {
+    const int q4 = p.E / 4, lo = range_lo(q4, gridDim.x, blockIdx.x), hi = range_lo(q4, gridDim.x, blockIdx.x + 1);
+    const int nv = p.tp_size * p.pv;
+#pragma unroll 1
+    for (int i4 = lo + threadIdx.x; i4 < hi; i4 += DK_THREADS) {
+        float4 v = __ldcg(reinterpret_cast<const float4*>(set) + i4);
+#pragma unroll 4
+        for (int q = 1; q < nv; ++q) {
+            const float4 b = __ldcg(reinterpret_cast<const float4*>(set + size_t(q) * p.E) + i4);
+            v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
         }
+        reinterpret_cast<float4*>(out)[i4] = v;
     }
-    if (sd_mask & 2) {
-        for (int e = b0 * 64 + tid; e < b1 * 64; e += DK_THREADS) {  // 16 sub-blocks x 4 limbs per block
-            const int S = e >> 2, l = e & 3;
-            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(g.lim + l * g.n_pad + S * 16));
-            int sum = __dp4a(int(x.x), 0x01010101, 0);
-            sum = __dp4a(int(x.y), 0x01010101, sum); sum = __dp4a(int(x.z), 0x01010101, sum); sum = __dp4a(int(x.w), 0x01010101, sum);
-            const int lo = ((sum + 128) & 255) - 128, blk = S >> 4, si = S & 15;
-            g.sd16[(blk * 8 + l) * 16 + si] = int8_t(lo);
-            g.sd16[(blk * 8 + 4 + l) * 16 + si] = int8_t((sum - lo) >> 8);
-        }
-    }
-    return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k);
 }
 
 __device__ __forceinline__ void dk_stamp(const DkParams& p, int l, int ev) {
@@ -363,7 +328,7 @@ __device__ __forceinline__ int kind_li(const DkParams& p, int l, int i) { return
 // Whole tiles of the matrix's group by default (no tile is shared between CTAs: the phase ends without any exchange;
 // a group with fewer tiles than CTAs occupies the first CTAs only); equal unit ranges for a balanced matrix.
 struct WarpRange { int cA, cB, wA, wB; };
-__device__ __forceinline__ WarpRange warp_range(const DkKind& m, int warp) {
+__device__ __noinline__ WarpRange warp_range(const DkKind& m, int warp) {
     const int c = blockIdx.x;
     WarpRange r;
     if (m.balanced) {
@@ -382,13 +347,15 @@ __device__ __forceinline__ WarpRange warp_range(const DkKind& m, int warp) {
 }
 
 // The shares of a warp (and of its CTA) in the matrices of every kind are computed once, when the kernel starts, and
-// kept in shared memory: sched[warp][kind] = {wA, wB}, cta[kind] = {cA, cB}.
+// kept in shared memory: warp[kind] = {wA, wB} and tiles[kind] = {first row tile, last row tile} of this warp's share,
+// cta[kind] = {cA, cB}.
 struct Sched {
-    const int2* warp;  // this warp's [DK_KINDS]
-    const int2* cta;   // [DK_KINDS]
+    const int2* warp;   // this warp's [DK_KINDS]
+    const int2* tiles;  // all warps' [DK_WARPS][DK_KINDS]
+    const int2* cta;    // [DK_KINDS]
 };
 
-// Prefetch cursor: the next unit of this warp's stream that has not been requested yet.
+// Prefetch cursor: the next unit of a warp's stream that has not been requested yet.
 struct Cursor {
     int l, i, u, end, unit_bytes;  // matrix i of layer l (l > n_layer: the stream has ended)
     const uint8_t* W;
@@ -397,9 +364,9 @@ __device__ __forceinline__ bool cursor_live(const DkParams& p, const Cursor& c) 
 __device__ __forceinline__ void cursor_next_matrix(const DkParams& p, Cursor& c) {
     if (c.l >= p.n_layer || ++c.i == p.n_qkv + 3) { c.i = 0; ++c.l; }
 }
-__device__ __forceinline__ void cursor_seek(const DkParams& p, Cursor& c, const Sched& sc) {  // first non-empty range from (l, i) on
+__device__ __forceinline__ void cursor_seek(const DkParams& p, Cursor& c, const int2* sched_warp) {  // first non-empty range from (l, i) on
     while (cursor_live(p, c)) {
-        const int2 r = sc.warp[kind_li(p, c.l, c.i)];
+        const int2 r = sched_warp[kind_li(p, c.l, c.i)];
         if (r.x < r.y) {
             c.u = r.x; c.end = r.y; c.W = p.W[c.l][c.i]; c.unit_bytes = unit_bytes_of(p.wtype[c.l][c.i]);
             return;
@@ -429,7 +396,7 @@ struct Ring {             // consumer side, in registers of the working warp
     int c_off;            // offset of the next unit to consume (before the wrap rule is applied)
     unsigned c_seq;       // units given up so far
     unsigned freed;       // bytes given up so far
-    unsigned* freed_out;  // where the producer reads it
+    uint32_t freed_out;   // where the producer reads it (shared-memory address)
 };
 
 __device__ __forceinline__ uint32_t dk_smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -448,16 +415,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // The producer warp: lane w < DK_WARPS walks the stream of working warp w and requests its units as room appears in that
 // warp's ring. All lanes run in step, so the bookkeeping is paid once for the sixteen rings. Ends when every stream
 // has been requested to its end, when the step is given up (dead flag), or when nothing has moved for too long.
-__device__ void producer_warp(const DkParams& p, const uint32_t ring0, const int ring_bytes, const uint32_t bars0,
-                              const int2* sched_all, RingShared* rs, const int* s_dead, const int lane) {
+__device__ __noinline__ void producer_warp(const DkParams& p, const uint32_t ring0, const int ring_bytes, const uint32_t bars0,
+                                           const int2* sched_all, RingShared* rs, const int* s_dead, const int lane) {
     const bool mine = lane < DK_WARPS;
-    const Sched sc{sched_all + (mine ? lane : 0) * DK_KINDS, nullptr};
+    const int2* sched_warp = sched_all + (mine ? lane : 0) * DK_KINDS;
     Cursor c;
     c.l = 0;
     c.i = 0;
     c.u = c.end = c.unit_bytes = 0;
     c.W = nullptr;
-    if (mine) cursor_seek(p, c, sc);
+    if (mine) cursor_seek(p, c, sched_warp);
     else c.l = p.n_layer + 1;
     const uint32_t base = ring0 + uint32_t(lane * ring_bytes), bars = bars0 + uint32_t(lane * DK_NBAR) * 8u;
     unsigned issued = 0, seq = 0, idle = 0;
@@ -484,7 +451,7 @@ __device__ void producer_warp(const DkParams& p, const uint32_t ring0, const int
                 did = true;
                 if (++c.u == c.end) {
                     cursor_next_matrix(p, c);
-                    cursor_seek(p, c, sc);
+                    cursor_seek(p, c, sched_warp);
                 }
             }
         }
@@ -513,6 +480,7 @@ __device__ __forceinline__ uint32_t ring_front(const DkParams& p, Ring& r, int u
     }
     const uint32_t bar = r.bars + (r.c_seq % DK_NBAR) * 8u, parity = (r.c_seq / DK_NBAR) & 1u;
     bool done = false;
+#pragma unroll 1
     for (unsigned it = 0; it < DK_MBAR_LIMIT && !done; ++it) done = mbar_try(bar, parity);
     if (!done && !*s_dead) {
         *s_dead = 1;
@@ -525,10 +493,10 @@ __device__ __forceinline__ void ring_pop(Ring& r, int ub, int lane) {
     r.c_off += ub;
     r.freed += unsigned(ub);
     ++r.c_seq;
-    if (lane == 0) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(dk_smem_u32(r.freed_out)), "r"(r.freed) : "memory");
+    if (lane == 0) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(r.freed_out), "r"(r.freed) : "memory");
 }
 // Before the kernel ends: the producer must have stopped and every copy it requested must have landed (bounded waits).
-__device__ __forceinline__ void ring_drain(Ring& r, const RingShared* rs, int warp) {
+__device__ __noinline__ void ring_drain(Ring& r, const RingShared* rs, int warp) {
     unsigned it = 0;
     while (!*reinterpret_cast<const volatile int*>(&rs->producer_done) && ++it < DK_SPIN_LIMIT) __nanosleep(100);
     const unsigned end = *reinterpret_cast<const volatile unsigned*>(&rs->issued[warp]);
@@ -546,44 +514,32 @@ enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU_AMAX = 2, DK_EPI_LOGITS = 
 struct PhaseSmem {
     Sched sched;
     ActSmem act;
-    float* red;      // [DK_WARPS][slots][16]
+    float* red;      // [DK_WARPS][slots][16] row sums of each warp's share, per row tile it touches
+    float* outs;     // [cta_tiles][16] row sums of the CTA's share
     double* red8;    // [DK_WARPS]
-    int* wfirst;     // [DK_WARPS]
-    int* wlast;      // [DK_WARPS]
     int* flags;      // [4]: dead (2), block amax bits (3)
 };
 
 template <int TYPE, bool CG>
-__device__ void run_units(const DkParams& p, const int upt, const WarpRange& r, Ring& rg,
-                          const PhaseSmem& s, int warp, int lane) {
+__device__ void run_units(const DkParams& p, const int upt, const int wA, const int wB, Ring& rg, const PhaseSmem& s, int warp,
+                          int lane) {
     const int g = lane >> 2, t = lane & 3;
     constexpr int UB = TYPE == ELB_Q4_K ? Q4K_UNIT : TYPE == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT;
     const int8_t* sd = TYPE == ELB_Q6_K ? s.act.sd16 : s.act.sd32;
     Acc a{{0.f, 0.f}, {0.f, 0.f}};
     int slot = 0;
-    int X = r.wA / upt, b = r.wA - X * upt;
-    if (lane == 0) { s.wfirst[warp] = X; s.wlast[warp] = r.wB > r.wA ? (r.wB - 1) / upt : X - 1; }
+    int b = wA % upt;
     const float wt = t < 2 ? (t & 1 ? 65536.0f : 1.0f) : 0.0f;
     const float wtm = (t & 1 ? 65536.0f : 1.0f) * (t & 2 ? 256.0f : 1.0f);
     DbgOut dbg{nullptr, nullptr, nullptr, 0, 0, 0, 0};
-#ifdef ELB_DK_UNITPROF  // diagnostics build: where warp 0 of CTA 0 spends its clocks inside the unit loop
-    const bool prof = p.prof && blockIdx.x == 0 && warp == 0;
-    long long tp = 0, tw = 0, tc = 0, te = 0, t0 = 0, t1 = 0;
-#define ELB_TICK(acc) if (prof) { t1 = clock64(); acc += t1 - t0; t0 = t1; }
-    if (prof) t0 = clock64();
-#else
-#define ELB_TICK(acc)
-#endif
-    for (int u = r.wA; u < r.wB; ++u) {
+#pragma unroll 1
+    for (int u = wA; u < wB; ++u) {
         Unit<TYPE> cur;
-        const uint32_t src = ring_front(p, rg, UB, &s.flags[2]);
-        ELB_TICK(tw)
-        load_unit(cur, dk_smem_ptr(src), lane);
+        load_unit(cur, dk_smem_ptr(ring_front(p, rg, UB, &s.flags[2])), lane);
         compute_unit<false, CG>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg);
         __syncwarp();  // every lane has its fragments of the unit in registers and has used them
         ring_pop(rg, UB, lane);
-        ELB_TICK(tc)
-        if (++b == upt || u + 1 == r.wB) {
+        if (++b == upt || u + 1 == wB) {
             float v0 = a.acc[0] * wt - a.accm[0] * wtm, v1 = a.acc[1] * wt - a.accm[1] * wtm;
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
@@ -595,114 +551,112 @@ __device__ void run_units(const DkParams& p, const int upt, const WarpRange& r, 
             }
             ++slot;
             a = Acc{{0.f, 0.f}, {0.f, 0.f}};
-            if (b == upt) { b = 0; ++X; }
+            b = 0;
         }
-        ELB_TICK(te)
     }
-#ifdef ELB_DK_UNITPROF
-    if (prof && lane == 0) {
-        atomicAdd(p.prof + 16, (unsigned long long)tp);
-        atomicAdd(p.prof + 17, (unsigned long long)tw);
-        atomicAdd(p.prof + 18, (unsigned long long)tc);
-        atomicAdd(p.prof + 19, (unsigned long long)te);
-        atomicAdd(p.prof + 20, (unsigned long long)(r.wB - r.wA));
-    }
-#endif
-#undef ELB_TICK
 }
 
-// y = W * act for one matrix; the activation limbs are already in shared memory. Ends with this CTA's share written:
+// What the epilogue of a matvec needs besides its sums
+struct EpiArgs {
+    int epi;
+    float* y;               // STORE / SILU: output vector
+    float inv_scale;
+    unsigned* amax_out;     // SILU: where max|y| goes
+    int xset;               // PART: set of partial-sum buffers
+    const float* x_old;     // PART: the residual stream the first contributor of a tile adds (null: nothing is added)
+};
+
+// y = W * act for one matrix; the activation limbs are already in shared memory (GACT: in global memory, written by other
+// CTAs before the last barrier, read through L2). Ends with this CTA's share written:
 //   DK_EPI_STORE      y[row] = sum                       (whole tiles)
 //   DK_EPI_SILU_AMAX  y[o] = silu(gate) * up, max|y|      (whole tiles of a gate|up pair)
-//   DK_EPI_PART       partial sums of a balanced matrix: the CTA that holds a tile's first unit writes vector 0, the
-//                     one that holds its last unit (when it is another CTA) vector 1 of this rank's pair in set `xset`;
-//                     a CTA that holds the whole tile writes zeros to vector 1. Stored on every tensor-parallel rank;
-//                     the consumer adds residual + all the vectors (convert_act).
+//   DK_EPI_PART       partial sums of a balanced matrix: the CTA that holds a tile's first unit writes x_old + sum to
+//                     vector 0, the one that holds its last unit (when it is another CTA) its sum to vector 1 of this
+//                     rank's pair in set `xset`; a CTA that holds the whole tile writes zeros to vector 1. Stored on every
+//                     tensor-parallel rank; the consumer adds the vectors.
 //   DK_EPI_LOGITS     y[v0 + row] = sum on every tensor-parallel rank (this rank's vocabulary rows of the head)
-__device__ void matvec_phase(const DkParams& p, const int type, const int kind, int epi, float* y, float inv_scale, Ring& rg,
-                             const PhaseSmem& s, unsigned* amax_out, int xset = 0, bool gact = false,
-                             bool after_matrix = true) {
+template <bool GACT>
+__device__ __forceinline__ void matvec_phase(const DkParams& p, const int type, const int kind, const EpiArgs& ea, Ring& rg,
+                                          const PhaseSmem& s, bool after_matrix, bool gact) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = p.kind[kind].upt, rows = p.kind[kind].rows;
     const int2 rc = s.sched.cta[kind], rw = s.sched.warp[kind];
-    const WarpRange r{rc.x, rc.y, rw.x, rw.y};
     if (tid == 0) s.flags[3] = 0;
     // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v); the first matrix
     // comes straight from the conversion, which ends with a CTA barrier
     if (after_matrix) dk_sync();
-    if (gact) {  // activation limbs in global memory (written by other CTAs before the last barrier): L2 loads
+    if (GACT && gact) {  // (only the kernel for models with a long FFN activation carries this code)
         switch (type) {
-            case ELB_Q4_K: run_units<ELB_Q4_K, true>(p, upt, r, rg, s, warp, lane); break;
-            case ELB_Q6_K: run_units<ELB_Q6_K, true>(p, upt, r, rg, s, warp, lane); break;
-            default: run_units<ELB_Q8_0, true>(p, upt, r, rg, s, warp, lane); break;
+            case ELB_Q4_K: run_units<ELB_Q4_K, GACT>(p, upt, rw.x, rw.y, rg, s, warp, lane); break;
+            case ELB_Q6_K: run_units<ELB_Q6_K, GACT>(p, upt, rw.x, rw.y, rg, s, warp, lane); break;
+            default: run_units<ELB_Q8_0, GACT>(p, upt, rw.x, rw.y, rg, s, warp, lane); break;
         }
     } else {
         switch (type) {
-            case ELB_Q4_K: run_units<ELB_Q4_K, false>(p, upt, r, rg, s, warp, lane); break;
-            case ELB_Q6_K: run_units<ELB_Q6_K, false>(p, upt, r, rg, s, warp, lane); break;
-            default: run_units<ELB_Q8_0, false>(p, upt, r, rg, s, warp, lane); break;
+            case ELB_Q4_K: run_units<ELB_Q4_K, false>(p, upt, rw.x, rw.y, rg, s, warp, lane); break;
+            case ELB_Q6_K: run_units<ELB_Q6_K, false>(p, upt, rw.x, rw.y, rg, s, warp, lane); break;
+            default: run_units<ELB_Q8_0, false>(p, upt, rw.x, rw.y, rg, s, warp, lane); break;
         }
     }
     dk_sync();
-    if (r.cA < r.cB) {
-        const int Xf = r.cA / upt, ntl = (r.cB - 1) / upt - Xf + 1;
-        float mx = 0.f;
-        for (int e = tid; e < ntl * 8; e += DK_THREADS) {  // sums over the warps in warp order, then the epilogue
-            const int Xt = Xf + (e >> 3), gg = e & 7;
-            float v0 = 0.f, v1 = 0.f;
-#pragma unroll
-            for (int w = 0; w < DK_WARPS; ++w) {
-                const int f = s.wfirst[w];
-                if (Xt < f || Xt > s.wlast[w]) continue;
-                v0 += s.red[(w * p.slots + (Xt - f)) * 16 + gg];
-                v1 += s.red[(w * p.slots + (Xt - f)) * 16 + gg + 8];
-            }
-            v0 *= inv_scale;
-            v1 *= inv_scale;
-            const int64_t r0 = 16 * int64_t(Xt) + gg, r1 = r0 + 8;
-            if (epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
-                const int64_t o = 8 * int64_t(Xt) + gg;
-                if (o < rows / 2) {
-                    const float act = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
-                    y[o] = act;
-                    mx = fmaxf(mx, fabsf(act));
-                }
-            } else if (epi == DK_EPI_PART) {
-                const bool first = r.cA <= Xt * upt, last = r.cB >= (Xt + 1) * upt;
-                const size_t pair = (size_t(xset) * p.tp_size + p.tp_rank) * p.pv * p.E;  // this rank's vectors of the set
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {  // constant indices into the parameter arrays
-                    if (q >= p.tp_size) break;
-                    float* base = p.part_peer[q] + pair;
-                    float* dst = first ? base : base + p.E;
-                    if (r0 < rows) dst[r0] = v0;
-                    if (r1 < rows) dst[r1] = v1;
-                    if (first && last && p.pv == 2) {
-                        if (r0 < rows) base[p.E + r0] = 0.f;
-                        if (r1 < rows) base[p.E + r1] = 0.f;
-                    }
-                }
-                if (p.tp_size > 1) __threadfence_system();  // on the peers before this CTA arrives at the exchange barrier
-            } else if (epi == DK_EPI_LOGITS) {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    if (q >= p.tp_size) break;
-                    if (r0 < rows) p.logits_peer[q][p.v0 + r0] = v0;
-                    if (r1 < rows) p.logits_peer[q][p.v0 + r1] = v1;
-                }
-                if (p.tp_size > 1) __threadfence_system();
-            } else {
-                if (r0 < rows) y[r0] = v0;
-                if (r1 < rows) y[r1] = v1;
-            }
-        }
-        if (epi == DK_EPI_SILU_AMAX) {
-            mx = warp_max(mx);
-            if (lane == 0) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
+    if (rc.x >= rc.y) return;  // (the whole CTA: it has no share of this matrix)
+    const int Xf = rc.x / upt, ntl = (rc.y - 1) / upt - Xf + 1;
+    // Row sums of the CTA's tiles: (row tile, row pair g / g+8) by (warp, half warp), the sixteen lanes of a half add the
+    // contributions of the sixteen working warps in a fixed tree.
+    {
+        const int w = lane & 15, half = lane >> 4;
+        const int2 tl = s.sched.tiles[w * DK_KINDS + kind];  // first and last row tile of warp w's share
+#pragma unroll 1
+        for (int pr = warp; pr < ntl * 8; pr += DK_WARPS) {
+            const int Xt = Xf + (pr >> 3), row = (pr & 7) + 8 * half;
+            float v = Xt >= tl.x && Xt <= tl.y ? s.red[(w * p.slots + (Xt - tl.x)) * 16 + row] : 0.f;
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            if (w == 0) s.outs[(pr >> 3) * 16 + row] = v * ea.inv_scale;
         }
     }
-    if (epi == DK_EPI_SILU_AMAX) {
+    dk_sync();
+    if (ea.epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
+        float mx = 0.f;
+#pragma unroll 1
+        for (int e = tid; e < ntl * 8; e += DK_THREADS) {
+            const int64_t o = 8 * int64_t(Xf) + e;
+            if (o < rows / 2) {
+                const float v0 = s.outs[(e >> 3) * 16 + (e & 7)], v1 = s.outs[(e >> 3) * 16 + (e & 7) + 8];
+                const float act = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
+                ea.y[o] = act;
+                mx = fmaxf(mx, fabsf(act));
+            }
+        }
+        mx = warp_max(mx);
+        if (lane == 0 && mx > 0.f) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
         dk_sync();
-        if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
+        if (tid == 0) atomicMax(ea.amax_out, unsigned(s.flags[3]));
+        return;
+    }
+#pragma unroll 1
+    for (int e = tid; e < ntl * 16; e += DK_THREADS) {
+        const int Xt = Xf + (e >> 4);
+        const int64_t r = 16 * int64_t(Xf) + e;
+        if (r >= rows) continue;
+        float v = s.outs[e];
+        if (ea.epi == DK_EPI_PART) {
+            const bool first = rc.x <= Xt * upt, last = rc.y >= (Xt + 1) * upt;
+            if (first && ea.x_old) v = __fadd_rn(__ldcg(ea.x_old + r), v);
+            const size_t pair = (size_t(ea.xset) * p.tp_size + p.tp_rank) * p.pv * p.E;  // this rank's vectors of the set
+#pragma unroll 1
+            for (int q = 0; q < p.tp_size; ++q) {
+                float* base = p.part_peer[q] + pair;
+                base[(first ? 0 : p.E) + r] = v;
+                if (first && last && p.pv == 2) base[p.E + r] = 0.f;
+            }
+        } else if (ea.epi == DK_EPI_LOGITS) {
+#pragma unroll 1
+            for (int q = 0; q < p.tp_size; ++q) p.logits_peer[q][p.v0 + r] = v;
+        } else {
+            ea.y[r] = v;
+        }
     }
 }
 
@@ -738,23 +692,33 @@ struct AttnSmem {
     float* qs;    // [DK_MAXG][128]
     float* knew;  // [128]
     float* vnew;  // [128]
-    float* Ks;    // [DK_KT][DK_KS]
+    float* Ks;    // [DK_KT][DK_KS]; Ks and Vs together also stage the partial results the last split combines
     float* Vs;    // [DK_KT][128]
     float* Ps;    // [DK_MAXG][DK_KT]
     float* corr;  // [DK_MAXG], then m [DK_MAXG], l [DK_MAXG]
     int* flags;
 };
+constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * DK_KS + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
+static_assert(DK_MAXSPLIT * 4 * DK_PS <= DK_KT * DK_KS + DK_KT * DK_HD, "the staged partial results of four heads must fit in the K/V tile area");
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
+}
+
+// Key splits of one KV head at T keys: a split should have a tile's worth of keys (fewer, longer splits keep the
+// combination short at small contexts), and there are at most p.nsplit of them.
+__device__ __forceinline__ int attn_splits(const DkParams& p, int T) { return max(1, min(p.nsplit, (T + DK_KT - 1) / DK_KT)); }
 
 // K and V rows t0 .. t0+nk-1 of one KV head -> shared memory with cp.async (row `pos`, which this step appends, is
 // filled in from shared memory by the caller). One commit group.
 __device__ __forceinline__ void attn_fetch_kv(const float* kc, const float* vc, const AttnSmem& s, int KD, int kvh, int t0, int nk, int pos) {
-    const unsigned ks = unsigned(__cvta_generic_to_shared(s.Ks)), vs = unsigned(__cvta_generic_to_shared(s.Vs));
+    const uint32_t ks = dk_smem_u32(s.Ks), vs = dk_smem_u32(s.Vs);
     for (int idx = threadIdx.x; idx < nk * (DK_HD / 4); idx += DK_THREADS) {
         const int j = idx / (DK_HD / 4), cc = (idx % (DK_HD / 4)) * 4, t = t0 + j;
         if (t == pos) continue;
         const size_t off = size_t(t) * KD + kvh * DK_HD + cc;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks + unsigned(j * DK_KS + cc) * 4u), "l"(kc + off));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs + unsigned(j * DK_HD + cc) * 4u), "l"(vc + off));
+        cp_async16(ks + uint32_t(j * DK_KS + cc) * 4u, kc + off);
+        cp_async16(vs + uint32_t(j * DK_HD + cc) * 4u, vc + off);
     }
     ring_commit();
 }
@@ -763,28 +727,27 @@ __device__ __forceinline__ void attn_fetch_kv(const float* kc, const float* vc, 
 // from shared memory): it is requested as soon as the q|k|v matvec has released the scratch area, so that it travels
 // while the CTAs meet at the barrier in front of the attention.
 __device__ __forceinline__ void attn_prefetch(const DkParams& p, const int l, const AttnSmem& s) {
-    const int c = blockIdx.x;
-    if (c >= p.HKV * p.nsplit) return;
-    const int kvh = c / p.nsplit, split = c - kvh * p.nsplit;
-    const int pos = p.pos[p.ctl[0]], T = pos + 1;
-    const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);
+    const int c = blockIdx.x, pos = p.pos[p.ctl[0]], T = pos + 1, ns = attn_splits(p, T);
+    if (c >= p.HKV * ns) return;
+    const int kvh = c / ns, split = c - kvh * ns;
+    const int t_begin = range_lo(T, ns, split), t_end = range_lo(T, ns, split + 1);
     attn_fetch_kv(p.kc + size_t(l) * p.kv_stride, p.vc + size_t(l) * p.kv_stride, s, p.HKV * DK_HD, kvh, t_begin, min(DK_KT, t_end - t_begin), pos);
 }
 
-// CTA c < HKV * nsplit works on KV head c / nsplit, key split c % nsplit: q/k norm + RoPE, KV append, flash decode
+// CTA c < HKV * splits works on KV head c / splits, key split c % splits: q/k norm + RoPE, KV append, flash decode
 // over its keys (DK_KT at a time, fetched while the heads are normalised), partial results to the scratch buffer; the
 // last split of a KV head to arrive combines them in split order and writes att (and max|att|).
 // Semantics: src/model.cpp:176-214 of the reference.
-__device__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, unsigned* amax_out) {
+__device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, unsigned* amax_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c = blockIdx.x;
-    if (c >= p.HKV * p.nsplit) return;
-    const int kvh = c / p.nsplit, split = c - kvh * p.nsplit, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
-    const int pos = p.pos[p.ctl[0]], T = pos + 1;
+    const int pos = p.pos[p.ctl[0]], T = pos + 1, ns = attn_splits(p, T);
+    if (c >= p.HKV * ns) return;
+    const int kvh = c / ns, split = c - kvh * ns, group = p.H / p.HKV, QD = p.H * DK_HD, KD = p.HKV * DK_HD;
     float* const kc = p.kc + size_t(l) * p.kv_stride;
     float* const vc = p.vc + size_t(l) * p.kv_stride;
     const float* const q_norm = p.norms + size_t(l) * p.norm_stride + 2 * p.E;
     const float* const k_norm = q_norm + DK_HD;
-    const int t_begin = range_lo(T, p.nsplit, split), t_end = range_lo(T, p.nsplit, split + 1);  // equal key ranges
+    const int t_begin = range_lo(T, ns, split), t_end = range_lo(T, ns, split + 1);  // equal key ranges
     // (the first tile was requested by attn_prefetch before the barrier)
     const float2* cs = reinterpret_cast<const float2*>(p.rope) + size_t(pos) * (p.rope_dim / 2);
     float* m_s = s.corr + DK_MAXG;
@@ -803,6 +766,7 @@ __device__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, un
     }
     float acc[2] = {0.f, 0.f};  // outputs (head tid/128 + 4i, dim tid%128)
     const int od = tid & (DK_HD - 1), oh = tid >> 7;
+#pragma unroll 1
     for (int t0 = t_begin; t0 < t_end; t0 += DK_KT) {
         const int nk = min(DK_KT, t_end - t0);
         if (t0 != t_begin) {
@@ -816,6 +780,7 @@ __device__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, un
         ring_wait<0>();
         dk_sync();
         // scores: warp = (head, 32-key slot), lane = key; dimension order, multiply then add, as the CPU path does
+#pragma unroll 1
         for (int w = warp; w < group * ((nk + 31) / 32); w += DK_WARPS) {
             const int h = w % group, j = (w / group) * 32 + lane;
             if (j < nk) {
@@ -871,15 +836,15 @@ __device__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, un
         }
     }
     dk_sync();
-    float* mine = p.attn_part + (size_t(kvh) * p.nsplit + split) * group * (DK_HD + 2);
+    float* mine = p.attn_part + (size_t(kvh) * p.nsplit + split) * group * DK_PS;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int h = oh + 4 * i;
-        if (h < group) mine[h * (DK_HD + 2) + od] = acc[i];
+        if (h < group) mine[h * DK_PS + od] = acc[i];
     }
     if (tid < group) {
-        mine[tid * (DK_HD + 2) + DK_HD] = m_s[tid];
-        mine[tid * (DK_HD + 2) + DK_HD + 1] = l_s[tid];
+        mine[tid * DK_PS + DK_HD] = m_s[tid];
+        mine[tid * DK_PS + DK_HD + 1] = l_s[tid];
     }
     dk_sync();
     if (tid == 0) {
@@ -887,81 +852,105 @@ __device__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, un
         // the count; acquire: the last arriver sees everybody else's
         unsigned old;
         asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.attn_counters + kvh) : "memory");
-        s.flags[0] = old == unsigned(p.nsplit - 1);
+        s.flags[0] = old == unsigned(ns - 1);
         if (s.flags[0]) p.attn_counters[kvh] = 0;
     }
     dk_sync();
     if (!s.flags[0]) return;
-    // (thread 0's acquire and the barrier above order the other parts' results before the L2 loads below)
-    const float* base = p.attn_part + size_t(kvh) * p.nsplit * group * (DK_HD + 2);
+    // (thread 0's acquire and the barrier above order the other parts' results before the copies below)
+    // The last split combines: the partial results of four heads at a time are staged in the K/V tile area (asynchronous
+    // copies in a rolled loop: one round trip for all of them), then thread (head, dimension) walks the splits in order.
+    const float* base = p.attn_part + size_t(kvh) * p.nsplit * group * DK_PS;
+    float* stage = s.Ks;  // [ns][4][DK_PS]
     float mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int h = oh + 4 * i;
-        if (h >= group) continue;
-        float ms[DK_MAXSPLIT], ls[DK_MAXSPLIT], as[DK_MAXSPLIT];  // every load of the pass is issued before the first use
-#pragma unroll
-        for (int q = 0; q < DK_MAXSPLIT; ++q) {
-            const float* ps = base + (size_t(q < p.nsplit ? q : 0) * group + h) * (DK_HD + 2);
-            ms[q] = q < p.nsplit ? __ldcg(ps + DK_HD) : -INFINITY;
-            ls[q] = __ldcg(ps + DK_HD + 1);
-            as[q] = __ldcg(ps + od);
+#pragma unroll 1
+    for (int hq = 0; hq < group; hq += 4) {
+        const int nh = min(4, group - hq), chunks = nh * (DK_PS / 4);  // 16-byte pieces per split
+        if (hq) dk_sync();  // the previous four heads have been read
+#pragma unroll 1
+        for (int idx = tid; idx < ns * chunks; idx += DK_THREADS) {
+            const int q = idx / chunks, o = (idx - q * chunks) * 4;
+            cp_async16(dk_smem_u32(stage + q * 4 * DK_PS + o), base + (size_t(q) * group + hq) * DK_PS + o);
         }
-        float M = -INFINITY;
-#pragma unroll
-        for (int q = 0; q < DK_MAXSPLIT; ++q) M = fmaxf(M, ms[q]);
-        float Lsum = 0.f, o = 0.f;
-#pragma unroll
-        for (int q = 0; q < DK_MAXSPLIT; ++q) {  // fixed split order
-            if (ms[q] == -INFINITY) continue;
-            const float w = expf(ms[q] - M);
-            Lsum = fmaf(ls[q], w, Lsum);
-            o = fmaf(as[q], w, o);
+        ring_commit();
+        ring_wait<0>();
+        dk_sync();
+        if (oh < nh) {
+            const float* ps = stage + oh * DK_PS;
+            float M = -INFINITY;
+#pragma unroll 1
+            for (int q = 0; q < ns; ++q) M = fmaxf(M, ps[q * 4 * DK_PS + DK_HD]);
+            float Lsum = 0.f, o = 0.f;
+#pragma unroll 1
+            for (int q = 0; q < ns; ++q) {  // fixed split order
+                const float mq = ps[q * 4 * DK_PS + DK_HD];
+                if (mq == -INFINITY) continue;
+                const float w = expf(mq - M);
+                Lsum = fmaf(ps[q * 4 * DK_PS + DK_HD + 1], w, Lsum);
+                o = fmaf(ps[q * 4 * DK_PS + od], w, o);
+            }
+            const float r = o / Lsum;
+            p.att[(kvh * group + hq + oh) * DK_HD + od] = r;
+            mx = fmaxf(mx, fabsf(r));
         }
-        const float r = o / Lsum;
-        p.att[(kvh * group + h) * DK_HD + od] = r;
-        mx = fmaxf(mx, fabsf(r));
     }
     mx = warp_max(mx);
-    if (lane == 0) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
+    if (lane == 0 && mx > 0.f) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
     dk_sync();
     if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
 }
 
 // ---------------------------------------------------------------- the step
 
-constexpr int DK_ATTN_FLOATS = DK_MAXG * DK_HD + 2 * DK_HD + DK_KT * DK_KS + DK_KT * DK_HD + DK_MAXG * DK_KT + 3 * DK_MAXG;
-
 __host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
     const size_t act = size_t(4) * (n_max + 32) + size_t(n_max / 256) * 192, attn = size_t(DK_ATTN_FLOATS) * 4;
     return ((act > attn ? act : attn) + 15) / 16 * 16;
 }
+// grid barriers of one launch (the arrival counter runs on from launch to launch)
+__host__ __device__ inline unsigned dk_barriers_per_launch(const DkParams& p) {
+    const unsigned per_layer = 5u + (p.act_global ? 1u : 0u) + (p.tp_size > 1 ? 2u : 0u);  // tensor parallel: one more behind each reduction
+    // (tensor parallel: the first conversion of a launch has nothing to reduce, the head's has, and the logits meet at one more)
+    return 1u + per_layer * unsigned(p.n_layer) + (p.tp_size > 1 ? 1u : 0u);
+}
+
+// token embedding (get_row, src/ops.cpp:76-82 of the reference): the CTAs decode slices of the row into the residual buffer
+__device__ __noinline__ void embed_token(const DkParams& p, float* x, unsigned step) {
+    const int64_t R = p.token[step];
+    const int lo = range_lo(p.E, gridDim.x, blockIdx.x), hi = range_lo(p.E, gridDim.x, blockIdx.x + 1);
+#pragma unroll 1
+    for (int k = lo + int(threadIdx.x); k < hi; k += DK_THREADS)
+        x[k] = p.embd_type == ELB_F16 ? __half2float(reinterpret_cast<const __half*>(p.embd)[R * p.E + k])
+                                      : elem_value(p.embd_type, tiled_elem(p.embd_type, p.embd, p.E, R, k));
+}
+
+template <bool GACT>
 __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_constant__ DkParams p, const int ring_bytes) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // shared memory: rings | scratch (limbs of the running matvec, or the attention tiles) | reduction buffers | mbarriers
+    // shared memory: rings | scratch (limbs of the running matvec, or the attention tiles) | reduction buffers | mbarriers | tables
     uint8_t* scratch = smem + size_t(DK_WARPS) * ring_bytes;
     uint8_t* tail = scratch + dk_scratch_bytes(p.n_max);
     PhaseSmem s;
-    s.act.lim = reinterpret_cast<int8_t*>(scratch);
     s.red = reinterpret_cast<float*>(tail);
-    s.red8 = reinterpret_cast<double*>(s.red + DK_WARPS * p.slots * 16);
-    s.wfirst = reinterpret_cast<int*>(s.red8 + DK_WARPS);
-    s.wlast = s.wfirst + DK_WARPS;
-    s.flags = s.wlast + DK_WARPS;
-    Ring rg;
-    rg.base = dk_smem_u32(smem) + uint32_t(warp * ring_bytes);
+    s.outs = s.red + DK_WARPS * p.slots * 16;
+    s.red8 = reinterpret_cast<double*>(s.outs + p.cta_tiles * 16);
+    s.flags = reinterpret_cast<int*>(s.red8 + DK_WARPS);
     uint64_t* bars0 = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(s.flags + 4) + 7) & ~uintptr_t(7));
-    rg.bars = dk_smem_u32(bars0 + warp * DK_NBAR);
-    int2* sched_w = reinterpret_cast<int2*>(bars0 + DK_WARPS * DK_NBAR);  // [DK_WARPS][DK_KINDS]
-    int2* sched_c = sched_w + DK_WARPS * DK_KINDS;                         // [DK_KINDS]
+    int2* sched_w = reinterpret_cast<int2*>(bars0 + DK_WARPS * DK_NBAR);  // [DK_WARPS][DK_KINDS] unit ranges
+    int2* sched_t = sched_w + DK_WARPS * DK_KINDS;                         // [DK_WARPS][DK_KINDS] row tile ranges
+    int2* sched_c = sched_t + DK_WARPS * DK_KINDS;                         // [DK_KINDS]
     RingShared* rshared = reinterpret_cast<RingShared*>(sched_c + DK_KINDS);
-    s.sched.warp = sched_w + (warp < DK_WARPS ? warp : 0) * DK_KINDS;
+    const int wk = warp < DK_WARPS ? warp : 0;
+    s.sched.warp = sched_w + wk * DK_KINDS;
+    s.sched.tiles = sched_t;
     s.sched.cta = sched_c;
+    Ring rg;
+    rg.base = dk_smem_u32(smem) + uint32_t(wk * ring_bytes);
+    rg.bars = dk_smem_u32(bars0 + wk * DK_NBAR);
     rg.bytes = ring_bytes;
     rg.c_off = 0;
     rg.c_seq = rg.freed = 0u;
-    rg.freed_out = rshared->freed + (warp < DK_WARPS ? warp : 0);
+    rg.freed_out = dk_smem_u32(rshared->freed + wk);
     AttnSmem as;
     as.qs = reinterpret_cast<float*>(scratch);
     as.knew = as.qs + DK_MAXG * DK_HD;
@@ -971,25 +960,19 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
     as.Ps = as.Vs + DK_KT * DK_HD;
     as.corr = as.Ps + DK_MAXG * DK_KT;
     as.flags = s.flags;
-    auto act_for = [&](int n) {
-        ActSmem a;
-        a.lim = reinterpret_cast<int8_t*>(scratch);
-        a.n_pad = n + 32;
-        a.sd32 = a.lim + 4 * a.n_pad;
-        a.sd16 = a.sd32 + (n / 256) * 64;
-        return a;
-    };
     if (tid == 0) { s.flags[2] = 0; rshared->producer_done = 0; }
     if (tid < DK_WARPS) { rshared->freed[tid] = 0u; rshared->issued[tid] = 0u; }
     if (warp < DK_WARPS && lane < DK_KINDS) {  // this warp's share of every kind of matrix (kinds the model does not have: empty)
         const int kind = lane;
-        const bool have = kind >= 3 || kind < p.n_qkv;
         WarpRange r{0, 0, 0, 0};
-        if (have) r = warp_range(p.kind[kind], warp);
+        if (kind >= 3 || kind < p.n_qkv) r = warp_range(p.kind[kind], warp);
+        const int upt = max(p.kind[kind].upt, 1);
         sched_w[warp * DK_KINDS + kind] = make_int2(r.wA, r.wB);
+        sched_t[warp * DK_KINDS + kind] = r.wA < r.wB ? make_int2(r.wA / upt, (r.wB - 1) / upt) : make_int2(0, -1);
         if (warp == 0) sched_c[kind] = make_int2(r.cA, r.cB);
     }
     if (warp < DK_WARPS && lane == 0) {
+#pragma unroll 1
         for (int i = 0; i < DK_NBAR; ++i)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(rg.bars + i * 8u), "r"(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1005,41 +988,25 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DK_REGS_WORKER));
     int* dead = &s.flags[2];
     const unsigned step = p.ctl[0], epoch = p.ctl[2];
-    unsigned nb = epoch * unsigned(1 + (5 + (p.act_global ? 1 : 0)) * p.n_layer + (p.tp_size > 1 ? 1 : 0)) * gridDim.x;  // arrivals before this launch
+    unsigned nb = epoch * dk_barriers_per_launch(p) * gridDim.x;  // arrivals before this launch
     unsigned* const amax_base = p.amax + (epoch & 1u) * 2 * p.n_layer;
     if (blockIdx.x == 0)  // the other half of the amax slots: untouched by this launch, zero for the next one
         for (int i = tid; i < 2 * p.n_layer; i += DK_THREADS) p.amax[((epoch + 1) & 1u) * 2 * p.n_layer + i] = 0u;
 
-    // token embedding (get_row, src/ops.cpp:76-82 of the reference): the CTAs decode slices of the row into the first
-    // residual buffer and clear the partial sums that the first conversion adds
-    {
-        const int64_t R = p.token[step];
-        const int lo = range_lo(p.E, gridDim.x, blockIdx.x), hi = range_lo(p.E, gridDim.x, blockIdx.x + 1);
-        for (int k = lo + tid; k < hi; k += DK_THREADS) {
-            p.xbuf[k] = p.embd_type == ELB_F16 ? __half2float(reinterpret_cast<const __half*>(p.embd)[R * p.E + k])
-                                               : elem_value(p.embd_type, tiled_elem(p.embd_type, p.embd, p.E, R, k));
-        }
-    }
+    embed_token(p, p.xbuf, step);
     bool ok = grid_barrier(p, nb, dead);
     int cur = 0;  // which half of xbuf holds the residual stream (without the pending partial sums)
     // exchanges (row-parallel matvec -> all ranks) are numbered from the first launch; number x uses set x & 1
     unsigned xn = epoch * unsigned(2 * p.n_layer + 1);
-    float* my_part = nullptr;  // this rank's copy of the partial-sum sets
-#pragma unroll
-    for (int q = 0; q < 8; ++q)
-        if (q == p.tp_rank) my_part = p.part_peer[q];
+    const bool tp = p.tp_size > 1;
+    float* const my_part = p.part_peer[p.tp_rank];  // this rank's copy of the partial-sum sets
     int pending = -1;  // set whose partial sums the next residual conversion adds (-1: none yet in this launch)
-    auto resid_step = [&](float* out) {
-        Resid r{p.xbuf + cur * p.E, pending < 0 ? nullptr : my_part + size_t(pending) * p.tp_size * p.pv * p.E,
-                pending < 0 ? 0 : p.pv * p.tp_size, out ? out : p.xbuf + (cur ^ 1) * p.E};
-        cur ^= 1;
-        return r;
-    };
+    int8_t* const lim_smem = reinterpret_cast<int8_t*>(scratch);
 
     // The step as ONE loop over its matvec stages - per layer q|k|v (0), attn_output (1), gate|up (2), ffn_down (3),
-    // then the head (4) - so that the conversion, the matvec and the attention code exist once in the kernel: unrolled
-    // per stage the code outgrows the instruction cache and the warps stall on instruction fetch.
+    // then the head (4) - so that the conversion, the matvec and the attention code exist once in the kernel.
     const int n_stages = 4 * p.n_layer + 1;
+#pragma unroll 1
     for (int stage = 0; stage < n_stages && ok; ++stage) {
         const bool head = stage + 1 == n_stages;
         const int l = head ? p.n_layer : stage >> 2, k = head ? 4 : stage & 3;
@@ -1055,45 +1022,58 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
         // the stage's activation: where it comes from, how it is normalised, which matrices consume it
         const float *src = nullptr, *norm_w = nullptr;
         const unsigned* amax_in = nullptr;
-        unsigned* amax_out = nullptr;
-        float* y = nullptr;
-        int n = p.E, nl = 4, nm = 1, epi = DK_EPI_PART;
+        EpiArgs ea{DK_EPI_PART, nullptr, 0.f, nullptr, int(xn & 1u), nullptr};
+        int n = p.E, nl = 4, nm = 1;
         int i0 = p.n_qkv, kind0 = 3;  // the stage's first matrix: index within the layer, kind
         bool resid = true;
         switch (k) {
-            case 0: norm_w = layer_norms; nl = p.nl_qkv; i0 = 0; kind0 = 0; nm = p.n_qkv; epi = DK_EPI_STORE; y = p.qkv; break;
+            case 0: norm_w = layer_norms; nl = p.nl_qkv; i0 = 0; kind0 = 0; nm = p.n_qkv; ea.epi = DK_EPI_STORE; ea.y = p.qkv; break;
             case 1: resid = false; src = p.att; n = p.H * DK_HD; amax_in = amax; nl = p.nl_wo; break;
-            case 2: norm_w = layer_norms + p.E; nl = p.nl_gu; i0 = p.n_qkv + 1; kind0 = 4; epi = DK_EPI_SILU_AMAX; y = p.act; amax_out = amax + 1; break;
+            case 2: norm_w = layer_norms + p.E; nl = p.nl_gu; i0 = p.n_qkv + 1; kind0 = 4; ea.epi = DK_EPI_SILU_AMAX; ea.y = p.act; ea.amax_out = amax + 1; break;
             case 3: resid = false; src = p.act; n = p.F; amax_in = amax + 1; nl = p.nl_down; i0 = p.n_qkv + 2; kind0 = 5; break;
-            default: norm_w = p.output_norm; epi = DK_EPI_LOGITS; i0 = 0; kind0 = 6; break;
+            default: norm_w = p.output_norm; ea.epi = DK_EPI_LOGITS; i0 = 0; kind0 = 6; break;
         }
         int need = 0;
         for (int i = 0; i < nm; ++i) need |= sd_need(p.wtype[l][i0 + i]);
-        const bool gact = k == 3 && p.act_global;
-        float inv;
+        const bool gact = GACT && k == 3;
         if (gact) {
-            ActSmem g;
-            g.lim = p.gact;
-            g.n_pad = n + 32;
-            g.sd32 = g.lim + 4 * g.n_pad;
-            g.sd16 = g.sd32 + (n / 256) * 64;
-            s.act = g;
-            inv = convert_act_global(src, n, amax_in, nl, g, need);
+            s.act = act_at(p.gact, n);
+            ea.inv_scale = convert_act_global(src, n, amax_in, nl, s.act, need);
             if (!(ok = grid_barrier(p, nb, dead))) break;
         } else {
-            s.act = act_for(n);
-            Resid rsd{nullptr, nullptr, 0, nullptr};
-            if (resid) rsd = resid_step(head ? p.x : nullptr);  // the last residual stream goes to p.x
-            inv = convert_act(src, resid ? &rsd : nullptr, n, norm_w, p.eps, amax_in, nl, s.act, s.red8, s.red, need);
+            s.act = act_at(lim_smem, n);
+            if (!resid) {
+                ea.inv_scale = convert_act(src, nullptr, nullptr, n, nullptr, p.eps, amax_in, nl, s.act, s.red8, s.red, need);
+            } else if (pending < 0) {  // the embedding: nothing to add, the residual stream is where it is
+                ea.inv_scale = convert_act(p.xbuf + cur * p.E, nullptr, nullptr, n, norm_w, p.eps, nullptr, nl, s.act, s.red8, s.red, need);
+            } else {
+                // the new residual stream: the partial sums of the last row-parallel matvec (its first buffer carries the
+                // old stream); it goes to the other half of xbuf, after the last layer to p.x
+                float* const xnew = head ? p.x : p.xbuf + (cur ^ 1) * p.E;
+                const float* const set = my_part + size_t(pending) * p.tp_size * p.pv * p.E;
+                if (tp) {
+                    reduce_ranks(p, set, xnew);
+                    if (!(ok = grid_barrier(p, nb, dead))) break;
+                    ea.inv_scale = convert_act(xnew, nullptr, nullptr, n, norm_w, p.eps, nullptr, nl, s.act, s.red8, s.red, need);
+                } else {
+                    ea.inv_scale = convert_act(set, set + p.E, xnew, n, norm_w, p.eps, nullptr, nl, s.act, s.red8, s.red, need);
+                }
+                cur ^= 1;
+            }
         }
+        // the residual stream a row-parallel matvec adds to its partial sums (under tensor parallelism: rank 0 alone)
+        ea.x_old = ea.epi == DK_EPI_PART && p.tp_rank == 0 ? p.xbuf + cur * p.E : nullptr;
         const int sb = k == 0 ? 0 : 3 * k + 2;  // profile stamps of the stage: conversion, matvec, barrier
         if (!head) dk_stamp(p, l, sb + 1);
-        for (int i = 0; i < nm; ++i)
-            matvec_phase(p, p.wtype[l][i0 + i], kind0 + i, epi, k == 0 ? y + p.qkv_col[i] : y, inv, rg, s, amax_out, int(xn & 1u), gact, i > 0);
+        for (int i = 0; i < nm; ++i) {
+            EpiArgs e2 = ea;
+            if (k == 0) e2.y = ea.y + p.qkv_col[i];
+            matvec_phase<GACT>(p, p.wtype[l][i0 + i], kind0 + i, e2, rg, s, i > 0, gact);
+        }
         if (!head) dk_stamp(p, l, sb + 2);
         if (k == 0) attn_prefetch(p, l, as);
-        if (k == 1 || k == 3 || (head && p.tp_size > 1)) {  // row-parallel matvecs and the logits meet all ranks
-            ok = exchange_barrier(p, nb, xn, dead);
+        if (k == 1 || k == 3 || (head && tp)) {  // row-parallel matvecs and the logits meet all ranks
+            ok = grid_barrier(p, nb, dead, tp, xn);
             pending = int(xn & 1u);
             ++xn;
         } else if (!head) {
@@ -1110,8 +1090,8 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
 
 // everything but the rings
 static size_t decode_fixed_smem(const DkParams& p) {
-    return dk_scratch_bytes(p.n_max) + size_t(DK_WARPS) * p.slots * 16 * 4 + DK_WARPS * 8 + 2 * DK_WARPS * 4 + 4 * 4 + 16 +
-           size_t(DK_WARPS) * DK_NBAR * 8 + size_t(DK_WARPS + 1) * DK_KINDS * 8 + sizeof(RingShared);
+    return dk_scratch_bytes(p.n_max) + size_t(DK_WARPS) * p.slots * 16 * 4 + size_t(p.cta_tiles) * 16 * 4 + DK_WARPS * 8 + 4 * 4 + 16 +
+           size_t(DK_WARPS) * DK_NBAR * 8 + size_t(2 * DK_WARPS + 1) * DK_KINDS * 8 + sizeof(RingShared);
 }
 size_t decode_smem_bytes(const DkParams& p, int ring_bytes) { return size_t(DK_WARPS) * ring_bytes + decode_fixed_smem(p); }
 
@@ -1127,29 +1107,36 @@ int decode_ring_bytes(const DkParams& p, int max_unit, int min_unit, int device)
     return per >= size_t(2) * max_unit ? int(per) : 0;
 }
 
-int decode_step_launch(const DkParams& p, int slot_bytes, int grid, cudaStream_t s) {
-    const size_t smem = decode_smem_bytes(p, slot_bytes);
-    ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(k_decode_step), smem));
-    void* args[] = {const_cast<DkParams*>(&p), const_cast<int*>(&slot_bytes)};
-    ELB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(k_decode_step), dim3(grid), dim3(DK_CTA_THREADS), args, smem, s));
+static const void* decode_kernel(const DkParams& p) {
+    return p.act_global ? reinterpret_cast<const void*>(k_decode_step<true>) : reinterpret_cast<const void*>(k_decode_step<false>);
+}
+
+int decode_step_launch(const DkParams& p, int ring_bytes, int grid, cudaStream_t s) {
+    const size_t smem = decode_smem_bytes(p, ring_bytes);
+    ELB_TRY(ensure_dyn_smem(decode_kernel(p), smem));
+    void* args[] = {const_cast<DkParams*>(&p), const_cast<int*>(&ring_bytes)};
+    ELB_CUDA(cudaLaunchCooperativeKernel(decode_kernel(p), dim3(grid), dim3(DK_CTA_THREADS), args, smem, s));
     return ELB_OK;
 }
 
 // can one CTA per SM of the step kernel be resident with this much shared memory?
-int decode_step_fits(const DkParams& p, int slot_bytes, int device, bool* fits) {
+int decode_step_fits(const DkParams& p, int ring_bytes, int device, bool* fits) {
     DeviceInfo di;
     ELB_TRY(device_info(device, &di));
-    const size_t smem = decode_smem_bytes(p, slot_bytes);
+    const size_t smem = decode_smem_bytes(p, ring_bytes);
     *fits = false;
     if (smem > di.smem_optin) return ELB_OK;
-    ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(k_decode_step), smem));
+    ELB_TRY(ensure_dyn_smem(decode_kernel(p), smem));
     int per_sm = 0;
-    ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, DK_CTA_THREADS, smem));
+    if (p.act_global) ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step<true>, DK_CTA_THREADS, smem));
+    else ELB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step<false>, DK_CTA_THREADS, smem));
     *fits = per_sm >= 1;
     return ELB_OK;
 }
 
 int decode_threads() { return DK_THREADS; }
 int decode_warps() { return DK_WARPS; }
+int decode_max_split() { return DK_MAXSPLIT; }
+int decode_part_stride() { return DK_PS; }
 
 }  // namespace elb

@@ -65,6 +65,7 @@ struct DkParams {
     unsigned* bar;          // grid barrier counter: counts arrivals for ever (compared modulo 2^32)
     int* err;               // raised when a barrier wait ran out
     int slots;              // row-tile slots per warp in the reduction buffer
+    int cta_tiles;          // most row tiles a CTA's share of a matrix can touch
     int n_max;              // longest activation vector
     unsigned long long* prof;  // diagnostics (ELB_DK_PROF=1): [n_layer][16] nanosecond stamps of CTA 0, else null
 };
@@ -77,5 +78,7 @@ size_t decode_smem_bytes(const DkParams& p, int ring_bytes);
 int decode_ring_bytes(const DkParams& p, int max_unit, int min_unit, int device);
 int decode_threads();
 int decode_warps();
+int decode_max_split();    // most key splits of one KV head
+int decode_part_stride();  // floats per (key split, head) of attn_part
 
 }  // namespace elb

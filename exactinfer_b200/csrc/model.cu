@@ -467,13 +467,14 @@ int setup_decode_kernel(Model* m) {
     p.W[c.n_layer][0] = m->head->tiled;
     p.wtype[c.n_layer][0] = uint8_t(m->head->type);
     int unit_max = m->head->unit_bytes, unit_min = m->head->unit_bytes;  // largest and smallest unit of the step
-    int slots = 0;
+    int slots = 0, cta_tiles = 0;
     auto account = [&](const Weight* w) {
         unit_max = std::max(unit_max, w->unit_bytes);
         unit_min = std::min(unit_min, w->unit_bytes);
         const int64_t per_cta = (w->tiles + di.sm_count - 1) / di.sm_count * w->units_per_tile;
         const int64_t per_warp = (per_cta + decode_warps() - 1) / decode_warps();
         slots = std::max(slots, int((per_warp + w->units_per_tile - 1) / w->units_per_tile + 2));
+        cta_tiles = std::max(cta_tiles, int((w->tiles + di.sm_count - 1) / di.sm_count + 2));
     };
     account(m->head);
     for (int l = 0; l < c.n_layer; ++l) {
@@ -534,7 +535,7 @@ int setup_decode_kernel(Model* m) {
     p.output_norm = m->output_norm;
     p.embd = m->embd->tiled; p.embd_type = m->embd->type;
     p.E = E; p.F = F; p.H = m->H; p.HKV = m->HKV; p.rope_dim = c.rope_dim; p.n_ctx = m->n_ctx;
-    p.nsplit = std::max(1, std::min({32, m->attn_split, di.sm_count / m->HKV}));
+    p.nsplit = std::max(1, std::min({decode_max_split(), m->attn_split, di.sm_count / m->HKV}));
     p.tp_rank = m->tp.rank; p.tp_size = N; p.pv = pv; p.v0 = int(m->tp.v0); p.xctl = m->xctl;
     for (int q = 0; q < N; ++q) {
         uint8_t* base = static_cast<uint8_t*>(m->xarea.peer[q]);
@@ -548,7 +549,7 @@ int setup_decode_kernel(Model* m) {
     p.x = m->x; p.qkv = m->qkv; p.att = m->att; p.act = m->act; p.logits = m->logits;
     p.xbuf = m->xbuf; p.bar = m->sync_words; p.ctl = m->sync_words + 1; p.amax = m->sync_words + 4;
     p.attn_part = m->attn_part; p.attn_counters = m->attn_counters;
-    p.err = err_dev; p.slots = slots; p.n_max = std::max({E, Fmax, QD});
+    p.err = err_dev; p.slots = slots; p.cta_tiles = cta_tiles; p.n_max = std::max({E, Fmax, QD});
     m->dk_grid = di.sm_count;
     // 32-bit unit arithmetic in the kernel
     bool small = true;
@@ -556,10 +557,10 @@ int setup_decode_kernel(Model* m) {
         for (const Weight* w : {m->layers[size_t(l)].wo, m->layers[size_t(l)].gu, m->layers[size_t(l)].down, m->head})
             if (w->tiles * w->units_per_tile * int64_t(di.sm_count) >= (int64_t(1) << 31) || w->max_grid < di.sm_count) small = false;
     // The rings of the warps take whatever shared memory the activation limbs and the reduction buffers leave; a ring
-    // shorter than ELB_DK_MIN_RING bytes (default: three of the largest units) would leave the weight stream too little
+    // shorter than ELB_DK_MIN_RING bytes (default: 8 KB, three to four units) would leave the weight stream too little
     // run-ahead, and the long FFN activation then goes to global memory instead.
     bool fits = false;
-    int min_ring = 3 * unit_max;
+    int min_ring = std::max(8192, 2 * unit_max);
     if (const char* v = std::getenv("ELB_DK_MIN_RING")) min_ring = std::max(2 * unit_max, std::atoi(v));
     auto try_fit = [&]() -> int {
         m->dk_slot = decode_ring_bytes(p, unit_max, unit_min, m->device);
@@ -858,7 +859,7 @@ int model_finalize(Model* m) {
     m->attn_split = std::max(1, std::min(32, (di.sm_count + m->HKV - 1) / m->HKV));
     if (const char* v = std::getenv("ELB_ATTN_SPLIT")) m->attn_split = std::max(1, std::min(32, std::atoi(v)));
     const int group = c.n_head / c.n_head_kv;
-    ELB_CUDA(cudaMalloc(&m->attn_part, size_t(m->HKV) * m->attn_split * group * (128 + 2) * 4));
+    ELB_CUDA(cudaMalloc(&m->attn_part, size_t(m->HKV) * m->attn_split * group * std::max(128 + 2, decode_part_stride()) * 4));
     ELB_CUDA(cudaMalloc(&m->attn_counters, size_t(m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->top_dev, TOP_BYTES));
@@ -1045,8 +1046,8 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
         if (t[20])  // a build with -DELB_DK_UNITPROF: clocks of warp 0 of CTA 0 per unit, all launches so far
             std::fprintf(stderr, "[dk prof] warp 0, clocks per unit: requests %.0f, waiting for the unit %.0f, arithmetic %.0f, row-tile ends %.0f (%llu units)\n",
                          double(t[16]) / double(t[20]), double(t[17]) / double(t[20]), double(t[18]) / double(t[20]), double(t[19]) / double(t[20]), t[20]);
-        if (t[23]) std::fprintf(stderr, "[dk prof] per request: issue %.0f clocks, bookkeeping and next-matrix lookup %.0f (%llu requests)\n",
-                                double(t[21]) / double(t[23]), double(t[22]) / double(t[23]), t[23]);
+        if (t[27]) std::fprintf(stderr, "[dk prof] per matrix of a layer (thread 0): own units %.0f clocks, waiting for the other warps %.0f, reduction and epilogue %.0f (%llu matrices)\n",
+                                double(t[24]) / double(t[27]), double(t[25]) / double(t[27]), double(t[26]) / double(t[27]), t[27]);
 
     }
     m->last_rows = 1;
