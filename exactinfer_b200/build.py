@@ -44,7 +44,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
         return LIB
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
-    extra = (["-Xptxas", "-v"] if verbose else []) + os.environ.get("ELB_NVCC_FLAGS", "").split()  # e.g. -DELB_DK_UNITPROF
+    extra = (["-Xptxas", "-v"] if verbose else []) + os.environ.get("ELB_NVCC_FLAGS", "").split()  # extra compiler flags for experiments
 
     def compile_one(src):
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")

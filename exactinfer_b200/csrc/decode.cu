@@ -78,8 +78,13 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 // the same on every rank) is complete when every rank's CTAs have arrived. Every CTA waits for the local arrivals; CTA 0
 // then raises this rank's flag of set x & 1 on every peer (system-scope release); every CTA waits for the peers' flags
 // in its own rank's flag words. What a CTA stored to its peers before the barrier is fenced once, by its arriving thread.
-__device__ __noinline__ bool grid_barrier(const DkParams& p, unsigned& target, int* s_dead, bool peers = false, unsigned x = 0) {
+__device__ __noinline__ bool grid_barrier(const DkParams& p, unsigned& target, int* s_dead, bool peers = false, unsigned x = 0, int ev = -1) {
     dk_sync();
+    if (ev >= 0 && threadIdx.x == 0) {  // diagnostics: when this CTA arrived
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.prof_cta[blockIdx.x * 16 + 2 * ev] = t;
+    }
     if (threadIdx.x == 0 && !*s_dead) {
         if (peers) __threadfence_system();  // the CTA's peer stores (ordered before this thread by the CTA barrier)
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");  // orders the CTA's writes before it
@@ -108,186 +113,193 @@ __device__ __noinline__ bool grid_barrier(const DkParams& p, unsigned& target, i
             atomicExch(p.err, 1);
         }
     }
+    if (ev >= 0 && threadIdx.x == 0) {  // ... and when it saw the barrier complete
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.prof_cta[blockIdx.x * 16 + 2 * ev + 1] = t;
+    }
     dk_sync();
     return !*s_dead;
 }
 
 // ---------------------------------------------------------------- activation -> limbs in shared memory
 
-// Block-wide maximum and sum of the conversion. No barrier behind the reads: the two use different buffers, and a
-// buffer is written again only in the next conversion, several CTA barriers later.
-__device__ __forceinline__ float dk_block_max(float v, float* red, int tid) {
-    v = warp_max(v);
-    if ((tid & 31) == 0) red[tid >> 5] = v;
-    dk_sync();
-    float m = red[0];
-#pragma unroll
-    for (int i = 1; i < DK_WARPS; ++i) m = fmaxf(m, red[i]);
-    return m;
-}
-__device__ __forceinline__ double dk_block_sum(double v, double* red, int tid) {
-    v = warp_sum(v);
-    if ((tid & 31) == 0) red[tid >> 5] = v;
-    dk_sync();
-    double s = 0.0;
-#pragma unroll
-    for (int i = 0; i < DK_WARPS; ++i) s += red[i];  // fixed order
-    return s;
-}
-
+// The split activation of a matvec: int8 limbs [4][n_pad], the sums of each limb over the 32-wide (Q4_K's min term) and
+// 16-wide (Q6_K's offset) sub-blocks as two balanced base-256 digits each, in the layout the matvec's extra MMA reads
+// (split.cuh), and one power-of-two scale per 256-block: here every 256-block is split on its own, with the shift
+// k = 8 nl - 2 - e of its own largest magnitude (k_split8 of the reference, src/cuda/model_cuda.cu:701-729, applied per
+// block; the matvec multiplies each block's exact integer sums by 2^-k of that block). A block is then converted
+// without knowing anything about the rest of the vector: no maximum over the whole vector has to be agreed on.
 struct ActSmem {
-    int8_t* lim;   // [4][n_pad]
-    int8_t* sd32;  // [n/256][8][8]
-    int8_t* sd16;  // [n/256][8][16]
+    int8_t* lim;    // [4][n_pad]
+    int8_t* sd32;   // [n/256][8][8]
+    int8_t* sd16;   // [n/256][8][16]
+    float* bscale;  // [n/256] 2^-k of each block
     int n_pad;
 };
+__host__ __device__ inline size_t dk_act_bytes(int n) {  // limbs, sums, scales (a multiple of 16)
+    return (size_t(4) * (n + 32) + size_t(n / 256) * 192 + size_t(n / 256) * 4 + 15) / 16 * 16;
+}
 __device__ __forceinline__ ActSmem act_at(int8_t* base, int n) {
     ActSmem a;
     a.lim = base;
     a.n_pad = n + 32;
     a.sd32 = a.lim + 4 * a.n_pad;
     a.sd16 = a.sd32 + (n / 256) * 64;
+    a.bscale = reinterpret_cast<float*>(a.sd16 + (n / 256) * 128);
     return a;
 }
+__device__ __forceinline__ int sd_need(int type) { return type == ELB_Q4_K ? 1 : type == ELB_Q6_K ? 2 : 0; }
+__device__ __forceinline__ int unit_bytes_of(int type) { return type == ELB_Q4_K ? Q4K_UNIT : type == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT; }
+// 1 / sqrt(x) in double from the single-precision estimate and two Newton steps (relative error ~1e-27 of the exact
+// value before the last rounding): what the reference's 1.0 / sqrt(x) in double gives, after rounding to float,
+// without the division and square root routines
+__device__ __forceinline__ double rsqrt_d(double x) {
+    double y = double(rsqrtf(float(x)));
+    y = y * fma(-0.5 * x, y * y, 1.5);
+    y = y * fma(-0.5 * x, y * y, 1.5);
+    return y;
+}
+__device__ __forceinline__ float pow2_neg(int k) { return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k); }
 
-// Four consecutive values (index idx, a multiple of 4) -> one packed word of each of the 4 limbs (split4 of split.cuh
-// without the sub-block sums, which limb_sums_w adds in a pass of its own).
-__device__ __forceinline__ void limbs4(const float4& f, const Pow2 sc, int8_t* lim, int stride, int idx) {
+// Four consecutive fixed-point values -> one packed word of each of the 4 limbs (balanced base-256 digits: adding 128 at
+// every byte position turns them into the ordinary digits of v + 0x80808080; a 4x4 byte transpose groups them by limb).
+__device__ __forceinline__ void limb_words(const float4& f, const Pow2 sc, uint32_t (&w)[4]) {
     const uint32_t a = (uint32_t(__float2int_rn(f.x * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t b = (uint32_t(__float2int_rn(f.y * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t c = (uint32_t(__float2int_rn(f.z * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t d = (uint32_t(__float2int_rn(f.w * sc.s1 * sc.s2)) + 0x80808080u) ^ 0x80808080u;
     const uint32_t ab01 = __byte_perm(a, b, 0x5140), ab23 = __byte_perm(a, b, 0x7362);  // a0 b0 a1 b1 | a2 b2 a3 b3
     const uint32_t cd01 = __byte_perm(c, d, 0x5140), cd23 = __byte_perm(c, d, 0x7362);
-    *reinterpret_cast<uint32_t*>(lim + idx) = __byte_perm(ab01, cd01, 0x5410);
-    *reinterpret_cast<uint32_t*>(lim + stride + idx) = __byte_perm(ab01, cd01, 0x7632);
-    *reinterpret_cast<uint32_t*>(lim + 2 * stride + idx) = __byte_perm(ab23, cd23, 0x5410);
-    *reinterpret_cast<uint32_t*>(lim + 3 * stride + idx) = __byte_perm(ab23, cd23, 0x7632);
+    w[0] = __byte_perm(ab01, cd01, 0x5410);
+    w[1] = __byte_perm(ab01, cd01, 0x7632);
+    w[2] = __byte_perm(ab23, cd23, 0x5410);
+    w[3] = __byte_perm(ab23, cd23, 0x7632);
 }
 
-// Sums of each limb over the sub-blocks [s0, s1) of width W (32: Q4_K's min term, 16: Q6_K's offset), as two balanced
-// base-256 digits, in the layout the matvec's extra MMA reads (split.cuh). One thread per (sub-block, limb). The limbs
-// are read with plain loads (shared memory) or through L2 (CG: global memory written by this CTA's own threads).
-template <int W, bool CG>
-__device__ __forceinline__ void limb_sums_w(const ActSmem& a, int s0, int s1) {
-    int8_t* sd = W == 32 ? a.sd32 : a.sd16;
-    constexpr int PER = 256 / W;  // sub-blocks per 256-block
-#pragma unroll 1
-    for (int e = s0 * 4 + threadIdx.x; e < s1 * 4; e += DK_THREADS) {
-        const int S = e >> 2, l = e & 3;
-        const uint4* src = reinterpret_cast<const uint4*>(a.lim + l * a.n_pad + S * W);
-        int sum = 0;
-#pragma unroll
-        for (int q = 0; q < W / 16; ++q) {
-            const uint4 x = CG ? __ldcg(src + q) : src[q];
-            sum = __dp4a(int(x.x), 0x01010101, sum);
-            sum = __dp4a(int(x.y), 0x01010101, sum);
-            sum = __dp4a(int(x.z), 0x01010101, sum);
-            sum = __dp4a(int(x.w), 0x01010101, sum);
-        }
-        const int lo = ((sum + 128) & 255) - 128, blk = S / PER, si = S % PER;
-        sd[(blk * 8 + l) * PER + si] = int8_t(lo);
-        sd[(blk * 8 + 4 + l) * PER + si] = int8_t((sum - lo) >> 8);
-    }
-}
-__device__ __forceinline__ int sd_need(int type) { return type == ELB_Q4_K ? 1 : type == ELB_Q6_K ? 2 : 0; }
-__device__ __forceinline__ int unit_bytes_of(int type) { return type == ELB_Q4_K ? Q4K_UNIT : type == ELB_Q6_K ? Q6K_UNIT : Q8_UNIT; }
-
-__device__ __forceinline__ float pow2_neg(int k) { return k <= 126 ? __int_as_float((127 - k) << 23) : ldexpf(1.0f, -k); }
-
-// Activation of the next matvec -> limbs in shared memory, by every CTA for itself: the vector is A (+ B when B is
-// not null: the two buffers of partial sums a row-parallel matvec left, the first of which already holds the residual
-// stream), read through L2 (written by other CTAs before the last barrier).
-//  * norm_w != nullptr (the residual stream in front of attn_norm / ffn_norm / output_norm): RMSNorm with the
-//    reference's operation order (src/ops.cpp:155-160), sum of squares in double; CTA c also stores its slice of A + B
-//    to `out` (when not null), the residual stream the next row-parallel matvec adds to.
-//  * otherwise max|A| is known (amax_bits, the bit pattern of a non-negative float).
-// Returns inv_scale = 2^-k.
-__device__ __noinline__ float convert_act(const float* A, const float* B, float* out, int n, const float* norm_w, float eps,
-                                          const unsigned* amax_bits, int nl, const ActSmem a, double* red, float* redf, int sd_mask) {
-    constexpr int V4 = 5;  // float4 per thread kept in registers: one pass over vectors of up to 10240 values
-    const int tid = threadIdx.x;
-    int k;
-    if (n <= V4 * 4 * DK_THREADS) {
-        // every load of the phase (vectors, norm weight) is issued before the first use: one round trip
-        float4 v[V4], w[V4];
-        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < V4; ++j) {
-            const int idx = (j * DK_THREADS + tid) * 4;
-            v[j] = idx < n ? __ldcg(reinterpret_cast<const float4*>(A + idx)) : z;
-            w[j] = idx < n && B ? __ldcg(reinterpret_cast<const float4*>(B + idx)) : z;
-        }
-        if (B) {
-#pragma unroll
-            for (int j = 0; j < V4; ++j) {
-                v[j].x = __fadd_rn(v[j].x, w[j].x); v[j].y = __fadd_rn(v[j].y, w[j].y);
-                v[j].z = __fadd_rn(v[j].z, w[j].z); v[j].w = __fadd_rn(v[j].w, w[j].w);
-            }
-        }
-        float m = 0.f;
-        if (norm_w) {
-#pragma unroll
-            for (int j = 0; j < V4; ++j) {
-                const int idx = (j * DK_THREADS + tid) * 4;
-                w[j] = idx < n ? __ldg(reinterpret_cast<const float4*>(norm_w + idx)) : z;
-            }
-            // this CTA's slice of the new residual stream (whole float4s; every CTA holds the same values)
-            const int q4 = n / 4, lo = out ? range_lo(q4, gridDim.x, blockIdx.x) : 0, hi = out ? range_lo(q4, gridDim.x, blockIdx.x + 1) : 0;
-            double ss = 0.0;
-#pragma unroll
-            for (int j = 0; j < V4; ++j) {
-                const int i4 = j * DK_THREADS + tid;
-                if (i4 >= lo && i4 < hi) *reinterpret_cast<float4*>(out + i4 * 4) = v[j];
-                ss += double(v[j].x) * v[j].x + double(v[j].y) * v[j].y + double(v[j].z) * v[j].z + double(v[j].w) * v[j].w;
-            }
-            ss = dk_block_sum(ss, red, tid);
-            const float inv = float(1.0 / sqrt(ss / n + double(eps)));
-#pragma unroll
-            for (int j = 0; j < V4; ++j) {
-                v[j] = norm4(v[j], inv, w[j]);
-                m = fmaxf(m, absmax4(v[j]));
-            }
-            m = dk_block_max(m, redf, tid);
-        } else {
-            m = __uint_as_float(__ldcg(amax_bits));
-        }
-        k = split_shift(m, nl);
-        const Pow2 sc = make_pow2(k);
-#pragma unroll
-        for (int j = 0; j < V4; ++j) {
-            const int idx = (j * DK_THREADS + tid) * 4;
-            if (idx < n) limbs4(v[j], sc, a.lim, a.n_pad, idx);
-        }
-    } else {  // longer vectors (no residual stream is that long: the host keeps such shapes off this kernel)
-        k = split_shift(__uint_as_float(__ldcg(amax_bits)), nl);
-        const Pow2 sc = make_pow2(k);
-#pragma unroll 2
-        for (int i = tid * 4; i < n; i += DK_THREADS * 4)
-            limbs4(__ldcg(reinterpret_cast<const float4*>(A + i)), sc, a.lim, a.n_pad, i);
-    }
-    dk_sync();
-    if (sd_mask & 1) limb_sums_w<32, false>(a, 0, n / 32);
-    if (sd_mask & 2) limb_sums_w<16, false>(a, 0, n / 16);
-    dk_sync();
-    return pow2_neg(k);
-}
-
-// The FFN activation when its limbs do not fit in shared memory: the CTAs convert 256-value blocks of it (equal
-// ranges) into global memory - limbs [4][n_pad], then the sub-block sums, the layout of ActSmem - and meet at a grid
-// barrier; ffn_down then reads the limbs through L2. max|src| is known (amax_bits). Returns inv_scale = 2^-k.
-__device__ __noinline__ float convert_act_global(const float* src, int n, const unsigned* amax_bits, int nl, const ActSmem g, int sd_mask) {
-    const int tid = threadIdx.x, nb = n / 256;
-    const int b0 = range_lo(nb, gridDim.x, blockIdx.x), b1 = range_lo(nb, gridDim.x, blockIdx.x + 1);
-    const int k = split_shift(__uint_as_float(__ldcg(amax_bits)), nl);
+// One warp splits 256-block b of a vector: lane holds its values 8*lane .. 8*lane+7 in v0, v1. Writes limbs, sub-block
+// sums (shuffles over the 2 / 4 neighbouring lanes that hold the rest of a sub-block; the sums of two limbs travel in
+// the halves of one word: |sum of 32 int8| < 2^12) and the block's scale. Every lane of the warp must call this together.
+__device__ __forceinline__ void split_block(const float4& v0, const float4& v1, const int b, const int nl, const ActSmem& a,
+                                            const int sd_mask, const int lane) {
+    float m = fmaxf(absmax4(v0), absmax4(v1));
+    m = warp_max(m);
+    const int k = split_shift(m, nl);
     const Pow2 sc = make_pow2(k);
+    uint32_t w0[4], w1[4];
+    limb_words(v0, sc, w0);
+    limb_words(v1, sc, w1);
+    const int idx = b * 256 + lane * 8;
+#pragma unroll
+    for (int l = 0; l < 4; ++l) *reinterpret_cast<uint2*>(a.lim + l * a.n_pad + idx) = make_uint2(w0[l], w1[l]);
+    if (sd_mask) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // limbs 2h and 2h+1 together
+            const int sa = __dp4a(int(w1[2 * h]), 0x01010101, __dp4a(int(w0[2 * h]), 0x01010101, 0));
+            const int sb = __dp4a(int(w1[2 * h + 1]), 0x01010101, __dp4a(int(w0[2 * h + 1]), 0x01010101, 0));
+            int pk = sa + (sb << 16);  // (the low half may borrow from the high one: undone when they are taken apart)
+            const int p16 = pk + __shfl_xor_sync(0xffffffffu, pk, 1);
+            const int p32 = p16 + __shfl_xor_sync(0xffffffffu, p16, 2);
+#pragma unroll
+            for (int wd = 0; wd < 2; ++wd) {
+                if (!(sd_mask & (wd ? 1 : 2))) continue;
+                const int pw = wd ? p32 : p16, per = wd ? 8 : 16, si = wd ? lane >> 2 : lane >> 1;
+                if ((lane & (wd ? 3 : 1)) != 0) continue;
+                int8_t* sd = wd ? a.sd32 : a.sd16;
+                const int s_lo = int(short(pw & 0xFFFF)), s_hi = (pw - s_lo) >> 16;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int sum = e ? s_hi : s_lo, l = 2 * h + e;
+                    const int lo = ((sum + 128) & 255) - 128;
+                    sd[(b * 8 + l) * per + si] = int8_t(lo);
+                    sd[(b * 8 + 4 + l) * per + si] = int8_t((sum - lo) >> 8);
+                }
+            }
+        }
+    }
+    if (lane == 0) a.bscale[b] = pow2_neg(k);
+}
+
+// Activation of the next matvec -> split blocks [b0, b1) of the vector A (+ B when B is not null: the two buffers of
+// partial sums a row-parallel matvec left, the first of which already holds the residual stream), read through L2
+// (written by other CTAs before the last barrier); warp w takes blocks b0 + w, b0 + w + 16, ...
+//  * NORM (the residual stream in front of attn_norm / ffn_norm / output_norm): the blocks of (A + B) * norm_w are
+//    split and the factor 1 / sqrt(mean(x^2) + eps) of the RMSNorm (src/ops.cpp:155-160 of the reference, sum of squares
+//    in double) is returned for the matvec to apply to its row sums: no block has to wait for the sum over the vector.
+//    CTA c also stores its slice of A + B to `out` (when not null), the residual stream the next row-parallel matvec
+//    adds to.
+//  * otherwise the blocks of A are split as they are; returns 1.
+// Ends with a CTA barrier: the limbs are visible to every warp.
+template <bool NORM>
+__device__ __noinline__ float convert_act(const float* A, const float* B, float* out, const int n, const int b0, const int b1,
+                                          const float* norm_w, const float eps, const int nl, const ActSmem a, double* red,
+                                          const int sd_mask) {
+    constexpr int NB = NORM ? 2 : 3;  // blocks of a warp in flight together: every load of a pass is issued before the first use
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q4 = n / 4, lo = out ? range_lo(q4, gridDim.x, blockIdx.x) : 0, hi = out ? range_lo(q4, gridDim.x, blockIdx.x + 1) : 0;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    double ss = 0.0;
 #pragma unroll 1
-    for (int i = b0 * 256 + tid * 4; i < b1 * 256; i += DK_THREADS * 4)
-        limbs4(__ldcg(reinterpret_cast<const float4*>(src + i)), sc, g.lim, g.n_pad, i);
-    dk_sync();  // this CTA's limbs are visible to its own threads (read back through L2: the addresses are reused every layer)
-    if (sd_mask & 1) limb_sums_w<32, true>(g, b0 * 8, b1 * 8);
-    if (sd_mask & 2) limb_sums_w<16, true>(g, b0 * 16, b1 * 16);
-    return pow2_neg(k);
+    for (int bb = b0 + warp; bb < b1; bb += NB * DK_WARPS) {
+        float4 v[NB][2], w[NB][2];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int b = bb + j * DK_WARPS;
+            const bool on = b < b1;
+            const float4* pa = reinterpret_cast<const float4*>(A + size_t(b) * 256) + lane * 2;
+            v[j][0] = on ? __ldcg(pa) : z;
+            v[j][1] = on ? __ldcg(pa + 1) : z;
+            if (NORM) {
+                const float4* pb = reinterpret_cast<const float4*>(B + size_t(b) * 256) + lane * 2;
+                w[j][0] = on && B ? __ldcg(pb) : z;
+                w[j][1] = on && B ? __ldcg(pb + 1) : z;
+            }
+        }
+        if (NORM) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int b = bb + j * DK_WARPS;
+                const bool on = b < b1;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float4& x = v[j][h];
+                    x.x = __fadd_rn(x.x, w[j][h].x); x.y = __fadd_rn(x.y, w[j][h].y);
+                    x.z = __fadd_rn(x.z, w[j][h].z); x.w = __fadd_rn(x.w, w[j][h].w);
+                    w[j][h] = on ? __ldg(reinterpret_cast<const float4*>(norm_w + size_t(b) * 256) + lane * 2 + h) : z;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int b = bb + j * DK_WARPS;
+            if (b >= b1) continue;  // (warp-uniform)
+            if (NORM) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float4& x = v[j][h];
+                    const int i4 = b * 64 + lane * 2 + h;
+                    if (i4 >= lo && i4 < hi) *reinterpret_cast<float4*>(out + size_t(i4) * 4) = x;
+                    ss += double(x.x) * x.x + double(x.y) * x.y + double(x.z) * x.z + double(x.w) * x.w;
+                    x.x = __fmul_rn(x.x, w[j][h].x); x.y = __fmul_rn(x.y, w[j][h].y);
+                    x.z = __fmul_rn(x.z, w[j][h].z); x.w = __fmul_rn(x.w, w[j][h].w);
+                }
+            }
+            split_block(v[j][0], v[j][1], b, nl, a, sd_mask, lane);
+        }
+    }
+    if (NORM) {
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+    }
+    dk_sync();
+    float inv = 1.0f;
+    if (NORM) {
+        double S = 0.0;
+#pragma unroll
+        for (int i = 0; i < DK_WARPS; ++i) S += red[i];  // fixed order
+        inv = float(rsqrt_d(S / n + double(eps)));
+    }
+    return inv;
 }
 
 // Tensor parallelism: after an exchange every rank holds, in its own copy of the set, the two partial-sum vectors of
@@ -509,7 +521,7 @@ __device__ __noinline__ void ring_drain(Ring& r, const RingShared* rs, int warp)
 
 // ---------------------------------------------------------------- one matvec phase
 
-enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU_AMAX = 2, DK_EPI_LOGITS = 3 };
+enum { DK_EPI_STORE = 0, DK_EPI_PART = 1, DK_EPI_SILU = 2, DK_EPI_LOGITS = 3 };
 
 struct PhaseSmem {
     Sched sched;
@@ -517,7 +529,7 @@ struct PhaseSmem {
     float* red;      // [DK_WARPS][slots][16] row sums of each warp's share, per row tile it touches
     float* outs;     // [cta_tiles][16] row sums of the CTA's share
     double* red8;    // [DK_WARPS]
-    int* flags;      // [4]: dead (2), block amax bits (3)
+    int* flags;      // [4]: attention: last-arriver flag (0); dead (2)
 };
 
 template <int TYPE, bool CG>
@@ -536,7 +548,7 @@ __device__ void run_units(const DkParams& p, const int upt, const int wA, const 
     for (int u = wA; u < wB; ++u) {
         Unit<TYPE> cur;
         load_unit(cur, dk_smem_ptr(ring_front(p, rg, UB, &s.flags[2])), lane);
-        compute_unit<false, CG>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg);
+        compute_unit<false, CG>(cur, b, s.act.lim, s.act.n_pad, sd, lane, a, dbg, s.act.bscale);
         __syncwarp();  // every lane has its fragments of the unit in registers and has used them
         ring_pop(rg, UB, lane);
         if (++b == upt || u + 1 == wB) {
@@ -560,8 +572,7 @@ __device__ void run_units(const DkParams& p, const int upt, const int wA, const 
 struct EpiArgs {
     int epi;
     float* y;               // STORE / SILU: output vector
-    float inv_scale;
-    unsigned* amax_out;     // SILU: where max|y| goes
+    float inv;              // factor of the row sums: 1 / rms of the RMSNorm in front of the matvec, or 1
     int xset;               // PART: set of partial-sum buffers
     const float* x_old;     // PART: the residual stream the first contributor of a tile adds (null: nothing is added)
 };
@@ -569,7 +580,7 @@ struct EpiArgs {
 // y = W * act for one matrix; the activation limbs are already in shared memory (GACT: in global memory, written by other
 // CTAs before the last barrier, read through L2). Ends with this CTA's share written:
 //   DK_EPI_STORE      y[row] = sum                       (whole tiles)
-//   DK_EPI_SILU_AMAX  y[o] = silu(gate) * up, max|y|      (whole tiles of a gate|up pair)
+//   DK_EPI_SILU       y[o] = silu(gate) * up              (whole tiles of a gate|up pair)
 //   DK_EPI_PART       partial sums of a balanced matrix: the CTA that holds a tile's first unit writes x_old + sum to
 //                     vector 0, the one that holds its last unit (when it is another CTA) its sum to vector 1 of this
 //                     rank's pair in set `xset`; a CTA that holds the whole tile writes zeros to vector 1. Stored on every
@@ -580,7 +591,13 @@ __device__ __forceinline__ void matvec_phase(const DkParams& p, const int type, 
                                           const PhaseSmem& s, bool after_matrix, bool gact) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, upt = p.kind[kind].upt, rows = p.kind[kind].rows;
     const int2 rc = s.sched.cta[kind], rw = s.sched.warp[kind];
-    if (tid == 0) s.flags[3] = 0;
+    // the residual stream the first contributor of a row tile adds: asked for now, used after the units
+    float xo = 0.f;
+    if (ea.x_old && rc.x < rc.y) {
+        const int Xf0 = rc.x / upt;
+        const int64_t r = 16 * int64_t(Xf0) + tid;
+        if (tid < ((rc.y - 1) / upt - Xf0 + 1) * 16 && r < rows && rc.x <= (Xf0 + (tid >> 4)) * upt) xo = __ldcg(ea.x_old + r);
+    }
     // the reduction buffers may still be read by the previous matrix of the same phase (q, k, v); the first matrix
     // comes straight from the conversion, which ends with a CTA barrier
     if (after_matrix) dk_sync();
@@ -613,26 +630,19 @@ __device__ __forceinline__ void matvec_phase(const DkParams& p, const int type, 
             v += __shfl_xor_sync(0xffffffffu, v, 4);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
             v += __shfl_xor_sync(0xffffffffu, v, 1);
-            if (w == 0) s.outs[(pr >> 3) * 16 + row] = v * ea.inv_scale;
+            if (w == 0) s.outs[(pr >> 3) * 16 + row] = v * ea.inv;
         }
     }
     dk_sync();
-    if (ea.epi == DK_EPI_SILU_AMAX) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
-        float mx = 0.f;
+    if (ea.epi == DK_EPI_SILU) {  // rows g = gate, g+8 = up of output row 8X+g (SwiGLU, src/model.cpp:222-225 of the reference)
 #pragma unroll 1
         for (int e = tid; e < ntl * 8; e += DK_THREADS) {
             const int64_t o = 8 * int64_t(Xf) + e;
             if (o < rows / 2) {
                 const float v0 = s.outs[(e >> 3) * 16 + (e & 7)], v1 = s.outs[(e >> 3) * 16 + (e & 7) + 8];
-                const float act = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
-                ea.y[o] = act;
-                mx = fmaxf(mx, fabsf(act));
+                ea.y[o] = __fmul_rn(__fdiv_rn(v0, 1.0f + expf(-v0)), v1);
             }
         }
-        mx = warp_max(mx);
-        if (lane == 0 && mx > 0.f) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
-        dk_sync();
-        if (tid == 0) atomicMax(ea.amax_out, unsigned(s.flags[3]));
         return;
     }
 #pragma unroll 1
@@ -643,7 +653,7 @@ __device__ __forceinline__ void matvec_phase(const DkParams& p, const int type, 
         float v = s.outs[e];
         if (ea.epi == DK_EPI_PART) {
             const bool first = rc.x <= Xt * upt, last = rc.y >= (Xt + 1) * upt;
-            if (first && ea.x_old) v = __fadd_rn(__ldcg(ea.x_old + r), v);
+            if (first && ea.x_old) v = __fadd_rn(e == tid ? xo : __ldcg(ea.x_old + r), v);  // (a CTA has few row tiles: e == tid)
             const size_t pair = (size_t(ea.xset) * p.tp_size + p.tp_rank) * p.pv * p.E;  // this rank's vectors of the set
 #pragma unroll 1
             for (int q = 0; q < p.tp_size; ++q) {
@@ -666,24 +676,32 @@ __device__ __forceinline__ void matvec_phase(const DkParams& p, const int type, 
 // one warp per head, lane owns elements lane, lane+32, lane+64, lane+96.
 __device__ __forceinline__ void dk_head_norm_rope(const float* src, const float* w, const float2* cs, int rope_dim, float eps,
                                                   float* dst, int lane) {
-    float v[4];
+    float v[4], wn[4];
+    float2 c[2];  // cos / sin of this lane's rotation pairs: asked for together with the head, used last
+    const int half = rope_dim / 2;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) c[j] = lane + 32 * j < half ? __ldg(cs + lane + 32 * j) : make_float2(1.f, 0.f);
     double ss = 0.0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         v[j] = __ldcg(src + lane + 32 * j);
-        ss += double(v[j]) * v[j];
+        wn[j] = __ldg(w + lane + 32 * j);
     }
-    ss = warp_sum(ss);
-    const float inv = float(1.0 / sqrt(ss / DK_HD + double(eps)));
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __fmul_rn(__fmul_rn(v[j], inv), w[lane + 32 * j]);
+    for (int j = 0; j < 4; ++j) ss += double(v[j]) * v[j];
+    ss = warp_sum(ss);
+    const float inv = float(rsqrt_d(ss / DK_HD + double(eps)));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __fmul_rn(__fmul_rn(v[j], inv), wn[j]);
     __syncwarp();
-    const int half = rope_dim / 2;
-    for (int i = lane; i < half; i += 32) {
-        const float2 c = cs[i];
-        const float a = dst[i], b = dst[i + half];
-        dst[i] = __fsub_rn(__fmul_rn(a, c.x), __fmul_rn(b, c.y));
-        dst[i + half] = __fadd_rn(__fmul_rn(a, c.y), __fmul_rn(b, c.x));
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half) {
+            const float a = dst[i], b = dst[i + half];
+            dst[i] = __fsub_rn(__fmul_rn(a, c[j].x), __fmul_rn(b, c[j].y));
+            dst[i + half] = __fadd_rn(__fmul_rn(a, c[j].y), __fmul_rn(b, c[j].x));
+        }
     }
     __syncwarp();
 }
@@ -738,7 +756,7 @@ __device__ __forceinline__ void attn_prefetch(const DkParams& p, const int l, co
 // over its keys (DK_KT at a time, fetched while the heads are normalised), partial results to the scratch buffer; the
 // last split of a KV head to arrive combines them in split order and writes att (and max|att|).
 // Semantics: src/model.cpp:176-214 of the reference.
-__device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s, unsigned* amax_out) {
+__device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const AttnSmem& s) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c = blockIdx.x;
     const int pos = p.pos[p.ctl[0]], T = pos + 1, ns = attn_splits(p, T);
     if (c >= p.HKV * ns) return;
@@ -758,7 +776,6 @@ __device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const
     }
     if (tid >= DK_THREADS - DK_HD) s.vnew[tid - (DK_THREADS - DK_HD)] = __ldcg(p.qkv + QD + KD + kvh * DK_HD + tid - (DK_THREADS - DK_HD));
     if (tid < DK_MAXG) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
-    if (tid == 0) s.flags[3] = 0;
     dk_sync();
     if (split == 0 && tid < DK_HD) {  // KV append (src/model.cpp:186-189): only row `pos` is written
         kc[size_t(pos) * KD + kvh * DK_HD + tid] = s.knew[tid];
@@ -779,40 +796,37 @@ __device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const
         }
         ring_wait<0>();
         dk_sync();
-        // scores: warp = (head, 32-key slot), lane = key; dimension order, multiply then add, as the CPU path does
-#pragma unroll 1
-        for (int w = warp; w < group * ((nk + 31) / 32); w += DK_WARPS) {
-            const int h = w % group, j = (w / group) * 32 + lane;
-            if (j < nk) {
-                float a = 0.f;
-                const float4* q = reinterpret_cast<const float4*>(s.qs + h * DK_HD);
-                const float4* kr = reinterpret_cast<const float4*>(s.Ks + j * DK_KS);
-#pragma unroll 8
-                for (int i = 0; i < DK_HD / 4; ++i) {
-                    const float4 qv = q[i], kv = kr[i];
-                    a = __fadd_rn(a, __fmul_rn(qv.x, kv.x));
-                    a = __fadd_rn(a, __fmul_rn(qv.y, kv.y));
-                    a = __fadd_rn(a, __fmul_rn(qv.z, kv.z));
-                    a = __fadd_rn(a, __fmul_rn(qv.w, kv.w));
-                }
-                s.Ps[h * DK_KT + j] = __fmul_rn(a, p.scale);
-            }
-        }
-        dk_sync();
-        if (warp < group) {  // softmax bookkeeping of head `warp` over the tile
-            float sc[(DK_KT + 31) / 32], mx = -INFINITY;
+        // scores and softmax bookkeeping of head `warp` over the tile: lane = key (a tile has up to two keys per lane);
+        // the 128 products of a score are added in four interleaved partial sums
+        if (warp < group) {
+            constexpr int NP = (DK_KT + 31) / 32;
+            float sc[NP], mx = -INFINITY;
+            const float4* q = reinterpret_cast<const float4*>(s.qs + warp * DK_HD);
 #pragma unroll
-            for (int q = 0; q < (DK_KT + 31) / 32; ++q) {
-                const int j = q * 32 + lane;
-                sc[q] = j < nk ? s.Ps[warp * DK_KT + j] : -INFINITY;
-                mx = fmaxf(mx, sc[q]);
+            for (int pass = 0; pass < NP; ++pass) {
+                const int j = pass * 32 + lane;
+                sc[pass] = -INFINITY;
+                if (pass * 32 < nk) {  // (warp-uniform)
+                    const float4* kr = reinterpret_cast<const float4*>(s.Ks + min(j, nk - 1) * DK_KS);
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 8
+                    for (int i = 0; i < DK_HD / 4; ++i) {
+                        const float4 qv = q[i], kv = kr[i];
+                        a0 = fmaf(qv.x, kv.x, a0);
+                        a1 = fmaf(qv.y, kv.y, a1);
+                        a2 = fmaf(qv.z, kv.z, a2);
+                        a3 = fmaf(qv.w, kv.w, a3);
+                    }
+                    if (j < nk) sc[pass] = __fmul_rn((a0 + a1) + (a2 + a3), p.scale);
+                }
+                mx = fmaxf(mx, sc[pass]);
             }
             const float m_old = m_s[warp], m_new = fmaxf(m_old, warp_max(mx));
             float sum = 0.f;
 #pragma unroll
-            for (int q = 0; q < (DK_KT + 31) / 32; ++q) {
-                const int j = q * 32 + lane;
-                const float pj = j < nk ? expf(sc[q] - m_new) : 0.f;
+            for (int pass = 0; pass < NP; ++pass) {
+                const int j = pass * 32 + lane;
+                const float pj = j < nk ? expf(sc[pass] - m_new) : 0.f;
                 if (j < nk) s.Ps[warp * DK_KT + j] = pj;
                 sum += pj;
             }
@@ -862,7 +876,6 @@ __device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const
     // copies in a rolled loop: one round trip for all of them), then thread (head, dimension) walks the splits in order.
     const float* base = p.attn_part + size_t(kvh) * p.nsplit * group * DK_PS;
     float* stage = s.Ks;  // [ns][4][DK_PS]
-    float mx = 0.f;
 #pragma unroll 1
     for (int hq = 0; hq < group; hq += 4) {
         const int nh = min(4, group - hq), chunks = nh * (DK_PS / 4);  // 16-byte pieces per split
@@ -889,21 +902,15 @@ __device__ __forceinline__ void attn_phase(const DkParams& p, const int l, const
                 Lsum = fmaf(ps[q * 4 * DK_PS + DK_HD + 1], w, Lsum);
                 o = fmaf(ps[q * 4 * DK_PS + od], w, o);
             }
-            const float r = o / Lsum;
-            p.att[(kvh * group + hq + oh) * DK_HD + od] = r;
-            mx = fmaxf(mx, fabsf(r));
+            p.att[(kvh * group + hq + oh) * DK_HD + od] = o / Lsum;
         }
     }
-    mx = warp_max(mx);
-    if (lane == 0 && mx > 0.f) atomicMax(reinterpret_cast<unsigned*>(&s.flags[3]), __float_as_uint(mx));
-    dk_sync();
-    if (tid == 0) atomicMax(amax_out, unsigned(s.flags[3]));
 }
 
 // ---------------------------------------------------------------- the step
 
 __host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
-    const size_t act = size_t(4) * (n_max + 32) + size_t(n_max / 256) * 192, attn = size_t(DK_ATTN_FLOATS) * 4;
+    const size_t act = dk_act_bytes(n_max), attn = size_t(DK_ATTN_FLOATS) * 4;
     return ((act > attn ? act : attn) + 15) / 16 * 16;
 }
 // grid barriers of one launch (the arrival counter runs on from launch to launch)
@@ -989,9 +996,6 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
     int* dead = &s.flags[2];
     const unsigned step = p.ctl[0], epoch = p.ctl[2];
     unsigned nb = epoch * dk_barriers_per_launch(p) * gridDim.x;  // arrivals before this launch
-    unsigned* const amax_base = p.amax + (epoch & 1u) * 2 * p.n_layer;
-    if (blockIdx.x == 0)  // the other half of the amax slots: untouched by this launch, zero for the next one
-        for (int i = tid; i < 2 * p.n_layer; i += DK_THREADS) p.amax[((epoch + 1) & 1u) * 2 * p.n_layer + i] = 0u;
 
     embed_token(p, p.xbuf, step);
     bool ok = grid_barrier(p, nb, dead);
@@ -1011,41 +1015,42 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
         const bool head = stage + 1 == n_stages;
         const int l = head ? p.n_layer : stage >> 2, k = head ? 4 : stage & 3;
         const float* const layer_norms = p.norms + size_t(l) * p.norm_stride;  // (not read for the head)
-        unsigned* amax = amax_base + 2 * (head ? 0 : l);
         if (k == 0) dk_stamp(p, l, 0);
+        const bool pc = p.prof_cta && l == p.prof_layer;  // diagnostics: every CTA stamps this layer's barriers
         if (k == 1) {  // attention sits between q|k|v and attn_output
-            attn_phase(p, l, as, amax);
+            attn_phase(p, l, as);
             dk_stamp(p, l, 4);
-            if (!(ok = grid_barrier(p, nb, dead))) break;
+            if (!(ok = grid_barrier(p, nb, dead, false, 0, pc ? 1 : -1))) break;
             dk_stamp(p, l, 5);
         }
         // the stage's activation: where it comes from, how it is normalised, which matrices consume it
         const float *src = nullptr, *norm_w = nullptr;
-        const unsigned* amax_in = nullptr;
-        EpiArgs ea{DK_EPI_PART, nullptr, 0.f, nullptr, int(xn & 1u), nullptr};
+        EpiArgs ea{DK_EPI_PART, nullptr, 1.0f, int(xn & 1u), nullptr};
         int n = p.E, nl = 4, nm = 1;
         int i0 = p.n_qkv, kind0 = 3;  // the stage's first matrix: index within the layer, kind
         bool resid = true;
         switch (k) {
             case 0: norm_w = layer_norms; nl = p.nl_qkv; i0 = 0; kind0 = 0; nm = p.n_qkv; ea.epi = DK_EPI_STORE; ea.y = p.qkv; break;
-            case 1: resid = false; src = p.att; n = p.H * DK_HD; amax_in = amax; nl = p.nl_wo; break;
-            case 2: norm_w = layer_norms + p.E; nl = p.nl_gu; i0 = p.n_qkv + 1; kind0 = 4; ea.epi = DK_EPI_SILU_AMAX; ea.y = p.act; ea.amax_out = amax + 1; break;
-            case 3: resid = false; src = p.act; n = p.F; amax_in = amax + 1; nl = p.nl_down; i0 = p.n_qkv + 2; kind0 = 5; break;
+            case 1: resid = false; src = p.att; n = p.H * DK_HD; nl = p.nl_wo; break;
+            case 2: norm_w = layer_norms + p.E; nl = p.nl_gu; i0 = p.n_qkv + 1; kind0 = 4; ea.epi = DK_EPI_SILU; ea.y = p.act; break;
+            case 3: resid = false; src = p.act; n = p.F; nl = p.nl_down; i0 = p.n_qkv + 2; kind0 = 5; break;
             default: norm_w = p.output_norm; ea.epi = DK_EPI_LOGITS; i0 = 0; kind0 = 6; break;
         }
         int need = 0;
         for (int i = 0; i < nm; ++i) need |= sd_need(p.wtype[l][i0 + i]);
         const bool gact = GACT && k == 3;
-        if (gact) {
+        const int nblk = n / 256;
+        if (gact) {  // the CTAs split equal ranges of blocks into global memory and meet; ffn_down reads them through L2
             s.act = act_at(p.gact, n);
-            ea.inv_scale = convert_act_global(src, n, amax_in, nl, s.act, need);
+            convert_act<false>(src, nullptr, nullptr, n, range_lo(nblk, gridDim.x, blockIdx.x), range_lo(nblk, gridDim.x, blockIdx.x + 1),
+                               nullptr, p.eps, nl, s.act, s.red8, need);
             if (!(ok = grid_barrier(p, nb, dead))) break;
         } else {
             s.act = act_at(lim_smem, n);
             if (!resid) {
-                ea.inv_scale = convert_act(src, nullptr, nullptr, n, nullptr, p.eps, amax_in, nl, s.act, s.red8, s.red, need);
+                convert_act<false>(src, nullptr, nullptr, n, 0, nblk, nullptr, p.eps, nl, s.act, s.red8, need);
             } else if (pending < 0) {  // the embedding: nothing to add, the residual stream is where it is
-                ea.inv_scale = convert_act(p.xbuf + cur * p.E, nullptr, nullptr, n, norm_w, p.eps, nullptr, nl, s.act, s.red8, s.red, need);
+                ea.inv = convert_act<true>(p.xbuf + cur * p.E, nullptr, nullptr, n, 0, nblk, norm_w, p.eps, nl, s.act, s.red8, need);
             } else {
                 // the new residual stream: the partial sums of the last row-parallel matvec (its first buffer carries the
                 // old stream); it goes to the other half of xbuf, after the last layer to p.x
@@ -1054,9 +1059,9 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
                 if (tp) {
                     reduce_ranks(p, set, xnew);
                     if (!(ok = grid_barrier(p, nb, dead))) break;
-                    ea.inv_scale = convert_act(xnew, nullptr, nullptr, n, norm_w, p.eps, nullptr, nl, s.act, s.red8, s.red, need);
+                    ea.inv = convert_act<true>(xnew, nullptr, nullptr, n, 0, nblk, norm_w, p.eps, nl, s.act, s.red8, need);
                 } else {
-                    ea.inv_scale = convert_act(set, set + p.E, xnew, n, norm_w, p.eps, nullptr, nl, s.act, s.red8, s.red, need);
+                    ea.inv = convert_act<true>(set, set + p.E, xnew, n, 0, nblk, norm_w, p.eps, nl, s.act, s.red8, need);
                 }
                 cur ^= 1;
             }
@@ -1073,11 +1078,11 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
         if (!head) dk_stamp(p, l, sb + 2);
         if (k == 0) attn_prefetch(p, l, as);
         if (k == 1 || k == 3 || (head && tp)) {  // row-parallel matvecs and the logits meet all ranks
-            ok = grid_barrier(p, nb, dead, tp, xn);
+            ok = grid_barrier(p, nb, dead, tp, xn, pc ? (k == 1 ? 2 : 4) : -1);
             pending = int(xn & 1u);
             ++xn;
         } else if (!head) {
-            ok = grid_barrier(p, nb, dead);
+            ok = grid_barrier(p, nb, dead, false, 0, pc ? (k == 0 ? 0 : 3) : -1);
         }
         if (!head) dk_stamp(p, l, sb + 3);
     }
@@ -1138,5 +1143,7 @@ int decode_threads() { return DK_THREADS; }
 int decode_warps() { return DK_WARPS; }
 int decode_max_split() { return DK_MAXSPLIT; }
 int decode_part_stride() { return DK_PS; }
+size_t decode_act_bytes(int n) { return dk_act_bytes(n); }
+
 
 }  // namespace elb

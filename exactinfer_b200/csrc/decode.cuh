@@ -67,7 +67,9 @@ struct DkParams {
     int slots;              // row-tile slots per warp in the reduction buffer
     int cta_tiles;          // most row tiles a CTA's share of a matrix can touch
     int n_max;              // longest activation vector
-    unsigned long long* prof;  // diagnostics (ELB_DK_PROF=1): [n_layer][16] nanosecond stamps of CTA 0, else null
+    unsigned long long* prof;  // diagnostics (ELB_DK_PROF=1): [n_layer][32] nanosecond stamps of CTA 0, else null
+    unsigned long long* prof_cta;  // diagnostics: [CTAs][16] stamps of every CTA at the barriers of layer prof_layer (arrival, release)
+    int prof_layer;
 };
 
 // one token at the position / token id stored on the device (step ctl[0] of the arrays); nothing to reset between launches.
@@ -80,5 +82,6 @@ int decode_threads();
 int decode_warps();
 int decode_max_split();    // most key splits of one KV head
 int decode_part_stride();  // floats per (key split, head) of attn_part
+size_t decode_act_bytes(int n);  // bytes of a split activation of n values (limbs, sub-block sums, block scales)
 
 }  // namespace elb

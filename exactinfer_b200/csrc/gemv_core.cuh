@@ -91,9 +91,12 @@ struct DbgOut {
 };
 
 // ---- Q4_K: one 256-block of 16 rows
+// bscale (optional): the activation was split block by block, 256-block b with its own power-of-two scale bscale[b];
+// the block's sums are multiplied by it before they join the row sums (null: one scale for the whole vector, applied
+// by the caller at the end).
 template <bool DBG, bool CG = false>
 __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, const int8_t* lim, int n_pad,
-                                             const int8_t* sd, int lane, Acc& a, const DbgOut& dbg) {
+                                             const int8_t* sd, int lane, Acc& a, const DbgOut& dbg, const float* bscale = nullptr) {
     const int g = lane >> 2, t = lane & 3;
     const int8_t* lcol = lim + (g & 3) * n_pad + b * QK_K + 8 * t;
     // 6-bit scales and mins of rows g and g+8 as packed bytes (q4k_scale_min of the reference, src/quant.h:44-52)
@@ -136,7 +139,8 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) I[i] += I16[i] >> 4;
-    const float dg = h2f_bits(u.h0.x & 0xFFFFu), dh = h2f_bits(u.h1.x & 0xFFFFu);
+    const float xs = bscale ? ld_act<CG>(bscale + b) : 1.0f;
+    const float dg = h2f_bits(u.h0.x & 0xFFFFu) * xs, dh = h2f_bits(u.h1.x & 0xFFFFu) * xs;
     a.acc[0] += dg * fmaf(float(I[1]), 256.0f, float(I[0]));
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
     // min term: J[col] = sum over the 8 sub-blocks of m * (digit `col>>2` of the limb sum S of limb `col&3`)
@@ -144,7 +148,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
     const uint32_t b0 = ld_act<CG>(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 8 + 4 * (t & 1)));
     int J[4];
     mma_u8s8_k16(J, a0, a1, b0);
-    const float ng = h2f_bits(u.h0.x >> 16), nh = h2f_bits(u.h1.x >> 16);
+    const float ng = h2f_bits(u.h0.x >> 16) * xs, nh = h2f_bits(u.h1.x >> 16) * xs;
     a.accm[0] += ng * fmaf(float(J[1]), 256.0f, float(J[0]));
     a.accm[1] += nh * fmaf(float(J[3]), 256.0f, float(J[2]));
     if (DBG) {
@@ -169,7 +173,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q4_K>& u, int b, con
 // offset -32 * sum sc*S comes from one extra MMA over the limb sums S of the 16-wide sub-blocks.
 template <bool DBG, bool CG = false>
 __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, const int8_t* lim, int n_pad,
-                                             const int8_t* sd, int lane, Acc& a, const DbgOut& dbg) {
+                                             const int8_t* sd, int lane, Acc& a, const DbgOut& dbg, const float* bscale = nullptr) {
     const int g = lane >> 2, t = lane & 3;
     const int8_t* lcol = lim + (g & 3) * n_pad + b * QK_K + 4 * t;
     int I[4] = {0, 0, 0, 0};
@@ -210,7 +214,8 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
             }
         }
     }
-    const float dg = h2f_bits(u.dd & 0xFFFFu), dh = h2f_bits(u.dd >> 16);
+    const float xs = bscale ? ld_act<CG>(bscale + b) : 1.0f;
+    const float dg = h2f_bits(u.dd & 0xFFFFu) * xs, dh = h2f_bits(u.dd >> 16) * xs;
     a.acc[0] += dg * fmaf(float(I[1]), 256.0f, float(I[0]));
     a.acc[1] += dh * fmaf(float(I[3]), 256.0f, float(I[2]));
     const uint32_t b0 = ld_act<CG>(reinterpret_cast<const uint32_t*>(sd + (b * 8 + g) * 16 + 4 * t));
@@ -239,8 +244,9 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q6_K>& u, int b, con
 // ---- Q8_0: four 32-blocks of 16 rows; fp16 scale per block, so fp32 after every MMA
 template <bool DBG, bool CG = false>
 __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, const int8_t* lim, int n_pad,
-                                             const int8_t*, int lane, Acc& a, const DbgOut& dbg) {
+                                             const int8_t*, int lane, Acc& a, const DbgOut& dbg, const float* bscale = nullptr) {
     const int g = lane >> 2, t = lane & 3;
+    const float xs = bscale ? ld_act<CG>(bscale + (b >> 1)) : 1.0f;  // a unit is half a 256-block
     const int8_t* lcol = lim + (g & 3) * n_pad + b * (QK8_0 * Q8_GROUP) + 8 * t;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -249,7 +255,7 @@ __device__ __forceinline__ void compute_unit(const Unit<ELB_Q8_0>& u, int b, con
         int C[4];
         mma_s8s8_k32(C, q.x, q.z, q.y, q.w, bf.x, bf.y);
         const uint32_t d0w = i < 2 ? u.d0.x : u.d0.y, d1w = i < 2 ? u.d1.x : u.d1.y;
-        const float dg = h2f_bits((d0w >> (16 * (i & 1))) & 0xFFFFu), dh = h2f_bits((d1w >> (16 * (i & 1))) & 0xFFFFu);
+        const float dg = h2f_bits((d0w >> (16 * (i & 1))) & 0xFFFFu) * xs, dh = h2f_bits((d1w >> (16 * (i & 1))) & 0xFFFFu) * xs;
         a.acc[0] += dg * fmaf(i2f_small(C[1]), 256.0f, i2f_small(C[0]));
         a.acc[1] += dh * fmaf(i2f_small(C[3]), 256.0f, i2f_small(C[2]));
         if (DBG && t < 2) {

@@ -453,7 +453,10 @@ int setup_decode_kernel(Model* m) {
         Fmax = std::max(Fmax, int(d.f1 - d.f0));
     }
     const int E = c.n_embd, F = int(m->F), QD = m->H * 128, KD = m->HKV * 128;
-    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 5 * 4 * decode_threads() || c.n_layer > DK_MAX_LAYERS) return ELB_OK;
+    // (the residual stream is split two blocks per warp and pass, other activations three: longer ones go to global memory)
+    if (!quant || nq > 3 || E % 256 || F % 256 || QD % 256 || E > 2 * 256 * decode_warps() || QD > 3 * 256 * decode_warps() ||
+        c.n_layer > DK_MAX_LAYERS)
+        return ELB_OK;
     // the kernel takes the shape of each kind of matrix from layer 0: every layer must repeat it (block formats may differ)
     for (const Layer& L : m->layers) {
         const Layer& L0 = m->layers[0];
@@ -577,7 +580,7 @@ int setup_decode_kernel(Model* m) {
         p.n_max = std::max(E, QD);
         ELB_TRY(try_fit());
         if (fits) {
-            ELB_CUDA(cudaMalloc(&m->gact, act_bytes(Fmax) + 4 * 32));
+            ELB_CUDA(cudaMalloc(&m->gact, decode_act_bytes(Fmax)));
             p.gact = m->gact;
         }
     }
@@ -591,6 +594,9 @@ int setup_decode_kernel(Model* m) {
     if (m->use_mega && env_on("ELB_DK_PROF")) {
         ELB_CUDA(cudaMalloc(&p.prof, size_t(c.n_layer) * 32 * sizeof(unsigned long long)));
         ELB_CUDA(cudaMemset(p.prof, 0, size_t(c.n_layer) * 32 * sizeof(unsigned long long)));
+        ELB_CUDA(cudaMalloc(&p.prof_cta, size_t(di.sm_count) * 16 * sizeof(unsigned long long)));
+        ELB_CUDA(cudaMemset(p.prof_cta, 0, size_t(di.sm_count) * 16 * sizeof(unsigned long long)));
+        p.prof_layer = c.n_layer / 2;
     }
     return ELB_OK;
 }
@@ -1043,12 +1049,24 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
             layer_total += sum / m->cfg.n_layer / 1000.0;
         }
         std::fprintf(stderr, "[dk prof] layer total   %7.2f us\n", layer_total);
-        if (t[20])  // a build with -DELB_DK_UNITPROF: clocks of warp 0 of CTA 0 per unit, all launches so far
-            std::fprintf(stderr, "[dk prof] warp 0, clocks per unit: requests %.0f, waiting for the unit %.0f, arithmetic %.0f, row-tile ends %.0f (%llu units)\n",
-                         double(t[16]) / double(t[20]), double(t[17]) / double(t[20]), double(t[18]) / double(t[20]), double(t[19]) / double(t[20]), t[20]);
-        if (t[27]) std::fprintf(stderr, "[dk prof] per matrix of a layer (thread 0): own units %.0f clocks, waiting for the other warps %.0f, reduction and epilogue %.0f (%llu matrices)\n",
-                                double(t[24]) / double(t[27]), double(t[25]) / double(t[27]), double(t[26]) / double(t[27]), t[27]);
-
+        if (m->dk.prof_cta) {  // every CTA's arrival at and release from the five barriers of one layer
+            std::vector<unsigned long long> a(size_t(m->dk_grid) * 16);
+            cudaMemcpy(a.data(), m->dk.prof_cta, a.size() * 8, cudaMemcpyDeviceToHost);
+            static const char* bn[5] = {"after q|k|v", "after attention", "after attn_output", "after gate|up", "after ffn_down"};
+            for (int b = 0; b < 5; ++b) {
+                unsigned long long first = ~0ull, last = 0, rel_first = ~0ull, rel_last = 0;
+                int who = 0;
+                for (int cta = 0; cta < m->dk_grid; ++cta) {
+                    const unsigned long long arr = a[size_t(cta) * 16 + 2 * b], rel = a[size_t(cta) * 16 + 2 * b + 1];
+                    if (arr < first) first = arr;
+                    if (arr > last) { last = arr; who = cta; }
+                    if (rel < rel_first) rel_first = rel;
+                    if (rel > rel_last) rel_last = rel;
+                }
+                std::fprintf(stderr, "[dk prof] barrier %-18s arrivals spread over %6.2f us (last: CTA %d), first release %5.2f us and last release %5.2f us after the last arrival\n",
+                             bn[b], (last - first) / 1000.0, who, (double(rel_first) - double(last)) / 1000.0, (double(rel_last) - double(last)) / 1000.0);
+            }
+        }
     }
     m->last_rows = 1;
     return ELB_OK;
