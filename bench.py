@@ -39,17 +39,28 @@ INT8_PEAK_TOPS = 4500.0  # nominal dense int8
 # The measured-peaks file has no int8 figure. A library int8 GEMM (torch._int_mm, 8192^3 and 16384x8192x8192, 20 launches
 # by CUDA events) reached 2857-2890 TOP/s on this pool's B200s: the practical ceiling of the int8 tensor pipe here.
 INT8_PROBE_TOPS = 2870.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-MICRO_TRAFFIC = 14_121_301  # profiles/k_gemv_q4_k_2560x9728_microbench.txt (mean of 3 launches)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised under profiles/: the figures
+# live in profiles/dram_traffic.txt (JSON) next to the summaries they were read from (kernel -> workload -> bytes)
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+
+
+def traffic_table():
+    try:
+        return json.load(open(TRAFFIC_FILE))
+    except (OSError, ValueError):
+        return {}
+
+
+def micro_traffic():
+    t = traffic_table().get("k_gemv", {}).get("q4_k_2560x9728")
+    return None if t is None else float(t["bytes_per_launch"])
 
 
 def decode_traffic(spec):
-    """DRAM bytes per k_decode_step launch, scaled per layer from the 4- and 8-layer ncu captures of the 4B shape
-    (profiles/k_decode_step_qwen3-4b-q4_k_m_4_and_8_layers.txt): 321.7 MB for head, embedding row and fixed part,
-    65.1 MB per layer at positions ~517. None for shapes that were not captured."""
-    if spec.name != "qwen3-4b-q4_k_m":
-        return None
-    return 321.7e6 + 65.1e6 * spec.n_layer
+    """DRAM bytes per k_decode_step launch, scaled per layer from the captures on 4 and 8 layers of the same shape
+    (fixed part for head and embedding row + a per-layer part, at positions ~517). None for shapes not captured."""
+    t = traffic_table().get("k_decode_step", {}).get(spec.name)
+    return None if t is None else float(t["fixed_bytes"]) + float(t["per_layer_bytes"]) * spec.n_layer
 
 
 def metric_name(spec):
@@ -81,6 +92,7 @@ def parse_args():
     ap.add_argument("--workload", default="qwen3-4b-q4_k_m", choices=sorted(synth.SPECS))
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp32b", action="store_true", help="skip the 32B-shaped block (tp_32b) of the default workload")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--gemm-micro", action="store_true",
                     help="only time the prompt-chunk GEMM on the five linear shapes of the 4B model at 512 tokens")
@@ -301,6 +313,96 @@ def microbench_gemm(args):
     emit(json.dumps(out))
 
 
+# ---------------------------------------------------------------- tensor parallelism: parity first, then the 32B shape
+
+TP_REL_TOL, TP_LOGPROB_TOL = 2e-4, 3e-5  # the bars of tests/test_gpu_tp.py
+
+
+def tp_parity(e, make_tp, local):
+    """Every rank evaluates a small model (uneven FFN cut, vocabulary not a multiple of 16) through the tensor-parallel
+    backend - the persistent decode kernel with its peer-memory exchange, then the kernel-per-op path - and compares the
+    gathered logits with the CPU oracle's whole-model result: the check of tests/tp_gpu_worker.py, run where the
+    multi-GPU numbers are taken. Returns (worst relative logit error, worst |delta logprob|, ok)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+
+    spec = synth.Spec(name="tp-small", n_layer=3, n_embd=512, n_ff=1280, n_head=8, n_head_kv=2, n_vocab=2043,
+                      layout="q4_k_m", head_sigma=2e-5)
+    tens = list(synth.generate(spec, 33))
+    n_prompt, n_decode = 40, 5
+    cpu = ol.OracleModel(spec, tens, n_prompt + n_decode + 1)
+    toks = list(synth.lcg_tokens(n_prompt, spec.n_vocab))
+    ref = [cpu.eval(toks, 0)]
+    for i in range(n_decode):
+        toks.append(int(np.argmax(ref[-1])))
+        ref.append(cpu.eval(toks[-1:], n_prompt + i))
+    cpu.close()
+
+    def rel(a, b):
+        return float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max() / max(np.abs(b).max(), 1e-30))
+
+    def logprobs(l):
+        return l.astype(np.float64) - ol.logsumexp(l)
+
+    worst_rel = worst_lp = 0.0
+    paths = []
+    for no_mega in ("0", "1"):
+        os.environ["ELB_TP_NO_MEGA"] = no_mega
+        gpu = e.Backend(spec, tens, n_prompt + n_decode + 1, device=local, tp=make_tp())
+        got = [gpu.eval(toks[:n_prompt], 0)]
+        for i in range(n_decode):
+            got.append(gpu.eval(toks[n_prompt + i:n_prompt + i + 1], n_prompt + i))
+        paths.append(int(gpu.last_eval_stats()[1]))
+        gpu.close()
+        for g, r in zip(got, ref):
+            top = np.argsort(r)[-8:]
+            worst_rel = max(worst_rel, rel(g, r))
+            worst_lp = max(worst_lp, float(np.abs(logprobs(g)[top] - logprobs(r)[top]).max()))
+    os.environ.pop("ELB_TP_NO_MEGA", None)
+    return worst_rel, worst_lp, bool(worst_rel <= TP_REL_TOL and worst_lp <= TP_LOGPROB_TOL), paths
+
+
+def bench_32b(e, tp, local, world, dist, barrier, max_over_ranks, hbm, steps):
+    """The configuration tensor parallelism is meant for: the 32B shape, one sequence (2048-token prompt, then single-token
+    steps) and sixteen sequences (512-token prompts, then batched steps), on `world` GPUs."""
+    spec = synth.SPECS["qwen3-32b-q4_k_m"]
+    tens = list(synth.generate(spec, SEED, share_layers=True))
+    P1, PB, NB = 2048, 512, 16
+    out = {"workload": f"{spec.name}: {spec.n_layer} layers, E{spec.n_embd} F{spec.n_ff} H{spec.n_head}/{spec.n_head_kv}, "
+                       f"prompt {P1} then {steps} steps (batch 1); {NB} sequences with {PB}-token prompts then {steps} batched steps"}
+    model = e.Backend(spec, tens, P1 + steps + 4, device=local, tp=tp, max_batch=PROMPT, n_seq=NB)  # one upload for both parts
+    toks = synth.lcg_tokens(P1 + steps + 3 + NB, spec.n_vocab)
+    # ---- sixteen sequences: rows of a batch carry their own sequence and position; no logits are read back
+    for sq in range(NB):
+        model.eval_batch(toks[:PB], np.full(PB, sq, np.int32), np.arange(PB, dtype=np.int32), want_logits=False)
+    seq = np.arange(NB, dtype=np.int32)
+    model.eval_batch(toks[PB:PB + NB], seq, np.full(NB, PB, np.int32), want_logits=False)  # warm-up step
+    barrier()
+    dev = []
+    for i in range(steps):
+        model.eval_batch(toks[PB + i:PB + i + NB], seq, np.full(NB, PB + 1 + i, np.int32), want_logits=False)
+        dev.append(model.last_eval_stats()[0])
+    ms16 = max_over_ranks(float(np.sum(dev)))
+    out["batch16"] = {"decode_ms_per_step": ms16 / steps, "decode_tok_s": NB * steps / (ms16 / 1000.0),
+                      "note": "one row per sequence and step, head not evaluated (no logits read back)"}
+    # ---- batch 1 (sequence 0 again, from position 0)
+    barrier()
+    t1 = time.perf_counter()
+    model.eval(toks[:P1], 0, want_logits=False)
+    pp_s = max_over_ranks(time.perf_counter() - t1)
+    model.eval_steps(toks[P1:P1 + 3], P1)
+    barrier()
+    ms = max_over_ranks(model.eval_steps(toks[P1 + 3:P1 + 3 + steps], P1 + 3))
+    step_bytes = model.weight_bytes + model.kv_bytes_per_token * (P1 + 3 + steps / 2.0)
+    step_s = ms / steps / 1000.0
+    out["batch1"] = {"decode_ms_per_step": ms / steps, "decode_tok_s": steps / (ms / 1000.0), "prefill_tok_s": P1 / pp_s,
+                     "per_gpu_bytes_per_step": step_bytes, "per_gpu_gbs": step_bytes / step_s / 1e9,
+                     "hbm_frac_of_per_gpu_share": step_bytes / step_s / 1e9 / hbm,
+                     "kernels_per_step": model.last_eval_stats()[1] / float(steps)}
+    model.close()
+    return out
+
+
 # ---------------------------------------------------------------- our arm
 
 def pinned_array(e, n_floats):
@@ -330,11 +432,32 @@ def run_ours(args):
     spec = get_spec(args)
     tens, gen_s = model_tensors(spec)
     t0 = time.time()
-    tp = None
-    if world > 1:  # tensor parallel: rank 0 makes the NCCL id of the library's own communicator, all ranks join it
+    def make_tp():
+        """Tensor parallel: rank 0 makes the NCCL id of the library's own communicator, all ranks join it. An id serves
+        one communicator, so every model gets its own."""
+        if world == 1:
+            return None
         box = [e.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
-        tp = (rank, world, box[0])
+        return (rank, world, box[0])
+
+    tp = make_tp()
+    parity = None
+    if world > 1:  # correctness of the tensor-parallel paths on these GPUs, before anything is timed
+        r, lp, ok_tp, paths = tp_parity(e, make_tp, local)
+        flags = [None] * world
+        dist.all_gather_object(flags, (r, lp, ok_tp))
+        parity = {"rel": max(f[0] for f in flags), "logprob": max(f[1] for f in flags), "ok": all(f[2] for f in flags),
+                  "bars": {"rel": TP_REL_TOL, "logprob": TP_LOGPROB_TOL}, "kernels_per_step": paths,
+                  "against": "CPU oracle, whole model, every rank; persistent kernel and kernel-per-op path"}
+        if not parity["ok"]:
+            if rank == 0:
+                emit(json.dumps({"metric": metric_name(spec), "value": None, "n_gpus": n_gpus, "tp_parity": parity,
+                                 "error": "tensor-parallel parity failed: nothing was timed"}))
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
+        t0 = time.time()
     model = e.Backend(spec, tens, PROMPT + W + K + 1, device=local, tp=tp)
     load_s = time.time() - t0
     toks = synth.lcg_tokens(PROMPT + W + K, spec.n_vocab)
@@ -384,15 +507,22 @@ def run_ours(args):
     e2e_s = max_over_ranks(time.perf_counter() - t1)
     clocks = sampler.stop() if rank == 0 else None
 
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    weight_bytes, kv_bytes_per_token = model.weight_bytes, model.kv_bytes_per_token
+    tp32 = None
+    if args.workload == "qwen3-4b-q4_k_m" and not args.layers and not args.no_tp32b:
+        model.close()  # the 32B shape takes the memory
+        model = None
+        tp32 = bench_32b(e, make_tp(), local, world, dist, barrier, max_over_ranks, hbm, max(8, min(K, 32)))
     if rank != 0:
-        model.close()
+        if model is not None:
+            model.close()
         dist.barrier()
         dist.destroy_process_group()
         return
-    peaks, peak_kind = measured_peaks()
-    hbm = float(peaks["hbm_gbs"])
     micro_ms = microbench_matvec(e, local) if spec.layout != "f16" else None
-    step_bytes = model.weight_bytes + model.kv_bytes_per_token * (PROMPT + W + K / 2.0)
+    step_bytes = weight_bytes + kv_bytes_per_token * (PROMPT + W + K / 2.0)
     tok_s = K / (dev_ms / 1000.0)  # one sequence: under tensor parallelism the ranks share every step
     out = {
         "metric": metric_name(spec), "value": tok_s, "unit": "tok/s",
@@ -437,7 +567,7 @@ def run_ours(args):
         micro = {"bound": "hbm", "kernel": "k_gemv<Q4_K> 2560x9728, 4 limbs, alone (24 weight copies in rotation)",
                  "achieved": ach, "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_kind": peak_kind,
                  "frac_of_8tbs": ach / 8000.0, "bytes_per_launch": MICRO_BYTES, "us_per_launch": micro_ms * 1000.0,
-                 "traffic": MICRO_TRAFFIC}
+                 "traffic": micro_traffic()}
         out["roofline_gemv"] = micro
         out.setdefault("roofline", micro)
     ops = 2.0 * spec_macs_per_token(spec)
@@ -448,7 +578,12 @@ def run_ours(args):
                                   "frac_of_probe": ops * out["prefill"]["value"] / 1e12 / INT8_PROBE_TOPS,
                                   "probe": "library int8 GEMM 8192^3 on this pool: 2870 TOP/s",
                                   "note": "2*M*N*K counted once; the limb planes issue (NL+1)x that on the tensor pipe"}
-    model.close()
+    if model is not None:
+        model.close()
+    if parity is not None:
+        out["tp_parity"] = parity
+    if tp32 is not None:
+        out["tp_32b"] = tp32
     if n_gpus == 1 and not args.no_cpu_baseline:
         base, _, _ = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)
         out["cpu_baseline"] = base

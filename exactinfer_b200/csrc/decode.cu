@@ -302,20 +302,40 @@ __device__ __noinline__ float convert_act(const float* A, const float* B, float*
     return inv;
 }
 
-// Tensor parallelism: after an exchange every rank holds, in its own copy of the set, the two partial-sum vectors of
-// every rank (rank 0's first one carries the residual stream). CTA c adds its slice of them in rank order — the same
-// order on every rank, so the residual stream stays bit-identical everywhere — and stores it to `out`; the CTAs then
-// meet at a grid barrier and the conversion reads `out` alone.
-__device__ __noinline__ void reduce_ranks(const DkParams& p, const float* set, float* out) {
+// Tensor parallelism: a row-parallel matvec stores every partial sum, on every rank, as an 8-byte word {value, number of
+// the exchange + 1}: data and "it has arrived" travel in one store, so there is neither a fence behind the peer stores nor
+// a barrier in front of the reduction. CTA c waits (bounded) for its slice of the two vectors of every rank in its own
+// rank's copy of the set, adds them in rank order — the same order on every rank, so the residual stream stays
+// bit-identical everywhere (rank 0's first vector carries the old stream) — and stores the slice to `out`; the CTAs then
+// meet at the grid barrier of this GPU and the conversion reads `out` alone. A set is written again two exchanges
+// later, when every rank has passed the barrier behind this reduction.
+__device__ __noinline__ void reduce_ranks(const DkParams& p, const uint2* set, float* out, const unsigned tag, int* s_dead) {
     const int q4 = p.E / 4, lo = range_lo(q4, gridDim.x, blockIdx.x), hi = range_lo(q4, gridDim.x, blockIdx.x + 1);
     const int nv = p.tp_size * p.pv;
 #pragma unroll 1
-    for (int i4 = lo + threadIdx.x; i4 < hi; i4 += DK_THREADS) {
-        float4 v = __ldcg(reinterpret_cast<const float4*>(set) + i4);
-#pragma unroll 4
-        for (int q = 1; q < nv; ++q) {
-            const float4 b = __ldcg(reinterpret_cast<const float4*>(set + size_t(q) * p.E) + i4);
-            v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+    for (int i4 = lo + int(threadIdx.x); i4 < hi; i4 += DK_THREADS) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (int q = 0; q < nv; ++q) {
+            const uint4* src = reinterpret_cast<const uint4*>(set + size_t(q) * p.E + size_t(i4) * 4);
+            uint4 a, b;
+            unsigned it = 0;
+            while (true) {
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 1) : "memory");
+                if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+                if (++it > DK_XSPIN_LIMIT || *reinterpret_cast<volatile int*>(s_dead)) {
+                    if (!*reinterpret_cast<volatile int*>(s_dead)) { *s_dead = 1; atomicExch(p.err, 1); }
+                    break;
+                }
+                if (it > 64) __nanosleep(100);
+            }
+            if (q == 0) {
+                v = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+            } else {
+                v.x = __fadd_rn(v.x, __uint_as_float(a.x)); v.y = __fadd_rn(v.y, __uint_as_float(a.z));
+                v.z = __fadd_rn(v.z, __uint_as_float(b.x)); v.w = __fadd_rn(v.w, __uint_as_float(b.z));
+            }
         }
         reinterpret_cast<float4*>(out)[i4] = v;
     }
@@ -574,6 +594,7 @@ struct EpiArgs {
     float* y;               // STORE / SILU: output vector
     float inv;              // factor of the row sums: 1 / rms of the RMSNorm in front of the matvec, or 1
     int xset;               // PART: set of partial-sum buffers
+    unsigned tag;           // PART under tensor parallelism: number of the exchange + 1, stored with every partial sum
     const float* x_old;     // PART: the residual stream the first contributor of a tile adds (null: nothing is added)
 };
 
@@ -655,11 +676,17 @@ __device__ __forceinline__ void matvec_phase(const DkParams& p, const int type, 
             const bool first = rc.x <= Xt * upt, last = rc.y >= (Xt + 1) * upt;
             if (first && ea.x_old) v = __fadd_rn(e == tid ? xo : __ldcg(ea.x_old + r), v);  // (a CTA has few row tiles: e == tid)
             const size_t pair = (size_t(ea.xset) * p.tp_size + p.tp_rank) * p.pv * p.E;  // this rank's vectors of the set
-#pragma unroll 1
-            for (int q = 0; q < p.tp_size; ++q) {
-                float* base = p.part_peer[q] + pair;
+            if (p.tp_size == 1) {
+                float* base = p.part_peer[0] + pair;
                 base[(first ? 0 : p.E) + r] = v;
                 if (first && last && p.pv == 2) base[p.E + r] = 0.f;
+            } else {  // every rank receives {value, tag} in one 8-byte store
+#pragma unroll 1
+                for (int q = 0; q < p.tp_size; ++q) {
+                    uint2* base = reinterpret_cast<uint2*>(p.part_peer[q]) + pair;
+                    base[(first ? 0 : p.E) + r] = make_uint2(__float_as_uint(v), ea.tag);
+                    if (first && last && p.pv == 2) base[p.E + r] = make_uint2(0u, ea.tag);
+                }
             }
         } else if (ea.epi == DK_EPI_LOGITS) {
 #pragma unroll 1
@@ -915,8 +942,10 @@ __host__ __device__ inline size_t dk_scratch_bytes(int n_max) {
 }
 // grid barriers of one launch (the arrival counter runs on from launch to launch)
 __host__ __device__ inline unsigned dk_barriers_per_launch(const DkParams& p) {
-    const unsigned per_layer = 5u + (p.act_global ? 1u : 0u) + (p.tp_size > 1 ? 2u : 0u);  // tensor parallel: one more behind each reduction
-    // (tensor parallel: the first conversion of a launch has nothing to reduce, the head's has, and the logits meet at one more)
+    // Per layer: behind q|k|v, attention, attn_output, gate|up, ffn_down. Tensor parallel: the barriers behind the two
+    // row-parallel matvecs move behind the reductions of their partial sums (the first conversion of a launch has nothing
+    // to reduce, the head's has), and the logits meet at one more.
+    const unsigned per_layer = 5u + (p.act_global ? 1u : 0u);
     return 1u + per_layer * unsigned(p.n_layer) + (p.tp_size > 1 ? 1u : 0u);
 }
 
@@ -1005,6 +1034,7 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
     const bool tp = p.tp_size > 1;
     float* const my_part = p.part_peer[p.tp_rank];  // this rank's copy of the partial-sum sets
     int pending = -1;  // set whose partial sums the next residual conversion adds (-1: none yet in this launch)
+    unsigned pending_tag = 0;  // tensor parallel: the tag those partial sums carry
     int8_t* const lim_smem = reinterpret_cast<int8_t*>(scratch);
 
     // The step as ONE loop over its matvec stages - per layer q|k|v (0), attn_output (1), gate|up (2), ffn_down (3),
@@ -1025,7 +1055,7 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
         }
         // the stage's activation: where it comes from, how it is normalised, which matrices consume it
         const float *src = nullptr, *norm_w = nullptr;
-        EpiArgs ea{DK_EPI_PART, nullptr, 1.0f, int(xn & 1u), nullptr};
+        EpiArgs ea{DK_EPI_PART, nullptr, 1.0f, int(xn & 1u), xn + 1u, nullptr};
         int n = p.E, nl = 4, nm = 1;
         int i0 = p.n_qkv, kind0 = 3;  // the stage's first matrix: index within the layer, kind
         bool resid = true;
@@ -1057,7 +1087,7 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
                 float* const xnew = head ? p.x : p.xbuf + (cur ^ 1) * p.E;
                 const float* const set = my_part + size_t(pending) * p.tp_size * p.pv * p.E;
                 if (tp) {
-                    reduce_ranks(p, set, xnew);
+                    reduce_ranks(p, reinterpret_cast<const uint2*>(my_part) + size_t(pending) * p.tp_size * p.pv * p.E, xnew, pending_tag, dead);
                     if (!(ok = grid_barrier(p, nb, dead))) break;
                     ea.inv = convert_act<true>(xnew, nullptr, nullptr, n, 0, nblk, norm_w, p.eps, nl, s.act, s.red8, need);
                 } else {
@@ -1077,9 +1107,15 @@ __global__ void __launch_bounds__(DK_CTA_THREADS, 1) k_decode_step(const __grid_
         }
         if (!head) dk_stamp(p, l, sb + 2);
         if (k == 0) attn_prefetch(p, l, as);
-        if (k == 1 || k == 3 || (head && tp)) {  // row-parallel matvecs and the logits meet all ranks
-            ok = grid_barrier(p, nb, dead, tp, xn, pc ? (k == 1 ? 2 : 4) : -1);
+        if (k == 1 || k == 3) {
+            // a row-parallel matvec: on one GPU its partial sums meet at the grid barrier; under tensor parallelism they
+            // carry their own arrival tag and the reduction waits for them, no barrier here
+            if (!tp) ok = grid_barrier(p, nb, dead, false, 0, pc ? (k == 1 ? 2 : 4) : -1);
             pending = int(xn & 1u);
+            pending_tag = xn + 1u;
+            ++xn;
+        } else if (head && tp) {  // the logits rows of all ranks: fenced peer stores and flags
+            ok = grid_barrier(p, nb, dead, true, xn);
             ++xn;
         } else if (!head) {
             ok = grid_barrier(p, nb, dead, false, 0, pc ? (k == 0 ? 0 : 3) : -1);

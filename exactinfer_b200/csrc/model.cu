@@ -513,7 +513,8 @@ int setup_decode_kernel(Model* m) {
     // exchange area: flags, partial sums [2 sets][ranks][2][E], logits; mapped into every rank under tensor parallelism
     const int N = m->tp.size;
     const int pv = 2;  // (one vector per rank with whole tiles measured slower at two ranks: 6.74 against 6.57 ms on the 32B shape)
-    const size_t part_floats = size_t(2) * N * pv * E, logit_floats = size_t(std::max<int64_t>(c.n_vocab, m->tp.vchunk * N));
+    // (under tensor parallelism every partial sum travels with a sequence number in the same 8-byte word)
+    const size_t part_floats = size_t(2) * N * pv * E * (N > 1 ? 2 : 1), logit_floats = size_t(std::max<int64_t>(c.n_vocab, m->tp.vchunk * N));
     const size_t xbytes = 256 + (part_floats + logit_floats) * sizeof(float);
     if (N > 1) {
         bool mapped = false;
