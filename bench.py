@@ -326,7 +326,8 @@ def tp_parity(e, make_tp, local):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
 
-    spec = synth.Spec(name="tp-small", n_layer=3, n_embd=512, n_ff=1280, n_head=8, n_head_kv=2, n_vocab=2043,
+    # 8 KV heads (2, 4 and 8 ranks divide them), 11 FFN blocks (an uneven cut at every rank count), odd vocabulary
+    spec = synth.Spec(name="tp-small", n_layer=3, n_embd=512, n_ff=2816, n_head=16, n_head_kv=8, n_vocab=2043,
                       layout="q4_k_m", head_sigma=2e-5)
     tens = list(synth.generate(spec, 33))
     n_prompt, n_decode = 40, 5

@@ -156,8 +156,13 @@ int elb_matvec(const elb_weight* w, const float* x, float* y, int nl) {
 static int matmul_dev_on(const Weight* w, const float* d_x, int64_t b, float* d_y, int nl, cudaStream_t s, Dev* scratch) {
     if (b <= 0) return fail(ELB_ERR_INVALID, "matmul: token count must be positive");
     if (w->pair) return fail(ELB_ERR_UNSUPPORTED, "matmul: paired weights are only used inside the model");
-    if (w->type == ELB_F16) return gemm_f16_launch(w, d_x, w->n, nullptr, 0.f, int(b), d_y, w->rows, nullptr, EPI_STORE, s);
     const size_t limb_bytes = size_t(4) * b * w->n, inv_off = (limb_bytes + 255) / 256 * 256;
+    if (w->type == ELB_F16) {
+        if (!gemm_f16_tc_usable(w, int(b))) return gemm_f16_launch(w, d_x, w->n, nullptr, 0.f, int(b), d_y, w->rows, nullptr, EPI_STORE, s);
+        if (!scratch->p) ELB_TRY(scratch->alloc(inv_off + size_t(b) * 4));  // hi and lo halves, then 2^-k per row
+        return gemm_f16_tc_launch(w, d_x, w->n, nullptr, 0.f, int(b), scratch->p, reinterpret_cast<float*>(scratch->as<int8_t>() + inv_off),
+                                  d_y, w->rows, nullptr, EPI_STORE, s, false);
+    }
     const size_t xs_off = inv_off + (size_t(b) * 4 + 255) / 256 * 256, total = xs_off + size_t(b) * (w->n / 32) * 4;
     if (!scratch->p) ELB_TRY(scratch->alloc(total));
     int8_t* limbs = scratch->as<int8_t>();
@@ -174,6 +179,7 @@ int elb_matmul_dev(const elb_weight* w, const float* d_x, int64_t b, float* d_y,
     Dev scratch;
     ELB_TRY(matmul_dev_on(W(w), d_x, b, d_y, nl, nullptr, &scratch));
     ELB_CUDA(cudaStreamSynchronize(nullptr));
+    ELB_TRY(gemm_f16_tc_check());
     return gemm_tc_check();
 }
 int elb_matmul(const elb_weight* w, const float* x, int64_t b, float* y, int nl) {

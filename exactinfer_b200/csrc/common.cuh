@@ -242,6 +242,12 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
 int gemm_tc_check();
 int gemm_f16_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, float* d_y,
                     int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
+// gemm_f16_tc.cu - tcgen05 path for F16 weights: the token rows are split into fp16 hi / lo halves (d_scratch: 4 * B * n
+// bytes) with 2^-k per row in d_inv_scale, then one tensor-core GEMM with fp32 accumulators in tensor memory
+bool gemm_f16_tc_usable(const Weight* w, int B);
+int gemm_f16_tc_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, void* d_scratch,
+                       float* d_inv_scale, float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl);
+int gemm_f16_tc_check();
 
 // attn.cu
 struct AttnDecodeArgs {

@@ -187,7 +187,13 @@ int check_shape(const HostTensor& t, int64_t rows, int64_t n, const char* what) 
 int linear_tokens(Model* m, const Weight* w, const float* xin, int64_t ldx, const float* norm_w, int B, float* y,
                   int64_t ldy, const float* resid, int epi, int nl) {
     ++m->launches;
-    if (w->type == ELB_F16) return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
+    if (w->type == ELB_F16) {
+        if (gemm_f16_tc_usable(w, B)) {
+            ++m->launches;  // the hi / lo split of the rows
+            return gemm_f16_tc_launch(w, xin, ldx, norm_w, m->cfg.eps, B, m->limbs, m->inv_scale, y, ldy, resid, epi, m->stream, m->use_pdl);
+        }
+        return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
+    }
     if (gemm_tc_usable(w, B)) return gemm_tc_launch(w, m->limbs, m->inv_scale, m->xsum, B, nl, y, ldy, resid, epi, m->stream, m->use_pdl);
     return gemm_planes_launch(w, m->limbs, m->inv_scale, m->xsum, B, y, ldy, resid, epi, m->stream);
 }
@@ -411,6 +417,7 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits, const
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
     if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
     ELB_TRY(gemm_tc_check());
+    ELB_TRY(gemm_f16_tc_check());
     float ms = 0.f;
     ELB_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->last_ms += ms;
@@ -988,6 +995,7 @@ int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq,
     if (out_dev) ELB_CUDA(cudaMemcpyAsync(logits, out_dev, rows.size() * size_t(V) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
     ELB_TRY(gemm_tc_check());
+    ELB_TRY(gemm_f16_tc_check());
     ELB_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
     m->last_launches = m->launches - before;
     return ELB_OK;
