@@ -94,6 +94,13 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp32b", action="store_true", help="skip the 32B-shaped block (tp_32b) of the default workload")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
+    ap.add_argument("--cpu-full", action="store_true",
+                    help="time the reference CPU build on its whole benchmark procedure (warm-up, 512-token prompt pass, "
+                         "128 single-token steps from position 0) instead of a bounded sample")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="concurrent sequences: above 1 the run is the batched workload (each sequence a --prompt-token "
+                         "prompt, then --steps batched steps, one row per sequence)")
+    ap.add_argument("--prompt", type=int, default=4096, help="prompt length of the batched workload")
     ap.add_argument("--gemm-micro", action="store_true",
                     help="only time the prompt-chunk GEMM on the five linear shapes of the 4B model at 512 tokens")
     return ap.parse_args()
@@ -248,6 +255,46 @@ def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
                       f"context shorter than the GPU run's {PROMPT}+), {dt:.1f} s"}, done, dt
 
 
+def cpu_full_bench(spec, tens, pp=PROMPT, tg=128):
+    """The reference's own benchmark procedure (`bench --backend cpu --pp 512 --tg 128`, src/main.cpp:621-647 of the
+    reference) on its CPU backend, all physical cores: 8 warm-up tokens, one timed pass over pp prompt tokens at position
+    0, then tg timed single-token evaluations at positions 0..tg-1 of the same token stream."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    import shutil
+
+    want = physical_cores()
+    toks = synth.lcg_tokens(max(pp, tg), spec.n_vocab)
+    tmp = None
+    if ol.have_ref():
+        kind = "reference"
+        tmp = tempfile.mkdtemp(prefix="elb_bench_")
+        path = os.path.join(tmp, "model.gguf")
+        synth.write_gguf(path, spec, tens)
+        ol.ref().ref_set_threads(want)
+        model = ol.RefModel(path, max(pp, tg) + 1)
+        cores = ol.ref().ref_threads()
+    else:
+        kind = "port"
+        ol.oracle().orc_set_threads(want)
+        model = ol.OracleModel(spec, tens, max(pp, tg) + 1)
+        cores = ol.oracle().orc_threads()
+    model.eval(toks[:8], 0)
+    t0 = time.perf_counter()
+    model.eval(toks[:pp], 0)
+    t1 = time.perf_counter()
+    for i in range(tg):
+        model.eval(toks[i:i + 1], i)
+    t2 = time.perf_counter()
+    model.close()
+    if tmp:
+        shutil.rmtree(tmp, ignore_errors=True)
+    return {"value": tg / (t2 - t1), "unit": "tok/s", "prefill_tok_s": pp / (t1 - t0), "cores": int(cores),
+            "physical_cores": int(want), "kind": kind,
+            "sample": f"the whole procedure of the reference's bench command: 8 warm-up tokens, pp{pp} in {t1 - t0:.1f} s, "
+                      f"tg{tg} (positions 0..{tg - 1}) in {t2 - t1:.1f} s"}
+
+
 def run_reference(args):
     rank, local, world = dist_env()
     if rank != 0:
@@ -255,13 +302,18 @@ def run_reference(args):
     spec = get_spec(args)
     tens, _ = model_tensors(spec)
     budget = 150.0
-    base, done, dt = cpu_decode_baseline(spec, tens, budget, max(2, args.steps))
+    if args.cpu_full:
+        base = cpu_full_bench(spec, tens)
+        done, dt = 128, 128 / base["value"]
+    else:
+        base, done, dt = cpu_decode_baseline(spec, tens, budget, max(2, args.steps))
     out = {"impl": "reference", "metric": metric_name(spec), "value": base["value"], "unit": "tok/s",
            "n_gpus": args.gpus, "steps": done, "steps_requested": args.steps, "warmup": 1,
            "ms_per_step": 1000.0 * dt / done, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
            "dtype": "f32", "data": "synthetic", "config": {"workload": workload_name(spec, args.steps),
-                      "sample": "CPU path, single-token steps from position 1 (no 512-token prompt: it alone would "
-                                "take minutes on the host), bounded to 150 s"},
+                      "sample": base["sample"] if args.cpu_full else
+                      "CPU path, single-token steps from position 1 (no 512-token prompt: it alone would "
+                      "take minutes on the host), bounded to 150 s"},
            "cpu_baseline": base,
            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(json.dumps(out))
@@ -586,12 +638,93 @@ def run_ours(args):
     if tp32 is not None:
         out["tp_32b"] = tp32
     if n_gpus == 1 and not args.no_cpu_baseline:
-        base, _, _ = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)
-        out["cpu_baseline"] = base
+        if args.cpu_full:
+            out["cpu_baseline"] = cpu_full_bench(spec, tens)
+        else:
+            out["cpu_baseline"] = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)[0]
     emit(json.dumps(out))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_batched(args):
+    """Many sequences on one GPU: --batch sequences, each with a --prompt-token prompt (chunks of 512 rows), then
+    --steps batched decode steps with one row per sequence. value = rows per second of the timed steps up to the last
+    layer; e2e evaluates the head as well and copies every row's logits to the host."""
+    import exactinfer_b200 as e
+    ok, why = e.cuda_available()
+    if not ok:
+        raise SystemExit(f"bench: the CUDA path is unavailable ({why}); there is no CPU fallback")
+    spec = get_spec(args)
+    tens, gen_s = model_tensors(spec)
+    NB, P, K, W = args.batch, args.prompt, args.steps, max(args.warmup, 3)
+    CH = 512
+    t0 = time.time()
+    model = e.Backend(spec, tens, P + W + K + 1, max_batch=CH, n_seq=NB)
+    load_s = time.time() - t0
+    toks = synth.lcg_tokens(P + W + K + NB + 1, spec.n_vocab)
+    seq = np.arange(NB, dtype=np.int32)
+    # ---- prompts: sequence s reads the token stream from offset s
+    pp_ms, pp_launch = 0.0, 0
+    t1 = time.perf_counter()
+    for s in range(NB):
+        for c0 in range(0, P, CH):
+            n = min(CH, P - c0)
+            model.eval_batch(toks[s + c0:s + c0 + n], np.full(n, s, np.int32), np.arange(c0, c0 + n, dtype=np.int32),
+                             want_logits=False)
+            st = model.last_eval_stats()
+            pp_ms += st[0]
+            pp_launch += st[1]
+    pp_wall = time.perf_counter() - t1
+    for i in range(W):
+        model.eval_batch(toks[P + i:P + i + NB], seq, np.full(NB, P + i, np.int32), want_logits=False)
+    sampler = ClockSampler(0)
+    sampler.start()
+    dev, launches = 0.0, 0
+    t1 = time.perf_counter()
+    for i in range(K):
+        model.eval_batch(toks[P + W + i:P + W + i + NB], seq, np.full(NB, P + W + i, np.int32), want_logits=False)
+        st = model.last_eval_stats()
+        dev += st[0]
+        launches += st[1]
+    wall = time.perf_counter() - t1
+    # the same step with the head evaluated and every row's logits copied to the host (a few steps: 39 MB per step)
+    KH = min(K, 8)
+    t1 = time.perf_counter()
+    for i in range(KH):
+        model.eval_batch(toks[P + W + i:P + W + i + NB], seq, np.full(NB, P + W + i, np.int32), want_logits=True)
+    head_wall = time.perf_counter() - t1
+    clocks = sampler.stop()
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    step_s = dev / K / 1000.0
+    kv_step = NB * model.kv_bytes_per_token * (P + W + K / 2.0)
+    step_bytes = model.weight_bytes + kv_step
+    out = {"metric": f"{spec.name} batched decode tok/s ({NB} sequences)", "value": NB * K / (dev / 1000.0), "unit": "tok/s",
+           "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": dev / K, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "int8 limbs x quantized ints -> int32, fp32 scales", "data": "synthetic",
+           "config": {"workload": f"{spec.name}: {spec.n_layer} layers, E{spec.n_embd} F{spec.n_ff} H{spec.n_head}/{spec.n_head_kv}, "
+                                  f"{NB} sequences x {P}-token prompts, then {K} batched steps (one row per sequence)",
+                      "l2": "inputs larger than L2: every step streams the weights and all sequences' KV rows from HBM",
+                      "seed": SEED, "head": "timed steps stop at the last layer (no logits); e2e evaluates the head and copies "
+                                            "every row's logits to the host"},
+           "e2e": {"value": NB * KH / head_wall, "unit": "tok/s", "h2d_bytes_per_step": NB * 12,
+                   "d2h_bytes_per_step": NB * spec.n_vocab * 4, "steps": KH,
+                   "without_head_tok_s": NB * K / wall},
+           "gpu_launches": int(launches), "clocks": clocks,
+           "prefill": {"value": NB * P / (pp_ms / 1000.0), "unit": "tok/s", "ms": pp_ms, "e2e_tok_s": NB * P / pp_wall,
+                       "gpu_launches": int(pp_launch)},
+           "roofline": {"bound": "hbm", "kernel": "the batched step as a whole (attention over every sequence's KV rows "
+                        "dominates the bytes)", "achieved": step_bytes / step_s / 1e9, "peak": hbm, "unit": "GB/s",
+                        "frac": step_bytes / step_s / 1e9 / hbm, "peak_kind": peak_kind, "bytes_per_launch": step_bytes,
+                        "kv_bytes_per_step": kv_step, "weight_bytes": model.weight_bytes, "us_per_launch": step_s * 1e6,
+                        "traffic": None},
+           "setup_s": {"generate": gen_s, "upload": load_s}}
+    model.close()
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)[0]
+    emit(json.dumps(out))
 
 
 def emit(line: str):
@@ -609,5 +742,7 @@ if __name__ == "__main__":
         microbench_gemm(a)
     elif a.impl == "reference":
         run_reference(a)
+    elif a.batch > 1:
+        run_batched(a)
     else:
         run_ours(a)

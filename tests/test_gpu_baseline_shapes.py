@@ -5,6 +5,7 @@ shapes that are timed are compared here as they are timed:
   * the Q4_K matvec 2560 x 9728 with a 4-limb N(0,1) activation (sub-block sums, block sums and min-term sums bit-exact,
     fp32 output within 1e-5), and the same weight over 512 rows of activations through the tensor-core matmul;
   * the whole 151 936-row Q6_K head;
+  * the layer shapes of the 0.6B model with F16 weights and of the 1.7B model in Q8_0, cut to 4 layers;
   * the layer shape of the 4B model (E 2560, F 9728, 32/8 heads, Q4_K_M layout, full vocabulary) cut to 4 layers and the
     layer shape of the 32B model (E 5120, F 25600, 64/8 heads) cut to 2: a 64-token prompt, then 8 single-token steps,
     with the head's block scales at the benchmark's 1e-3 and at 2e-5 (logits of the size a trained model has).
@@ -157,11 +158,24 @@ def test_layer_shape_prefill_and_decode(elb, shape, head_sigma):
     lands 4e-5 from float64 on one step of the 32B shape), and with the benchmark's head scale the logits reach
     10^2..10^3, where one fp32 ulp already exceeds 3e-5. The CUDA path may then be at most 1.5 times as far from
     float64 as the CPU path is (for log-probabilities: or 8 ulp of the largest logit, whichever is larger)."""
-    from f64_model import f64_last_token
     base, layers = LAYER_SHAPES[shape]
     spec = dataclasses.replace(base, name=f"{shape}-cut", n_layer=layers, head_sigma=head_sigma)
+    check_layer_shape(elb, spec, f"{shape} layer shape x{layers}, head sigma {head_sigma:g}", persistent=True)
+
+
+@pytest.mark.parametrize("name,layers", (("qwen3-0.6b-f16", 4), ("qwen3-1.7b-q8_0", 4)))
+def test_layer_shape_f16_and_q8_0(elb, name, layers):
+    """The 0.6B shape with F16 weights (prompt rows through the tcgen05 kind::f16 GEMM, steps through the F16 matvec)
+    and the 1.7B shape in Q8_0, cut to 4 layers, full vocabulary; same bars and adjudication as above."""
+    spec = dataclasses.replace(synth.SPECS[name], name=f"{name}-cut", n_layer=layers)
+    check_layer_shape(elb, spec, f"{name} layer shape x{layers}", persistent=False)
+
+
+def check_layer_shape(elb, spec, label, persistent):
+    from f64_model import f64_last_token
     tens, steps, launches = run_pair(elb, spec, seed=41, n_prompt=64, n_decode=8)
-    assert launches == 1, "the persistent decode kernel must be the path that ran"
+    if persistent:
+        assert launches == 1, "the persistent decode kernel must be the path that ran"
     worst = dict(lp=0.0, rel=0.0, hid=0.0, big=0.0)
     missed = []  # evaluations that miss a bar against the CPU path: (severity, index)
     for i, (toks, lg, lc, hg, hc) in enumerate(steps):
@@ -187,6 +201,6 @@ def test_layer_shape_prefill_and_decode(elb, shape, head_sigma):
         assert d_gpu <= max(LOGPROB_TOL, 1.5 * d_cpu, floor), (len(toks), d_gpu, d_cpu, floor)
         assert rel(lg, lx) <= max(MODEL_REL_TOL, 1.5 * rel(lc, lx)), (len(toks), rel(lg, lx), rel(lc, lx))
         assert rel(hg, hx) <= max(MODEL_REL_TOL, 1.5 * rel(hc, hx)), (len(toks), rel(hg, hx), rel(hc, hx))
-    print(f"\n{shape} layer shape x{layers}, head sigma {head_sigma:g}: against the CPU path max |dlogprob| {worst['lp']:.2e}, "
+    print(f"\n{label}: against the CPU path max |dlogprob| {worst['lp']:.2e}, "
           f"logits rel {worst['rel']:.2e}, residual rel {worst['hid']:.2e}, max |logit| {worst['big']:.3g}; "
           f"{len(missed)} of {len(steps)} evaluations miss a bar against the CPU path, the worst {min(2, len(missed))} adjudicated by float64")
