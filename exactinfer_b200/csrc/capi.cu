@@ -157,11 +157,18 @@ static int matmul_dev_on(const Weight* w, const float* d_x, int64_t b, float* d_
     if (b <= 0) return fail(ELB_ERR_INVALID, "matmul: token count must be positive");
     if (w->pair) return fail(ELB_ERR_UNSUPPORTED, "matmul: paired weights are only used inside the model");
     const size_t limb_bytes = size_t(4) * b * w->n, inv_off = (limb_bytes + 255) / 256 * 256;
-    if (w->type == ELB_F16) {
+    if (w->type == ELB_F16 || gemm_f16_tc_usable(w, int(b))) {
         if (!gemm_f16_tc_usable(w, int(b))) return gemm_f16_launch(w, d_x, w->n, nullptr, 0.f, int(b), d_y, w->rows, nullptr, EPI_STORE, s);
-        if (!scratch->p) ELB_TRY(scratch->alloc(inv_off + size_t(b) * 4));  // hi and lo halves, then 2^-k per row
-        return gemm_f16_tc_launch(w, d_x, w->n, nullptr, 0.f, int(b), scratch->p, reinterpret_cast<float*>(scratch->as<int8_t>() + inv_off),
-                                  d_y, w->rows, nullptr, EPI_STORE, s, false);
+        // hi and lo halves, 2^-k per row, then the partial tiles and arrival counters of the k splits
+        const size_t part_off = (inv_off + size_t(b) * 4 + 255) / 256 * 256, cnt_off = part_off + gemm_f16_tc_part_bytes();
+        if (!scratch->p) {
+            ELB_TRY(scratch->alloc(cnt_off + size_t(gemm_f16_tc_counters()) * 4));
+            ELB_CUDA(cudaMemsetAsync(scratch->as<int8_t>() + cnt_off, 0, size_t(gemm_f16_tc_counters()) * 4, s));
+        }
+        int8_t* base = scratch->as<int8_t>();
+        return gemm_f16_tc_launch(w, d_x, w->n, nullptr, 0.f, int(b), base, reinterpret_cast<float*>(base + inv_off), d_y, w->rows,
+                                  nullptr, EPI_STORE, s, false, reinterpret_cast<float*>(base + part_off),
+                                  reinterpret_cast<unsigned*>(base + cnt_off));
     }
     const size_t xs_off = inv_off + (size_t(b) * 4 + 255) / 256 * 256, total = xs_off + size_t(b) * (w->n / 32) * 4;
     if (!scratch->p) ELB_TRY(scratch->alloc(total));

@@ -75,6 +75,9 @@ struct Weight {
     int8_t* planes = nullptr;  // [n_planes][tiles*16][n]
     __half* pl_d = nullptr;    // [tiles*16][n/blk] block scale d (blk = 256, Q8_0: 32)
     float* pl_dm = nullptr;    // Q4_K: [tiles*16][n/32] fl(dmin * m)
+    // Q8_0 on the fp16 tensor-core path: the weight d * q (18 significant bits) as an exact sum of two fp16 values,
+    // [2][tiles*16][n] (hi, then lo); present instead of the digit plane unless some d * q leaves the fp16 range
+    __half* f16pair = nullptr;
     // scratch of the split-K matvec (per weight so that matvecs of different weights may overlap)
     float* part = nullptr;     // [grid][2][16]
     unsigned* counters = nullptr;  // [tiles]
@@ -242,11 +245,16 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
 int gemm_tc_check();
 int gemm_f16_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, float* d_y,
                     int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
-// gemm_f16_tc.cu - tcgen05 path for F16 weights: the token rows are split into fp16 hi / lo halves (d_scratch: 4 * B * n
-// bytes) with 2^-k per row in d_inv_scale, then one tensor-core GEMM with fp32 accumulators in tensor memory
+// gemm_f16_tc.cu - tcgen05 path for F16 weights and for Q8_0 weights held as fp16 pairs: the token rows are split into
+// fp16 hi / lo halves (d_scratch: 4 * B * n bytes) with 2^-k per row in d_inv_scale, then one tensor-core GEMM with fp32
+// accumulators in tensor memory. d_part (gemm_f16_tc_part_bytes() bytes) and d_counters (gemm_f16_tc_counters() zeroed
+// words) let a matrix of few tiles be cut along k over more CTAs; null: no cut.
 bool gemm_f16_tc_usable(const Weight* w, int B);
+size_t gemm_f16_tc_part_bytes();
+int gemm_f16_tc_counters();
 int gemm_f16_tc_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, void* d_scratch,
-                       float* d_inv_scale, float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl);
+                       float* d_inv_scale, float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl,
+                       float* d_part = nullptr, unsigned* d_counters = nullptr);
 int gemm_f16_tc_check();
 
 // attn.cu

@@ -498,11 +498,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             }
         }
         if (ok) {
+            // every load before the first store: Y may be the residual stream itself, and a load that has to wait for
+            // the store before it turns the tile's output into a chain of memory round trips
+            float sc[TH], res[TH];
+#pragma unroll
+            for (int t = 0; t < TH; ++t) {
+                const int tok = tok0 + th * TH + t;
+                sc[t] = tok < p.B ? __ldcg(p.inv_scale + tok) : 0.f;
+                res[t] = p.epilogue == EPI_ADD && tok < p.B && R < p.rows ? __ldcg(p.resid + int64_t(tok) * p.ldy + R) : 0.f;
+            }
 #pragma unroll
             for (int t = 0; t < TH; ++t) {
                 const int tok = tok0 + th * TH + t;
                 const bool tok_ok = tok < p.B;
-                const float y = accf[t] * (tok_ok ? __ldcg(p.inv_scale + tok) : 0.f);
+                const float y = accf[t] * sc[t];
                 if (p.epilogue == EPI_SILU) {  // tile rows 0..7 gate, 8..15 up (16-row groups): partner is 8 lanes up
                     const float up = __shfl_down_sync(0xffffffffu, y, 8);
                     const int64_t o = R / 16 * 8 + (R & 7);
@@ -510,7 +519,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                         p.Y[int64_t(tok) * p.ldy + o] = __fmul_rn(__fdiv_rn(y, 1.0f + expf(-y)), up);
                 } else if (tok_ok && R < p.rows) {
                     const int64_t o = int64_t(tok) * p.ldy + R;
-                    p.Y[o] = p.epilogue == EPI_ADD ? p.resid[o] + y : y;
+                    p.Y[o] = p.epilogue == EPI_ADD ? res[t] + y : y;
                 }
             }
         }

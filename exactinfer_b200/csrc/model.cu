@@ -54,6 +54,8 @@ struct Model {
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
     int8_t* limbs = nullptr;
     float *inv_scale = nullptr, *xsum = nullptr;
+    float* tc_part = nullptr;         // partial tiles and arrival counters of the fp16 tensor-core GEMM's k splits
+    unsigned* tc_counters = nullptr;
     int32_t* tokens_dev = nullptr;
     int* pos_dev = nullptr;
     int32_t* tokens_host = nullptr;  // pinned
@@ -187,13 +189,12 @@ int check_shape(const HostTensor& t, int64_t rows, int64_t n, const char* what) 
 int linear_tokens(Model* m, const Weight* w, const float* xin, int64_t ldx, const float* norm_w, int B, float* y,
                   int64_t ldy, const float* resid, int epi, int nl) {
     ++m->launches;
-    if (w->type == ELB_F16) {
-        if (gemm_f16_tc_usable(w, B)) {
-            ++m->launches;  // the hi / lo split of the rows
-            return gemm_f16_tc_launch(w, xin, ldx, norm_w, m->cfg.eps, B, m->limbs, m->inv_scale, y, ldy, resid, epi, m->stream, m->use_pdl);
-        }
-        return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
+    if (gemm_f16_tc_usable(w, B)) {  // F16, and Q8_0 held as fp16 pairs
+        ++m->launches;  // the hi / lo split of the rows
+        return gemm_f16_tc_launch(w, xin, ldx, norm_w, m->cfg.eps, B, m->limbs, m->inv_scale, y, ldy, resid, epi, m->stream, m->use_pdl,
+                                  m->tc_part, m->tc_counters);
     }
+    if (w->type == ELB_F16) return gemm_f16_launch(w, xin, ldx, norm_w, m->cfg.eps, B, y, ldy, resid, epi, m->stream);
     if (gemm_tc_usable(w, B)) return gemm_tc_launch(w, m->limbs, m->inv_scale, m->xsum, B, nl, y, ldy, resid, epi, m->stream, m->use_pdl);
     return gemm_planes_launch(w, m->limbs, m->inv_scale, m->xsum, B, y, ldy, resid, epi, m->stream);
 }
@@ -221,7 +222,7 @@ int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
         float* kc = m->kcache + (size_t(l) * m->n_seq + (mixed ? 0 : seq0)) * seq_stride;
         float* vc = m->vcache + (size_t(l) * m->n_seq + (mixed ? 0 : seq0)) * seq_stride;
         bool q = false;
-        for (auto& s : L.qkv) q |= s.w->type != ELB_F16;
+        for (auto& s : L.qkv) q |= !gemm_f16_tc_usable(s.w, B) && s.w->type != ELB_F16;
         ELB_TRY(split_tokens(m, m->x, E, E, m->nl_qkv, L.attn_norm, B, q));
         for (auto& s : L.qkv) ELB_TRY(linear_tokens(m, s.w, m->x, E, L.attn_norm, B, m->qkv + s.col, QKV, nullptr, EPI_STORE, m->nl_qkv));
         if (mixed) {
@@ -234,12 +235,12 @@ int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
             ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream, m->ap_part, m->ap_counters));
         }
         m->launches += 2;
-        ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16));
+        ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16 && !gemm_f16_tc_usable(L.wo, B)));
         ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, yo, E, res, epi_o, m->nl_wo));
         if (tp) ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(B) * E, m->stream));
-        ELB_TRY(split_tokens(m, m->x, E, E, m->nl_gu, L.ffn_norm, B, L.gu->type != ELB_F16));
+        ELB_TRY(split_tokens(m, m->x, E, E, m->nl_gu, L.ffn_norm, B, L.gu->type != ELB_F16 && !gemm_f16_tc_usable(L.gu, B)));
         ELB_TRY(linear_tokens(m, L.gu, m->x, E, L.ffn_norm, B, m->act, F, nullptr, EPI_SILU, m->nl_gu));
-        ELB_TRY(split_tokens(m, m->act, F, F, m->nl_down, nullptr, B, L.down->type != ELB_F16));
+        ELB_TRY(split_tokens(m, m->act, F, F, m->nl_down, nullptr, B, L.down->type != ELB_F16 && !gemm_f16_tc_usable(L.down, B)));
         ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, yo, E, res, epi_o, m->nl_down));
         if (tp) ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(B) * E, m->stream));
     }
@@ -680,7 +681,7 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact);
+    cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact); cudaFree(m->tc_part); cudaFree(m->tc_counters);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev); cudaFree(m->mask_dev);
@@ -842,6 +843,9 @@ int model_finalize(Model* m) {
     }
     ELB_CUDA(cudaMalloc(&m->limbs, size_t(4) * B * maxn));
     ELB_CUDA(cudaMalloc(&m->inv_scale, size_t(B) * 4));
+    ELB_CUDA(cudaMalloc(&m->tc_part, gemm_f16_tc_part_bytes()));
+    ELB_CUDA(cudaMalloc(&m->tc_counters, size_t(gemm_f16_tc_counters()) * sizeof(unsigned)));
+    ELB_CUDA(cudaMemset(m->tc_counters, 0, size_t(gemm_f16_tc_counters()) * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->xsum, size_t(B) * (maxn / 32 + 1) * 4));
     ELB_CUDA(cudaMalloc(&m->tokens_dev, size_t(B) * sizeof(int32_t)));
     ELB_CUDA(cudaMalloc(&m->pos_dev, sizeof(int)));
@@ -978,7 +982,7 @@ int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq,
                 ELB_CUDA(cudaMemcpyAsync(xh + r * E, m->x + size_t(rows[r]) * E, size_t(E) * sizeof(float), cudaMemcpyDeviceToDevice, m->stream));
         }
         const int R = int(rows.size());
-        if (m->head->type != ELB_F16 && !m->head->planes) {  // no digit planes: row by row
+        if (m->head->type != ELB_F16 && !m->head->planes && !gemm_f16_tc_usable(m->head, R)) {  // no digit planes: row by row
             for (int r = 0; r < R; ++r) {
                 ELB_TRY(prep_limbs_launch(xh + size_t(r) * E, E, m->output_norm, m->cfg.eps, 4, m->dlimbs[0], m->dinv, false, m->stream));
                 ++m->launches;
@@ -986,7 +990,7 @@ int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq,
                              nullptr, EPI_STORE, PostOp{}));
             }
         } else {
-            ELB_TRY(split_tokens(m, xh, E, E, 4, m->output_norm, R, m->head->type != ELB_F16));
+            ELB_TRY(split_tokens(m, xh, E, E, 4, m->output_norm, R, m->head->type != ELB_F16 && !gemm_f16_tc_usable(m->head, R)));
             ELB_TRY(linear_tokens(m, m->head, xh, E, m->output_norm, R, m->logits_rows, V, nullptr, EPI_STORE, 4));
         }
         out_dev = m->logits_rows;

@@ -1,6 +1,7 @@
 // Weight upload: file bytes -> tiled device layout (a pure permutation), optional int8 digit planes for the
 // tensor-core path, and the row decoders (embedding gather / parity checks) that read the tiled layout back.
 #include <vector>
+#include <cstdlib>
 
 #include <map>
 #include <mutex>
@@ -75,6 +76,24 @@ __global__ void k_planes(int type, const uint8_t* __restrict__ tiled, int64_t ro
         if (p1) p1[o] = int8_t((w - w0) >> 8);
         if (k % blk == 0) pl_d[R * (n / blk) + k / blk] = __float2half_rn(e.d);  // exact: d came from fp16
         if (pl_dm && k % 32 == 0) pl_dm[R * (n / 32) + k / 32] = __fmul_rn(e.dmin, float(e.mn));
+    }
+}
+
+// Q8_0 for the fp16 tensor cores: v = d * q is exact in fp32 (11 x 7 significant bits) and a multiple of 2^-24, hi =
+// fp16(v), lo = v - hi has at most 8 significant bits and is again a multiple of 2^-24: hi + lo = v exactly. *bad is
+// raised when that fails (hi overflows: |d * q| > 65504).
+__global__ void k_q8_pair(const uint8_t* __restrict__ tiled, int64_t rows16, int64_t n, __half* __restrict__ hi,
+                          __half* __restrict__ lo, int* __restrict__ bad) {
+    const int64_t total = rows16 * n;
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+        const QElem e = tiled_elem(ELB_Q8_0, tiled, n, o / n, o % n);
+        const float v = __fmul_rn(e.d, float(e.sc * e.q));
+        const __half h = __float2half_rn(v);
+        const float r = v - __half2float(h);
+        const __half l = __float2half_rn(r);
+        if (isinf(__half2float(h)) || __half2float(l) != r) *bad = 1;
+        hi[o] = h;
+        lo[o] = l;
     }
 }
 
@@ -168,7 +187,29 @@ int weight_create(int device, int type, int64_t rows_one, int64_t n, const void*
     cudaFree(raw);
     raw = nullptr;
 
-    if ((flags & ELB_W_PLANES) && type != ELB_F16) {
+    if ((flags & ELB_W_PLANES) && type == ELB_Q8_0 && n % 64 == 0) {
+        static const bool off = [] { const char* v = std::getenv("ELB_Q8_PLANES"); return v && v[0] == '1'; }();
+        const int64_t rows16 = w->tiles * 16;
+        int* bad = nullptr;
+        if (!off && cudaMalloc(&bad, sizeof(int)) == cudaSuccess && cudaMemset(bad, 0, sizeof(int)) == cudaSuccess &&
+            cudaMalloc(&w->f16pair, size_t(2) * rows16 * n * sizeof(__half)) == cudaSuccess) {
+            const int64_t tot = rows16 * n;
+            k_q8_pair<<<int(std::min<int64_t>((tot + 255) / 256, 148 * 32)), 256>>>(w->tiled, rows16, n, w->f16pair,
+                                                                                   w->f16pair + rows16 * n, bad);
+            int h_bad = 1;
+            if (cudaGetLastError() != cudaSuccess || cudaMemcpy(&h_bad, bad, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+                cudaFree(bad);
+                return cleanup(fail(ELB_ERR_CUDA, "weight_create: fp16 pair kernel failed"));
+            }
+            if (h_bad) {  // out of the fp16 range: this weight stays on the digit plane
+                cudaFree(w->f16pair);
+                w->f16pair = nullptr;
+            }
+        }
+        cudaGetLastError();
+        cudaFree(bad);
+    }
+    if ((flags & ELB_W_PLANES) && type != ELB_F16 && !w->f16pair) {
         const int64_t rows16 = w->tiles * 16;
         w->n_planes = type == ELB_Q8_0 ? 1 : 2;
         const int blk = type == ELB_Q8_0 ? QK8_0 : QK_K;
@@ -207,7 +248,7 @@ void weight_destroy(Weight* w) {
     if (!w) return;
     cudaSetDevice(w->device);
     if (w->view) w->tiled = nullptr;
-    cudaFree(w->tiled); cudaFree(w->planes); cudaFree(w->pl_d); cudaFree(w->pl_dm); cudaFree(w->part); cudaFree(w->counters); cudaFree(w->xlimbs); cudaFree(w->xinv);
+    cudaFree(w->tiled); cudaFree(w->planes); cudaFree(w->f16pair); cudaFree(w->pl_d); cudaFree(w->pl_dm); cudaFree(w->part); cudaFree(w->counters); cudaFree(w->xlimbs); cudaFree(w->xinv);
     delete w;
 }
 
