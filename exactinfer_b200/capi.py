@@ -36,6 +36,7 @@ SIGNATURES = {
     "elb_memcpy_d2h": (C.c_int, [_vp, _vp, C.c_size_t]),
     "elb_device_sync": (C.c_int, [C.c_int]),
     "elb_device_mem_info": (C.c_int, [C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "elb_selftest_wait_expiry": (C.c_int, [C.c_int]),
     "elb_weight_create": (C.c_int, [C.c_int, C.c_int, C.c_int64, C.c_int64, _vp, C.c_size_t, C.c_int, C.POINTER(_vp)]),
     "elb_weight_destroy": (None, [_vp]),
     "elb_weight_rows": (C.c_int64, [_vp]),

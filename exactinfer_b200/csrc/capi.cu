@@ -80,6 +80,12 @@ int elb_device_mem_info(int device, size_t* free_bytes, size_t* total_bytes) {
     ELB_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
     return ELB_OK;
 }
+int elb_selftest_wait_expiry(int device) {
+    ELB_CUDA(cudaSetDevice(device));
+    ELB_TRY(gemm_f16_tc_wait_expiry(nullptr));
+    ELB_CUDA(cudaStreamSynchronize(nullptr));
+    return gemm_f16_tc_check();  // ELB_ERR_CUDA when the wait ran out and was reported, as it must
+}
 int elb_device_sync(int device) {
     ELB_CUDA(cudaSetDevice(device));
     ELB_CUDA(cudaDeviceSynchronize());

@@ -256,6 +256,7 @@ int gemm_f16_tc_launch(const Weight* w, const float* d_x, int64_t ldx, const flo
                        float* d_inv_scale, float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl,
                        float* d_part = nullptr, unsigned* d_counters = nullptr);
 int gemm_f16_tc_check();
+int gemm_f16_tc_wait_expiry(cudaStream_t s);  // test hook: a bounded wait that must run out
 
 // attn.cu
 struct AttnDecodeArgs {

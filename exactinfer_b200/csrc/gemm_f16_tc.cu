@@ -42,9 +42,9 @@ __device__ __forceinline__ void f_mbar_expect_tx(uint64_t* bar, uint32_t bytes) 
 __device__ __forceinline__ void f_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(f_smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool f_mbar_wait(uint64_t* bar, uint32_t parity) {  // bounded; false when it ran out
+__device__ __forceinline__ bool f_mbar_wait(uint64_t* bar, uint32_t parity, unsigned limit = FT_SPIN_LIMIT) {  // bounded; false when it ran out
     const uint32_t a = f_smem_u32(bar);
-    for (unsigned it = 0; it < FT_SPIN_LIMIT; ++it) {
+    for (unsigned it = 0; it < limit; ++it) {
         uint32_t done;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -356,6 +356,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1) k_gemm_f16_tc(const __grid_cons
     if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(S::TMEM_COLS) : "memory");
 }
 
+// The kernel's bounded wait on a barrier that nobody arrives at (a short limit): it must give up, raise the error word
+// and return, leaving the context usable. Host-made failure for the tests; nothing faults.
+__global__ void k_wait_expiry(int* err) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        f_mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!f_mbar_wait(&bar, 0, 1u << 12)) atomicExch(err, 3);
+    }
+}
+
 // ---------------------------------------------------------------- hi / lo split of the token rows
 
 // One block per token row: optional RMSNorm (src/ops.cpp:155-160, sum of squares in double), scale 2^k that brings the
@@ -447,6 +458,15 @@ bool gemm_f16_tc_usable(const Weight* w, int B) {
     static const int min_b = [] { const char* v = std::getenv("ELB_TC_MIN_ROWS"); return v ? std::max(1, atoi(v)) : 2; }();
     const bool fp16 = w->type == ELB_F16 || (w->type == ELB_Q8_0 && w->f16pair);
     return !off && fp16 && w->n % FT_K == 0 && B >= min_b && f_encode_fn() != nullptr;
+}
+
+int gemm_f16_tc_wait_expiry(cudaStream_t s) {  // launches the probe; gemm_f16_tc_check() after a synchronize reports it
+    int* err_host = f_error_word();
+    int* err_dev = nullptr;
+    if (!err_host || cudaHostGetDevicePointer(&err_dev, err_host, 0) != cudaSuccess) return fail(ELB_ERR_CUDA, "selftest: no error word");
+    k_wait_expiry<<<1, 32, 0, s>>>(err_dev);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
 }
 
 int gemm_f16_tc_check() {  // after a synchronize: did the kernel give up on a wait?

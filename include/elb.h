@@ -47,6 +47,11 @@ int elb_device_sync(int device);
 /* Free and total device memory in bytes (cudaMemGetInfo; the reference's pre-flight check reads the same figures,
  * src/cuda/model_cuda.cu:1578-1591). */
 int elb_device_mem_info(int device, size_t* free_bytes, size_t* total_bytes);
+/* Self-test of the failure path (no counterpart in the reference, whose kernels have no device-side waits): runs the
+ * tensor-core kernels' bounded barrier wait on a barrier that nobody arrives at, with a short limit. The wait must give
+ * up and report: the call returns ELB_ERR_CUDA (elb_last_error names the wait) and the device stays usable; ELB_OK
+ * would mean the expiry went unnoticed. Nothing faults or hangs. */
+int elb_selftest_wait_expiry(int device);
 
 /* ---- weights ------------------------------------------------------------------------------------------------
  * One weight matrix W[rows][n] in a ggml block format, uploaded and re-laid out for the GPU kernels

@@ -160,3 +160,43 @@ def test_rmsnorm_matches_oracle(elb):
         for i in range(3):
             want = ol.rmsnorm(x[i], w, 1e-6)
             assert np.abs(got[i] - want).max() <= 2e-7 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("t", (synth.Q8_0, synth.F16))
+@pytest.mark.parametrize("b", (3, 64, 200))
+def test_matmul_fp16_tensor_cores_long_rows(elb, t, b):
+    """F16 and Q8_0 weights on the tcgen05 kind::f16 kernel with a long row (n = 6144: 24 accumulation segments, k splits
+    when the batch has few tiles): against float64 on the decoded weights the result must be as good as the CPU path's to
+    within 2e-6 of the largest output (a single tensor-memory chain over all of k was 3e-5 off), and twice the same bits."""
+    rng = np.random.default_rng(7 * b + t)
+    rows, n = 384, 6144
+    wb = synth.rand_weight(rng, t, rows, n)
+    x = (rng.normal(size=(b, n)) + 0.5).astype(np.float32)  # a non-zero mean: long sums of one sign
+    w = elb.Weight(t, rows, n, wb, planes=True)
+    y = w.matmul(x, 4)
+    deq = ol.dequant_rows(t, rows, n, wb).astype(np.float64)
+    exact = x.astype(np.float64) @ deq.T
+    scale = np.abs(exact).max(axis=1, keepdims=True)
+    e_gpu = float((np.abs(y - exact) / scale).max())
+    ref = np.stack([ol.matvec(t, rows, n, wb, x[i]) for i in range(0, b, max(1, b // 8))])
+    e_cpu = float((np.abs(ref - exact[::max(1, b // 8)]) / scale[::max(1, b // 8)]).max())
+    print(f"\ntype {t} b {b}: relative error against float64: gpu {e_gpu:.2e}, cpu path {e_cpu:.2e}")
+    assert e_gpu <= e_cpu + 2e-6, (e_gpu, e_cpu)
+    assert np.array_equal(bits(y), bits(w.matmul(x, 4))), "matmul must be deterministic"
+
+
+def test_bounded_wait_expiry_is_reported(elb):
+    """The failure path of the device-side waits, made on the host: a barrier that nobody arrives at. The kernel's
+    bounded wait must give up and raise the error word; the library reports ELB_ERR_CUDA, and the device stays usable."""
+    from exactinfer_b200 import capi
+    rc = capi.lib().elb_selftest_wait_expiry(0)
+    assert rc == capi.ERR_CUDA, rc
+    assert b"wait" in capi.lib().elb_last_error()
+    assert capi.lib().elb_selftest_wait_expiry(0) == capi.ERR_CUDA  # the error word was cleared and is raised again
+    rng = np.random.default_rng(3)
+    wb = synth.rand_weight(rng, synth.F16, 64, 256)
+    x = rng.normal(size=(20, 256)).astype(np.float32)
+    w = elb.Weight(synth.F16, 64, 256, wb)
+    y = w.matmul(x, 4)  # the same kernel family, after the expiry
+    for i in (0, 19):
+        check_matvec(y[i], wb, synth.F16, 64, 256, x[i])
