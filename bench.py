@@ -106,6 +106,35 @@ def parse_args():
     return ap.parse_args()
 
 
+def int8_probe(device: int):
+    """Peak of the int8 tensor pipe as a library GEMM reaches it on this GPU, measured in this run: torch._int_mm at
+    8192^3, best of 10 launches by CUDA events (TOP/s = 2 N^3 / t). The denominator of the prompt pass's roofline: the
+    driver-written peaks file has no int8 figure. None when the probe cannot run."""
+    try:
+        import torch
+        dev = torch.device("cuda", device)
+        n = 8192
+        a = torch.randint(-127, 127, (n, n), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 127, (n, n), dtype=torch.int8, device=dev)
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        del a, b
+        torch.cuda.empty_cache()
+        return 2.0 * n ** 3 / (best / 1000.0) / 1e12
+    except Exception as exc:  # noqa: BLE001 - a missing probe must not cost the benchmark line
+        print(f"bench: int8 probe unavailable ({exc})", file=sys.stderr)
+        return None
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -624,13 +653,25 @@ def run_ours(args):
         out["roofline_gemv"] = micro
         out.setdefault("roofline", micro)
     ops = 2.0 * spec_macs_per_token(spec)
-    out["prefill"]["roofline"] = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 kind::i8) + attention + splits",
-                                  "achieved": ops * out["prefill"]["value"] / 1e12, "peak": INT8_PEAK_TOPS,
-                                  "unit": "TOP/s", "frac": ops * out["prefill"]["value"] / 1e12 / INT8_PEAK_TOPS,
-                                  "peak_kind": "nominal dense int8 (not in MEASURED_PEAKS.json)",
-                                  "frac_of_probe": ops * out["prefill"]["value"] / 1e12 / INT8_PROBE_TOPS,
-                                  "probe": "library int8 GEMM 8192^3 on this pool: 2870 TOP/s",
-                                  "note": "2*M*N*K counted once; the limb planes issue (NL+1)x that on the tensor pipe"}
+    ach_tops = ops * out["prefill"]["value"] / 1e12
+    if spec.layout in ("f16", "q8_0"):  # fp16 tensor pipe: the driver-measured bf16 GEMM peak is the denominator
+        issued = 2 if spec.layout == "f16" else 3
+        peak = float(peaks.get("bf16_tflops", 1590.0))
+        out["prefill"]["roofline"] = {"bound": "tensor", "kernel": "k_gemm_f16_tc (tcgen05 kind::f16) + attention + splits",
+                                      "achieved": ach_tops, "peak": peak, "unit": "TFLOP/s", "frac": ach_tops / peak,
+                                      "peak_kind": peak_kind + " (bf16 GEMM burst figure of MEASURED_PEAKS.json)",
+                                      "issued_over_counted": issued,
+                                      "note": f"2*M*N*K counted once; the fp16 halves issue {issued}x that on the tensor pipe"}
+    else:
+        probe = int8_probe(local)
+        out["prefill"]["roofline"] = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 kind::i8) + attention + splits",
+                                      "achieved": ach_tops, "peak": probe if probe else INT8_PROBE_TOPS, "unit": "TOP/s",
+                                      "frac": ach_tops / (probe if probe else INT8_PROBE_TOPS),
+                                      "peak_kind": "library int8 GEMM (torch._int_mm 8192^3) measured in this run" if probe else
+                                      "library int8 GEMM measured earlier on this pool (the probe could not run)",
+                                      "frac_of_nominal": ach_tops / INT8_PEAK_TOPS, "nominal_dense_int8": INT8_PEAK_TOPS,
+                                      "note": "2*M*N*K counted once; the digit planes and limb columns issue 2*(NL+1) = 8-10x "
+                                              "that on the tensor pipe"}
     if model is not None:
         model.close()
     if parity is not None:

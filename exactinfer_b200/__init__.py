@@ -98,6 +98,14 @@ class Weight:
         check(lib().elb_limb_sums(self._h, capi.fptr(x), nl, ip(P), ip(I), ip(J)))
         return P, I, J
 
+    def matmul_acc(self, x: np.ndarray, nl: int = 4) -> np.ndarray:
+        """The int32 accumulator columns of the tensor-core limb GEMM, A[b][n/256][nl + 1][rows] (elb_matmul_acc)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        b = x.shape[0]
+        A = np.empty((b, self.n // 256, nl + 1, self.rows), dtype=np.int32)
+        check(lib().elb_matmul_acc(self._h, capi.fptr(x), b, nl, A.ctypes.data_as(C.POINTER(C.c_int32))))
+        return A
+
     def close(self):
         if getattr(self, '_h', None):
             lib().elb_weight_destroy(self._h)

@@ -52,6 +52,7 @@ SIGNATURES = {
     "elb_rmsnorm": (C.c_int, [_f32p, _f32p, _f32p, C.c_int, C.c_float, C.c_int]),
     "elb_split_limbs": (C.c_int, [C.c_int, _f32p, C.c_int64, C.c_int64, C.c_int, _i8p, _f32p]),
     "elb_limb_sums": (C.c_int, [_vp, _f32p, C.c_int, _i32p, _i32p, _i32p]),
+    "elb_matmul_acc": (C.c_int, [_vp, _f32p, C.c_int64, C.c_int, _i32p]),
     "elb_model_create": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.POINTER(_vp)]),
     "elb_model_set_tensor": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, _vp, C.c_size_t]),
     "elb_model_finalize": (C.c_int, [_vp]),

@@ -1,6 +1,7 @@
 // extern "C" surface of libelb.so (declared in include/elb.h): status codes in, no exceptions out.
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <vector>
 
 #include "common.cuh"
@@ -184,6 +185,39 @@ static int matmul_dev_on(const Weight* w, const float* d_x, int64_t b, float* d_
     ELB_TRY(split_launch(d_x, w->n, b, int(w->n), nl == 0 ? 4 : nl, nullptr, 0.f, limbs, inv, xs, s));
     if (gemm_tc_usable(w, int(b))) return gemm_tc_launch(w, limbs, inv, xs, int(b), nl == 0 ? 4 : nl, d_y, w->rows, nullptr, EPI_STORE, s);
     return gemm_planes_launch(w, limbs, inv, xs, int(b), d_y, w->rows, nullptr, EPI_STORE, s);
+}
+
+int elb_matmul_acc(const elb_weight* w, const float* x, int64_t b, int nl, int32_t* A) {
+    if (!w || !x || !A) return fail(ELB_ERR_INVALID, "matmul_acc: null argument");
+    const Weight* ww = W(w);
+    if (b <= 0 || b > 4096) return fail(ELB_ERR_INVALID, "matmul_acc: token count out of range");
+    if (nl == 0) nl = 4;
+    if (nl != 3 && nl != 4) return fail(ELB_ERR_INVALID, "matmul_acc: 3 or 4 limbs");
+    ELB_CUDA(cudaSetDevice(ww->device));
+    if (!gemm_tc_usable(ww, int(b))) return fail(ELB_ERR_UNSUPPORTED, "matmul_acc: the weight does not run on the int8 tensor-core kernel");
+    const int64_t rows16 = ww->tiles * 16, nblk = ww->n / 256;
+    const size_t limb_bytes = size_t(4) * b * ww->n, inv_off = (limb_bytes + 255) / 256 * 256;
+    const size_t xs_off = inv_off + (size_t(b) * 4 + 255) / 256 * 256, total = xs_off + size_t(b) * (ww->n / 32) * 4;
+    const size_t nA = size_t(b) * nblk * (nl + 1) * rows16;
+    Dev dx, dy, scratch, dA;
+    ELB_TRY(dx.alloc(size_t(b) * ww->n * 4));
+    ELB_TRY(dy.alloc(size_t(b) * ww->rows * 4));
+    ELB_TRY(scratch.alloc(total));
+    ELB_TRY(dA.alloc(nA * 4));
+    ELB_CUDA(cudaMemset(dA.p, 0, nA * 4));
+    ELB_CUDA(cudaMemcpy(dx.p, x, size_t(b) * ww->n * 4, cudaMemcpyHostToDevice));
+    int8_t* limbs = scratch.as<int8_t>();
+    float* inv = reinterpret_cast<float*>(limbs + inv_off);
+    float* xs = reinterpret_cast<float*>(limbs + xs_off);
+    ELB_TRY(split_launch(dx.as<float>(), ww->n, b, int(ww->n), nl, nullptr, 0.f, limbs, inv, xs, nullptr));
+    ELB_TRY(gemm_tc_launch(ww, limbs, inv, xs, int(b), nl, dy.as<float>(), ww->rows, nullptr, EPI_STORE, nullptr, false, dA.as<int32_t>()));
+    ELB_CUDA(cudaStreamSynchronize(nullptr));
+    ELB_TRY(gemm_tc_check());
+    std::vector<int32_t> tmp(nA);
+    ELB_CUDA(cudaMemcpy(tmp.data(), dA.p, nA * 4, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < size_t(b) * nblk * (nl + 1); ++i)  // rows16 -> rows
+        std::memcpy(A + i * ww->rows, tmp.data() + i * rows16, size_t(ww->rows) * 4);
+    return ELB_OK;
 }
 
 int elb_matmul_dev(const elb_weight* w, const float* d_x, int64_t b, float* d_y, int nl) {

@@ -241,7 +241,8 @@ int gemm_planes_launch(const Weight* w, const int8_t* d_limbs, const float* d_in
 // gemm_tc.cu — tcgen05 path for the two-plane weights (Q4_K, Q6_K)
 bool gemm_tc_usable(const Weight* w, int B);
 int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B, int nl,
-                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl = false);
+                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl = false,
+                   int32_t* d_dbg_acc = nullptr);  // d_dbg_acc: [B][n/256][nl + 1][rows16] accumulator columns (parity checks)
 int gemm_tc_check();
 int gemm_f16_launch(const Weight* w, const float* d_x, int64_t ldx, const float* d_norm_w, float eps, int B, float* d_y,
                     int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s);
@@ -316,7 +317,7 @@ struct TpPeerBuf {
     void* peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int size = 0;
 };
-int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok);
+int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok, bool local_ok = true);
 void tp_peer_free(TpPeerBuf* b, int rank);
 int tp_agree(TpComm* c, bool mine, cudaStream_t s, bool* all);
 

@@ -303,16 +303,34 @@ __global__ void __launch_bounds__(FT_THREADS, 1) k_gemm_f16_tc(const __grid_cons
                     const float4 a = __ldcg(reinterpret_cast<const float4*>(mine + t));
                     accf[t] = a.x; accf[t + 1] = a.y; accf[t + 2] = a.z; accf[t + 3] = a.w;
                 }
-                for (int s2 = 1; s2 < p.splits; ++s2) {
-                    const float* q = mine + size_t(s2) * FT_ROWS * T;
+                // (32 tokens of two partial tiles are requested before the first of them is added: the loop is a chain
+                // of round trips to L2 otherwise; the order of the additions stays split 1, 2, 3, ...)
+                for (int s2 = 1; s2 < p.splits; s2 += 2) {
+                    const float* q0 = mine + size_t(s2) * FT_ROWS * T;
+                    const bool two = s2 + 1 < p.splits;
+                    const float* q1 = two ? q0 + size_t(FT_ROWS) * T : q0;
 #pragma unroll
-                    for (int t = 0; t < T; t += 4) {
-                        const float4 a = __ldcg(reinterpret_cast<const float4*>(q + t));
-                        accf[t] += a.x; accf[t + 1] += a.y; accf[t + 2] += a.z; accf[t + 3] += a.w;
+                    for (int c = 0; c < T; c += 32) {
+                        float4 a[8], b[8];
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            a[t] = __ldcg(reinterpret_cast<const float4*>(q0 + c) + t);
+                            b[t] = __ldcg(reinterpret_cast<const float4*>(q1 + c) + t);
+                        }
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            accf[c + 4 * t] += a[t].x; accf[c + 4 * t + 1] += a[t].y; accf[c + 4 * t + 2] += a[t].z; accf[c + 4 * t + 3] += a[t].w;
+                        }
+                        if (two) {
+#pragma unroll
+                            for (int t = 0; t < 8; ++t) {
+                                accf[c + 4 * t] += b[t].x; accf[c + 4 * t + 1] += b[t].y; accf[c + 4 * t + 2] += b[t].z; accf[c + 4 * t + 3] += b[t].w;
+                            }
+                        }
                     }
                 }
             }
-            // The finished tile goes back to tensor memory, from where a compact loop writes it out 16 tokens at a
+            // The finished tile goes back to tensor memory, from where a compact loop writes it out 32 tokens at a
             // time (a loop over the register array would have to be unrolled: code that runs once per tile, straight
             // from instruction memory).
             const uint32_t tdone = tmem_base + 2 * T + (uint32_t(warp * 32) << 16);
@@ -320,20 +338,20 @@ __global__ void __launch_bounds__(FT_THREADS, 1) k_gemm_f16_tc(const __grid_cons
             for (int c = 0; c < T; c += 32) f_tmem_st32(tdone + c, *reinterpret_cast<const float(*)[32]>(&accf[c]));
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 #pragma unroll 1
-            for (int c = 0; c < T; c += 16) {
-                float v[16];
-                f_tmem_ld16(tdone + c, v);
-                // every load of the 16 tokens before the first store: Y may be the residual stream itself, and a load
+            for (int c = 0; c < T; c += 32) {
+                float v[32];
+                f_tmem_ld32(tdone + c, v);
+                // every load of the 32 tokens before the first store: Y may be the residual stream itself, and a load
                 // that has to wait for the store before it turns the chunk into a chain of memory round trips
-                float sc[16], r[16];
+                float sc[32], r[32];
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
+                for (int t = 0; t < 32; ++t) {
                     const int tok = tok0 + c + t;
                     sc[t] = tok < p.B ? __ldcg(p.inv_scale + tok) : 0.f;
                     r[t] = p.epilogue == EPI_ADD && tok < p.B && R < p.rows ? __ldcg(p.resid + int64_t(tok) * p.ldy + R) : 0.f;
                 }
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
+                for (int t = 0; t < 32; ++t) {
                     const int tok = tok0 + c + t;
                     const bool tok_ok = tok < p.B;
                     const float y = v[t] * sc[t];

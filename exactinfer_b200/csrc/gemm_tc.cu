@@ -147,6 +147,8 @@ struct TcParams {
                                // launch replayed from a graph numbers itself like any other
     int* err;
     int prof;
+    int32_t* dbgA;             // parity checks: the int32 accumulator columns as they leave tensor memory,
+                               // [B][n/256][NL + 1][rows16]; null in normal use
 };
 
 // A grid of one CTA per SM walks the output tiles in whole waves; the tiles that do not fill a wave would leave most
@@ -200,7 +202,9 @@ template <int NL, int TT> struct TcShape {
     static constexpr int SMEM = LIMB_AREA + TC_STAGES * 2 * A_BYTES + 256 + XS_BYTES + SC_BYTES + 1024;  // + barriers + slack
 };
 
-template <int NL, int TT>
+// DBG: also writes the int32 accumulator columns to p.dbgA (parity checks; its own instantiation, because the extra
+// addressing does not fit into the 96 registers of the production kernel without spills)
+template <int NL, int TT, bool DBG = false>
 __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapW,
                                                           const __grid_constant__ CUtensorMap mapX, const TcParams p) {
     using S = TcShape<NL, TT>;
@@ -397,6 +401,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             // src/cuda/model_cuda.cu:962-994); the top column of four limbs is small enough for the exact
             // add-a-constant conversion
             auto join = [&](const int(&w)[NL + 1][4], const int t0) {
+                if constexpr (DBG) {
+#pragma unroll
+                    for (int j = 0; j <= NL; ++j)
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const int tok = tok0 + th * TH + t0 + t;
+                            if (tok < p.B && R < p.rows16) p.dbgA[((int64_t(tok) * nblk + kb) * (NL + 1) + j) * p.rows16 + R] = w[j][t];
+                        }
+                }
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
                     const int i01 = w[0][t] + (w[1][t] << 8), i23 = w[2][t] + (w[3][t] << 8);
@@ -423,6 +436,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 }
                 tmem_ld_wait();
                 release();
+                if constexpr (DBG) {
+#pragma unroll
+                    for (int j = 0; j <= NL; ++j)
+#pragma unroll
+                        for (int t = 0; t < TH; ++t) {
+                            const int tok = tok0 + th * TH + t;
+                            if (tok < p.B && R < p.rows16) p.dbgA[((int64_t(tok) * nblk + kb) * (NL + 1) + j) * p.rows16 + R] = v[j][t];
+                        }
+                }
 #pragma unroll
                 for (int t = 0; t < TH; ++t) {
                     const int i01 = v[0][t] + (v[1][t] << 8), i23 = v[2][t] + (v[3][t] << 8);
@@ -613,7 +635,7 @@ int gemm_tc_check() {  // after a synchronize: did a tensor-core GEMM give up on
 }
 
 int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_scale, const float* d_xsum, int B, int nl,
-                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl) {
+                   float* d_y, int64_t ldy, const float* d_resid, int epilogue, cudaStream_t s, bool pdl, int32_t* d_dbg_acc) {
     if (!gemm_tc_usable(w, B)) return fail(ELB_ERR_STATE, "matmul: tensor-core path not usable for this weight");
     if (epilogue == EPI_SILU && !w->pair) return fail(ELB_ERR_INVALID, "matmul: SwiGLU epilogue needs a paired weight");
     int* err_host = error_word();
@@ -650,7 +672,7 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
         ELB_CUDA(cudaMemset(ctl[w->device], 0, 2 * sizeof(unsigned)));
     }
     TcParams p{w->pl_d, w->pl_dm, d_xsum, d_inv_scale, d_y, d_resid, rows16, w->rows, ldy, B, int(w->n), epilogue,
-               row_tiles, tok_tiles, waves, per, scratch[w->device], flags[w->device], ctl[w->device], err_dev, tc_prof_on() ? 1 : 0};
+               row_tiles, tok_tiles, waves, per, scratch[w->device], flags[w->device], ctl[w->device], err_dev, tc_prof_on() ? 1 : 0, d_dbg_acc};
     const dim3 grid{unsigned(grid_n)};
     auto launch = [&](auto kernel, int smem) -> int {
         ELB_TRY(ensure_dyn_smem(reinterpret_cast<const void*>(kernel), size_t(smem)));
@@ -667,8 +689,11 @@ int gemm_tc_launch(const Weight* w, const int8_t* d_limbs, const float* d_inv_sc
         ELB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mapW, mapX, p));
         return ELB_OK;
     };
-#define ELB_TC_CASE(NL_, T_) \
-    if ((four ? 4 : 3) == NL_ && T == T_) ELB_TRY(launch(k_gemm_tc<NL_, T_>, TcShape<NL_, T_>::SMEM));
+#define ELB_TC_CASE(NL_, T_)                                                                            \
+    if ((four ? 4 : 3) == NL_ && T == T_) {                                                             \
+        if (d_dbg_acc) ELB_TRY(launch(k_gemm_tc<NL_, T_, true>, TcShape<NL_, T_>::SMEM));               \
+        else ELB_TRY(launch(k_gemm_tc<NL_, T_, false>, TcShape<NL_, T_>::SMEM));                        \
+    }
     ELB_TC_CASE(3, 16) ELB_TC_CASE(3, 32) ELB_TC_CASE(3, 64) ELB_TC_CASE(4, 16) ELB_TC_CASE(4, 32) ELB_TC_CASE(4, 48)
 #undef ELB_TC_CASE
     ELB_CUDA(cudaGetLastError());

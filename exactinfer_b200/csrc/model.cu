@@ -429,7 +429,9 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits, const
 
 // Fill the parameters of the persistent decode kernel; it is used when every weight is quantized and the step's
 // shared memory (rings + the longest activation's limbs) fits on one SM. ELB_NO_MEGA=1 keeps the kernel-per-op path.
-int setup_decode_kernel(Model* m) {
+// local_ok: false when this rank already failed earlier in its set-up. Under tensor parallelism it still walks through
+// the collectives of this function (the other ranks are on their way into them) with "failed" as its answer.
+int setup_decode_kernel(Model* m, bool local_ok = true) {
     const elb_config& c = m->cfg;
     if (env_on("ELB_NO_MEGA") || (m->tp.size > 1 && env_on("ELB_TP_NO_MEGA"))) return ELB_OK;
     DeviceInfo di;
@@ -517,7 +519,11 @@ int setup_decode_kernel(Model* m) {
     p.kc = m->kcache;  // sequence 0
     p.vc = m->vcache;
     p.kv_stride = size_t(m->n_seq) * m->n_ctx * KD;
-    ELB_CUDA(cudaMalloc(&m->xbuf, size_t(2) * E * sizeof(float)));  // residual stream [2][E]
+    if (local_ok && cudaMalloc(&m->xbuf, size_t(2) * E * sizeof(float)) != cudaSuccess) {  // residual stream [2][E]
+        cudaGetLastError();
+        local_ok = false;
+        fail(ELB_ERR_MEMORY, "decode kernel set-up: out of device memory");
+    }
     // exchange area: flags, partial sums [2 sets][ranks][2][E], logits; mapped into every rank under tensor parallelism
     const int N = m->tp.size;
     const int pv = 2;  // (one vector per rank with whole tiles measured slower at two ranks: 6.74 against 6.57 ms on the 32B shape)
@@ -526,23 +532,29 @@ int setup_decode_kernel(Model* m) {
     const size_t xbytes = 256 + (part_floats + logit_floats) * sizeof(float);
     if (N > 1) {
         bool mapped = false;
-        ELB_TRY(tp_peer_alloc(m->comm, m->device, xbytes, m->stream, &m->xarea, &mapped));
+        ELB_TRY(tp_peer_alloc(m->comm, m->device, xbytes, m->stream, &m->xarea, &mapped, local_ok));
+        if (!local_ok) return ELB_ERR_MEMORY;  // (every rank has seen it: none of them maps, none waits for this one)
         if (!mapped) return ELB_OK;  // no peer mapping: the kernel-per-op path with NCCL stays
     } else {
+        if (!local_ok) return ELB_ERR_MEMORY;
         ELB_CUDA(cudaMalloc(&m->xarea.local, xbytes));
         ELB_CUDA(cudaMemset(m->xarea.local, 0, xbytes));
         m->xarea.peer[0] = m->xarea.local;
         m->xarea.size = 1;
     }
-    ELB_CUDA(cudaMalloc(&m->xctl, 2 * sizeof(unsigned)));
-    ELB_CUDA(cudaMemset(m->xctl, 0, 2 * sizeof(unsigned)));
-    ELB_CUDA(cudaMalloc(&m->sync_words, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
-    ELB_CUDA(cudaMemset(m->sync_words, 0, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
-    ELB_CUDA(cudaMalloc(&m->pos_steps, size_t(m->max_batch) * sizeof(int)));
-    ELB_CUDA(cudaHostAlloc(&m->err_host, sizeof(int), cudaHostAllocMapped));
-    *m->err_host = 0;
     int* err_dev = nullptr;
-    ELB_CUDA(cudaHostGetDevicePointer(&err_dev, m->err_host, 0));
+    auto local_words = [&]() -> int {
+        ELB_CUDA(cudaMalloc(&m->xctl, 2 * sizeof(unsigned)));
+        ELB_CUDA(cudaMemset(m->xctl, 0, 2 * sizeof(unsigned)));
+        ELB_CUDA(cudaMalloc(&m->sync_words, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
+        ELB_CUDA(cudaMemset(m->sync_words, 0, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
+        ELB_CUDA(cudaMalloc(&m->pos_steps, size_t(m->max_batch) * sizeof(int)));
+        ELB_CUDA(cudaHostAlloc(&m->err_host, sizeof(int), cudaHostAllocMapped));
+        *m->err_host = 0;
+        ELB_CUDA(cudaHostGetDevicePointer(&err_dev, m->err_host, 0));
+        return ELB_OK;
+    };
+    int rc_local = local_words();  // a failure is carried to the agreement below, not returned before it
     p.n_layer = c.n_layer; p.n_qkv = int(nq);
     p.output_norm = m->output_norm;
     p.embd = m->embd->tiled; p.embd_type = m->embd->type;
@@ -581,23 +593,29 @@ int setup_decode_kernel(Model* m) {
         if (m->dk_slot >= min_ring) ELB_TRY(decode_step_fits(p, m->dk_slot, m->device, &fits));
         return ELB_OK;
     };
-    ELB_TRY(try_fit());
-    if ((!fits || env_on("ELB_DK_GACT")) && Fmax > std::max(E, QD)) {  // (the variable forces the mode, for tests)
-        // the limbs of the FFN activation do not fit next to the rings: keep them in global memory (one more grid barrier
-        // per layer, ffn_down reads them through L2); every rank decides from the longest FFN cut, so all decide alike
-        p.act_global = 1;
-        p.n_max = std::max(E, QD);
+    auto local_fit = [&]() -> int {
         ELB_TRY(try_fit());
-        if (fits) {
-            ELB_CUDA(cudaMalloc(&m->gact, decode_act_bytes(Fmax)));
-            p.gact = m->gact;
+        if ((!fits || env_on("ELB_DK_GACT")) && Fmax > std::max(E, QD)) {  // (the variable forces the mode, for tests)
+            // the limbs of the FFN activation do not fit next to the rings: keep them in global memory (one more grid
+            // barrier per layer, ffn_down reads them through L2); every rank decides from the longest FFN cut, so all
+            // decide alike
+            p.act_global = 1;
+            p.n_max = std::max(E, QD);
+            ELB_TRY(try_fit());
+            if (fits) {
+                ELB_CUDA(cudaMalloc(&m->gact, decode_act_bytes(Fmax)));
+                p.gact = m->gact;
+            }
         }
-    }
-    fits = fits && small;
+        return ELB_OK;
+    };
+    if (rc_local == ELB_OK) rc_local = local_fit();
+    fits = fits && small && rc_local == ELB_OK;
     int coop = 0;
-    ELB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device) != cudaSuccess) { cudaGetLastError(); coop = 0; }
     bool all = false;  // under tensor parallelism every rank must take the same path: its kernels wait for the peers'
     ELB_TRY(tp_agree(m->comm, fits && coop, m->stream, &all));
+    if (rc_local != ELB_OK) return rc_local;  // (after the agreement: the other ranks fell back to the kernel-per-op path together)
     m->use_mega = all;
     if (m->use_mega) m->logits_step = p.logits_peer[m->tp.rank];  // the kernel leaves the logits in the exchange area
     if (m->use_mega && env_on("ELB_DK_PROF")) {
@@ -698,9 +716,8 @@ void model_destroy(Model* m) {
     delete m;
 }
 
-int model_finalize(Model* m) {
-    if (!m) return fail(ELB_ERR_INVALID, "finalize: null model");
-    if (m->finalized) return fail(ELB_ERR_STATE, "finalize: called twice");
+// everything of finalize that concerns this rank alone: uploads, re-layout, allocations; no collective in here
+static int finalize_local(Model* m) {
     ELB_CUDA(cudaSetDevice(m->device));
     const elb_config& c = m->cfg;
     const int64_t E = c.n_embd, V = c.n_vocab, B = m->max_batch;
@@ -837,7 +854,6 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->act, size_t(B) * F * 4));
     ELB_CUDA(cudaMalloc(&m->logits, size_t(std::max<int64_t>(V, m->tp.vchunk * m->tp.size)) * 4));
     if (m->tp.size > 1) {
-        if (!env_on("ELB_TP_NCCL")) ELB_TRY(tp_reduce_create(m->comm, m->device, m->tp.rank, m->tp.size, int(E), m->stream, &m->tpr));
         ELB_CUDA(cudaMalloc(&m->xr, size_t(B) * E * 4));
         ELB_CUDA(cudaMalloc(&m->logits_local, size_t(m->tp.vchunk) * 4));
     }
@@ -886,7 +902,43 @@ int model_finalize(Model* m) {
     ELB_CUDA(cudaMalloc(&m->ap_part, attn_prefill_scratch_floats(m->max_batch, m->H, m->HKV) * sizeof(float)));
     ELB_CUDA(cudaMalloc(&m->ap_counters, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->ap_counters, 0, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
-    ELB_TRY(setup_decode_kernel(m));
+    // test hook: a rank that fails on its own once everything local is in place (as it would running out of memory)
+    if (const char* v = std::getenv("ELB_TEST_FAIL_FINALIZE_RANK"))
+        if (m->tp.size > 1 && std::atoi(v) == m->tp.rank) return fail(ELB_ERR_MEMORY, "finalize: injected failure of this rank (test)");
+    return ELB_OK;
+}
+
+// Under tensor parallelism the ranks set up peer memory with collectives. A rank that fails on its own (out of memory
+// while uploading, say) must not leave the others waiting in one: the ranks first agree that the local part worked
+// everywhere, every rank then passes through the same collectives whatever happens to it locally, and a last agreement
+// makes the outcome the same on all of them - all finalized, or an error on every rank.
+int model_finalize(Model* m) {
+    if (!m) return fail(ELB_ERR_INVALID, "finalize: null model");
+    if (m->finalized) return fail(ELB_ERR_STATE, "finalize: called twice");
+    int rc = finalize_local(m);
+    const bool tp = m->tp.size > 1 && m->comm;
+    const char* other = "finalize: another rank of the tensor-parallel group failed to set up its model";
+    if (tp) {
+        bool all = false;
+        const int rc_a = tp_agree(m->comm, rc == ELB_OK, m->stream, &all);
+        if (rc != ELB_OK) return rc;
+        if (rc_a != ELB_OK) return rc_a;
+        if (!all) return fail(ELB_ERR_STATE, other);
+        if (!env_on("ELB_TP_NCCL")) rc = tp_reduce_create(m->comm, m->device, m->tp.rank, m->tp.size, m->cfg.n_embd, m->stream, &m->tpr);
+    } else if (rc != ELB_OK) {
+        return rc;
+    }
+    const int rc_k = setup_decode_kernel(m, rc == ELB_OK);
+    if (rc == ELB_OK) rc = rc_k;
+    if (tp) {
+        bool all = false;
+        const int rc_a = tp_agree(m->comm, rc == ELB_OK, m->stream, &all);
+        if (rc != ELB_OK) return rc;
+        if (rc_a != ELB_OK) return rc_a;
+        if (!all) return fail(ELB_ERR_STATE, other);
+    } else if (rc != ELB_OK) {
+        return rc;
+    }
     m->pending.clear();
     m->pending.shrink_to_fit();
     m->shard_store.clear();

@@ -139,7 +139,11 @@ int nccl_fail(Nccl* n, ncclResult_t r, const char* what) {
 struct TpComm {
     ncclComm_t comm = nullptr;
     int rank = 0, size = 1;
+    // staging for the small set-up collectives (IPC handles, agreement flags), allocated with the communicator so that
+    // a rank whose later allocations fail can still take part in them: [68 send][68 * 8 receive][16 flag]
+    uint8_t* d_small = nullptr;
 };
+constexpr size_t TP_SMALL_RECV = 128, TP_SMALL_FLAG = 128 + 68 * 8 + 32, TP_SMALL_BYTES = TP_SMALL_FLAG + 16;
 
 int tp_unique_id(void* id128) {
     static_assert(sizeof(ncclUniqueId) == 128, "NCCL unique id is 128 bytes");
@@ -164,6 +168,11 @@ int tp_comm_create(int device, int rank, int size, const void* id128, TpComm** o
     c->rank = rank; c->size = size;
     const ncclResult_t r = n->CommInitRank(&c->comm, size, id, rank);
     if (r != ncclSuccess) { delete c; return nccl_fail(n, r, "ncclCommInitRank"); }
+    if (cudaMalloc(&c->d_small, TP_SMALL_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        tp_comm_destroy(c);
+        return fail(ELB_ERR_MEMORY, "tp_comm_create: out of device memory");
+    }
     *out = c;
     return ELB_OK;
 }
@@ -171,6 +180,7 @@ int tp_comm_create(int device, int rank, int size, const void* id128, TpComm** o
 void tp_comm_destroy(TpComm* c) {
     if (!c) return;
     if (c->comm) nccl()->CommDestroy(c->comm);
+    cudaFree(c->d_small);
     delete c;
 }
 
@@ -189,30 +199,34 @@ int tp_all_gather(TpComm* c, const float* in, float* out, size_t count_per_rank,
 // Every rank allocates `bytes` of device memory, zeroes it, and the ranks exchange CUDA IPC handles through the
 // communicator; peer[r] is rank r's buffer as mapped into this process (peer[rank] = the local one). `ok` comes back
 // false on every rank when any rank could not map a peer (the caller then keeps to NCCL).
-int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok) {
+int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf* out, bool* ok, bool local_ok) {
     *ok = false;
     *out = TpPeerBuf{};
     if (!c || c->size < 2 || c->size > 8) return ELB_OK;
-    ELB_CUDA(cudaSetDevice(device));
+    // A rank whose own part fails (out of memory, no IPC handle) does NOT return before the two collectives below: the
+    // other ranks are on their way into them. It takes part with "failed" as its answer, and every rank sees it.
+    int good = local_ok ? 1 : 0;
+    if (cudaSetDevice(device) != cudaSuccess) good = 0;
     out->size = c->size;
-    ELB_CUDA(cudaMalloc(&out->local, bytes));
-    ELB_CUDA(cudaMemset(out->local, 0, bytes));
-    cudaIpcMemHandle_t mine;
-    int good = cudaIpcGetMemHandle(&mine, out->local) == cudaSuccess ? 1 : 0;
+    if (good && (cudaMalloc(&out->local, bytes) != cudaSuccess || cudaMemset(out->local, 0, bytes) != cudaSuccess)) good = 0;
+    cudaIpcMemHandle_t mine{};
+    if (good && cudaIpcGetMemHandle(&mine, out->local) != cudaSuccess) good = 0;
     if (!good) cudaGetLastError();
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle is 64 bytes");
-    uint8_t *d_send = nullptr, *d_recv = nullptr;
-    ELB_CUDA(cudaMalloc(&d_send, 64 + 4));
-    ELB_CUDA(cudaMalloc(&d_recv, size_t(68) * c->size));
+    uint8_t *d_send = c->d_small, *d_recv = c->d_small + TP_SMALL_RECV;
+    float* d_flag = reinterpret_cast<float*>(c->d_small + TP_SMALL_FLAG);
     uint8_t pack[68];
     std::memcpy(pack, &mine, 64);
     std::memcpy(pack + 64, &good, 4);
-    ELB_CUDA(cudaMemcpyAsync(d_send, pack, 68, cudaMemcpyHostToDevice, s));
-    ncclResult_t r = nccl()->AllGather(d_send, d_recv, 68, ncclInt8, c->comm, s);
-    if (r != ncclSuccess) return nccl_fail(nccl(), r, "ncclAllGather (peer handles)");
     std::vector<uint8_t> all(size_t(68) * c->size);
-    ELB_CUDA(cudaMemcpyAsync(all.data(), d_recv, all.size(), cudaMemcpyDeviceToHost, s));
-    ELB_CUDA(cudaStreamSynchronize(s));
+    int rc = ELB_OK;
+    auto cleanup = [&](int code) { tp_peer_free(out, c->rank); return code; };
+    // (a failing copy or collective here is a broken stream or communicator: nothing the other ranks could be told through)
+    if (cudaMemcpyAsync(d_send, pack, 68, cudaMemcpyHostToDevice, s) != cudaSuccess) return cleanup(fail(ELB_ERR_CUDA, "tp_peer_alloc: staging copy failed"));
+    ncclResult_t r = nccl()->AllGather(d_send, d_recv, 68, ncclInt8, c->comm, s);
+    if (r != ncclSuccess) return cleanup(nccl_fail(nccl(), r, "ncclAllGather (peer handles)"));
+    if (cudaMemcpyAsync(all.data(), d_recv, all.size(), cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+        return cleanup(fail(ELB_ERR_CUDA, "tp_peer_alloc: reading the handles failed"));
     for (int p = 0; p < c->size; ++p) {
         int g = 0;
         std::memcpy(&g, all.data() + size_t(p) * 68 + 64, 4);
@@ -229,31 +243,27 @@ int tp_peer_alloc(TpComm* c, int device, size_t bytes, cudaStream_t s, TpPeerBuf
         }
     }
     // every rank must take the same path: agree on the outcome
-    float flag = good ? 0.f : 1.f, *d_flag = reinterpret_cast<float*>(d_send);
-    ELB_CUDA(cudaMemcpyAsync(d_flag, &flag, 4, cudaMemcpyHostToDevice, s));
+    float flag = good ? 0.f : 1.f;
+    if (cudaMemcpyAsync(d_flag, &flag, 4, cudaMemcpyHostToDevice, s) != cudaSuccess) return cleanup(fail(ELB_ERR_CUDA, "tp_peer_alloc: staging copy failed"));
     r = nccl()->AllReduce(d_flag, d_flag, 1, ncclFloat, ncclSum, c->comm, s);
-    if (r != ncclSuccess) return nccl_fail(nccl(), r, "ncclAllReduce (peer mapping outcome)");
-    ELB_CUDA(cudaMemcpyAsync(&flag, d_flag, 4, cudaMemcpyDeviceToHost, s));
-    ELB_CUDA(cudaStreamSynchronize(s));
-    cudaFree(d_send);
-    cudaFree(d_recv);
+    if (r != ncclSuccess) return cleanup(nccl_fail(nccl(), r, "ncclAllReduce (peer mapping outcome)"));
+    if (cudaMemcpyAsync(&flag, d_flag, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+        return cleanup(fail(ELB_ERR_CUDA, "tp_peer_alloc: reading the outcome failed"));
     *ok = flag == 0.f;
     if (!*ok) tp_peer_free(out, c->rank);
-    return ELB_OK;
+    return rc;
 }
 
 // true on every rank only when `mine` is true on every rank (collective; one rank: its own answer)
 int tp_agree(TpComm* c, bool mine, cudaStream_t s, bool* all) {
     *all = mine;
     if (!c || c->size < 2) return ELB_OK;
-    float flag = mine ? 0.f : 1.f, *d_flag = nullptr;
-    ELB_CUDA(cudaMalloc(&d_flag, sizeof(float)));
-    ELB_CUDA(cudaMemcpyAsync(d_flag, &flag, sizeof(float), cudaMemcpyHostToDevice, s));
+    float flag = mine ? 0.f : 1.f, *d_flag = reinterpret_cast<float*>(c->d_small + TP_SMALL_FLAG);
+    if (cudaMemcpyAsync(d_flag, &flag, sizeof(float), cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(ELB_ERR_CUDA, "tp_agree: staging copy failed");
     const ncclResult_t r = nccl()->AllReduce(d_flag, d_flag, 1, ncclFloat, ncclSum, c->comm, s);
-    if (r != ncclSuccess) { cudaFree(d_flag); return nccl_fail(nccl(), r, "ncclAllReduce (agreement)"); }
-    ELB_CUDA(cudaMemcpyAsync(&flag, d_flag, sizeof(float), cudaMemcpyDeviceToHost, s));
-    ELB_CUDA(cudaStreamSynchronize(s));
-    cudaFree(d_flag);
+    if (r != ncclSuccess) return nccl_fail(nccl(), r, "ncclAllReduce (agreement)");
+    if (cudaMemcpyAsync(&flag, d_flag, sizeof(float), cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+        return fail(ELB_ERR_CUDA, "tp_agree: reading the outcome failed");
     *all = flag == 0.f;
     return ELB_OK;
 }

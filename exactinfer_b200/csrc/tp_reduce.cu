@@ -123,16 +123,22 @@ int tp_reduce_create(TpComm* c, int device, int rank, int size, int n_max, cudaS
     r->rank = rank; r->size = size; r->n_max = n_max;
     bool ok = false;
     const size_t bytes = TPR_FLAG_BYTES + size_t(2) * size * n_max * sizeof(float);
-    const int rc = tp_peer_alloc(c, device, bytes, s, &r->buf, &ok);
-    if (rc != ELB_OK || !ok) { delete r; return rc; }
-    if (cudaMalloc(&r->seq, sizeof(unsigned)) != cudaSuccess || cudaMemset(r->seq, 0, sizeof(unsigned)) != cudaSuccess ||
-        cudaHostAlloc(&r->err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
-        cudaGetLastError();
-        tp_reduce_destroy(r);
-        return fail(ELB_ERR_MEMORY, "tp_reduce: out of memory");
+    // the local pieces first, so that a rank that cannot have them says so IN the collectives of tp_peer_alloc
+    // instead of leaving before them
+    bool local_ok = cudaSetDevice(device) == cudaSuccess && cudaMalloc(&r->seq, sizeof(unsigned)) == cudaSuccess &&
+                    cudaMemset(r->seq, 0, sizeof(unsigned)) == cudaSuccess &&
+                    cudaHostAlloc(&r->err_host, sizeof(int), cudaHostAllocMapped) == cudaSuccess;
+    if (local_ok) {
+        *r->err_host = 0;
+        local_ok = cudaHostGetDevicePointer(&r->err_dev, r->err_host, 0) == cudaSuccess;
     }
-    *r->err_host = 0;
-    ELB_CUDA(cudaHostGetDevicePointer(&r->err_dev, r->err_host, 0));
+    if (!local_ok) cudaGetLastError();
+    const int rc = tp_peer_alloc(c, device, bytes, s, &r->buf, &ok, local_ok);
+    if (rc != ELB_OK || !ok) {  // every rank gets here together: all keep to NCCL, the rank that failed reports why
+        tp_reduce_destroy(r);
+        if (rc != ELB_OK) return rc;
+        return local_ok ? ELB_OK : fail(ELB_ERR_MEMORY, "tp_reduce: out of memory");
+    }
     *out = r;
     return ELB_OK;
 }

@@ -113,6 +113,13 @@ int elb_split_limbs(int device, const float* x, int64_t b, int64_t n, int nl, in
  *   J[rows][n/blk][nl]  = Q4_K only: sum of min * (sum of the limb over the sub-block); zero otherwise
  * Any of P, I, J may be NULL. Computed by the same device code path as elb_matvec. */
 int elb_limb_sums(const elb_weight* w, const float* x, int nl, int32_t* P, int32_t* I, int32_t* J);
+/* The same check for the multi-token kernel (k_gemm_tc of the reference forms these sums in mma.sync fragments,
+ * src/cuda/model_cuda.cu:402-492; here they are tcgen05 accumulators in tensor memory): the int32 accumulator columns
+ * of every (token, 256-block) as they leave tensor memory, A[b][n/256][nl + 1][rows]. With the weight w = sc * q written
+ * as balanced digits w = w0 + 256 w1, column c holds sum(w0 * limb_c + w1 * limb_(c-1)), so that
+ * sum over c of 256^c A[..][c][row] = sum over l of 256^l I[row][block][l] of elb_limb_sums, exactly.
+ * Q4_K and Q6_K weights created with ELB_W_PLANES, b >= 16, nl = 3 or 4 (0 = 4); ELB_ERR_UNSUPPORTED otherwise. */
+int elb_matmul_acc(const elb_weight* w, const float* x, int64_t b, int nl, int32_t* A);
 
 /* ---- model (el::Backend, src/model.h:42-57) -------------------------------------------------------------------*/
 typedef struct {

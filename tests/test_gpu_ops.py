@@ -200,3 +200,26 @@ def test_bounded_wait_expiry_is_reported(elb):
     y = w.matmul(x, 4)  # the same kernel family, after the expiry
     for i in (0, 19):
         check_matvec(y[i], wb, synth.F16, 64, 256, x[i])
+
+
+@pytest.mark.parametrize("t", (synth.Q4_K, synth.Q6_K))
+@pytest.mark.parametrize("b,nl", ((24, 4), (70, 3), (200, 4)))
+def test_matmul_accumulator_columns_bit_exact(elb, t, b, nl):
+    """The int32 accumulators of the tcgen05 limb GEMM as they leave tensor memory, joined over their columns, are the
+    block sums of the limb products: sum_c 256^c A[token][block][c][row] == sum_l 256^l I[row][block][l] with I from the
+    oracle's integer path, for every token, row and 256-block, exactly (no tolerance: these are integers)."""
+    rng = np.random.default_rng(11 * b + t)
+    rows, n = 200, 1024
+    wb = synth.rand_weight(rng, t, rows, n)
+    x = rng.normal(size=(b, n)).astype(np.float32)
+    x[1] *= 300.0
+    w = elb.Weight(t, rows, n, wb, planes=True)
+    A = w.matmul_acc(x, nl).astype(np.int64)  # [b][nblk][nl + 1][rows]
+    got = sum(A[:, :, c, :] << (8 * c) for c in range(nl + 1))  # [b][nblk][rows]
+    assert np.abs(A).max() < 2 ** 23, "a column must stay below the bound the join relies on"
+    for i in range(b):
+        limbs, _, _ = ol.split_limbs(x[i], nl)
+        I, _ = ol.limb_block_sums(t, rows, n, wb, limbs)  # [rows][nblk][nl]
+        want = sum(I[:, :, l].astype(np.int64) << (8 * l) for l in range(nl))
+        assert np.array_equal(got[i], want.T), f"token {i}"
+    w.close()

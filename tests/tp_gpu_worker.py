@@ -1,6 +1,7 @@
 """One rank of the 2-GPU tensor-parallel parity check (started by test_gpu_tp.py): Backend(tp=...) on GPU `rank`, a prompt
 chunk then single-token steps, every rank compares the gathered logits with the CPU oracle's whole-model result.
-usage: tp_gpu_worker.py RANK SIZE ID_FILE LAYOUT [gguf]   (gguf: every rank loads the same GGUF file itself)"""
+usage: tp_gpu_worker.py RANK SIZE ID_FILE LAYOUT [gguf|fail]   (gguf: every rank loads the same GGUF file itself;
+fail: one rank's set-up is made to fail on the host (ELB_TEST_FAIL_FINALIZE_RANK) and EVERY rank must get an error)"""
 import os
 import sys
 import time
@@ -49,6 +50,13 @@ def main():
                 raise SystemExit("rank 0 never wrote the model file")
             time.sleep(0.05)
         gpu = e.Backend.from_gguf(path, n_prompt + n_decode + 1, device=rank, tp=(rank, size, ident))
+    elif len(sys.argv) > 5 and sys.argv[5] == "fail":
+        try:
+            e.Backend(spec, tens, n_prompt + n_decode + 1, device=rank, tp=(rank, size, ident))
+        except (MemoryError, RuntimeError) as exc:
+            print(f"rank {rank}: set-up failed as it must: {exc}")
+            return
+        raise SystemExit(f"rank {rank}: the model came up although a rank of the group failed")
     else:
         gpu = e.Backend(spec, tens, n_prompt + n_decode + 1, device=rank, tp=(rank, size, ident))
     cpu = ol.OracleModel(spec, tens, n_prompt + n_decode + 1)
