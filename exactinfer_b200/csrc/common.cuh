@@ -277,6 +277,11 @@ int attn_rows_launch(const float* qkv, int64_t ld, const float* kc, const float*
 int attn_prefill_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att,
                         int pos0, int B, int H, int HKV, float scale, cudaStream_t s, float* part = nullptr,
                         unsigned* counters = nullptr);
+// attn_tc.cu - the same on the tensor cores (fp16 pairs); kv16: attn_prefill_tc_scratch_halves(n_ctx, HKV * 128) halves
+bool attn_prefill_tc_usable(int H, int HKV, int64_t ld, int64_t ld_att);
+size_t attn_prefill_tc_scratch_halves(int n_ctx, int KD);
+int attn_prefill_tc_launch(const float* qkv, int64_t ld, const float* kc, const float* vc, float* att, int64_t ld_att, int pos0,
+                           int B, int H, int HKV, float scale, cudaStream_t s, float* part, unsigned* counters, void* kv16);
 size_t attn_prefill_scratch_floats(int max_batch, int H, int HKV);  // `part` of attn_prefill_launch
 size_t attn_prefill_counters(int max_batch, int H, int HKV);        // `counters` (zero before the first launch)
 int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps, int rows, cudaStream_t s);

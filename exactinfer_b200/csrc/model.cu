@@ -54,6 +54,7 @@ struct Model {
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
     int8_t* limbs = nullptr;
     float *inv_scale = nullptr, *xsum = nullptr;
+    void* kv16 = nullptr;             // keys and values of one layer as fp16 pairs (tensor-core prompt attention)
     float* tc_part = nullptr;         // partial tiles and arrival counters of the fp16 tensor-core GEMM's k splits
     unsigned* tc_counters = nullptr;
     int32_t* tokens_dev = nullptr;
@@ -232,7 +233,12 @@ int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
                                      m->rows_counters, B, H, HKV, m->rows_split, scale, m->stream));
         } else {
             ELB_TRY(qkv_post_launch(m->qkv, QKV, L.q_norm, L.k_norm, m->rope, pos0, B, kc, vc, H, HKV, c.rope_dim, c.eps, m->stream));
-            ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream, m->ap_part, m->ap_counters));
+            if (m->kv16 && attn_prefill_tc_usable(H, HKV, QKV, QD)) {
+                ELB_TRY(attn_prefill_tc_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream, m->ap_part, m->ap_counters, m->kv16));
+                ++m->launches;  // the fp16 split of the layer's keys and values
+            } else {
+                ELB_TRY(attn_prefill_launch(m->qkv, QKV, kc, vc, m->att, QD, pos0, B, H, HKV, scale, m->stream, m->ap_part, m->ap_counters));
+            }
         }
         m->launches += 2;
         ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16 && !gemm_f16_tc_usable(L.wo, B)));
@@ -699,7 +705,7 @@ void model_destroy(Model* m) {
                     (void*)m->tokens_dev, (void*)m->pos_dev, (void*)m->attn_part, (void*)m->attn_counters, (void*)m->dlimbs[0],
                     (void*)m->dlimbs[1], (void*)m->dlimbs[2], (void*)m->dlimbs[3], (void*)m->dinv, (void*)m->done})
         cudaFree(p);
-    cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact); cudaFree(m->tc_part); cudaFree(m->tc_counters);
+    cudaFree(m->xbuf); cudaFree(m->xctl); cudaFree(m->gact); cudaFree(m->tc_part); cudaFree(m->tc_counters); cudaFree(m->kv16);
     if (m->xarea.local) tp_peer_free(&m->xarea, m->tp.rank); cudaFree(m->sync_words); cudaFree(m->pos_steps);
     cudaFree(m->xr); cudaFree(m->logits_local);
     cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev); cudaFree(m->mask_dev);
@@ -902,6 +908,7 @@ static int finalize_local(Model* m) {
     ELB_CUDA(cudaMalloc(&m->ap_part, attn_prefill_scratch_floats(m->max_batch, m->H, m->HKV) * sizeof(float)));
     ELB_CUDA(cudaMalloc(&m->ap_counters, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMemset(m->ap_counters, 0, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
+    ELB_CUDA(cudaMalloc(&m->kv16, attn_prefill_tc_scratch_halves(m->n_ctx, m->HKV * 128) * 2));
     // test hook: a rank that fails on its own once everything local is in place (as it would running out of memory)
     if (const char* v = std::getenv("ELB_TEST_FAIL_FINALIZE_RANK"))
         if (m->tp.size > 1 && std::atoi(v) == m->tp.rank) return fail(ELB_ERR_MEMORY, "finalize: injected failure of this rank (test)");
