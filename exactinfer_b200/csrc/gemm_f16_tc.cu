@@ -29,7 +29,7 @@ namespace elb {
 namespace {
 
 constexpr int FT_ROWS = 128, FT_K = 64, FT_THREADS = 192;
-constexpr int FT_SEG = 4;  // k tiles (of 64) accumulated in tensor memory before the sum moves to registers
+constexpr int FT_SEG = 2;  // k tiles (of 64) accumulated in tensor memory before the sum moves to registers
 constexpr unsigned FT_SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t f_smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
