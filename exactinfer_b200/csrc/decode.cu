@@ -369,9 +369,18 @@ __device__ __noinline__ WarpRange warp_range(const DkKind& m, int warp) {
         r.cB = range_lo(U, gridDim.x, c + 1);
     } else {
         const int G = min(int(gridDim.x), m.group_tiles);
-        const int gA = c < G ? range_lo(m.group_tiles, G, c) : 0, gB = c < G ? range_lo(m.group_tiles, G, c + 1) : 0;
-        r.cA = min(max(gA - m.group_off, 0), m.tiles) * m.upt;
-        r.cB = min(max(gB - m.group_off, 0), m.tiles) * m.upt;
+        if (m.group_cost > 0) {  // CTA c takes the tiles whose cost position lies in [C c / G, C (c + 1) / G)
+            auto bound = [&](int cc) {  // first tile of this matrix at or behind the cost position of boundary cc
+                const long long rel = (long long)m.group_cost * cc / G - m.group_cost_off;
+                return rel <= 0 ? 0 : int(min((rel + m.cost - 1) / m.cost, (long long)m.tiles));
+            };
+            r.cA = (c < G ? bound(c) : m.tiles) * m.upt;
+            r.cB = (c < G ? bound(c + 1) : m.tiles) * m.upt;
+        } else {
+            const int gA = c < G ? range_lo(m.group_tiles, G, c) : 0, gB = c < G ? range_lo(m.group_tiles, G, c + 1) : 0;
+            r.cA = min(max(gA - m.group_off, 0), m.tiles) * m.upt;
+            r.cB = min(max(gB - m.group_off, 0), m.tiles) * m.upt;
+        }
     }
     r.wA = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp);
     r.wB = r.cA + range_lo(r.cB - r.cA, DK_WARPS, warp + 1);

@@ -19,6 +19,10 @@ struct DkKind {  // one kind of weight matrix, in tiled layout
     // balanced: the CTAs cut the (tile, k block) units into equal ranges instead; a tile then has up to two
     // contributors, which leave their partial sums in two buffers for the consumer to add (wo, down).
     int group_tiles, group_off, balanced, pad;
+    // The matrices of a group may differ in block format and so in the time a tile takes (a Q6_K unit costs 1.66 Q4_K
+    // units): the CTAs cut the group by cost, not by tile count. cost: of one tile of this matrix; group_cost_off: cost
+    // of the group's matrices before this one; group_cost: of the whole group (0: cut by tiles).
+    int cost, group_cost_off, group_cost, pad2;
 };
 
 struct DkParams {

@@ -520,6 +520,19 @@ int setup_decode_kernel(Model* m, bool local_ok = true) {
             account(rest[i]);
         }
     }
+    if (nq > 1 && !env_on("ELB_DK_EVEN_TILES")) {  // q|k|v cut by cost: a tile's units times the time a unit of its format takes
+        auto unit_cost = [](int type) { return type == ELB_Q6_K ? 1455 : type == ELB_Q8_0 ? 481 : 875; };  // SM clocks, measured
+        long long off = 0;
+        for (size_t i = 0; i < nq; ++i) {
+            long long sum = 0;
+            for (int l = 0; l < c.n_layer; ++l) sum += unit_cost(p.wtype[l][i]);
+            p.kind[i].cost = int(sum / c.n_layer) * p.kind[i].upt;
+            p.kind[i].group_cost_off = int(off);
+            off += (long long)p.kind[i].cost * p.kind[i].tiles;
+        }
+        if (off < (1ll << 30))
+            for (size_t i = 0; i < nq; ++i) p.kind[i].group_cost = int(off);
+    }
     p.norms = m->norm_arena;
     p.norm_stride = int(2 * E + 2 * c.head_dim);
     p.kc = m->kcache;  // sequence 0
