@@ -399,20 +399,43 @@ __global__ void __launch_bounds__(256) k_split_f16(const float* __restrict__ X, 
     const int tid = threadIdx.x;
     const int64_t b = blockIdx.x;
     const float* x = X + b * ldx;
+    // the row is read once and kept in registers (rows of up to 256 * SF_MAX values; longer rows read it three times)
+    constexpr int SF_MAX = 24;
+    const bool in_regs = n <= 256 * SF_MAX;
+    float v[SF_MAX];
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < SF_MAX; ++j) v[j] = tid + 256 * j < n ? __ldcg(x + tid + 256 * j) : 0.f;
+    }
     float inv = 1.0f;
     if (norm_w) {
         double ss = 0.0;
-        for (int i = tid; i < n; i += 256) { const double v = __ldcg(x + i); ss += v * v; }
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < SF_MAX; ++j) ss += double(v[j]) * double(v[j]);
+        } else {
+            for (int i = tid; i < n; i += 256) { const double t = __ldcg(x + i); ss += t * t; }
+        }
         ss = warp_sum(ss);
         if ((tid & 31) == 0) red8[tid >> 5] = ss;
         __syncthreads();
         ss = 0.0;
         for (int i = 0; i < 8; ++i) ss += red8[i];
         inv = float(1.0 / sqrt(ss / n + double(eps)));
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < SF_MAX; ++j)
+                if (tid + 256 * j < n) v[j] = __fmul_rn(__fmul_rn(v[j], inv), norm_w[tid + 256 * j]);
+        }
     }
     auto val = [&](int i) { return norm_w ? __fmul_rn(__fmul_rn(__ldcg(x + i), inv), norm_w[i]) : __ldcg(x + i); };
     float m = 0.f;
-    for (int i = tid; i < n; i += 256) m = fmaxf(m, fabsf(val(i)));
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < SF_MAX; ++j) m = fmaxf(m, fabsf(v[j]));
+    } else {
+        for (int i = tid; i < n; i += 256) m = fmaxf(m, fabsf(val(i)));
+    }
     m = warp_max(m);
     if ((tid & 31) == 0) redf[tid >> 5] = m;
     __syncthreads();
@@ -422,11 +445,18 @@ __global__ void __launch_bounds__(256) k_split_f16(const float* __restrict__ X, 
     if (m > 0.f) frexpf(m, &e);
     const int k = m > 0.f ? 15 - e : 0;
     const Pow2 sc = make_pow2(k);
-    for (int i = tid; i < n; i += 256) {
-        const float v = val(i) * sc.s1 * sc.s2;
-        const __half h = __float2half_rn(v);
+    auto put = [&](int i, float xv) {
+        const float s = xv * sc.s1 * sc.s2;
+        const __half h = __float2half_rn(s);
         hi[b * n + i] = h;
-        lo[b * n + i] = __float2half_rn(v - __half2float(h));
+        lo[b * n + i] = __float2half_rn(s - __half2float(h));
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < SF_MAX; ++j)
+            if (tid + 256 * j < n) put(tid + 256 * j, v[j]);
+    } else {
+        for (int i = tid; i < n; i += 256) put(i, val(i));
     }
     if (tid == 0) inv_scale[b] = ldexpf(1.0f, -k);
 }
