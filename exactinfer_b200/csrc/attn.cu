@@ -224,15 +224,16 @@ __global__ void __launch_bounds__(AD_THREADS) k_attn_decode(const AttnDecodePara
 
 // ---------------------------------------------------------------- prompt chunk
 
-// grid (B, H + 2 HKV), one warp per (token, head). q heads: norm + rope in place. k heads: norm + rope in place and
+// grid (B, ceil((H + 2 HKV) / 8)), blocks of 8 warps, one warp per (token, head). q heads: norm + rope in place. k heads: norm + rope in place and
 // store to the cache row pos0 + b. v heads: store.
 // posv / seqv (both or neither): row b sits at position posv[b] of sequence seqv[b], whose cache starts seq_stride
 // floats after kc / vc; without them row b sits at position pos0 + b of the cache at kc / vc.
-__global__ void __launch_bounds__(32) k_qkv_post(float* qkv, int64_t ld, const float* q_norm, const float* k_norm,
+__global__ void __launch_bounds__(256) k_qkv_post(float* qkv, int64_t ld, const float* q_norm, const float* k_norm,
                                                  const float2* rope, int pos0, float* kc, float* vc, int H, int HKV,
                                                  int rope_dim, float eps, const int* posv, const int* seqv,
                                                  size_t seq_stride) {
-    const int b = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x, QD = H * D, KD = HKV * D;
+    const int b = blockIdx.x, hd = blockIdx.y * 8 + threadIdx.y, lane = threadIdx.x, QD = H * D, KD = HKV * D;
+    if (hd >= H + 2 * HKV) return;  // (warps only: nothing below synchronises the block)
     const int pos = posv ? posv[b] : pos0 + b;
     if (seqv) { kc += size_t(seqv[b]) * seq_stride; vc += size_t(seqv[b]) * seq_stride; }
     float* row = qkv + int64_t(b) * ld;
@@ -811,7 +812,7 @@ int attn_decode_launch(const AttnDecodeArgs& a, cudaStream_t s) {
 int qkv_post_launch(float* qkv, int64_t ld, const float* q_norm, const float* k_norm, const float* rope, int pos0, int B,
                     float* kc, float* vc, int H, int HKV, int rope_dim, float eps, cudaStream_t s, const int* posv,
                     const int* seqv, size_t seq_stride) {
-    k_qkv_post<<<dim3(B, H + 2 * HKV), 32, 0, s>>>(qkv, ld, q_norm, k_norm, reinterpret_cast<const float2*>(rope), pos0, kc,
+    k_qkv_post<<<dim3(B, (H + 2 * HKV + 7) / 8), dim3(32, 8), 0, s>>>(qkv, ld, q_norm, k_norm, reinterpret_cast<const float2*>(rope), pos0, kc,
                                                    vc, H, HKV, rope_dim, eps, posv, seqv, seq_stride);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
