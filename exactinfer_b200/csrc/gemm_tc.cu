@@ -600,7 +600,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t k, uint64_t d1, uint64
 int* error_word() {  // pinned, mapped: raised by a kernel whose bounded wait ran out
     static int* host = [] {
         int* p = nullptr;
-        if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return static_cast<int*>(nullptr);
+        if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return static_cast<int*>(nullptr);
         *p = 0;
         return p;
     }();

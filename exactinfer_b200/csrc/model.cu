@@ -568,7 +568,7 @@ int setup_decode_kernel(Model* m, bool local_ok = true) {
         ELB_CUDA(cudaMalloc(&m->sync_words, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
         ELB_CUDA(cudaMemset(m->sync_words, 0, size_t(4 + 4 * c.n_layer) * sizeof(unsigned)));
         ELB_CUDA(cudaMalloc(&m->pos_steps, size_t(m->max_batch) * sizeof(int)));
-        ELB_CUDA(cudaHostAlloc(&m->err_host, sizeof(int), cudaHostAllocMapped));
+        ELB_CUDA(cudaHostAlloc(&m->err_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
         *m->err_host = 0;
         ELB_CUDA(cudaHostGetDevicePointer(&err_dev, m->err_host, 0));
         return ELB_OK;

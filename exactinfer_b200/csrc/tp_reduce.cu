@@ -127,7 +127,7 @@ int tp_reduce_create(TpComm* c, int device, int rank, int size, int n_max, cudaS
     // instead of leaving before them
     bool local_ok = cudaSetDevice(device) == cudaSuccess && cudaMalloc(&r->seq, sizeof(unsigned)) == cudaSuccess &&
                     cudaMemset(r->seq, 0, sizeof(unsigned)) == cudaSuccess &&
-                    cudaHostAlloc(&r->err_host, sizeof(int), cudaHostAllocMapped) == cudaSuccess;
+                    cudaHostAlloc(&r->err_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess;
     if (local_ok) {
         *r->err_host = 0;
         local_ok = cudaHostGetDevicePointer(&r->err_dev, r->err_host, 0) == cudaSuccess;
