@@ -616,7 +616,9 @@ static bool tc_prof_on() {
 
 bool gemm_tc_usable(const Weight* w, int B) {
     static const bool off = [] { const char* v = std::getenv("ELB_NO_TC"); return v && v[0] == '1'; }();
-    return !off && w->planes && w->n_planes == 2 && w->n % 256 == 0 && w->n % 16 == 0 && B >= 16 && encode_fn() != nullptr;
+    // (batches below 16 rows run on the 16-token tile: the rows that are not there come in as zeros and are not stored)
+    static const int min_b = [] { const char* v = std::getenv("ELB_TC_MIN_ROWS"); return v ? std::max(1, atoi(v)) : 2; }();
+    return !off && w->planes && w->n_planes == 2 && w->n % 256 == 0 && w->n % 16 == 0 && B >= min_b && encode_fn() != nullptr;
 }
 
 int gemm_tc_check() {  // after a synchronize: did a tensor-core GEMM give up on a wait?

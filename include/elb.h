@@ -118,7 +118,7 @@ int elb_limb_sums(const elb_weight* w, const float* x, int nl, int32_t* P, int32
  * of every (token, 256-block) as they leave tensor memory, A[b][n/256][nl + 1][rows]. With the weight w = sc * q written
  * as balanced digits w = w0 + 256 w1, column c holds sum(w0 * limb_c + w1 * limb_(c-1)), so that
  * sum over c of 256^c A[..][c][row] = sum over l of 256^l I[row][block][l] of elb_limb_sums, exactly.
- * Q4_K and Q6_K weights created with ELB_W_PLANES, b >= 16, nl = 3 or 4 (0 = 4); ELB_ERR_UNSUPPORTED otherwise. */
+ * Q4_K and Q6_K weights created with ELB_W_PLANES, b >= 2, nl = 3 or 4 (0 = 4); ELB_ERR_UNSUPPORTED otherwise. */
 int elb_matmul_acc(const elb_weight* w, const float* x, int64_t b, int nl, int32_t* A);
 
 /* ---- model (el::Backend, src/model.h:42-57) -------------------------------------------------------------------*/
