@@ -340,6 +340,20 @@ void tp_reduce_destroy(TpReduce* r);
 // norm_w != null) as prep_limbs_launch leaves it. Collective: every rank launches it with the same n.
 int tp_reduce_split_launch(TpReduce* r, const float* part, float* x, int n, const float* norm_w, float eps, int nl,
                            int8_t* limbs, float* inv_scale, cudaStream_t s);
+// the same for a small batch of rows (up to n_max floats), without the split: every value crosses NVLink with its tag in
+// one 8-byte word, no flags, no fences (k_tp_rows_allreduce)
+struct TpRows {
+    TpPeerBuf buf;       // per rank: slots [2 sets][size][n_max] of {value, tag}
+    int rank = 0, size = 1;
+    size_t n_max = 0;
+    unsigned count = 0;  // reductions so far (the next one's tag); all ranks call in step
+    int* err_host = nullptr;  // pinned, mapped: raised when a peer's data did not arrive in time
+    int* err_dev = nullptr;
+};
+// collective; *out null: unavailable. caller_ok false: this rank has already failed and only walks through the collectives
+int tp_rows_create(TpComm* c, int device, int rank, int size, size_t n_max, cudaStream_t s, TpRows** out, bool caller_ok = true);
+void tp_rows_destroy(TpRows* r);
+int tp_rows_all_reduce(TpRows* r, const float* in, float* out, size_t n, cudaStream_t s);  // out != in, n even, n <= n_max
 }  // namespace elb
 
 // model.cu

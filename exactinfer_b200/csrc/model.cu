@@ -91,6 +91,7 @@ struct Model {
     TpDims tp{};
     TpComm* comm = nullptr;
     TpReduce* tpr = nullptr;  // single-token all-reduce through peer memory (null: NCCL)
+    TpRows* tprows = nullptr; // all-reduce of a small batch of rows through peer memory (null: NCCL)
     int H = 0, HKV = 0;
     int64_t F = 0;
     // several sequences (n_seq > 1): rows of a batch carry their own sequence and position
@@ -206,6 +207,13 @@ int split_tokens(Model* m, const float* xin, int64_t ldx, int n, int nl, const f
     return split_launch(xin, ldx, B, n, nl, norm_w, m->cfg.eps, m->limbs, m->inv_scale, m->xsum, m->stream, m->use_pdl);
 }
 
+// xr (every rank's partial sums of B rows) -> x on every rank: through peer memory for a small batch, NCCL otherwise
+int rows_all_reduce(Model* m, int B) {
+    const size_t n = size_t(B) * m->cfg.n_embd;
+    if (m->tprows && n <= m->tprows->n_max) return tp_rows_all_reduce(m->tprows, m->xr, m->x, n, m->stream);
+    return tp_all_reduce(m->comm, m->xr, m->x, n, m->stream);
+}
+
 // Rows of one sequence at consecutive positions (seq0, pos0 + b), or (mixed) row b at posv_dev[b] of sequence seq_dev[b].
 int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
     const elb_config& c = m->cfg;
@@ -243,12 +251,12 @@ int body_prefill(Model* m, int B, int pos0, int seq0 = 0, bool mixed = false) {
         m->launches += 2;
         ELB_TRY(split_tokens(m, m->att, QD, QD, m->nl_wo, nullptr, B, L.wo->type != ELB_F16 && !gemm_f16_tc_usable(L.wo, B)));
         ELB_TRY(linear_tokens(m, L.wo, m->att, QD, nullptr, B, yo, E, res, epi_o, m->nl_wo));
-        if (tp) ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(B) * E, m->stream));
+        if (tp) ELB_TRY(rows_all_reduce(m, B));
         ELB_TRY(split_tokens(m, m->x, E, E, m->nl_gu, L.ffn_norm, B, L.gu->type != ELB_F16 && !gemm_f16_tc_usable(L.gu, B)));
         ELB_TRY(linear_tokens(m, L.gu, m->x, E, L.ffn_norm, B, m->act, F, nullptr, EPI_SILU, m->nl_gu));
         ELB_TRY(split_tokens(m, m->act, F, F, m->nl_down, nullptr, B, L.down->type != ELB_F16 && !gemm_f16_tc_usable(L.down, B)));
         ELB_TRY(linear_tokens(m, L.down, m->act, F, nullptr, B, yo, E, res, epi_o, m->nl_down));
-        if (tp) ELB_TRY(tp_all_reduce(m->comm, m->xr, m->x, size_t(B) * E, m->stream));
+        if (tp) ELB_TRY(rows_all_reduce(m, B));
     }
     return ELB_OK;
 }
@@ -422,7 +430,8 @@ int chunk(Model* m, const int32_t* tokens, int B, int pos0, float* logits, const
         std::memcpy(top->vals, r + 8 + 4 * TOP_MAXK, size_t(top->k) * sizeof(float));
     }
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
-    if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
+    if ((m->tpr && *m->tpr->err_host) || (m->tprows && *m->tprows->err_host))
+        return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
     ELB_TRY(gemm_tc_check());
     ELB_TRY(gemm_f16_tc_check());
     float ms = 0.f;
@@ -725,6 +734,7 @@ void model_destroy(Model* m) {
     if (m->top_host) cudaFreeHost(m->top_host);
     cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);
+    tp_rows_destroy(m->tprows);
     tp_comm_destroy(m->comm);
     if (m->err_host) cudaFreeHost(m->err_host);
     if (m->tokens_host) cudaFreeHost(m->tokens_host);
@@ -944,7 +954,13 @@ int model_finalize(Model* m) {
         if (rc != ELB_OK) return rc;
         if (rc_a != ELB_OK) return rc_a;
         if (!all) return fail(ELB_ERR_STATE, other);
-        if (!env_on("ELB_TP_NCCL")) rc = tp_reduce_create(m->comm, m->device, m->tp.rank, m->tp.size, m->cfg.n_embd, m->stream, &m->tpr);
+        if (!env_on("ELB_TP_NCCL")) {
+            rc = tp_reduce_create(m->comm, m->device, m->tp.rank, m->tp.size, m->cfg.n_embd, m->stream, &m->tpr);
+            // (a rank that failed above still walks through this one's collectives, with "failed" as its answer)
+            const int rc2 = tp_rows_create(m->comm, m->device, m->tp.rank, m->tp.size, size_t(16) * m->cfg.n_embd, m->stream, &m->tprows,
+                                           rc == ELB_OK);
+            if (rc == ELB_OK) rc = rc2;
+        }
     } else if (rc != ELB_OK) {
         return rc;
     }
@@ -1118,7 +1134,8 @@ int model_eval_steps(Model* m, const int32_t* tokens, int n, int pos0, float* de
     if (rc != ELB_OK) return rc;
     ELB_CUDA(e);
     if (m->err_host && *m->err_host) return fail(ELB_ERR_CUDA, "decode kernel: a grid barrier wait ran out");
-    if (m->tpr && *m->tpr->err_host) return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
+    if ((m->tpr && *m->tpr->err_host) || (m->tprows && *m->tprows->err_host))
+        return fail(ELB_ERR_CUDA, "tensor parallel: a peer did not arrive at an all-reduce in time");
     ELB_CUDA(cudaEventElapsedTime(device_ms, m->ev0, m->ev1));
     m->last_ms = *device_ms;
     m->last_launches = m->launches - before;
