@@ -45,6 +45,11 @@ constexpr int DK_REGS_LAUNCH = 96, DK_REGS_WORKER = 112, DK_REGS_PRODUCER = 32;
 static_assert(4 * 32 * (DK_REGS_LAUNCH - DK_REGS_PRODUCER) >= DK_THREADS * (DK_REGS_WORKER - DK_REGS_LAUNCH),
               "the working warps would wait for registers that nobody releases");
 constexpr int DK_NBAR = 8;  // mbarriers per warp = most units a warp can have requested and not yet consumed
+// How long the producer warp sleeps when no ring has room (ns). It shares a scheduler with four working warps: polled
+// every 40 ns it took a fifth of the kernel's instructions; 500-1000 ns measured 0.6 % faster per step, 2000 ns 2 % slower.
+#ifndef DK_PRODUCER_NAP
+#define DK_PRODUCER_NAP 500
+#endif
 constexpr int DK_HD = 128, DK_KT = 40, DK_KS = DK_HD + 4, DK_MAXG = 8;  // DK_KS: row stride of the K tile (float4 reads without bank conflicts)
 constexpr int DK_MAXSPLIT = 18;         // key splits of one KV head (their partial results are staged in the K/V tile area)
 constexpr int DK_PS = DK_HD + 4;        // floats per (split, head) of the attention's partial results: 128 outputs, m, l, padding
@@ -500,7 +505,7 @@ __device__ __noinline__ void producer_warp(const DkParams& p, const uint32_t rin
             idle = 0;
         } else {
             if (*reinterpret_cast<const volatile int*>(s_dead) || ++idle > DK_SPIN_LIMIT) break;
-            __nanosleep(40);
+            __nanosleep(DK_PRODUCER_NAP);
         }
     }
     if (mine) rs->issued[lane] = seq;
