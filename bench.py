@@ -242,7 +242,7 @@ def physical_cores() -> int:
     return max(1, len(allowed))
 
 
-def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
+def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int, gpu_context: int = PROMPT):
     """Decode tok/s of the reference CPU backend on the host cores, on a bounded sample: one warm-up token, then
     single-token steps from position 1 until `seconds` have passed (at most max_steps). Uses the reference's own code
     (oracle/_ref/libelref.so over a GGUF written to a temporary file) when that build is present, else the restated
@@ -281,7 +281,7 @@ def cpu_decode_baseline(spec, tens, seconds: float, max_steps: int):
         shutil.rmtree(tmp, ignore_errors=True)
     return {"value": done / dt, "unit": "tok/s", "cores": int(cores), "physical_cores": int(want), "kind": kind,
             "sample": f"{done} single-token decode steps at positions 1..{done} of the same model (1 warm-up token; "
-                      f"context shorter than the GPU run's {PROMPT}+), {dt:.1f} s"}, done, dt
+                      f"context shorter than the GPU run's {gpu_context}+), {dt:.1f} s"}, done, dt
 
 
 def cpu_full_bench(spec, tens, pp=PROMPT, tg=128):
@@ -764,7 +764,8 @@ def run_batched(args):
            "setup_s": {"generate": gen_s, "upload": load_s}}
     model.close()
     if not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64)[0]
+        out["cpu_baseline"] = cpu_decode_baseline(spec, tens, args.cpu_seconds, 64, P)[0]
+        out["cpu_baseline"]["sample"] += " (one sequence: the reference has no batched path)"
     emit(json.dumps(out))
 
 
