@@ -13,7 +13,7 @@
 // arrives last adds the partial tiles in split order, so the result does not depend on which CTA that was.
 //
 // Warp roles (192 threads): warps 0-3 epilogue (warp w drains TMEM lanes 32w.. = weight rows), warp 4 TMA producer,
-// warp 5 MMA issuer and TMEM owner. Operands arrive by TMA (no multicast) into a ring of 128-byte-swizzled K-major
+// warp 5 MMA issuer and TMEM owner. Operands arrive by TMA into a ring of 128-byte-swizzled K-major
 // tiles (64 k per stage); two accumulators, so that the drain of one tile overlaps the MMAs of the next. A persistent
 // grid walks the output tiles. Every mbarrier wait is bounded: on timeout the kernel raises an error word and winds down.
 #include <cuda.h>

@@ -10,8 +10,8 @@
 // combination sum_j 256^j R_j is one Horner chain per (row, token) per 256-block in the epilogue, where the fp16
 // block scale d (and Q4_K's dmin*m term) is applied in fp32.
 //
-// Warp roles (320 threads): warps 0-7 epilogue (warp w drains TMEM lanes 32(w%4).. = weight rows, for half w/4 of the
-// tile's tokens), warp 8 TMA producer, warp 9 MMA issuer and TMEM owner. Operands arrive by TMA (no multicast) into a 3-stage ring of
+// Warp roles (576 threads): warps 0-15 epilogue (warp w drains TMEM lanes 32(w%4).. = weight rows, for quarter w/4 of
+// the tile's tokens), warp 16 TMA producer, warp 17 MMA issuer and TMEM owner. Operands arrive by TMA into a 3-stage ring of
 // 128-byte-swizzled K-major tiles; TMEM accumulators are double buffered so that the drain of one 256-block overlaps
 // the MMAs of the next. Every mbarrier wait is bounded: on timeout the kernel raises an error word and winds down.
 #include <cuda.h>
