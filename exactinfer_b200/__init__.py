@@ -286,6 +286,21 @@ class Backend:
                                          out.ctypes.data_as(C.c_void_p) if want_logits else None))
         return out
 
+    def eval_batch_top(self, tokens, seq, pos, k: int = 1, want=None):
+        """eval_batch with every wanted row reduced on the device: (ids[R][k], logits[R][k], lse[R])."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        seq = np.ascontiguousarray(seq, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        n = tokens.size
+        w = None if want is None else np.ascontiguousarray(want, dtype=np.uint8)
+        R = n if w is None else int(np.count_nonzero(w))
+        ids, vals, lse = np.empty((R, k), np.int32), np.empty((R, k), np.float32), np.empty(R, np.float64)
+        i32 = C.POINTER(C.c_int32)
+        check(lib().elb_model_eval_batch_top(self._h, n, tokens.ctypes.data_as(i32), seq.ctypes.data_as(i32), pos.ctypes.data_as(i32),
+                                             w.ctypes.data_as(C.c_void_p) if w is not None else None, k, ids.ctypes.data_as(i32),
+                                             capi.fptr(vals), lse.ctypes.data_as(C.POINTER(C.c_double))))
+        return ids, vals, lse
+
     def eval_steps(self, tokens, pos0: int) -> float:
         """Single-token steps back to back, logits left on the device; returns the device time in ms."""
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -63,6 +63,7 @@ SIGNATURES = {
     "elb_model_eval_top": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, C.c_int, _i32p, _f32p, C.POINTER(C.c_double)]),
     "elb_model_eval_top_masked": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, C.c_int, _vp, _i32p, _f32p, C.POINTER(C.c_double)]),
     "elb_model_eval_batch": (C.c_int, [_vp, C.c_int, _i32p, _i32p, _i32p, _vp, _vp]),
+    "elb_model_eval_batch_top": (C.c_int, [_vp, C.c_int, _i32p, _i32p, _i32p, _vp, C.c_int, _i32p, _f32p, C.POINTER(C.c_double)]),
     "elb_model_eval_steps": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, _f32p]),
     "elb_model_last_eval_stats": (C.c_int, [_vp, _f32p, C.POINTER(C.c_int64)]),
     "elb_model_hidden": (C.c_int, [_vp, _f32p]),

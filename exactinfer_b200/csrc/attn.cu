@@ -724,8 +724,11 @@ __global__ void __launch_bounds__(256) k_rmsnorm_rows(float* out, const float* x
 // What the reference's generate loop does on the host with the n_vocab logits of every token (src/main.cpp:309-320):
 // log-sum-exp in double precision and the k best tokens ordered by (logit descending, id ascending). One block.
 // allowed != nullptr: bit i of the array says whether token i may be picked (the log-sum-exp still covers all tokens).
+// Block b reduces row b: logits + b * ld -> out + b * TOP_BYTES (one row: one block).
 __global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ logits, int n, int k, uint8_t* __restrict__ out,
-                                                     const uint32_t* __restrict__ allowed) {
+                                                     const uint32_t* __restrict__ allowed, int64_t ld) {
+    logits += int64_t(blockIdx.x) * ld;
+    out += size_t(blockIdx.x) * TOP_BYTES;
     __shared__ double red_d[32];
     __shared__ float red_f[32];
     __shared__ int red_i[32];
@@ -784,7 +787,15 @@ __global__ void __launch_bounds__(1024) k_logits_top(const float* __restrict__ l
 
 int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s, const uint32_t* d_allowed) {
     if (!logits || !out || n < 1 || k < 1 || k > TOP_MAXK || k > n) return fail(ELB_ERR_INVALID, "logits_top: bad argument");
-    k_logits_top<<<1, 1024, 0, s>>>(logits, n, k, out, d_allowed);
+    k_logits_top<<<1, 1024, 0, s>>>(logits, n, k, out, d_allowed, 0);
+    ELB_CUDA(cudaGetLastError());
+    return ELB_OK;
+}
+
+// rows of logits [rows][ld] -> out [rows][TOP_BYTES], one block per row
+int logits_top_rows_launch(const float* logits, int n, int64_t ld, int rows, int k, uint8_t* out, cudaStream_t s) {
+    if (!logits || !out || n < 1 || rows < 1 || k < 1 || k > TOP_MAXK || k > n) return fail(ELB_ERR_INVALID, "logits_top: bad argument");
+    k_logits_top<<<rows, 1024, 0, s>>>(logits, n, k, out, nullptr, ld);
     ELB_CUDA(cudaGetLastError());
     return ELB_OK;
 }

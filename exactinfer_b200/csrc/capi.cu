@@ -397,6 +397,10 @@ int elb_model_eval_batch(elb_model* m, int n, const int32_t* tokens, const int32
                          const uint8_t* want, float* logits) {
     return model_eval_batch(M(m), n, tokens, seq, pos, want, logits);
 }
+int elb_model_eval_batch_top(elb_model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos,
+                             const uint8_t* want, int k, int32_t* ids, float* top_logits, double* lse) {
+    return model_eval_batch_top(M(m), n, tokens, seq, pos, want, k, ids, top_logits, lse);
+}
 int elb_model_eval_steps(elb_model* m, const int32_t* tokens, int n, int pos0, float* device_ms) {
     return model_eval_steps(M(m), tokens, n, pos0, device_ms);
 }

@@ -290,6 +290,7 @@ int rmsnorm_launch(float* out, const float* x, const float* w, int n, float eps,
 constexpr int TOP_MAXK = 64;
 constexpr size_t TOP_BYTES = 8 + size_t(TOP_MAXK) * 8;
 int logits_top_launch(const float* logits, int n, int k, uint8_t* out, cudaStream_t s, const uint32_t* d_allowed = nullptr);
+int logits_top_rows_launch(const float* logits, int n, int64_t ld, int rows, int k, uint8_t* out, cudaStream_t s);
 
 
 }  // namespace elb
@@ -373,6 +374,8 @@ int model_eval_top(Model* m, const int32_t* tokens, int n, int pos0, int k, int3
                    const uint32_t* allowed = nullptr);
 int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
                      float* logits);
+int model_eval_batch_top(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want, int k,
+                         int32_t* ids, float* vals, double* lse);
 int model_stats(const Model* m, float* ms, int64_t* launches);
 int model_hidden(Model* m, float* out);
 size_t model_weight_bytes(const Model* m);

@@ -102,6 +102,7 @@ struct Model {
     int rows_split = 1;
     uint8_t* top_dev = nullptr;      // device-side logits post-processing: lse, ids, logits
     uint8_t* top_host = nullptr;     // pinned
+    uint8_t *top_rows_dev = nullptr, *top_rows_host = nullptr;  // the same for every wanted row of a batch: [n_seq][TOP_BYTES]
     uint32_t* mask_dev = nullptr;    // allowed-token bits of a constrained pick
     float* ap_part = nullptr;        // partial results of the chunked prompt attention
     unsigned* ap_counters = nullptr;
@@ -732,6 +733,8 @@ void model_destroy(Model* m) {
     cudaFree(m->xr); cudaFree(m->logits_local);
     cudaFree(m->ap_part); cudaFree(m->ap_counters); cudaFree(m->top_dev); cudaFree(m->mask_dev);
     if (m->top_host) cudaFreeHost(m->top_host);
+    cudaFree(m->top_rows_dev);
+    if (m->top_rows_host) cudaFreeHost(m->top_rows_host);
     cudaFree(m->seq_dev); cudaFree(m->posv_dev); cudaFree(m->logits_rows); cudaFree(m->rows_part); cudaFree(m->rows_counters);
     tp_reduce_destroy(m->tpr);
     tp_rows_destroy(m->tprows);
@@ -927,6 +930,8 @@ static int finalize_local(Model* m) {
     ELB_CUDA(cudaMemset(m->attn_counters, 0, size_t(m->HKV) * sizeof(unsigned)));
     ELB_CUDA(cudaMalloc(&m->top_dev, TOP_BYTES));
     ELB_CUDA(cudaMallocHost(&m->top_host, TOP_BYTES));
+    ELB_CUDA(cudaMalloc(&m->top_rows_dev, size_t(m->n_seq) * TOP_BYTES));
+    ELB_CUDA(cudaMallocHost(&m->top_rows_host, size_t(m->n_seq) * TOP_BYTES));
     ELB_CUDA(cudaMalloc(&m->mask_dev, size_t((V + 31) / 32) * 4));
     ELB_CUDA(cudaMalloc(&m->ap_part, attn_prefill_scratch_floats(m->max_batch, m->H, m->HKV) * sizeof(float)));
     ELB_CUDA(cudaMalloc(&m->ap_counters, attn_prefill_counters(m->max_batch, m->H, m->HKV) * sizeof(unsigned)));
@@ -1019,8 +1024,26 @@ int model_eval_impl(Model* m, const int32_t* tokens, int n, int pos0, float* log
 // Rows of several sequences in one pass: the prompt-chunk path with per-row sequence and position (body_prefill, mixed)
 // or, when all rows belong to one sequence at consecutive positions, exactly the prompt-chunk path on that sequence's
 // cache. The head runs over the wanted rows only.
+namespace { struct TopRows { int k; int32_t* ids; float* vals; double* lse; }; }
+static int eval_batch_impl(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
+                           float* logits, const TopRows* top);
+
 int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
                      float* logits) {
+    return eval_batch_impl(m, n, tokens, seq, pos, want, logits, nullptr);
+}
+
+// the wanted rows' logits reduced on the device: ids[r][k], vals[r][k], lse[r] for wanted row r (in row order)
+int model_eval_batch_top(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want, int k,
+                         int32_t* ids, float* vals, double* lse) {
+    if (!ids || !vals || !lse) return fail(ELB_ERR_INVALID, "eval_batch_top: null argument");
+    if (k < 1 || k > TOP_MAXK || (m && k > m->cfg.n_vocab)) return fail(ELB_ERR_INVALID, "eval_batch_top: k must be between 1 and 64 (and at most n_vocab)");
+    const TopRows top{k, ids, vals, lse};
+    return eval_batch_impl(m, n, tokens, seq, pos, want, nullptr, &top);
+}
+
+static int eval_batch_impl(Model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos, const uint8_t* want,
+                           float* logits, const TopRows* top) {
     if (!m || !tokens || !seq || !pos) return fail(ELB_ERR_INVALID, "eval_batch: null argument");
     if (!m->finalized) return fail(ELB_ERR_STATE, "eval_batch: model not finalized");
     if (n <= 0) return fail(ELB_ERR_INVALID, "eval_batch: empty batch");
@@ -1032,7 +1055,7 @@ int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq,
         if (seq[i] < 0 || seq[i] >= m->n_seq) return fail(ELB_ERR_RANGE, "eval_batch: sequence index out of range");
         if (pos[i] < 0 || pos[i] >= m->n_ctx) return fail(ELB_ERR_RANGE, "eval_batch: context window full");
         uniform = uniform && seq[i] == seq[0] && pos[i] == pos[0] + i;
-        if (logits && (!want || want[i])) rows.push_back(i);
+        if ((logits || top) && (!want || want[i])) rows.push_back(i);
     }
     for (int i = 0; i < n; ++i)  // rows of one sequence: increasing, consecutive positions
         for (int j = i + 1; j < n; ++j)
@@ -1083,11 +1106,23 @@ int model_eval_batch(Model* m, int n, const int32_t* tokens, const int32_t* seq,
         }
         out_dev = m->logits_rows;
     }
+    if (out_dev && top) {  // k best tokens and the log-sum-exp of every wanted row, on the device
+        ELB_TRY(logits_top_rows_launch(out_dev, int(V), V, int(rows.size()), top->k, m->top_rows_dev, m->stream));
+        ++m->launches;
+    }
     ELB_CUDA(cudaEventRecord(m->ev1, m->stream));
-    if (out_dev) ELB_CUDA(cudaMemcpyAsync(logits, out_dev, rows.size() * size_t(V) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+    if (out_dev && top) ELB_CUDA(cudaMemcpyAsync(m->top_rows_host, m->top_rows_dev, rows.size() * TOP_BYTES, cudaMemcpyDeviceToHost, m->stream));
+    else if (out_dev) ELB_CUDA(cudaMemcpyAsync(logits, out_dev, rows.size() * size_t(V) * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
     ELB_CUDA(cudaStreamSynchronize(m->stream));
     ELB_TRY(gemm_tc_check());
     ELB_TRY(gemm_f16_tc_check());
+    if (out_dev && top)
+        for (size_t r = 0; r < rows.size(); ++r) {  // layout per row: lse (double), then k ids, then k logits
+            const uint8_t* src = m->top_rows_host + r * TOP_BYTES;
+            std::memcpy(top->lse + r, src, sizeof(double));
+            std::memcpy(top->ids + r * top->k, src + 8, size_t(top->k) * sizeof(int32_t));
+            std::memcpy(top->vals + r * top->k, src + 8 + 4 * TOP_MAXK, size_t(top->k) * sizeof(float));
+        }
     ELB_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
     m->last_launches = m->launches - before;
     return ELB_OK;

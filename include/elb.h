@@ -191,6 +191,13 @@ int elb_model_eval_top_masked(elb_model* m, const int32_t* tokens, int n, int po
  * sequence. elb_model_eval(tokens, n, pos0) is the same as rows (seq 0, pos0 + i) with only the last row wanted. */
 int elb_model_eval_batch(elb_model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos,
                          const uint8_t* want, float* logits);
+/* elb_model_eval_batch with every wanted row's logits reduced on the device as elb_model_eval_top reduces one row's
+ * (the sampler of src/main.cpp:309-320 once per sequence): for wanted row r, in row order, ids[r * k .. r * k + k) and
+ * top_logits[...] hold its k best tokens by (logit descending, id ascending) and lse[r] its log-sum-exp over the whole
+ * vocabulary in double precision. A batched decode step of 64 sequences then returns 64 * (8 + 8 k) bytes to the host
+ * instead of 64 * n_vocab floats (39 MB). 1 <= k <= 64. */
+int elb_model_eval_batch_top(elb_model* m, int n, const int32_t* tokens, const int32_t* seq, const int32_t* pos,
+                             const uint8_t* want, int k, int32_t* ids, float* top_logits, double* lse);
 
 /* n single-token steps at positions pos0.., enqueued back to back without reading logits back (the tg loop of the
  * reference's bench command, src/main.cpp:639, without its per-token host round trip). device_ms receives the device

@@ -86,3 +86,36 @@ def test_argument_errors(elb):
     with pytest.raises(IndexError):
         gpu.eval_batch(list(range(9)), [0] * 9, list(range(9)))  # more rows than max_batch
     gpu.close()
+
+
+def test_batch_top_equals_host_reduction_of_the_same_logits(elb):
+    """elb_model_eval_batch_top: the k best tokens (logit descending, id ascending) and the double-precision log-sum-exp
+    of every wanted row, computed on the device, against the host's reduction of the logits elb_model_eval_batch returns
+    for the same rows (two models with the same weights and the same history, so both see the same step)."""
+    spec = synth.Spec(name="batch-top", n_layer=2, n_embd=512, n_ff=1024, n_head=8, n_head_kv=2, n_vocab=1200, layout="q4_k_m",
+                      head_sigma=2e-5)
+    tens = list(synth.generate(spec, 19))
+    n_seq, n_ctx, k = 4, 32, 5
+    a = elb.Backend(spec, tens, n_ctx, max_batch=16, n_seq=n_seq)
+    b = elb.Backend(spec, tens, n_ctx, max_batch=16, n_seq=n_seq)
+    rng = np.random.default_rng(8)
+    for s in range(n_seq):  # prompts of different lengths, one sequence each
+        p = rng.integers(0, spec.n_vocab, size=4 + 2 * s).astype(np.int32)
+        for m in (a, b):
+            m.eval_batch(p, np.full(p.size, s, np.int32), np.arange(p.size, dtype=np.int32), want_logits=False)
+    toks = rng.integers(0, spec.n_vocab, size=n_seq).astype(np.int32)
+    seq = np.arange(n_seq, dtype=np.int32)
+    pos = np.array([4 + 2 * s for s in range(n_seq)], np.int32)
+    want = np.array([1, 0, 1, 1], np.uint8)
+    logits = a.eval_batch(toks, seq, pos, want=want)  # [3][V]
+    ids, vals, lse = b.eval_batch_top(toks, seq, pos, k=k, want=want)
+    assert ids.shape == (3, k) and vals.shape == (3, k) and lse.shape == (3,)
+    for r in range(3):
+        order = np.lexsort((np.arange(spec.n_vocab), -logits[r].astype(np.float64)))[:k]
+        assert np.array_equal(ids[r], order), r
+        assert np.array_equal(vals[r].view(np.uint32), logits[r][order].view(np.uint32)), r
+        assert abs(lse[r] - ol.logsumexp(logits[r])) <= 1e-9 * max(1.0, abs(lse[r])), r
+    with pytest.raises(ValueError):
+        b.eval_batch_top(toks, seq, pos + 1, k=0)
+    a.close()
+    b.close()
